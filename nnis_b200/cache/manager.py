@@ -1,0 +1,206 @@
+"""The cache: per-sequence slots over paged key/value storage, and state.
+
+Each schedule entry of a model may ask for one of two things:
+
+* ``KVRequest`` - keys and values of every position (``window == 0``) or of the
+  last ``window`` positions.  Entries with the same (kv_heads, head_dim, window)
+  form a *group* with storage and a page pool of its own:
+  ``k, v: [entries, pages, kv_heads, page_size, head_dim]``.  A page id is
+  valid for every entry of its group, so one page table per group and sequence
+  serves all its layers.  A windowed group gives pages back as soon as they fall
+  wholly out of the window.
+* ``StateRequest`` - a fixed-size tensor per sequence, ``[slots, *shape]``,
+  zeroed when a slot is taken.  The Llama decoder asks for none; the area
+  exists so that a recurrent mixer needs no change here.
+
+Lengths are per slot (all layers advance together inside a step).  Positions at
+or beyond a slot's length are never read, so a reused slot cannot see what its
+last owner left (NNIS relies on the same rule:
+crates/nnis-rt/src/kv_cache.rs:368-395).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple, Union
+
+import torch
+
+from .slots import CacheFull, FreeList, SlotError
+
+PAGE_SIZE = 64
+
+
+@dataclass(frozen=True)
+class KVRequest:
+    kv_heads: int
+    head_dim: int
+    window: int = 0
+
+
+@dataclass(frozen=True)
+class StateRequest:
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class KVView:
+    """What an attention-like part gets: its own layer of a group's storage."""
+    group: int
+    k: torch.Tensor  # [pages, kv_heads, page_size, head_dim]
+    v: torch.Tensor
+    page_size: int
+    window: int
+
+
+@dataclass
+class StateView:
+    state: torch.Tensor  # [slots, *shape]
+
+
+class _KVGroup:
+    def __init__(self, key: Tuple[int, int, int], entries: List[int], pages: int,
+                 dtype: torch.dtype, device: torch.device):
+        self.kv_heads, self.head_dim, self.window = key
+        self.entries = entries
+        self.pool = FreeList(pages, "page")
+        shape = (len(entries), pages, self.kv_heads, PAGE_SIZE, self.head_dim)
+        self.k = torch.zeros(shape, dtype=dtype, device=device)
+        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        # per slot: logical page index -> page id, -1 where given back
+        self.tables: Dict[int, List[int]] = {}
+
+    def first_needed_page(self, length: int) -> int:
+        """Pages before this one hold no key that a later position may read."""
+        if self.window <= 0:
+            return 0
+        return max(0, length - self.window + 1) // PAGE_SIZE if length > 0 else 0
+
+
+class CacheManager:
+    def __init__(self, requests: Sequence[Optional[Union[KVRequest, StateRequest]]],
+                 dtype: torch.dtype, device: torch.device, max_tokens: int, max_slots: int,
+                 max_positions: int):
+        if max_tokens <= 0 or max_slots <= 0:
+            raise ValueError("max_tokens and max_slots must be positive")
+        self.dtype, self.device = dtype, torch.device(device)
+        self.max_positions = max_positions
+        self.pages_total = -(-max_tokens // PAGE_SIZE)
+        self.slots = FreeList(max_slots, "slot")
+        self.lengths: List[int] = [0] * max_slots
+        self.groups: List[_KVGroup] = []
+        self._views: List[Optional[Union[KVView, StateView]]] = []
+        by_key: Dict[Tuple[int, int, int], List[int]] = {}
+        for i, r in enumerate(requests):
+            if isinstance(r, KVRequest):
+                by_key.setdefault((r.kv_heads, r.head_dim, r.window), []).append(i)
+        group_of: Dict[int, Tuple[int, int]] = {}
+        for key, entries in by_key.items():
+            g = _KVGroup(key, entries, self.pages_total, dtype, self.device)
+            for j, e in enumerate(entries):
+                group_of[e] = (len(self.groups), j)
+            self.groups.append(g)
+        self._states: List[torch.Tensor] = []
+        for i, r in enumerate(requests):
+            if isinstance(r, KVRequest):
+                gi, j = group_of[i]
+                g = self.groups[gi]
+                self._views.append(KVView(gi, g.k[j], g.v[j], PAGE_SIZE, g.window))
+            elif isinstance(r, StateRequest):
+                t = torch.zeros((max_slots, *r.shape), dtype=r.dtype, device=self.device)
+                self._states.append(t)
+                self._views.append(StateView(t))
+            elif r is None:
+                self._views.append(None)
+            else:
+                raise TypeError(f"schedule entry {i}: unknown cache request {r!r}")
+
+    # -- what parts see ---------------------------------------------------
+    def view(self, entry: int):
+        return self._views[entry]
+
+    # -- slots --------------------------------------------------------------
+    def acquire(self) -> int:
+        slot = self.slots.take()
+        self.lengths[slot] = 0
+        for g in self.groups:
+            g.tables[slot] = []
+        for t in self._states:
+            t[slot].zero_()
+        return slot
+
+    def release(self, slot: int) -> None:
+        if not self.slots.is_held(slot):
+            raise SlotError(f"slot {slot} is not held (freed twice?)")
+        for g in self.groups:
+            for page in g.tables.pop(slot):
+                if page >= 0:
+                    g.pool.give(page)
+        self.lengths[slot] = 0
+        self.slots.give(slot)
+
+    def length(self, slot: int) -> int:
+        if not self.slots.is_held(slot):
+            raise SlotError(f"slot {slot} is not held")
+        return self.lengths[slot]
+
+    # -- growth -------------------------------------------------------------
+    def reserve(self, slots: Sequence[int], new_lengths: Sequence[int]) -> None:
+        """Make room for positions below ``new_lengths``; all or nothing."""
+        if len(set(slots)) != len(slots):
+            raise SlotError(f"a slot appears twice in one step: {list(slots)}")
+        need = [0] * len(self.groups)
+        for slot, n in zip(slots, new_lengths):
+            if not self.slots.is_held(slot):
+                raise SlotError(f"slot {slot} is not held")
+            if n < self.lengths[slot]:
+                raise SlotError(f"slot {slot}: length cannot shrink ({self.lengths[slot]} -> {n})")
+            if n > self.max_positions:
+                raise CacheFull(f"slot {slot}: {n} positions exceed the model's "
+                                f"{self.max_positions}")
+            for gi, g in enumerate(self.groups):
+                need[gi] += max(0, -(-n // PAGE_SIZE) - len(g.tables[slot]))
+        for gi, g in enumerate(self.groups):
+            if need[gi] > g.pool.free:
+                raise CacheFull(f"{need[gi]} pages wanted, {g.pool.free} of {g.pool.count} free "
+                                f"(group {gi}); raise max_tokens")
+        for slot, n in zip(slots, new_lengths):
+            for g in self.groups:
+                table = g.tables[slot]
+                table.extend(g.pool.take_many(-(-n // PAGE_SIZE) - len(table)))
+
+    def commit(self, slots: Sequence[int], new_lengths: Sequence[int]) -> None:
+        """The step has been issued: lengths advance, windowed groups give back
+        the pages that no later position can read."""
+        for slot, n in zip(slots, new_lengths):
+            self.lengths[slot] = n
+            for g in self.groups:
+                if g.window > 0:
+                    table = g.tables[slot]
+                    for i in range(min(g.first_needed_page(n), len(table))):
+                        if table[i] >= 0:
+                            g.pool.give(table[i])
+                            table[i] = -1
+
+    def page_table(self, group: int, slot: int) -> List[int]:
+        return self.groups[group].tables[slot]
+
+    # -- telemetry (crates/nnis-rt/src/kv_telemetry.rs:42-80) ----------------
+    def usage(self) -> Dict[str, object]:
+        return {
+            "slots_held": self.slots.held, "slots_total": self.slots.count,
+            "pages_held": [g.pool.held for g in self.groups], "pages_total": self.pages_total,
+            "live_tokens": sum(self.lengths[s] for s in range(self.slots.count)
+                               if self.slots.is_held(s)),
+            "kv_bytes": sum(g.k.numel() * g.k.element_size() * 2 for g in self.groups),
+        }
+
+    def check(self) -> None:
+        self.slots.check()
+        for g in self.groups:
+            g.pool.check()
+            held = [p for t in g.tables.values() for p in t if p >= 0]
+            if len(set(held)) != len(held):
+                raise SlotError("a page is in two page tables")
+            if len(held) != g.pool.held:
+                raise SlotError(f"{g.pool.held} pages held, {len(held)} in page tables")

@@ -1,0 +1,204 @@
+"""Python face of the CUDA entry points.
+
+Each function checks dtypes, shapes, contiguity and device before it hands raw
+pointers to the library, and turns a non-zero return code into an exception: a
+size that a kernel does not take is refused with a message, never run.  Nothing
+here computes; without the compiled library nothing works, on purpose.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import build as _build
+
+F32, BF16 = 0, 1
+_DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16}
+_ARG_ERRORS = {-1: "bad argument", -2: "unsupported size or dtype", -3: "misaligned pointer",
+               -4: "a kernel reported an error status"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _lib() -> ctypes.CDLL:
+    return _build.load()
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code < 0:
+        raise KernelError(f"{what}: {_ARG_ERRORS.get(code, 'error')} (code {code})")
+    raise KernelError(f"{what}: CUDA error {code} at launch")
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+def _cuda(*tensors: Optional[torch.Tensor]) -> None:
+    for t in tensors:
+        if t is not None:
+            _need(t.is_cuda, "kernels take CUDA tensors only (there is no CPU path)")
+            _need(t.is_contiguous(), "kernels take contiguous tensors")
+
+
+def code_of(dtype: torch.dtype) -> int:
+    _need(dtype in _DTYPE_CODE, f"dtype {dtype} is not supported (float32 or bfloat16)")
+    return _DTYPE_CODE[dtype]
+
+
+# ---------------------------------------------------------------------------
+def embed(table: torch.Tensor, tokens: torch.Tensor, hidden: torch.Tensor,
+          status: torch.Tensor) -> None:
+    """hidden[n] = table[tokens[n]] widened to float32; an id outside the table
+    sets ``status[0]`` and yields a zero row."""
+    _cuda(table, tokens, hidden, status)
+    n, width = hidden.shape
+    _need(tokens.dtype == torch.int32 and tokens.numel() >= n, "tokens: int32 [n]")
+    _need(hidden.dtype == torch.float32 and table.shape[1] == width, "hidden: float32 [n, width]")
+    _need(status.dtype == torch.int32, "status: int32")
+    _check(_lib().nnis_embed(_ptr(table), code_of(table.dtype), _ptr(tokens), _ptr(hidden), n, width,
+                             table.shape[0], _ptr(status), _stream()), "embed")
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+            rows: Optional[torch.Tensor] = None) -> None:
+    """out[r] = rmsnorm(x[rows[r]] or x[r]) * weight, statistics in float32."""
+    _cuda(x, weight, out, rows)
+    n, width = out.shape
+    _need(x.dtype == torch.float32 and x.shape[1] == width, "x: float32 [*, width]")
+    _need(weight.dtype == torch.float32 and weight.numel() == width, "weight: float32 [width]")
+    if rows is not None:
+        _need(rows.dtype == torch.int32 and rows.numel() >= n, "rows: int32 [n]")
+    else:
+        _need(x.shape[0] >= n, "x has fewer rows than out")
+    _check(_lib().nnis_rmsnorm(_ptr(x), _ptr(rows), _ptr(weight), _ptr(out), code_of(out.dtype), n,
+                               width, ctypes.c_float(eps), _stream()), "rmsnorm")
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out = silu(gate_up[:, :I]) * gate_up[:, I:], gate_up float32 [n, 2I]."""
+    _cuda(gate_up, out)
+    n, inter = out.shape
+    _need(gate_up.dtype == torch.float32 and tuple(gate_up.shape) == (n, 2 * inter),
+          "gate_up: float32 [n, 2 * inter]")
+    _check(_lib().nnis_silu_mul(_ptr(gate_up), _ptr(out), code_of(out.dtype),
+                                ctypes.c_longlong(n), inter, _stream()), "silu_mul")
+
+
+def rope_store(qkv: torch.Tensor, token_pos: torch.Tensor, token_seq: torch.Tensor,
+               page_table: Optional[torch.Tensor], cos: Optional[torch.Tensor],
+               sin: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
+               v_cache: Optional[torch.Tensor], heads: int, kv_heads: int, head_dim: int,
+               page_size: int) -> None:
+    """Rotate q and k heads of packed rows in place, store k and v in the cache.
+    ``kv_heads == 0``: the rows hold q only and nothing is stored."""
+    _cuda(qkv, token_pos, token_seq, page_table, cos, sin, k_cache, v_cache)
+    n = qkv.shape[0]
+    _need(qkv.shape[1] == (heads + 2 * kv_heads) * head_dim, "qkv: [n, (heads + 2 kv_heads) * d]")
+    _need(token_pos.dtype == torch.int32 and token_seq.dtype == torch.int32, "positions: int32")
+    cols = 0
+    if kv_heads > 0:
+        _need(page_table is not None and page_table.dtype == torch.int32, "page_table: int32")
+        _need(k_cache is not None and k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype,
+              "cache dtype differs from qkv")
+        _need(tuple(k_cache.shape[1:]) == (kv_heads, page_size, head_dim), "cache: [pages, kv, page, d]")
+        cols = page_table.shape[1]
+    rotate = 0
+    if cos is not None:
+        _need(cos.dtype == torch.float32 and cos.shape[1] == head_dim // 2, "cos/sin: float32 [C, d/2]")
+        rotate = 1
+    _check(_lib().nnis_rope_store(_ptr(qkv), code_of(qkv.dtype), _ptr(token_pos), _ptr(token_seq),
+                                  _ptr(page_table), cols, _ptr(cos), _ptr(sin), _ptr(k_cache),
+                                  _ptr(v_cache), n, heads, kv_heads, head_dim, page_size, rotate,
+                                  _stream()), "rope_store")
+
+
+STORE, STORE_F32, ADD_F32 = 0, 1, 2
+
+
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+              mode: int) -> None:
+    """out (op)= a . w^T + bias on the CUDA cores; float32 accumulation."""
+    _cuda(a, w, bias, out)
+    m, k = a.shape
+    n = w.shape[0]
+    _need(w.shape[1] == k and a.dtype == w.dtype, "gemm: a [m, k], w [n, k] of one dtype")
+    _need(tuple(out.shape) == (m, n), "gemm: out [m, n]")
+    _need(out.dtype == (a.dtype if mode == STORE else torch.float32), "gemm: out dtype vs mode")
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() == n, "gemm: bias float32 [n]")
+    _check(_lib().nnis_gemm_simt(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), m, n, k, code_of(a.dtype),
+                                 mode, _stream()), "gemm_simt")
+
+
+def attention_generic(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                      token_pos: torch.Tensor, token_seq: torch.Tensor, page_table: torch.Tensor,
+                      out: torch.Tensor, heads: int, kv_heads: int, head_dim: int, window: int,
+                      scale: float, n_splits: int = 1,
+                      partial: Optional[torch.Tensor] = None) -> None:
+    """Causal attention of packed query tokens over the paged cache."""
+    _cuda(k_cache, v_cache, token_pos, token_seq, page_table, out, partial)
+    _need(q.is_cuda, "q: CUDA tensor")
+    n = out.shape[0]
+    pages, nkv, page_size, d = k_cache.shape
+    _need(nkv == kv_heads and d == head_dim, "cache shape differs from the heads given")
+    _need(head_dim % 16 == 0 and 16 <= head_dim <= 256,
+          f"attention: head_dim {head_dim} is not a multiple of 16 in 16..256")
+    _need(heads % kv_heads == 0, "attention: heads is not a multiple of kv_heads")
+    _need(pages * nkv * page_size < 2 ** 31, "attention: the cache has too many rows")
+    _need(out.shape[1] == heads * head_dim and out.dtype == k_cache.dtype == q.dtype,
+          "attention: out [n, heads * d] in the cache dtype")
+    if n_splits > 1:
+        _need(partial is not None and partial.dtype == torch.float32
+              and partial.numel() >= n * heads * n_splits * (head_dim + 2),
+              "attention: partial scratch too small")
+    _check(_lib().nnis_attention_generic(
+        _ptr(q), q_stride, _ptr(k_cache), _ptr(v_cache), _ptr(token_pos), _ptr(token_seq),
+        _ptr(page_table), page_table.shape[1], _ptr(out), _ptr(partial), n, heads, kv_heads, head_dim,
+        page_size, window, ctypes.c_float(scale), n_splits, code_of(out.dtype), _stream()),
+        "attention_generic")
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    _cuda(logits, out)
+    _need(logits.dtype == torch.float32 and out.dtype == torch.int32, "argmax: float32 -> int32")
+    n, vocab = logits.shape
+    _need(out.numel() >= n, "argmax: out too small")
+    _check(_lib().nnis_argmax(_ptr(logits), _ptr(out), n, vocab, _stream()), "argmax")
+
+
+def sample_temperature(logits: torch.Tensor, temperature: torch.Tensor, rng_state: torch.Tensor,
+                       out: torch.Tensor) -> None:
+    """One seeded draw per row; ``rng_state`` (int64, SplitMix64) advances."""
+    _cuda(logits, temperature, rng_state, out)
+    n, vocab = logits.shape
+    _need(logits.dtype == torch.float32 and out.dtype == torch.int32, "sample: float32 -> int32")
+    _need(temperature.dtype == torch.float32 and temperature.numel() >= n, "temperature: float32 [n]")
+    _need(rng_state.dtype == torch.int64 and rng_state.numel() >= n, "rng_state: int64 [n]")
+    _check(_lib().nnis_sample_temperature(_ptr(logits), _ptr(temperature), _ptr(rng_state),
+                                          _ptr(out), n, vocab, _stream()), "sample_temperature")
+
+
+def gemm_tc_takes(m: int, n: int, k: int) -> bool:
+    """Whether the tcgen05 kernel runs this bfloat16 product (else CUDA cores)."""
+    return False
+
+
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+            mode: int) -> None:
+    raise KernelError("gemm_tc: not available")

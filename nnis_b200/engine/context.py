@@ -1,0 +1,55 @@
+"""What a step tells the parts: where each packed token sits.
+
+All tensors are int32 on the device.  ``token_pos[n]`` is the position of token
+n in its sequence (-1 marks a padding row, which no kernel stores or reads);
+``token_seq[n]`` is the row of its sequence in this step's batch, which indexes
+``page_tables[g]`` (one table per cache group) and ``seq_slots``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Sequence
+
+import torch
+
+from .workspace import Workspace
+
+_SM_COUNT = {}
+
+
+def sm_count(device: torch.device) -> int:
+    key = torch.device(device).index or 0
+    if key not in _SM_COUNT:
+        _SM_COUNT[key] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _SM_COUNT[key]
+
+
+@dataclass
+class StepContext:
+    n_tokens: int
+    n_seqs: int
+    tokens: torch.Tensor
+    token_pos: torch.Tensor
+    token_seq: torch.Tensor
+    seq_slots: torch.Tensor
+    page_tables: List[torch.Tensor]
+    workspace: Workspace
+    decode: bool
+    max_context: int  # longest sequence after this step (host knowledge)
+    # host-side copies, for parts that loop on the host (toy mixers in tests)
+    host_slots: Sequence[int] = field(default_factory=list)
+    host_counts: Sequence[int] = field(default_factory=list)
+    host_starts: Sequence[int] = field(default_factory=list)
+    fixed_splits: int = 0  # > 0: a captured graph fixed the split count
+
+    def attention_splits(self, query_rows: int) -> int:
+        """How many ways to cut each query's key range so the GPU is full when
+        there are few queries and many keys (decoding)."""
+        if self.fixed_splits > 0:
+            return self.fixed_splits
+        if not self.decode:
+            return 1
+        warps_wanted = sm_count(self.tokens.device) * 16
+        by_rows = max(1, warps_wanted // max(1, query_rows))
+        by_keys = max(1, -(-self.max_context // 128))
+        return int(min(by_rows, by_keys, 64))

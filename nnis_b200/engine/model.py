@@ -1,0 +1,90 @@
+"""A decoder put together from a ``ModelSpec``: embedding, blocks in their run
+order, final norm, head.  It holds weights and runs packed tokens; it owns no
+cache and no batch logic.  NNIS's ``Model`` plays the same role with a fixed
+decoder (crates/nnis-model/src/runtime.rs:109-128, :918-1120).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Mapping, Optional
+
+import torch
+
+from ..cache import KVRequest, KVView, StateRequest
+from ..config.spec import ModelSpec
+from ..parts import BLOCKS, NORMS, LinearHead, TokenEmbedding
+from ..weights.loader import WeightSpec
+
+
+class DecoderModel:
+    def __init__(self, spec: ModelSpec, dtype: torch.dtype, device: torch.device):
+        spec.validate()
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"compute dtype must be float32 or bfloat16; got {dtype}")
+        self.spec, self.dtype, self.device = spec, dtype, torch.device(device)
+        self.embedding = TokenEmbedding(spec.embedding.params, "", dtype, self.device)
+        self.blocks = [BLOCKS.build(layer.block, layer, dtype, self.device) for layer in spec.layers]
+        self.final_norm = NORMS.build(spec.final_norm.kind, spec.final_norm.params, "", dtype,
+                                      self.device)
+        self.head = LinearHead(spec.head.params, "", dtype, self.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        for i, entry in enumerate(spec.schedule):
+            wants = self.blocks[entry.layer].mixer.cache_request()
+            if entry.cache_of is not None and wants is not None:
+                raise ValueError(f"schedule[{i}] reads the cache of entry {entry.cache_of} but its "
+                                 f"mixer writes one of its own")
+
+    # -- weights ------------------------------------------------------------
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        specs: Dict[str, WeightSpec] = {}
+        for part in (self.embedding, *self.blocks, self.final_norm, self.head):
+            for name, ws in part.weight_specs().items():
+                if name in specs and specs[name].shape != ws.shape:
+                    raise ValueError(f"tensor {name} is wanted with two shapes")
+                specs.setdefault(name, ws)
+        return specs
+
+    @staticmethod
+    def weight_specs_of(spec: ModelSpec) -> Dict[str, WeightSpec]:
+        """Names and shapes without building device state (random-weights mode)."""
+        return DecoderModel(spec, torch.float32, torch.device("cpu")).weight_specs()
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        for part in (self.embedding, *self.blocks, self.final_norm, self.head):
+            part.load(tensors)
+
+    def parameter_bytes(self) -> int:
+        """Bytes of weights one step reads: each scheduled block once per run,
+        norms, the head; the embedding only through the head when tied."""
+        total = self.final_norm.parameter_bytes() + self.head.parameter_bytes()
+        for entry in self.spec.schedule:
+            total += self.blocks[entry.layer].parameter_bytes()
+        return total
+
+    # -- cache ----------------------------------------------------------------
+    def cache_requests(self) -> List[Optional[object]]:
+        return [None if e.cache_of is not None else self.blocks[e.layer].mixer.cache_request()
+                for e in self.spec.schedule]
+
+    def bind_cache(self, cache) -> None:
+        self._views = []
+        for i, entry in enumerate(self.spec.schedule):
+            view = cache.view(entry.cache_of if entry.cache_of is not None else i)
+            if entry.cache_of is not None:
+                self.blocks[entry.layer].mixer.check_shared_cache(view)
+            self._views.append(view)
+
+    # -- run ------------------------------------------------------------------
+    def forward(self, ctx, want_rows: torch.Tensor, logits: torch.Tensor) -> None:
+        """Run ``ctx.n_tokens`` packed tokens; write the logits of the rows that
+        ``want_rows`` (int32, indices into the packed tokens) names."""
+        ws = ctx.workspace
+        n = ctx.n_tokens
+        hidden = ws.get("hidden", (n, self.spec.hidden_size), torch.float32)
+        self.embedding.forward(ctx.tokens, hidden, self.status)
+        for i, entry in enumerate(self.spec.schedule):
+            self.blocks[entry.layer].forward(hidden, ctx, self._views[i])
+        r = logits.shape[0]
+        if r:
+            final = ws.get("final", (r, self.spec.hidden_size), self.dtype)
+            self.final_norm.forward(hidden, final, want_rows)
+            self.head.forward(final, logits)

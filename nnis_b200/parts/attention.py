@@ -1,0 +1,113 @@
+"""Causal grouped-query attention over the paged cache.
+
+One fused projection makes q, k and v (the three checkpoint matrices are
+stacked along their output rows when they are loaded); the RoPE kernel rotates
+q and k in place and stores k and v at each token's position; the attention
+kernel reads every visible key from the cache; the output projection adds into
+the residual stream.  Steps 4-12 of NNIS's token pass
+(crates/nnis-model/src/runtime.rs:959-1044).
+
+params: hidden_size, heads, kv_heads, head_dim, bias, window (0: all keys),
+position (a PartSpec), names {q, k, v, o}, kv ("own" | "shared").  With
+``kv == "shared"`` the part has no k/v projection and reads the cache that the
+model hands it (another schedule entry's).
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Mapping, Optional
+
+import torch
+
+from ..cache import KVRequest, KVView
+from ..csrc import ops
+from ..weights.loader import WeightSpec
+from .base import MIXERS, POSITIONS, Part
+from .linear import ADD_F32, STORE, linear
+
+
+class Attention(Part):
+    def __init__(self, params, prefix, dtype, device):
+        super().__init__(params, prefix, dtype, device)
+        self.hidden = int(params["hidden_size"])
+        self.heads = int(params["heads"])
+        self.kv_heads = int(params["kv_heads"])
+        self.head_dim = int(params["head_dim"])
+        self.bias = bool(params.get("bias", False))
+        self.window = int(params.get("window", 0))
+        self.own_kv = params.get("kv", "own") == "own"
+        self.names = params["names"]
+        if self.heads % self.kv_heads:
+            raise ValueError(f"heads={self.heads} is not a multiple of kv_heads={self.kv_heads}")
+        if self.head_dim % 16 or not 16 <= self.head_dim <= 256:
+            raise ValueError(f"attention kernels take head sizes 16..256 in steps of 16; "
+                             f"got {self.head_dim}")
+        pos = params["position"]
+        self.position = POSITIONS.build(pos.kind, pos.params, prefix, dtype, device)
+        self.scale = 1.0 / math.sqrt(float(self.head_dim))
+        self.stored_kv = self.kv_heads if self.own_kv else 0
+        self.w_qkv = self.b_qkv = self.w_o = self.b_o = None
+
+    # -- weights ----------------------------------------------------------
+    def _proj_names(self):
+        return ("q", "k", "v") if self.own_kv else ("q",)
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        d, H = self.head_dim, self.hidden
+        rows = {"q": self.heads * d, "k": self.kv_heads * d, "v": self.kv_heads * d}
+        specs = {}
+        for p in self._proj_names():
+            specs[self.tensor_name(self.names[p])] = WeightSpec((rows[p], H), "matrix", fan_in=H)
+            if self.bias:
+                specs[self.tensor_name(self.names[p], "bias")] = WeightSpec((rows[p],), "vector")
+        specs[self.tensor_name(self.names["o"])] = WeightSpec((H, self.heads * d), "matrix",
+                                                              fan_in=self.heads * d)
+        if self.bias:
+            specs[self.tensor_name(self.names["o"], "bias")] = WeightSpec((H,), "vector")
+        return specs
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        ps = self._proj_names()
+        self.w_qkv = torch.cat([tensors[self.tensor_name(self.names[p])] for p in ps], 0).contiguous()
+        self.w_o = tensors[self.tensor_name(self.names["o"])]
+        if self.bias:
+            self.b_qkv = torch.cat([tensors[self.tensor_name(self.names[p], "bias")] for p in ps],
+                                   0).contiguous()
+            self.b_o = tensors[self.tensor_name(self.names["o"], "bias")]
+
+    def parameter_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.w_qkv, self.w_o, self.b_qkv, self.b_o)
+                   if t is not None)
+
+    # -- cache ------------------------------------------------------------
+    def cache_request(self) -> Optional[KVRequest]:
+        return KVRequest(self.kv_heads, self.head_dim, self.window) if self.own_kv else None
+
+    def check_shared_cache(self, view: KVView) -> None:
+        if not isinstance(view, KVView) or tuple(view.k.shape[1:]) != \
+                (self.kv_heads, view.page_size, self.head_dim) or view.window != self.window:
+            raise ValueError("the shared cache does not fit this attention's heads or window")
+
+    # -- run --------------------------------------------------------------
+    def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor, cache: KVView) -> None:
+        n = x.shape[0]
+        d, nq, nkv = self.head_dim, self.heads, self.kv_heads
+        ws = ctx.workspace
+        qkv = ws.get("qkv", (n, (nq + 2 * self.stored_kv) * d), self.dtype)
+        linear(x, self.w_qkv, self.b_qkv, qkv, STORE)
+        table = ctx.page_tables[cache.group]
+        tables = self.position.rotary_tables()
+        cos, sin = tables if tables is not None else (None, None)
+        ops.rope_store(qkv, ctx.token_pos, ctx.token_seq, table if self.own_kv else None, cos, sin,
+                       cache.k if self.own_kv else None, cache.v if self.own_kv else None, nq,
+                       self.stored_kv, d, cache.page_size)
+        attn = ws.get("attn", (n, nq * d), self.dtype)
+        splits = ctx.attention_splits(n * nq)
+        partial = ws.get("attn_partial", (n * nq * splits * (d + 2),), torch.float32) \
+            if splits > 1 else None
+        ops.attention_generic(qkv, qkv.shape[1], cache.k, cache.v, ctx.token_pos, ctx.token_seq,
+                              table, attn, nq, nkv, d, self.window, self.scale, splits, partial)
+        linear(attn, self.w_o, self.b_o, residual, ADD_F32)
+
+
+MIXERS.register("attention", Attention)

@@ -1,0 +1,74 @@
+"""Interfaces of the parts a block is put together from, and their registries.
+
+A part is built from the ``params`` of its ``PartSpec`` (sizes and constants),
+the tensor-name prefix of its block, the operand dtype and the device.  It never
+learns which model it is in.  Every part says which tensors it wants
+(``weight_specs``), takes them (``load``) and runs on packed tokens.
+
+====================  =====================================================
+registry              interface beyond ``weight_specs`` / ``load``
+====================  =====================================================
+``NORMS``             ``forward(x_f32 [n, width], out [m, width], rows=None)``
+``POSITIONS``         ``rotary_tables()`` -> (cos, sin) or None; ``apply(qk, ctx)``
+``MIXERS``            ``cache_request()``; ``forward(x, ctx, residual, cache)``
+``FEED_FORWARDS``     ``forward(x, ctx, residual)``
+``BLOCKS``            ``forward(hidden_f32, ctx, cache)`` over four parts
+====================  =====================================================
+
+Mixers and feed-forwards read ``x`` (operand dtype, ``[n, width]``) and *add*
+their result to ``residual`` (float32, ``[n, width]``): the residual sum is
+float32 in every dtype, and a fused epilogue may add in place.
+"""
+from __future__ import annotations
+
+from typing import Any, Callable, Dict, Mapping, Optional
+
+import torch
+
+from ..weights.loader import WeightSpec
+
+
+class Part:
+    def __init__(self, params: Mapping[str, Any], prefix: str, dtype: torch.dtype,
+                 device: torch.device):
+        self.params = params
+        self.prefix = prefix
+        self.dtype = dtype
+        self.device = device
+
+    def tensor_name(self, stem: str, leaf: str = "weight") -> str:
+        return f"{self.prefix}.{stem}.{leaf}" if self.prefix else f"{stem}.{leaf}"
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {}
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        pass
+
+    def parameter_bytes(self) -> int:
+        """Bytes of weights that one step reads."""
+        return 0
+
+
+class Registry:
+    def __init__(self, what: str):
+        self.what = what
+        self._kinds: Dict[str, Callable[..., Part]] = {}
+
+    def register(self, kind: str, factory: Callable[..., Part]) -> None:
+        self._kinds[kind] = factory
+
+    def build(self, kind: str, *args, **kwargs) -> Part:
+        if kind not in self._kinds:
+            raise KeyError(f"unknown {self.what} {kind!r}; known: {sorted(self._kinds)}")
+        return self._kinds[kind](*args, **kwargs)
+
+    def known(self):
+        return sorted(self._kinds)
+
+
+NORMS = Registry("norm")
+POSITIONS = Registry("position encoding")
+MIXERS = Registry("mixer")
+FEED_FORWARDS = Registry("feed-forward")
+BLOCKS = Registry("block arrangement")

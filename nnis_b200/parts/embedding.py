@@ -1,0 +1,62 @@
+"""Token embedding and the linear head that ends the model.
+
+The head reads the embedding's table when the two are tied; there is no second
+copy (NNIS keeps a transposed copy: crates/nnis-model/src/safetensors_loader.rs:755-786).
+Logits are float32 in every dtype (crates/nnis-model/src/runtime.rs:1109-1116).
+"""
+from __future__ import annotations
+
+from typing import Dict, Mapping, Optional
+
+import torch
+
+from ..csrc import ops
+from ..weights.loader import WeightSpec
+from .base import Part
+from .linear import STORE_F32, linear
+
+
+class TokenEmbedding(Part):
+    """params: vocab_size, hidden_size, name."""
+
+    def __init__(self, params, prefix, dtype, device):
+        super().__init__(params, prefix, dtype, device)
+        self.vocab = int(params["vocab_size"])
+        self.width = int(params["hidden_size"])
+        self.name = self.tensor_name(params["name"])
+        self.table: Optional[torch.Tensor] = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {self.name: WeightSpec((self.vocab, self.width), "matrix")}
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.table = tensors[self.name]
+
+    def forward(self, tokens: torch.Tensor, hidden: torch.Tensor, status: torch.Tensor) -> None:
+        ops.embed(self.table, tokens, hidden, status)
+
+
+class LinearHead(Part):
+    """params: vocab_size, hidden_size, name, tied_to (tensor stem or None)."""
+
+    def __init__(self, params, prefix, dtype, device):
+        super().__init__(params, prefix, dtype, device)
+        self.vocab = int(params["vocab_size"])
+        self.width = int(params["hidden_size"])
+        tied = params.get("tied_to")
+        self.tied = tied is not None
+        self.name = self.tensor_name(tied if self.tied else params["name"])
+        self.weight: Optional[torch.Tensor] = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {self.name: WeightSpec((self.vocab, self.width), "matrix",
+                                      fan_in=0 if self.tied else self.width)}
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.weight = tensors[self.name]
+
+    def parameter_bytes(self) -> int:
+        return self.weight.numel() * self.weight.element_size()
+
+    def forward(self, x: torch.Tensor, logits: torch.Tensor) -> None:
+        linear(x, self.weight, None, logits, STORE_F32)

@@ -1,0 +1,69 @@
+"""Gated feed-forward: down( act(gate(x)) * up(x) ), added to the residual.
+
+Gate and up are one projection (their matrices stacked along the output rows
+at load) with float32 output; the activation kernel rounds once to the operand
+dtype.  Steps 14-18 of NNIS's token pass
+(crates/nnis-model/src/runtime.rs:1054-1093).
+
+params: hidden_size, intermediate_size, activation ("silu"), bias,
+names {gate, up, down}.
+"""
+from __future__ import annotations
+
+from typing import Dict, Mapping
+
+import torch
+
+from ..csrc import ops
+from ..weights.loader import WeightSpec
+from .base import FEED_FORWARDS, Part
+from .linear import ADD_F32, STORE_F32, linear
+
+
+class GatedMLP(Part):
+    def __init__(self, params, prefix, dtype, device):
+        super().__init__(params, prefix, dtype, device)
+        self.hidden = int(params["hidden_size"])
+        self.inter = int(params["intermediate_size"])
+        self.bias = bool(params.get("bias", False))
+        self.names = params["names"]
+        if params.get("activation", "silu") != "silu":
+            raise ValueError(f"gated_mlp: activation {params['activation']!r} has no kernel")
+        self.w_gu = self.b_gu = self.w_down = self.b_down = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        H, I = self.hidden, self.inter
+        specs = {self.tensor_name(self.names["gate"]): WeightSpec((I, H), "matrix", fan_in=H),
+                 self.tensor_name(self.names["up"]): WeightSpec((I, H), "matrix", fan_in=H),
+                 self.tensor_name(self.names["down"]): WeightSpec((H, I), "matrix", fan_in=I)}
+        if self.bias:
+            specs[self.tensor_name(self.names["gate"], "bias")] = WeightSpec((I,), "vector")
+            specs[self.tensor_name(self.names["up"], "bias")] = WeightSpec((I,), "vector")
+            specs[self.tensor_name(self.names["down"], "bias")] = WeightSpec((H,), "vector")
+        return specs
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        n = self.names
+        self.w_gu = torch.cat([tensors[self.tensor_name(n["gate"])],
+                               tensors[self.tensor_name(n["up"])]], 0).contiguous()
+        self.w_down = tensors[self.tensor_name(n["down"])]
+        if self.bias:
+            self.b_gu = torch.cat([tensors[self.tensor_name(n["gate"], "bias")],
+                                   tensors[self.tensor_name(n["up"], "bias")]], 0).contiguous()
+            self.b_down = tensors[self.tensor_name(n["down"], "bias")]
+
+    def parameter_bytes(self) -> int:
+        return sum(t.numel() * t.element_size()
+                   for t in (self.w_gu, self.w_down, self.b_gu, self.b_down) if t is not None)
+
+    def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor) -> None:
+        n = x.shape[0]
+        ws = ctx.workspace
+        gate_up = ws.get("gate_up", (n, 2 * self.inter), torch.float32)
+        linear(x, self.w_gu, self.b_gu, gate_up, STORE_F32)
+        act = ws.get("act", (n, self.inter), self.dtype)
+        ops.silu_mul(gate_up, act)
+        linear(act, self.w_down, self.b_down, residual, ADD_F32)
+
+
+FEED_FORWARDS.register("gated_mlp", GatedMLP)

@@ -1,0 +1,145 @@
+"""The cache's bookkeeping on the host: no slot or page lost, held twice or
+freed twice; requests that cannot be met change nothing (no GPU)."""
+import random
+
+import pytest
+import torch
+
+from nnis_b200.cache import (PAGE_SIZE, CacheFull, CacheManager, FreeList, KVRequest, SlotError,
+                             StateRequest)
+
+
+def make(max_tokens=64 * 8, max_slots=4, requests=None, max_positions=10_000):
+    requests = requests if requests is not None else [KVRequest(2, 16), KVRequest(2, 16)]
+    return CacheManager(requests, torch.float32, torch.device("cpu"), max_tokens, max_slots,
+                        max_positions)
+
+
+def test_free_list_never_hands_out_twice_and_reuses_lowest():
+    f = FreeList(3, "slot")
+    a, b, c = f.take(), f.take(), f.take()
+    assert sorted((a, b, c)) == [0, 1, 2]
+    with pytest.raises(CacheFull):
+        f.take()
+    f.give(1)
+    with pytest.raises(SlotError):
+        f.give(1)
+    with pytest.raises(SlotError):
+        f.give(9)
+    assert f.take() == 1
+    f.check()
+
+
+def test_slots_are_given_back_and_used_again():
+    c = make()
+    held = [c.acquire() for _ in range(4)]
+    assert sorted(held) == [0, 1, 2, 3]
+    with pytest.raises(CacheFull):
+        c.acquire()
+    c.release(2)
+    with pytest.raises(SlotError):
+        c.release(2)
+    assert c.acquire() == 2
+    c.check()
+
+
+def test_pages_follow_lengths_and_return_on_release():
+    c = make()
+    s = c.acquire()
+    c.reserve([s], [1])
+    c.commit([s], [1])
+    assert len(c.page_table(0, s)) == 1
+    c.reserve([s], [PAGE_SIZE])
+    assert len(c.page_table(0, s)) == 1
+    c.reserve([s], [PAGE_SIZE + 1])
+    c.commit([s], [PAGE_SIZE + 1])
+    assert len(c.page_table(0, s)) == 2 and c.length(s) == PAGE_SIZE + 1
+    assert c.usage()["pages_held"] == [2]
+    c.release(s)
+    assert c.usage()["pages_held"] == [0]
+    c.check()
+
+
+def test_layers_of_one_shape_share_a_group_and_others_have_their_own():
+    c = make(requests=[KVRequest(2, 16), KVRequest(2, 16), KVRequest(1, 32), KVRequest(2, 16, 128),
+                       None, StateRequest((3, 5))])
+    assert len(c.groups) == 3
+    assert c.view(0).group == c.view(1).group != c.view(2).group
+    assert c.view(3).group not in (c.view(0).group, c.view(2).group) and c.view(3).window == 128
+    assert c.view(0).k.data_ptr() != c.view(1).k.data_ptr()
+    assert c.view(4) is None
+    assert tuple(c.view(5).state.shape) == (4, 3, 5)
+    assert tuple(c.view(2).k.shape) == (8, 1, PAGE_SIZE, 32)
+
+
+def test_failed_reserve_changes_nothing():
+    c = make(max_tokens=PAGE_SIZE * 3)
+    a, b = c.acquire(), c.acquire()
+    c.reserve([a], [PAGE_SIZE * 2])
+    c.commit([a], [PAGE_SIZE * 2])
+    before = (list(c.page_table(0, a)), list(c.page_table(0, b)), c.usage()["pages_held"])
+    with pytest.raises(CacheFull):
+        c.reserve([a, b], [PAGE_SIZE * 2 + 1, PAGE_SIZE + 1])
+    assert before == (list(c.page_table(0, a)), list(c.page_table(0, b)), c.usage()["pages_held"])
+    with pytest.raises(SlotError):
+        c.reserve([a, a], [PAGE_SIZE * 2, PAGE_SIZE * 2])
+    with pytest.raises(SlotError):
+        c.reserve([3], [1])
+    with pytest.raises(SlotError):
+        c.reserve([a], [5])  # shrinking
+    c.check()
+
+
+def test_positions_beyond_the_model_are_refused():
+    c = make(max_positions=100)
+    s = c.acquire()
+    with pytest.raises(CacheFull, match="100"):
+        c.reserve([s], [101])
+
+
+def test_window_group_gives_back_pages_behind_the_window():
+    c = make(max_tokens=PAGE_SIZE * 8, requests=[KVRequest(1, 16, 70)])
+    s = c.acquire()
+    c.reserve([s], [300])
+    assert c.usage()["pages_held"] == [5]
+    c.commit([s], [300])
+    # next query at 300 sees keys 231..300: pages 0..2 (keys 0..191) are free again
+    assert c.page_table(0, s)[:3] == [-1, -1, -1] and c.usage()["pages_held"] == [2]
+    c.release(s)
+    c.check()
+    assert c.usage()["pages_held"] == [0]
+
+
+def test_state_rows_are_zeroed_when_a_slot_is_taken():
+    c = make(requests=[StateRequest((4,))])
+    s = c.acquire()
+    c.view(0).state[s] += 3.0
+    c.release(s)
+    assert c.acquire() == s
+    assert float(c.view(0).state[s].abs().sum()) == 0.0
+
+
+def test_random_traffic_loses_nothing():
+    rng = random.Random(0)
+    c = make(max_tokens=PAGE_SIZE * 40, max_slots=6)
+    live = {}
+    for _ in range(2000):
+        r = rng.random()
+        if r < 0.3 and len(live) < 6:
+            live[c.acquire()] = 0
+        elif r < 0.8 and live:
+            s = rng.choice(list(live))
+            n = live[s] + rng.randrange(1, 90)
+            try:
+                c.reserve([s], [n])
+                c.commit([s], [n])
+                live[s] = n
+            except CacheFull:
+                pass
+        elif live:
+            s = rng.choice(list(live))
+            c.release(s)
+            del live[s]
+        c.check()
+        assert c.usage()["pages_held"] == [sum(-(-n // PAGE_SIZE) for n in live.values())]
+        assert c.usage()["live_tokens"] == sum(live.values())
