@@ -7,3 +7,20 @@ feed-forward, block), ``cache`` (slots, paged keys and values, state),
 ``csrc`` (CUDA kernels and their build), ``cli``.
 """
 __version__ = "0.1.0"
+
+
+def __getattr__(name):
+    # the entry points import torch and the kernels; keep "import nnis_b200" light
+    if name in ("LLM", "InferenceSession"):
+        from .engine import api
+        return getattr(api, name)
+    if name in ("GenerationConfig", "GenerationRequest", "GenerationResult"):
+        from .engine import generate
+        return getattr(generate, name)
+    if name == "SamplingConfig":
+        from .sampling import SamplingConfig
+        return SamplingConfig
+    if name == "Engine":
+        from .engine import Engine
+        return Engine
+    raise AttributeError(name)

@@ -28,8 +28,9 @@ _DTYPE = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 def random_tensors(wanted: Mapping[str, WeightSpec], seed: int, std: float = 0.02,
                    norm_std: float = 0.01, norm_center: float = 1.0,
                    std_by_fan_in: bool = False) -> Dict[str, torch.Tensor]:
-    """``std_by_fan_in`` draws matrices with std/sqrt(fan_in/64): activations
-    then keep their size through the layers, which tests of attention need."""
+    """``std_by_fan_in`` draws projections with std / sqrt(fan_in): with std 1
+    activations keep their size through the layers and attention scores are of
+    order one, which tests of attention need."""
     gen = torch.Generator(device="cpu")
     gen.manual_seed(int(seed))
     out: Dict[str, torch.Tensor] = {}
@@ -41,7 +42,7 @@ def random_tensors(wanted: Mapping[str, WeightSpec], seed: int, std: float = 0.0
         if spec.init == "ones":
             out[name] = norm_center + x * norm_std
         elif std_by_fan_in and spec.fan_in > 0:
-            out[name] = x * (std / (spec.fan_in / 64.0) ** 0.5)
+            out[name] = x * (std / spec.fan_in ** 0.5)
         else:
             out[name] = x * std
     return out

@@ -46,7 +46,7 @@ def make_model(tmp_dir: str, config: dict, seed: int, healthy: bool = True) -> s
     N(0, 0.02) everywhere attention is nearly uniform and hides faults."""
     from nnis_b200.weights import write_random_model
     if healthy:
-        return write_random_model(config, seed, tmp_dir, std=0.5, norm_std=0.1, std_by_fan_in=True)
+        return write_random_model(config, seed, tmp_dir, std=1.0, norm_std=0.1, std_by_fan_in=True)
     return write_random_model(config, seed, tmp_dir)
 
 
