@@ -1,0 +1,234 @@
+"""``nnis generate`` and ``nnis generate-batch`` with NNIS's options and rules
+(crates/nnis-cli/src/main.rs:21-23 usage and defaults, :179-365 and :367-498
+flag rules, :117-132 the JSON of generate-batch, :1348-1390 exit codes).
+
+Additions: ``--model`` is a Hugging Face folder; ``--prompt-ids 1,2,3`` gives a
+prompt as token ids, and then ``--tokenizer`` may be left out (ids are printed);
+``--dtype bfloat16|float32``.
+"""
+from __future__ import annotations
+
+import json
+import math
+import sys
+from dataclasses import dataclass, field
+from typing import List, Optional
+
+DEFAULT_DEVICE_ORDINAL = 0
+DEFAULT_MAX_NEW_TOKENS = 16
+GENERATE_BATCH_JSON_SCHEMA_VERSION = 1
+USAGE = """Usage:
+  nnis generate --model DIR [--tokenizer FILE] --prompt TEXT | --prompt-ids IDS [--device N] [--max-new-tokens N] [--dtype bfloat16|float32] [--sample --seed U64] [--temperature F] [--top-k N] [--top-p F] [--stream]
+  nnis generate-batch --model DIR [--tokenizer FILE] --prompt TEXT [--prompt TEXT ...] | --prompt-ids IDS [--prompt-ids IDS ...] --seed U64 [--seed U64 ...] [--device N] [--max-new-tokens N] [--dtype bfloat16|float32] [--temperature F] [--top-k N] [--top-p F] [--json]
+
+Default decoding on `generate` is greedy. Opt-in `--sample` requires `--seed`. Optional `--temperature`, `--top-k`, and `--top-p` apply only with `--sample`. `--stream` is valid only with `--sample` and prints each token as it is emitted. `generate-batch` requires one `--seed` per prompt and always samples; `--json` emits versioned JSON. CUDA device ordinal defaults to 0."""
+
+
+class UsageError(Exception):
+    pass
+
+
+@dataclass
+class GenerateArgs:
+    model_dir: str = ""
+    tokenizer_file: Optional[str] = None
+    prompts: List[str] = field(default_factory=list)
+    prompt_ids: List[List[int]] = field(default_factory=list)
+    device_ordinal: int = DEFAULT_DEVICE_ORDINAL
+    max_new_tokens: int = DEFAULT_MAX_NEW_TOKENS
+    dtype: str = "bfloat16"
+    sample: bool = False
+    stream: bool = False
+    json: bool = False
+    seeds: List[int] = field(default_factory=list)
+    temperature: Optional[float] = None
+    top_k: Optional[int] = None
+    top_p: Optional[float] = None
+    command: str = "generate"
+
+
+def _positive_float(flag: str, raw: str) -> float:
+    try:
+        value = float(raw)
+    except ValueError:
+        raise UsageError(f"invalid {flag} {raw!r}") from None
+    if not math.isfinite(value) or value <= 0:
+        raise UsageError(f"{flag} must be finite and positive; got {raw}")
+    return value
+
+
+def _unsigned(flag: str, raw: str, positive: bool = False, limit: int = (1 << 64) - 1) -> int:
+    try:
+        value = int(raw)
+    except ValueError:
+        raise UsageError(f"invalid {flag} {raw!r}") from None
+    if value < 0 or value > limit or (positive and value == 0):
+        raise UsageError(f"{flag} must be {'positive' if positive else 'non-negative'}; got {raw}")
+    return value
+
+
+def _ids(raw: str) -> List[int]:
+    try:
+        ids = [int(x) for x in raw.replace(" ", "").split(",") if x != ""]
+    except ValueError:
+        raise UsageError(f"invalid --prompt-ids {raw!r}") from None
+    if not ids or any(i < 0 for i in ids):
+        raise UsageError(f"--prompt-ids needs non-negative integers; got {raw!r}")
+    return ids
+
+
+def parse_args(argv: List[str]) -> Optional[GenerateArgs]:
+    """None for help.  Raises UsageError with NNIS's rules."""
+    if not argv or argv[0] in ("-h", "--help", "help"):
+        return None
+    command = argv[0]
+    if command not in ("generate", "generate-batch"):
+        raise UsageError(f"unknown command {command!r}")
+    a = GenerateArgs(command=command)
+    batch = command == "generate-batch"
+    seen = set()
+    it = iter(argv[1:])
+    for flag in it:
+        if flag in ("-h", "--help"):
+            return None
+        if flag in ("--sample", "--stream", "--json"):
+            if (flag == "--json") != batch and flag == "--json":
+                raise UsageError("--json belongs to generate-batch")
+            if batch and flag != "--json":
+                raise UsageError(f"{flag} does not apply to generate-batch (it always samples)")
+            setattr(a, flag[2:], True)
+            continue
+        try:
+            value = next(it)
+        except StopIteration:
+            raise UsageError(f"{flag} needs a value") from None
+        repeatable = batch and flag in ("--prompt", "--prompt-ids", "--seed")
+        if flag in seen and not repeatable:
+            raise UsageError(f"{flag} given twice")
+        seen.add(flag)
+        if flag == "--model":
+            a.model_dir = value
+        elif flag == "--tokenizer":
+            a.tokenizer_file = value
+        elif flag == "--prompt":
+            a.prompts.append(value)
+        elif flag == "--prompt-ids":
+            a.prompt_ids.append(_ids(value))
+        elif flag == "--device":
+            a.device_ordinal = _unsigned(flag, value, limit=(1 << 31) - 1)
+        elif flag == "--max-new-tokens":
+            a.max_new_tokens = _unsigned(flag, value, positive=True, limit=65536)
+        elif flag == "--dtype":
+            if value not in ("bfloat16", "float32"):
+                raise UsageError(f"--dtype must be bfloat16 or float32; got {value!r}")
+            a.dtype = value
+        elif flag == "--seed":
+            a.seeds.append(_unsigned(flag, value))
+        elif flag == "--temperature":
+            a.temperature = _positive_float(flag, value)
+        elif flag == "--top-k":
+            a.top_k = _unsigned(flag, value, positive=True)
+        elif flag == "--top-p":
+            a.top_p = _positive_float(flag, value)
+            if a.top_p > 1:
+                raise UsageError(f"--top-p must be in (0, 1]; got {value}")
+        else:
+            raise UsageError(f"unknown flag {flag!r}")
+    if not a.model_dir:
+        raise UsageError("--model is required")
+    if a.prompts and a.prompt_ids:
+        raise UsageError("give --prompt or --prompt-ids, not both")
+    n_prompts = len(a.prompts) + len(a.prompt_ids)
+    if n_prompts == 0:
+        raise UsageError("--prompt is required")
+    if a.prompts and not a.tokenizer_file:
+        raise UsageError("--tokenizer is required with --prompt")
+    if batch:
+        if len(a.seeds) != n_prompts:
+            raise UsageError(f"generate-batch needs one --seed per prompt: {n_prompts} prompts, "
+                             f"{len(a.seeds)} seeds")
+        a.sample = True
+    else:
+        if n_prompts != 1:
+            raise UsageError("generate takes one prompt")
+        if not a.sample:
+            for name, given in (("--seed", a.seeds), ("--temperature", a.temperature),
+                                ("--top-k", a.top_k), ("--top-p", a.top_p), ("--stream", a.stream)):
+                if given:
+                    raise UsageError(f"{name} requires --sample")
+        elif len(a.seeds) != 1:
+            raise UsageError("--sample requires --seed")
+    return a
+
+
+def _policy(a: GenerateArgs, seed: int):
+    from ..sampling import SamplingConfig
+    return SamplingConfig(seed=seed, temperature=a.temperature if a.temperature is not None else 1.0,
+                          top_k=a.top_k, top_p=a.top_p)
+
+
+def run(a: GenerateArgs, out=sys.stdout) -> int:
+    from ..engine.api import LLM
+    from ..sampling import SAMPLING_POLICY_VERSION
+    prompts = a.prompts if a.prompts else a.prompt_ids
+    llm = LLM(a.model_dir, dtype=a.dtype, device_ordinal=a.device_ordinal,
+              tokenizer_file=a.tokenizer_file, max_batch=max(1, len(prompts)),
+              max_tokens=max(4096, sum(len(p) for p in prompts) + len(prompts) * (a.max_new_tokens + 64)))
+
+    def text_of(ids):
+        return llm.decode(ids) if llm.tokenizer is not None else " ".join(str(i) for i in ids)
+
+    sampling = [_policy(a, s) for s in a.seeds] if a.sample else None
+    emitted = {}
+
+    def on_token(index, token):
+        # print only what the new token adds to the decoded text
+        ids = emitted.setdefault(index, [])
+        before = text_of(ids)
+        ids.append(token)
+        after = text_of(ids)
+        out.write(after[len(before):] if after.startswith(before) else after)
+        out.flush()
+
+    results = llm.generate(prompts, max_new_tokens=a.max_new_tokens, sampling=sampling,
+                           on_token=on_token if a.stream else None)
+    failed = any(not r.ok for r in results)
+    if a.command == "generate":
+        r = results[0]
+        if not r.ok:
+            print(f"error: {r.error}", file=sys.stderr)
+            return 1
+        out.write("\n" if a.stream else text_of(r.token_ids) + "\n")
+        return 0
+    if a.json:
+        json.dump({"schema_version": GENERATE_BATCH_JSON_SCHEMA_VERSION,
+                   "sampling_policy_version": SAMPLING_POLICY_VERSION,
+                   "session_count": len(results),
+                   "results": [{"batch_index": r.index, "seed": a.seeds[r.index], "ok": r.ok,
+                                "text": text_of(r.token_ids) if r.ok else None,
+                                "error": r.error} for r in results]}, out)
+        out.write("\n")
+    else:
+        for r in results:
+            if r.ok:
+                out.write(f"[{r.index}] seed={a.seeds[r.index]}: {text_of(r.token_ids)}\n")
+            else:
+                out.write(f"[{r.index}] seed={a.seeds[r.index]}: error: {r.error}\n")
+    return 1 if failed else 0
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    try:
+        args = parse_args(argv)
+    except UsageError as e:
+        print(f"error: {e}\n\n{USAGE}", file=sys.stderr)
+        return 2
+    if args is None:
+        print(USAGE)
+        return 0
+    try:
+        return run(args)
+    except Exception as e:  # a run failure, not a usage error
+        print(f"error: {type(e).__name__}: {e}", file=sys.stderr)
+        return 1

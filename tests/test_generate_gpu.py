@@ -1,0 +1,92 @@
+"""Generation through the Python entry point and the command line on the GPU."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+import plain_llama as P
+from helpers import CONFIGS, load_plain_weights, make_model, read_config_json
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def model_dirs(tmp_path_factory):
+    return {n: make_model(str(tmp_path_factory.mktemp(f"gen{n}")), c, seed=40 + i)
+            for i, (n, c) in enumerate(CONFIGS.items())}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_matches_the_plain_loop(model_dirs, name, dtype):
+    from nnis_b200 import LLM
+    d = model_dirs[name]
+    cfg = read_config_json(d)
+    bf = dtype == "bfloat16"
+    w = load_plain_weights(d, as_bf16=bf)
+    llm = LLM(d, dtype=dtype, max_tokens=64 * 32, max_batch=3)
+    prompts = [[5, 9, 1, 200, 33], [7], [100, 101, 102, 103, 104, 105, 106, 107, 108], [250, 3],
+               [9] * 70]
+    results = llm.generate(prompts, max_new_tokens=12, stop_token_ids=())
+    for p, r in zip(prompts, results):
+        assert r.ok and r.finish_reason == "length"
+        assert r.token_ids == P.greedy_generate(cfg, w, p, 12, None, bf), (name, dtype, p)
+    # a stop token ends its sequence early; the others go on
+    stop = results[0].token_ids[3]
+    again = llm.generate(prompts[:2], max_new_tokens=12, stop_token_ids=[stop])
+    cut = results[0].token_ids[:results[0].token_ids.index(stop) + 1]
+    assert again[0].token_ids == cut and again[0].finish_reason == "stop"
+    want1 = results[1].token_ids
+    if stop in want1:
+        want1 = want1[:want1.index(stop) + 1]
+    assert again[1].token_ids == want1
+    assert llm.engine.cache.usage()["slots_held"] == 0
+
+
+def test_sampled_generation_is_seeded_and_sessions_work(model_dirs):
+    from nnis_b200 import LLM, GenerationConfig, SamplingConfig
+    from nnis_b200.sampling import HostLogitSampler
+    d = model_dirs["B"]  # its head is not tied, so its logits are of order one
+    llm = LLM(d, dtype="float32", max_tokens=64 * 16, max_batch=4)
+    policy = SamplingConfig(seed=11, temperature=0.8, top_k=20, top_p=0.9)
+    a = llm.generate([[1, 2, 3], [4, 5]], max_new_tokens=8, sampling=policy, stop_token_ids=())
+    b = llm.generate([[1, 2, 3], [4, 5]], max_new_tokens=8, sampling=policy, stop_token_ids=())
+    c = llm.generate([[1, 2, 3]], max_new_tokens=8, sampling=SamplingConfig(seed=12), stop_token_ids=())
+    assert [r.token_ids for r in a] == [r.token_ids for r in b]
+    assert a[0].token_ids != c[0].token_ids
+    # the session surface: prefill + decode_one with the host sampler gives the same tokens
+    session = llm.new_session()
+    sampler = HostLogitSampler(policy, 515)
+    logits = session.prefill([1, 2, 3])
+    tokens = []
+    for _ in range(8):
+        tokens.append(sampler.sample(logits))
+        logits = session.decode_one(tokens[-1])
+    assert tokens == a[0].token_ids and session.position() == 3 + 8
+    assert session.generate_sampled([1, 2, 3], GenerationConfig(8), policy) == a[0].token_ids
+    session.close()
+    assert llm.engine.cache.usage()["slots_held"] == 0
+
+
+def test_command_line_generates(model_dirs):
+    d = model_dirs["A"]
+    cfg = read_config_json(d)
+    w = load_plain_weights(d, as_bf16=False)
+    run = lambda *args: subprocess.run([sys.executable, os.path.join(ROOT, "bin", "nnis"), *args],
+                                       capture_output=True, text=True, timeout=600)
+    r = run("generate", "--model", d, "--prompt-ids", "5,9,1", "--max-new-tokens", "6", "--dtype",
+            "float32")
+    assert r.returncode == 0, r.stderr[-2000:]
+    want = P.greedy_generate(cfg, w, [5, 9, 1], 6, 7)
+    assert r.stdout.split() == [str(t) for t in want]
+    r = run("generate-batch", "--model", d, "--prompt-ids", "5,9,1", "--prompt-ids", "3,999",
+            "--seed", "1", "--seed", "2", "--json", "--dtype", "float32", "--max-new-tokens", "4")
+    assert r.returncode == 1
+    out = json.loads(r.stdout)
+    assert out["schema_version"] == 1 and out["session_count"] == 2
+    assert out["results"][0]["ok"] and not out["results"][1]["ok"]
+    assert "vocabulary" in out["results"][1]["error"]
+    assert run("generate", "--model", d, "--prompt-ids", "1", "--seed", "3").returncode == 2

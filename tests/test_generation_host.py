@@ -1,0 +1,220 @@
+"""The generation loop's decisions with a scripted backend, the host sampler,
+and the command line's rules (no GPU)."""
+import numpy as np
+import pytest
+
+import plain_llama as P
+from nnis_b200.cli.main import UsageError, parse_args
+from nnis_b200.engine.generate import (GenerationConfig, GenerationRequest, Generator,
+                                       pages_needed, plan_batches)
+from nnis_b200.sampling import HostLogitSampler, SamplingConfig, SamplingError, SplitMix64
+
+VOCAB = 50
+
+
+class ScriptedBackend:
+    """The next token of a sequence is (sum of its tokens) % VOCAB, so every
+    sequence has a known continuation; slots and steps are recorded."""
+
+    def __init__(self, n_slots=8, fail_on_step=None):
+        self.free = list(range(n_slots))
+        self.held = {}
+        self.steps = []
+        self.fail_on_step = fail_on_step
+        self.max_held = 0
+
+    def acquire_slot(self):
+        slot = min(self.free)
+        self.free.remove(slot)
+        self.held[slot] = []
+        self.max_held = max(self.max_held, len(self.held))
+        return slot
+
+    def release_slot(self, slot):
+        assert slot in self.held, "slot freed twice or never held"
+        del self.held[slot]
+        self.free.append(slot)
+
+    def step(self, batch):
+        if self.fail_on_step is not None and len(self.steps) == self.fail_on_step:
+            self.steps.append("boom")
+            raise RuntimeError("boom")
+        self.steps.append([(s.slot, len(s.tokens)) for s in batch])
+        rows = []
+        for s in batch:
+            assert s.slot in self.held
+            self.held[s.slot].extend(s.tokens)
+            row = np.full(VOCAB, -1.0, dtype=np.float32)
+            row[sum(self.held[s.slot]) % VOCAB] = 5.0
+            rows.append(row)
+        return np.stack(rows)
+
+    def greedy(self, logits):
+        return [int(np.argmax(r)) for r in logits]
+
+    def host_rows(self, logits, rows):
+        return logits[list(rows)]
+
+
+def expected(prompt, n, stops=()):
+    seq, out = list(prompt), []
+    for _ in range(n):
+        t = sum(seq) % VOCAB
+        out.append(t)
+        seq.append(t)
+        if t in stops:
+            break
+    return out
+
+
+def gen(backend, max_batch=4, max_tokens=64 * 64, max_positions=1000):
+    return Generator(backend, VOCAB, max_positions, max_batch, max_tokens)
+
+
+def test_unequal_prompts_stop_tokens_and_early_ends():
+    b = ScriptedBackend()
+    reqs = [GenerationRequest([1, 2, 3], GenerationConfig(6)),
+            GenerationRequest([7], GenerationConfig(2)),
+            GenerationRequest([4, 4], GenerationConfig(9, stop_token_ids=(expected([4, 4], 3)[2],)))]
+    res = gen(b).generate(reqs)
+    assert res[0].token_ids == expected([1, 2, 3], 6) and res[0].finish_reason == "length"
+    assert res[1].token_ids == expected([7], 2) and res[1].finish_reason == "length"
+    assert res[2].token_ids == expected([4, 4], 3) and res[2].finish_reason == "stop"
+    # one prompt step with all three, then the batch shrinks as sequences end;
+    # the last token of a sequence is never run
+    assert [len(s) for s in b.steps] == [3, 3, 2, 1, 1, 1]
+    assert b.steps[0] == [(0, 3), (1, 1), (2, 2)]
+    assert not b.held and sorted(b.free) == list(range(8))
+
+
+def test_batches_follow_one_another_and_reuse_slots():
+    b = ScriptedBackend(n_slots=2)
+    reqs = [GenerationRequest([i + 1], GenerationConfig(3)) for i in range(5)]
+    res = gen(b, max_batch=2).generate(reqs)
+    assert [r.token_ids for r in res] == [expected([i + 1], 3) for i in range(5)]
+    assert b.max_held == 2 and not b.held
+    assert [len(s) for s in b.steps] == [2, 2, 2, 2, 2, 2, 1, 1, 1]
+
+
+def test_plan_respects_pages():
+    reqs = [GenerationRequest([0] * 60, GenerationConfig(5)),   # 64 positions -> 1 page
+            GenerationRequest([0] * 60, GenerationConfig(6)),   # 65 -> 2 pages
+            GenerationRequest([0] * 10, GenerationConfig(5))]
+    assert [pages_needed(r) for r in reqs] == [1, 2, 1]
+    assert plan_batches(reqs, [True] * 3, 8, 3) == [[0, 1], [2]]
+    assert plan_batches(reqs, [True, False, True], 8, 3) == [[0, 2]]
+    assert plan_batches(reqs, [True] * 3, 1, 100) == [[0], [1], [2]]
+
+
+def test_bad_requests_fail_alone():
+    b = ScriptedBackend()
+    reqs = [GenerationRequest([], GenerationConfig(2)),
+            GenerationRequest([1, VOCAB], GenerationConfig(2)),
+            GenerationRequest([1], GenerationConfig(2000)),
+            GenerationRequest([1], GenerationConfig(2), SamplingConfig(seed=1, temperature=0.0)),
+            GenerationRequest([1], GenerationConfig(0)),
+            GenerationRequest([5], GenerationConfig(2))]
+    res = gen(b).generate(reqs)
+    assert [r.ok for r in res] == [False] * 5 + [True]
+    assert "empty" in res[0].error and "vocabulary" in res[1].error and "positions" in res[2].error
+    assert "temperature" in res[3].error and "max_new_tokens" in res[4].error
+    assert res[5].token_ids == expected([5], 2)
+    assert b.steps[0] == [(0, 1)]
+
+
+def test_a_failing_step_fails_its_batch_only_and_frees_slots():
+    b = ScriptedBackend(n_slots=2, fail_on_step=1)
+    reqs = [GenerationRequest([i + 1], GenerationConfig(3)) for i in range(3)]
+    res = gen(b, max_batch=2).generate(reqs)
+    assert not res[0].ok and not res[1].ok and "boom" in res[0].error
+    assert res[2].ok and res[2].token_ids == expected([3], 3)
+    assert not b.held
+
+
+def test_sampled_requests_use_their_own_seeded_sampler():
+    b = ScriptedBackend()
+    reqs = [GenerationRequest([3], GenerationConfig(4), SamplingConfig(seed=9).with_top_k(1)),
+            GenerationRequest([3], GenerationConfig(4))]
+    res = gen(b).generate(reqs)
+    assert res[0].token_ids == res[1].token_ids == expected([3], 4)  # top-k 1 is greedy
+    seen = []
+    gen(ScriptedBackend()).generate(reqs, on_token=lambda i, t: seen.append((i, t)))
+    assert [t for i, t in seen if i == 0] == expected([3], 4)
+
+
+# ---------------------------------------------------------------------------
+def test_splitmix_and_frozen_sequence():
+    # crates/nnis-model/src/sampling.rs:326-333
+    s = HostLogitSampler(SamplingConfig.seeded(42), 4)
+    assert [s.sample([0.0] * 4) for _ in range(10)] == [2, 0, 1, 1, 0, 3, 0, 3, 1, 2]
+    a, b = SplitMix64(7), P.PlainSplitMix64(7)
+    assert [a.next_u64() for _ in range(5)] == [b.next_u64() for _ in range(5)]
+
+
+def test_sampler_rules_of_the_reference():
+    assert HostLogitSampler(SamplingConfig.seeded(7).with_top_k(1), 4).sample([1, 4, 4, -2]) == 1
+    s = HostLogitSampler(SamplingConfig.seeded(9).with_top_p(0.1), 3)
+    assert all(s.sample([3.0, 2.0, 1.0]) == 0 for _ in range(32))
+    s = HostLogitSampler(SamplingConfig.seeded(123).with_top_k(2), 4)
+    assert all(s.sample([4.0, 3.0, 2.0, 1.0]) <= 1 for _ in range(64))
+    s = HostLogitSampler(SamplingConfig.seeded(1), 2)
+    for bad in ([1.0], [1.0, float("nan")], [1.0, float("inf")]):
+        with pytest.raises(SamplingError):
+            s.sample(bad)
+    for cfg, vocab in ((SamplingConfig.seeded(1), 0),
+                       (SamplingConfig.seeded(1).with_temperature(0.0), 4),
+                       (SamplingConfig.seeded(1).with_temperature(float("nan")), 4),
+                       (SamplingConfig.seeded(1).with_top_k(0), 4),
+                       (SamplingConfig.seeded(1).with_top_k(5), 4),
+                       (SamplingConfig.seeded(1).with_top_p(0.0), 4),
+                       (SamplingConfig.seeded(1).with_top_p(1.1), 4),
+                       (SamplingConfig.seeded(-1), 4)):
+        with pytest.raises(SamplingError):
+            cfg.validate(vocab)
+
+
+def test_host_sampler_equals_the_plain_sampler():
+    rng = np.random.default_rng(0)
+    for seed, t, k, p in ((1, 1.0, None, None), (2, 0.7, 5, None), (3, 1.3, None, 0.8),
+                          (4, 0.5, 12, 0.6), (5, 2.0, 40, 0.99)):
+        cfg = SamplingConfig(seed=seed, temperature=t, top_k=k, top_p=p)
+        ours, theirs = HostLogitSampler(cfg, 40), P.PlainSplitMix64(seed)
+        for _ in range(50):
+            logits = rng.normal(size=40).astype(np.float32)
+            logits[rng.integers(40)] = logits[rng.integers(40)]  # a tie now and then
+            assert ours.sample(logits) == P.plain_sample(logits, theirs, t, k, p)
+
+
+# ---------------------------------------------------------------------------
+def test_cli_rules():
+    a = parse_args(["generate", "--model", "m", "--tokenizer", "t", "--prompt", "hi"])
+    assert (a.device_ordinal, a.max_new_tokens, a.sample) == (0, 16, False)
+    a = parse_args(["generate", "--model", "m", "--prompt-ids", "1,2,3", "--sample", "--seed", "5",
+                    "--temperature", "0.5", "--top-k", "3", "--top-p", "0.9", "--stream",
+                    "--max-new-tokens", "4", "--device", "1", "--dtype", "float32"])
+    assert a.prompt_ids == [[1, 2, 3]] and a.seeds == [5] and a.stream and a.dtype == "float32"
+    assert parse_args(["--help"]) is None
+    bad = [
+        ["generate", "--model", "m", "--prompt-ids", "1", "--seed", "5"],          # needs --sample
+        ["generate", "--model", "m", "--prompt-ids", "1", "--temperature", "1"],
+        ["generate", "--model", "m", "--prompt-ids", "1", "--stream"],
+        ["generate", "--model", "m", "--prompt-ids", "1", "--sample"],               # needs --seed
+        ["generate", "--model", "m", "--prompt", "hi"],                              # tokenizer
+        ["generate", "--prompt-ids", "1"],                                           # model
+        ["generate", "--model", "m"],                                                # prompt
+        ["generate", "--model", "m", "--prompt-ids", "1", "--max-new-tokens", "0"],
+        ["generate", "--model", "m", "--prompt-ids", "1", "--device", "-1"],
+        ["generate", "--model", "m", "--prompt-ids", "1", "--sample", "--seed", "1", "--top-p", "1.5"],
+        ["generate", "--model", "m", "--prompt-ids", "1", "--sample", "--seed", "1", "--temperature", "0"],
+        ["generate", "--model", "m", "--prompt-ids", "1", "--bogus", "1"],
+        ["generate", "--model", "m", "--prompt-ids", "1", "--model", "n"],
+        ["generate-batch", "--model", "m", "--prompt-ids", "1", "--prompt-ids", "2", "--seed", "1"],
+        ["generate-batch", "--model", "m", "--prompt-ids", "1", "--seed", "1", "--sample"],
+        ["frobnicate"],
+    ]
+    for argv in bad:
+        with pytest.raises(UsageError):
+            parse_args(argv)
+    a = parse_args(["generate-batch", "--model", "m", "--prompt-ids", "1", "--prompt-ids", "2,3",
+                    "--seed", "1", "--seed", "2", "--json"])
+    assert a.seeds == [1, 2] and a.json and a.sample and len(a.prompt_ids) == 2

@@ -1,0 +1,292 @@
+"""Each CUDA kernel alone against a plain float64 reference, at sizes other
+than the engine's: widths and vocabularies that are no power of two, head sizes
+in steps of 16, odd numbers of heads and groups, windows, split key ranges."""
+import math
+import random
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def tol(dtype):
+    return dict(rtol=2e-5, atol=2e-5) if dtype == "float32" else dict(rtol=1.6e-2, atol=1e-2)
+
+
+def close(got, want, dtype, what=""):
+    got, want = got.double().cpu(), want.double().cpu()
+    t = tol(dtype)
+    ok = torch.isclose(got, want, **t)
+    assert ok.all(), (f"{what}: {int((~ok).sum())} of {ok.numel()} differ, max abs "
+                      f"{float((got - want).abs().max()):.3e}")
+
+
+def ops():
+    from nnis_b200.csrc import ops as o
+    return o
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+def test_embed_and_bad_ids(dtype):
+    o = ops()
+    table = torch.randn(301, 70).to(DT[dtype])
+    tokens = torch.tensor([0, 300, 5, 17, 17], dtype=torch.int32)
+    hidden = torch.empty(5, 70, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    o.embed(table.to(DEV), tokens.to(DEV), hidden, status)
+    assert torch.equal(hidden.cpu(), P.embed(table, tokens.tolist()).float())
+    assert int(status.item()) == 0
+    o.embed(table.to(DEV), torch.tensor([3, 301, -1, 4, 2], dtype=torch.int32, device=DEV), hidden,
+            status)
+    assert int(status.item()) == 1
+    assert float(hidden[1].abs().sum()) == 0 and float(hidden[2].abs().sum()) == 0
+    assert torch.equal(hidden[0].cpu(), table[3].float())
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+@pytest.mark.parametrize("width", [16, 100, 576, 2050])
+def test_rmsnorm(dtype, width):
+    o = ops()
+    x = torch.randn(9, width) * 3
+    w = 1 + 0.1 * torch.randn(width)
+    out = torch.empty(9, width, dtype=DT[dtype], device=DEV)
+    o.rmsnorm(x.to(DEV), w.to(DEV), 1e-5, out)
+    close(out, P.rms_norm(x, w, 1e-5), dtype, "rmsnorm")
+    rows = torch.tensor([8, 0, 3], dtype=torch.int32)
+    out2 = torch.empty(3, width, dtype=DT[dtype], device=DEV)
+    o.rmsnorm(x.to(DEV), w.to(DEV), 1e-5, out2, rows.to(DEV))
+    assert torch.equal(out2, out[rows.long().to(DEV)])
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+def test_silu_mul(dtype):
+    o = ops()
+    gu = torch.randn(7, 2 * 45) * 4
+    out = torch.empty(7, 45, dtype=DT[dtype], device=DEV)
+    o.silu_mul(gu.to(DEV), out)
+    close(out, P.swiglu(gu[:, :45], gu[:, 45:]), dtype, "silu_mul")
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+@pytest.mark.parametrize("m", [1, 2, 3, 7, 16, 17, 100])
+@pytest.mark.parametrize("n,k", [(5, 16), (64, 30), (130, 100), (257, 576)])
+def test_gemm_simt(dtype, m, n, k):
+    o = ops()
+    g = torch.Generator().manual_seed(m * 1000 + n + k)
+    a = torch.randn(m, k, generator=g).to(DT[dtype])
+    w = (torch.randn(n, k, generator=g) / math.sqrt(k)).to(DT[dtype])
+    bias = torch.randn(n, generator=g)
+    want = P.linear(a, w, bias)
+    for mode, out_dtype in ((o.STORE, DT[dtype]), (o.STORE_F32, torch.float32)):
+        out = torch.empty(m, n, dtype=out_dtype, device=DEV)
+        o.gemm_simt(a.to(DEV), w.to(DEV), bias.to(DEV), out, mode)
+        close(out, want, dtype if mode == o.STORE else "float32", f"gemm mode {mode}")
+    base = torch.randn(m, n, generator=g)
+    acc = base.to(DEV).clone()
+    o.gemm_simt(a.to(DEV), w.to(DEV), None, acc, o.ADD_F32)
+    close(acc, base.double() + P.linear(a, w), "float32", "gemm add")
+
+
+class PagedCase:
+    """Sequences of unequal length in a paged cache whose pages are shuffled."""
+
+    def __init__(self, lengths, new_counts, nq, nkv, d, dtype, seed=0, page=64, scale=1.0):
+        rng = random.Random(seed)
+        g = torch.Generator().manual_seed(seed)
+        self.nq, self.nkv, self.d, self.page = nq, nkv, d, page
+        self.lengths, self.new = lengths, new_counts
+        n_pages = sum(-(-L // page) for L in lengths) + 3
+        ids = list(range(n_pages))
+        rng.shuffle(ids)
+        cols = max(-(-L // page) for L in lengths)
+        self.table = torch.full((len(lengths), cols), -1, dtype=torch.int32)
+        self.q = [torch.randn(L, nq, d, generator=g) * scale for L in lengths]
+        self.k = [torch.randn(L, nkv, d, generator=g) * scale for L in lengths]
+        self.v = [torch.randn(L, nkv, d, generator=g) for L in lengths]
+        if dtype == "bfloat16":
+            self.q = [x.bfloat16().float() for x in self.q]
+            self.k = [x.bfloat16().float() for x in self.k]
+            self.v = [x.bfloat16().float() for x in self.v]
+        # stale contents everywhere: a reused page is never clean
+        self.k_cache = torch.randn(n_pages, nkv, page, d, generator=g) * 50
+        self.v_cache = torch.randn(n_pages, nkv, page, d, generator=g) * 50
+        for s, L in enumerate(lengths):
+            for j in range(-(-L // page)):
+                self.table[s, j] = ids.pop()
+
+    def fill_cache(self, upto_new=True):
+        """Write keys/values of the positions that precede this step's tokens."""
+        for s, L in enumerate(self.lengths):
+            old = L - self.new[s]
+            for t in range(old):
+                pg = int(self.table[s, t // self.page])
+                self.k_cache[pg, :, t % self.page] = self.k[s][t]
+                self.v_cache[pg, :, t % self.page] = self.v[s][t]
+
+    def packed(self):
+        pos, seq, rows_q, rows_k, rows_v = [], [], [], [], []
+        for s, L in enumerate(self.lengths):
+            for t in range(L - self.new[s], L):
+                pos.append(t)
+                seq.append(s)
+                rows_q.append(self.q[s][t])
+                rows_k.append(self.k[s][t])
+                rows_v.append(self.v[s][t])
+        return (torch.tensor(pos, dtype=torch.int32), torch.tensor(seq, dtype=torch.int32),
+                torch.stack(rows_q), torch.stack(rows_k), torch.stack(rows_v))
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+@pytest.mark.parametrize("nq,nkv,d", [(6, 2, 16), (5, 5, 48), (4, 1, 80), (3, 3, 128), (2, 1, 256)])
+@pytest.mark.parametrize("window", [0, 37])
+def test_rope_store_then_attention(dtype, nq, nkv, d, window):
+    """Prompt chunks and single tokens in one packed batch: rotate, store, attend."""
+    o = ops()
+    lengths, new = [70, 1, 130, 64, 200], [70, 1, 5, 1, 1]
+    case = PagedCase(lengths, new, nq, nkv, d, dtype, seed=d + nq)
+    cos, sin = P.rope_tables(256, d, 10000.0)
+    # the cache holds rotated keys of earlier positions
+    rot_k = [P.rope_rotate_half(k, cos[:L], sin[:L]).float() for k, L in zip(case.k, lengths)]
+    rot_q = [P.rope_rotate_half(q, cos[:L], sin[:L]).float() for q, L in zip(case.q, lengths)]
+    if dtype == "bfloat16":
+        rot_k = [x.bfloat16().float() for x in rot_k]
+        rot_q = [x.bfloat16().float() for x in rot_q]
+    plain_k, case.k = case.k, rot_k
+    case.fill_cache()
+    case.k = plain_k
+    pos, seq, q, k, v = case.packed()
+    n = pos.numel()
+    qkv = torch.cat([q.reshape(n, -1), k.reshape(n, -1), v.reshape(n, -1)], 1).to(DT[dtype]).to(DEV)
+    kc, vc = case.k_cache.to(DT[dtype]).to(DEV), case.v_cache.to(DT[dtype]).to(DEV)
+    table = case.table.to(DEV)
+    o.rope_store(qkv, pos.to(DEV), seq.to(DEV), table, cos.float().to(DEV), sin.float().to(DEV), kc,
+                 vc, nq, nkv, d, 64)
+    # the rotated rows, in place and in the cache
+    want_q = torch.stack([rot_q[s][t] for t, s in zip(pos.tolist(), seq.tolist())]).reshape(n, -1)
+    close(qkv[:, :nq * d], want_q, dtype, "rotated q")
+    for i, (t, s) in enumerate(zip(pos.tolist(), seq.tolist())):
+        pg = int(case.table[s, t // 64])
+        close(kc[pg, :, t % 64], rot_k[s][t], dtype, "stored k")
+        assert torch.equal(vc[pg, :, t % 64].float().cpu(), case.v[s][t].to(DT[dtype]).float())
+    for splits in (1, 3):
+        out = torch.empty(n, nq * d, dtype=DT[dtype], device=DEV)
+        partial = torch.empty(n * nq * splits * (d + 2), device=DEV) if splits > 1 else None
+        o.attention_generic(qkv, qkv.shape[1], kc, vc, pos.to(DEV), seq.to(DEV), table, out, nq, nkv,
+                            d, window, 1.0 / math.sqrt(d), splits, partial)
+        i = 0
+        for s, L in enumerate(lengths):
+            full = P.causal_attention(rot_q[s], rot_k[s], case.v[s].to(DT[dtype]).float(), window)
+            want = full[L - new[s]:].reshape(new[s], -1)
+            close(out[i:i + new[s]], want, dtype, f"attention seq {s} splits {splits}")
+            i += new[s]
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+def test_attention_finds_one_far_key_and_respects_the_window_edge(dtype):
+    """One key far back is made to dominate; with a window that just excludes
+    it, it must vanish, and with one that just includes it, it must win."""
+    o = ops()
+    nq, nkv, d, L, far = 4, 2, 32, 500, 123
+    case = PagedCase([L], [1], nq, nkv, d, dtype, seed=3, scale=0.3)
+    case.k[0][far] = case.q[0][L - 1][::2] * 40.0  # kv head h serves query heads 2h, 2h+1
+    case.v[0][far] = 7.0
+    if dtype == "bfloat16":
+        case.k[0] = case.k[0].bfloat16().float()
+    case.fill_cache()
+    # the step's own token is written by hand here (no rotation in this test)
+    pg = int(case.table[0, (L - 1) // 64])
+    case.k_cache[pg, :, (L - 1) % 64] = case.k[0][L - 1]
+    case.v_cache[pg, :, (L - 1) % 64] = case.v[0][L - 1]
+    pos, seq, q, _, _ = case.packed()
+    qd = q.reshape(1, -1).to(DT[dtype]).to(DEV)
+    kc, vc = case.k_cache.to(DT[dtype]).to(DEV), case.v_cache.to(DT[dtype]).to(DEV)
+    for window, sees in ((0, True), (L - far, True), (L - far - 1, False)):
+        for splits in (1, 4):
+            out = torch.empty(1, nq * d, dtype=DT[dtype], device=DEV)
+            partial = torch.empty(nq * splits * (d + 2), device=DEV) if splits > 1 else None
+            o.attention_generic(qd, nq * d, kc, vc, pos.to(DEV), seq.to(DEV), case.table.to(DEV), out,
+                                nq, nkv, d, window, 1.0 / math.sqrt(d), splits, partial)
+            want = P.causal_attention(case.q[0], case.k[0], case.v[0].to(DT[dtype]).float(),
+                                      window)[L - 1:].reshape(1, -1)
+            close(out, want, dtype, f"far key window {window} splits {splits}")
+            even_heads = out.view(nq, d)[0::2].float()
+            assert bool((even_heads > 6.5).all()) == sees
+
+
+def test_padding_rows_store_nothing_and_come_out_zero():
+    o = ops()
+    nq, nkv, d = 2, 1, 16
+    kc = torch.zeros(2, nkv, 64, d, device=DEV)
+    vc = torch.zeros(2, nkv, 64, d, device=DEV)
+    qkv = torch.ones(3, (nq + 2 * nkv) * d, device=DEV)
+    pos = torch.tensor([0, -1, 1], dtype=torch.int32, device=DEV)
+    seq = torch.tensor([0, 0, 0], dtype=torch.int32, device=DEV)
+    table = torch.tensor([[1]], dtype=torch.int32, device=DEV)
+    o.rope_store(qkv, pos, seq, table, None, None, kc, vc, nq, nkv, d, 64)
+    assert float(kc[1, 0, :2].sum()) == 2 * d and float(kc.sum()) == 2 * d
+    out = torch.full((3, nq * d), 9.0, device=DEV)
+    o.attention_generic(qkv, qkv.shape[1], kc, vc, pos, seq, table, out, nq, nkv, d, 0, 0.25)
+    assert float(out[1].abs().sum()) == 0 and torch.allclose(out[0], torch.ones(nq * d, device=DEV))
+
+
+def test_sizes_the_kernels_do_not_take_are_refused():
+    o = ops()
+    kc = torch.zeros(1, 1, 64, 24, device=DEV)
+    q = torch.zeros(1, 24, device=DEV)
+    i = torch.zeros(1, dtype=torch.int32, device=DEV)
+    with pytest.raises(o.KernelError, match="multiple of 16"):
+        o.attention_generic(q, 24, kc, kc, i, i, i.view(1, 1), q.clone(), 1, 1, 24, 0, 1.0)
+    with pytest.raises(o.KernelError):
+        o.gemm_simt(torch.zeros(2, 4), torch.zeros(2, 4), None, torch.zeros(2, 2), 0)  # CPU tensors
+    with pytest.raises(o.KernelError):
+        o.rmsnorm(torch.zeros(2, 4, device=DEV), torch.zeros(5, device=DEV), 1e-5,
+                  torch.zeros(2, 4, device=DEV))
+
+
+def test_argmax_takes_the_lowest_index_among_equals():
+    o = ops()
+    rng = np.random.default_rng(0)
+    logits = rng.normal(size=(6, 49157)).astype(np.float32)
+    logits[0, [77, 40000]] = 9.0
+    logits[1, :] = 0.0
+    logits[2, 49156] = 12.0
+    logits[3, :] = -np.inf
+    logits[3, 5] = -1e30
+    out = torch.empty(6, dtype=torch.int32, device=DEV)
+    o.argmax(torch.from_numpy(logits).to(DEV), out)
+    want = [P.argmax_lowest(torch.from_numpy(r)) for r in logits]
+    assert out.tolist() == want and want[:4] == [77, 0, 49156, 5]
+
+
+def test_temperature_sampling_follows_the_seeded_draws():
+    """Inverse CDF in id order with SplitMix64 draws, checked against a float64
+    reference; the chosen id's interval must contain the draw."""
+    o = ops()
+    from nnis_b200.sampling.device import seed_states
+    rng = np.random.default_rng(1)
+    vocab, rows = 1003, 5
+    logits = (rng.normal(size=(rows, vocab)) * 3).astype(np.float32)
+    temps = np.array([1.0, 0.5, 2.0, 0.05, 1.3], dtype=np.float32)
+    seeds = [42, 7, 2 ** 63 + 5, 0, 99]
+    state = seed_states(seeds, DEV)
+    plains = [P.PlainSplitMix64(s) for s in seeds]
+    dl, dt = torch.from_numpy(logits).to(DEV), torch.from_numpy(temps).to(DEV)
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    counts = np.zeros(vocab)
+    for _ in range(200):
+        o.sample_temperature(dl, dt, state, out)
+        got = out.tolist()
+        for r in range(rows):
+            u = plains[r].next_unit()
+            w = np.exp((logits[r].astype(np.float64) - logits[r].max()) / float(temps[r]))
+            cdf = np.cumsum(w)
+            want = int(np.searchsorted(cdf, u * cdf[-1], side="right"))
+            assert abs(got[r] - want) <= 0 or abs(cdf[got[r]] - u * cdf[-1]) < 1e-9 * cdf[-1]
+        counts[got[0]] += 1
+    assert counts.argmax() == logits[0].argmax() or counts.max() < 20
