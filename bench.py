@@ -1,0 +1,276 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the SmolLM2-135M shape on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one decode step of a batch of 8 sequences whose context ends at 4,096
+tokens (prompt 2,048 + 2,048 decoded); ``value`` is decoded tokens per second,
+timed with CUDA events over K graph launches.  ``e2e`` is the same through the
+Python entry point with every step's tokens coming from and going back to the
+host.  The line also carries a 2,048-token prefill, the decode step's HBM
+roofline, and decoding at batch 1 and 64.  Weights are random (seeded), token
+ids are uniform random: no checkpoint or dataset is read.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import random
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# The shape of SmolLM2-135M (BASELINE.json configs[2]); nothing below the
+# configuration knows these numbers.
+SMOLLM2_135M = dict(
+    architectures=["LlamaForCausalLM"], model_type="llama", vocab_size=49152, hidden_size=576,
+    intermediate_size=1536, num_hidden_layers=30, num_attention_heads=9, num_key_value_heads=3,
+    max_position_embeddings=8192, rms_norm_eps=1e-5, rope_theta=100000.0, hidden_act="silu",
+    tie_word_embeddings=True, attention_bias=False, torch_dtype="bfloat16")
+CONTEXT = 4096
+PROMPT = 2048
+BATCH = 8
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            raw = json.load(f)
+        return {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"]),
+                "source": "measured"}
+    except (OSError, KeyError, ValueError, TypeError):
+        return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples, self.proc = [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append((time.time(), [x.strip() for x in line.split(",")]))
+
+    def mark(self):
+        return time.time()
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+
+    def summary(self, windows):
+        rows = [s for t, s in self.samples if any(a <= t <= b for a, b in windows)] or \
+               [s for _, s in self.samples]
+        sm = sorted(int(r[0]) for r in rows if r[0].isdigit())
+        mx = [int(r[1]) for r in rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i] == "Active"
+                                                         for r in rows)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(rows)}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has")
+    ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "Memorithm/NNIS is a Rust workspace (cargo, NVRTC); pip cannot install it "
+                          "and no Rust toolchain is present"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+
+    from nnis_b200 import LLM
+    from nnis_b200.csrc import ops
+    from nnis_b200.engine import SequenceStep
+    from nnis_b200.engine.decode import GraphDecoder
+    from nnis_b200.weights import write_random_model
+
+    pk = peaks()
+    cfg = dict(SMOLLM2_135M)
+    full_layers = cfg["num_hidden_layers"]
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    rng = random.Random(0)
+    vocab = cfg["vocab_size"]
+    K, W = args.steps, args.warmup
+    clocks = ClockSampler()
+    windows = []
+
+    with tempfile.TemporaryDirectory() as tmp:
+        write_random_model(cfg, seed=0, out_dir=tmp, std=1.0, norm_std=0.1, std_by_fan_in=True)
+        llm = LLM(tmp, dtype="bfloat16", device_ordinal=0, max_tokens=64 * (CONTEXT + 64),
+                  max_batch=64, pipeline_decode=False)
+        engine = llm.engine
+        spec = engine.spec
+        mixer = engine.model.blocks[0].mixer
+        kv_bytes_per_token = 2 * len(spec.schedule) * mixer.kv_heads * mixer.head_dim * 2
+        weight_bytes = engine.model.parameter_bytes()
+        clocks.start()
+
+        def timed(fn, n):
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            t0 = clocks.mark()
+            start.record()
+            for _ in range(n):
+                fn()
+            end.record()
+            torch.cuda.synchronize()
+            windows.append((t0, clocks.mark()))
+            return start.elapsed_time(end)
+
+        def decode_point(batch, steps, warmup):
+            """Device-timed decode: the contexts end at CONTEXT after the timed steps."""
+            begin = CONTEXT - steps - warmup
+            slots = [engine.acquire_slot() for _ in range(batch)]
+            fed = 0
+            while fed < begin:  # fill the cache in chunks of at most 2,048 tokens per sequence
+                n = min(PROMPT, begin - fed)
+                per_step = max(1, 16384 // n)
+                for i in range(0, batch, per_step):
+                    engine.step([SequenceStep(s, [rng.randrange(vocab) for _ in range(n)], [])
+                                 for s in slots[i:i + per_step]])
+                fed += n
+            dec = GraphDecoder(engine, batch, CONTEXT)
+            engine.cache.reserve(slots, [CONTEXT] * batch)
+            for r, s in enumerate(slots):
+                dec.set_row(r, s, rng.randrange(vocab), begin)
+            dec.capture()
+            for _ in range(warmup):
+                dec.launch()
+            before = ops.launch_count()
+            ms = timed(dec.launch, steps)
+            launches = dec.launches_per_step * steps + (ops.launch_count() - before)
+            engine.cache.commit(slots, [CONTEXT] * batch)
+            for s in slots:
+                engine.release_slot(s)
+            mean_context = CONTEXT - (steps + 1) / 2.0
+            step_bytes = weight_bytes + batch * mean_context * kv_bytes_per_token
+            return {"tok_s": batch * steps / (ms * 1e-3), "ms_per_step": ms / steps,
+                    "launches": launches, "bytes_per_step": step_bytes,
+                    "gbs": step_bytes / (ms / steps * 1e-3) / 1e9}
+
+        main_point = decode_point(BATCH, K, W)
+
+        # -- prefill of 2,048 tokens ------------------------------------------------
+        prompt = [rng.randrange(vocab) for _ in range(PROMPT)]
+
+        def prefill_once():
+            slot = engine.acquire_slot()
+            engine.step([SequenceStep(slot, prompt, [PROMPT - 1])])
+            engine.release_slot(slot)
+
+        for _ in range(3):
+            prefill_once()
+        reps = 5
+        prefill_ms = timed(prefill_once, reps) / reps
+        H, I = cfg["hidden_size"], cfg["intermediate_size"]
+        d, nq, nkv = mixer.head_dim, mixer.heads, mixer.kv_heads
+        per_layer = 2 * PROMPT * (H * (nq + 2 * nkv) * d + nq * d * H + 3 * H * I) \
+            + 4 * nq * d * PROMPT * (PROMPT + 1) / 2
+        prefill_flops = len(spec.schedule) * per_layer + 2 * H * vocab
+        prefill = {"value": PROMPT / (prefill_ms * 1e-3), "tokens": PROMPT, "ms": prefill_ms,
+                   "frac": prefill_flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)}
+
+        # -- end to end: host tokens in and out every step -----------------------------
+        e2e_new = min(K, 256) + 1
+        prompts = [[rng.randrange(vocab) for _ in range(CONTEXT - e2e_new)] for _ in range(BATCH)]
+        llm.generate([p[:64] for p in prompts], max_new_tokens=4, stop_token_ids=())
+        llm.backend._decoder(BATCH, CONTEXT, False).capture()  # the graph the timed run will launch
+        stamps = []
+        h2d0, d2h0 = llm.backend.h2d_bytes + engine.h2d_bytes, llm.backend.d2h_bytes
+        first_done = {}
+
+        def on_token(i, t):
+            if i not in first_done:
+                first_done[i] = True
+                if len(first_done) == BATCH:
+                    torch.cuda.synchronize()
+                    stamps.append((time.perf_counter(), llm.backend.h2d_bytes + engine.h2d_bytes,
+                                   llm.backend.d2h_bytes))
+        t0 = clocks.mark()
+        results = llm.generate(prompts, max_new_tokens=e2e_new, stop_token_ids=(), on_token=on_token)
+        torch.cuda.synchronize()
+        t_end = time.perf_counter()
+        windows.append((t0, clocks.mark()))
+        assert all(r.ok and len(r.token_ids) == e2e_new for r in results), \
+            [r.error for r in results if not r.ok]
+        t_first, h2d1, d2h1 = stamps[0]
+        e2e_steps = e2e_new - 1
+        e2e = {"value": BATCH * e2e_steps / (t_end - t_first), "unit": "tokens/s",
+               "h2d_bytes_per_step": (llm.backend.h2d_bytes + engine.h2d_bytes - h2d1) // e2e_steps,
+               "d2h_bytes_per_step": (llm.backend.d2h_bytes - d2h1) // e2e_steps,
+               "steps": e2e_steps}
+
+        points = {}
+        if not args.skip_points:
+            p1 = decode_point(1, min(K, 256), W)
+            p64 = decode_point(64, min(K, 64), W)
+            points = {"decode_b1": p1["tok_s"], "decode_b64": p64["tok_s"],
+                      "decode_b1_hbm_frac": p1["gbs"] / pk["hbm_gbs"],
+                      "decode_b64_hbm_frac": p64["gbs"] / pk["hbm_gbs"]}
+        clocks.stop()
+
+    line = {
+        "metric": "decode tok/s @ batch 8, context 4096 (SmolLM2-135M bf16)",
+        "value": main_point["tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": main_point["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded random weights and token ids)",
+        "impl": "ours",
+        "config": {"model": "SmolLM2-135M shape", "global_batch": BATCH, "seq_len": CONTEXT,
+                   "parallelism": "single GPU", "prompt_len": PROMPT, "layers": cfg["num_hidden_layers"],
+                   "layers_of_shape": full_layers, "hidden_size": cfg["hidden_size"],
+                   "intermediate_size": cfg["intermediate_size"], "heads": cfg["num_attention_heads"],
+                   "kv_heads": cfg["num_key_value_heads"], "head_dim": mixer.head_dim,
+                   "vocab_size": vocab, "rope_theta": cfg["rope_theta"],
+                   "rms_norm_eps": cfg["rms_norm_eps"], "tied_embeddings": True,
+                   "cache_page_tokens": 64, "l2": "inputs larger than L2 (weights + KV per step)",
+                   "peaks": pk["source"]},
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": main_point["gbs"], "peak": pk["hbm_gbs"],
+                     "unit": "GB/s", "frac": main_point["gbs"] / pk["hbm_gbs"]},
+        "points": points,
+        "e2e": e2e,
+        "gpu_launches": main_point["launches"],
+        "clocks": clocks.summary(windows),
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

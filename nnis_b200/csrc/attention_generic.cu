@@ -168,6 +168,14 @@ static int launch_attention(const void* q, int q_stride, const void* k_cache, co
 
 }  // namespace nnis
 
+// The merge alone, for kernels that write the same partial records.
+extern "C" int nnis_attention_merge_bf16(const float* partial, void* out, long long n_rows, int d,
+                                         int n_splits, cudaStream_t stream) {
+    nnis::attn_merge_kernel<nnis::bf16><<<(unsigned)((n_rows + 3) / 4), 128, 0, stream>>>(
+        partial, (nnis::bf16*)out, (size_t)n_rows, d, n_splits);
+    NNIS_RETURN_LAUNCH();
+}
+
 // Scratch: `partial` needs n_tokens * nq * n_splits * (d + 2) floats when
 // n_splits > 1 and may be null otherwise.
 NNIS_API int nnis_attention_generic(const void* q, int q_stride, const void* k_cache,

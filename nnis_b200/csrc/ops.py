@@ -24,12 +24,22 @@ class KernelError(RuntimeError):
     pass
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels of this library launched (or captured) so far in this process."""
+    return _launches
+
+
 def _lib() -> ctypes.CDLL:
     return _build.load()
 
 
-def _check(code: int, what: str) -> None:
+def _check(code: int, what: str, kernels: int = 1) -> None:
+    global _launches
     if code == 0:
+        _launches += kernels
         return
     if code < 0:
         raise KernelError(f"{what}: {_ARG_ERRORS.get(code, 'error')} (code {code})")
@@ -171,7 +181,7 @@ def attention_generic(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_c
         _ptr(q), q_stride, _ptr(k_cache), _ptr(v_cache), _ptr(token_pos), _ptr(token_seq),
         _ptr(page_table), page_table.shape[1], _ptr(out), _ptr(partial), n, heads, kv_heads, head_dim,
         page_size, window, ctypes.c_float(scale), n_splits, code_of(out.dtype), _stream()),
-        "attention_generic")
+        "attention_generic", 2 if n_splits > 1 else 1)
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
@@ -194,6 +204,169 @@ def sample_temperature(logits: torch.Tensor, temperature: torch.Tensor, rng_stat
                                           _ptr(out), n, vocab, _stream()), "sample_temperature")
 
 
+EPI_STORE, EPI_STORE_F32, EPI_ADD_F32, EPI_GATED, EPI_QKV, EPI_ARGMAX = 0, 1, 2, 3, 4, 5
+# programmatic dependent launch between the decode kernels (NNIS_PDL=0 turns it off)
+PDL = 0 if __import__("os").environ.get("NNIS_PDL", "1") == "0" else 1
+_status = {}
+
+
+def status_word(device) -> torch.Tensor:
+    """One int32 per device that kernels set when a bounded wait runs out."""
+    key = torch.device(device).index or 0
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def check_status(device) -> None:
+    """Raise if a kernel gave up a wait since the last check (synchronises)."""
+    word = status_word(device)
+    if int(word.item()) != 0:
+        word.zero_()
+        raise KernelError("a kernel gave up waiting for an asynchronous copy; results are invalid")
+
+
+def gemv_grid(m: int, n: int, k: int, device) -> int:
+    return int(_lib().nnis_gemv_grid(m, n, k, sm_count(device)))
+_sm_count = {}
+
+
+def sm_count(device) -> int:
+    key = torch.device(device).index or 0
+    if key not in _sm_count:
+        _sm_count[key] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _sm_count[key]
+
+
+def gemv_takes(m: int, n: int, k: int, epilogue: int = EPI_STORE) -> bool:
+    """Whether the decode projection kernel runs this shape (else the general kernels)."""
+    mt = 1 if m <= 1 else 2 if m <= 2 else 4 if m <= 4 else 8 if m <= 8 else 16
+    return m <= 16 and k % 8 == 0 and n % (8 if epilogue == EPI_GATED else 4) == 0 \
+        and (mt + 32) * k * 2 + 64 <= 200 * 1024
+
+
+def gemv_bf16(w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, epilogue: int,
+              x: Optional[torch.Tensor] = None, hidden: Optional[torch.Tensor] = None,
+              norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0,
+              rows: Optional[torch.Tensor] = None, m: Optional[int] = None,
+              token_pos: Optional[torch.Tensor] = None, token_seq: Optional[torch.Tensor] = None,
+              page_table: Optional[torch.Tensor] = None, cos: Optional[torch.Tensor] = None,
+              sin: Optional[torch.Tensor] = None, k_cache: Optional[torch.Tensor] = None,
+              v_cache: Optional[torch.Tensor] = None, heads: int = 0, kv_heads: int = 0,
+              head_dim: int = 0, page_size: int = 0, partial: Optional[torch.Tensor] = None,
+              splits: int = 0, logits: Optional[torch.Tensor] = None,
+              scratch: Optional[torch.Tensor] = None, next_tokens: Optional[torch.Tensor] = None,
+              next_pos: Optional[torch.Tensor] = None) -> None:
+    """A decode-step projection with its prologue and epilogue fused (at most 16
+    rows).  The input is ``x`` (bfloat16 [m, k]), or ``hidden`` (float32 residual
+    rows, normed with ``norm_weight``/``eps`` on the way in; ``rows`` picks them),
+    or ``partial`` (split-KV records of the decode attention kernel, merged on the
+    way in; ``heads``/``head_dim``/``splits`` describe them).  EPI_ARGMAX writes
+    int32 picks to ``out``; ``scratch`` (int32, ``argmax_scratch_ints``) is its
+    workspace, ``logits`` optional, ``next_tokens``/``next_pos`` the decode state."""
+    _cuda(w, bias, out, x, hidden, norm_weight, rows, token_pos, token_seq, page_table, cos, sin,
+          k_cache, v_cache, partial, logits, scratch, next_tokens, next_pos)
+    n, k = w.shape
+    _need(w.dtype == torch.bfloat16, "gemv: bfloat16 weights")
+    if hidden is not None:
+        _need(hidden.dtype == torch.float32 and hidden.shape[1] == k, "gemv: hidden float32 [*, k]")
+        _need(norm_weight is not None and norm_weight.dtype == torch.float32
+              and norm_weight.numel() == k, "gemv: norm weight float32 [k]")
+        rows_m = rows.numel() if rows is not None else hidden.shape[0]
+        m = rows_m if m is None else m
+        if rows is not None:
+            _need(rows.dtype == torch.int32, "gemv: rows int32")
+    elif partial is not None:
+        _need(partial.dtype == torch.float32 and m is not None and heads * head_dim == k
+              and 0 < splits <= 64 and partial.numel() >= m * heads * splits * (head_dim + 2),
+              "gemv: partial float32 [m * heads, splits, d + 2]")
+    else:
+        _need(x is not None and x.dtype == torch.bfloat16 and x.shape[1] == k, "gemv: x bfloat16 [m, k]")
+        m = x.shape[0] if m is None else m
+    _need(gemv_takes(m, n, k, epilogue), f"gemv: shape m={m} n={n} k={k} is not taken")
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() == n, "gemv: bias float32 [n]")
+    if epilogue == EPI_STORE:
+        _need(out.dtype == torch.bfloat16 and tuple(out.shape) == (m, n), "gemv: out bfloat16 [m, n]")
+    elif epilogue in (EPI_STORE_F32, EPI_ADD_F32):
+        _need(out.dtype == torch.float32 and tuple(out.shape) == (m, n), "gemv: out float32 [m, n]")
+    elif epilogue == EPI_GATED:
+        _need(out.dtype == torch.bfloat16 and tuple(out.shape) == (m, n // 2),
+              "gemv: out bfloat16 [m, n / 2]")
+    elif epilogue == EPI_QKV:
+        _need(n == (heads + 2 * kv_heads) * head_dim and head_dim % 16 == 0, "gemv: qkv rows")
+        _need(out.dtype == torch.bfloat16 and tuple(out.shape) == (m, heads * head_dim),
+              "gemv: q out bfloat16 [m, heads * d]")
+        _need(token_pos is not None and token_pos.dtype == torch.int32 and token_pos.numel() >= m,
+              "gemv: token_pos int32 [m]")
+        if kv_heads > 0:
+            _need(k_cache is not None and k_cache.dtype == torch.bfloat16
+                  and tuple(k_cache.shape[1:]) == (kv_heads, page_size, head_dim)
+                  and page_table is not None and token_seq is not None, "gemv: cache [pages, kv, page, d]")
+        if cos is not None:
+            _need(cos.dtype == torch.float32 and cos.shape[1] == head_dim // 2, "gemv: cos/sin tables")
+    elif epilogue == EPI_ARGMAX:
+        _need(out.dtype == torch.int32 and out.numel() >= m, "gemv: picks int32 [m]")
+        _need(scratch is not None and scratch.dtype == torch.int32
+              and scratch.numel() >= argmax_scratch_ints(m, n, k, w.device), "gemv: argmax scratch")
+        if logits is not None:
+            _need(logits.dtype == torch.float32 and tuple(logits.shape) == (m, n), "gemv: logits [m, n]")
+        if next_tokens is not None:
+            _need(next_pos is not None and next_tokens.dtype == next_pos.dtype == torch.int32
+                  and next_tokens.numel() >= m and next_pos.numel() >= m, "gemv: decode state int32")
+    else:
+        raise KernelError(f"gemv: unknown epilogue {epilogue}")
+    cols = page_table.shape[1] if page_table is not None else 0
+    best_val = best_idx = ticket = 0
+    if epilogue == EPI_ARGMAX:
+        grid = gemv_grid(m, n, k, w.device)
+        base = scratch.data_ptr()
+        ticket, best_val, best_idx = base, base + 16, base + 16 + 4 * m * grid
+    _check(_lib().nnis_gemv_bf16(
+        _ptr(x), _ptr(hidden), _ptr(rows), _ptr(norm_weight), ctypes.c_float(eps), _ptr(partial),
+        splits, _ptr(w), _ptr(bias), _ptr(out), m, n, k, epilogue, _ptr(token_pos), _ptr(token_seq),
+        _ptr(page_table), cols, _ptr(cos), _ptr(sin), _ptr(k_cache), _ptr(v_cache), heads, kv_heads,
+        head_dim, page_size, _ptr(logits), ctypes.c_void_p(best_val), ctypes.c_void_p(best_idx),
+        ctypes.c_void_p(ticket), _ptr(next_tokens), _ptr(next_pos), _ptr(status_word(w.device)),
+        sm_count(w.device), PDL, _stream()), "gemv_bf16")
+
+
+def argmax_scratch_ints(m: int, n: int, k: int, device) -> int:
+    """int32 words of scratch for EPI_ARGMAX: a ticket, then per-CTA bests.  The
+    buffer must be zero before its first use (the kernel re-zeroes the ticket)."""
+    return 4 + 2 * m * gemv_grid(m, n, k, device)
+
+
+def attention_decode(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                     token_pos: torch.Tensor, token_seq: torch.Tensor, page_table: torch.Tensor,
+                     out: torch.Tensor, heads: int, kv_heads: int, head_dim: int, window: int,
+                     scale: float, n_splits: int = 1, partial: Optional[torch.Tensor] = None,
+                     merge: bool = True) -> None:
+    """One query token per sequence over the paged bfloat16 cache.  With
+    ``merge=False`` and several splits, ``partial`` is left for the consumer."""
+    _cuda(k_cache, v_cache, token_pos, token_seq, page_table, out, partial)
+    _need(q.is_cuda and q.dtype == torch.bfloat16 == k_cache.dtype == out.dtype,
+          "attention_decode: bfloat16 tensors")
+    n = out.shape[0]
+    pages, nkv, page_size, d = k_cache.shape
+    _need(nkv == kv_heads and d == head_dim, "cache shape differs from the heads given")
+    _need(head_dim % 16 == 0 and 16 <= head_dim <= 256,
+          f"attention: head_dim {head_dim} is not a multiple of 16 in 16..256")
+    _need(heads % kv_heads == 0, "attention: heads is not a multiple of kv_heads")
+    _need(pages * nkv * page_size < 2 ** 31, "attention: the cache has too many rows")
+    _need(out.shape[1] == heads * head_dim and n <= 65535, "attention_decode: out [n <= 65535, heads * d]")
+    if n_splits > 1:
+        _need(partial is not None and partial.dtype == torch.float32
+              and partial.numel() >= n * heads * n_splits * (head_dim + 2),
+              "attention: partial scratch too small")
+    _check(_lib().nnis_attention_decode(
+        _ptr(q), q_stride, _ptr(k_cache), _ptr(v_cache), _ptr(token_pos), _ptr(token_seq),
+        _ptr(page_table), page_table.shape[1], _ptr(out), _ptr(partial), n, heads, kv_heads, head_dim,
+        page_size, window, ctypes.c_float(scale), n_splits, 1 if merge else 0,
+        _ptr(status_word(out.device)), PDL, _stream()),
+        "attention_decode", 2 if n_splits > 1 and merge else 1)
+
+
 def gemm_tc_takes(m: int, n: int, k: int) -> bool:
     """Whether the tcgen05 kernel runs this bfloat16 product (else CUDA cores)."""
     return False
@@ -202,3 +375,12 @@ def gemm_tc_takes(m: int, n: int, k: int) -> bool:
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
             mode: int) -> None:
     raise KernelError("gemm_tc: not available")
+
+
+def advance(tokens: torch.Tensor, pos: torch.Tensor, picked: torch.Tensor) -> None:
+    """tokens = picked; pos += 1 on live rows (pos >= 0)."""
+    _cuda(tokens, pos, picked)
+    _need(tokens.dtype == pos.dtype == picked.dtype == torch.int32, "advance: int32")
+    n = tokens.numel()
+    _need(pos.numel() == n and picked.numel() >= n, "advance: sizes differ")
+    _check(_lib().nnis_advance(_ptr(tokens), _ptr(pos), _ptr(picked), n, _stream()), "advance")

@@ -106,7 +106,23 @@ sample_temperature_kernel(const float* __restrict__ logits, const float* __restr
     if (tid == 0) out[blockIdx.x] = pick_s;
 }
 
+// After a decode step on the device: the picked token becomes the next input
+// and live rows (position >= 0) move on by one.
+__global__ void advance_kernel(int* __restrict__ tokens, int* __restrict__ pos,
+                               const int* __restrict__ picked, int n) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n || pos[i] < 0) return;
+    tokens[i] = picked[i];
+    pos[i] += 1;
+}
+
 }  // namespace nnis
+
+NNIS_API int nnis_advance(int* tokens, int* pos, const int* picked, int n, cudaStream_t stream) {
+    if (n <= 0) return NNIS_ERR_ARGUMENT;
+    nnis::advance_kernel<<<(n + 127) / 128, 128, 0, stream>>>(tokens, pos, picked, n);
+    NNIS_RETURN_LAUNCH();
+}
 
 NNIS_API int nnis_argmax(const float* logits, int* out, int n_rows, int vocab, cudaStream_t stream) {
     if (n_rows <= 0 || vocab <= 0) return NNIS_ERR_ARGUMENT;

@@ -19,7 +19,9 @@ import torch
 
 from ..sampling import SamplingConfig
 from ..sampling import device as device_sampling
-from .engine import Engine, SequenceStep
+from ..cache import PAGE_SIZE
+from .decode import GraphDecoder
+from .engine import Engine, SequenceStep, StepError
 from .generate import (DEFAULT_MAX_NEW_TOKENS, GenerationConfig, GenerationRequest,
                        GenerationResult, Generator)
 
@@ -29,8 +31,21 @@ Prompt = Union[str, Sequence[int]]
 class EngineBackend:
     """What the generation loop needs of an engine."""
 
-    def __init__(self, engine: Engine):
+    def __init__(self, engine: Engine, max_rows: int = 64, pipeline: bool = True):
         self.engine = engine
+        self.max_rows = max_rows
+        # True: all-greedy batches keep tokens on the device and the host reads
+        # picks one step late.  False: every step's tokens come from the host.
+        self.pipeline = pipeline
+        self._decoders = {}
+        self._pinned = None
+        self._picked = None
+        self._picked_for = None
+        self.h2d_bytes = 0  # counted from the tensors copied, for measurements
+        self.d2h_bytes = 0
+        parts = [p for b in engine.model.blocks for p in b.parts()]
+        if not all(getattr(p, "device_only", True) for p in parts):
+            self.decode_greedy = None  # a part loops on the host: no graph
 
     def acquire_slot(self) -> int:
         return self.engine.acquire_slot()
@@ -38,12 +53,38 @@ class EngineBackend:
     def release_slot(self, slot: int) -> None:
         self.engine.release_slot(slot)
 
-    def step(self, batch):
-        return self.engine.step(batch)
+    def step(self, batch, need_logits: bool = True):
+        """Logits [len(batch) wanted rows, vocab] (or None when ``need_logits`` is
+        false and the step could pick on the device: ``greedy`` then has the
+        picks).  Steps in which every sequence brings one token and wants its
+        logits run as a CUDA graph whose inputs (tokens, positions, page tables)
+        come from the host in one copy."""
+        single = all(len(s.tokens) == 1 and list(s.want) == [0] for s in batch)
+        if not single or self.decode_greedy is None or len(batch) > self.max_rows:
+            self._picked = None
+            return self.engine.step(batch)
+        engine, cache = self.engine, self.engine.cache
+        slots = [s.slot for s in batch]
+        positions = [cache.length(s) for s in slots]
+        for s in batch:
+            if not 0 <= int(s.tokens[0]) < engine.spec.vocab_size:
+                raise StepError(f"slot {s.slot}: token {s.tokens[0]} is outside the vocabulary")
+        new_lengths = [p + 1 for p in positions]
+        cache.reserve(slots, new_lengths)
+        dec = self._decoder(len(batch), max(new_lengths), need_logits)
+        self.h2d_bytes += dec.upload([int(s.tokens[0]) for s in batch], positions, slots)
+        dec.launch()
+        cache.commit(slots, new_lengths)
+        self._picked = dec.picked[:len(batch)]
+        return dec.logits[:len(batch)] if need_logits else None
 
-    def greedy(self, logits: torch.Tensor) -> List[int]:
+    def greedy(self, logits: Optional[torch.Tensor]) -> List[int]:
+        if self._picked is not None:
+            self.d2h_bytes += self._picked.numel() * 4
+            return self._picked.tolist()  # the graph has picked already
         out = self.engine.workspace.get("picked", (logits.shape[0],), torch.int32)
         device_sampling.greedy(logits, out)
+        self.d2h_bytes += out.numel() * 4
         return out.tolist()
 
     def host_rows(self, logits: torch.Tensor, rows: Sequence[int]) -> np.ndarray:
@@ -51,6 +92,69 @@ class EngineBackend:
             return logits.cpu().numpy()
         index = torch.tensor(list(rows), dtype=torch.long, device=logits.device)
         return logits[index].cpu().numpy()
+
+
+    # -- greedy decoding with the batch's state on the device -------------------
+    def _decoder(self, rows: int, max_context: int, want_logits: bool = False) -> GraphDecoder:
+        bucket = 1
+        while bucket < rows:
+            bucket *= 2
+        pages = 4
+        while pages * PAGE_SIZE < max_context:
+            pages *= 2
+        context = min(pages * PAGE_SIZE, self.engine.spec.max_positions)
+        key = (bucket, context, want_logits)
+        if key not in self._decoders:
+            self._decoders[key] = GraphDecoder(self.engine, bucket, context, want_logits)
+        return self._decoders[key]
+
+    def decode_greedy(self, rows, emit) -> None:
+        """rows: (request, slot, next input token, its position, tokens still to
+        pick).  Calls ``emit(request, token)`` for every pick in order; a False
+        return means that sequence has ended (its slot is already given back)."""
+        cache = self.engine.cache
+        dec = self._decoder(len(rows), max(pos + left + 1 for _, _, _, pos, left in rows))
+        live = {}
+        for r, (i, slot, token, pos, left) in enumerate(rows):
+            dec.set_row(r, slot, token, pos)
+            live[r] = [i, slot, pos, left]
+        for r in range(len(rows), dec.rows):
+            dec.clear_row(r)
+        if self._pinned is None or self._pinned.shape[1] < dec.rows:
+            self._pinned = torch.empty((2, max(dec.rows, self.max_rows)), dtype=torch.int32,
+                                       pin_memory=True)
+        ended = set()
+        pending = None
+        turn = 0
+        while live or pending is not None:
+            launched = None
+            if live:
+                for r, (i, slot, pos, left) in live.items():
+                    cache.reserve([slot], [pos + 1])
+                    dec.sync_pages(r, slot)
+                    cache.commit([slot], [pos + 1])
+                dec.launch()
+                buf = self._pinned[turn % 2]
+                turn += 1
+                launched = (dec.picks_to_host(buf[:dec.rows]), buf, {r: v[0] for r, v in live.items()})
+                for r in list(live):
+                    live[r][2] += 1
+                    live[r][3] -= 1
+                    if live[r][3] == 0:  # this step picked its last token
+                        del live[r]
+                        dec.clear_row(r)
+            if pending is not None:
+                event, buf, who = pending
+                event.synchronize()
+                for r, i in who.items():
+                    if i in ended:
+                        continue  # it had stopped before this step was read: the pick is dropped
+                    if not emit(i, int(buf[r])):
+                        ended.add(i)
+                        if r in live:
+                            del live[r]
+                            dec.clear_row(r)
+            pending = launched
 
 
 def load_tokenizer(tokenizer_file: str):
@@ -61,7 +165,8 @@ def load_tokenizer(tokenizer_file: str):
 class LLM:
     def __init__(self, model_dir: str, dtype: str = "bfloat16", device_ordinal: int = 0,
                  device: Optional[str] = None, max_tokens: Optional[int] = None,
-                 max_batch: int = 64, tokenizer_file: Optional[str] = None):
+                 max_batch: int = 64, tokenizer_file: Optional[str] = None,
+                 pipeline_decode: bool = True):
         device = device if device is not None else f"cuda:{int(device_ordinal)}"
         self.max_batch = max_batch
         if max_tokens is None:
@@ -70,7 +175,8 @@ class LLM:
                                       max_slots=max(max_batch, 1))
         self.spec = self.engine.spec
         self.tokenizer = load_tokenizer(tokenizer_file) if tokenizer_file else None
-        self._generator = Generator(EngineBackend(self.engine), self.spec.vocab_size,
+        self.backend = EngineBackend(self.engine, max_batch, pipeline_decode)
+        self._generator = Generator(self.backend, self.spec.vocab_size,
                                     self.spec.max_positions, max_batch, max_tokens)
 
     # -- text ---------------------------------------------------------------

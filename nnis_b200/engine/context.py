@@ -53,3 +53,10 @@ class StepContext:
         by_rows = max(1, warps_wanted // max(1, query_rows))
         by_keys = max(1, -(-self.max_context // 128))
         return int(min(by_rows, by_keys, 64))
+
+    def decode_splits(self, ctas: int) -> int:
+        """The same for the decode kernel, whose CTAs (4 warps) each own a kv head
+        of a sequence: fill the SMs a few times over, at least 256 keys a slice."""
+        by_ctas = max(1, sm_count(self.tokens.device) * 4 // max(1, ctas))
+        by_keys = max(1, -(-self.max_context // 256))
+        return int(min(by_ctas, by_keys, 64))

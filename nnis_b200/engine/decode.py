@@ -1,0 +1,160 @@
+"""Decoding as one CUDA graph per step, with the batch's state on the device.
+
+A ``GraphDecoder`` holds, for a fixed number of rows, the current token and
+position of each row, its slot's page tables and the picked tokens.  One graph
+runs embedding, every block, final norm, head and the pick, then moves each live
+row on by one; the host launches it once per step, copies the picks to pinned
+memory and reads them one step late, so the GPU never waits for the host.  Rows
+without a sequence carry position -1: no kernel stores or reads for them, which
+is how padding changes no result.
+
+NNIS enqueues its fixed-length greedy loop once and synchronises at the end
+(crates/nnis-model/src/runtime.rs:814-846); with a stop token it reads one id
+per step (:848-899).  The graph with a one-step lag gives the first form's
+overlap with the second form's stops.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..cache import PAGE_SIZE
+from ..csrc import ops
+from ..sampling import device as device_sampling
+from .context import StepContext, sm_count
+from .workspace import Workspace
+
+
+class GraphDecoder:
+    def __init__(self, engine, rows: int, max_context: int, want_logits: bool = False):
+        self.engine = engine
+        self.want_logits = want_logits
+        self.rows = rows
+        self.device = engine.device
+        self.max_context = min(max_context, engine.spec.max_positions)
+        self.cols = max(1, -(-self.max_context // PAGE_SIZE))
+        n_groups = len(engine.cache.groups)
+        dev = self.device
+        # tokens | positions | slots | one page table per group: one buffer, so
+        # that the host can replace the whole state with one copy
+        self.state_ints = rows * (3 + n_groups * self.cols)
+        self.state = torch.full((self.state_ints,), -1, dtype=torch.int32, device=dev)
+        self.tokens = self.state[0:rows]
+        self.pos = self.state[rows:2 * rows]
+        self.slots = self.state[2 * rows:3 * rows]
+        self.tables = [self.state[3 * rows + g * rows * self.cols:
+                                  3 * rows + (g + 1) * rows * self.cols].view(rows, self.cols)
+                       for g in range(n_groups)]
+        self.tokens.zero_()
+        self.slots.zero_()
+        self.seq = torch.arange(rows, dtype=torch.int32, device=dev)
+        self.want = torch.arange(rows, dtype=torch.int32, device=dev)
+        self.host_state = torch.empty(self.state_ints, dtype=torch.int32, pin_memory=True)
+        self._host_state_free = torch.cuda.Event()
+        self._host_state_free.record()
+        self.logits = torch.empty((rows, engine.spec.vocab_size), dtype=torch.float32, device=dev) \
+            if want_logits else None
+        self.picked = torch.zeros(rows, dtype=torch.int32, device=dev)
+        self.workspace = Workspace(dev)
+        warps_wanted = sm_count(dev) * 16
+        n_heads = max(1, rows * self._query_heads())
+        splits = int(min(max(1, warps_wanted // n_heads), max(1, -(-self.max_context // 128)), 64))
+        self.ctx = StepContext(
+            n_tokens=rows, n_seqs=rows, tokens=self.tokens, token_pos=self.pos, token_seq=self.seq,
+            seq_slots=self.slots, page_tables=self.tables, workspace=self.workspace, decode=True,
+            max_context=self.max_context, fixed_splits=splits)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.launches_per_step = 0
+        # host side of the rows
+        self.host_tables = [[[-1] * self.cols for _ in range(rows)] for _ in range(n_groups)]
+        self._pinned_out: Optional[torch.Tensor] = None
+
+    def _query_heads(self) -> int:
+        heads = [getattr(b.mixer, "heads", 1) for b in self.engine.model.blocks]
+        return max(heads) if heads else 1
+
+    # -- the captured step ----------------------------------------------------
+    def _body(self) -> None:
+        self.engine.model.forward_and_pick(self.ctx, self.want, self.picked, self.logits, self.tokens,
+                                           self.pos)
+
+    def capture(self) -> None:
+        if self.graph is not None:
+            return
+        side = torch.cuda.Stream(device=self.device)
+        saved = self.pos.clone()
+        self.pos.fill_(-1)  # the warm-up run must not touch the cache, tokens or positions
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self._body()
+        torch.cuda.current_stream().wait_stream(side)
+        self.workspace.frozen = True
+        graph = torch.cuda.CUDAGraph()
+        before = ops.launch_count()
+        with torch.cuda.graph(graph):
+            self._body()
+        self.launches_per_step = ops.launch_count() - before
+        self.graph = graph
+        self.pos.copy_(saved)
+
+    # -- rows ---------------------------------------------------------------------
+    def set_row(self, row: int, slot: int, token: int, position: int) -> None:
+        """Put a sequence on a row: its next input token and that token's position."""
+        cache = self.engine.cache
+        update = torch.tensor([token, position, slot], dtype=torch.int32).pin_memory()
+        self.tokens[row:row + 1].copy_(update[0:1], non_blocking=True)
+        self.pos[row:row + 1].copy_(update[1:2], non_blocking=True)
+        self.slots[row:row + 1].copy_(update[2:3], non_blocking=True)
+        for g in range(len(self.tables)):
+            pages = cache.page_table(g, slot)[:self.cols]
+            line = pages + [-1] * (self.cols - len(pages))
+            self.host_tables[g][row] = line
+            self.tables[g][row].copy_(torch.tensor(line, dtype=torch.int32).pin_memory(),
+                                      non_blocking=True)
+
+    def clear_row(self, row: int) -> None:
+        self.pos[row:row + 1].fill_(-1)
+
+    def sync_pages(self, row: int, slot: int) -> None:
+        """After the cache reserved more room for ``slot``: send new page ids."""
+        cache = self.engine.cache
+        for g in range(len(self.tables)):
+            pages = cache.page_table(g, slot)[:self.cols]
+            line = self.host_tables[g][row]
+            for j, page in enumerate(pages):
+                if line[j] != page:
+                    line[j] = page
+                    self.tables[g][row, j:j + 1].fill_(page)
+
+    def upload(self, tokens: Sequence[int], positions: Sequence[int], slots: Sequence[int]) -> int:
+        """Replace the state of all rows from the host in one copy: row r gets
+        the r-th sequence; rows beyond them are padding.  Returns the bytes sent."""
+        cache = self.engine.cache
+        rows, cols, n = self.rows, self.cols, len(tokens)
+        ints = list(tokens) + [0] * (rows - n) + list(positions) + [-1] * (rows - n) \
+            + list(slots) + [0] * (rows - n)
+        for g in range(len(self.tables)):
+            for slot in slots:
+                pages = cache.page_table(g, slot)[:cols]
+                ints += pages + [-1] * (cols - len(pages))
+            ints += [-1] * ((rows - n) * cols)
+        self._host_state_free.synchronize()
+        self.host_state.copy_(torch.tensor(ints, dtype=torch.int32))
+        self.state.copy_(self.host_state, non_blocking=True)
+        self._host_state_free.record()
+        for g in range(len(self.tables)):  # the partial-update path starts from scratch next time
+            self.host_tables[g] = [[None] * cols for _ in range(rows)]
+        return self.state_ints * 4
+
+    # -- stepping -------------------------------------------------------------------
+    def launch(self) -> None:
+        self.capture()
+        self.graph.replay()
+
+    def picks_to_host(self, into: torch.Tensor) -> torch.cuda.Event:
+        """Copy this step's picks into pinned ``into``; the event says when."""
+        into.copy_(self.picked, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return event

@@ -21,6 +21,7 @@ import torch
 
 from ..cache import PAGE_SIZE, CacheManager
 from ..config import read_config
+from ..csrc import ops
 from ..config.spec import ModelSpec
 from ..weights import load_weights
 from .context import StepContext
@@ -71,6 +72,7 @@ class Engine:
         self.model.bind_cache(self.cache)
         self.workspace = Workspace(self.device)
         self._staging: Optional[torch.Tensor] = None  # pinned host ints of one step
+        self.h2d_bytes = 0  # bytes of step tables copied so far (for measurements)
 
     # -- construction -------------------------------------------------------
     @classmethod
@@ -118,6 +120,7 @@ class Engine:
         self._staging[:n] = torch.tensor(ints, dtype=torch.int32)
         dev = self.workspace.get("step_ints", (n,), torch.int32)
         dev.copy_(self._staging[:n], non_blocking=True)
+        self.h2d_bytes += 4 * n
         self._staging_free.record()
         return dev
 
@@ -198,6 +201,7 @@ class Engine:
         if int(self.model.status.item()) != 0:
             self.model.status.zero_()
             raise StepError("a kernel met a token id outside the vocabulary")
+        ops.check_status(self.device)
 
     # -- figures ----------------------------------------------------------------
     def memory(self) -> Dict[str, object]:

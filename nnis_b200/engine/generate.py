@@ -158,6 +158,11 @@ class Generator:
             live = list(batch)
             logits = self.backend.step([SequenceStep(slots[i], list(requests[i].prompt),
                                                      [len(requests[i].prompt) - 1]) for i in live])
+            if all(requests[i].sampling is None for i in batch) and \
+                    getattr(self.backend, "decode_greedy", None) is not None and \
+                    getattr(self.backend, "pipeline", True):
+                self._run_greedy_on_device(batch, requests, results, slots, logits, on_token)
+                return
             while True:
                 tokens = self._pick(logits, live, requests, samplers)
                 still = []
@@ -177,7 +182,9 @@ class Generator:
                 if not still:
                     break
                 live = [i for i, _ in still]
-                logits = self.backend.step([SequenceStep(slots[i], [t], [0]) for i, t in still])
+                logits = self.backend.step([SequenceStep(slots[i], [t], [0]) for i, t in still],
+                                           need_logits=any(requests[i].sampling is not None
+                                                           for i in live))
         except Exception as e:  # the batch's requests fail together, later batches still run
             for i in batch:
                 if results[i].finish_reason is None:
@@ -185,3 +192,33 @@ class Generator:
         finally:
             for slot in slots.values():
                 self.backend.release_slot(slot)
+
+    def _run_greedy_on_device(self, batch, requests, results, slots, logits, on_token) -> None:
+        """All-greedy batches: the backend keeps tokens and positions on the
+        device and tells this loop each step's picks one step late.  The rules
+        are the same: a stop token is emitted and ends its sequence, a sequence
+        at its length ends, an ended sequence gives its slot back at once."""
+        first = self.backend.greedy(logits)
+
+        def emit(i: int, t: int) -> bool:
+            """Record token t of request i; True if the sequence goes on."""
+            res, gen = results[i], requests[i].generation
+            res.token_ids.append(int(t))
+            if on_token is not None:
+                on_token(i, int(t))
+            if t in gen.stop_token_ids:
+                res.finish_reason = "stop"
+            elif len(res.token_ids) >= gen.max_new_tokens:
+                res.finish_reason = "length"
+            else:
+                return True
+            self.backend.release_slot(slots.pop(i))
+            return False
+
+        rows = []
+        for i, t in zip(batch, first):
+            if emit(i, t):
+                rows.append((i, slots[i], int(t), len(requests[i].prompt),
+                             requests[i].generation.max_new_tokens - 1))
+        if rows:
+            self.backend.decode_greedy(rows, emit)

@@ -10,6 +10,7 @@ from typing import Dict, List, Mapping, Optional
 import torch
 
 from ..cache import KVRequest, KVView, StateRequest
+from ..csrc import ops
 from ..config.spec import ModelSpec
 from ..parts import BLOCKS, NORMS, LinearHead, TokenEmbedding
 from ..weights.loader import WeightSpec
@@ -27,6 +28,7 @@ class DecoderModel:
                                       self.device)
         self.head = LinearHead(spec.head.params, "", dtype, self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._pick_scratch: Dict[int, torch.Tensor] = {}
         for i, entry in enumerate(spec.schedule):
             wants = self.blocks[entry.layer].mixer.cache_request()
             if entry.cache_of is not None and wants is not None:
@@ -74,17 +76,49 @@ class DecoderModel:
             self._views.append(view)
 
     # -- run ------------------------------------------------------------------
+    def forward_and_pick(self, ctx, want_rows: torch.Tensor, picks: torch.Tensor,
+                         logits: Optional[torch.Tensor], tokens: torch.Tensor,
+                         pos: torch.Tensor) -> None:
+        """A decode step that ends in the greedy pick: ``picks`` gets the token of
+        each wanted row, ``tokens``/``pos`` (the step's own inputs) move on to the
+        next step on live rows; ``logits`` is written too when it is given."""
+        r = picks.numel()
+        if self.head.fuses_norm(self.final_norm, r):
+            self._run_blocks(ctx)
+            ws = ctx.workspace
+            hidden = ws.get("hidden", (ctx.n_tokens, self.spec.hidden_size), torch.float32)
+            need = self.head.pick_scratch_ints(r)
+            scratch = self._pick_scratch.get(need)
+            if scratch is None:
+                # zeroed once (the kernel leaves its ticket at zero) and kept for
+                # good: a captured graph holds its address
+                scratch = torch.zeros(need, dtype=torch.int32, device=self.device)
+                self._pick_scratch[need] = scratch
+            self.head.forward_pick(hidden, self.final_norm, want_rows, picks, scratch, logits,
+                                   tokens, pos)
+            return
+        if logits is None:
+            logits = ctx.workspace.get("logits", (r, self.spec.vocab_size), torch.float32)
+        self.forward(ctx, want_rows, logits)
+        ops.argmax(logits, picks)
+        ops.advance(tokens, pos, picks)
+
+    def _run_blocks(self, ctx) -> torch.Tensor:
+        hidden = ctx.workspace.get("hidden", (ctx.n_tokens, self.spec.hidden_size), torch.float32)
+        self.embedding.forward(ctx.tokens, hidden, self.status)
+        for i, entry in enumerate(self.spec.schedule):
+            self.blocks[entry.layer].forward(hidden, ctx, self._views[i])
+        return hidden
+
     def forward(self, ctx, want_rows: torch.Tensor, logits: torch.Tensor) -> None:
         """Run ``ctx.n_tokens`` packed tokens; write the logits of the rows that
         ``want_rows`` (int32, indices into the packed tokens) names."""
         ws = ctx.workspace
-        n = ctx.n_tokens
-        hidden = ws.get("hidden", (n, self.spec.hidden_size), torch.float32)
-        self.embedding.forward(ctx.tokens, hidden, self.status)
-        for i, entry in enumerate(self.spec.schedule):
-            self.blocks[entry.layer].forward(hidden, ctx, self._views[i])
+        hidden = self._run_blocks(ctx)
         r = logits.shape[0]
-        if r:
+        if r and self.head.fuses_norm(self.final_norm, r):
+            self.head.forward_normed(hidden, self.final_norm, want_rows, logits)
+        elif r:
             final = ws.get("final", (r, self.spec.hidden_size), self.dtype)
             self.final_norm.forward(hidden, final, want_rows)
             self.head.forward(final, logits)

@@ -89,25 +89,72 @@ class Attention(Part):
             raise ValueError("the shared cache does not fit this attention's heads or window")
 
     # -- run --------------------------------------------------------------
+    def _decode_kernels(self, ctx, n: int) -> bool:
+        """The fused bfloat16 decode path: few rows, one token per sequence."""
+        return (self.dtype == torch.bfloat16 and ctx.decode
+                and ops.gemv_takes(n, self.w_qkv.shape[0], self.hidden, ops.EPI_QKV)
+                and ops.gemv_takes(n, self.hidden, self.heads * self.head_dim))
+
+    def fuses_norm(self, norm, ctx, n: int) -> bool:
+        return getattr(norm, "kind", None) == "rmsnorm" and self._decode_kernels(ctx, n)
+
     def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor, cache: KVView) -> None:
-        n = x.shape[0]
+        self._run(ctx, residual, cache, x=x)
+
+    def forward_normed(self, hidden: torch.Tensor, norm, ctx, cache: KVView) -> None:
+        """The same with the block's norm folded into the first projection."""
+        self._run(ctx, hidden, cache, hidden=hidden, norm=norm)
+
+    def _run(self, ctx, residual, cache, x=None, hidden=None, norm=None) -> None:
+        n = residual.shape[0]
         d, nq, nkv = self.head_dim, self.heads, self.kv_heads
         ws = ctx.workspace
-        qkv = ws.get("qkv", (n, (nq + 2 * self.stored_kv) * d), self.dtype)
-        linear(x, self.w_qkv, self.b_qkv, qkv, STORE)
         table = ctx.page_tables[cache.group]
         tables = self.position.rotary_tables()
         cos, sin = tables if tables is not None else (None, None)
-        ops.rope_store(qkv, ctx.token_pos, ctx.token_seq, table if self.own_kv else None, cos, sin,
-                       cache.k if self.own_kv else None, cache.v if self.own_kv else None, nq,
-                       self.stored_kv, d, cache.page_size)
         attn = ws.get("attn", (n, nq * d), self.dtype)
-        splits = ctx.attention_splits(n * nq)
-        partial = ws.get("attn_partial", (n * nq * splits * (d + 2),), torch.float32) \
-            if splits > 1 else None
-        ops.attention_generic(qkv, qkv.shape[1], cache.k, cache.v, ctx.token_pos, ctx.token_seq,
-                              table, attn, nq, nkv, d, self.window, self.scale, splits, partial)
-        linear(attn, self.w_o, self.b_o, residual, ADD_F32)
+        if self._decode_kernels(ctx, n):
+            q = ws.get("q", (n, nq * d), self.dtype)
+            ops.gemv_bf16(self.w_qkv, self.b_qkv, q, ops.EPI_QKV, x=x, hidden=hidden,
+                          norm_weight=norm.weight if norm is not None else None,
+                          eps=norm.eps if norm is not None else 0.0, m=n,
+                          token_pos=ctx.token_pos, token_seq=ctx.token_seq,
+                          page_table=table if self.own_kv else None, cos=cos, sin=sin,
+                          k_cache=cache.k if self.own_kv else None,
+                          v_cache=cache.v if self.own_kv else None, heads=nq,
+                          kv_heads=self.stored_kv, head_dim=d, page_size=cache.page_size)
+            q_buf, q_stride = q, nq * d
+        else:
+            qkv = ws.get("qkv", (n, (nq + 2 * self.stored_kv) * d), self.dtype)
+            linear(x, self.w_qkv, self.b_qkv, qkv, STORE)
+            ops.rope_store(qkv, ctx.token_pos, ctx.token_seq, table if self.own_kv else None, cos,
+                           sin, cache.k if self.own_kv else None, cache.v if self.own_kv else None,
+                           nq, self.stored_kv, d, cache.page_size)
+            q_buf, q_stride = qkv, qkv.shape[1]
+        merged = True
+        if self.dtype == torch.bfloat16 and ctx.decode and n <= 65535:
+            tiles = -(-(nq // nkv) // 4)
+            splits = ctx.decode_splits(n * nkv * tiles)
+            partial = ws.get("attn_partial", (n * nq * splits * (d + 2),), torch.float32) \
+                if splits > 1 else None
+            # with the fused output projection the split records are merged there
+            merged = not (splits > 1 and self._decode_kernels(ctx, n))
+            ops.attention_decode(q_buf, q_stride, cache.k, cache.v, ctx.token_pos, ctx.token_seq,
+                                 table, attn, nq, nkv, d, self.window, self.scale, splits, partial,
+                                 merge=merged)
+        else:
+            splits = ctx.attention_splits(n * nq)
+            partial = ws.get("attn_partial", (n * nq * splits * (d + 2),), torch.float32) \
+                if splits > 1 else None
+            ops.attention_generic(q_buf, q_stride, cache.k, cache.v, ctx.token_pos, ctx.token_seq,
+                                  table, attn, nq, nkv, d, self.window, self.scale, splits, partial)
+        if self._decode_kernels(ctx, n) and not merged:
+            ops.gemv_bf16(self.w_o, self.b_o, residual, ops.EPI_ADD_F32, partial=partial,
+                          splits=splits, heads=nq, head_dim=d, m=n)
+        elif self._decode_kernels(ctx, n):
+            ops.gemv_bf16(self.w_o, self.b_o, residual, ops.EPI_ADD_F32, x=attn)
+        else:
+            linear(attn, self.w_o, self.b_o, residual, ADD_F32)
 
 
 MIXERS.register("attention", Attention)

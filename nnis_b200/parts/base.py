@@ -29,6 +29,11 @@ from ..weights.loader import WeightSpec
 
 
 class Part:
+    # True: ``forward`` works from the device tensors of the step context alone,
+    # so a step can be captured in a CUDA graph.  A part that reads the context's
+    # host-side fields (``host_slots`` ...) sets this to False.
+    device_only = True
+
     def __init__(self, params: Mapping[str, Any], prefix: str, dtype: torch.dtype,
                  device: torch.device):
         self.params = params

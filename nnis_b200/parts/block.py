@@ -44,10 +44,17 @@ class PreNormBlock:
     def forward(self, hidden: torch.Tensor, ctx, cache) -> None:
         n, width = hidden.shape
         normed = ctx.workspace.get("normed", (n, width), self.dtype)
-        self.mixer_norm.forward(hidden, normed)
-        self.mixer.forward(normed, ctx, hidden, cache)
-        self.ffn_norm.forward(hidden, normed)
-        self.ffn.forward(normed, ctx, hidden)
+        # a part may fold the norm before it into its first kernel (decode steps)
+        if getattr(self.mixer, "fuses_norm", None) and self.mixer.fuses_norm(self.mixer_norm, ctx, n):
+            self.mixer.forward_normed(hidden, self.mixer_norm, ctx, cache)
+        else:
+            self.mixer_norm.forward(hidden, normed)
+            self.mixer.forward(normed, ctx, hidden, cache)
+        if getattr(self.ffn, "fuses_norm", None) and self.ffn.fuses_norm(self.ffn_norm, ctx, n):
+            self.ffn.forward_normed(hidden, self.ffn_norm, ctx)
+        else:
+            self.ffn_norm.forward(hidden, normed)
+            self.ffn.forward(normed, ctx, hidden)
 
 
 BLOCKS.register("prenorm", PreNormBlock)

@@ -60,3 +60,26 @@ class LinearHead(Part):
 
     def forward(self, x: torch.Tensor, logits: torch.Tensor) -> None:
         linear(x, self.weight, None, logits, STORE_F32)
+
+    def fuses_norm(self, norm, rows: int) -> bool:
+        return (getattr(norm, "kind", None) == "rmsnorm" and self.dtype == torch.bfloat16
+                and ops.gemv_takes(rows, self.vocab, self.width))
+
+    def forward_pick(self, hidden: torch.Tensor, norm, rows: torch.Tensor, picks: torch.Tensor,
+                     scratch: torch.Tensor, logits: Optional[torch.Tensor] = None,
+                     next_tokens: Optional[torch.Tensor] = None,
+                     next_pos: Optional[torch.Tensor] = None) -> None:
+        """Final norm, head and greedy pick in one kernel; optionally the logits
+        too, and the decode state moved on (tokens = picks, positions + 1)."""
+        ops.gemv_bf16(self.weight, None, picks, ops.EPI_ARGMAX, hidden=hidden,
+                      norm_weight=norm.weight, eps=norm.eps, rows=rows, m=picks.numel(),
+                      logits=logits, scratch=scratch, next_tokens=next_tokens, next_pos=next_pos)
+
+    def pick_scratch_ints(self, rows: int) -> int:
+        return ops.argmax_scratch_ints(rows, self.vocab, self.width, self.device)
+
+    def forward_normed(self, hidden: torch.Tensor, norm, rows: torch.Tensor,
+                       logits: torch.Tensor) -> None:
+        """Final norm of the wanted rows folded into the head (few rows)."""
+        ops.gemv_bf16(self.weight, None, logits, ops.EPI_STORE_F32, hidden=hidden,
+                      norm_weight=norm.weight, eps=norm.eps, rows=rows, m=logits.shape[0])

@@ -56,12 +56,33 @@ class GatedMLP(Part):
         return sum(t.numel() * t.element_size()
                    for t in (self.w_gu, self.w_down, self.b_gu, self.b_down) if t is not None)
 
+    def _decode_kernels(self, ctx, n: int) -> bool:
+        return (self.dtype == torch.bfloat16 and ctx.decode
+                and ops.gemv_takes(n, 2 * self.inter, self.hidden, ops.EPI_GATED)
+                and ops.gemv_takes(n, self.hidden, self.inter))
+
+    def fuses_norm(self, norm, ctx, n: int) -> bool:
+        return getattr(norm, "kind", None) == "rmsnorm" and self._decode_kernels(ctx, n)
+
     def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor) -> None:
-        n = x.shape[0]
+        self._run(ctx, residual, x=x)
+
+    def forward_normed(self, hidden: torch.Tensor, norm, ctx) -> None:
+        """The same with the block's norm folded into the gate/up projection."""
+        self._run(ctx, hidden, hidden=hidden, norm=norm)
+
+    def _run(self, ctx, residual, x=None, hidden=None, norm=None) -> None:
+        n = residual.shape[0]
         ws = ctx.workspace
+        act = ws.get("act", (n, self.inter), self.dtype)
+        if self._decode_kernels(ctx, n):
+            ops.gemv_bf16(self.w_gu, self.b_gu, act, ops.EPI_GATED, x=x, hidden=hidden,
+                          norm_weight=norm.weight if norm is not None else None,
+                          eps=norm.eps if norm is not None else 0.0, m=n)
+            ops.gemv_bf16(self.w_down, self.b_down, residual, ops.EPI_ADD_F32, x=act)
+            return
         gate_up = ws.get("gate_up", (n, 2 * self.inter), torch.float32)
         linear(x, self.w_gu, self.b_gu, gate_up, STORE_F32)
-        act = ws.get("act", (n, self.inter), self.dtype)
         ops.silu_mul(gate_up, act)
         linear(act, self.w_down, self.b_down, residual, ADD_F32)
 

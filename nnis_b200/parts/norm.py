@@ -12,6 +12,7 @@ from .base import NORMS, Part
 
 class RMSNorm(Part):
     """params: size, eps, name (tensor stem)."""
+    kind = "rmsnorm"  # parts that can fold this norm into their first projection look for it
 
     def __init__(self, params, prefix, dtype, device):
         super().__init__(params, prefix, dtype, device)

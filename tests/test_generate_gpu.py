@@ -90,3 +90,26 @@ def test_command_line_generates(model_dirs):
     assert out["results"][0]["ok"] and not out["results"][1]["ok"]
     assert "vocabulary" in out["results"][1]["error"]
     assert run("generate", "--model", d, "--prompt-ids", "1", "--seed", "3").returncode == 2
+
+
+@pytest.mark.parametrize("pipeline", [True, False])
+def test_both_decode_paths_agree_with_the_plain_loop(model_dirs, pipeline):
+    """Tokens kept on the device with picks read one step late, and tokens sent
+    from the host every step: same results, stops included, slots all free."""
+    from nnis_b200 import LLM
+    d = model_dirs["C"]
+    cfg = read_config_json(d)
+    w = load_plain_weights(d, as_bf16=False)
+    llm = LLM(d, dtype="float32", max_tokens=64 * 40, max_batch=8, pipeline_decode=pipeline)
+    prompts = [[i + 1, 2 * i + 3, 900 - i] * (1 + i % 3) for i in range(11)] + [[4] * 63, [5] * 64]
+    plain = [P.greedy_generate(cfg, w, p, 20, None) for p in prompts]
+    stop = plain[2][6]
+    want = [t[:t.index(stop) + 1] if stop in t else t for t in plain]
+    got = llm.generate(prompts, max_new_tokens=20, stop_token_ids=[stop])
+    assert [r.token_ids for r in got] == want
+    assert got[2].finish_reason == "stop"
+    assert llm.engine.cache.usage()["slots_held"] == 0 and llm.engine.cache.usage()["pages_held"] == [0]
+    llm.engine.cache.check()
+    # a second call reuses decoders, graphs and slots
+    again = llm.generate(prompts[:3], max_new_tokens=5, stop_token_ids=())
+    assert [r.token_ids for r in again] == [t[:5] for t in plain[:3]]

@@ -35,7 +35,7 @@ class ScriptedBackend:
         del self.held[slot]
         self.free.append(slot)
 
-    def step(self, batch):
+    def step(self, batch, need_logits=True):
         if self.fail_on_step is not None and len(self.steps) == self.fail_on_step:
             self.steps.append("boom")
             raise RuntimeError("boom")

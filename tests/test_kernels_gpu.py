@@ -290,3 +290,205 @@ def test_temperature_sampling_follows_the_seeded_draws():
             assert abs(got[r] - want) <= 0 or abs(cdf[got[r]] - u * cdf[-1]) < 1e-9 * cdf[-1]
         counts[got[0]] += 1
     assert counts.argmax() == logits[0].argmax() or counts.max() < 20
+
+
+# ---------------------------------------------------------------------------
+# the fused bfloat16 decode kernels
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("m", [1, 2, 3, 8, 11, 16])
+@pytest.mark.parametrize("n,k", [(8, 16), (100, 72), (960, 576), (1000, 1536)])
+def test_gemv_plain_epilogues_and_norm_prologue(m, n, k):
+    o = ops()
+    g = torch.Generator().manual_seed(m + n + k)
+    w = (torch.randn(n, k, generator=g) / math.sqrt(k)).bfloat16()
+    bias = torch.randn(n, generator=g)
+    x = torch.randn(m, k, generator=g).bfloat16()
+    want = P.linear(x, w, bias)
+    out = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    o.gemv_bf16(w.to(DEV), bias.to(DEV), out, o.EPI_STORE, x=x.to(DEV))
+    close(out, want, "bfloat16", "gemv store")
+    out32 = torch.empty(m, n, device=DEV)
+    o.gemv_bf16(w.to(DEV), None, out32, o.EPI_STORE_F32, x=x.to(DEV))
+    close(out32, P.linear(x, w), "float32", "gemv store f32")
+    base = torch.randn(m, n, generator=g)
+    acc = base.to(DEV).clone()
+    o.gemv_bf16(w.to(DEV), bias.to(DEV), acc, o.EPI_ADD_F32, x=x.to(DEV))
+    close(acc, base.double() + want, "float32", "gemv add")
+    # norm prologue with gathered rows
+    hidden = torch.randn(m + 5, k, generator=g) * 2
+    nw = 1 + 0.1 * torch.randn(k, generator=g)
+    rows = torch.randperm(m + 5, generator=g)[:m].to(torch.int32)
+    normed = P.rms_norm(hidden[rows.long()], nw, 1e-5).bfloat16()
+    o.gemv_bf16(w.to(DEV), None, out32, o.EPI_STORE_F32, hidden=hidden.to(DEV),
+                norm_weight=nw.to(DEV), eps=1e-5, rows=rows.to(DEV))
+    close(out32, P.linear(normed, w), "float32", "gemv norm prologue")
+
+
+@pytest.mark.parametrize("m", [1, 5, 16])
+def test_gemv_gated_epilogue(m):
+    o = ops()
+    g = torch.Generator().manual_seed(m)
+    k, inter = 72, 100
+    w = (torch.randn(2 * inter, k, generator=g) / math.sqrt(k) * 3).bfloat16()
+    bias = torch.randn(2 * inter, generator=g)
+    x = torch.randn(m, k, generator=g).bfloat16()
+    y = P.linear(x, w, bias)
+    out = torch.empty(m, inter, dtype=torch.bfloat16, device=DEV)
+    o.gemv_bf16(w.to(DEV), bias.to(DEV), out, o.EPI_GATED, x=x.to(DEV))
+    close(out, P.swiglu(y[:, :inter], y[:, inter:]), "bfloat16", "gemv gated")
+
+
+@pytest.mark.parametrize("nq,nkv,d,rotate", [(6, 2, 16, True), (3, 1, 48, True), (4, 4, 64, False),
+                                             (2, 0, 32, True)])
+def test_gemv_qkv_epilogue_rotates_and_stores(nq, nkv, d, rotate):
+    o = ops()
+    g = torch.Generator().manual_seed(nq * d)
+    m, k, page = 5, 40, 64
+    n = (nq + 2 * nkv) * d
+    w = (torch.randn(n, k, generator=g) / math.sqrt(k)).bfloat16()
+    bias = torch.randn(n, generator=g)
+    x = torch.randn(m, k, generator=g).bfloat16()
+    pos = torch.tensor([0, 63, 64, -1, 130], dtype=torch.int32)
+    seq = torch.tensor([0, 1, 2, 0, 3], dtype=torch.int32)
+    table = torch.tensor([[5, -1, -1], [2, -1, -1], [7, 1, -1], [0, 3, 4]], dtype=torch.int32)
+    kc = torch.zeros(8, max(nkv, 1), page, d, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    cos, sin = P.rope_tables(200, d, 10000.0)
+    q_out = torch.full((m, nq * d), 9.0, dtype=torch.bfloat16, device=DEV)
+    o.gemv_bf16(w.to(DEV), bias.to(DEV), q_out, o.EPI_QKV, x=x.to(DEV), token_pos=pos.to(DEV),
+                token_seq=seq.to(DEV), page_table=table.to(DEV) if nkv else None,
+                cos=cos.float().to(DEV) if rotate else None, sin=sin.float().to(DEV) if rotate else None,
+                k_cache=kc if nkv else None, v_cache=vc if nkv else None, heads=nq, kv_heads=nkv,
+                head_dim=d, page_size=page)
+    y = P.linear(x, w, bias).bfloat16().double()
+    for i in range(m):
+        p = int(pos[i])
+        if p < 0:
+            assert float((q_out[i].float() - 9.0).abs().max()) == 0  # padding row untouched
+            continue
+        c, s = (cos[p:p + 1], sin[p:p + 1]) if rotate else (torch.ones(1, d // 2).double(),
+                                                            torch.zeros(1, d // 2).double())
+        heads = y[i].view(nq + 2 * nkv, d)
+        rq = P.rope_rotate_half(heads[:nq][None], c, s)[0]
+        close(q_out[i].view(nq, d), rq, "bfloat16", "q")
+        if nkv:
+            rk = P.rope_rotate_half(heads[nq:nq + nkv][None], c, s)[0]
+            pg = int(table[int(seq[i]), p // page])
+            close(kc[pg, :, p % page], rk, "bfloat16", "k")
+            close(vc[pg, :, p % page], heads[nq + nkv:], "bfloat16", "v")
+    if nkv:
+        assert int((kc.float().abs().sum(-1) > 0).sum()) == 4 * nkv  # nothing else was written
+
+
+def test_gemv_refuses_what_it_does_not_take():
+    o = ops()
+    assert not o.gemv_takes(17, 64, 64) and not o.gemv_takes(4, 64, 60) and not o.gemv_takes(4, 66, 64)
+    assert not o.gemv_takes(4, 68, 64, o.EPI_GATED) and o.gemv_takes(4, 68, 64)
+    with pytest.raises(o.KernelError, match="not taken"):
+        o.gemv_bf16(torch.zeros(66, 64, dtype=torch.bfloat16, device=DEV), None,
+                    torch.zeros(2, 66, dtype=torch.bfloat16, device=DEV), o.EPI_STORE,
+                    x=torch.zeros(2, 64, dtype=torch.bfloat16, device=DEV))
+
+
+@pytest.mark.parametrize("nq,nkv,d", [(6, 2, 16), (5, 5, 48), (4, 1, 80), (9, 3, 64), (16, 2, 128),
+                                      (2, 1, 256)])
+@pytest.mark.parametrize("window", [0, 100])
+def test_attention_decode_kernel(nq, nkv, d, window):
+    """One token per sequence, contexts from 1 to many pages, with padding rows."""
+    o = ops()
+    lengths = [1, 64, 65, 300, 1000, 7]
+    case = PagedCase(lengths, [1] * len(lengths), nq, nkv, d, "bfloat16", seed=nq + d)
+    case.fill_cache()
+    for s, L in enumerate(lengths):  # the step's own key and value
+        pg = int(case.table[s, (L - 1) // 64])
+        case.k_cache[pg, :, (L - 1) % 64] = case.k[s][L - 1]
+        case.v_cache[pg, :, (L - 1) % 64] = case.v[s][L - 1]
+    pos, seq, q, _, _ = case.packed()
+    pos = torch.cat([pos, torch.tensor([-1], dtype=torch.int32)])  # a padding row at the end
+    seq = torch.cat([seq, torch.tensor([0], dtype=torch.int32)])
+    n = pos.numel()
+    qd = torch.cat([q.reshape(n - 1, -1), torch.ones(1, nq * d)]).bfloat16().to(DEV)
+    kc, vc = case.k_cache.bfloat16().to(DEV), case.v_cache.bfloat16().to(DEV)
+    want = torch.cat([P.causal_attention(case.q[s], case.k[s], case.v[s].bfloat16().float(),
+                                         window)[L - 1:].reshape(1, -1)
+                      for s, L in enumerate(lengths)])
+    for splits in (1, 2, 7):
+        out = torch.full((n, nq * d), 5.0, dtype=torch.bfloat16, device=DEV)
+        partial = torch.empty(n * nq * splits * (d + 2), device=DEV) if splits > 1 else None
+        o.attention_decode(qd, nq * d, kc, vc, pos.to(DEV), seq.to(DEV), case.table.to(DEV), out, nq,
+                           nkv, d, window, 1.0 / math.sqrt(d), splits, partial)
+        close(out[:n - 1], want, "bfloat16", f"decode attention splits {splits}")
+        assert float(out[n - 1].float().abs().max()) == 0
+
+
+@pytest.mark.parametrize("m", [1, 6, 16])
+@pytest.mark.parametrize("n,k", [(8, 16), (1000, 72), (49152, 576)])
+def test_gemv_argmax_epilogue_picks_moves_on_and_can_write_logits(m, n, k):
+    o = ops()
+    g = torch.Generator().manual_seed(m + n)
+    w = (torch.randn(n, k, generator=g) / math.sqrt(k)).bfloat16()
+    w[n // 2] = w[3]  # two equal logits in every row: the lower index must win when they lead
+    hidden = torch.randn(m, k, generator=g)
+    hidden[0] = w[3].float() * 4  # row 0 is led by index 3 (and its twin)
+    nw = torch.ones(k)
+    want_logits = P.linear(P.rms_norm(hidden, nw, 1e-5).bfloat16(), w)
+    want = [P.argmax_lowest(r) for r in want_logits]
+    assert want[0] == 3
+    rows = torch.arange(m, dtype=torch.int32, device=DEV)
+    scratch = torch.zeros(o.argmax_scratch_ints(m, n, k, DEV), dtype=torch.int32, device=DEV)
+    tokens = torch.full((m,), 7, dtype=torch.int32, device=DEV)
+    pos = torch.arange(10, 10 + m, dtype=torch.int32, device=DEV)
+    pos[m - 1] = -1  # a padding row keeps its state
+    for with_logits in (False, True, False):  # the scratch is reused across launches
+        picks = torch.full((m,), -5, dtype=torch.int32, device=DEV)
+        logits = torch.zeros(m, n, device=DEV) if with_logits else None
+        t, p = tokens.clone(), pos.clone()
+        o.gemv_bf16(w.to(DEV), None, picks, o.EPI_ARGMAX, hidden=hidden.to(DEV), norm_weight=nw.to(DEV),
+                    eps=1e-5, rows=rows, m=m, logits=logits, scratch=scratch, next_tokens=t, next_pos=p)
+        got = picks.tolist()
+        for r in range(m):  # equal up to rounding: accept any index whose logit ties the best
+            assert got[r] == want[r] or abs(float(want_logits[r, got[r]] - want_logits[r, want[r]])) < 1e-3
+        assert got[0] == 3
+        assert t.tolist()[:m - 1] == got[:m - 1] and p.tolist()[:m - 1] == list(range(11, 10 + m))
+        if m > 1:
+            assert int(t[m - 1]) == 7 and int(p[m - 1]) == -1
+        if with_logits:
+            close(logits, want_logits, "float32", "argmax logits")
+    o.check_status(DEV)
+
+
+@pytest.mark.parametrize("nq,nkv,d,splits", [(9, 3, 64, 5), (4, 4, 16, 2), (6, 1, 128, 40)])
+def test_split_records_merged_in_the_output_projection(nq, nkv, d, splits):
+    """Decode attention leaves its split records; the next projection merges
+    them on the way in.  Same result as merging first."""
+    o = ops()
+    lengths = [700, 1, 130]
+    case = PagedCase(lengths, [1] * 3, nq, nkv, d, "bfloat16", seed=d)
+    case.fill_cache()
+    for s, L in enumerate(lengths):
+        pg = int(case.table[s, (L - 1) // 64])
+        case.k_cache[pg, :, (L - 1) % 64] = case.k[s][L - 1]
+        case.v_cache[pg, :, (L - 1) % 64] = case.v[s][L - 1]
+    pos, seq, q, _, _ = case.packed()
+    n = 3
+    qd = q.reshape(n, -1).bfloat16().to(DEV)
+    kc, vc = case.k_cache.bfloat16().to(DEV), case.v_cache.bfloat16().to(DEV)
+    g = torch.Generator().manual_seed(1)
+    wo = (torch.randn(40, nq * d, generator=g) / math.sqrt(nq * d)).bfloat16()
+    attn = torch.empty(n, nq * d, dtype=torch.bfloat16, device=DEV)
+    partial = torch.empty(n * nq * splits * (d + 2), device=DEV)
+    args = (qd, nq * d, kc, vc, pos.to(DEV), seq.to(DEV), case.table.to(DEV), attn, nq, nkv, d, 0,
+            1.0 / math.sqrt(d), splits, partial)
+    o.attention_decode(*args, merge=True)
+    first = torch.zeros(n, 40, device=DEV)
+    o.gemv_bf16(wo.to(DEV), None, first, o.EPI_ADD_F32, x=attn)
+    o.attention_decode(*args, merge=False)
+    second = torch.zeros(n, 40, device=DEV)
+    o.gemv_bf16(wo.to(DEV), None, second, o.EPI_ADD_F32, partial=partial, splits=splits, heads=nq,
+                head_dim=d, m=n)
+    want = torch.cat([P.causal_attention(case.q[s], case.k[s], case.v[s].bfloat16().float())[L - 1:]
+                      .reshape(1, -1) for s, L in enumerate(lengths)])
+    close(attn, want, "bfloat16", "merged attention")
+    close(second, P.linear(want.bfloat16(), wo), "bfloat16", "projection of merged records")
+    close(second, first, "bfloat16", "merge in the prologue vs merge kernel")
+    o.check_status(DEV)

@@ -71,8 +71,9 @@ def test_position_part_builds_the_reference_table():
     assert POSITIONS.build("none", {}, "", torch.float32, DEV).rotary_tables() is None
 
 
+@pytest.mark.parametrize("decode", [False, True])
 @pytest.mark.parametrize("dtype", list(DT))
-def test_feed_forward_part(dtype):
+def test_feed_forward_part(dtype, decode):
     from nnis_b200.engine.workspace import Workspace
     from nnis_b200.parts import FEED_FORWARDS
     H, I = 40, 88
@@ -89,8 +90,9 @@ def test_feed_forward_part(dtype):
     residual = torch.randn(6, H)
     res = residual.to(DEV).clone()
 
-    class Ctx:
+    class Ctx:  # decode steps take the fused kernels in bfloat16
         workspace = Workspace(DEV)
+    Ctx.decode = decode
     part.forward(x.to(DEV), Ctx, res)
     bf = dtype == "bfloat16"
     gate = P.linear(x, w["L.g.weight"], w["L.g.bias"])
