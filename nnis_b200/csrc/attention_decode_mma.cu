@@ -1,0 +1,427 @@
+// Decode attention over the paged bfloat16 cache on the tensor cores, for head
+// sizes 64 and 128: one query token per sequence against its whole context.
+//
+// The query heads that share a kv head (up to 16) form the 16 rows of an
+// m16n8k16 tile, so K and V are read once for the whole group and the scores and
+// the weighted sum of values are matrix products; the softmax between them stays
+// in float32 registers.  One CTA of four warps owns (kv head, group of query
+// heads, sequence, slice of the key range).  Pages of K and V (64 keys) come
+// into shared memory with 16-byte cp.async copies, several pages ahead, into
+// rows whose 16-byte chunks are XOR-swizzled so that ldmatrix meets no bank
+// conflict; each warp takes 16 keys of every page and keeps its own running
+// (max, sum, output); warps are merged through shared memory at the end.  With
+// several slices the partial results go to scratch, and the slice that arrives
+// last (a ticket per group) merges them, in a fixed order, into the output.
+//
+// The step is bound by the bytes of K and V; the tensor cores are here to keep
+// the instruction count per byte low, not for their throughput.
+// NNIS: crates/nnis-model/src/kernels.rs:66-125 (one thread per query head).
+#include <float.h>
+
+#include "async_copy.cuh"
+#include "common.cuh"
+
+namespace nnis {
+
+constexpr int kMmaWarps = 4;
+constexpr int kPage = 64;
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ void cp_async16(void* dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dst_smem)), "l"(src)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// element offset of 16-byte chunk `chunk` of row `row` in a [rows, D] tile
+template <int D>
+__device__ __forceinline__ int swz(int row, int chunk) {
+    return row * D + (((chunk & ~7) | ((chunk & 7) ^ (row & 7))) << 3);
+}
+
+template <int D>
+__global__ void __launch_bounds__(kMmaWarps * 32)
+attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ k_cache,
+                       const bf16* __restrict__ v_cache, const int* __restrict__ token_pos,
+                       const int* __restrict__ token_seq, const int* __restrict__ page_table,
+                       int table_cols, bf16* __restrict__ out, float* __restrict__ partial,
+                       unsigned* __restrict__ tickets, int nq, int nkv, int window, float scale,
+                       int n_splits, int head_tiles, int stages) {
+    constexpr int CH = D / 8;    // 16-byte chunks per row
+    constexpr int NT = D / 8;    // n-tiles of the output
+    constexpr int KS = D / 16;   // k-steps of the score product
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    bf16* q_s = reinterpret_cast<bf16*>(smem_raw);           // [16, D] swizzled
+    bf16* tiles = q_s + 16 * D;                              // stages x (K [64, D], V [64, D])
+    __shared__ float sm_ml[kMmaWarps][16][2];
+    __shared__ bool is_last;
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, tid = threadIdx.x;
+    const int hk = blockIdx.x / head_tiles, tile = blockIdx.x % head_tiles;
+    const int G = nq / nkv;
+    const int g0 = tile * 16;
+    const int gcount = min(16, G - g0);
+    const int n = blockIdx.y, split = blockIdx.z;
+
+    pdl_wait();
+    const int pos = token_pos[n];
+    const int r_lo = lane >> 2, c_lo = (lane & 3) * 2;  // this thread's rows r_lo, r_lo + 8
+
+    float o[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+    if (pos >= 0) {
+        const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+        const int hi = pos + 1;
+        const int first_page = lo / kPage, last_page = (hi - 1) / kPage;
+        const int per = (last_page - first_page + n_splits) / n_splits;
+        const int p0 = first_page + split * per;
+        const int count = max(0, min(last_page + 1, p0 + per) - p0);
+        const int* table = page_table + (size_t)token_seq[n] * table_cols;
+        const size_t tile_elems = (size_t)kPage * D;
+
+        auto load_page = [&](int it) {
+            if (it < count) {
+                int page = table[p0 + it];
+                const bf16* ksrc = k_cache + (size_t)(page * nkv + hk) * tile_elems;
+                const bf16* vsrc = v_cache + (size_t)(page * nkv + hk) * tile_elems;
+                bf16* kd = tiles + (size_t)(it % stages) * 2 * tile_elems;
+                bf16* vd = kd + tile_elems;
+                for (int c = tid; c < kPage * CH; c += kMmaWarps * 32) {
+                    int row = c / CH, chunk = c % CH;
+                    cp_async16(kd + swz<D>(row, chunk), ksrc + (size_t)c * 8);
+                    cp_async16(vd + swz<D>(row, chunk), vsrc + (size_t)c * 8);
+                }
+            }
+            cp_async_commit();
+        };
+        for (int it = 0; it < stages - 1; ++it) load_page(it);
+        pdl_launch_dependents();
+
+        // the group's query rows, zero beyond the group
+        for (int c = tid; c < 16 * CH; c += kMmaWarps * 32) {
+            int row = c / CH, chunk = c % CH;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (row < gcount)
+                v = *reinterpret_cast<const uint4*>(q + (size_t)n * q_stride +
+                                                    (size_t)(hk * G + g0 + row) * D + chunk * 8);
+            *reinterpret_cast<uint4*>(q_s + swz<D>(row, chunk)) = v;
+        }
+        __syncthreads();
+        uint32_t qa[KS][4];
+#pragma unroll
+        for (int kk = 0; kk < KS; ++kk)
+            ldmatrix_x4(qa[kk], q_s + swz<D>(lane & 15, kk * 2 + (lane >> 4)));
+
+        const float sc = scale * kLog2e;
+        for (int it = 0; it < count; ++it) {
+            if (stages == 2) cp_async_wait<0>();
+            else if (stages == 3) cp_async_wait<1>();
+            else cp_async_wait<2>();
+            __syncthreads();  // page `it` has landed for everyone; the stage of page it-1 is free
+            load_page(it + stages - 1);
+            const bf16* kt = tiles + (size_t)(it % stages) * 2 * tile_elems;
+            const bf16* vt = kt + tile_elems;
+            const int key0 = warp * 16;  // this warp's 16 keys of the page
+            const int t0 = (p0 + it) * kPage + key0;
+
+            // scores: S[16 heads, 16 keys] = Q . K^T
+            float s[2][4];
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
+#pragma unroll
+            for (int kk = 0; kk < KS; kk += 2) {
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    // four 8x8 tiles: keys j*8.., dims kk*16 .. kk*16+31
+                    uint32_t b[4];
+                    ldmatrix_x4(b, kt + swz<D>(key0 + j * 8 + (lane & 7), kk * 2 + (lane >> 3)));
+                    mma_bf16(s[j], qa[kk], b[0], b[1]);
+                    mma_bf16(s[j], qa[kk + 1], b[2], b[3]);
+                }
+            }
+            // mask, scale (in log2 units) and this slice's row maxima
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    int t = t0 + j * 8 + c_lo + (e & 1);
+                    float v = (t >= lo && t < hi) ? s[j][e] * sc : -INFINITY;
+                    s[j][e] = v;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+            }
+            float alpha[2], base[2];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                float mn = fmaxf(m_run[r], mx[r]);
+                base[r] = mn == -INFINITY ? 0.f : mn;  // nothing seen yet: avoid inf - inf
+                alpha[r] = exp2f(m_run[r] - base[r]);
+                m_run[r] = mn;
+            }
+            uint32_t pa[4];
+            float psum[2] = {0.f, 0.f};
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                float p0v = exp2f(s[j][0] - base[0]), p1v = exp2f(s[j][1] - base[0]);
+                float p2v = exp2f(s[j][2] - base[1]), p3v = exp2f(s[j][3] - base[1]);
+                psum[0] += p0v + p1v;
+                psum[1] += p2v + p3v;
+                pa[j * 2] = pack_bf16(p0v, p1v);
+                pa[j * 2 + 1] = pack_bf16(p2v, p3v);
+            }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) l_run[r] = l_run[r] * alpha[r] + psum[r];
+            // output: O = O * alpha + P . V
+#pragma unroll
+            for (int jn = 0; jn < NT; jn += 2) {
+                uint32_t b[4];
+                // keys 0-7 / 8-15 of this warp's slice, dims jn*8 .. jn*8+15
+                ldmatrix_x4_trans(b, vt + swz<D>(key0 + (lane & 15), jn + (lane >> 4)));
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    o[jn][e] *= alpha[e >> 1];
+                    o[jn + 1][e] *= alpha[e >> 1];
+                }
+                mma_bf16(o[jn], pa, b[0], b[1]);
+                mma_bf16(o[jn + 1], pa, b[2], b[3]);
+            }
+        }
+        cp_async_wait<0>();
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+            l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+        }
+    }
+    __syncthreads();  // everyone is done with the tiles: reuse them for the merge
+
+    // ---- merge the four warps: (m, l) through sm_ml, outputs through the tiles ----
+    float* o_s = reinterpret_cast<float*>(smem_raw);  // [warps, 16, D] float32
+    if ((lane & 3) == 0) {
+        sm_ml[warp][r_lo][0] = m_run[0];
+        sm_ml[warp][r_lo][1] = l_run[0];
+        sm_ml[warp][r_lo + 8][0] = m_run[1];
+        sm_ml[warp][r_lo + 8][1] = l_run[1];
+    }
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        float* base0 = o_s + ((size_t)warp * 16 + r_lo) * D + j * 8 + c_lo;
+        base0[0] = o[j][0];
+        base0[1] = o[j][1];
+        base0[8 * D] = o[j][2];
+        base0[8 * D + 1] = o[j][3];
+    }
+    __syncthreads();
+    // thread -> (row, 8 dims); 16 rows x D/8 chunks = 2 D items over 128 threads
+    for (int item = tid; item < 16 * CH; item += kMmaWarps * 32) {
+        int row = item / CH, chunk = item % CH;
+        if (row >= gcount) continue;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kMmaWarps; ++w) mm = fmaxf(mm, sm_ml[w][row][0]);
+        float ll = 0.f, acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (mm != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < kMmaWarps; ++w) {
+                float f = exp2f(sm_ml[w][row][0] - mm);
+                ll += sm_ml[w][row][1] * f;
+                const float* src = o_s + ((size_t)w * 16 + row) * D + chunk * 8;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[e] = fmaf(src[e], f, acc[e]);
+            }
+        }
+        int hq = hk * G + g0 + row;
+        if (n_splits == 1) {
+            float inv = ll > 0.f ? 1.0f / ll : 0.f;
+            bf16* dst = out + ((size_t)n * nq + hq) * D + chunk * 8;
+            store4(dst, make_float4(acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv));
+            store4(dst + 4, make_float4(acc[4] * inv, acc[5] * inv, acc[6] * inv, acc[7] * inv));
+        } else {
+            float* rec = partial + (((size_t)n * nq + hq) * n_splits + split) * (size_t)(D + 2);
+            if (chunk == 0) {
+                rec[0] = mm;  // log2 units
+                rec[1] = ll;
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) rec[2 + chunk * 8 + e] = acc[e];
+        }
+    }
+    if (n_splits == 1) return;
+
+    // ---- the slice that arrives last merges all slices of its group ----------------
+    __threadfence();
+    __syncthreads();
+    unsigned* ticket = tickets + ((size_t)n * nkv + hk) * head_tiles + tile;
+    if (tid == 0) is_last = atomicAdd(ticket, 1u) == (unsigned)n_splits - 1u;
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    // Every load of a phase is independent of the others, so each phase costs one
+    // trip to L2: (max, sum) of all slices -> weights in shared memory -> four
+    // interleaved groups of slices summed side by side -> the groups added in order.
+    float* w_s = reinterpret_cast<float*>(smem_raw);            // [n_splits, 16] weights
+    float* l_s = w_s + 64 * 16;                                 // [16] total sums
+    float* g_s = l_s + 16;                                      // [4, 16, D] group sums
+    for (int item = tid; item < n_splits * gcount; item += kMmaWarps * 32) {
+        int sp = item / gcount, row = item % gcount;
+        const float* r = partial + (((size_t)n * nq + hk * G + g0 + row) * n_splits + sp) * (size_t)(D + 2);
+        float mv = r[0], lv = r[1];
+        w_s[sp * 16 + row] = lv > 0.f ? mv : -INFINITY;  // the max, for now
+        w_s[(64 + sp) * 16 + row] = lv;                  // parked beyond the weights
+    }
+    __syncthreads();
+    if (tid < gcount) {
+        float mm = -INFINITY;
+        for (int sp = 0; sp < n_splits; ++sp) mm = fmaxf(mm, w_s[sp * 16 + tid]);
+        float ll = 0.f;
+        for (int sp = 0; sp < n_splits; ++sp) {
+            float mv = w_s[sp * 16 + tid];
+            float f = mv == -INFINITY ? 0.f : exp2f(mv - mm);
+            w_s[sp * 16 + tid] = f;
+            ll += w_s[(64 + sp) * 16 + tid] * f;
+        }
+        l_s[tid] = ll;
+    }
+    __syncthreads();
+    for (int item = tid; item < gcount * CH * 4; item += kMmaWarps * 32) {
+        int grp4 = item & 3, rc = item >> 2;
+        int row = rc / CH, chunk = rc % CH;
+        const float* rec = partial + ((size_t)n * nq + hk * G + g0 + row) * n_splits * (size_t)(D + 2) +
+                           2 + chunk * 8;
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+        for (int sp = grp4; sp < n_splits; sp += 4) {
+            float f = w_s[sp * 16 + row];
+            const float* r = rec + (size_t)sp * (D + 2);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[e] = fmaf(r[e], f, acc[e]);
+        }
+        float* dst = g_s + ((size_t)grp4 * 16 + row) * D + chunk * 8;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) dst[e] = acc[e];
+    }
+    __syncthreads();
+    for (int item = tid; item < gcount * CH; item += kMmaWarps * 32) {
+        int row = item / CH, chunk = item % CH;
+        int hq = hk * G + g0 + row;
+        float ll = l_s[row];
+        float inv = ll > 0.f ? 1.0f / ll : 0.f;
+        float acc[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float* src = g_s + (size_t)row * D + chunk * 8 + e;
+            acc[e] = ((src[0] + src[16 * D]) + src[32 * D]) + src[48 * D];
+        }
+        bf16* dst = out + ((size_t)n * nq + hq) * D + chunk * 8;
+        store4(dst, make_float4(acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv));
+        store4(dst + 4, make_float4(acc[4] * inv, acc[5] * inv, acc[6] * inv, acc[7] * inv));
+    }
+    if (tid == 0) *ticket = 0u;
+}
+
+template <int D>
+static int launch_mma(dim3 grid, bool pdl, cudaStream_t stream, const bf16* q, int q_stride,
+                      const bf16* k, const bf16* v, const int* pos, const int* seq, const int* table,
+                      int cols, bf16* out, float* partial, unsigned* tickets, int nq, int nkv,
+                      int window, float scale, int n_splits, int head_tiles) {
+    size_t stage_bytes = 2 * (size_t)kPage * D * sizeof(bf16);
+    int stages = D <= 64 ? 4 : 3;
+    size_t smem = 16 * D * sizeof(bf16) + stages * stage_bytes;
+    size_t merge_bytes = ((size_t)kMmaWarps * 16 * D + 2 * 64 * 16 + 16) * sizeof(float);
+    if (smem < merge_bytes) smem = merge_bytes;
+    auto kernel = attn_decode_mma_kernel<D>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kMmaWarps * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, q, q_stride, k, v, pos, seq, table, cols, out,
+                                       partial, tickets, nq, nkv, window, scale, n_splits, head_tiles,
+                                       stages);
+    return e == cudaSuccess ? NNIS_OK : (int)e;
+}
+
+}  // namespace nnis
+
+// Takes head sizes 64 and 128 with 64-key pages; anything else is refused with
+// NNIS_ERR_UNSUPPORTED and goes to the general decode kernel.  Scratch: with
+// n_splits > 1, `partial` (n_tokens * nq * n_splits * (d + 2) floats) and
+// `tickets` (n_tokens * nkv * ceil(group / 16) counters, zero before the first
+// launch; the kernel leaves them zero).
+NNIS_API int nnis_attention_decode_mma(const void* q, int q_stride, const void* k_cache,
+                                       const void* v_cache, const int* token_pos,
+                                       const int* token_seq, const int* page_table, int table_cols,
+                                       void* out, float* partial, unsigned* tickets, int n_tokens,
+                                       int nq, int nkv, int d, int page_size, int window, float scale,
+                                       int n_splits, int pdl, cudaStream_t stream) {
+    using namespace nnis;
+    if (n_tokens <= 0 || nq <= 0 || nkv <= 0 || nq % nkv || table_cols <= 0 || n_splits <= 0 ||
+        window < 0)
+        return NNIS_ERR_ARGUMENT;
+    if ((d != 64 && d != 128) || page_size != kPage) return NNIS_ERR_UNSUPPORTED;
+    if (n_tokens > 65535 || n_splits > 64) return NNIS_ERR_UNSUPPORTED;
+    if (n_splits > 1 && (!partial || !tickets)) return NNIS_ERR_ARGUMENT;
+    if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) % 16 ||
+        (q_stride % 8))
+        return NNIS_ERR_ALIGNMENT;
+    int G = nq / nkv;
+    int head_tiles = (G + 15) / 16;
+    dim3 grid(nkv * head_tiles, n_tokens, n_splits);
+    if (d == 64)
+        return launch_mma<64>(grid, pdl != 0, stream, (const bf16*)q, q_stride, (const bf16*)k_cache,
+                              (const bf16*)v_cache, token_pos, token_seq, page_table, table_cols,
+                              (bf16*)out, partial, tickets, nq, nkv, window, scale, n_splits,
+                              head_tiles);
+    return launch_mma<128>(grid, pdl != 0, stream, (const bf16*)q, q_stride, (const bf16*)k_cache,
+                           (const bf16*)v_cache, token_pos, token_seq, page_table, table_cols,
+                           (bf16*)out, partial, tickets, nq, nkv, window, scale, n_splits, head_tiles);
+}

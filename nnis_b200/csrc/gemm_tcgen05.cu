@@ -1,0 +1,347 @@
+// bfloat16 matrix product on the fifth-generation tensor cores of sm_100a:
+// C[M, N] (op)= A[M, K] . W[N, K]^T + bias, float32 accumulation in tensor memory.
+//
+// One CTA computes a 128 x BN tile (BN = 64 or 128).  Its six warps have fixed
+// roles:
+//   warp 0  one lane issues TMA tile loads (cp.async.bulk.tensor, 128-byte
+//           swizzle) of A and W, 64 columns of K at a time, into a ring of shared
+//           memory stages, each guarded by a "full" and an "empty" mbarrier;
+//   warp 1  allocates tensor memory, and one lane issues tcgen05.mma
+//           (kind::f16, M = 128, N = BN, K = 16) four times per stage from shared
+//           memory descriptors, then tcgen05.commit to hand the stage back and,
+//           after the last one, to tell the epilogue that the accumulator is done;
+//   warps 2-5  read the accumulator with tcgen05.ld (each warp its own 32 lanes
+//           of tensor memory = 32 rows of the tile), add the bias and store, as
+//           bfloat16, as float32, or added into a float32 destination.
+// Rows and columns beyond M, N and K are zero-filled by TMA on the way in and
+// masked on the way out, so any M and N and any K that is a multiple of 8 work.
+//
+// Every wait is bounded: a wait that runs out sets a status word and an abort
+// flag that the other roles see; all warps still meet at the end, and tensor
+// memory is always freed.
+// NNIS computes the same product on CUDA cores: crates/nnis-kernels/src/gemm.rs:16-64.
+#include <cuda.h>
+
+#include "async_copy.cuh"
+#include "common.cuh"
+
+namespace nnis {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;          // 64 bfloat16 = one 128-byte swizzle row
+constexpr int kUmmaK = 16;
+constexpr int kGemmThreads = 192;
+
+__device__ __forceinline__ void tma_load_2d(void* dst_smem, const CUtensorMap* map, int c0, int c1,
+                                            uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_addr(dst_smem)), "l"(map), "r"(c0), "r"(c1), "r"(smem_addr(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t columns) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_addr(dst_smem)),
+                 "r"(columns)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t columns) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(columns)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+// The mbarrier gets one arrival when every tcgen05.mma issued so far by this
+// thread has completed.
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                     smem_addr(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                       uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+          "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+          "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+          "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+          "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared memory matrix descriptor of a K-major tile whose rows are 128 bytes
+// (64 bfloat16) and 128-byte swizzled: 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_k128(uint32_t smem_byte_addr) {
+    uint64_t desc = 0;
+    desc |= (uint64_t)((smem_byte_addr >> 4) & 0x3FFF);   // start address, 16-byte units
+    desc |= (uint64_t)1 << 16;                            // leading byte offset (unused with swizzle)
+    desc |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset between 8-row groups
+    desc |= (uint64_t)1 << 46;                            // descriptor version of sm_100
+    desc |= (uint64_t)2 << 61;                            // SWIZZLE_128B
+    return desc;
+}
+
+// kind::f16 instruction descriptor: bfloat16 x bfloat16 -> float32, both K-major.
+__host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
+    return (1u << 4)                    // accumulator float32
+         | (1u << 7)                    // A bfloat16
+         | (1u << 10)                   // B bfloat16
+         | ((uint32_t)(n >> 3) << 17)   // N / 8
+         | ((uint32_t)(m >> 4) << 24);  // M / 16
+}
+
+struct GemmArgs {
+    const float* bias;
+    void* out;
+    int M, N, K;
+    int mode;  // 0 bfloat16, 1 float32, 2 add into float32
+    int* status;
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kGemmThreads)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+               GemmArgs g) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    // the swizzle pattern follows address bits: tiles start on 1024-byte boundaries
+    unsigned char* base = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr uint32_t kBytesA = kBM * kBK * 2, kBytesB = BN * kBK * 2;
+    unsigned char* tile_a = base;
+    unsigned char* tile_b = base + (size_t)STAGES * kBytesA;
+    __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar;
+    __shared__ uint32_t tmem_base_s;
+    __shared__ volatile int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * kBM, n0 = blockIdx.x * BN;
+    const int k_blocks = (g.K + kBK - 1) / kBK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(&acc_bar, 1);
+        abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) tmem_alloc(&tmem_base_s, BN);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_acc = tmem_base_s;
+
+    // A depends on the kernel before this one; W does not, but both come through
+    // the same ring, so wait first
+    pdl_wait();
+    pdl_launch_dependents();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                int s = kb % STAGES;
+                if (kb >= STAGES && !mbar_wait(&empty_bar[s], (uint32_t)(kb / STAGES - 1) & 1u)) {
+                    abort_flag = 1;
+                    break;
+                }
+                if (abort_flag) break;
+                mbar_expect_tx(&full_bar[s], kBytesA + kBytesB);
+                tma_load_2d(tile_a + (size_t)s * kBytesA, &map_a, kb * kBK, m0, &full_bar[s]);
+                tma_load_2d(tile_b + (size_t)s * kBytesB, &map_w, kb * kBK, n0, &full_bar[s]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc(kBM, BN);
+            bool ok = true;
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                int s = kb % STAGES;
+                if (!mbar_wait(&full_bar[s], (uint32_t)(kb / STAGES) & 1u) || abort_flag) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                uint32_t a_addr = smem_addr(tile_a + (size_t)s * kBytesA);
+                uint32_t b_addr = smem_addr(tile_b + (size_t)s * kBytesB);
+#pragma unroll
+                for (int k = 0; k < kBK / kUmmaK; ++k) {
+                    // 16 columns of K further along the swizzled row: 32 bytes
+                    tc_mma(tmem_acc, smem_desc_k128(a_addr + k * kUmmaK * 2),
+                           smem_desc_k128(b_addr + k * kUmmaK * 2), idesc, (kb | k) != 0);
+                }
+                tc_commit(&empty_bar[s]);  // the stage is free once these MMAs have read it
+            }
+            if (!ok) abort_flag = 1;
+            tc_commit(&acc_bar);  // arrives when all MMAs above are complete (also after an abort)
+        }
+    } else {
+        // epilogue: warp w reads tensor-memory lanes 32 (w % 4) .. + 31 = tile rows
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        const int m = m0 + row;
+        bool ok = mbar_wait(&acc_bar, 0);
+        ok = __all_sync(0xffffffffu, ok) && !abort_flag;
+        if (!ok) {
+            abort_flag = 1;
+        } else {
+            tc_fence_after();
+            const bool vec_ok = (g.N % 8 == 0);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t v[32];
+                tmem_load32(tmem_acc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+                if (m >= g.M) continue;
+                const int nb = n0 + c0;
+                if (nb >= g.N) continue;
+                const size_t off = (size_t)m * g.N + nb;
+                if (vec_ok && nb + 32 <= g.N) {
+                    float f[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        f[i] = __uint_as_float(v[i]) + (g.bias ? g.bias[nb + i] : 0.f);
+                    if (g.mode == 0) {
+                        bf16* o = reinterpret_cast<bf16*>(g.out) + off;
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            uint4 pk;
+                            __nv_bfloat162 p0 = __floats2bfloat162_rn(f[i], f[i + 1]);
+                            __nv_bfloat162 p1 = __floats2bfloat162_rn(f[i + 2], f[i + 3]);
+                            __nv_bfloat162 p2 = __floats2bfloat162_rn(f[i + 4], f[i + 5]);
+                            __nv_bfloat162 p3 = __floats2bfloat162_rn(f[i + 6], f[i + 7]);
+                            pk.x = *reinterpret_cast<uint32_t*>(&p0);
+                            pk.y = *reinterpret_cast<uint32_t*>(&p1);
+                            pk.z = *reinterpret_cast<uint32_t*>(&p2);
+                            pk.w = *reinterpret_cast<uint32_t*>(&p3);
+                            *reinterpret_cast<uint4*>(o + i) = pk;
+                        }
+                    } else {
+                        float* o = reinterpret_cast<float*>(g.out) + off;
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) {
+                            float4 cur = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (g.mode == 2) cur = *reinterpret_cast<const float4*>(o + i);
+                            *reinterpret_cast<float4*>(o + i) =
+                                make_float4(cur.x + f[i], cur.y + f[i + 1], cur.z + f[i + 2],
+                                            cur.w + f[i + 3]);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        int n = nb + i;
+                        if (n < g.N) {
+                            float val = __uint_as_float(v[i]) + (g.bias ? g.bias[n] : 0.f);
+                            if (g.mode == 0) reinterpret_cast<bf16*>(g.out)[off + i] = __float2bfloat16_rn(val);
+                            else if (g.mode == 1) reinterpret_cast<float*>(g.out)[off + i] = val;
+                            else reinterpret_cast<float*>(g.out)[off + i] += val;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_acc, BN);
+    }
+    if (threadIdx.x == 0 && abort_flag && g.status) atomicExch(g.status, 3);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) ==
+                cudaSuccess && qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// [rows, K] row-major bfloat16, boxes of box_rows x 64 columns, 128-byte swizzle
+static bool make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
+    EncodeTiledFn fn = encode_tiled();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box,
+              elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int STAGES>
+static int launch_gemm_tc(const CUtensorMap& ma, const CUtensorMap& mw, const GemmArgs& g, bool pdl,
+                          cudaStream_t stream) {
+    size_t smem = (size_t)STAGES * (kBM + BN) * kBK * 2 + 1024;
+    auto kernel = gemm_tc_kernel<BN, STAGES>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((g.N + BN - 1) / BN, (g.M + kBM - 1) / kBM);
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    e = cudaLaunchKernelEx(&cfg, kernel, ma, mw, g);
+    return e == cudaSuccess ? NNIS_OK : (int)e;
+}
+
+}  // namespace nnis
+
+// Refuses (NNIS_ERR_UNSUPPORTED): K not a multiple of 8, grids too large, a
+// driver without tensor-map encoding; operands must be 16-byte aligned.
+NNIS_API int nnis_gemm_tc(const void* A, const void* W, const float* bias, void* C, int M, int N,
+                          int K, int mode, int sm_count, int* status, int pdl, cudaStream_t stream) {
+    using namespace nnis;
+    if (M <= 0 || N <= 0 || K <= 0 || !A || !W || !C || mode < 0 || mode > 2) return NNIS_ERR_ARGUMENT;
+    if (K % 8) return NNIS_ERR_UNSUPPORTED;
+    if (((uintptr_t)A | (uintptr_t)W) % 16) return NNIS_ERR_ALIGNMENT;
+    if (((uintptr_t)C % 16) != 0) return NNIS_ERR_ALIGNMENT;
+    if ((M + kBM - 1) / kBM > 65535) return NNIS_ERR_UNSUPPORTED;
+    int sms = sm_count > 0 ? sm_count : 148;
+    long tiles128 = (long)((N + 127) / 128) * ((M + kBM - 1) / kBM);
+    bool wide = tiles128 >= sms;
+    CUtensorMap ma, mw;
+    if (!make_map(&ma, A, M, K, kBM) || !make_map(&mw, W, N, K, wide ? 128 : 64))
+        return NNIS_ERR_UNSUPPORTED;
+    GemmArgs g;
+    g.bias = bias; g.out = C; g.M = M; g.N = N; g.K = K; g.mode = mode; g.status = status;
+    if (wide) return launch_gemm_tc<128, 5>(ma, mw, g, pdl != 0, stream);
+    return launch_gemm_tc<64, 6>(ma, mw, g, pdl != 0, stream);
+}

@@ -367,20 +367,68 @@ def attention_decode(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_ca
         "attention_decode", 2 if n_splits > 1 and merge else 1)
 
 
+def attention_decode_mma_takes(head_dim: int, page_size: int) -> bool:
+    return head_dim in (64, 128) and page_size == 64
+
+
+def attention_decode_mma(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                         token_pos: torch.Tensor, token_seq: torch.Tensor, page_table: torch.Tensor,
+                         out: torch.Tensor, heads: int, kv_heads: int, head_dim: int, window: int,
+                         scale: float, n_splits: int = 1, partial: Optional[torch.Tensor] = None,
+                         tickets: Optional[torch.Tensor] = None) -> None:
+    """Decode attention on the tensor cores (head sizes 64 and 128).  With several
+    splits the slice that finishes last merges them: ``out`` is always complete.
+    ``tickets``: int32 zeros, ``mma_ticket_count`` of them, left zero."""
+    _cuda(k_cache, v_cache, token_pos, token_seq, page_table, out, partial, tickets)
+    _need(q.is_cuda and q.dtype == torch.bfloat16 == k_cache.dtype == out.dtype,
+          "attention_decode_mma: bfloat16 tensors")
+    n = out.shape[0]
+    pages, nkv, page_size, d = k_cache.shape
+    _need(nkv == kv_heads and d == head_dim, "cache shape differs from the heads given")
+    _need(attention_decode_mma_takes(head_dim, page_size),
+          f"attention_decode_mma: head_dim {head_dim} / page {page_size} is not taken")
+    _need(heads % kv_heads == 0, "attention: heads is not a multiple of kv_heads")
+    _need(pages * nkv * page_size < 2 ** 31, "attention: the cache has too many rows")
+    _need(out.shape[1] == heads * head_dim and n <= 65535, "attention: out [n <= 65535, heads * d]")
+    if n_splits > 1:
+        _need(partial is not None and partial.dtype == torch.float32
+              and partial.numel() >= n * heads * n_splits * (head_dim + 2),
+              "attention: partial scratch too small")
+        _need(tickets is not None and tickets.dtype == torch.int32
+              and tickets.numel() >= mma_ticket_count(n, heads, kv_heads), "attention: tickets")
+    _check(_lib().nnis_attention_decode_mma(
+        _ptr(q), q_stride, _ptr(k_cache), _ptr(v_cache), _ptr(token_pos), _ptr(token_seq),
+        _ptr(page_table), page_table.shape[1], _ptr(out), _ptr(partial), _ptr(tickets), n, heads,
+        kv_heads, head_dim, page_size, window, ctypes.c_float(scale), n_splits, PDL, _stream()),
+        "attention_decode_mma")
+
+
+def mma_ticket_count(n: int, heads: int, kv_heads: int) -> int:
+    return n * kv_heads * (-(-(heads // kv_heads) // 16))
+
+
+TC_GEMM = 0 if __import__("os").environ.get("NNIS_TC_GEMM", "1") == "0" else 1
+
+
 def gemm_tc_takes(m: int, n: int, k: int) -> bool:
-    """Whether the tcgen05 kernel runs this bfloat16 product (else CUDA cores)."""
-    return False
+    """Whether the tcgen05 kernel runs this bfloat16 product (else CUDA cores):
+    K a multiple of 8 (rows of 16 bytes for TMA) and enough rows to fill a tile."""
+    return bool(TC_GEMM) and m > 16 and k % 8 == 0 and -(-m // 128) <= 65535
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
             mode: int) -> None:
-    raise KernelError("gemm_tc: not available")
-
-
-def advance(tokens: torch.Tensor, pos: torch.Tensor, picked: torch.Tensor) -> None:
-    """tokens = picked; pos += 1 on live rows (pos >= 0)."""
-    _cuda(tokens, pos, picked)
-    _need(tokens.dtype == pos.dtype == picked.dtype == torch.int32, "advance: int32")
-    n = tokens.numel()
-    _need(pos.numel() == n and picked.numel() >= n, "advance: sizes differ")
-    _check(_lib().nnis_advance(_ptr(tokens), _ptr(pos), _ptr(picked), n, _stream()), "advance")
+    """out (op)= a . w^T + bias on the tensor cores (tcgen05, float32 accumulation
+    in tensor memory); bfloat16 operands."""
+    _cuda(a, w, bias, out)
+    m, k = a.shape
+    n = w.shape[0]
+    _need(a.dtype == w.dtype == torch.bfloat16 and w.shape[1] == k, "gemm_tc: bfloat16 a [m, k], w [n, k]")
+    _need(tuple(out.shape) == (m, n), "gemm_tc: out [m, n]")
+    _need(out.dtype == (torch.bfloat16 if mode == STORE else torch.float32), "gemm_tc: out dtype vs mode")
+    _need(gemm_tc_takes(m, n, k), f"gemm_tc: shape m={m} n={n} k={k} is not taken")
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() == n, "gemm_tc: bias float32 [n]")
+    _check(_lib().nnis_gemm_tc(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), m, n, k, mode,
+                               sm_count(a.device), _ptr(status_word(a.device)), PDL, _stream()),
+           "gemm_tc")

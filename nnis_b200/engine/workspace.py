@@ -32,5 +32,20 @@ class Workspace:
             self._buffers[key] = buf
         return buf[:count].view(*shape)
 
+    def zeros(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+        """A buffer that is zero when first handed out and that its users leave
+        zero (tickets of kernels that reset them); never moved once made."""
+        count = 1
+        for s in shape:
+            count *= int(s)
+        key = (name + "#zeros", dtype, count)
+        buf = self._buffers.get(key)
+        if buf is None:
+            if self.frozen:
+                raise RuntimeError(f"workspace buffer {name!r} would be made after graph capture")
+            buf = torch.zeros(max(count, 1), dtype=dtype, device=self.device)
+            self._buffers[key] = buf
+        return buf[:count].view(*shape)
+
     def bytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in self._buffers.values())

@@ -131,27 +131,32 @@ class Attention(Part):
                            sin, cache.k if self.own_kv else None, cache.v if self.own_kv else None,
                            nq, self.stored_kv, d, cache.page_size)
             q_buf, q_stride = qkv, qkv.shape[1]
-        merged = True
-        if self.dtype == torch.bfloat16 and ctx.decode and n <= 65535:
+        if self.dtype == torch.bfloat16 and ctx.decode and n <= 65535 \
+                and ops.attention_decode_mma_takes(d, cache.page_size):
+            # tensor-core kernel: a CTA per (kv head, up to 16 query heads, slice)
+            tiles = -(-(nq // nkv) // 16)
+            splits = ctx.decode_splits(n * nkv * tiles)
+            partial = tickets = None
+            if splits > 1:
+                partial = ws.get("attn_partial", (n * nq * splits * (d + 2),), torch.float32)
+                tickets = ws.zeros("attn_tickets", (ops.mma_ticket_count(n, nq, nkv),), torch.int32)
+            ops.attention_decode_mma(q_buf, q_stride, cache.k, cache.v, ctx.token_pos, ctx.token_seq,
+                                     table, attn, nq, nkv, d, self.window, self.scale, splits,
+                                     partial, tickets)
+        elif self.dtype == torch.bfloat16 and ctx.decode and n <= 65535:
             tiles = -(-(nq // nkv) // 4)
             splits = ctx.decode_splits(n * nkv * tiles)
             partial = ws.get("attn_partial", (n * nq * splits * (d + 2),), torch.float32) \
                 if splits > 1 else None
-            # with the fused output projection the split records are merged there
-            merged = not (splits > 1 and self._decode_kernels(ctx, n))
             ops.attention_decode(q_buf, q_stride, cache.k, cache.v, ctx.token_pos, ctx.token_seq,
-                                 table, attn, nq, nkv, d, self.window, self.scale, splits, partial,
-                                 merge=merged)
+                                 table, attn, nq, nkv, d, self.window, self.scale, splits, partial)
         else:
             splits = ctx.attention_splits(n * nq)
             partial = ws.get("attn_partial", (n * nq * splits * (d + 2),), torch.float32) \
                 if splits > 1 else None
             ops.attention_generic(q_buf, q_stride, cache.k, cache.v, ctx.token_pos, ctx.token_seq,
                                   table, attn, nq, nkv, d, self.window, self.scale, splits, partial)
-        if self._decode_kernels(ctx, n) and not merged:
-            ops.gemv_bf16(self.w_o, self.b_o, residual, ops.EPI_ADD_F32, partial=partial,
-                          splits=splits, heads=nq, head_dim=d, m=n)
-        elif self._decode_kernels(ctx, n):
+        if self._decode_kernels(ctx, n):
             ops.gemv_bf16(self.w_o, self.b_o, residual, ops.EPI_ADD_F32, x=attn)
         else:
             linear(attn, self.w_o, self.b_o, residual, ADD_F32)

@@ -492,3 +492,104 @@ def test_split_records_merged_in_the_output_projection(nq, nkv, d, splits):
     close(second, P.linear(want.bfloat16(), wo), "bfloat16", "projection of merged records")
     close(second, first, "bfloat16", "merge in the prologue vs merge kernel")
     o.check_status(DEV)
+
+
+@pytest.mark.parametrize("nq,nkv,d", [(9, 3, 64), (4, 4, 64), (32, 1, 64), (20, 1, 128), (6, 2, 128)])
+@pytest.mark.parametrize("window", [0, 100])
+def test_attention_decode_on_tensor_cores(nq, nkv, d, window):
+    """Head sizes 64 and 128, groups below, at and above 16 heads, contexts from
+    one key to many pages, a padding row, one slice and many."""
+    o = ops()
+    lengths = [1, 64, 65, 300, 1000, 7, 129]
+    case = PagedCase(lengths, [1] * len(lengths), nq, nkv, d, "bfloat16", seed=nq + d)
+    case.fill_cache()
+    for s, L in enumerate(lengths):
+        pg = int(case.table[s, (L - 1) // 64])
+        case.k_cache[pg, :, (L - 1) % 64] = case.k[s][L - 1]
+        case.v_cache[pg, :, (L - 1) % 64] = case.v[s][L - 1]
+    pos, seq, q, _, _ = case.packed()
+    pos = torch.cat([pos, torch.tensor([-1], dtype=torch.int32)])
+    seq = torch.cat([seq, torch.tensor([0], dtype=torch.int32)])
+    n = pos.numel()
+    qd = torch.cat([q.reshape(n - 1, -1), torch.ones(1, nq * d)]).bfloat16().to(DEV)
+    kc, vc = case.k_cache.bfloat16().to(DEV), case.v_cache.bfloat16().to(DEV)
+    want = torch.cat([P.causal_attention(case.q[s], case.k[s], case.v[s].bfloat16().float(),
+                                         window)[L - 1:].reshape(1, -1)
+                      for s, L in enumerate(lengths)])
+    tickets = torch.zeros(o.mma_ticket_count(n, nq, nkv), dtype=torch.int32, device=DEV)
+    for splits in (1, 2, 7, 1, 16):
+        out = torch.full((n, nq * d), 5.0, dtype=torch.bfloat16, device=DEV)
+        partial = torch.empty(n * nq * splits * (d + 2), device=DEV) if splits > 1 else None
+        o.attention_decode_mma(qd, nq * d, kc, vc, pos.to(DEV), seq.to(DEV), case.table.to(DEV), out,
+                               nq, nkv, d, window, 1.0 / math.sqrt(d), splits, partial, tickets)
+        close(out[:n - 1], want, "bfloat16", f"tensor-core decode attention splits {splits}")
+        assert float(out[n - 1].float().abs().max()) == 0
+        assert int(tickets.abs().sum()) == 0
+    assert not o.attention_decode_mma_takes(48, 64) and not o.attention_decode_mma_takes(64, 32)
+
+
+def test_tensor_core_decode_attention_finds_one_far_key():
+    o = ops()
+    nq, nkv, d, L, far = 8, 2, 64, 900, 77
+    case = PagedCase([L], [1], nq, nkv, d, "bfloat16", seed=9, scale=0.3)
+    for h in range(nkv):
+        case.k[0][far, h] = case.q[0][L - 1, h * 4] * 30.0
+    case.k[0] = case.k[0].bfloat16().float()
+    case.v[0][far] = 7.0
+    case.fill_cache()
+    pg = int(case.table[0, (L - 1) // 64])
+    case.k_cache[pg, :, (L - 1) % 64] = case.k[0][L - 1]
+    case.v_cache[pg, :, (L - 1) % 64] = case.v[0][L - 1]
+    pos, seq, q, _, _ = case.packed()
+    qd = q.reshape(1, -1).bfloat16().to(DEV)
+    kc, vc = case.k_cache.bfloat16().to(DEV), case.v_cache.bfloat16().to(DEV)
+    tickets = torch.zeros(o.mma_ticket_count(1, nq, nkv), dtype=torch.int32, device=DEV)
+    for window, sees in ((0, True), (L - far, True), (L - far - 1, False)):
+        for splits in (1, 5):
+            out = torch.empty(1, nq * d, dtype=torch.bfloat16, device=DEV)
+            partial = torch.empty(nq * splits * (d + 2), device=DEV)
+            o.attention_decode_mma(qd, nq * d, kc, vc, pos.to(DEV), seq.to(DEV), case.table.to(DEV),
+                                   out, nq, nkv, d, window, 1.0 / math.sqrt(d), splits, partial, tickets)
+            want = P.causal_attention(case.q[0], case.k[0], case.v[0].bfloat16().float(),
+                                      window)[L - 1:].reshape(1, -1)
+            close(out, want, "bfloat16", f"far key window {window} splits {splits}")
+            lead = out.view(nq, d)[0::4].float()
+            assert bool((lead > 6.5).all()) == sees
+
+
+@pytest.mark.parametrize("m", [17, 64, 128, 129, 300, 2048])
+@pytest.mark.parametrize("n,k", [(8, 16), (64, 72), (130, 200), (576, 576), (960, 576), (515, 1536)])
+def test_gemm_on_tcgen05(m, n, k):
+    """Any M and N, K in steps of 8: tails are zero-filled on the way in and
+    masked on the way out; bias, and the three output modes."""
+    o = ops()
+    assert o.gemm_tc_takes(m, n, k) and not o.gemm_tc_takes(m, n, k + 4) and not o.gemm_tc_takes(16, n, k)
+    g = torch.Generator().manual_seed(m * 7 + n + k)
+    a = torch.randn(m, k, generator=g).bfloat16()
+    w = (torch.randn(n, k, generator=g) / math.sqrt(k)).bfloat16()
+    bias = torch.randn(n, generator=g)
+    want = P.linear(a, w, bias)
+    out = torch.full((m, n), 7.0, dtype=torch.bfloat16, device=DEV)
+    o.gemm_tc(a.to(DEV), w.to(DEV), bias.to(DEV), out, o.STORE)
+    close(out, want, "bfloat16", "tcgen05 store")
+    out32 = torch.full((m, n), 7.0, device=DEV)
+    o.gemm_tc(a.to(DEV), w.to(DEV), None, out32, o.STORE_F32)
+    close(out32, P.linear(a, w), "float32", "tcgen05 store f32")
+    base = torch.randn(m, n, generator=g)
+    acc = base.to(DEV).clone()
+    o.gemm_tc(a.to(DEV), w.to(DEV), bias.to(DEV), acc, o.ADD_F32)
+    close(acc, base.double() + want, "float32", "tcgen05 add")
+    o.check_status(DEV)
+
+
+def test_gemm_on_tcgen05_many_k_blocks_reuse_every_stage():
+    o = ops()
+    g = torch.Generator().manual_seed(0)
+    m, n, k = 256, 256, 64 * 23 + 8
+    a = torch.randn(m, k, generator=g).bfloat16()
+    w = (torch.randn(n, k, generator=g) / math.sqrt(k)).bfloat16()
+    out = torch.empty(m, n, device=DEV)
+    for _ in range(3):
+        o.gemm_tc(a.to(DEV), w.to(DEV), None, out, o.STORE_F32)
+    close(out, P.linear(a, w), "float32", "tcgen05 long k")
+    o.check_status(DEV)
