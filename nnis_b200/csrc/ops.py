@@ -432,3 +432,12 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out:
     _check(_lib().nnis_gemm_tc(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), m, n, k, mode,
                                sm_count(a.device), _ptr(status_word(a.device)), PDL, _stream()),
            "gemm_tc")
+
+
+def advance(tokens: torch.Tensor, pos: torch.Tensor, picked: torch.Tensor) -> None:
+    """tokens = picked; pos += 1, on live rows (pos >= 0) only."""
+    _cuda(tokens, pos, picked)
+    _need(tokens.dtype == pos.dtype == picked.dtype == torch.int32, "advance: int32")
+    n = tokens.numel()
+    _need(pos.numel() == n and picked.numel() >= n, "advance: sizes differ")
+    _check(_lib().nnis_advance(_ptr(tokens), _ptr(pos), _ptr(picked), n, _stream()), "advance")
