@@ -403,6 +403,32 @@ def attention_decode_mma(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, 
         "attention_decode_mma")
 
 
+def attention_prefill_mma(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                          tiles: torch.Tensor, seq_first_row: torch.Tensor, seq_start: torch.Tensor,
+                          seq_count: torch.Tensor, page_table: torch.Tensor, out: torch.Tensor,
+                          heads: int, kv_heads: int, head_dim: int, window: int, scale: float) -> None:
+    """Prompt attention on the tensor cores (head sizes 64 and 128): packed query
+    tokens, 64 per tile, each over its own sequence's keys in the paged cache."""
+    _cuda(k_cache, v_cache, tiles, seq_first_row, seq_start, seq_count, page_table, out)
+    _need(q.is_cuda and q.dtype == torch.bfloat16 == k_cache.dtype == out.dtype,
+          "attention_prefill_mma: bfloat16 tensors")
+    pages, nkv, page_size, d = k_cache.shape
+    _need(nkv == kv_heads and d == head_dim, "cache shape differs from the heads given")
+    _need(attention_decode_mma_takes(head_dim, page_size),
+          f"attention_prefill_mma: head_dim {head_dim} / page {page_size} is not taken")
+    _need(heads % kv_heads == 0, "attention: heads is not a multiple of kv_heads")
+    _need(pages * nkv * page_size < 2 ** 31, "attention: the cache has too many rows")
+    _need(out.shape[1] == heads * head_dim, "attention: out [n, heads * d]")
+    for t in (tiles, seq_first_row, seq_start, seq_count):
+        _need(t.dtype == torch.int32, "attention_prefill_mma: int32 tables")
+    _need(tiles.dim() == 2 and tiles.shape[1] == 2 and tiles.shape[0] > 0, "tiles: int32 [n_tiles, 2]")
+    _check(_lib().nnis_attention_prefill_mma(
+        _ptr(q), q_stride, _ptr(k_cache), _ptr(v_cache), _ptr(tiles), tiles.shape[0],
+        _ptr(seq_first_row), _ptr(seq_start), _ptr(seq_count), _ptr(page_table), page_table.shape[1],
+        _ptr(out), heads, kv_heads, head_dim, page_size, window, ctypes.c_float(scale), _stream()),
+        "attention_prefill_mma")
+
+
 def mma_ticket_count(n: int, heads: int, kv_heads: int) -> int:
     return n * kv_heads * (-(-(heads // kv_heads) // 16))
 

@@ -8,7 +8,7 @@ n in its sequence (-1 marks a padding row, which no kernel stores or reads);
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import List, Sequence
+from typing import List, Optional, Sequence
 
 import torch
 
@@ -41,6 +41,14 @@ class StepContext:
     host_counts: Sequence[int] = field(default_factory=list)
     host_starts: Sequence[int] = field(default_factory=list)
     fixed_splits: int = 0  # > 0: a captured graph fixed the split count
+    # per sequence of the batch (device int32 [n_seqs]): the packed row of its
+    # first token in this step, that token's position, its number of tokens; and
+    # the 64-query tiles of the step, [n_tiles, 2] = (sequence, first query).
+    # None in decode steps and in contexts built without them.
+    seq_first_row: Optional[torch.Tensor] = None
+    seq_start: Optional[torch.Tensor] = None
+    seq_count: Optional[torch.Tensor] = None
+    q_tiles: Optional[torch.Tensor] = None
 
     def attention_splits(self, query_rows: int) -> int:
         """How many ways to cut each query's key range so the GPU is full when

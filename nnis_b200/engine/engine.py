@@ -28,6 +28,8 @@ from .context import StepContext
 from .model import DecoderModel
 from .workspace import Workspace
 
+QUERY_TILE = 64  # queries per CTA of the prompt attention kernel
+
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
            "f32": torch.float32, torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
 
@@ -167,6 +169,16 @@ class Engine:
         flat = tokens + pos + seq + slots + want_rows
         for rows in tables:
             flat += rows
+        decode = all(c == 1 for c in counts)
+        first_rows, tiles = [], []
+        if not decode:
+            row = 0
+            for i, c in enumerate(counts):
+                first_rows.append(row)
+                row += c
+                for q0 in range(0, c, QUERY_TILE):
+                    tiles += [i, q0]
+            flat += first_rows + starts + counts + tiles
         dev = self._stage(flat)
         o = 0
 
@@ -182,8 +194,11 @@ class Engine:
         ctx = StepContext(
             n_tokens=n, n_seqs=b, tokens=d_tokens, token_pos=d_pos, token_seq=d_seq,
             seq_slots=d_slots, page_tables=d_tables, workspace=self.workspace,
-            decode=all(c == 1 for c in counts), max_context=max(new_lengths),
+            decode=decode, max_context=max(new_lengths),
             host_slots=slots, host_counts=counts, host_starts=starts)
+        if not decode:
+            ctx.seq_first_row, ctx.seq_start, ctx.seq_count = take(b), take(b), take(b)
+            ctx.q_tiles = take(len(tiles)).view(-1, 2)
         return ctx, d_want, slots, new_lengths
 
     def step(self, batch: Sequence[SequenceStep]) -> torch.Tensor:

@@ -150,6 +150,11 @@ class Attention(Part):
                 if splits > 1 else None
             ops.attention_decode(q_buf, q_stride, cache.k, cache.v, ctx.token_pos, ctx.token_seq,
                                  table, attn, nq, nkv, d, self.window, self.scale, splits, partial)
+        elif self.dtype == torch.bfloat16 and not ctx.decode and ctx.q_tiles is not None \
+                and ops.attention_decode_mma_takes(d, cache.page_size):
+            ops.attention_prefill_mma(q_buf, q_stride, cache.k, cache.v, ctx.q_tiles,
+                                      ctx.seq_first_row, ctx.seq_start, ctx.seq_count, table, attn,
+                                      nq, nkv, d, self.window, self.scale)
         else:
             splits = ctx.attention_splits(n * nq)
             partial = ws.get("attn_partial", (n * nq * splits * (d + 2),), torch.float32) \

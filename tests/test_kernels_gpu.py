@@ -593,3 +593,37 @@ def test_gemm_on_tcgen05_many_k_blocks_reuse_every_stage():
         o.gemm_tc(a.to(DEV), w.to(DEV), None, out, o.STORE_F32)
     close(out, P.linear(a, w), "float32", "tcgen05 long k")
     o.check_status(DEV)
+
+
+@pytest.mark.parametrize("nq,nkv,d", [(9, 3, 64), (2, 2, 64), (4, 1, 128)])
+@pytest.mark.parametrize("window", [0, 70])
+def test_prompt_attention_on_tensor_cores(nq, nkv, d, window):
+    """Whole prompts and later chunks of unequal length in one packed batch."""
+    o = ops()
+    lengths, new = [70, 1, 200, 64, 333, 129], [70, 1, 5, 64, 200, 65]
+    case = PagedCase(lengths, new, nq, nkv, d, "bfloat16", seed=d + nq)
+    case.fill_cache()
+    for s, L in enumerate(lengths):  # the step's own keys and values are stored already
+        for t in range(L - new[s], L):
+            pg = int(case.table[s, t // 64])
+            case.k_cache[pg, :, t % 64] = case.k[s][t]
+            case.v_cache[pg, :, t % 64] = case.v[s][t]
+    pos, seq, q, _, _ = case.packed()
+    n = pos.numel()
+    qd = q.reshape(n, -1).bfloat16().to(DEV)
+    kc, vc = case.k_cache.bfloat16().to(DEV), case.v_cache.bfloat16().to(DEV)
+    first, tiles, row = [], [], 0
+    for i, c in enumerate(new):
+        first.append(row)
+        row += c
+        tiles += [[i, q0] for q0 in range(0, c, 64)]
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    out = torch.full((n, nq * d), 5.0, dtype=torch.bfloat16, device=DEV)
+    o.attention_prefill_mma(qd, nq * d, kc, vc, i32(tiles), i32(first),
+                            i32([L - c for L, c in zip(lengths, new)]), i32(new), case.table.to(DEV),
+                            out, nq, nkv, d, window, 1.0 / math.sqrt(d))
+    r = 0
+    for s, L in enumerate(lengths):
+        full = P.causal_attention(case.q[s], case.k[s], case.v[s].bfloat16().float(), window)
+        close(out[r:r + new[s]], full[L - new[s]:].reshape(new[s], -1), "bfloat16", f"prompt attention seq {s}")
+        r += new[s]
