@@ -99,6 +99,8 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has")
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
+    ap.add_argument("--skip-e2e", action="store_true", help="leave out the end-to-end run")
+    ap.add_argument("--batch", type=int, default=BATCH, help="sequences of the main decode point")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -184,7 +186,7 @@ def main() -> int:
                     "launches": launches, "bytes_per_step": step_bytes,
                     "gbs": step_bytes / (ms / steps * 1e-3) / 1e9}
 
-        main_point = decode_point(BATCH, K, W)
+        main_point = decode_point(args.batch, K, W)
 
         # -- prefill of 2,048 tokens ------------------------------------------------
         prompt = [rng.randrange(vocab) for _ in range(PROMPT)]
@@ -207,34 +209,36 @@ def main() -> int:
                    "frac": prefill_flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)}
 
         # -- end to end: host tokens in and out every step -----------------------------
-        e2e_new = min(K, 256) + 1
-        prompts = [[rng.randrange(vocab) for _ in range(CONTEXT - e2e_new)] for _ in range(BATCH)]
-        llm.generate([p[:64] for p in prompts], max_new_tokens=4, stop_token_ids=())
-        llm.backend._decoder(BATCH, CONTEXT, False).capture()  # the graph the timed run will launch
-        stamps = []
-        h2d0, d2h0 = llm.backend.h2d_bytes + engine.h2d_bytes, llm.backend.d2h_bytes
-        first_done = {}
+        e2e = None
+        if not args.skip_e2e:
+            e2e_new = min(K, 256) + 1
+            prompts = [[rng.randrange(vocab) for _ in range(CONTEXT - e2e_new)] for _ in range(BATCH)]
+            llm.generate([p[:64] for p in prompts], max_new_tokens=4, stop_token_ids=())
+            llm.backend._decoder(BATCH, CONTEXT, False).capture()  # the graph the timed run will launch
+            stamps = []
+            h2d0, d2h0 = llm.backend.h2d_bytes + engine.h2d_bytes, llm.backend.d2h_bytes
+            first_done = {}
 
-        def on_token(i, t):
-            if i not in first_done:
-                first_done[i] = True
-                if len(first_done) == BATCH:
-                    torch.cuda.synchronize()
-                    stamps.append((time.perf_counter(), llm.backend.h2d_bytes + engine.h2d_bytes,
-                                   llm.backend.d2h_bytes))
-        t0 = clocks.mark()
-        results = llm.generate(prompts, max_new_tokens=e2e_new, stop_token_ids=(), on_token=on_token)
-        torch.cuda.synchronize()
-        t_end = time.perf_counter()
-        windows.append((t0, clocks.mark()))
-        assert all(r.ok and len(r.token_ids) == e2e_new for r in results), \
-            [r.error for r in results if not r.ok]
-        t_first, h2d1, d2h1 = stamps[0]
-        e2e_steps = e2e_new - 1
-        e2e = {"value": BATCH * e2e_steps / (t_end - t_first), "unit": "tokens/s",
-               "h2d_bytes_per_step": (llm.backend.h2d_bytes + engine.h2d_bytes - h2d1) // e2e_steps,
-               "d2h_bytes_per_step": (llm.backend.d2h_bytes - d2h1) // e2e_steps,
-               "steps": e2e_steps}
+            def on_token(i, t):
+                if i not in first_done:
+                    first_done[i] = True
+                    if len(first_done) == BATCH:
+                        torch.cuda.synchronize()
+                        stamps.append((time.perf_counter(), llm.backend.h2d_bytes + engine.h2d_bytes,
+                                       llm.backend.d2h_bytes))
+            t0 = clocks.mark()
+            results = llm.generate(prompts, max_new_tokens=e2e_new, stop_token_ids=(), on_token=on_token)
+            torch.cuda.synchronize()
+            t_end = time.perf_counter()
+            windows.append((t0, clocks.mark()))
+            assert all(r.ok and len(r.token_ids) == e2e_new for r in results), \
+                [r.error for r in results if not r.ok]
+            t_first, h2d1, d2h1 = stamps[0]
+            e2e_steps = e2e_new - 1
+            e2e = {"value": BATCH * e2e_steps / (t_end - t_first), "unit": "tokens/s",
+                   "h2d_bytes_per_step": (llm.backend.h2d_bytes + engine.h2d_bytes - h2d1) // e2e_steps,
+                   "d2h_bytes_per_step": (llm.backend.d2h_bytes - d2h1) // e2e_steps,
+                   "steps": e2e_steps}
 
         points = {}
         if not args.skip_points:
@@ -251,7 +255,7 @@ def main() -> int:
         "ms_per_step": main_point["ms_per_step"], "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded random weights and token ids)",
         "impl": "ours",
-        "config": {"model": "SmolLM2-135M shape", "global_batch": BATCH, "seq_len": CONTEXT,
+        "config": {"model": "SmolLM2-135M shape", "global_batch": args.batch, "seq_len": CONTEXT,
                    "parallelism": "single GPU", "prompt_len": PROMPT, "layers": cfg["num_hidden_layers"],
                    "layers_of_shape": full_layers, "hidden_size": cfg["hidden_size"],
                    "intermediate_size": cfg["intermediate_size"], "heads": cfg["num_attention_heads"],
