@@ -50,8 +50,21 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __r
     const int gcount = min(16, G - g0);
     const int n = blockIdx.y, split = blockIdx.z;
 
-    pdl_wait();
+    // Slices are fixed ranges of the page table (not of this sequence's length), so
+    // the page ids of a slice can be asked for together with the position instead
+    // of after it.
+    // Under programmatic dependent launch this kernel may start while the kernel
+    // before it (the one that writes this step's query, key and value) still runs.
+    // Every kernel of the step releases its dependents only after its own wait, so
+    // all kernels before that one are complete: positions, page tables and every
+    // cache page except the one that holds this step's token may be read at once.
+    const int per = (table_cols + n_splits - 1) / n_splits;
+    const int p0 = split * per;
+    const int* table = page_table + (size_t)token_seq[n] * table_cols;
     const int pos = token_pos[n];
+    int first_ids[3];
+#pragma unroll
+    for (int i = 0; i < 3; ++i) first_ids[i] = (i < per && p0 + i < table_cols) ? table[p0 + i] : 0;
     const int r_lo = lane >> 2, c_lo = (lane & 3) * 2;  // this thread's rows r_lo, r_lo + 8
 
     float o[NT][4];
@@ -65,15 +78,16 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __r
         const int lo = window > 0 ? max(0, pos - window + 1) : 0;
         const int hi = pos + 1;
         const int first_page = lo / kPage, last_page = (hi - 1) / kPage;
-        const int per = (last_page - first_page + n_splits) / n_splits;
-        const int p0 = first_page + split * per;
-        const int count = max(0, min(last_page + 1, p0 + per) - p0);
-        const int* table = page_table + (size_t)token_seq[n] * table_cols;
+        // this slice's pages that the query can see: [begin, begin + count)
+        const int begin = max(p0, first_page);
+        const int count = max(0, min(last_page + 1, p0 + per) - begin);
         const size_t tile_elems = (size_t)kPage * D;
 
         auto load_page = [&](int it) {
             if (it < count) {
-                int page = table[p0 + it];
+                int idx = begin + it - p0;  // place within the slice
+                int page = idx < 3 ? (idx == 0 ? first_ids[0] : idx == 1 ? first_ids[1] : first_ids[2])
+                                   : table[begin + it];
                 const bf16* ksrc = k_cache + (size_t)(page * nkv + hk) * tile_elems;
                 const bf16* vsrc = v_cache + (size_t)(page * nkv + hk) * tile_elems;
                 bf16* kd = tiles + (size_t)(it % stages) * 2 * tile_elems;
@@ -86,8 +100,13 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __r
             }
             cp_async_commit();
         };
-        for (int it = 0; it < stages - 1; ++it) load_page(it);
+        // the page of this step's token is the last one of the sequence: it waits
+        const int hot = last_page - begin;
+        int issued = 0;
+        for (; issued < stages - 1 && issued != hot; ++issued) load_page(issued);
+        pdl_wait();
         pdl_launch_dependents();
+        for (; issued < stages - 1; ++issued) load_page(issued);
 
         // the group's query rows, zero beyond the group
         for (int c = tid; c < 16 * CH; c += kMmaWarps * 32) {
@@ -114,7 +133,7 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __r
             const bf16* kt = tiles + (size_t)(it % stages) * 2 * tile_elems;
             const bf16* vt = kt + tile_elems;
             const int key0 = warp * 16;  // this warp's 16 keys of the page
-            const int t0 = (p0 + it) * kPage + key0;
+            const int t0 = (begin + it) * kPage + key0;
 
             // scores: S[16 heads, 16 keys] = Q . K^T
             float s[2][4];
@@ -191,6 +210,10 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __r
             l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
             l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
         }
+    }
+    if (pos < 0) {
+        pdl_wait();
+        pdl_launch_dependents();
     }
     __syncthreads();  // everyone is done with the tiles: reuse them for the merge
 

@@ -342,6 +342,8 @@ NNIS_API int nnis_gemm_tc(const void* A, const void* W, const float* bias, void*
         return NNIS_ERR_UNSUPPORTED;
     GemmArgs g;
     g.bias = bias; g.out = C; g.M = M; g.N = N; g.K = K; g.mode = mode; g.status = status;
-    if (wide) return launch_gemm_tc<128, 5>(ma, mw, g, pdl != 0, stream);
-    return launch_gemm_tc<64, 6>(ma, mw, g, pdl != 0, stream);
+    // three or four stages (96 KB): two CTAs share an SM, so one CTA's epilogue
+    // overlaps the other's products
+    if (wide) return launch_gemm_tc<128, 3>(ma, mw, g, pdl != 0, stream);
+    return launch_gemm_tc<64, 4>(ma, mw, g, pdl != 0, stream);
 }

@@ -150,20 +150,69 @@ gemv_kernel(GemvArgs a) {
 #pragma unroll
         for (int s = 0; s < S; ++s) issue(s);
     }
-    pdl_launch_dependents();
+    // what does not depend on earlier kernels: the norm weights of this lane's columns
+    constexpr int NW = 6;  // float4 per lane kept in registers: covers K <= 768
+    float4 nw[NW];
+    const int k4 = K >> 2;
+    if (PRO == PRO_NORM) {
+#pragma unroll
+        for (int j = 0; j < NW; ++j) {
+            int c = lane + 32 * j;
+            nw[j] = c < k4 ? reinterpret_cast<const float4*>(a.norm_w)[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    // Dependents are released only after this kernel's own wait: a kernel that
+    // starts early may then rely on everything before its immediate predecessor
+    // (the decode attention kernel reads old cache pages before its wait).
     pdl_wait();
+    pdl_launch_dependents();
+
+    // operands of the first unit's epilogue, asked for now and used after the products
+    const int lane_m = (EPI == EPI_QKV) ? (lane >> 1) : (lane >> 2);
+    int pre_pos = -1;
+    if (EPI == EPI_QKV && lane_m < M) pre_pos = a.token_pos[lane_m];
 
     // ---- x into shared memory ------------------------------------------------
     if (PRO == PRO_NORM) {
+        const bool in_regs = k4 <= 32 * NW;
         for (int m = warp; m < MT; m += kGemvWarps) {
             if (m < M) {
                 const float* h = a.hidden + (size_t)(a.rows ? a.rows[m] : m) * K;
+                const float4* h4 = reinterpret_cast<const float4*>(h);
+                float4 hv[NW];
                 float ss = 0.f;
-                for (int k = lane; k < K; k += 32) ss = fmaf(h[k], h[k], ss);
+                if (in_regs) {
+#pragma unroll
+                    for (int j = 0; j < NW; ++j) {
+                        int c = lane + 32 * j;
+                        hv[j] = c < k4 ? h4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+#pragma unroll
+                    for (int j = 0; j < NW; ++j) {
+                        ss = fmaf(hv[j].x, hv[j].x, ss);
+                        ss = fmaf(hv[j].y, hv[j].y, ss);
+                        ss = fmaf(hv[j].z, hv[j].z, ss);
+                        ss = fmaf(hv[j].w, hv[j].w, ss);
+                    }
+                } else {
+                    for (int k = lane; k < K; k += 32) ss = fmaf(h[k], h[k], ss);
+                }
                 ss = warp_sum(ss);
                 float s = 1.0f / sqrtf(ss * (1.0f / (float)K) + a.eps);
-                for (int k = lane; k < K; k += 32)
-                    xs[(size_t)m * K + k] = __float2bfloat16_rn((h[k] * s) * a.norm_w[k]);
+                if (in_regs) {
+#pragma unroll
+                    for (int j = 0; j < NW; ++j) {
+                        int c = lane + 32 * j;
+                        if (c < k4) {
+                            float4 r = make_float4((hv[j].x * s) * nw[j].x, (hv[j].y * s) * nw[j].y,
+                                                   (hv[j].z * s) * nw[j].z, (hv[j].w * s) * nw[j].w);
+                            store4(xs + (size_t)m * K + c * 4, r);
+                        }
+                    }
+                } else {
+                    for (int k = lane; k < K; k += 32)
+                        xs[(size_t)m * K + k] = __float2bfloat16_rn((h[k] * s) * a.norm_w[k]);
+                }
             } else {
                 for (int k = lane; k < K; k += 32) xs[(size_t)m * K + k] = __float2bfloat16_rn(0.f);
             }
@@ -217,6 +266,28 @@ gemv_kernel(GemvArgs a) {
     // ---- units of four output rows ---------------------------------------------
     const int half = a.d >> 1;
     const int inter = a.N >> 1;
+    float pre_c = 1.f, pre_s = 0.f, pre_old0 = 0.f, pre_old1 = 0.f;
+    int pre_page = 0;
+    if (first_unit < n_units) {
+        int r0, r2;
+        unit_rows<EPI>(a, first_unit, r0, r2);
+        if (EPI == EPI_QKV && pre_pos >= 0) {
+            int head = r0 / a.d, j = r0 - head * a.d + (lane & 1);
+            if (a.sin_t && head < a.nq + a.nkv) {
+                pre_c = a.cos_t[(size_t)pre_pos * half + j];
+                pre_s = a.sin_t[(size_t)pre_pos * half + j];
+            }
+            if (head >= a.nq)
+                pre_page = a.page_table[(size_t)a.token_seq[lane_m] * a.table_cols + pre_pos / a.page_size];
+        }
+        if (EPI == EPI_ADD_F32) {
+            int r = lane & 3;
+            int n = (r < 2 ? r0 + r : r2 + r - 2);
+            if (lane_m < M) pre_old0 = reinterpret_cast<const float*>(a.out)[(size_t)lane_m * a.N + n];
+            if (MT * 4 > 32 && lane_m + 8 < M)
+                pre_old1 = reinterpret_cast<const float*>(a.out)[(size_t)(lane_m + 8) * a.N + n];
+        }
+    }
     constexpr int SLOTS = (MT * 4 + 31) / 32;
     float best_v[SLOTS];
     int best_i[SLOTS];
@@ -283,15 +354,16 @@ gemv_kernel(GemvArgs a) {
                         out[(size_t)m * inter + unit * 2 + p] =
                             __float2bfloat16_rn((va / (1.0f + expf(-va))) * vb);
                     } else {
-                        int pos = a.token_pos[m];
+                        const bool first = (i == 0);
+                        int pos = first ? pre_pos : a.token_pos[m];
                         if (pos >= 0) {
                             int head = r0 / a.d, j = r0 - head * a.d + p;
                             va = round_bf16(va);
                             vb = round_bf16(vb);
                             bool is_v = head >= a.nq + a.nkv;
                             if (a.sin_t && !is_v) {
-                                float c = a.cos_t[(size_t)pos * half + j];
-                                float s = a.sin_t[(size_t)pos * half + j];
+                                float c = first ? pre_c : a.cos_t[(size_t)pos * half + j];
+                                float s = first ? pre_s : a.sin_t[(size_t)pos * half + j];
                                 float ra = va * c - vb * s, rb = vb * c + va * s;
                                 va = ra;
                                 vb = rb;
@@ -305,8 +377,9 @@ gemv_kernel(GemvArgs a) {
                             } else {
                                 int hk = is_v ? head - a.nq - a.nkv : head - a.nq;
                                 bf16* cache = is_v ? a.v_cache : a.k_cache;
-                                int page = a.page_table[(size_t)a.token_seq[m] * a.table_cols +
-                                                        pos / a.page_size];
+                                int page = first ? pre_page
+                                                 : a.page_table[(size_t)a.token_seq[m] * a.table_cols +
+                                                                pos / a.page_size];
                                 size_t dst = ((size_t)(page * a.nkv + hk) * a.page_size +
                                               (pos % a.page_size)) * a.d;
                                 cache[dst + j] = ta;
@@ -324,7 +397,11 @@ gemv_kernel(GemvArgs a) {
                     size_t o = (size_t)m * a.N + n;
                     if (EPI == EPI_STORE) reinterpret_cast<bf16*>(a.out)[o] = __float2bfloat16_rn(v);
                     else if (EPI == EPI_STORE_F32) reinterpret_cast<float*>(a.out)[o] = v;
-                    else if (EPI == EPI_ADD_F32) reinterpret_cast<float*>(a.out)[o] += v;
+                    else if (EPI == EPI_ADD_F32) {
+                        float old = (i == 0) ? (pass == 0 ? pre_old0 : pre_old1)
+                                             : reinterpret_cast<const float*>(a.out)[o];
+                        reinterpret_cast<float*>(a.out)[o] = old + v;
+                    }
                     else {
                         if (a.logits) a.logits[o] = v;
                         if (better(v, n, best_v[pass], best_i[pass])) {
