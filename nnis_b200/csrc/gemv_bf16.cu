@@ -1,15 +1,18 @@
 // Projections of a decode step in bfloat16: y[M, N] = x[M, K] . W[N, K]^T with
-// at most 16 rows of x.  The step is bound by the bytes of W and by latency, so
+// at most 64 rows of x.  The step is bound by the bytes of W and by latency, so
 //
 //  * W is brought into shared memory by bulk asynchronous copies (one per
 //    weight row, completing on an mbarrier), issued before anything else in the
 //    kernel - before the wait of programmatic dependent launch, hence while the
-//    kernel before it still runs - and double-buffered per warp;
+//    kernel before it still runs - and double-buffered per warp where that pays;
+//  * the products run on the tensor cores (mma.sync m16n8k16, float32
+//    accumulation): x is the 16-row A operand (one to four tiles of rows), eight
+//    weight rows are the B operand, so a warp needs about a hundred instructions
+//    per eight outputs instead of a thousand on the CUDA cores, and no reduction
+//    across lanes;
 //  * what surrounds the product is fused so that no activation makes a round
 //    trip through its own kernel:
 //      prologue  NORM:  x = bf16(rmsnorm(hidden_f32[rows]) * w_norm);
-//                MERGE: x = bf16(attention output) merged from the split-KV
-//                       partial records of the decode attention kernel;
 //      epilogue  STORE (bfloat16), STORE_F32, ADD_F32 (into the residual stream),
 //                GATED:  out[m, i] = bf16(silu(y[m, i]) * y[m, I + i]),
 //                QKV:    bias, round, rotate-half RoPE of q and k heads at each
@@ -19,20 +22,19 @@
 //                        index), optionally the float32 logits too, and the move
 //                        of the decode state to the next token.
 //
-// A warp owns four output rows at a time (a "unit"); lanes split K in chunks of
-// eight.  Sums are float32 fmaf chains, reduced across the warp by a butterfly.
-// NNIS's one-token projection: crates/nnis-kernels/src/gemv.rs:45-61; its fused
-// gate/up/SiLU kernel: crates/nnis-model/src/fused_swiglu.rs:14-27; its greedy
-// pick: crates/nnis-kernels/src/top_k.rs:57-70.
+// A warp owns eight output rows at a time (a "unit").  Shared-memory rows are
+// padded by 16 bytes so that ldmatrix meets no bank conflict when K is a multiple
+// of 16.  NNIS's one-token projection: crates/nnis-kernels/src/gemv.rs:45-61; its
+// fused gate/up/SiLU kernel: crates/nnis-model/src/fused_swiglu.rs:14-27; its
+// greedy pick: crates/nnis-kernels/src/top_k.rs:57-70.
 #include <float.h>
 
-#include "async_copy.cuh"
-#include "common.cuh"
+#include "mma_helpers.cuh"
 
 namespace nnis {
 
 enum { EPI_STORE = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_GATED = 3, EPI_QKV = 4, EPI_ARGMAX = 5 };
-enum { PRO_PLAIN = 0, PRO_NORM = 1, PRO_MERGE = 2 };
+enum { PRO_PLAIN = 0, PRO_NORM = 1 };
 
 struct GemvArgs {
     const bf16* x;          // [M, K] (plain prologue)
@@ -40,14 +42,12 @@ struct GemvArgs {
     const int* rows;        // optional row of `hidden` per x row
     const float* norm_w;    // [K]
     float eps;
-    const float* partial;   // merge prologue: [M * nq, splits, d + 2]
-    int splits;
     const bf16* w;          // [N, K]
     const float* bias;      // [N] or null
     void* out;              // see epilogues
     int M, N, K;
     int* status;            // set non-zero when a bounded wait runs out
-    // QKV epilogue (nq, d also describe the merge prologue)
+    // QKV epilogue
     const int* token_pos;
     const int* token_seq;
     const int* page_table;
@@ -66,80 +66,75 @@ struct GemvArgs {
     int* next_pos;          // ... and their positions (+1 on live rows)
 };
 
-__device__ __forceinline__ void unpack8f(const uint4& raw, float* f) {
-    f[0] = __uint_as_float(raw.x << 16);
-    f[1] = __uint_as_float(raw.x & 0xffff0000u);
-    f[2] = __uint_as_float(raw.y << 16);
-    f[3] = __uint_as_float(raw.y & 0xffff0000u);
-    f[4] = __uint_as_float(raw.z << 16);
-    f[5] = __uint_as_float(raw.z & 0xffff0000u);
-    f[6] = __uint_as_float(raw.w << 16);
-    f[7] = __uint_as_float(raw.w & 0xffff0000u);
-}
-
 __device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
-
-// value number `idx` of a register array, without dynamic indexing
-template <int COUNT>
-__device__ __forceinline__ float pick(const float* v, int idx) {
-    float r = 0.f;
-#pragma unroll
-    for (int i = 0; i < COUNT; ++i) r = (idx == i) ? v[i] : r;
-    return r;
-}
 
 __device__ __forceinline__ bool better(float v, int i, float bv, int bi) {
     return bi < 0 || v > bv || (v == bv && i < bi);
 }
 
-constexpr int kGemvWarps = 8;
-
-template <int EPI>
-__device__ __forceinline__ void unit_rows(const GemvArgs& a, int unit, int& r0, int& r2) {
-    if (EPI == EPI_GATED) {
-        r0 = unit * 2;
-        r2 = (a.N >> 1) + unit * 2;
-    } else if (EPI == EPI_QKV) {
-        int per_head = a.d >> 2;
-        int head = unit / per_head, jj = (unit - head * per_head) * 2;
-        r0 = head * a.d + jj;
-        r2 = r0 + (a.d >> 1);
-    } else {
-        r0 = unit * 4;
-        r2 = r0 + 2;
-    }
+__device__ __forceinline__ void ldmatrix_x2(uint32_t& r0, uint32_t& r1, const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];"
+                 : "=r"(r0), "=r"(r1)
+                 : "r"(smem_addr(p)));
 }
 
-template <int MT, int EPI, int PRO, int S>
-__global__ void __launch_bounds__(kGemvWarps * 32)
+// Output row of column c (0..7) of unit `unit`: columns 0-3 and 4-7 are the two
+// halves of a pair in the GATED (gate, up) and QKV (j, j + d/2) epilogues.
+template <int EPI>
+__device__ __forceinline__ int unit_row(const GemvArgs& a, int unit, int c) {
+    if (EPI == EPI_GATED) return (c < 4 ? 0 : (a.N >> 1) - 4) + unit * 4 + c;
+    if (EPI == EPI_QKV) {
+        int per_head = a.d >> 3;
+        int head = unit / per_head, jj = (unit - head * per_head) * 4;
+        return head * a.d + jj + (c < 4 ? c : (a.d >> 1) + c - 4);
+    }
+    return unit * 8 + c;
+}
+
+// MTILES tiles of 16 rows of x; WARPS warps per CTA; S stages of weights per warp.
+// SPLITK: the CTA owns one unit and its warps share K (each a run of 16-column
+// steps), which shortens the chain of dependent products when there are fewer
+// units than the GPU has room for; the partial sums meet in shared memory and
+// warp 0 adds them in order and runs the epilogue.
+template <int MTILES, int EPI, int PRO, int S, int WARPS, bool SPLITK>
+__global__ void __launch_bounds__(WARPS * 32)
 gemv_kernel(GemvArgs a) {
+    constexpr int MT = MTILES * 16;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int K = a.K, M = a.M;
-    bf16* xs = reinterpret_cast<bf16*>(smem_raw);                                    // [MT, K]
-    bf16* wst = xs + (size_t)MT * K + (size_t)warp * S * 4 * K;                      // [S, 4, K]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(xs + (size_t)(MT + kGemvWarps * S * 4) * K) + warp * S;
-    __shared__ float cta_val[kGemvWarps][MT];
-    __shared__ int cta_idx[kGemvWarps][MT];
+    const int KP = K + 8;  // padded row, in elements
+    bf16* xs = reinterpret_cast<bf16*>(smem_raw);                          // [MT, KP]
+    // weight stages: one set per warp, or one shared set when the warps split K
+    bf16* wst = xs + (size_t)MT * KP + (SPLITK ? 0 : (size_t)warp * S * 8 * KP);
+    constexpr int kSets = SPLITK ? 1 : WARPS * S;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(xs + (size_t)(MT + kSets * 8) * KP) + warp * S;
+    float* red = reinterpret_cast<float*>(bars - warp * S + WARPS * S);     // SPLITK: [WARPS, MTILES*4, 32]
+    __shared__ float cta_val[WARPS][MT];
+    __shared__ int cta_idx[WARPS][MT];
     __shared__ bool is_last;
 
-    const int n_units = a.N >> 2;
-    const int unit_stride = gridDim.x * kGemvWarps;
-    const int first_unit = blockIdx.x * kGemvWarps + warp;
-    const uint32_t row_bytes = (uint32_t)K * 2u;
+    const int n_units = a.N >> 3;
+    const int unit_stride = SPLITK ? gridDim.x : gridDim.x * WARPS;
+    // units are dealt to CTAs first, so that few units still spread over many SMs
+    const int first_unit = SPLITK ? blockIdx.x : warp * gridDim.x + blockIdx.x;
+    // this warp's columns of K: all of them, or its share of the 16-column steps
+    const int steps = K >> 4;
+    const int steps_per_warp = (steps + WARPS - 1) / WARPS;
+    const int k_begin = SPLITK ? min(steps, warp * steps_per_warp) * 16 : 0;
+    const int k_end = SPLITK ? min(steps, (warp + 1) * steps_per_warp) * 16 : K;
+    const uint32_t row_bytes = (uint32_t)(k_end - k_begin) * 2u;
 
     auto issue = [&](int i) {  // lane 0 only
         int unit = first_unit + i * unit_stride;
-        if (unit >= n_units) return;
-        int r0, r2;
-        unit_rows<EPI>(a, unit, r0, r2);
+        if (unit >= n_units || row_bytes == 0) return;
         uint64_t* bar = bars + (i % S);
-        bf16* dst = wst + (size_t)(i % S) * 4 * K;
-        mbar_expect_tx(bar, 4u * row_bytes);
-        bulk_load(dst, a.w + (size_t)r0 * K, row_bytes, bar);
-        bulk_load(dst + K, a.w + (size_t)(r0 + 1) * K, row_bytes, bar);
-        bulk_load(dst + 2 * (size_t)K, a.w + (size_t)r2 * K, row_bytes, bar);
-        bulk_load(dst + 3 * (size_t)K, a.w + (size_t)(r2 + 1) * K, row_bytes, bar);
+        bf16* dst = wst + (size_t)(i % S) * 8 * KP + k_begin;
+        mbar_expect_tx(bar, 8u * row_bytes);
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+            bulk_load(dst + (size_t)c * KP, a.w + (size_t)unit_row<EPI>(a, unit, c) * K + k_begin,
+                      row_bytes, bar);
     };
 
     // ---- weights first: they depend on no earlier kernel ---------------------
@@ -150,7 +145,7 @@ gemv_kernel(GemvArgs a) {
 #pragma unroll
         for (int s = 0; s < S; ++s) issue(s);
     }
-    // what does not depend on earlier kernels: the norm weights of this lane's columns
+    // ... and the norm weights of this lane's columns
     constexpr int NW = 6;  // float4 per lane kept in registers: covers K <= 768
     float4 nw[NW];
     const int k4 = K >> 2;
@@ -167,15 +162,10 @@ gemv_kernel(GemvArgs a) {
     pdl_wait();
     pdl_launch_dependents();
 
-    // operands of the first unit's epilogue, asked for now and used after the products
-    const int lane_m = (EPI == EPI_QKV) ? (lane >> 1) : (lane >> 2);
-    int pre_pos = -1;
-    if (EPI == EPI_QKV && lane_m < M) pre_pos = a.token_pos[lane_m];
-
     // ---- x into shared memory ------------------------------------------------
     if (PRO == PRO_NORM) {
         const bool in_regs = k4 <= 32 * NW;
-        for (int m = warp; m < MT; m += kGemvWarps) {
+        for (int m = warp; m < MT; m += WARPS) {
             if (m < M) {
                 const float* h = a.hidden + (size_t)(a.rows ? a.rows[m] : m) * K;
                 const float4* h4 = reinterpret_cast<const float4*>(h);
@@ -206,207 +196,182 @@ gemv_kernel(GemvArgs a) {
                         if (c < k4) {
                             float4 r = make_float4((hv[j].x * s) * nw[j].x, (hv[j].y * s) * nw[j].y,
                                                    (hv[j].z * s) * nw[j].z, (hv[j].w * s) * nw[j].w);
-                            store4(xs + (size_t)m * K + c * 4, r);
+                            store4(xs + (size_t)m * KP + c * 4, r);
                         }
                     }
                 } else {
                     for (int k = lane; k < K; k += 32)
-                        xs[(size_t)m * K + k] = __float2bfloat16_rn((h[k] * s) * a.norm_w[k]);
+                        xs[(size_t)m * KP + k] = __float2bfloat16_rn((h[k] * s) * a.norm_w[k]);
                 }
             } else {
-                for (int k = lane; k < K; k += 32) xs[(size_t)m * K + k] = __float2bfloat16_rn(0.f);
-            }
-        }
-    } else if (PRO == PRO_MERGE) {
-        // one warp per (row, head): weights of the splits, then the weighted sum
-        const int d = a.d, nq = a.nq, sp = a.splits;
-        for (int p = warp; p < MT * nq; p += kGemvWarps) {
-            int m = p / nq, hq = p - m * nq;
-            bf16* dst = xs + (size_t)m * K + (size_t)hq * d;
-            if (m >= M) {
-                for (int i = lane; i < d; i += 32) dst[i] = __float2bfloat16_rn(0.f);
-                continue;
-            }
-            const float* rec = a.partial + ((size_t)m * nq + hq) * sp * (size_t)(d + 2);
-            float m0 = -FLT_MAX, l0 = 0.f, m1 = -FLT_MAX, l1 = 0.f;
-            if (lane < sp) {
-                m0 = rec[(size_t)lane * (d + 2)];
-                l0 = rec[(size_t)lane * (d + 2) + 1];
-            }
-            if (lane + 32 < sp) {
-                m1 = rec[(size_t)(lane + 32) * (d + 2)];
-                l1 = rec[(size_t)(lane + 32) * (d + 2) + 1];
-            }
-            float mx = warp_max(fmaxf(l0 > 0.f ? m0 : -FLT_MAX, l1 > 0.f ? m1 : -FLT_MAX));
-            float w0 = l0 > 0.f ? __expf(m0 - mx) : 0.f;
-            float w1 = l1 > 0.f ? __expf(m1 - mx) : 0.f;
-            float total = warp_sum(l0 * w0 + l1 * w1);
-            float inv = total > 0.f ? 1.0f / total : 0.f;
-            for (int i0 = 0; i0 < d; i0 += 32) {
-                int i = i0 + lane;
-                float o = 0.f;
-                for (int s = 0; s < sp; ++s) {
-                    float ws = __shfl_sync(0xffffffffu, s < 32 ? w0 : w1, s & 31);
-                    if (i < d) o = fmaf(ws, rec[(size_t)s * (d + 2) + 2 + i], o);
-                }
-                if (i < d) dst[i] = __float2bfloat16_rn(o * inv);
+                for (int k = lane; k < K; k += 32) xs[(size_t)m * KP + k] = __float2bfloat16_rn(0.f);
             }
         }
     } else {
-        const int chunks = MT * K / 8;
-        for (int c = threadIdx.x; c < chunks; c += kGemvWarps * 32) {
-            int m = (c * 8) / K;
+        const int per_row = K >> 3;  // 16-byte chunks
+        for (int c = threadIdx.x; c < MT * per_row; c += WARPS * 32) {
+            int m = c / per_row, ch = c - m * per_row;
             uint4 v = make_uint4(0, 0, 0, 0);
-            if (m < M) v = *reinterpret_cast<const uint4*>(a.x + (size_t)c * 8);
-            *reinterpret_cast<uint4*>(xs + (size_t)c * 8) = v;
+            if (m < M) v = *reinterpret_cast<const uint4*>(a.x + (size_t)m * K + ch * 8);
+            *reinterpret_cast<uint4*>(xs + (size_t)m * KP + ch * 8) = v;
         }
     }
     __syncthreads();
 
-    // ---- units of four output rows ---------------------------------------------
+    // ---- units of eight output rows --------------------------------------------
     const int half = a.d >> 1;
     const int inter = a.N >> 1;
-    float pre_c = 1.f, pre_s = 0.f, pre_old0 = 0.f, pre_old1 = 0.f;
-    int pre_page = 0;
-    if (first_unit < n_units) {
-        int r0, r2;
-        unit_rows<EPI>(a, first_unit, r0, r2);
-        if (EPI == EPI_QKV && pre_pos >= 0) {
-            int head = r0 / a.d, j = r0 - head * a.d + (lane & 1);
-            if (a.sin_t && head < a.nq + a.nkv) {
-                pre_c = a.cos_t[(size_t)pre_pos * half + j];
-                pre_s = a.sin_t[(size_t)pre_pos * half + j];
-            }
-            if (head >= a.nq)
-                pre_page = a.page_table[(size_t)a.token_seq[lane_m] * a.table_cols + pre_pos / a.page_size];
-        }
-        if (EPI == EPI_ADD_F32) {
-            int r = lane & 3;
-            int n = (r < 2 ? r0 + r : r2 + r - 2);
-            if (lane_m < M) pre_old0 = reinterpret_cast<const float*>(a.out)[(size_t)lane_m * a.N + n];
-            if (MT * 4 > 32 && lane_m + 8 < M)
-                pre_old1 = reinterpret_cast<const float*>(a.out)[(size_t)(lane_m + 8) * a.N + n];
-        }
-    }
-    constexpr int SLOTS = (MT * 4 + 31) / 32;
-    float best_v[SLOTS];
-    int best_i[SLOTS];
+    const int r_lo = lane >> 2, c_lo = (lane & 3) * 2;  // rows r_lo, r_lo + 8; columns c_lo, c_lo + 1
+    float best_v[MTILES][2];
+    int best_i[MTILES][2];
 #pragma unroll
-    for (int t = 0; t < SLOTS; ++t) {
-        best_v[t] = -FLT_MAX;
-        best_i[t] = -1;
+    for (int t = 0; t < MTILES; ++t) {
+        best_v[t][0] = best_v[t][1] = -FLT_MAX;
+        best_i[t][0] = best_i[t][1] = -1;
     }
     bool failed = false;
     for (int i = 0;; ++i) {
         int unit = first_unit + i * unit_stride;
         if (unit >= n_units) break;
-        int r0, r2;
-        unit_rows<EPI>(a, unit, r0, r2);
         // the whole warp leaves together if any lane's wait ran out
-        if (!__all_sync(0xffffffffu, mbar_wait(bars + (i % S), (uint32_t)(i / S) & 1u))) {
+        if (row_bytes != 0 &&
+            !__all_sync(0xffffffffu, mbar_wait(bars + (i % S), (uint32_t)(i / S) & 1u))) {
             failed = true;
-            break;
+            if (!SPLITK) break;
         }
-        const bf16* wbuf = wst + (size_t)(i % S) * 4 * K;
-        float acc[MT * 4];
+        const bf16* wbuf = wst + (size_t)(i % S) * 8 * KP;
+        float acc[MTILES][4];
 #pragma unroll
-        for (int j = 0; j < MT * 4; ++j) acc[j] = 0.f;
-        for (int k = lane * 8; k < K; k += 256) {
-            float f0[8], f1[8], f2[8], f3[8];
-            unpack8f(*reinterpret_cast<const uint4*>(wbuf + k), f0);
-            unpack8f(*reinterpret_cast<const uint4*>(wbuf + K + k), f1);
-            unpack8f(*reinterpret_cast<const uint4*>(wbuf + 2 * (size_t)K + k), f2);
-            unpack8f(*reinterpret_cast<const uint4*>(wbuf + 3 * (size_t)K + k), f3);
+        for (int t = 0; t < MTILES; ++t)
 #pragma unroll
-            for (int m = 0; m < MT; ++m) {
-                float xf[8];
-                unpack8f(*reinterpret_cast<const uint4*>(xs + (size_t)m * K + k), xf);
+            for (int e = 0; e < 4; ++e) acc[t][e] = 0.f;
+        // lanes 0-7: weight rows at columns k0..k0+7, lanes 8-15: k0+8..k0+15
+        const bf16* b_ptr = wbuf + (size_t)(lane & 7) * KP + ((lane >> 3) & 1) * 8;
+        const bf16* a_ptr = xs + (size_t)(lane & 15) * KP + (lane >> 4) * 8;
+        // with one tile of rows, two chains of products halve the dependent latency
+        float acc2[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+        for (int k0 = k_begin; k0 < k_end; k0 += 16) {
+            uint32_t b0, b1;
+            ldmatrix_x2(b0, b1, b_ptr + k0);
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    acc[m * 4 + 0] = fmaf(xf[e], f0[e], acc[m * 4 + 0]);
-                    acc[m * 4 + 1] = fmaf(xf[e], f1[e], acc[m * 4 + 1]);
-                    acc[m * 4 + 2] = fmaf(xf[e], f2[e], acc[m * 4 + 2]);
-                    acc[m * 4 + 3] = fmaf(xf[e], f3[e], acc[m * 4 + 3]);
-                }
+            for (int t = 0; t < MTILES; ++t) {
+                uint32_t af[4];
+                ldmatrix_x4(af, a_ptr + (size_t)t * 16 * KP + k0);
+                if (MTILES == 1 && (k0 & 16)) mma_bf16(acc2, af, b0, b1);
+                else mma_bf16(acc[t], af, b0, b1);
             }
         }
-        __syncwarp();  // every lane has read this stage: it may be filled again
-        if (lane == 0) issue(i + S);
+        if (MTILES == 1) {
 #pragma unroll
-        for (int j = 0; j < MT * 4; ++j) acc[j] = warp_sum(acc[j]);
+            for (int e = 0; e < 4; ++e) acc[0][e] += acc2[e];
+        }
+        if (SPLITK) {
+            // partial sums of the warps, added by warp 0 in warp order
+#pragma unroll
+            for (int t = 0; t < MTILES; ++t)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) red[((size_t)warp * MTILES * 4 + t * 4 + e) * 32 + lane] = acc[t][e];
+            __syncthreads();
+            if (warp != 0) break;  // one unit per CTA: the other warps are done
+#pragma unroll
+            for (int t = 0; t < MTILES; ++t)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float sum = acc[t][e];
+                    for (int w = 1; w < WARPS; ++w) sum += red[((size_t)w * MTILES * 4 + t * 4 + e) * 32 + lane];
+                    acc[t][e] = sum;
+                }
+        } else {
+            __syncwarp();  // every lane has read this stage: it may be filled again
+            if (lane == 0) issue(i + S);
+        }
 
-        // ---- epilogue: lane j finishes value j (two passes when MT = 16) ---------
+        // ---- epilogue: this thread holds rows r_lo (+8) and columns c_lo, c_lo + 1 ---
+        if (EPI == EPI_GATED || EPI == EPI_QKV) {
+            // columns 0-3 pair with 4-7: the lanes of the second half hand theirs over
+            const bool low = (lane & 3) < 2;
+            const int n_a = unit_row<EPI>(a, unit, c_lo & 3);
+            const int n_b = unit_row<EPI>(a, unit, (c_lo & 3) + 4);
 #pragma unroll
-        for (int pass = 0; pass < SLOTS; ++pass) {
-            if (EPI == EPI_GATED || EPI == EPI_QKV) {
-                // pairs: (m, p) with partner row r2 + p; 2 * MT pairs
-                int idx = pass * 32 + lane;
-                int m = idx >> 1, p = idx & 1;
-                if (idx < MT * 2 && m < M) {
-                    float va = pick<MT * 4>(acc, m * 4 + p);
-                    float vb = pick<MT * 4>(acc, m * 4 + 2 + p);
+            for (int t = 0; t < MTILES; ++t) {
+                float pv[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) pv[e] = __shfl_xor_sync(0xffffffffu, acc[t][e], 2);
+                if (!low) continue;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    int m = t * 16 + r_lo + (e >> 1) * 8;
+                    if (m >= M) continue;
+                    int na = n_a + (e & 1), nb = n_b + (e & 1);
+                    float va = acc[t][e], vb = pv[e];
                     if (a.bias) {
-                        va += a.bias[r0 + p];
-                        vb += a.bias[r2 + p];
+                        va += a.bias[na];
+                        vb += a.bias[nb];
                     }
                     if (EPI == EPI_GATED) {
-                        bf16* out = reinterpret_cast<bf16*>(a.out);
-                        out[(size_t)m * inter + unit * 2 + p] =
+                        reinterpret_cast<bf16*>(a.out)[(size_t)m * inter + na] =
                             __float2bfloat16_rn((va / (1.0f + expf(-va))) * vb);
                     } else {
-                        const bool first = (i == 0);
-                        int pos = first ? pre_pos : a.token_pos[m];
-                        if (pos >= 0) {
-                            int head = r0 / a.d, j = r0 - head * a.d + p;
-                            va = round_bf16(va);
-                            vb = round_bf16(vb);
-                            bool is_v = head >= a.nq + a.nkv;
-                            if (a.sin_t && !is_v) {
-                                float c = first ? pre_c : a.cos_t[(size_t)pos * half + j];
-                                float s = first ? pre_s : a.sin_t[(size_t)pos * half + j];
-                                float ra = va * c - vb * s, rb = vb * c + va * s;
-                                va = ra;
-                                vb = rb;
-                            }
-                            bf16 ta = __float2bfloat16_rn(va), tb = __float2bfloat16_rn(vb);
-                            if (head < a.nq) {
-                                bf16* out = reinterpret_cast<bf16*>(a.out) +
-                                            ((size_t)m * a.nq + head) * a.d;
-                                out[j] = ta;
-                                out[j + half] = tb;
-                            } else {
-                                int hk = is_v ? head - a.nq - a.nkv : head - a.nq;
-                                bf16* cache = is_v ? a.v_cache : a.k_cache;
-                                int page = first ? pre_page
-                                                 : a.page_table[(size_t)a.token_seq[m] * a.table_cols +
-                                                                pos / a.page_size];
-                                size_t dst = ((size_t)(page * a.nkv + hk) * a.page_size +
-                                              (pos % a.page_size)) * a.d;
-                                cache[dst + j] = ta;
-                                cache[dst + j + half] = tb;
-                            }
+                        int pos = a.token_pos[m];
+                        if (pos < 0) continue;
+                        int head = na / a.d, j = na - head * a.d;
+                        va = round_bf16(va);
+                        vb = round_bf16(vb);
+                        bool is_v = head >= a.nq + a.nkv;
+                        if (a.sin_t && !is_v) {
+                            float c = a.cos_t[(size_t)pos * half + j];
+                            float s = a.sin_t[(size_t)pos * half + j];
+                            float ra = va * c - vb * s, rb = vb * c + va * s;
+                            va = ra;
+                            vb = rb;
+                        }
+                        bf16 ta = __float2bfloat16_rn(va), tb = __float2bfloat16_rn(vb);
+                        if (head < a.nq) {
+                            bf16* o = reinterpret_cast<bf16*>(a.out) + ((size_t)m * a.nq + head) * a.d;
+                            o[j] = ta;
+                            o[j + half] = tb;
+                        } else {
+                            int hk = is_v ? head - a.nq - a.nkv : head - a.nq;
+                            bf16* cache = is_v ? a.v_cache : a.k_cache;
+                            int page = a.page_table[(size_t)a.token_seq[m] * a.table_cols +
+                                                    pos / a.page_size];
+                            size_t dst = ((size_t)(page * a.nkv + hk) * a.page_size +
+                                          (pos % a.page_size)) * a.d;
+                            cache[dst + j] = ta;
+                            cache[dst + j + half] = tb;
                         }
                     }
                 }
-            } else {
-                int idx = pass * 32 + lane;
-                int m = idx >> 2, r = idx & 3;
-                if (idx < MT * 4 && m < M) {
-                    int n = (r < 2 ? r0 + r : r2 + r - 2);
-                    float v = pick<MT * 4>(acc, idx) + (a.bias ? a.bias[n] : 0.f);
-                    size_t o = (size_t)m * a.N + n;
-                    if (EPI == EPI_STORE) reinterpret_cast<bf16*>(a.out)[o] = __float2bfloat16_rn(v);
-                    else if (EPI == EPI_STORE_F32) reinterpret_cast<float*>(a.out)[o] = v;
-                    else if (EPI == EPI_ADD_F32) {
-                        float old = (i == 0) ? (pass == 0 ? pre_old0 : pre_old1)
-                                             : reinterpret_cast<const float*>(a.out)[o];
-                        reinterpret_cast<float*>(a.out)[o] = old + v;
-                    }
-                    else {
-                        if (a.logits) a.logits[o] = v;
-                        if (better(v, n, best_v[pass], best_i[pass])) {
-                            best_v[pass] = v;
-                            best_i[pass] = n;
+            }
+        } else {
+            const int n0 = unit * 8 + c_lo;
+            const float b0v = a.bias ? a.bias[n0] : 0.f, b1v = a.bias ? a.bias[n0 + 1] : 0.f;
+#pragma unroll
+            for (int t = 0; t < MTILES; ++t) {
+#pragma unroll
+                for (int hrow = 0; hrow < 2; ++hrow) {
+                    int m = t * 16 + r_lo + hrow * 8;
+                    if (m >= M) continue;
+                    float v0 = acc[t][hrow * 2] + b0v, v1 = acc[t][hrow * 2 + 1] + b1v;
+                    size_t o = (size_t)m * a.N + n0;
+                    if (EPI == EPI_STORE) {
+                        *reinterpret_cast<uint32_t*>(reinterpret_cast<bf16*>(a.out) + o) = pack_bf16(v0, v1);
+                    } else if (EPI == EPI_STORE_F32) {
+                        *reinterpret_cast<float2*>(reinterpret_cast<float*>(a.out) + o) = make_float2(v0, v1);
+                    } else if (EPI == EPI_ADD_F32) {
+                        float2* p = reinterpret_cast<float2*>(reinterpret_cast<float*>(a.out) + o);
+                        float2 old = *p;
+                        *p = make_float2(old.x + v0, old.y + v1);
+                    } else {
+                        if (a.logits) *reinterpret_cast<float2*>(a.logits + o) = make_float2(v0, v1);
+                        if (better(v0, n0, best_v[t][hrow], best_i[t][hrow])) {
+                            best_v[t][hrow] = v0;
+                            best_i[t][hrow] = n0;
+                        }
+                        if (better(v1, n0 + 1, best_v[t][hrow], best_i[t][hrow])) {
+                            best_v[t][hrow] = v1;
+                            best_i[t][hrow] = n0 + 1;
                         }
                     }
                 }
@@ -416,31 +381,31 @@ gemv_kernel(GemvArgs a) {
     if (failed && lane == 0 && a.status) atomicExch(a.status, 2);
 
     if (EPI == EPI_ARGMAX) {
-        // lanes 4m .. 4m+3 (of pass p) hold row m's candidates: fold them, then the
-        // warps, then the CTAs; the last CTA to arrive finishes the rows.
+        // the four lanes of a row hold its candidates: fold them, then the warps,
+        // then the CTAs; the last CTA to arrive finishes the rows.
 #pragma unroll
-        for (int pass = 0; pass < SLOTS; ++pass) {
+        for (int t = 0; t < MTILES; ++t)
 #pragma unroll
-            for (int o = 1; o < 4; o <<= 1) {
-                float ov = __shfl_xor_sync(0xffffffffu, best_v[pass], o);
-                int oi = __shfl_xor_sync(0xffffffffu, best_i[pass], o);
-                if (oi >= 0 && better(ov, oi, best_v[pass], best_i[pass])) {
-                    best_v[pass] = ov;
-                    best_i[pass] = oi;
+            for (int hrow = 0; hrow < 2; ++hrow) {
+#pragma unroll
+                for (int o = 1; o < 4; o <<= 1) {
+                    float ov = __shfl_xor_sync(0xffffffffu, best_v[t][hrow], o);
+                    int oi = __shfl_xor_sync(0xffffffffu, best_i[t][hrow], o);
+                    if (oi >= 0 && better(ov, oi, best_v[t][hrow], best_i[t][hrow])) {
+                        best_v[t][hrow] = ov;
+                        best_i[t][hrow] = oi;
+                    }
+                }
+                if ((lane & 3) == 0) {
+                    cta_val[warp][t * 16 + r_lo + hrow * 8] = best_v[t][hrow];
+                    cta_idx[warp][t * 16 + r_lo + hrow * 8] = best_i[t][hrow];
                 }
             }
-            int m = (pass * 32 + lane) >> 2;
-            if ((lane & 3) == 0 && m < MT) {
-                cta_val[warp][m] = best_v[pass];
-                cta_idx[warp][m] = best_i[pass];
-            }
-        }
         __syncthreads();
-        if (threadIdx.x < MT && threadIdx.x < M) {
-            int m = threadIdx.x;
+        for (int m = threadIdx.x; m < M; m += WARPS * 32) {
             float bv = -FLT_MAX;
             int bi = -1;
-            for (int w = 0; w < kGemvWarps; ++w) {
+            for (int w = 0; w < WARPS; ++w) {
                 if (cta_idx[w][m] >= 0 && better(cta_val[w][m], cta_idx[w][m], bv, bi)) {
                     bv = cta_val[w][m];
                     bi = cta_idx[w][m];
@@ -455,7 +420,7 @@ gemv_kernel(GemvArgs a) {
         __syncthreads();
         if (is_last) {
             __threadfence();
-            for (int m = warp; m < M; m += kGemvWarps) {
+            for (int m = warp; m < M; m += WARPS) {
                 float bv = -FLT_MAX;
                 int bi = -1;
                 for (int c = lane; c < (int)gridDim.x; c += 32) {
@@ -489,18 +454,68 @@ gemv_kernel(GemvArgs a) {
     }
 }
 
-template <int MT, int EPI, int PRO, int S>
-static int launch_gemv_final(const GemvArgs& a, int grid, size_t smem, bool pdl, cudaStream_t stream) {
-    auto kernel = gemv_kernel<MT, EPI, PRO, S>;
-    if (smem > 48 * 1024) {
+struct GemvPlan {
+    int mtiles, warps, stages, grid;
+    bool splitk;
+    size_t smem;
+};
+
+// Shared memory of one CTA: x, the weight stages, the barriers, and with split K
+// the warps' partial sums.
+static size_t gemv_smem(int mtiles, int warps, int stages, int K, bool splitk) {
+    size_t sets = splitk ? 1 : (size_t)warps * stages;
+    return ((size_t)mtiles * 16 + sets * 8) * (K + 8) * sizeof(bf16) + (size_t)warps * stages * 8 +
+           (splitk ? (size_t)warps * mtiles * 4 * 32 * sizeof(float) : 0);
+}
+
+static bool gemv_plan(int M, int N, int K, int sm_count, GemvPlan* plan) {
+    if (M <= 0 || M > 64 || K <= 0 || K % 16 || N <= 0 || N % 8) return false;
+    int sms = sm_count > 0 ? sm_count : 148;
+    int mtiles = (M + 15) / 16;
+    int units = N / 8;
+    const size_t budget = 200 * 1024;
+    // Few units: one per CTA, its eight warps sharing K.
+    {
+        size_t smem = gemv_smem(mtiles, 8, 1, K, true);
+        size_t per_sm = smem + 1024;
+        int fit = (int)((220 * 1024) / per_sm);
+        if (fit > 8) fit = 8;
+        if (smem <= budget && fit >= 1 && units <= sms * fit) {
+            plan->mtiles = mtiles; plan->warps = 8; plan->stages = 1; plan->grid = units;
+            plan->splitk = true; plan->smem = smem;
+            return true;
+        }
+    }
+    for (int warps = 8; warps >= 4; warps -= 4) {
+        // Many units: as many CTAs as fit (units are dealt to CTAs first), each
+        // warp streaming its own units through one or two stages.
+        for (int stages = 2; stages >= 1; --stages) {
+            size_t smem = gemv_smem(mtiles, warps, stages, K, false);
+            if (smem > budget) continue;
+            int cap = smem > 110 * 1024 ? sms : sms * 2;
+            int grid = units < cap ? units : cap;
+            bool many = units > grid * warps;  // some warp has several units
+            if (stages == 2 && (!many || smem > 100 * 1024)) continue;
+            plan->mtiles = mtiles; plan->warps = warps; plan->stages = stages; plan->grid = grid;
+            plan->splitk = false; plan->smem = smem;
+            return true;
+        }
+    }
+    return false;
+}
+
+template <int MTILES, int EPI, int PRO, int S, int WARPS, bool SPLITK>
+static int launch_gemv_final(const GemvArgs& a, const GemvPlan& plan, bool pdl, cudaStream_t stream) {
+    auto kernel = gemv_kernel<MTILES, EPI, PRO, S, WARPS, SPLITK>;
+    if (plan.smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)smem);
+                                             (int)plan.smem);
         if (e != cudaSuccess) return (int)e;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(kGemvWarps * 32);
-    cfg.dynamicSmemBytes = smem;
+    cfg.gridDim = dim3(plan.grid);
+    cfg.blockDim = dim3(WARPS * 32);
+    cfg.dynamicSmemBytes = plan.smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -511,24 +526,26 @@ static int launch_gemv_final(const GemvArgs& a, int grid, size_t smem, bool pdl,
     return e == cudaSuccess ? NNIS_OK : (int)e;
 }
 
-template <int MT, int EPI, int PRO>
-static int launch_gemv_stages(const GemvArgs& a, int stages, int grid, size_t smem, bool pdl,
-                              cudaStream_t stream) {
-    if (stages == 2) return launch_gemv_final<MT, EPI, PRO, 2>(a, grid, smem, pdl, stream);
-    return launch_gemv_final<MT, EPI, PRO, 1>(a, grid, smem, pdl, stream);
+template <int MTILES, int EPI, int PRO>
+static int launch_gemv_shape(const GemvArgs& a, const GemvPlan& p, bool pdl, cudaStream_t stream) {
+    if (p.splitk) return launch_gemv_final<MTILES, EPI, PRO, 1, 8, true>(a, p, pdl, stream);
+    if (p.warps == 8)
+        return p.stages == 2 ? launch_gemv_final<MTILES, EPI, PRO, 2, 8, false>(a, p, pdl, stream)
+                             : launch_gemv_final<MTILES, EPI, PRO, 1, 8, false>(a, p, pdl, stream);
+    return p.stages == 2 ? launch_gemv_final<MTILES, EPI, PRO, 2, 4, false>(a, p, pdl, stream)
+                         : launch_gemv_final<MTILES, EPI, PRO, 1, 4, false>(a, p, pdl, stream);
 }
 
-template <int MT>
-static int launch_gemv_epi(const GemvArgs& a, int epi, int pro, int stages, int grid, size_t smem,
-                           bool pdl, cudaStream_t stream) {
-#define NNIS_GEMV(EPI, PRO) return launch_gemv_stages<MT, EPI, PRO>(a, stages, grid, smem, pdl, stream)
+template <int MTILES>
+static int launch_gemv_epi(const GemvArgs& a, int epi, int pro, const GemvPlan& p, bool pdl,
+                           cudaStream_t stream) {
+#define NNIS_GEMV(EPI, PRO) return launch_gemv_shape<MTILES, EPI, PRO>(a, p, pdl, stream)
     // the pairs of prologue and epilogue that the decode step uses
     if (epi == EPI_QKV && pro == PRO_NORM) NNIS_GEMV(EPI_QKV, PRO_NORM);
     if (epi == EPI_QKV && pro == PRO_PLAIN) NNIS_GEMV(EPI_QKV, PRO_PLAIN);
     if (epi == EPI_GATED && pro == PRO_NORM) NNIS_GEMV(EPI_GATED, PRO_NORM);
     if (epi == EPI_GATED && pro == PRO_PLAIN) NNIS_GEMV(EPI_GATED, PRO_PLAIN);
     if (epi == EPI_ADD_F32 && pro == PRO_PLAIN) NNIS_GEMV(EPI_ADD_F32, PRO_PLAIN);
-    if (epi == EPI_ADD_F32 && pro == PRO_MERGE) NNIS_GEMV(EPI_ADD_F32, PRO_MERGE);
     if (epi == EPI_STORE && pro == PRO_PLAIN) NNIS_GEMV(EPI_STORE, PRO_PLAIN);
     if (epi == EPI_STORE_F32 && pro == PRO_PLAIN) NNIS_GEMV(EPI_STORE_F32, PRO_PLAIN);
     if (epi == EPI_STORE_F32 && pro == PRO_NORM) NNIS_GEMV(EPI_STORE_F32, PRO_NORM);
@@ -540,70 +557,59 @@ static int launch_gemv_epi(const GemvArgs& a, int epi, int pro, int stages, int 
 
 }  // namespace nnis
 
+// Whether nnis_gemv_bf16 takes a shape (1) or the caller must use the general
+// kernels (0): at most 64 rows, K a multiple of 16, N a multiple of 8, and x plus
+// the weight stages must fit shared memory.
+NNIS_API int nnis_gemv_takes(int M, int N, int K, int sm_count) {
+    nnis::GemvPlan p;
+    return nnis::gemv_plan(M, N, K, sm_count, &p) ? 1 : 0;
+}
+
 // How many CTAs a launch with these sizes has: the ARGMAX scratch is
 // [M, this many] values and indices.
 NNIS_API int nnis_gemv_grid(int M, int N, int K, int sm_count) {
-    int units = N / 4;
-    int grid = (units + nnis::kGemvWarps - 1) / nnis::kGemvWarps;
-    int cap = (sm_count > 0 ? sm_count : 148) * 2;
-    return grid > cap ? cap : grid;
+    nnis::GemvPlan p;
+    return nnis::gemv_plan(M, N, K, sm_count, &p) ? p.grid : 0;
 }
 
-// Refuses (NNIS_ERR_UNSUPPORTED) what it does not take: M > 16, K not a multiple
-// of 8, N not a multiple of 4, operands too large for shared memory; the caller
-// then takes the general kernels.  Scratch: the merge prologue reads `partial`
-// (written by the decode attention kernel); the ARGMAX epilogue uses `best_val`,
-// `best_idx` ([M, nnis_gemv_grid()] each) and `ticket` (one zeroed counter).
+// Scratch: the ARGMAX epilogue uses `best_val`, `best_idx` ([M, nnis_gemv_grid()]
+// each) and `ticket` (one zeroed counter, left zero).
 NNIS_API int nnis_gemv_bf16(const void* x, const float* hidden, const int* rows, const float* norm_w,
-                            float eps, const float* partial, int splits, const void* w,
-                            const float* bias, void* out, int M, int N, int K, int epilogue,
-                            const int* token_pos, const int* token_seq, const int* page_table,
-                            int table_cols, const float* cos_t, const float* sin_t, void* k_cache,
-                            void* v_cache, int nq, int nkv, int d, int page_size, float* logits,
-                            float* best_val, int* best_idx, unsigned* ticket, int* next_tokens,
-                            int* next_pos, int* status, int sm_count, int pdl, cudaStream_t stream) {
+                            float eps, const void* w, const float* bias, void* out, int M, int N,
+                            int K, int epilogue, const int* token_pos, const int* token_seq,
+                            const int* page_table, int table_cols, const float* cos_t,
+                            const float* sin_t, void* k_cache, void* v_cache, int nq, int nkv, int d,
+                            int page_size, float* logits, float* best_val, int* best_idx,
+                            unsigned* ticket, int* next_tokens, int* next_pos, int* status,
+                            int sm_count, int pdl, cudaStream_t stream) {
     using namespace nnis;
     if (M <= 0 || N <= 0 || K <= 0 || !w || !out) return NNIS_ERR_ARGUMENT;
-    if (M > 16 || K % 8 || N % 4) return NNIS_ERR_UNSUPPORTED;
-    int pro = hidden ? PRO_NORM : (partial ? PRO_MERGE : PRO_PLAIN);
+    GemvPlan plan;
+    if (!gemv_plan(M, N, K, sm_count, &plan)) return NNIS_ERR_UNSUPPORTED;
+    int pro = hidden ? PRO_NORM : PRO_PLAIN;
     if (pro == PRO_PLAIN && !x) return NNIS_ERR_ARGUMENT;
     if (pro == PRO_NORM && (!norm_w || !(eps > 0.f))) return NNIS_ERR_ARGUMENT;
-    if (pro == PRO_MERGE && (splits <= 0 || splits > 64 || nq <= 0 || d <= 0 || nq * d != K))
-        return NNIS_ERR_ARGUMENT;
-    if (((uintptr_t)w | (uintptr_t)x) % 16) return NNIS_ERR_ALIGNMENT;
-    if (epilogue == EPI_GATED && N % 8) return NNIS_ERR_UNSUPPORTED;
+    if (((uintptr_t)w | (uintptr_t)x | (uintptr_t)hidden | (uintptr_t)norm_w | (uintptr_t)out) % 16)
+        return NNIS_ERR_ALIGNMENT;
     if (epilogue == EPI_QKV) {
-        if (!token_pos || d <= 0 || d % 4 || N != (nq + 2 * nkv) * d) return NNIS_ERR_ARGUMENT;
+        if (!token_pos || d <= 0 || d % 8 || N != (nq + 2 * nkv) * d) return NNIS_ERR_ARGUMENT;
         if (nkv > 0 && (!token_seq || !page_table || !k_cache || !v_cache || page_size <= 0))
             return NNIS_ERR_ARGUMENT;
     }
     if (epilogue == EPI_ARGMAX && (!best_val || !best_idx || !ticket)) return NNIS_ERR_ARGUMENT;
     if (epilogue == EPI_ARGMAX && next_tokens && !next_pos) return NNIS_ERR_ARGUMENT;
-    int mt = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : M <= 8 ? 8 : 16;
-    int grid = nnis_gemv_grid(M, N, K, sm_count);
-    int units = N / 4;
-    // a second stage only pays when a warp has more than one unit
-    int stages = units > grid * kGemvWarps ? 2 : 1;
-    auto bytes = [&](int s) {
-        return ((size_t)mt + (size_t)kGemvWarps * s * 4) * K * sizeof(bf16) + kGemvWarps * s * 8;
-    };
-    if (stages == 2 && bytes(2) > 100 * 1024) stages = 1;
-    size_t smem = bytes(stages);
-    if (smem > 200 * 1024) return NNIS_ERR_UNSUPPORTED;
     GemvArgs a;
     a.x = (const bf16*)x; a.hidden = hidden; a.rows = rows; a.norm_w = norm_w; a.eps = eps;
-    a.partial = partial; a.splits = splits;
     a.w = (const bf16*)w; a.bias = bias; a.out = out; a.M = M; a.N = N; a.K = K; a.status = status;
     a.token_pos = token_pos; a.token_seq = token_seq; a.page_table = page_table;
     a.table_cols = table_cols; a.cos_t = cos_t; a.sin_t = sin_t; a.k_cache = (bf16*)k_cache;
-    a.v_cache = (bf16*)v_cache; a.nq = nq; a.nkv = nkv; a.d = d > 0 ? d : 4; a.page_size = page_size;
+    a.v_cache = (bf16*)v_cache; a.nq = nq; a.nkv = nkv; a.d = d > 0 ? d : 8; a.page_size = page_size;
     a.logits = logits; a.best_val = best_val; a.best_idx = best_idx; a.ticket = ticket;
     a.next_tokens = next_tokens; a.next_pos = next_pos;
-    switch (mt) {
-        case 1: return launch_gemv_epi<1>(a, epilogue, pro, stages, grid, smem, pdl != 0, stream);
-        case 2: return launch_gemv_epi<2>(a, epilogue, pro, stages, grid, smem, pdl != 0, stream);
-        case 4: return launch_gemv_epi<4>(a, epilogue, pro, stages, grid, smem, pdl != 0, stream);
-        case 8: return launch_gemv_epi<8>(a, epilogue, pro, stages, grid, smem, pdl != 0, stream);
-        default: return launch_gemv_epi<16>(a, epilogue, pro, stages, grid, smem, pdl != 0, stream);
+    switch (plan.mtiles) {
+        case 1: return launch_gemv_epi<1>(a, epilogue, pro, plan, pdl != 0, stream);
+        case 2: return launch_gemv_epi<2>(a, epilogue, pro, plan, pdl != 0, stream);
+        case 3: return launch_gemv_epi<3>(a, epilogue, pro, plan, pdl != 0, stream);
+        default: return launch_gemv_epi<4>(a, epilogue, pro, plan, pdl != 0, stream);
     }
 }

@@ -238,11 +238,14 @@ def sm_count(device) -> int:
     return _sm_count[key]
 
 
-def gemv_takes(m: int, n: int, k: int, epilogue: int = EPI_STORE) -> bool:
-    """Whether the decode projection kernel runs this shape (else the general kernels)."""
-    mt = 1 if m <= 1 else 2 if m <= 2 else 4 if m <= 4 else 8 if m <= 8 else 16
-    return m <= 16 and k % 8 == 0 and n % (8 if epilogue == EPI_GATED else 4) == 0 \
-        and (mt + 32) * k * 2 + 64 <= 200 * 1024
+def gemv_takes(m: int, n: int, k: int, epilogue: int = EPI_STORE, device=None) -> bool:
+    """Whether the decode projection kernel runs this shape (else the general
+    kernels): at most 64 rows, K in steps of 16, N in steps of 8, operands that fit
+    shared memory."""
+    if m > 64 or k % 16 or n % 8:
+        return False
+    sms = sm_count(device) if device is not None else 148
+    return bool(_lib().nnis_gemv_takes(m, n, k, sms))
 
 
 def gemv_bf16(w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, epilogue: int,
@@ -253,19 +256,17 @@ def gemv_bf16(w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, 
               page_table: Optional[torch.Tensor] = None, cos: Optional[torch.Tensor] = None,
               sin: Optional[torch.Tensor] = None, k_cache: Optional[torch.Tensor] = None,
               v_cache: Optional[torch.Tensor] = None, heads: int = 0, kv_heads: int = 0,
-              head_dim: int = 0, page_size: int = 0, partial: Optional[torch.Tensor] = None,
-              splits: int = 0, logits: Optional[torch.Tensor] = None,
+              head_dim: int = 0, page_size: int = 0, logits: Optional[torch.Tensor] = None,
               scratch: Optional[torch.Tensor] = None, next_tokens: Optional[torch.Tensor] = None,
               next_pos: Optional[torch.Tensor] = None) -> None:
-    """A decode-step projection with its prologue and epilogue fused (at most 16
-    rows).  The input is ``x`` (bfloat16 [m, k]), or ``hidden`` (float32 residual
-    rows, normed with ``norm_weight``/``eps`` on the way in; ``rows`` picks them),
-    or ``partial`` (split-KV records of the decode attention kernel, merged on the
-    way in; ``heads``/``head_dim``/``splits`` describe them).  EPI_ARGMAX writes
+    """A decode-step projection with its prologue and epilogue fused (at most 64
+    rows).  The input is ``x`` (bfloat16 [m, k]) or ``hidden`` (float32 residual
+    rows, normed with ``norm_weight``/``eps`` on the way in; ``rows`` picks them).
+    EPI_ARGMAX writes
     int32 picks to ``out``; ``scratch`` (int32, ``argmax_scratch_ints``) is its
     workspace, ``logits`` optional, ``next_tokens``/``next_pos`` the decode state."""
     _cuda(w, bias, out, x, hidden, norm_weight, rows, token_pos, token_seq, page_table, cos, sin,
-          k_cache, v_cache, partial, logits, scratch, next_tokens, next_pos)
+          k_cache, v_cache, logits, scratch, next_tokens, next_pos)
     n, k = w.shape
     _need(w.dtype == torch.bfloat16, "gemv: bfloat16 weights")
     if hidden is not None:
@@ -276,14 +277,10 @@ def gemv_bf16(w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, 
         m = rows_m if m is None else m
         if rows is not None:
             _need(rows.dtype == torch.int32, "gemv: rows int32")
-    elif partial is not None:
-        _need(partial.dtype == torch.float32 and m is not None and heads * head_dim == k
-              and 0 < splits <= 64 and partial.numel() >= m * heads * splits * (head_dim + 2),
-              "gemv: partial float32 [m * heads, splits, d + 2]")
     else:
         _need(x is not None and x.dtype == torch.bfloat16 and x.shape[1] == k, "gemv: x bfloat16 [m, k]")
         m = x.shape[0] if m is None else m
-    _need(gemv_takes(m, n, k, epilogue), f"gemv: shape m={m} n={n} k={k} is not taken")
+    _need(gemv_takes(m, n, k, epilogue, w.device), f"gemv: shape m={m} n={n} k={k} is not taken")
     if bias is not None:
         _need(bias.dtype == torch.float32 and bias.numel() == n, "gemv: bias float32 [n]")
     if epilogue == EPI_STORE:
@@ -323,8 +320,7 @@ def gemv_bf16(w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, 
         base = scratch.data_ptr()
         ticket, best_val, best_idx = base, base + 16, base + 16 + 4 * m * grid
     _check(_lib().nnis_gemv_bf16(
-        _ptr(x), _ptr(hidden), _ptr(rows), _ptr(norm_weight), ctypes.c_float(eps), _ptr(partial),
-        splits, _ptr(w), _ptr(bias), _ptr(out), m, n, k, epilogue, _ptr(token_pos), _ptr(token_seq),
+        _ptr(x), _ptr(hidden), _ptr(rows), _ptr(norm_weight), ctypes.c_float(eps), _ptr(w), _ptr(bias), _ptr(out), m, n, k, epilogue, _ptr(token_pos), _ptr(token_seq),
         _ptr(page_table), cols, _ptr(cos), _ptr(sin), _ptr(k_cache), _ptr(v_cache), heads, kv_heads,
         head_dim, page_size, _ptr(logits), ctypes.c_void_p(best_val), ctypes.c_void_p(best_idx),
         ctypes.c_void_p(ticket), _ptr(next_tokens), _ptr(next_pos), _ptr(status_word(w.device)),

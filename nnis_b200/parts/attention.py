@@ -90,10 +90,14 @@ class Attention(Part):
 
     # -- run --------------------------------------------------------------
     def _decode_kernels(self, ctx, n: int) -> bool:
-        """The fused bfloat16 decode path: few rows, one token per sequence."""
+        """The fused bfloat16 decode kernel for q, k, v: few rows, one token each."""
         return (self.dtype == torch.bfloat16 and ctx.decode
-                and ops.gemv_takes(n, self.w_qkv.shape[0], self.hidden, ops.EPI_QKV)
-                and ops.gemv_takes(n, self.hidden, self.heads * self.head_dim))
+                and ops.gemv_takes(n, self.w_qkv.shape[0], self.hidden, ops.EPI_QKV, self.device))
+
+    def _fused_out(self, ctx, n: int) -> bool:
+        return (self.dtype == torch.bfloat16 and ctx.decode
+                and ops.gemv_takes(n, self.hidden, self.heads * self.head_dim, ops.EPI_ADD_F32,
+                                   self.device))
 
     def fuses_norm(self, norm, ctx, n: int) -> bool:
         return getattr(norm, "kind", None) == "rmsnorm" and self._decode_kernels(ctx, n)
@@ -161,7 +165,7 @@ class Attention(Part):
                 if splits > 1 else None
             ops.attention_generic(q_buf, q_stride, cache.k, cache.v, ctx.token_pos, ctx.token_seq,
                                   table, attn, nq, nkv, d, self.window, self.scale, splits, partial)
-        if self._decode_kernels(ctx, n):
+        if self._fused_out(ctx, n):
             ops.gemv_bf16(self.w_o, self.b_o, residual, ops.EPI_ADD_F32, x=attn)
         else:
             linear(attn, self.w_o, self.b_o, residual, ADD_F32)

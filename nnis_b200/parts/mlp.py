@@ -56,13 +56,17 @@ class GatedMLP(Part):
         return sum(t.numel() * t.element_size()
                    for t in (self.w_gu, self.w_down, self.b_gu, self.b_down) if t is not None)
 
-    def _decode_kernels(self, ctx, n: int) -> bool:
+    def _fused_gate_up(self, ctx, n: int) -> bool:
+        """The fused bfloat16 decode kernel for gate/up (few rows, one token each)."""
         return (self.dtype == torch.bfloat16 and ctx.decode
-                and ops.gemv_takes(n, 2 * self.inter, self.hidden, ops.EPI_GATED)
-                and ops.gemv_takes(n, self.hidden, self.inter))
+                and ops.gemv_takes(n, 2 * self.inter, self.hidden, ops.EPI_GATED, self.device))
+
+    def _fused_down(self, ctx, n: int) -> bool:
+        return (self.dtype == torch.bfloat16 and ctx.decode
+                and ops.gemv_takes(n, self.hidden, self.inter, ops.EPI_ADD_F32, self.device))
 
     def fuses_norm(self, norm, ctx, n: int) -> bool:
-        return getattr(norm, "kind", None) == "rmsnorm" and self._decode_kernels(ctx, n)
+        return getattr(norm, "kind", None) == "rmsnorm" and self._fused_gate_up(ctx, n)
 
     def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor) -> None:
         self._run(ctx, residual, x=x)
@@ -75,16 +79,18 @@ class GatedMLP(Part):
         n = residual.shape[0]
         ws = ctx.workspace
         act = ws.get("act", (n, self.inter), self.dtype)
-        if self._decode_kernels(ctx, n):
+        if self._fused_gate_up(ctx, n):
             ops.gemv_bf16(self.w_gu, self.b_gu, act, ops.EPI_GATED, x=x, hidden=hidden,
                           norm_weight=norm.weight if norm is not None else None,
                           eps=norm.eps if norm is not None else 0.0, m=n)
+        else:
+            gate_up = ws.get("gate_up", (n, 2 * self.inter), torch.float32)
+            linear(x, self.w_gu, self.b_gu, gate_up, STORE_F32)
+            ops.silu_mul(gate_up, act)
+        if self._fused_down(ctx, n):
             ops.gemv_bf16(self.w_down, self.b_down, residual, ops.EPI_ADD_F32, x=act)
-            return
-        gate_up = ws.get("gate_up", (n, 2 * self.inter), torch.float32)
-        linear(x, self.w_gu, self.b_gu, gate_up, STORE_F32)
-        ops.silu_mul(gate_up, act)
-        linear(act, self.w_down, self.b_down, residual, ADD_F32)
+        else:
+            linear(act, self.w_down, self.b_down, residual, ADD_F32)
 
 
 FEED_FORWARDS.register("gated_mlp", GatedMLP)

@@ -295,10 +295,13 @@ def test_temperature_sampling_follows_the_seeded_draws():
 # ---------------------------------------------------------------------------
 # the fused bfloat16 decode kernels
 # ---------------------------------------------------------------------------
-@pytest.mark.parametrize("m", [1, 2, 3, 8, 11, 16])
-@pytest.mark.parametrize("n,k", [(8, 16), (100, 72), (960, 576), (1000, 1536)])
+@pytest.mark.parametrize("m", [1, 2, 3, 8, 11, 16, 17, 40, 64])
+@pytest.mark.parametrize("n,k", [(8, 16), (104, 80), (960, 576), (1000, 1536)])
 def test_gemv_plain_epilogues_and_norm_prologue(m, n, k):
     o = ops()
+    if not o.gemv_takes(m, n, k, device=DEV):
+        assert m > 32 and k == 1536  # x and the weight stages do not fit shared memory
+        return
     g = torch.Generator().manual_seed(m + n + k)
     w = (torch.randn(n, k, generator=g) / math.sqrt(k)).bfloat16()
     bias = torch.randn(n, generator=g)
@@ -324,11 +327,11 @@ def test_gemv_plain_epilogues_and_norm_prologue(m, n, k):
     close(out32, P.linear(normed, w), "float32", "gemv norm prologue")
 
 
-@pytest.mark.parametrize("m", [1, 5, 16])
+@pytest.mark.parametrize("m", [1, 5, 16, 33, 64])
 def test_gemv_gated_epilogue(m):
     o = ops()
     g = torch.Generator().manual_seed(m)
-    k, inter = 72, 100
+    k, inter = 80, 100
     w = (torch.randn(2 * inter, k, generator=g) / math.sqrt(k) * 3).bfloat16()
     bias = torch.randn(2 * inter, generator=g)
     x = torch.randn(m, k, generator=g).bfloat16()
@@ -343,7 +346,7 @@ def test_gemv_gated_epilogue(m):
 def test_gemv_qkv_epilogue_rotates_and_stores(nq, nkv, d, rotate):
     o = ops()
     g = torch.Generator().manual_seed(nq * d)
-    m, k, page = 5, 40, 64
+    m, k, page = 5, 48, 64
     n = (nq + 2 * nkv) * d
     w = (torch.randn(n, k, generator=g) / math.sqrt(k)).bfloat16()
     bias = torch.randn(n, generator=g)
@@ -382,11 +385,11 @@ def test_gemv_qkv_epilogue_rotates_and_stores(nq, nkv, d, rotate):
 
 def test_gemv_refuses_what_it_does_not_take():
     o = ops()
-    assert not o.gemv_takes(17, 64, 64) and not o.gemv_takes(4, 64, 60) and not o.gemv_takes(4, 66, 64)
-    assert not o.gemv_takes(4, 68, 64, o.EPI_GATED) and o.gemv_takes(4, 68, 64)
+    assert not o.gemv_takes(65, 64, 64) and not o.gemv_takes(4, 64, 56) and not o.gemv_takes(4, 68, 64)
+    assert o.gemv_takes(64, 64, 64) and not o.gemv_takes(64, 64, 4096)
     with pytest.raises(o.KernelError, match="not taken"):
-        o.gemv_bf16(torch.zeros(66, 64, dtype=torch.bfloat16, device=DEV), None,
-                    torch.zeros(2, 66, dtype=torch.bfloat16, device=DEV), o.EPI_STORE,
+        o.gemv_bf16(torch.zeros(68, 64, dtype=torch.bfloat16, device=DEV), None,
+                    torch.zeros(2, 68, dtype=torch.bfloat16, device=DEV), o.EPI_STORE,
                     x=torch.zeros(2, 64, dtype=torch.bfloat16, device=DEV))
 
 
@@ -421,8 +424,8 @@ def test_attention_decode_kernel(nq, nkv, d, window):
         assert float(out[n - 1].float().abs().max()) == 0
 
 
-@pytest.mark.parametrize("m", [1, 6, 16])
-@pytest.mark.parametrize("n,k", [(8, 16), (1000, 72), (49152, 576)])
+@pytest.mark.parametrize("m", [1, 6, 16, 50])
+@pytest.mark.parametrize("n,k", [(8, 16), (1000, 80), (49152, 576)])
 def test_gemv_argmax_epilogue_picks_moves_on_and_can_write_logits(m, n, k):
     o = ops()
     g = torch.Generator().manual_seed(m + n)
@@ -454,43 +457,6 @@ def test_gemv_argmax_epilogue_picks_moves_on_and_can_write_logits(m, n, k):
             assert int(t[m - 1]) == 7 and int(p[m - 1]) == -1
         if with_logits:
             close(logits, want_logits, "float32", "argmax logits")
-    o.check_status(DEV)
-
-
-@pytest.mark.parametrize("nq,nkv,d,splits", [(9, 3, 64, 5), (4, 4, 16, 2), (6, 1, 128, 40)])
-def test_split_records_merged_in_the_output_projection(nq, nkv, d, splits):
-    """Decode attention leaves its split records; the next projection merges
-    them on the way in.  Same result as merging first."""
-    o = ops()
-    lengths = [700, 1, 130]
-    case = PagedCase(lengths, [1] * 3, nq, nkv, d, "bfloat16", seed=d)
-    case.fill_cache()
-    for s, L in enumerate(lengths):
-        pg = int(case.table[s, (L - 1) // 64])
-        case.k_cache[pg, :, (L - 1) % 64] = case.k[s][L - 1]
-        case.v_cache[pg, :, (L - 1) % 64] = case.v[s][L - 1]
-    pos, seq, q, _, _ = case.packed()
-    n = 3
-    qd = q.reshape(n, -1).bfloat16().to(DEV)
-    kc, vc = case.k_cache.bfloat16().to(DEV), case.v_cache.bfloat16().to(DEV)
-    g = torch.Generator().manual_seed(1)
-    wo = (torch.randn(40, nq * d, generator=g) / math.sqrt(nq * d)).bfloat16()
-    attn = torch.empty(n, nq * d, dtype=torch.bfloat16, device=DEV)
-    partial = torch.empty(n * nq * splits * (d + 2), device=DEV)
-    args = (qd, nq * d, kc, vc, pos.to(DEV), seq.to(DEV), case.table.to(DEV), attn, nq, nkv, d, 0,
-            1.0 / math.sqrt(d), splits, partial)
-    o.attention_decode(*args, merge=True)
-    first = torch.zeros(n, 40, device=DEV)
-    o.gemv_bf16(wo.to(DEV), None, first, o.EPI_ADD_F32, x=attn)
-    o.attention_decode(*args, merge=False)
-    second = torch.zeros(n, 40, device=DEV)
-    o.gemv_bf16(wo.to(DEV), None, second, o.EPI_ADD_F32, partial=partial, splits=splits, heads=nq,
-                head_dim=d, m=n)
-    want = torch.cat([P.causal_attention(case.q[s], case.k[s], case.v[s].bfloat16().float())[L - 1:]
-                      .reshape(1, -1) for s, L in enumerate(lengths)])
-    close(attn, want, "bfloat16", "merged attention")
-    close(second, P.linear(want.bfloat16(), wo), "bfloat16", "projection of merged records")
-    close(second, first, "bfloat16", "merge in the prologue vs merge kernel")
     o.check_status(DEV)
 
 
