@@ -5,7 +5,10 @@
 // already, so a sequence may bring a whole prompt or a later chunk of it.
 //
 // One CTA of four warps owns 64 consecutive query tokens of one sequence and one
-// query head (each warp 16 rows of an m16n8k16 tile).  It walks the sequence's
+// query head, each warp 16 rows of an m16n8k16 tile.  (The kernel is written for
+// MT row tiles per warp; two tiles per warp halve the shared-memory reads per
+// product but, with 128-query CTAs, left a single 2,048-token prompt with too few
+// and too unequal CTAs, and measured slower.)  It walks the sequence's
 // pages (64 keys) up to its last query: K and V pages come into swizzled shared
 // memory with 16-byte cp.async copies, two pages ahead; scores S = Q K^T and the
 // update O += P V are matrix products; the online softmax between them is float32
@@ -20,13 +23,13 @@
 
 namespace nnis {
 
-constexpr int kPrefillWarps = 4;
 constexpr int kPrefillRows = 64;   // query rows per CTA
 constexpr int kPrefillPage = 64;
 constexpr int kPrefillStages = 3;
 
-template <int D>
-__global__ void __launch_bounds__(kPrefillWarps * 32)
+// MT row tiles of 16 per warp; 128 / (16 MT) warps
+template <int D, int MT>
+__global__ void __launch_bounds__(kPrefillRows / (16 * MT) * 32)
 attn_prefill_mma_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ k_cache,
                         const bf16* __restrict__ v_cache, const int* __restrict__ tiles,
                         const int* __restrict__ seq_first_row, const int* __restrict__ seq_start,
@@ -34,6 +37,8 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
                         int table_cols, bf16* __restrict__ out, int nq, int nkv, int window,
                         float scale) {
     constexpr int CH = D / 8, NT = D / 8, KS = D / 16;
+    constexpr int kPrefillWarps = kPrefillRows / (16 * MT);
+    constexpr int WR = 16 * MT;  // rows per warp
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* q_s = reinterpret_cast<bf16*>(smem_raw);                  // [64, D] swizzled
     bf16* kv_s = q_s + kPrefillRows * D;                            // stages x (K, V) [64, D]
@@ -78,22 +83,35 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
         *reinterpret_cast<uint4*>(q_s + swz<D>(row, chunk)) = v;
     }
     __syncthreads();
-    uint32_t qa[KS][4];
+    uint32_t qa[MT][KS][4];
 #pragma unroll
-    for (int kk = 0; kk < KS; ++kk)
-        ldmatrix_x4(qa[kk], q_s + swz<D>(warp * 16 + (lane & 15), kk * 2 + (lane >> 4)));
+    for (int t = 0; t < MT; ++t)
+#pragma unroll
+        for (int kk = 0; kk < KS; ++kk)
+            ldmatrix_x4(qa[t][kk], q_s + swz<D>(warp * WR + t * 16 + (lane & 15), kk * 2 + (lane >> 4)));
 
     const int r_lo = lane >> 2, c_lo = (lane & 3) * 2;
-    // positions of this thread's two rows (r_lo and r_lo + 8 of the warp's 16)
-    const int pos_a = pos0 + warp * 16 + r_lo, pos_b = pos_a + 8;
-    const int lo_a = window > 0 ? pos_a - window + 1 : 0, lo_b = window > 0 ? pos_b - window + 1 : 0;
+    // positions of this thread's rows: tile t, rows r_lo and r_lo + 8
+    int pos_r[MT][2], lo_r[MT][2];
+#pragma unroll
+    for (int t = 0; t < MT; ++t)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            pos_r[t][h] = pos0 + warp * WR + t * 16 + r_lo + h * 8;
+            lo_r[t][h] = window > 0 ? pos_r[t][h] - window + 1 : 0;
+        }
 
-    float o[NT][4];
+    float o[MT][NT][4];
+    float m_run[MT][2], l_run[MT][2];
 #pragma unroll
-    for (int j = 0; j < NT; ++j)
+    for (int t = 0; t < MT; ++t) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
-    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[t][j][e] = 0.f;
+        m_run[t][0] = m_run[t][1] = -INFINITY;
+        l_run[t][0] = l_run[t][1] = 0.f;
+    }
     const float sc = scale * kLog2e;
 
     for (int it = 0; it < n_pages; ++it) {
@@ -104,106 +122,120 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
         const bf16* vt = kt + tile_elems;
         const int t0 = (first_page + it) * kPrefillPage;
         // a warp whose rows all lie before this page has nothing to see in it
-        if (t0 > pos0 + warp * 16 + 15) continue;
+        if (t0 > pos0 + warp * WR + WR - 1) continue;
 
-        float s[8][4];
+        float s[MT][8][4];
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
+        for (int t = 0; t < MT; ++t)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[t][j][e] = 0.f;
 #pragma unroll
         for (int kk = 0; kk < KS; kk += 2) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 uint32_t b[4];
                 ldmatrix_x4(b, kt + swz<D>(j * 8 + (lane & 7), kk * 2 + (lane >> 3)));
-                mma_bf16(s[j], qa[kk], b[0], b[1]);
-                mma_bf16(s[j], qa[kk + 1], b[2], b[3]);
+#pragma unroll
+                for (int t = 0; t < MT; ++t) {
+                    mma_bf16(s[t][j], qa[t][kk], b[0], b[1]);
+                    mma_bf16(s[t][j], qa[t][kk + 1], b[2], b[3]);
+                }
             }
         }
-        float mx[2] = {-INFINITY, -INFINITY};
+        uint32_t pa[MT][4][4];  // four k-steps of 16 keys
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
+        for (int t = 0; t < MT; ++t) {
+            float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                int t = t0 + j * 8 + c_lo + (e & 1);
-                bool ok = (e < 2) ? (t <= pos_a && t >= lo_a) : (t <= pos_b && t >= lo_b);
-                float v = ok ? s[j][e] * sc : -INFINITY;
-                s[j][e] = v;
-                mx[e >> 1] = fmaxf(mx[e >> 1], v);
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    int key = t0 + j * 8 + c_lo + (e & 1);
+                    bool ok = key <= pos_r[t][e >> 1] && key >= lo_r[t][e >> 1];
+                    float v = ok ? s[t][j][e] * sc : -INFINITY;
+                    s[t][j][e] = v;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                }
+            float alpha[2], base[2];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                float mn = fmaxf(m_run[t][r], mx[r]);
+                base[r] = mn == -INFINITY ? 0.f : mn;
+                alpha[r] = exp2f(m_run[t][r] - base[r]);
+                m_run[t][r] = mn;
             }
-        float alpha[2], base[2];
+            float psum[2] = {0.f, 0.f};
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-            float mn = fmaxf(m_run[r], mx[r]);
-            base[r] = mn == -INFINITY ? 0.f : mn;
-            alpha[r] = exp2f(m_run[r] - base[r]);
-            m_run[r] = mn;
+            for (int j = 0; j < 8; ++j) {
+                float p0v = exp2f(s[t][j][0] - base[0]), p1v = exp2f(s[t][j][1] - base[0]);
+                float p2v = exp2f(s[t][j][2] - base[1]), p3v = exp2f(s[t][j][3] - base[1]);
+                psum[0] += p0v + p1v;
+                psum[1] += p2v + p3v;
+                pa[t][j >> 1][(j & 1) * 2] = pack_bf16(p0v, p1v);
+                pa[t][j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2v, p3v);
+            }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) l_run[t][r] = l_run[t][r] * alpha[r] + psum[r];
+#pragma unroll
+            for (int jn = 0; jn < NT; ++jn)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) o[t][jn][e] *= alpha[e >> 1];
         }
-        float psum[2] = {0.f, 0.f};
-        uint32_t pa[4][4];  // four k-steps of 16 keys
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            float p0v = exp2f(s[j][0] - base[0]), p1v = exp2f(s[j][1] - base[0]);
-            float p2v = exp2f(s[j][2] - base[1]), p3v = exp2f(s[j][3] - base[1]);
-            psum[0] += p0v + p1v;
-            psum[1] += p2v + p3v;
-            pa[j >> 1][(j & 1) * 2] = pack_bf16(p0v, p1v);
-            pa[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2v, p3v);
-        }
-#pragma unroll
-        for (int r = 0; r < 2; ++r) l_run[r] = l_run[r] * alpha[r] + psum[r];
-#pragma unroll
-        for (int jn = 0; jn < NT; ++jn)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) o[jn][e] *= alpha[e >> 1];
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
 #pragma unroll
             for (int jn = 0; jn < NT; jn += 2) {
                 uint32_t b[4];
                 ldmatrix_x4_trans(b, vt + swz<D>(ks * 16 + (lane & 15), jn + (lane >> 4)));
-                mma_bf16(o[jn], pa[ks], b[0], b[1]);
-                mma_bf16(o[jn + 1], pa[ks], b[2], b[3]);
+#pragma unroll
+                for (int t = 0; t < MT; ++t) {
+                    mma_bf16(o[t][jn], pa[t][ks], b[0], b[1]);
+                    mma_bf16(o[t][jn + 1], pa[t][ks], b[2], b[3]);
+                }
             }
         }
     }
     cp_async_wait<0>();
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
-        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
-    }
-    const float inv_a = l_run[0] > 0.f ? 1.0f / l_run[0] : 0.f;
-    const float inv_b = l_run[1] > 0.f ? 1.0f / l_run[1] : 0.f;
-    const int ra = warp * 16 + r_lo, rb = ra + 8;
+    for (int t = 0; t < MT; ++t) {
 #pragma unroll
-    for (int jn = 0; jn < NT; ++jn) {
-        int col = hq * D + jn * 8 + c_lo;
-        if (ra < rows)
-            *reinterpret_cast<uint32_t*>(out + (size_t)(row_base + ra) * nq * D + col) =
-                pack_bf16(o[jn][0] * inv_a, o[jn][1] * inv_a);
-        if (rb < rows)
-            *reinterpret_cast<uint32_t*>(out + (size_t)(row_base + rb) * nq * D + col) =
-                pack_bf16(o[jn][2] * inv_b, o[jn][3] * inv_b);
+        for (int r = 0; r < 2; ++r) {
+            l_run[t][r] += __shfl_xor_sync(0xffffffffu, l_run[t][r], 1);
+            l_run[t][r] += __shfl_xor_sync(0xffffffffu, l_run[t][r], 2);
+        }
+        const float inv_a = l_run[t][0] > 0.f ? 1.0f / l_run[t][0] : 0.f;
+        const float inv_b = l_run[t][1] > 0.f ? 1.0f / l_run[t][1] : 0.f;
+        const int ra = warp * WR + t * 16 + r_lo, rb = ra + 8;
+#pragma unroll
+        for (int jn = 0; jn < NT; ++jn) {
+            int col = hq * D + jn * 8 + c_lo;
+            if (ra < rows)
+                *reinterpret_cast<uint32_t*>(out + (size_t)(row_base + ra) * nq * D + col) =
+                    pack_bf16(o[t][jn][0] * inv_a, o[t][jn][1] * inv_a);
+            if (rb < rows)
+                *reinterpret_cast<uint32_t*>(out + (size_t)(row_base + rb) * nq * D + col) =
+                    pack_bf16(o[t][jn][2] * inv_b, o[t][jn][3] * inv_b);
+        }
     }
 }
 
-template <int D>
+template <int D, int MT>
 static int launch_prefill(dim3 grid, cudaStream_t stream, const bf16* q, int q_stride, const bf16* k,
                           const bf16* v, const int* tiles, const int* first_row, const int* start,
                           const int* count, const int* table, int cols, bf16* out, int nq, int nkv,
                           int window, float scale) {
     size_t smem = ((size_t)kPrefillRows * D + (size_t)kPrefillStages * 2 * kPrefillPage * D) * sizeof(bf16);
-    auto kernel = attn_prefill_mma_kernel<D>;
+    auto kernel = attn_prefill_mma_kernel<D, MT>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    kernel<<<grid, kPrefillWarps * 32, smem, stream>>>(q, q_stride, k, v, tiles, first_row, start,
+    kernel<<<grid, kPrefillRows / (16 * MT) * 32, smem, stream>>>(q, q_stride, k, v, tiles, first_row, start,
                                                        count, table, cols, out, nq, nkv, window, scale);
     NNIS_RETURN_LAUNCH();
 }
@@ -231,10 +263,10 @@ NNIS_API int nnis_attention_prefill_mma(const void* q, int q_stride, const void*
         return NNIS_ERR_ALIGNMENT;
     dim3 grid(n_tiles, nq);
     if (d == 64)
-        return launch_prefill<64>(grid, stream, (const bf16*)q, q_stride, (const bf16*)k_cache,
+        return launch_prefill<64, 1>(grid, stream, (const bf16*)q, q_stride, (const bf16*)k_cache,
                                   (const bf16*)v_cache, tiles, seq_first_row, seq_start, seq_count,
                                   page_table, table_cols, (bf16*)out, nq, nkv, window, scale);
-    return launch_prefill<128>(grid, stream, (const bf16*)q, q_stride, (const bf16*)k_cache,
+    return launch_prefill<128, 1>(grid, stream, (const bf16*)q, q_stride, (const bf16*)k_cache,
                                (const bf16*)v_cache, tiles, seq_first_row, seq_start, seq_count,
                                page_table, table_cols, (bf16*)out, nq, nkv, window, scale);
 }

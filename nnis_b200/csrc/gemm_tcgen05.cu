@@ -109,15 +109,30 @@ __host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
          | ((uint32_t)(m >> 4) << 24);  // M / 16
 }
 
+enum { GEMM_STORE = 0, GEMM_STORE_F32 = 1, GEMM_ADD_F32 = 2, GEMM_GATED = 3, GEMM_QKV = 4 };
+
 struct GemmArgs {
     const float* bias;
     void* out;
     int M, N, K;
-    int mode;  // 0 bfloat16, 1 float32, 2 add into float32
     int* status;
+    // GEMM_QKV: rotate-half RoPE of q and k heads at each row's position, q to
+    // `out` [M, nq * d], k and v into the paged cache (one head per column tile)
+    const int* token_pos;
+    const int* token_seq;
+    const int* page_table;
+    int table_cols;
+    const float* cos_t;
+    const float* sin_t;
+    bf16* k_cache;
+    bf16* v_cache;
+    int nq, nkv, d, page_size;
 };
 
-template <int BN, int STAGES>
+// MODE GEMM_GATED: W holds gate rows then up rows ([2 I, K]); the CTA multiplies
+// A by a gate tile and by the matching up tile into two accumulators and writes
+// bf16(silu(gate) * up) to out [M, I].  MODE GEMM_QKV: BN equals the head size.
+template <int BN, int STAGES, int MODE>
 __global__ void __launch_bounds__(kGemmThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                GemmArgs g) {
@@ -125,7 +140,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // the swizzle pattern follows address bits: tiles start on 1024-byte boundaries
     unsigned char* base = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr int NB = MODE == GEMM_GATED ? 2 : 1;  // B tiles (and accumulators) per stage
     constexpr uint32_t kBytesA = kBM * kBK * 2, kBytesB = BN * kBK * 2;
+    constexpr uint32_t kTmemCols = NB * BN;
     unsigned char* tile_a = base;
     unsigned char* tile_b = base + (size_t)STAGES * kBytesA;
     __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar;
@@ -135,6 +152,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.y * kBM, n0 = blockIdx.x * BN;
     const int k_blocks = (g.K + kBK - 1) / kBK;
+    const int inter = g.N >> 1;  // GEMM_GATED: columns of the output
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -145,7 +163,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         abort_flag = 0;
         mbar_fence_init();
     }
-    if (warp == 1) tmem_alloc(&tmem_base_s, BN);
+    if (warp == 1) tmem_alloc(&tmem_base_s, kTmemCols);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -165,9 +183,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     break;
                 }
                 if (abort_flag) break;
-                mbar_expect_tx(&full_bar[s], kBytesA + kBytesB);
+                mbar_expect_tx(&full_bar[s], kBytesA + NB * kBytesB);
                 tma_load_2d(tile_a + (size_t)s * kBytesA, &map_a, kb * kBK, m0, &full_bar[s]);
-                tma_load_2d(tile_b + (size_t)s * kBytesB, &map_w, kb * kBK, n0, &full_bar[s]);
+                tma_load_2d(tile_b + (size_t)s * NB * kBytesB, &map_w, kb * kBK, n0, &full_bar[s]);
+                if (NB == 2)
+                    tma_load_2d(tile_b + (size_t)s * NB * kBytesB + kBytesB, &map_w, kb * kBK,
+                                inter + n0, &full_bar[s]);
             }
         }
     } else if (warp == 1) {
@@ -182,12 +203,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
                 tc_fence_after();
                 uint32_t a_addr = smem_addr(tile_a + (size_t)s * kBytesA);
-                uint32_t b_addr = smem_addr(tile_b + (size_t)s * kBytesB);
+                uint32_t b_addr = smem_addr(tile_b + (size_t)s * NB * kBytesB);
 #pragma unroll
                 for (int k = 0; k < kBK / kUmmaK; ++k) {
                     // 16 columns of K further along the swizzled row: 32 bytes
-                    tc_mma(tmem_acc, smem_desc_k128(a_addr + k * kUmmaK * 2),
-                           smem_desc_k128(b_addr + k * kUmmaK * 2), idesc, (kb | k) != 0);
+                    uint64_t da = smem_desc_k128(a_addr + k * kUmmaK * 2);
+                    tc_mma(tmem_acc, da, smem_desc_k128(b_addr + k * kUmmaK * 2), idesc, (kb | k) != 0);
+                    if (NB == 2)
+                        tc_mma(tmem_acc + BN, da, smem_desc_k128(b_addr + kBytesB + k * kUmmaK * 2),
+                               idesc, (kb | k) != 0);
                 }
                 tc_commit(&empty_bar[s]);  // the stage is free once these MMAs have read it
             }
@@ -199,27 +223,113 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
         const int m = m0 + row;
+        const uint32_t lane_base = tmem_acc + ((uint32_t)(quarter * 32) << 16);
         bool ok = mbar_wait(&acc_bar, 0);
         ok = __all_sync(0xffffffffu, ok) && !abort_flag;
         if (!ok) {
             abort_flag = 1;
+        } else if (MODE == GEMM_QKV) {
+            tc_fence_after();
+            // BN == head size: this thread holds one row of one head; columns j and
+            // j + BN/2 are a rotation pair, in chunks c0 and c0 + BN/2
+            const int head = n0 / g.d, half = BN / 2;
+            const bool is_q = head < g.nq, is_v = head >= g.nq + g.nkv;
+            const int pos = m < g.M ? g.token_pos[m] : -1;
+            bf16* dst = nullptr;
+            if (pos >= 0) {
+                if (is_q) {
+                    dst = reinterpret_cast<bf16*>(g.out) + ((size_t)m * g.nq + head) * BN;
+                } else {
+                    int hk = is_v ? head - g.nq - g.nkv : head - g.nq;
+                    int page = g.page_table[(size_t)g.token_seq[m] * g.table_cols + pos / g.page_size];
+                    dst = (is_v ? g.v_cache : g.k_cache) +
+                          ((size_t)(page * g.nkv + hk) * g.page_size + (pos % g.page_size)) * BN;
+                }
+            }
+#pragma unroll 1
+            for (int c0 = 0; c0 < half; c0 += 32) {
+                uint32_t va[32], vb[32];
+                tmem_load32(lane_base + (uint32_t)c0, va);
+                tmem_load32(lane_base + (uint32_t)(c0 + half), vb);
+                if (pos < 0) continue;
+                uint32_t oa[16], ob[16];
+                float cs[32], sn[32];
+                if (g.sin_t && !is_v) {
+                    const float4* c4 = reinterpret_cast<const float4*>(g.cos_t + (size_t)pos * half + c0);
+                    const float4* s4 = reinterpret_cast<const float4*>(g.sin_t + (size_t)pos * half + c0);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        float4 cv = c4[i], sv = s4[i];
+                        cs[i * 4] = cv.x; cs[i * 4 + 1] = cv.y; cs[i * 4 + 2] = cv.z; cs[i * 4 + 3] = cv.w;
+                        sn[i * 4] = sv.x; sn[i * 4 + 1] = sv.y; sn[i * 4 + 2] = sv.z; sn[i * 4 + 3] = sv.w;
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float a0 = __uint_as_float(va[i]), a1 = __uint_as_float(va[i + 1]);
+                    float b0 = __uint_as_float(vb[i]), b1 = __uint_as_float(vb[i + 1]);
+                    if (g.bias) {
+                        a0 += g.bias[n0 + c0 + i];
+                        a1 += g.bias[n0 + c0 + i + 1];
+                        b0 += g.bias[n0 + c0 + half + i];
+                        b1 += g.bias[n0 + c0 + half + i + 1];
+                    }
+                    // q, k and v are bfloat16 before the rotation, as in the unfused path
+                    a0 = __bfloat162float(__float2bfloat16_rn(a0));
+                    a1 = __bfloat162float(__float2bfloat16_rn(a1));
+                    b0 = __bfloat162float(__float2bfloat16_rn(b0));
+                    b1 = __bfloat162float(__float2bfloat16_rn(b1));
+                    if (g.sin_t && !is_v) {
+                        float c_0 = cs[i], c_1 = cs[i + 1], s_0 = sn[i], s_1 = sn[i + 1];
+                        float r0 = a0 * c_0 - b0 * s_0, r1 = a1 * c_1 - b1 * s_1;
+                        b0 = b0 * c_0 + a0 * s_0;
+                        b1 = b1 * c_1 + a1 * s_1;
+                        a0 = r0;
+                        a1 = r1;
+                    }
+                    __nv_bfloat162 pa = __floats2bfloat162_rn(a0, a1), pb = __floats2bfloat162_rn(b0, b1);
+                    oa[i >> 1] = *reinterpret_cast<uint32_t*>(&pa);
+                    ob[i >> 1] = *reinterpret_cast<uint32_t*>(&pb);
+                }
+#pragma unroll
+                for (int i = 0; i < 16; i += 4) {
+                    *reinterpret_cast<uint4*>(dst + c0 + i * 2) = make_uint4(oa[i], oa[i + 1], oa[i + 2], oa[i + 3]);
+                    *reinterpret_cast<uint4*>(dst + c0 + half + i * 2) =
+                        make_uint4(ob[i], ob[i + 1], ob[i + 2], ob[i + 3]);
+                }
+            }
         } else {
             tc_fence_after();
-            const bool vec_ok = (g.N % 8 == 0);
+            // each thread owns one row and writes its 32 consecutive outputs of a chunk
+            const int out_cols = MODE == GEMM_GATED ? inter : g.N;
+            const bool vec_ok = (out_cols % 8 == 0);
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t v[32];
-                tmem_load32(tmem_acc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
-                if (m >= g.M) continue;
+                tmem_load32(lane_base + (uint32_t)c0, v);
                 const int nb = n0 + c0;
-                if (nb >= g.N) continue;
-                const size_t off = (size_t)m * g.N + nb;
-                if (vec_ok && nb + 32 <= g.N) {
-                    float f[32];
+                float f[32];
+                if (MODE == GEMM_GATED) {
+                    uint32_t u[32];
+                    tmem_load32(lane_base + (uint32_t)(BN + c0), u);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        float gv = __uint_as_float(v[i]), uv = __uint_as_float(u[i]);
+                        if (g.bias && nb + i < inter) {
+                            gv += g.bias[nb + i];
+                            uv += g.bias[inter + nb + i];
+                        }
+                        f[i] = (gv / (1.0f + expf(-gv))) * uv;
+                    }
+                } else {
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
-                        f[i] = __uint_as_float(v[i]) + (g.bias ? g.bias[nb + i] : 0.f);
-                    if (g.mode == 0) {
+                        f[i] = __uint_as_float(v[i]) + ((g.bias && nb + i < g.N) ? g.bias[nb + i] : 0.f);
+                }
+                if (m >= g.M || nb >= out_cols) continue;
+                const size_t off = (size_t)m * out_cols + nb;
+                if (vec_ok && nb + 32 <= out_cols) {
+                    if (MODE == GEMM_STORE || MODE == GEMM_GATED) {
                         bf16* o = reinterpret_cast<bf16*>(g.out) + off;
 #pragma unroll
                         for (int i = 0; i < 32; i += 8) {
@@ -236,24 +346,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         }
                     } else {
                         float* o = reinterpret_cast<float*>(g.out) + off;
+                        float4 cur[8];
+                        if (MODE == GEMM_ADD_F32) {
 #pragma unroll
-                        for (int i = 0; i < 32; i += 4) {
-                            float4 cur = make_float4(0.f, 0.f, 0.f, 0.f);
-                            if (g.mode == 2) cur = *reinterpret_cast<const float4*>(o + i);
-                            *reinterpret_cast<float4*>(o + i) =
-                                make_float4(cur.x + f[i], cur.y + f[i + 1], cur.z + f[i + 2],
-                                            cur.w + f[i + 3]);
+                            for (int i = 0; i < 8; ++i) cur[i] = *reinterpret_cast<const float4*>(o + i * 4);
+                        }
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            float4 c4 = MODE == GEMM_ADD_F32 ? cur[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+                            *reinterpret_cast<float4*>(o + i * 4) =
+                                make_float4(c4.x + f[i * 4], c4.y + f[i * 4 + 1], c4.z + f[i * 4 + 2],
+                                            c4.w + f[i * 4 + 3]);
                         }
                     }
                 } else {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
-                        int n = nb + i;
-                        if (n < g.N) {
-                            float val = __uint_as_float(v[i]) + (g.bias ? g.bias[n] : 0.f);
-                            if (g.mode == 0) reinterpret_cast<bf16*>(g.out)[off + i] = __float2bfloat16_rn(val);
-                            else if (g.mode == 1) reinterpret_cast<float*>(g.out)[off + i] = val;
-                            else reinterpret_cast<float*>(g.out)[off + i] += val;
+                        if (nb + i < out_cols) {
+                            if (MODE == GEMM_STORE || MODE == GEMM_GATED)
+                                reinterpret_cast<bf16*>(g.out)[off + i] = __float2bfloat16_rn(f[i]);
+                            else if (MODE == GEMM_STORE_F32)
+                                reinterpret_cast<float*>(g.out)[off + i] = f[i];
+                            else
+                                reinterpret_cast<float*>(g.out)[off + i] += f[i];
                         }
                     }
                 }
@@ -264,7 +379,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_acc, BN);
+        tmem_dealloc(tmem_acc, kTmemCols);
     }
     if (threadIdx.x == 0 && abort_flag && g.status) atomicExch(g.status, 3);
 }
@@ -301,15 +416,17 @@ static bool make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box
               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int MODE>
 static int launch_gemm_tc(const CUtensorMap& ma, const CUtensorMap& mw, const GemmArgs& g, bool pdl,
                           cudaStream_t stream) {
-    size_t smem = (size_t)STAGES * (kBM + BN) * kBK * 2 + 1024;
-    auto kernel = gemm_tc_kernel<BN, STAGES>;
+    constexpr int NB = MODE == GEMM_GATED ? 2 : 1;
+    size_t smem = (size_t)STAGES * (kBM + NB * BN) * kBK * 2 + 1024;
+    auto kernel = gemm_tc_kernel<BN, STAGES, MODE>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
+    int n_cols = MODE == GEMM_GATED ? g.N / 2 : g.N;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((g.N + BN - 1) / BN, (g.M + kBM - 1) / kBM);
+    cfg.gridDim = dim3((n_cols + BN - 1) / BN, (g.M + kBM - 1) / kBM);
     cfg.blockDim = dim3(kGemmThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
@@ -324,26 +441,53 @@ static int launch_gemm_tc(const CUtensorMap& ma, const CUtensorMap& mw, const Ge
 
 }  // namespace nnis
 
+// Modes: 0 store bfloat16, 1 store float32, 2 add into float32, 3 gated
+// (W = [gate rows; up rows], out [M, N / 2] = bf16(silu(gate) * up)), 4 QKV (bias,
+// RoPE, q to out [M, nq * d], k and v into the paged cache; d must be 64 or 128).
 // Refuses (NNIS_ERR_UNSUPPORTED): K not a multiple of 8, grids too large, a
 // driver without tensor-map encoding; operands must be 16-byte aligned.
 NNIS_API int nnis_gemm_tc(const void* A, const void* W, const float* bias, void* C, int M, int N,
-                          int K, int mode, int sm_count, int* status, int pdl, cudaStream_t stream) {
+                          int K, int mode, const int* token_pos, const int* token_seq,
+                          const int* page_table, int table_cols, const float* cos_t,
+                          const float* sin_t, void* k_cache, void* v_cache, int nq, int nkv, int d,
+                          int page_size, int sm_count, int* status, int pdl, cudaStream_t stream) {
     using namespace nnis;
-    if (M <= 0 || N <= 0 || K <= 0 || !A || !W || !C || mode < 0 || mode > 2) return NNIS_ERR_ARGUMENT;
+    if (M <= 0 || N <= 0 || K <= 0 || !A || !W || !C || mode < 0 || mode > 4) return NNIS_ERR_ARGUMENT;
     if (K % 8) return NNIS_ERR_UNSUPPORTED;
     if (((uintptr_t)A | (uintptr_t)W) % 16) return NNIS_ERR_ALIGNMENT;
     if (((uintptr_t)C % 16) != 0) return NNIS_ERR_ALIGNMENT;
     if ((M + kBM - 1) / kBM > 65535) return NNIS_ERR_UNSUPPORTED;
+    GemmArgs g;
+    g.bias = bias; g.out = C; g.M = M; g.N = N; g.K = K; g.status = status;
+    g.token_pos = token_pos; g.token_seq = token_seq; g.page_table = page_table;
+    g.table_cols = table_cols; g.cos_t = cos_t; g.sin_t = sin_t; g.k_cache = (bf16*)k_cache;
+    g.v_cache = (bf16*)v_cache; g.nq = nq; g.nkv = nkv; g.d = d; g.page_size = page_size;
     int sms = sm_count > 0 ? sm_count : 148;
+    CUtensorMap ma, mw;
+    if (mode == GEMM_QKV) {
+        if ((d != 64 && d != 128) || N != (nq + 2 * nkv) * d || !token_pos) return NNIS_ERR_UNSUPPORTED;
+        if (nkv > 0 && (!token_seq || !page_table || !k_cache || !v_cache || page_size <= 0))
+            return NNIS_ERR_ARGUMENT;
+        if (!make_map(&ma, A, M, K, kBM) || !make_map(&mw, W, N, K, d)) return NNIS_ERR_UNSUPPORTED;
+        if (d == 64) return launch_gemm_tc<64, 4, GEMM_QKV>(ma, mw, g, pdl != 0, stream);
+        return launch_gemm_tc<128, 3, GEMM_QKV>(ma, mw, g, pdl != 0, stream);
+    }
+    if (mode == GEMM_GATED) {
+        if (N % 2) return NNIS_ERR_UNSUPPORTED;
+        if (!make_map(&ma, A, M, K, kBM) || !make_map(&mw, W, N, K, 64)) return NNIS_ERR_UNSUPPORTED;
+        return launch_gemm_tc<64, 3, GEMM_GATED>(ma, mw, g, pdl != 0, stream);
+    }
     long tiles128 = (long)((N + 127) / 128) * ((M + kBM - 1) / kBM);
     bool wide = tiles128 >= sms;
-    CUtensorMap ma, mw;
     if (!make_map(&ma, A, M, K, kBM) || !make_map(&mw, W, N, K, wide ? 128 : 64))
         return NNIS_ERR_UNSUPPORTED;
-    GemmArgs g;
-    g.bias = bias; g.out = C; g.M = M; g.N = N; g.K = K; g.mode = mode; g.status = status;
-    // three or four stages (96 KB): two CTAs share an SM, so one CTA's epilogue
-    // overlaps the other's products
-    if (wide) return launch_gemm_tc<128, 3>(ma, mw, g, pdl != 0, stream);
-    return launch_gemm_tc<64, 4>(ma, mw, g, pdl != 0, stream);
+    // three or four stages (about 100 KB): two CTAs share an SM, so one CTA's
+    // epilogue overlaps the other's products
+#define NNIS_GEMM_TC(MODE) \
+    return wide ? launch_gemm_tc<128, 3, MODE>(ma, mw, g, pdl != 0, stream) \
+                : launch_gemm_tc<64, 4, MODE>(ma, mw, g, pdl != 0, stream)
+    if (mode == GEMM_STORE) NNIS_GEMM_TC(GEMM_STORE);
+    if (mode == GEMM_STORE_F32) NNIS_GEMM_TC(GEMM_STORE_F32);
+    NNIS_GEMM_TC(GEMM_ADD_F32);
+#undef NNIS_GEMM_TC
 }

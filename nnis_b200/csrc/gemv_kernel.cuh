@@ -1,0 +1,519 @@
+// (Kernel and launch templates; gemv_bf16.cu holds the entry point and gemv_tiles*.cu
+// the instantiations, one file per number of row tiles, so that they compile side by side.)
+//
+// Projections of a decode step in bfloat16: y[M, N] = x[M, K] . W[N, K]^T with
+// at most 64 rows of x.  The step is bound by the bytes of W and by latency, so
+//
+//  * W is brought into shared memory by bulk asynchronous copies (one per
+//    weight row, completing on an mbarrier), issued before anything else in the
+//    kernel - before the wait of programmatic dependent launch, hence while the
+//    kernel before it still runs - and double-buffered per warp where that pays;
+//  * the products run on the tensor cores (mma.sync m16n8k16, float32
+//    accumulation): x is the 16-row A operand (one to four tiles of rows), eight
+//    weight rows are the B operand, so a warp needs about a hundred instructions
+//    per eight outputs instead of a thousand on the CUDA cores, and no reduction
+//    across lanes;
+//  * what surrounds the product is fused so that no activation makes a round
+//    trip through its own kernel:
+//      prologue  NORM:  x = bf16(rmsnorm(hidden_f32[rows]) * w_norm);
+//      epilogue  STORE (bfloat16), STORE_F32, ADD_F32 (into the residual stream),
+//                GATED:  out[m, i] = bf16(silu(y[m, i]) * y[m, I + i]),
+//                QKV:    bias, round, rotate-half RoPE of q and k heads at each
+//                        row's position, q to a packed buffer, k and v into the
+//                        paged cache,
+//                ARGMAX: the index of the largest y per row (ties to the lower
+//                        index), optionally the float32 logits too, and the move
+//                        of the decode state to the next token.
+//
+// A warp owns eight output rows at a time (a "unit").  Shared-memory rows are
+// padded by 16 bytes so that ldmatrix meets no bank conflict when K is a multiple
+// of 16.  NNIS's one-token projection: crates/nnis-kernels/src/gemv.rs:45-61; its
+// fused gate/up/SiLU kernel: crates/nnis-model/src/fused_swiglu.rs:14-27; its
+// greedy pick: crates/nnis-kernels/src/top_k.rs:57-70.
+#include <float.h>
+
+#pragma once
+
+#include "mma_helpers.cuh"
+
+namespace nnis {
+
+enum { EPI_STORE = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_GATED = 3, EPI_QKV = 4, EPI_ARGMAX = 5 };
+enum { PRO_PLAIN = 0, PRO_NORM = 1 };
+
+struct GemvArgs {
+    const bf16* x;          // [M, K] (plain prologue)
+    const float* hidden;    // [*, K] float32 residual stream (norm prologue)
+    const int* rows;        // optional row of `hidden` per x row
+    const float* norm_w;    // [K]
+    float eps;
+    const bf16* w;          // [N, K]
+    const float* bias;      // [N] or null
+    void* out;              // see epilogues
+    int M, N, K;
+    int* status;            // set non-zero when a bounded wait runs out
+    // QKV epilogue
+    const int* token_pos;
+    const int* token_seq;
+    const int* page_table;
+    int table_cols;
+    const float* cos_t;
+    const float* sin_t;     // null: no rotation
+    bf16* k_cache;
+    bf16* v_cache;
+    int nq, nkv, d, page_size;
+    // ARGMAX epilogue
+    float* logits;          // optional [M, N]
+    float* best_val;        // [M, gridDim.x]
+    int* best_idx;          // [M, gridDim.x]
+    unsigned* ticket;       // one counter, zero between launches
+    int* next_tokens;       // optional: tokens of the next step (picked) ...
+    int* next_pos;          // ... and their positions (+1 on live rows)
+};
+
+__device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+__device__ __forceinline__ bool better(float v, int i, float bv, int bi) {
+    return bi < 0 || v > bv || (v == bv && i < bi);
+}
+
+__device__ __forceinline__ void ldmatrix_x2(uint32_t& r0, uint32_t& r1, const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];"
+                 : "=r"(r0), "=r"(r1)
+                 : "r"(smem_addr(p)));
+}
+
+// Output row of column c (0..7) of unit `unit`: columns 0-3 and 4-7 are the two
+// halves of a pair in the GATED (gate, up) and QKV (j, j + d/2) epilogues.
+template <int EPI>
+__device__ __forceinline__ int unit_row(const GemvArgs& a, int unit, int c) {
+    if (EPI == EPI_GATED) return (c < 4 ? 0 : (a.N >> 1) - 4) + unit * 4 + c;
+    if (EPI == EPI_QKV) {
+        int per_head = a.d >> 3;
+        int head = unit / per_head, jj = (unit - head * per_head) * 4;
+        return head * a.d + jj + (c < 4 ? c : (a.d >> 1) + c - 4);
+    }
+    return unit * 8 + c;
+}
+
+// MTILES tiles of 16 rows of x; WARPS warps per CTA; S stages of weights per warp.
+// SPLITK: the CTA owns one unit and its warps share K (each a run of 16-column
+// steps), which shortens the chain of dependent products when there are fewer
+// units than the GPU has room for; the partial sums meet in shared memory and
+// warp 0 adds them in order and runs the epilogue.
+template <int MTILES, int EPI, int PRO, int S, int WARPS, bool SPLITK>
+__global__ void __launch_bounds__(WARPS * 32)
+gemv_kernel(GemvArgs a) {
+    constexpr int MT = MTILES * 16;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int K = a.K, M = a.M;
+    const int KP = K + 8;  // padded row, in elements
+    bf16* xs = reinterpret_cast<bf16*>(smem_raw);                          // [MT, KP]
+    // weight stages: one set per warp, or one shared set when the warps split K
+    bf16* wst = xs + (size_t)MT * KP + (SPLITK ? 0 : (size_t)warp * S * 8 * KP);
+    constexpr int kSets = SPLITK ? 1 : WARPS * S;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(xs + (size_t)(MT + kSets * 8) * KP) + warp * S;
+    float* red = reinterpret_cast<float*>(bars - warp * S + WARPS * S);     // SPLITK: [WARPS, MTILES*4, 32]
+    __shared__ float cta_val[WARPS][MT];
+    __shared__ int cta_idx[WARPS][MT];
+    __shared__ bool is_last;
+
+    const int n_units = a.N >> 3;
+    const int unit_stride = SPLITK ? gridDim.x : gridDim.x * WARPS;
+    // units are dealt to CTAs first, so that few units still spread over many SMs
+    const int first_unit = SPLITK ? blockIdx.x : warp * gridDim.x + blockIdx.x;
+    // this warp's columns of K: all of them, or its share of the 16-column steps
+    const int steps = K >> 4;
+    const int steps_per_warp = (steps + WARPS - 1) / WARPS;
+    const int k_begin = SPLITK ? min(steps, warp * steps_per_warp) * 16 : 0;
+    const int k_end = SPLITK ? min(steps, (warp + 1) * steps_per_warp) * 16 : K;
+    const uint32_t row_bytes = (uint32_t)(k_end - k_begin) * 2u;
+
+    auto issue = [&](int i) {  // lane 0 only
+        int unit = first_unit + i * unit_stride;
+        if (unit >= n_units || row_bytes == 0) return;
+        uint64_t* bar = bars + (i % S);
+        bf16* dst = wst + (size_t)(i % S) * 8 * KP + k_begin;
+        mbar_expect_tx(bar, 8u * row_bytes);
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+            bulk_load(dst + (size_t)c * KP, a.w + (size_t)unit_row<EPI>(a, unit, c) * K + k_begin,
+                      row_bytes, bar);
+    };
+
+    // ---- weights first: they depend on no earlier kernel ---------------------
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < S; ++s) mbar_init(bars + s, 1);
+        mbar_fence_init();
+#pragma unroll
+        for (int s = 0; s < S; ++s) issue(s);
+    }
+    // ... and the norm weights of this lane's columns
+    constexpr int NW = 6;  // float4 per lane kept in registers: covers K <= 768
+    float4 nw[NW];
+    const int k4 = K >> 2;
+    if (PRO == PRO_NORM) {
+#pragma unroll
+        for (int j = 0; j < NW; ++j) {
+            int c = lane + 32 * j;
+            nw[j] = c < k4 ? reinterpret_cast<const float4*>(a.norm_w)[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    // Dependents are released only after this kernel's own wait: a kernel that
+    // starts early may then rely on everything before its immediate predecessor
+    // (the decode attention kernel reads old cache pages before its wait).
+    pdl_wait();
+    pdl_launch_dependents();
+
+    // ---- x into shared memory ------------------------------------------------
+    if (PRO == PRO_NORM) {
+        const bool in_regs = k4 <= 32 * NW;
+        for (int m = warp; m < MT; m += WARPS) {
+            if (m < M) {
+                const float* h = a.hidden + (size_t)(a.rows ? a.rows[m] : m) * K;
+                const float4* h4 = reinterpret_cast<const float4*>(h);
+                float4 hv[NW];
+                float ss = 0.f;
+                if (in_regs) {
+#pragma unroll
+                    for (int j = 0; j < NW; ++j) {
+                        int c = lane + 32 * j;
+                        hv[j] = c < k4 ? h4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+#pragma unroll
+                    for (int j = 0; j < NW; ++j) {
+                        ss = fmaf(hv[j].x, hv[j].x, ss);
+                        ss = fmaf(hv[j].y, hv[j].y, ss);
+                        ss = fmaf(hv[j].z, hv[j].z, ss);
+                        ss = fmaf(hv[j].w, hv[j].w, ss);
+                    }
+                } else {
+                    for (int k = lane; k < K; k += 32) ss = fmaf(h[k], h[k], ss);
+                }
+                ss = warp_sum(ss);
+                float s = 1.0f / sqrtf(ss * (1.0f / (float)K) + a.eps);
+                if (in_regs) {
+#pragma unroll
+                    for (int j = 0; j < NW; ++j) {
+                        int c = lane + 32 * j;
+                        if (c < k4) {
+                            float4 r = make_float4((hv[j].x * s) * nw[j].x, (hv[j].y * s) * nw[j].y,
+                                                   (hv[j].z * s) * nw[j].z, (hv[j].w * s) * nw[j].w);
+                            store4(xs + (size_t)m * KP + c * 4, r);
+                        }
+                    }
+                } else {
+                    for (int k = lane; k < K; k += 32)
+                        xs[(size_t)m * KP + k] = __float2bfloat16_rn((h[k] * s) * a.norm_w[k]);
+                }
+            } else {
+                for (int k = lane; k < K; k += 32) xs[(size_t)m * KP + k] = __float2bfloat16_rn(0.f);
+            }
+        }
+    } else {
+        const int per_row = K >> 3;  // 16-byte chunks
+        for (int c = threadIdx.x; c < MT * per_row; c += WARPS * 32) {
+            int m = c / per_row, ch = c - m * per_row;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (m < M) v = *reinterpret_cast<const uint4*>(a.x + (size_t)m * K + ch * 8);
+            *reinterpret_cast<uint4*>(xs + (size_t)m * KP + ch * 8) = v;
+        }
+    }
+    __syncthreads();
+
+    // ---- units of eight output rows --------------------------------------------
+    const int half = a.d >> 1;
+    const int inter = a.N >> 1;
+    const int r_lo = lane >> 2, c_lo = (lane & 3) * 2;  // rows r_lo, r_lo + 8; columns c_lo, c_lo + 1
+    float best_v[MTILES][2];
+    int best_i[MTILES][2];
+#pragma unroll
+    for (int t = 0; t < MTILES; ++t) {
+        best_v[t][0] = best_v[t][1] = -FLT_MAX;
+        best_i[t][0] = best_i[t][1] = -1;
+    }
+    bool failed = false;
+    for (int i = 0;; ++i) {
+        int unit = first_unit + i * unit_stride;
+        if (unit >= n_units) break;
+        // the whole warp leaves together if any lane's wait ran out
+        if (row_bytes != 0 &&
+            !__all_sync(0xffffffffu, mbar_wait(bars + (i % S), (uint32_t)(i / S) & 1u))) {
+            failed = true;
+            if (!SPLITK) break;
+        }
+        const bf16* wbuf = wst + (size_t)(i % S) * 8 * KP;
+        float acc[MTILES][4];
+#pragma unroll
+        for (int t = 0; t < MTILES; ++t)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[t][e] = 0.f;
+        // lanes 0-7: weight rows at columns k0..k0+7, lanes 8-15: k0+8..k0+15
+        const bf16* b_ptr = wbuf + (size_t)(lane & 7) * KP + ((lane >> 3) & 1) * 8;
+        const bf16* a_ptr = xs + (size_t)(lane & 15) * KP + (lane >> 4) * 8;
+        // with one tile of rows, two chains of products halve the dependent latency
+        float acc2[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+        for (int k0 = k_begin; k0 < k_end; k0 += 16) {
+            uint32_t b0, b1;
+            ldmatrix_x2(b0, b1, b_ptr + k0);
+#pragma unroll
+            for (int t = 0; t < MTILES; ++t) {
+                uint32_t af[4];
+                ldmatrix_x4(af, a_ptr + (size_t)t * 16 * KP + k0);
+                if (MTILES == 1 && (k0 & 16)) mma_bf16(acc2, af, b0, b1);
+                else mma_bf16(acc[t], af, b0, b1);
+            }
+        }
+        if (MTILES == 1) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[0][e] += acc2[e];
+        }
+        if (SPLITK) {
+            // partial sums of the warps, added by warp 0 in warp order
+#pragma unroll
+            for (int t = 0; t < MTILES; ++t)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) red[((size_t)warp * MTILES * 4 + t * 4 + e) * 32 + lane] = acc[t][e];
+            __syncthreads();
+            if (warp != 0) break;  // one unit per CTA: the other warps are done
+#pragma unroll
+            for (int t = 0; t < MTILES; ++t)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float sum = acc[t][e];
+                    for (int w = 1; w < WARPS; ++w) sum += red[((size_t)w * MTILES * 4 + t * 4 + e) * 32 + lane];
+                    acc[t][e] = sum;
+                }
+        } else {
+            __syncwarp();  // every lane has read this stage: it may be filled again
+            if (lane == 0) issue(i + S);
+        }
+
+        // ---- epilogue: this thread holds rows r_lo (+8) and columns c_lo, c_lo + 1 ---
+        if (EPI == EPI_GATED || EPI == EPI_QKV) {
+            // columns 0-3 pair with 4-7: the lanes of the second half hand theirs over
+            const bool low = (lane & 3) < 2;
+            const int n_a = unit_row<EPI>(a, unit, c_lo & 3);
+            const int n_b = unit_row<EPI>(a, unit, (c_lo & 3) + 4);
+#pragma unroll
+            for (int t = 0; t < MTILES; ++t) {
+                float pv[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) pv[e] = __shfl_xor_sync(0xffffffffu, acc[t][e], 2);
+                if (!low) continue;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    int m = t * 16 + r_lo + (e >> 1) * 8;
+                    if (m >= M) continue;
+                    int na = n_a + (e & 1), nb = n_b + (e & 1);
+                    float va = acc[t][e], vb = pv[e];
+                    if (a.bias) {
+                        va += a.bias[na];
+                        vb += a.bias[nb];
+                    }
+                    if (EPI == EPI_GATED) {
+                        reinterpret_cast<bf16*>(a.out)[(size_t)m * inter + na] =
+                            __float2bfloat16_rn((va / (1.0f + expf(-va))) * vb);
+                    } else {
+                        int pos = a.token_pos[m];
+                        if (pos < 0) continue;
+                        int head = na / a.d, j = na - head * a.d;
+                        va = round_bf16(va);
+                        vb = round_bf16(vb);
+                        bool is_v = head >= a.nq + a.nkv;
+                        if (a.sin_t && !is_v) {
+                            float c = a.cos_t[(size_t)pos * half + j];
+                            float s = a.sin_t[(size_t)pos * half + j];
+                            float ra = va * c - vb * s, rb = vb * c + va * s;
+                            va = ra;
+                            vb = rb;
+                        }
+                        bf16 ta = __float2bfloat16_rn(va), tb = __float2bfloat16_rn(vb);
+                        if (head < a.nq) {
+                            bf16* o = reinterpret_cast<bf16*>(a.out) + ((size_t)m * a.nq + head) * a.d;
+                            o[j] = ta;
+                            o[j + half] = tb;
+                        } else {
+                            int hk = is_v ? head - a.nq - a.nkv : head - a.nq;
+                            bf16* cache = is_v ? a.v_cache : a.k_cache;
+                            int page = a.page_table[(size_t)a.token_seq[m] * a.table_cols +
+                                                    pos / a.page_size];
+                            size_t dst = ((size_t)(page * a.nkv + hk) * a.page_size +
+                                          (pos % a.page_size)) * a.d;
+                            cache[dst + j] = ta;
+                            cache[dst + j + half] = tb;
+                        }
+                    }
+                }
+            }
+        } else {
+            const int n0 = unit * 8 + c_lo;
+            const float b0v = a.bias ? a.bias[n0] : 0.f, b1v = a.bias ? a.bias[n0 + 1] : 0.f;
+#pragma unroll
+            for (int t = 0; t < MTILES; ++t) {
+#pragma unroll
+                for (int hrow = 0; hrow < 2; ++hrow) {
+                    int m = t * 16 + r_lo + hrow * 8;
+                    if (m >= M) continue;
+                    float v0 = acc[t][hrow * 2] + b0v, v1 = acc[t][hrow * 2 + 1] + b1v;
+                    size_t o = (size_t)m * a.N + n0;
+                    if (EPI == EPI_STORE) {
+                        *reinterpret_cast<uint32_t*>(reinterpret_cast<bf16*>(a.out) + o) = pack_bf16(v0, v1);
+                    } else if (EPI == EPI_STORE_F32) {
+                        *reinterpret_cast<float2*>(reinterpret_cast<float*>(a.out) + o) = make_float2(v0, v1);
+                    } else if (EPI == EPI_ADD_F32) {
+                        float2* p = reinterpret_cast<float2*>(reinterpret_cast<float*>(a.out) + o);
+                        float2 old = *p;
+                        *p = make_float2(old.x + v0, old.y + v1);
+                    } else {
+                        if (a.logits) *reinterpret_cast<float2*>(a.logits + o) = make_float2(v0, v1);
+                        if (better(v0, n0, best_v[t][hrow], best_i[t][hrow])) {
+                            best_v[t][hrow] = v0;
+                            best_i[t][hrow] = n0;
+                        }
+                        if (better(v1, n0 + 1, best_v[t][hrow], best_i[t][hrow])) {
+                            best_v[t][hrow] = v1;
+                            best_i[t][hrow] = n0 + 1;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    if (failed && lane == 0 && a.status) atomicExch(a.status, 2);
+
+    if (EPI == EPI_ARGMAX) {
+        // the four lanes of a row hold its candidates: fold them, then the warps,
+        // then the CTAs; the last CTA to arrive finishes the rows.
+#pragma unroll
+        for (int t = 0; t < MTILES; ++t)
+#pragma unroll
+            for (int hrow = 0; hrow < 2; ++hrow) {
+#pragma unroll
+                for (int o = 1; o < 4; o <<= 1) {
+                    float ov = __shfl_xor_sync(0xffffffffu, best_v[t][hrow], o);
+                    int oi = __shfl_xor_sync(0xffffffffu, best_i[t][hrow], o);
+                    if (oi >= 0 && better(ov, oi, best_v[t][hrow], best_i[t][hrow])) {
+                        best_v[t][hrow] = ov;
+                        best_i[t][hrow] = oi;
+                    }
+                }
+                if ((lane & 3) == 0) {
+                    cta_val[warp][t * 16 + r_lo + hrow * 8] = best_v[t][hrow];
+                    cta_idx[warp][t * 16 + r_lo + hrow * 8] = best_i[t][hrow];
+                }
+            }
+        __syncthreads();
+        for (int m = threadIdx.x; m < M; m += WARPS * 32) {
+            float bv = -FLT_MAX;
+            int bi = -1;
+            for (int w = 0; w < WARPS; ++w) {
+                if (cta_idx[w][m] >= 0 && better(cta_val[w][m], cta_idx[w][m], bv, bi)) {
+                    bv = cta_val[w][m];
+                    bi = cta_idx[w][m];
+                }
+            }
+            a.best_val[(size_t)m * gridDim.x + blockIdx.x] = bv;
+            a.best_idx[(size_t)m * gridDim.x + blockIdx.x] = bi;
+        }
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) is_last = atomicAdd(a.ticket, 1u) == gridDim.x - 1;
+        __syncthreads();
+        if (is_last) {
+            __threadfence();
+            for (int m = warp; m < M; m += WARPS) {
+                float bv = -FLT_MAX;
+                int bi = -1;
+                for (int c = lane; c < (int)gridDim.x; c += 32) {
+                    float v = a.best_val[(size_t)m * gridDim.x + c];
+                    int ix = a.best_idx[(size_t)m * gridDim.x + c];
+                    if (ix >= 0 && better(v, ix, bv, bi)) {
+                        bv = v;
+                        bi = ix;
+                    }
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                    int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                    if (oi >= 0 && better(ov, oi, bv, bi)) {
+                        bv = ov;
+                        bi = oi;
+                    }
+                }
+                if (lane == 0) {
+                    int picked = bi < 0 ? 0 : bi;
+                    reinterpret_cast<int*>(a.out)[m] = picked;
+                    if (a.next_tokens && a.next_pos[m] >= 0) {
+                        a.next_tokens[m] = picked;
+                        a.next_pos[m] += 1;
+                    }
+                }
+            }
+            if (threadIdx.x == 0) *a.ticket = 0u;
+        }
+    }
+}
+
+struct GemvPlan {
+    int mtiles, warps, stages, grid;
+    bool splitk;
+    size_t smem;
+};
+
+template <int MTILES, int EPI, int PRO, int S, int WARPS, bool SPLITK>
+static inline int launch_gemv_final(const GemvArgs& a, const GemvPlan& plan, bool pdl, cudaStream_t stream) {
+    auto kernel = gemv_kernel<MTILES, EPI, PRO, S, WARPS, SPLITK>;
+    if (plan.smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)plan.smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(plan.grid);
+    cfg.blockDim = dim3(WARPS * 32);
+    cfg.dynamicSmemBytes = plan.smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, a);
+    return e == cudaSuccess ? NNIS_OK : (int)e;
+}
+
+template <int MTILES, int EPI, int PRO>
+static inline int launch_gemv_shape(const GemvArgs& a, const GemvPlan& p, bool pdl, cudaStream_t stream) {
+    if (p.splitk) return launch_gemv_final<MTILES, EPI, PRO, 1, 8, true>(a, p, pdl, stream);
+    if (p.warps == 8)
+        return p.stages == 2 ? launch_gemv_final<MTILES, EPI, PRO, 2, 8, false>(a, p, pdl, stream)
+                             : launch_gemv_final<MTILES, EPI, PRO, 1, 8, false>(a, p, pdl, stream);
+    return p.stages == 2 ? launch_gemv_final<MTILES, EPI, PRO, 2, 4, false>(a, p, pdl, stream)
+                         : launch_gemv_final<MTILES, EPI, PRO, 1, 4, false>(a, p, pdl, stream);
+}
+
+template <int MTILES>
+int launch_gemv_epi(const GemvArgs& a, int epi, int pro, const GemvPlan& p, bool pdl,
+                           cudaStream_t stream) {
+#define NNIS_GEMV(EPI, PRO) return launch_gemv_shape<MTILES, EPI, PRO>(a, p, pdl, stream)
+    // the pairs of prologue and epilogue that the decode step uses
+    if (epi == EPI_QKV && pro == PRO_NORM) NNIS_GEMV(EPI_QKV, PRO_NORM);
+    if (epi == EPI_QKV && pro == PRO_PLAIN) NNIS_GEMV(EPI_QKV, PRO_PLAIN);
+    if (epi == EPI_GATED && pro == PRO_NORM) NNIS_GEMV(EPI_GATED, PRO_NORM);
+    if (epi == EPI_GATED && pro == PRO_PLAIN) NNIS_GEMV(EPI_GATED, PRO_PLAIN);
+    if (epi == EPI_ADD_F32 && pro == PRO_PLAIN) NNIS_GEMV(EPI_ADD_F32, PRO_PLAIN);
+    if (epi == EPI_STORE && pro == PRO_PLAIN) NNIS_GEMV(EPI_STORE, PRO_PLAIN);
+    if (epi == EPI_STORE_F32 && pro == PRO_PLAIN) NNIS_GEMV(EPI_STORE_F32, PRO_PLAIN);
+    if (epi == EPI_STORE_F32 && pro == PRO_NORM) NNIS_GEMV(EPI_STORE_F32, PRO_NORM);
+    if (epi == EPI_ARGMAX && pro == PRO_NORM) NNIS_GEMV(EPI_ARGMAX, PRO_NORM);
+    if (epi == EPI_ARGMAX && pro == PRO_PLAIN) NNIS_GEMV(EPI_ARGMAX, PRO_PLAIN);
+#undef NNIS_GEMV
+    return NNIS_ERR_UNSUPPORTED;
+}
+
+}  // namespace nnis

@@ -1,0 +1,13 @@
+// Decode projections with 3 tiles of 16 rows of x (up to 48 rows): the instantiations of
+// gemv_kernel.cuh for that many tiles, in a file of their own so that the four files
+// compile side by side.
+#include "gemv_kernel.cuh"
+
+namespace nnis {
+
+int gemv_launch_tiles3(const GemvArgs& a, int epilogue, int prologue, const GemvPlan& plan, bool pdl,
+                        cudaStream_t stream) {
+    return launch_gemv_epi<3>(a, epilogue, prologue, plan, pdl, stream);
+}
+
+}  // namespace nnis

@@ -438,22 +438,56 @@ def gemm_tc_takes(m: int, n: int, k: int) -> bool:
     return bool(TC_GEMM) and m > 16 and k % 8 == 0 and -(-m // 128) <= 65535
 
 
+GEMM_GATED, GEMM_QKV = 3, 4
+
+
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-            mode: int) -> None:
+            mode: int, token_pos: Optional[torch.Tensor] = None,
+            token_seq: Optional[torch.Tensor] = None, page_table: Optional[torch.Tensor] = None,
+            cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None,
+            k_cache: Optional[torch.Tensor] = None, v_cache: Optional[torch.Tensor] = None,
+            heads: int = 0, kv_heads: int = 0, head_dim: int = 0, page_size: int = 0) -> None:
     """out (op)= a . w^T + bias on the tensor cores (tcgen05, float32 accumulation
-    in tensor memory); bfloat16 operands."""
-    _cuda(a, w, bias, out)
+    in tensor memory); bfloat16 operands.  Modes: STORE, STORE_F32, ADD_F32,
+    GEMM_GATED (w = [gate; up] rows, out bfloat16 [m, n / 2] = silu(gate) * up) and
+    GEMM_QKV (bias, RoPE at each row's position, q to out [m, heads * d], k and v
+    into the paged cache; head_dim 64 or 128)."""
+    _cuda(a, w, bias, out, token_pos, token_seq, page_table, cos, sin, k_cache, v_cache)
     m, k = a.shape
     n = w.shape[0]
     _need(a.dtype == w.dtype == torch.bfloat16 and w.shape[1] == k, "gemm_tc: bfloat16 a [m, k], w [n, k]")
-    _need(tuple(out.shape) == (m, n), "gemm_tc: out [m, n]")
-    _need(out.dtype == (torch.bfloat16 if mode == STORE else torch.float32), "gemm_tc: out dtype vs mode")
     _need(gemm_tc_takes(m, n, k), f"gemm_tc: shape m={m} n={n} k={k} is not taken")
     if bias is not None:
         _need(bias.dtype == torch.float32 and bias.numel() == n, "gemm_tc: bias float32 [n]")
-    _check(_lib().nnis_gemm_tc(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), m, n, k, mode,
+    if mode == GEMM_GATED:
+        _need(n % 2 == 0 and out.dtype == torch.bfloat16 and tuple(out.shape) == (m, n // 2),
+              "gemm_tc: gated out bfloat16 [m, n / 2]")
+    elif mode == GEMM_QKV:
+        _need(gemm_tc_qkv_takes(head_dim) and n == (heads + 2 * kv_heads) * head_dim,
+              "gemm_tc: qkv rows / head_dim not taken")
+        _need(out.dtype == torch.bfloat16 and tuple(out.shape) == (m, heads * head_dim),
+              "gemm_tc: q out bfloat16 [m, heads * d]")
+        _need(token_pos is not None and token_pos.dtype == torch.int32 and token_pos.numel() >= m,
+              "gemm_tc: token_pos int32 [m]")
+        if kv_heads > 0:
+            _need(k_cache is not None and k_cache.dtype == torch.bfloat16
+                  and tuple(k_cache.shape[1:]) == (kv_heads, page_size, head_dim)
+                  and page_table is not None and token_seq is not None, "gemm_tc: cache [pages, kv, page, d]")
+        if cos is not None:
+            _need(cos.dtype == torch.float32 and cos.shape[1] == head_dim // 2, "gemm_tc: cos/sin tables")
+    else:
+        _need(tuple(out.shape) == (m, n), "gemm_tc: out [m, n]")
+        _need(out.dtype == (torch.bfloat16 if mode == STORE else torch.float32), "gemm_tc: out dtype vs mode")
+    cols = page_table.shape[1] if page_table is not None else 0
+    _check(_lib().nnis_gemm_tc(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), m, n, k, mode, _ptr(token_pos),
+                               _ptr(token_seq), _ptr(page_table), cols, _ptr(cos), _ptr(sin),
+                               _ptr(k_cache), _ptr(v_cache), heads, kv_heads, head_dim, page_size,
                                sm_count(a.device), _ptr(status_word(a.device)), PDL, _stream()),
            "gemm_tc")
+
+
+def gemm_tc_qkv_takes(head_dim: int) -> bool:
+    return head_dim in (64, 128)
 
 
 def advance(tokens: torch.Tensor, pos: torch.Tensor, picked: torch.Tensor) -> None:

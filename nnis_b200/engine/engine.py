@@ -17,6 +17,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Dict, List, Mapping, Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..cache import PAGE_SIZE, CacheManager
@@ -29,6 +30,8 @@ from .model import DecoderModel
 from .workspace import Workspace
 
 QUERY_TILE = 64  # queries per CTA of the prompt attention kernel
+GRAPH_MIN_TOKENS = 256  # prompt steps at least this large are captured when they recur
+MAX_STEP_GRAPHS = 4
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
            "f32": torch.float32, torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
@@ -74,6 +77,9 @@ class Engine:
         self.model.bind_cache(self.cache)
         self.workspace = Workspace(self.device)
         self._staging: Optional[torch.Tensor] = None  # pinned host ints of one step
+        self._step_graphs: Dict[object, dict] = {}  # captured prompt steps by shape
+        parts = [p for blk in self.model.blocks for p in blk.parts()]
+        self._graph_safe = all(getattr(p, "device_only", True) for p in parts)
         self.h2d_bytes = 0  # bytes of step tables copied so far (for measurements)
 
     # -- construction -------------------------------------------------------
@@ -110,76 +116,77 @@ class Engine:
         self.cache.release(slot)
 
     # -- the step -----------------------------------------------------------
-    def _stage(self, ints: List[int]) -> torch.Tensor:
-        """One pinned buffer -> one async copy -> int32 device tensor."""
-        n = len(ints)
+    def _stage(self, parts: List[np.ndarray], workspace: Optional[Workspace] = None) -> torch.Tensor:
+        """Int arrays -> one pinned buffer -> one async copy -> int32 device tensor."""
+        workspace = workspace if workspace is not None else self.workspace
+        n = int(sum(p.size for p in parts))
         if self._staging is None or self._staging.numel() < n:
-            self._staging = torch.empty(max(n, 4096), dtype=torch.int32, pin_memory=True)
+            self._staging = torch.empty(max(2 * n, 4096), dtype=torch.int32, pin_memory=True)
+            self._staging_np = self._staging.numpy()
             self._staging_free = torch.cuda.Event()
             self._staging_free.record()
         # the previous copy out of the pinned buffer must be over before it is rewritten
         self._staging_free.synchronize()
-        self._staging[:n] = torch.tensor(ints, dtype=torch.int32)
-        dev = self.workspace.get("step_ints", (n,), torch.int32)
+        o = 0
+        for p in parts:
+            self._staging_np[o:o + p.size] = p
+            o += p.size
+        dev = workspace.get("step_ints", (n,), torch.int32)
         dev.copy_(self._staging[:n], non_blocking=True)
         self.h2d_bytes += 4 * n
         self._staging_free.record()
         return dev
 
-    def prepare(self, batch: Sequence[SequenceStep]):
-        """Validate, reserve pages, upload the tables; returns (ctx, want_rows)."""
+    def prepare(self, batch: Sequence[SequenceStep], workspace: Optional[Workspace] = None):
+        """Validate, reserve pages, upload the tables; returns (ctx, want_rows,
+        slots, new lengths).  ``workspace``: where the step's buffers live (the
+        engine's own unless a captured graph has one of its own)."""
+        workspace = workspace if workspace is not None else self.workspace
         if not batch:
             raise StepError("a step needs at least one sequence")
         vocab = self.spec.vocab_size
         slots = [s.slot for s in batch]
-        counts, starts = [], []
+        counts, starts, token_arrays = [], [], []
         for s in batch:
-            if len(s.tokens) == 0:
+            tok = np.asarray(s.tokens, dtype=np.int64).reshape(-1)
+            if tok.size == 0:
                 raise StepError(f"slot {s.slot}: a sequence in a step brings at least one token")
-            for t in s.tokens:
-                if not 0 <= int(t) < vocab:
-                    raise StepError(f"slot {s.slot}: token {t} is outside the vocabulary of {vocab}")
+            if int(tok.min()) < 0 or int(tok.max()) >= vocab:
+                bad = int(tok[(tok < 0) | (tok >= vocab)][0])
+                raise StepError(f"slot {s.slot}: token {bad} is outside the vocabulary of {vocab}")
             for w in s.want:
-                if not 0 <= int(w) < len(s.tokens):
+                if not 0 <= int(w) < tok.size:
                     raise StepError(f"slot {s.slot}: wanted place {w} is outside its "
-                                    f"{len(s.tokens)} tokens")
-            counts.append(len(s.tokens))
+                                    f"{tok.size} tokens")
+            token_arrays.append(tok.astype(np.int32))
+            counts.append(int(tok.size))
             starts.append(self.cache.length(s.slot))
         new_lengths = [a + b for a, b in zip(starts, counts)]
         self.cache.reserve(slots, new_lengths)
 
-        tokens, pos, seq, want_rows = [], [], [], []
-        base = 0
-        for i, s in enumerate(batch):
-            tokens.extend(int(t) for t in s.tokens)
-            pos.extend(range(starts[i], new_lengths[i]))
-            seq.extend([i] * counts[i])
-            want_rows.extend(base + int(w) for w in s.want)
-            base += counts[i]
-        n, b = base, len(batch)
-        tables, cols = [], []
+        i32 = lambda x: np.asarray(x, dtype=np.int32).reshape(-1)
+        n, b = int(sum(counts)), len(batch)
+        pos = np.concatenate([np.arange(a, e, dtype=np.int32) for a, e in zip(starts, new_lengths)])
+        seq = np.repeat(np.arange(b, dtype=np.int32), counts)
+        first_rows = np.concatenate([[0], np.cumsum(counts)[:-1]]).astype(np.int32)
+        want_rows = i32([first_rows[i] + int(w) for i, s in enumerate(batch) for w in s.want])
+        parts = [np.concatenate(token_arrays), pos, seq, i32(slots), want_rows]
+        cols = []
         for g in range(len(self.cache.groups)):
             width = max(1, max(-(-L // PAGE_SIZE) for L in new_lengths))
-            rows = []
-            for s in slots:
-                t = self.cache.page_table(g, s)
-                rows.extend(t[:width] + [-1] * (width - len(t[:width])))
-            tables.append(rows)
+            table = np.full((b, width), -1, dtype=np.int32)
+            for r, slot in enumerate(slots):
+                t = self.cache.page_table(g, slot)[:width]
+                table[r, :len(t)] = t
+            parts.append(table.reshape(-1))
             cols.append(width)
-        flat = tokens + pos + seq + slots + want_rows
-        for rows in tables:
-            flat += rows
         decode = all(c == 1 for c in counts)
-        first_rows, tiles = [], []
+        n_tiles = 0
         if not decode:
-            row = 0
-            for i, c in enumerate(counts):
-                first_rows.append(row)
-                row += c
-                for q0 in range(0, c, QUERY_TILE):
-                    tiles += [i, q0]
-            flat += first_rows + starts + counts + tiles
-        dev = self._stage(flat)
+            tiles = [(i, q0) for i, c in enumerate(counts) for q0 in range(0, c, QUERY_TILE)]
+            n_tiles = len(tiles)
+            parts += [first_rows, i32(starts), i32(counts), i32(tiles)]
+        dev = self._stage(parts, workspace)
         o = 0
 
         def take(k):
@@ -189,27 +196,71 @@ class Engine:
             return out
 
         d_tokens, d_pos, d_seq, d_slots = take(n), take(n), take(n), take(b)
-        d_want = take(len(want_rows))
+        d_want = take(want_rows.size)
         d_tables = [take(b * c).view(b, c) for c in cols]
         ctx = StepContext(
             n_tokens=n, n_seqs=b, tokens=d_tokens, token_pos=d_pos, token_seq=d_seq,
-            seq_slots=d_slots, page_tables=d_tables, workspace=self.workspace,
+            seq_slots=d_slots, page_tables=d_tables, workspace=workspace,
             decode=decode, max_context=max(new_lengths),
             host_slots=slots, host_counts=counts, host_starts=starts)
         if not decode:
             ctx.seq_first_row, ctx.seq_start, ctx.seq_count = take(b), take(b), take(b)
-            ctx.q_tiles = take(len(tiles)).view(-1, 2)
+            ctx.q_tiles = take(2 * n_tiles).view(-1, 2)
         return ctx, d_want, slots, new_lengths
 
     def step(self, batch: Sequence[SequenceStep]) -> torch.Tensor:
         """Run one step; returns float32 logits [wanted places, vocab] in the
-        order of the batch and of each sequence's ``want``."""
+        order of the batch and of each sequence's ``want``.
+
+        Large prompt steps whose shape (token counts, start positions, number of
+        wanted places) comes a second time are captured as a CUDA graph with buffers
+        of their own and replayed from then on: such a step is a few hundred small
+        launches, and the host is the slower side of them."""
+        key = None
+        if sum(len(s.tokens) for s in batch) >= GRAPH_MIN_TOKENS and \
+                any(len(s.tokens) > 1 for s in batch) and self._graph_safe:
+            key = (tuple(len(s.tokens) for s in batch),
+                   tuple(self.cache.lengths[s.slot] for s in batch),
+                   tuple(len(s.want) for s in batch))
+        entry = self._step_graphs.get(key) if key is not None else None
+        if entry is not None and entry["graph"] is not None:
+            ctx, d_want, slots, new_lengths = self.prepare(batch, entry["workspace"])
+            entry["graph"].replay()
+            self.cache.commit(slots, new_lengths)
+            return entry["logits"].clone()
+        if key is not None and entry is None:
+            if len(self._step_graphs) >= MAX_STEP_GRAPHS:
+                self._step_graphs.pop(next(iter(self._step_graphs)))
+            self._step_graphs[key] = {"graph": None, "workspace": None, "logits": None}
+        elif key is not None:
+            return self._capture_step(batch, entry)
         ctx, d_want, slots, new_lengths = self.prepare(batch)
         logits = torch.empty((d_want.numel(), self.spec.vocab_size), dtype=torch.float32,
                              device=self.device)
         self.model.forward(ctx, d_want, logits)
         self.cache.commit(slots, new_lengths)
         return logits
+
+    def _capture_step(self, batch: Sequence[SequenceStep], entry) -> torch.Tensor:
+        """Second time a prompt shape is seen: run it into buffers of its own under
+        capture, then launch the graph."""
+        workspace = Workspace(self.device)
+        ctx, d_want, slots, new_lengths = self.prepare(batch, workspace)
+        logits = torch.empty((d_want.numel(), self.spec.vocab_size), dtype=torch.float32,
+                             device=self.device)
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):  # allocates the workspace; results are overwritten below
+            self.model.forward(ctx, d_want, logits)
+        torch.cuda.current_stream().wait_stream(side)
+        workspace.frozen = True
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.model.forward(ctx, d_want, logits)
+        graph.replay()
+        self.cache.commit(slots, new_lengths)
+        entry.update(graph=graph, workspace=workspace, logits=logits)
+        return logits.clone()
 
     def check_status(self) -> None:
         """Raise if a kernel flagged bad input since the last check (syncs)."""

@@ -128,6 +128,16 @@ class Attention(Part):
                           v_cache=cache.v if self.own_kv else None, heads=nq,
                           kv_heads=self.stored_kv, head_dim=d, page_size=cache.page_size)
             q_buf, q_stride = q, nq * d
+        elif self.dtype == torch.bfloat16 and ops.gemm_tc_qkv_takes(d) \
+                and ops.gemm_tc_takes(n, self.w_qkv.shape[0], self.hidden):
+            # tensor-core product with bias, RoPE and the cache store in its epilogue
+            q = ws.get("q", (n, nq * d), self.dtype)
+            ops.gemm_tc(x, self.w_qkv, self.b_qkv, q, ops.GEMM_QKV, token_pos=ctx.token_pos,
+                        token_seq=ctx.token_seq, page_table=table if self.own_kv else None, cos=cos,
+                        sin=sin, k_cache=cache.k if self.own_kv else None,
+                        v_cache=cache.v if self.own_kv else None, heads=nq, kv_heads=self.stored_kv,
+                        head_dim=d, page_size=cache.page_size)
+            q_buf, q_stride = q, nq * d
         else:
             qkv = ws.get("qkv", (n, (nq + 2 * self.stored_kv) * d), self.dtype)
             linear(x, self.w_qkv, self.b_qkv, qkv, STORE)

@@ -83,6 +83,9 @@ class GatedMLP(Part):
             ops.gemv_bf16(self.w_gu, self.b_gu, act, ops.EPI_GATED, x=x, hidden=hidden,
                           norm_weight=norm.weight if norm is not None else None,
                           eps=norm.eps if norm is not None else 0.0, m=n)
+        elif self.dtype == torch.bfloat16 and ops.gemm_tc_takes(n, 2 * self.inter, self.hidden):
+            # tensor-core product with the activation in its epilogue
+            ops.gemm_tc(x, self.w_gu, self.b_gu, act, ops.GEMM_GATED)
         else:
             gate_up = ws.get("gate_up", (n, 2 * self.inter), torch.float32)
             linear(x, self.w_gu, self.b_gu, gate_up, STORE_F32)

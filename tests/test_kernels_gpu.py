@@ -593,3 +593,59 @@ def test_prompt_attention_on_tensor_cores(nq, nkv, d, window):
         full = P.causal_attention(case.q[s], case.k[s], case.v[s].bfloat16().float(), window)
         close(out[r:r + new[s]], full[L - new[s]:].reshape(new[s], -1), "bfloat16", f"prompt attention seq {s}")
         r += new[s]
+
+
+@pytest.mark.parametrize("m", [17, 128, 200])
+@pytest.mark.parametrize("inter,k", [(100, 72), (1536, 576), (64, 64)])
+def test_gemm_on_tcgen05_gated_epilogue(m, inter, k):
+    o = ops()
+    g = torch.Generator().manual_seed(m + inter)
+    w = (torch.randn(2 * inter, k, generator=g) / math.sqrt(k) * 3).bfloat16()
+    bias = torch.randn(2 * inter, generator=g)
+    x = torch.randn(m, k, generator=g).bfloat16()
+    y = P.linear(x, w, bias)
+    out = torch.full((m, inter), 9.0, dtype=torch.bfloat16, device=DEV)
+    o.gemm_tc(x.to(DEV), w.to(DEV), bias.to(DEV), out, o.GEMM_GATED)
+    close(out, P.swiglu(y[:, :inter], y[:, inter:]), "bfloat16", "tcgen05 gated")
+    o.check_status(DEV)
+
+
+@pytest.mark.parametrize("nq,nkv,d,rotate", [(9, 3, 64, True), (2, 2, 128, True), (3, 1, 64, False),
+                                             (4, 0, 128, True)])
+def test_gemm_on_tcgen05_qkv_epilogue_rotates_and_stores(nq, nkv, d, rotate):
+    o = ops()
+    g = torch.Generator().manual_seed(nq * d)
+    m, k, page = 150, 72, 64
+    n = (nq + 2 * nkv) * d
+    w = (torch.randn(n, k, generator=g) / math.sqrt(k)).bfloat16()
+    bias = torch.randn(n, generator=g)
+    x = torch.randn(m, k, generator=g).bfloat16()
+    # two sequences: positions 0..99 and 30..78, one padding row
+    pos = torch.tensor(list(range(100)) + list(range(30, 79)) + [-1], dtype=torch.int32)
+    seq = torch.tensor([0] * 100 + [1] * 49 + [0], dtype=torch.int32)
+    table = torch.tensor([[5, 2], [7, 1]], dtype=torch.int32)
+    kc = torch.zeros(8, max(nkv, 1), page, d, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    cos, sin = P.rope_tables(200, d, 10000.0)
+    q_out = torch.full((m, nq * d), 9.0, dtype=torch.bfloat16, device=DEV)
+    o.gemm_tc(x.to(DEV), w.to(DEV), bias.to(DEV), q_out, o.GEMM_QKV, token_pos=pos.to(DEV),
+              token_seq=seq.to(DEV), page_table=table.to(DEV) if nkv else None,
+              cos=cos.float().to(DEV) if rotate else None, sin=sin.float().to(DEV) if rotate else None,
+              k_cache=kc if nkv else None, v_cache=vc if nkv else None, heads=nq, kv_heads=nkv,
+              head_dim=d, page_size=page)
+    y = P.linear(x, w, bias).bfloat16().double()
+    assert float((q_out[m - 1].float() - 9.0).abs().max()) == 0  # padding row untouched
+    valid = pos >= 0
+    p_idx = pos[valid].long()
+    c, s = (cos[p_idx], sin[p_idx]) if rotate else (torch.ones(len(p_idx), d // 2).double(),
+                                                    torch.zeros(len(p_idx), d // 2).double())
+    heads = y[valid].view(-1, nq + 2 * nkv, d)
+    close(q_out[:m - 1].view(-1, nq, d), P.rope_rotate_half(heads[:, :nq], c, s), "bfloat16", "q")
+    if nkv:
+        rk = P.rope_rotate_half(heads[:, nq:nq + nkv], c, s)
+        for i in (0, 63, 64, 99, 100, 148):
+            pg = int(table[int(seq[i]), int(pos[i]) // page])
+            close(kc[pg, :, int(pos[i]) % page], rk[i], "bfloat16", "k")
+            close(vc[pg, :, int(pos[i]) % page], heads[i, nq + nkv:], "bfloat16", "v")
+        assert int((kc.float().abs().sum(-1) > 0).sum()) == 149 * nkv
+    o.check_status(DEV)

@@ -213,3 +213,29 @@ def test_trace_run_as_a_program(models, dtype, tmp_path):
         want = torch.stack([plain_logits(models, name, dtype, sequences[rid])[pos]
                             for rid, pos in rows])
         check_logits(got, want, dtype, f"program {dtype} step {step}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_recurring_prompt_shapes_are_replayed_from_a_graph(models, dtype, tmp_path):
+    """A large prompt step whose shape comes again is captured and then replayed:
+    other tokens, other slots and pages each time, same rules."""
+    name = "A"
+    rng = random.Random(9)
+    vocab = CONFIGS[name]["vocab_size"]
+    sequences, trace = {}, TraceBuilder()
+    hold = random_tokens(rng, 70, vocab)  # keeps a slot and two pages busy so pages differ per run
+    sequences["hold"] = hold
+    trace.step([("hold", hold, [69])])
+    for i in range(4):
+        a, b = random_tokens(rng, 300, vocab), random_tokens(rng, 41, vocab)
+        sequences[f"a{i}"], sequences[f"b{i}"] = a, b
+        trace.step([(f"a{i}", a[:290], [0, 150, 289]), (f"b{i}", b[:40], [39])])
+        trace.step([(f"a{i}", a[290:291], [0]), (f"b{i}", b[40:41], [0])], end=[f"b{i}"])
+        trace.step([(f"a{i}", a[291:300], range(9))], end=[f"a{i}"])
+    trace.step([("hold", [1], [])], end=["hold"])
+    sequences["hold"] = hold + [1]
+    engine = engine_for(models, name, dtype)
+    before = len(engine._step_graphs)
+    run_and_check(models, name, dtype, trace, sequences, tmp_path, "graph replay")
+    assert len(engine._step_graphs) > before
+    assert any(e["graph"] is not None for e in engine._step_graphs.values())
