@@ -87,6 +87,26 @@ class EngineBackend:
         self.d2h_bytes += out.numel() * 4
         return out.tolist()
 
+    def new_rng(self, seed: int) -> torch.Tensor:
+        """A SplitMix64 state on the device (int64 [1]) for one request."""
+        return device_sampling.seed_states([seed], self.engine.device)
+
+    def sample_temperature(self, logits: torch.Tensor, rows: Sequence[int],
+                           temperatures: Sequence[float], states: Sequence[torch.Tensor]) -> List[int]:
+        """One seeded draw per named row of ``logits`` on the device; each row's
+        generator state advances in place."""
+        index = torch.tensor(list(rows), dtype=torch.long, device=logits.device)
+        picked_rows = logits if len(rows) == logits.shape[0] and list(rows) == list(range(len(rows))) \
+            else logits[index].contiguous()
+        temps = torch.tensor([float(t) for t in temperatures], dtype=torch.float32, device=logits.device)
+        state = torch.cat(list(states))
+        out = torch.empty(len(rows), dtype=torch.int32, device=logits.device)
+        device_sampling.temperature(picked_rows, temps, state, out)
+        for s, new in zip(states, state.split(1)):
+            s.copy_(new)
+        self.d2h_bytes += out.numel() * 4
+        return out.tolist()
+
     def host_rows(self, logits: torch.Tensor, rows: Sequence[int]) -> np.ndarray:
         if len(rows) == logits.shape[0]:
             return logits.cpu().numpy()
@@ -166,7 +186,7 @@ class LLM:
     def __init__(self, model_dir: str, dtype: str = "bfloat16", device_ordinal: int = 0,
                  device: Optional[str] = None, max_tokens: Optional[int] = None,
                  max_batch: int = 64, tokenizer_file: Optional[str] = None,
-                 pipeline_decode: bool = True):
+                 pipeline_decode: bool = True, device_sampling: bool = False):
         device = device if device is not None else f"cuda:{int(device_ordinal)}"
         self.max_batch = max_batch
         if max_tokens is None:
@@ -177,7 +197,7 @@ class LLM:
         self.tokenizer = load_tokenizer(tokenizer_file) if tokenizer_file else None
         self.backend = EngineBackend(self.engine, max_batch, pipeline_decode)
         self._generator = Generator(self.backend, self.spec.vocab_size,
-                                    self.spec.max_positions, max_batch, max_tokens)
+                                    self.spec.max_positions, max_batch, max_tokens, device_sampling)
 
     # -- text ---------------------------------------------------------------
     def encode(self, text: str) -> List[int]:

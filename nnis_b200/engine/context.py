@@ -7,6 +7,7 @@ n in its sequence (-1 marks a padding row, which no kernel stores or reads);
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence
 
@@ -15,6 +16,9 @@ import torch
 from .workspace import Workspace
 
 _SM_COUNT = {}
+# tuning of the decode attention split: CTAs per SM to aim for, fewest keys per slice
+_FILL = int(os.environ.get("NNIS_DECODE_FILL", "8"))
+_SLICE_KEYS = int(os.environ.get("NNIS_DECODE_SLICE_KEYS", "256"))
 
 
 def sm_count(device: torch.device) -> int:
@@ -65,6 +69,6 @@ class StepContext:
     def decode_splits(self, ctas: int) -> int:
         """The same for the decode kernel, whose CTAs (4 warps) each own a kv head
         of a sequence: fill the SMs a few times over, at least 256 keys a slice."""
-        by_ctas = max(1, sm_count(self.tokens.device) * 4 // max(1, ctas))
-        by_keys = max(1, -(-self.max_context // 256))
+        by_ctas = max(1, sm_count(self.tokens.device) * _FILL // max(1, ctas))
+        by_keys = max(1, -(-self.max_context // _SLICE_KEYS))
         return int(min(by_ctas, by_keys, 64))

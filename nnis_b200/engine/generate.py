@@ -88,7 +88,7 @@ def plan_batches(requests: Sequence[GenerationRequest], runnable: Sequence[bool]
 
 class Generator:
     def __init__(self, backend, vocab_size: int, max_positions: int, max_batch: int,
-                 max_tokens: int):
+                 max_tokens: int, device_sampling: bool = False):
         if max_batch <= 0:
             raise ValueError("max_batch must be positive")
         self.backend = backend
@@ -96,6 +96,11 @@ class Generator:
         self.max_positions = max_positions
         self.max_batch = max_batch
         self.max_pages = -(-max_tokens // PAGE_SIZE)
+        self._device_rng = {}
+        # True: requests that sample with a temperature only (no top-k, no top-p) draw
+        # on the device, from SplitMix64 states kept there (same generator and seed as
+        # the host sampler, candidates walked in token-id order instead of logit order)
+        self.device_sampling = device_sampling and hasattr(backend, "sample_temperature")
 
     # -- checks made before any work -------------------------------------------
     def _refusal(self, r: GenerationRequest) -> Optional[str]:
@@ -127,6 +132,14 @@ class Generator:
             tokens = list(self.backend.greedy(logits))
         else:
             tokens = [0] * len(rows)
+        on_device = [j for j in sampled if rows[j] in self._device_rng]
+        if on_device:
+            drawn = self.backend.sample_temperature(
+                logits, on_device, [requests[rows[j]].sampling.temperature for j in on_device],
+                [self._device_rng[rows[j]] for j in on_device])
+            for j, t in zip(on_device, drawn):
+                tokens[j] = t
+            sampled = [j for j in sampled if rows[j] not in self._device_rng]
         if sampled:
             host = self.backend.host_rows(logits, sampled)
             for k, j in enumerate(sampled):
@@ -144,8 +157,14 @@ class Generator:
             if why is not None:
                 results[i].error, results[i].finish_reason = why, "error"
             runnable.append(why is None)
+        self._device_rng = {}
+        if self.device_sampling:
+            self._device_rng = {i: self.backend.new_rng(r.sampling.seed) for i, r in enumerate(requests)
+                                if runnable[i] and r.sampling is not None
+                                and r.sampling.top_k is None and r.sampling.top_p is None}
         samplers = {i: HostLogitSampler(r.sampling, self.vocab_size)
-                    for i, r in enumerate(requests) if runnable[i] and r.sampling is not None}
+                    for i, r in enumerate(requests)
+                    if runnable[i] and r.sampling is not None and i not in self._device_rng}
         for batch in plan_batches(requests, runnable, self.max_batch, self.max_pages):
             self._run_batch(batch, requests, results, samplers, on_token)
         return results

@@ -113,3 +113,30 @@ def test_both_decode_paths_agree_with_the_plain_loop(model_dirs, pipeline):
     # a second call reuses decoders, graphs and slots
     again = llm.generate(prompts[:3], max_new_tokens=5, stop_token_ids=())
     assert [r.token_ids for r in again] == [t[:5] for t in plain[:3]]
+
+
+def test_temperature_sampling_on_the_device_follows_the_seeded_draws(model_dirs):
+    """With device_sampling the draws come from the sampling kernel: same seeds,
+    same tokens on every run, and the tokens the plain inverse CDF (token-id order,
+    float64) picks from the engine's own logits."""
+    import numpy as np
+    from nnis_b200 import LLM, SamplingConfig
+    d = model_dirs["B"]
+    llm = LLM(d, dtype="float32", max_tokens=64 * 16, max_batch=4, device_sampling=True)
+    policies = [SamplingConfig(seed=5, temperature=0.9), SamplingConfig(seed=6, temperature=1.4)]
+    prompts = [[1, 2, 3], [9, 8]]
+    a = llm.generate(prompts, max_new_tokens=10, sampling=policies, stop_token_ids=())
+    b = llm.generate(prompts, max_new_tokens=10, sampling=policies, stop_token_ids=())
+    assert [r.token_ids for r in a] == [r.token_ids for r in b] and all(r.ok for r in a)
+    # replay request 0 by hand: its logits through a session, its draws through the plain generator
+    session = llm.new_session()
+    rng = P.PlainSplitMix64(5)
+    logits = session.prefill(prompts[0])
+    for t in a[0].token_ids:
+        w = np.exp((logits.astype(np.float64) - logits.max()) / float(np.float32(0.9)))
+        cdf = np.cumsum(w)
+        u = rng.next_unit() * cdf[-1]
+        want = int(np.searchsorted(cdf, u, side="right"))
+        assert t == want or abs(cdf[t] - u) < 1e-9 * cdf[-1]
+        logits = session.decode_one(t)
+    session.close()
