@@ -20,10 +20,7 @@
 // flag that the other roles see; all warps still meet at the end, and tensor
 // memory is always freed.
 // NNIS computes the same product on CUDA cores: crates/nnis-kernels/src/gemm.rs:16-64.
-#include <cuda.h>
-
-#include "async_copy.cuh"
-#include "common.cuh"
+#include "tcgen05_helpers.cuh"
 
 namespace nnis {
 
@@ -31,83 +28,6 @@ constexpr int kBM = 128;
 constexpr int kBK = 64;          // 64 bfloat16 = one 128-byte swizzle row
 constexpr int kUmmaK = 16;
 constexpr int kGemmThreads = 192;
-
-__device__ __forceinline__ void tma_load_2d(void* dst_smem, const CUtensorMap* map, int c0, int c1,
-                                            uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(smem_addr(dst_smem)), "l"(map), "r"(c0), "r"(c1), "r"(smem_addr(bar))
-        : "memory");
-}
-
-__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t columns) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                     smem_addr(dst_smem)),
-                 "r"(columns)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t columns) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(columns)
-                 : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() {
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-// The mbarrier gets one arrival when every tcgen05.mma issued so far by this
-// thread has completed.
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                     smem_addr(bar))
-                 : "memory");
-}
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                       uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&v)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
-          "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
-          "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
-          "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
-          "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Shared memory matrix descriptor of a K-major tile whose rows are 128 bytes
-// (64 bfloat16) and 128-byte swizzled: 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t smem_desc_k128(uint32_t smem_byte_addr) {
-    uint64_t desc = 0;
-    desc |= (uint64_t)((smem_byte_addr >> 4) & 0x3FFF);   // start address, 16-byte units
-    desc |= (uint64_t)1 << 16;                            // leading byte offset (unused with swizzle)
-    desc |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset between 8-row groups
-    desc |= (uint64_t)1 << 46;                            // descriptor version of sm_100
-    desc |= (uint64_t)2 << 61;                            // SWIZZLE_128B
-    return desc;
-}
-
-// kind::f16 instruction descriptor: bfloat16 x bfloat16 -> float32, both K-major.
-__host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
-    return (1u << 4)                    // accumulator float32
-         | (1u << 7)                    // A bfloat16
-         | (1u << 10)                   // B bfloat16
-         | ((uint32_t)(n >> 3) << 17)   // N / 8
-         | ((uint32_t)(m >> 4) << 24);  // M / 16
-}
 
 enum { GEMM_STORE = 0, GEMM_STORE_F32 = 1, GEMM_ADD_F32 = 2, GEMM_GATED = 3, GEMM_QKV = 4 };
 
@@ -194,6 +114,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = instr_desc(kBM, BN);
+            const uint64_t desc_a0 = smem_desc_k128(smem_addr(tile_a));
+            const uint64_t desc_b0 = smem_desc_k128(smem_addr(tile_b));
             bool ok = true;
             for (int kb = 0; kb < k_blocks; ++kb) {
                 int s = kb % STAGES;
@@ -202,16 +124,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     break;
                 }
                 tc_fence_after();
-                uint32_t a_addr = smem_addr(tile_a + (size_t)s * kBytesA);
-                uint32_t b_addr = smem_addr(tile_b + (size_t)s * NB * kBytesB);
+                const uint64_t da = desc_advance(desc_a0, (uint32_t)s * kBytesA);
+                const uint64_t db = desc_advance(desc_b0, (uint32_t)s * NB * kBytesB);
 #pragma unroll
                 for (int k = 0; k < kBK / kUmmaK; ++k) {
                     // 16 columns of K further along the swizzled row: 32 bytes
-                    uint64_t da = smem_desc_k128(a_addr + k * kUmmaK * 2);
-                    tc_mma(tmem_acc, da, smem_desc_k128(b_addr + k * kUmmaK * 2), idesc, (kb | k) != 0);
+                    tc_mma(tmem_acc, desc_advance(da, k * kUmmaK * 2), desc_advance(db, k * kUmmaK * 2),
+                           idesc, (kb | k) != 0);
                     if (NB == 2)
-                        tc_mma(tmem_acc + BN, da, smem_desc_k128(b_addr + kBytesB + k * kUmmaK * 2),
-                               idesc, (kb | k) != 0);
+                        tc_mma(tmem_acc + BN, desc_advance(da, k * kUmmaK * 2),
+                               desc_advance(db, kBytesB + k * kUmmaK * 2), idesc, (kb | k) != 0);
                 }
                 tc_commit(&empty_bar[s]);  // the stage is free once these MMAs have read it
             }
@@ -382,38 +304,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         tmem_dealloc(tmem_acc, kTmemCols);
     }
     if (threadIdx.x == 0 && abort_flag && g.status) atomicExch(g.status, 3);
-}
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled() {
-    static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) ==
-                cudaSuccess && qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
-    return fn;
-}
-
-// [rows, K] row-major bfloat16, boxes of box_rows x 64 columns, 128-byte swizzle
-static bool make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
-    EncodeTiledFn fn = encode_tiled();
-    if (!fn) return false;
-    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-    cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
-    cuuint32_t elem[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box,
-              elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 template <int BN, int STAGES, int MODE>

@@ -425,6 +425,102 @@ def attention_prefill_mma(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor,
         "attention_prefill_mma")
 
 
+WIDE_QUERY_TILE = 128  # queries per CTA of attention_prefill_tc
+TC_ATTENTION = 0 if __import__("os").environ.get("NNIS_TC_ATTENTION", "1") == "0" else 1
+
+
+def attention_prefill_tc_takes(head_dim: int, page_size: int, q_stride: int) -> bool:
+    """Whether the tcgen05 prompt attention kernel runs these sizes."""
+    return bool(TC_ATTENTION) and head_dim == 64 and page_size == 64 and q_stride % 8 == 0
+
+
+def prefill_tc_plan(counts, starts, window: int, heads: int, sms: int):
+    """Work list of attention_prefill_tc for a step whose sequences bring
+    ``counts`` tokens after ``starts`` cached ones.
+
+    A tile is 128 queries of one sequence; its keys are the pages from its first
+    query's window start to its last query.  Tiles are cut into chunks of pages
+    when there would be CTAs (units x heads) for less than half of the SMs: chunks
+    of 32 pages if that gives enough, else of 16 (a chunk costs a CTA's start and
+    end and a pass of the merge kernel, about as much as eight pages, so cutting
+    pays only when most SMs would idle: one long prompt, few heads).  Returns
+    ``units`` int32 [n, 4] (sequence, first query, chunk | chunks << 16, first
+    scratch slot), longest first, ``merges`` int32 [m, 4] (sequence, first query,
+    chunks, first slot) for the tiles that were cut, and the number of scratch
+    slots."""
+    import numpy as np
+    tiles = []
+    for i, (c, st) in enumerate(zip(counts, starts)):
+        for q0 in range(0, int(c), WIDE_QUERY_TILE):
+            rows = min(WIDE_QUERY_TILE, int(c) - q0)
+            pos0 = int(st) + q0
+            lo = max(0, pos0 - window + 1) if window > 0 else 0
+            tiles.append((i, q0, (pos0 + rows - 1) // 64 - lo // 64 + 1))
+    chunk_pages = 16
+    for cand in (1 << 30, 32):
+        if 2 * sum(-(-p // cand) for _, _, p in tiles) * heads >= sms:
+            chunk_pages = cand
+            break
+    units, merges, slot = [], [], 0
+    for i, q0, pages in tiles:
+        n = -(-pages // chunk_pages)
+        while n > 1 and (n - 1) * (-(-pages // n)) >= pages:  # no chunk may be empty
+            n -= 1
+        per = -(-pages // n)
+        for c in range(n):
+            units.append((min(per, pages - c * per), i, q0, c | (n << 16), slot if n > 1 else 0))
+        if n > 1:
+            merges.append((i, q0, n, slot))
+            slot += n
+    units.sort(key=lambda u: -u[0])
+    return (np.asarray([u[1:] for u in units], dtype=np.int32).reshape(-1, 4),
+            np.asarray(merges, dtype=np.int32).reshape(-1, 4), slot)
+
+
+PREFILL_TC_PARTIAL = 66 * WIDE_QUERY_TILE  # float32 per (scratch slot, head)
+
+
+def attention_prefill_tc(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                         units: torch.Tensor, merges: Optional[torch.Tensor],
+                         partial: Optional[torch.Tensor], seq_first_row: torch.Tensor,
+                         seq_start: torch.Tensor, seq_count: torch.Tensor, page_table: torch.Tensor,
+                         out: torch.Tensor, heads: int, kv_heads: int, head_dim: int, window: int,
+                         scale: float) -> None:
+    """Prompt attention on tcgen05 (head size 64): packed query tokens, each over
+    its own sequence's keys in the paged cache.  ``units`` and ``merges`` come
+    from ``prefill_tc_plan``; ``partial`` is float32 scratch of
+    slots x heads x PREFILL_TC_PARTIAL values when tiles were cut."""
+    _cuda(k_cache, v_cache, units, seq_first_row, seq_start, seq_count, page_table, out)
+    _need(q.is_cuda and q.dtype == torch.bfloat16 == k_cache.dtype == out.dtype,
+          "attention_prefill_tc: bfloat16 tensors")
+    pages, nkv, page_size, d = k_cache.shape
+    _need(nkv == kv_heads and d == head_dim, "cache shape differs from the heads given")
+    _need(attention_prefill_tc_takes(head_dim, page_size, q_stride),
+          f"attention_prefill_tc: head_dim {head_dim} / page {page_size} / stride {q_stride} is not taken")
+    _need(heads % kv_heads == 0, "attention: heads is not a multiple of kv_heads")
+    _need(pages * nkv * page_size < 2 ** 31, "attention: the cache has too many rows")
+    _need(out.shape[1] == heads * head_dim and out.is_contiguous(), "attention: out [n, heads * d]")
+    _need(k_cache.is_contiguous() and v_cache.is_contiguous(), "attention: contiguous cache")
+    for t in (units, seq_first_row, seq_start, seq_count):
+        _need(t.dtype == torch.int32, "attention_prefill_tc: int32 tables")
+    _need(units.dim() == 2 and units.shape[1] == 4 and units.shape[0] > 0 and units.is_contiguous(),
+          "units: int32 [n_units, 4]")
+    n_merges = 0 if merges is None else merges.shape[0]
+    if n_merges:
+        _cuda(merges, partial)
+        _need(merges.dtype == torch.int32 and merges.dim() == 2 and merges.shape[1] == 4
+              and merges.is_contiguous(), "merges: int32 [n_merges, 4]")
+        _need(partial.dtype == torch.float32, "partial: float32 scratch")
+    _check(_lib().nnis_attention_prefill_tc(
+        _ptr(q), q_stride, out.shape[0], _ptr(k_cache), _ptr(v_cache),
+        ctypes.c_longlong(pages * nkv * page_size), _ptr(units), units.shape[0],
+        _ptr(merges) if n_merges else None, n_merges, _ptr(partial) if n_merges else None,
+        _ptr(seq_first_row), _ptr(seq_start), _ptr(seq_count), _ptr(page_table), page_table.shape[1],
+        _ptr(out), heads, kv_heads, head_dim, page_size, window, ctypes.c_float(scale),
+        _ptr(status_word(out.device)), _stream()),
+        "attention_prefill_tc")
+
+
 def mma_ticket_count(n: int, heads: int, kv_heads: int) -> int:
     return n * kv_heads * (-(-(heads // kv_heads) // 16))
 

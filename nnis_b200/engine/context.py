@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import os
 from dataclasses import dataclass, field
-from typing import List, Optional, Sequence
+from typing import Dict, List, Optional, Sequence
 
 import torch
 
@@ -53,6 +53,9 @@ class StepContext:
     seq_start: Optional[torch.Tensor] = None
     seq_count: Optional[torch.Tensor] = None
     q_tiles: Optional[torch.Tensor] = None
+    # what the parts asked for with ``step_tables``: device copies and the arrays
+    tables: Dict[str, torch.Tensor] = field(default_factory=dict)
+    host_tables: Dict[str, object] = field(default_factory=dict)
 
     def attention_splits(self, query_rows: int) -> int:
         """How many ways to cut each query's key range so the GPU is full when

@@ -186,6 +186,12 @@ class Engine:
             tiles = [(i, q0) for i, c in enumerate(counts) for q0 in range(0, c, QUERY_TILE)]
             n_tiles = len(tiles)
             parts += [first_rows, i32(starts), i32(counts), i32(tiles)]
+            # 16-byte alignment for the tables the parts asked for
+            parts.append(np.zeros(-int(sum(p.size for p in parts)) % 4, dtype=np.int32))
+            extra = self.model.step_tables(counts, starts)
+            for name, arr in extra.items():
+                flat = np.ascontiguousarray(arr, dtype=np.int32).reshape(-1)
+                parts += [flat, np.zeros(-flat.size % 4, dtype=np.int32)]
         dev = self._stage(parts, workspace)
         o = 0
 
@@ -206,6 +212,11 @@ class Engine:
         if not decode:
             ctx.seq_first_row, ctx.seq_start, ctx.seq_count = take(b), take(b), take(b)
             ctx.q_tiles = take(2 * n_tiles).view(-1, 2)
+            take(-o % 4)
+            for name, arr in extra.items():
+                ctx.tables[name] = take(arr.size).view(arr.shape)
+                ctx.host_tables[name] = arr
+                take(-arr.size % 4)
         return ctx, d_want, slots, new_lengths
 
     def step(self, batch: Sequence[SequenceStep]) -> torch.Tensor:

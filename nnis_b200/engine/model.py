@@ -75,6 +75,14 @@ class DecoderModel:
                 self.blocks[entry.layer].mixer.check_shared_cache(view)
             self._views.append(view)
 
+    def step_tables(self, counts, starts) -> Dict[str, object]:
+        """The work lists that the scheduled blocks want uploaded for a prompt step."""
+        tables: Dict[str, object] = {}
+        for layer in sorted({e.layer for e in self.spec.schedule}):
+            for name, arr in self.blocks[layer].step_tables(counts, starts).items():
+                tables.setdefault(name, arr)
+        return tables
+
     # -- run ------------------------------------------------------------------
     def forward_and_pick(self, ctx, want_rows: torch.Tensor, picks: torch.Tensor,
                          logits: Optional[torch.Tensor], tokens: torch.Tensor,

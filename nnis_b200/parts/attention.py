@@ -19,7 +19,7 @@ from typing import Dict, Mapping, Optional
 
 import torch
 
-from ..cache import KVRequest, KVView
+from ..cache import PAGE_SIZE, KVRequest, KVView
 from ..csrc import ops
 from ..weights.loader import WeightSpec
 from .base import MIXERS, POSITIONS, Part
@@ -87,6 +87,21 @@ class Attention(Part):
         if not isinstance(view, KVView) or tuple(view.k.shape[1:]) != \
                 (self.kv_heads, view.page_size, self.head_dim) or view.window != self.window:
             raise ValueError("the shared cache does not fit this attention's heads or window")
+
+    # -- work lists ---------------------------------------------------------
+    def _tc_plan_name(self) -> str:
+        return f"prefill_tc/window{self.window}/heads{self.heads}"
+
+    def step_tables(self, counts, starts):
+        """Units and merges of the tcgen05 prompt attention kernel (bfloat16, head
+        size 64), shared by all layers with this window and number of heads."""
+        if self.dtype != torch.bfloat16 or not ops.attention_prefill_tc_takes(
+                self.head_dim, PAGE_SIZE, self.heads * self.head_dim):
+            return {}
+        units, merges, _ = ops.prefill_tc_plan(counts, starts, self.window, self.heads,
+                                               ops.sm_count(self.device))
+        name = self._tc_plan_name()
+        return {name + "/units": units, name + "/merges": merges}
 
     # -- run --------------------------------------------------------------
     def _decode_kernels(self, ctx, n: int) -> bool:
@@ -164,6 +179,19 @@ class Attention(Part):
                 if splits > 1 else None
             ops.attention_decode(q_buf, q_stride, cache.k, cache.v, ctx.token_pos, ctx.token_seq,
                                  table, attn, nq, nkv, d, self.window, self.scale, splits, partial)
+        elif self.dtype == torch.bfloat16 and not ctx.decode \
+                and self._tc_plan_name() + "/units" in ctx.tables \
+                and ops.attention_prefill_tc_takes(d, cache.page_size, q_stride):
+            # tcgen05 kernel: a CTA per (128 queries of a sequence, query head, chunk of pages)
+            name = self._tc_plan_name()
+            merges = ctx.tables[name + "/merges"]
+            slots = int(ctx.host_tables[name + "/merges"][:, 2].sum())
+            partial = ws.get("attn_tc_partial", (slots * nq * ops.PREFILL_TC_PARTIAL,),
+                             torch.float32) if slots else None
+            ops.attention_prefill_tc(q_buf, q_stride, cache.k, cache.v, ctx.tables[name + "/units"],
+                                     merges if slots else None, partial, ctx.seq_first_row,
+                                     ctx.seq_start, ctx.seq_count, table, attn, nq, nkv, d,
+                                     self.window, self.scale)
         elif self.dtype == torch.bfloat16 and not ctx.decode and ctx.q_tiles is not None \
                 and ops.attention_decode_mma_takes(d, cache.page_size):
             ops.attention_prefill_mma(q_buf, q_stride, cache.k, cache.v, ctx.q_tiles,

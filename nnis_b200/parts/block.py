@@ -41,6 +41,15 @@ class PreNormBlock:
     def parameter_bytes(self) -> int:
         return sum(part.parameter_bytes() for part in self.parts())
 
+    def step_tables(self, counts, starts) -> Dict[str, object]:
+        tables: Dict[str, object] = {}
+        for part in self.parts():
+            wants = getattr(part, "step_tables", None)
+            if wants is not None:
+                for name, arr in wants(counts, starts).items():
+                    tables.setdefault(name, arr)
+        return tables
+
     def forward(self, hidden: torch.Tensor, ctx, cache) -> None:
         n, width = hidden.shape
         normed = ctx.workspace.get("normed", (n, width), self.dtype)

@@ -595,6 +595,52 @@ def test_prompt_attention_on_tensor_cores(nq, nkv, d, window):
         r += new[s]
 
 
+@pytest.mark.parametrize("nq,nkv", [(9, 3), (2, 2), (4, 1)])
+@pytest.mark.parametrize("window", [0, 70])
+@pytest.mark.parametrize("pad,sms", [(0, 1000), (24, 2), (0, 0)])
+def test_prompt_attention_on_tcgen05(nq, nkv, window, pad, sms):
+    """Head size 64 on the fifth-generation tensor cores: whole prompts and later
+    chunks of unequal length in one packed batch, 128 queries per tile, more pages
+    than the ring of stages holds, queries inside wider rows (``pad``); tiles cut
+    into chunks of pages and merged (planned as for very many SMs), or whole (as for few)."""
+    o = ops()
+    d = 64
+    lengths, new = [70, 1, 200, 64, 333, 129, 1500], [70, 1, 5, 64, 200, 65, 1500]
+    case = PagedCase(lengths, new, nq, nkv, d, "bfloat16", seed=3 * nq + window)
+    case.fill_cache()
+    for s, L in enumerate(lengths):  # the step's own keys and values are stored already
+        for t in range(L - new[s], L):
+            pg = int(case.table[s, t // 64])
+            case.k_cache[pg, :, t % 64] = case.k[s][t]
+            case.v_cache[pg, :, t % 64] = case.v[s][t]
+    pos, seq, q, _, _ = case.packed()
+    n = pos.numel()
+    stride = nq * d + pad
+    assert o.attention_prefill_tc_takes(d, 64, stride) and not o.attention_prefill_tc_takes(128, 64, stride)
+    qd = torch.full((n, stride), 3.0, dtype=torch.bfloat16, device=DEV)
+    qd[:, :nq * d] = q.reshape(n, -1).bfloat16().to(DEV)
+    kc, vc = case.k_cache.bfloat16().to(DEV), case.v_cache.bfloat16().to(DEV)
+    starts = [L - c for L, c in zip(lengths, new)]
+    first = [sum(new[:i]) for i in range(len(new))]
+    units, merges, slots = o.prefill_tc_plan(new, starts, window, nq, sms)
+    assert (slots > 0) == (sms == 1000 and window == 0)  # the long prompt is cut only when SMs would idle
+    covered = sorted((int(u[0]), int(u[1]), int(u[2]) & 0xffff) for u in units)
+    assert len(set(covered)) == len(covered)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    partial = torch.full((max(slots, 1) * nq * o.PREFILL_TC_PARTIAL,), float("nan"), device=DEV)
+    out = torch.full((n, nq * d), 5.0, dtype=torch.bfloat16, device=DEV)
+    for _ in range(2):
+        o.attention_prefill_tc(qd, stride, kc, vc, i32(units), i32(merges) if slots else None,
+                               partial if slots else None, i32(first), i32(starts), i32(new),
+                               case.table.to(DEV), out, nq, nkv, d, window, 1.0 / math.sqrt(d))
+    o.check_status(DEV)
+    r = 0
+    for s, L in enumerate(lengths):
+        full = P.causal_attention(case.q[s], case.k[s], case.v[s].bfloat16().float(), window)
+        close(out[r:r + new[s]], full[L - new[s]:].reshape(new[s], -1), "bfloat16", f"prompt attention seq {s}")
+        r += new[s]
+
+
 @pytest.mark.parametrize("m", [17, 128, 200])
 @pytest.mark.parametrize("inter,k", [(100, 72), (1536, 576), (64, 64)])
 def test_gemm_on_tcgen05_gated_epilogue(m, inter, k):
