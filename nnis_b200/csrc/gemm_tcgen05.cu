@@ -4,17 +4,19 @@
 // One CTA computes a 128 x BN tile (BN = 64 or 128).  Its six warps have fixed
 // roles:
 //   warp 0  one lane issues TMA tile loads (cp.async.bulk.tensor, 128-byte
-//           swizzle) of A and W, 64 columns of K at a time, into a ring of shared
-//           memory stages, each guarded by a "full" and an "empty" mbarrier;
+//           swizzle) of A, one or two slices of 64 columns of K per stage, into a
+//           ring of shared memory stages, each guarded by a "full" and an "empty"
+//           mbarrier; lane 0 of warp 2 does the same for W;
 //   warp 1  allocates tensor memory, and one lane issues tcgen05.mma
-//           (kind::f16, M = 128, N = BN, K = 16) four times per stage from shared
+//           (kind::f16, M = 128, N = BN, K = 16) four times per slice from shared
 //           memory descriptors, then tcgen05.commit to hand the stage back and,
 //           after the last one, to tell the epilogue that the accumulator is done;
 //   warps 2-5  read the accumulator with tcgen05.ld (each warp its own 32 lanes
-//           of tensor memory = 32 rows of the tile), add the bias and store, as
-//           bfloat16, as float32, or added into a float32 destination.
+//           of tensor memory = 32 rows of the tile), add the bias, and hand the
+//           tile through shared memory to a TMA store (bfloat16 or float32) or a
+//           TMA addition into a float32 destination.
 // Rows and columns beyond M, N and K are zero-filled by TMA on the way in and
-// masked on the way out, so any M and N and any K that is a multiple of 8 work.
+// clipped on the way out, so any M and N and any K that is a multiple of 8 work.
 //
 // Every wait is bounded: a wait that runs out sets a status word and an abort
 // flag that the other roles see; all warps still meet at the end, and tensor
@@ -36,6 +38,7 @@ struct GemmArgs {
     void* out;
     int M, N, K;
     int* status;
+    int out_by_tma;  // the output's rows start on 16-byte boundaries: tiles leave through shared memory
     // GEMM_QKV: rotate-half RoPE of q and k heads at each row's position, q to
     // `out` [M, nq * d], k and v into the paged cache (one head per column tile)
     const int* token_pos;
@@ -49,13 +52,18 @@ struct GemmArgs {
     int nq, nkv, d, page_size;
 };
 
+// Two CTAs share an SM when their stages leave room for it.
+constexpr int gemm_ctas_per_sm(int bn, int stages, int mode, int ksub) {
+    return stages * ksub * (kBM + (mode == GEMM_GATED ? 2 : 1) * bn) * kBK * 2 <= 110 * 1024 ? 2 : 1;
+}
+
 // MODE GEMM_GATED: W holds gate rows then up rows ([2 I, K]); the CTA multiplies
 // A by a gate tile and by the matching up tile into two accumulators and writes
 // bf16(silu(gate) * up) to out [M, I].  MODE GEMM_QKV: BN equals the head size.
-template <int BN, int STAGES, int MODE>
-__global__ void __launch_bounds__(kGemmThreads)
+template <int BN, int STAGES, int MODE, int KSUB>
+__global__ void __launch_bounds__(kGemmThreads, gemm_ctas_per_sm(BN, STAGES, MODE, KSUB))
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-               GemmArgs g) {
+               const __grid_constant__ CUtensorMap map_out, GemmArgs g) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // the swizzle pattern follows address bits: tiles start on 1024-byte boundaries
     unsigned char* base = reinterpret_cast<unsigned char*>(
@@ -63,23 +71,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     constexpr int NB = MODE == GEMM_GATED ? 2 : 1;  // B tiles (and accumulators) per stage
     constexpr uint32_t kBytesA = kBM * kBK * 2, kBytesB = BN * kBK * 2;
     constexpr uint32_t kTmemCols = NB * BN;
+    // a stage holds KSUB slices of 64 columns of K: [KSUB] A tiles, then [KSUB][NB] W tiles
+    constexpr uint32_t kStageA = KSUB * kBytesA, kStageB = KSUB * NB * kBytesB;
     unsigned char* tile_a = base;
-    unsigned char* tile_b = base + (size_t)STAGES * kBytesA;
-    __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar;
+    unsigned char* tile_b = base + (size_t)STAGES * kStageA;
+    __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar, staged_bar;
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile int abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.y * kBM, n0 = blockIdx.x * BN;
-    const int k_blocks = (g.K + kBK - 1) / kBK;
+    const int k_slices = (g.K + kBK - 1) / kBK;
+    const int k_blocks = (k_slices + KSUB - 1) / KSUB;
     const int inter = g.N >> 1;  // GEMM_GATED: columns of the output
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(&full_bar[s], 1);
+            mbar_init(&full_bar[s], 2);   // the two loaders
             mbar_init(&empty_bar[s], 1);
         }
         mbar_init(&acc_bar, 1);
+        mbar_init(&staged_bar, 4);
         abort_flag = 0;
         mbar_fence_init();
     }
@@ -94,23 +106,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     pdl_wait();
     pdl_launch_dependents();
 
-    if (warp == 0) {
-        if (lane == 0) {
-            for (int kb = 0; kb < k_blocks; ++kb) {
-                int s = kb % STAGES;
-                if (kb >= STAGES && !mbar_wait(&empty_bar[s], (uint32_t)(kb / STAGES - 1) & 1u)) {
-                    abort_flag = 1;
-                    break;
+    // Issuing a TMA load costs its thread about 130 cycles, so A and W each have a
+    // loader of their own: lane 0 of warp 0 and lane 0 of warp 2 (which joins the
+    // epilogue afterwards).  Each announces its own bytes; a stage is full when both
+    // have arrived and all bytes are there.
+    if (lane == 0 && (warp == 0 || warp == 2)) {
+        const bool loads_a = warp == 0;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+            int s = kb % STAGES;
+            if (kb >= STAGES && !mbar_wait(&empty_bar[s], (uint32_t)(kb / STAGES - 1) & 1u)) {
+                abort_flag = 1;
+                break;
+            }
+            if (abort_flag) break;
+            // (slices beyond K arrive as zeros and are not multiplied)
+            mbar_expect_tx(&full_bar[s], loads_a ? kStageA : kStageB);
+#pragma unroll
+            for (int h = 0; h < KSUB; ++h) {
+                const int k0 = (kb * KSUB + h) * kBK;
+                if (loads_a) {
+                    tma_load_2d(tile_a + (size_t)s * kStageA + (size_t)h * kBytesA, &map_a, k0, m0,
+                                &full_bar[s]);
+                } else {
+                    unsigned char* b_dst = tile_b + (size_t)s * kStageB + (size_t)h * NB * kBytesB;
+                    tma_load_2d(b_dst, &map_w, k0, n0, &full_bar[s]);
+                    if (NB == 2) tma_load_2d(b_dst + kBytesB, &map_w, k0, inter + n0, &full_bar[s]);
                 }
-                if (abort_flag) break;
-                mbar_expect_tx(&full_bar[s], kBytesA + NB * kBytesB);
-                tma_load_2d(tile_a + (size_t)s * kBytesA, &map_a, kb * kBK, m0, &full_bar[s]);
-                tma_load_2d(tile_b + (size_t)s * NB * kBytesB, &map_w, kb * kBK, n0, &full_bar[s]);
-                if (NB == 2)
-                    tma_load_2d(tile_b + (size_t)s * NB * kBytesB + kBytesB, &map_w, kb * kBK,
-                                inter + n0, &full_bar[s]);
             }
         }
+    }
+    __syncwarp();
+    if (warp == 0) {
+        // nothing more: the loader of A waits for the end with its warp
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = instr_desc(kBM, BN);
@@ -124,16 +151,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     break;
                 }
                 tc_fence_after();
-                const uint64_t da = desc_advance(desc_a0, (uint32_t)s * kBytesA);
-                const uint64_t db = desc_advance(desc_b0, (uint32_t)s * NB * kBytesB);
 #pragma unroll
-                for (int k = 0; k < kBK / kUmmaK; ++k) {
-                    // 16 columns of K further along the swizzled row: 32 bytes
-                    tc_mma(tmem_acc, desc_advance(da, k * kUmmaK * 2), desc_advance(db, k * kUmmaK * 2),
-                           idesc, (kb | k) != 0);
-                    if (NB == 2)
-                        tc_mma(tmem_acc + BN, desc_advance(da, k * kUmmaK * 2),
-                               desc_advance(db, kBytesB + k * kUmmaK * 2), idesc, (kb | k) != 0);
+                for (int h = 0; h < KSUB; ++h) {
+                    if (kb * KSUB + h >= k_slices) break;
+                    const uint64_t da = desc_advance(desc_a0, (uint32_t)s * kStageA + h * kBytesA);
+                    const uint64_t db = desc_advance(desc_b0, (uint32_t)s * kStageB + h * NB * kBytesB);
+#pragma unroll
+                    for (int k = 0; k < kBK / kUmmaK; ++k) {
+                        // 16 columns of K further along the swizzled row: 32 bytes
+                        tc_mma(tmem_acc, desc_advance(da, k * kUmmaK * 2), desc_advance(db, k * kUmmaK * 2),
+                               idesc, (kb | h | k) != 0);
+                        if (NB == 2)
+                            tc_mma(tmem_acc + BN, desc_advance(da, k * kUmmaK * 2),
+                                   desc_advance(db, kBytesB + k * kUmmaK * 2), idesc, (kb | h | k) != 0);
+                    }
                 }
                 tc_commit(&empty_bar[s]);  // the stage is free once these MMAs have read it
             }
@@ -222,9 +253,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
         } else {
             tc_fence_after();
-            // each thread owns one row and writes its 32 consecutive outputs of a chunk
+            // Each thread owns one row.  The tile leaves through shared memory (the
+            // ring is idle by now): rows of 128 bytes, 16-byte units swizzled as the
+            // output's tensor map says, then one TMA store per 128-byte-wide box, or
+            // a TMA addition into the float32 destination, which spares reading it.
+            // TMA clips rows and columns beyond M and N.  An output whose rows do not
+            // start on 16-byte boundaries is written element by element.
             const int out_cols = MODE == GEMM_GATED ? inter : g.N;
-            const bool vec_ok = (out_cols % 8 == 0);
+            constexpr bool kOut16 = MODE == GEMM_STORE || MODE == GEMM_GATED;
+            constexpr int kBoxCols = kOut16 ? 64 : 32;
+            unsigned char* stage_row = base + (size_t)row * 128;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t v[32];
@@ -241,51 +279,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             gv += g.bias[nb + i];
                             uv += g.bias[inter + nb + i];
                         }
-                        f[i] = (gv / (1.0f + expf(-gv))) * uv;
+                        f[i] = __fdividef(gv, 1.0f + __expf(-gv)) * uv;
                     }
                 } else {
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
                         f[i] = __uint_as_float(v[i]) + ((g.bias && nb + i < g.N) ? g.bias[nb + i] : 0.f);
                 }
-                if (m >= g.M || nb >= out_cols) continue;
-                const size_t off = (size_t)m * out_cols + nb;
-                if (vec_ok && nb + 32 <= out_cols) {
-                    if (MODE == GEMM_STORE || MODE == GEMM_GATED) {
-                        bf16* o = reinterpret_cast<bf16*>(g.out) + off;
+                if (g.out_by_tma) {
+                    unsigned char* box = stage_row + (size_t)(c0 / kBoxCols) * (kBM * 128);
+                    if (kOut16) {
+                        const int u0 = (c0 % 64) / 8;
 #pragma unroll
-                        for (int i = 0; i < 32; i += 8) {
-                            uint4 pk;
-                            __nv_bfloat162 p0 = __floats2bfloat162_rn(f[i], f[i + 1]);
-                            __nv_bfloat162 p1 = __floats2bfloat162_rn(f[i + 2], f[i + 3]);
-                            __nv_bfloat162 p2 = __floats2bfloat162_rn(f[i + 4], f[i + 5]);
-                            __nv_bfloat162 p3 = __floats2bfloat162_rn(f[i + 6], f[i + 7]);
-                            pk.x = *reinterpret_cast<uint32_t*>(&p0);
-                            pk.y = *reinterpret_cast<uint32_t*>(&p1);
-                            pk.z = *reinterpret_cast<uint32_t*>(&p2);
-                            pk.w = *reinterpret_cast<uint32_t*>(&p3);
-                            *reinterpret_cast<uint4*>(o + i) = pk;
+                        for (int j = 0; j < 4; ++j) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                __nv_bfloat162 pk = __floats2bfloat162_rn(f[j * 8 + 2 * e], f[j * 8 + 2 * e + 1]);
+                                w[e] = *reinterpret_cast<uint32_t*>(&pk);
+                            }
+                            *reinterpret_cast<uint4*>(box + (((u0 + j) ^ (row & 7)) << 4)) =
+                                make_uint4(w[0], w[1], w[2], w[3]);
                         }
                     } else {
-                        float* o = reinterpret_cast<float*>(g.out) + off;
-                        float4 cur[8];
-                        if (MODE == GEMM_ADD_F32) {
 #pragma unroll
-                            for (int i = 0; i < 8; ++i) cur[i] = *reinterpret_cast<const float4*>(o + i * 4);
-                        }
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            float4 c4 = MODE == GEMM_ADD_F32 ? cur[i] : make_float4(0.f, 0.f, 0.f, 0.f);
-                            *reinterpret_cast<float4*>(o + i * 4) =
-                                make_float4(c4.x + f[i * 4], c4.y + f[i * 4 + 1], c4.z + f[i * 4 + 2],
-                                            c4.w + f[i * 4 + 3]);
-                        }
+                        for (int j = 0; j < 8; ++j)
+                            *reinterpret_cast<float4*>(box + ((j ^ (row & 7)) << 4)) =
+                                make_float4(f[j * 4], f[j * 4 + 1], f[j * 4 + 2], f[j * 4 + 3]);
                     }
-                } else {
+                } else if (m < g.M) {
+                    const size_t off = (size_t)m * out_cols + nb;
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         if (nb + i < out_cols) {
-                            if (MODE == GEMM_STORE || MODE == GEMM_GATED)
+                            if (kOut16)
                                 reinterpret_cast<bf16*>(g.out)[off + i] = __float2bfloat16_rn(f[i]);
                             else if (MODE == GEMM_STORE_F32)
                                 reinterpret_cast<float*>(g.out)[off + i] = f[i];
@@ -293,6 +320,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                 reinterpret_cast<float*>(g.out)[off + i] += f[i];
                         }
                     }
+                }
+            }
+            if (g.out_by_tma) {
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&staged_bar);  // the four epilogue warps
+                if (threadIdx.x == 64 && !mbar_wait(&staged_bar, 0)) {
+                    abort_flag = 1;
+                } else if (threadIdx.x == 64) {
+#pragma unroll 1
+                    for (int c0 = 0; c0 < BN && n0 + c0 < out_cols; c0 += kBoxCols) {
+                        const unsigned char* src = base + (size_t)(c0 / kBoxCols) * (kBM * 128);
+                        if (MODE == GEMM_ADD_F32) tma_add_2d(&map_out, n0 + c0, m0, src);
+                        else tma_store_2d(&map_out, n0 + c0, m0, src);
+                    }
+                    tma_store_commit_wait();
                 }
             }
         }
@@ -306,12 +349,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (threadIdx.x == 0 && abort_flag && g.status) atomicExch(g.status, 3);
 }
 
-template <int BN, int STAGES, int MODE>
-static int launch_gemm_tc(const CUtensorMap& ma, const CUtensorMap& mw, const GemmArgs& g, bool pdl,
+template <int BN, int STAGES, int MODE, int KSUB>
+static int launch_gemm_tc(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mo,
+                          const GemmArgs& g, bool pdl,
                           cudaStream_t stream) {
     constexpr int NB = MODE == GEMM_GATED ? 2 : 1;
-    size_t smem = (size_t)STAGES * (kBM + NB * BN) * kBK * 2 + 1024;
-    auto kernel = gemm_tc_kernel<BN, STAGES, MODE>;
+    size_t smem = (size_t)STAGES * KSUB * (kBM + NB * BN) * kBK * 2 + 1024;
+    auto kernel = gemm_tc_kernel<BN, STAGES, MODE, KSUB>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     int n_cols = MODE == GEMM_GATED ? g.N / 2 : g.N;
@@ -325,7 +369,7 @@ static int launch_gemm_tc(const CUtensorMap& ma, const CUtensorMap& mw, const Ge
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    e = cudaLaunchKernelEx(&cfg, kernel, ma, mw, g);
+    e = cudaLaunchKernelEx(&cfg, kernel, ma, mw, mo, g);
     return e == cudaSuccess ? NNIS_OK : (int)e;
 }
 
@@ -353,31 +397,49 @@ NNIS_API int nnis_gemm_tc(const void* A, const void* W, const float* bias, void*
     g.table_cols = table_cols; g.cos_t = cos_t; g.sin_t = sin_t; g.k_cache = (bf16*)k_cache;
     g.v_cache = (bf16*)v_cache; g.nq = nq; g.nkv = nkv; g.d = d; g.page_size = page_size;
     int sms = sm_count > 0 ? sm_count : 148;
-    CUtensorMap ma, mw;
+    CUtensorMap ma, mw, mo;
+    const long m_tiles = (M + kBM - 1) / kBM;
+    // Two ring sizes per tile shape.  About 96 KB lets two CTAs share an SM, so that
+    // one's epilogue runs under the other's products; when there are no more CTAs
+    // than SMs a CTA takes about 192 KB instead, which keeps a microsecond of loads
+    // in flight (a stage comes back about 1,000 cycles after its load is issued).
+#define NNIS_GEMM_TC64(MODE, CTAS) \
+    return (CTAS) <= sms ? launch_gemm_tc<64, 4, MODE, 2>(ma, mw, mo, g, pdl != 0, stream) \
+                         : launch_gemm_tc<64, 2, MODE, 2>(ma, mw, mo, g, pdl != 0, stream)
+#define NNIS_GEMM_TC128(BN, MODE, CTAS) \
+    return (CTAS) <= sms ? launch_gemm_tc<BN, 3, MODE, 2>(ma, mw, mo, g, pdl != 0, stream) \
+                         : launch_gemm_tc<BN, 3, MODE, 1>(ma, mw, mo, g, pdl != 0, stream)
     if (mode == GEMM_QKV) {
         if ((d != 64 && d != 128) || N != (nq + 2 * nkv) * d || !token_pos) return NNIS_ERR_UNSUPPORTED;
         if (nkv > 0 && (!token_seq || !page_table || !k_cache || !v_cache || page_size <= 0))
             return NNIS_ERR_ARGUMENT;
         if (!make_map(&ma, A, M, K, kBM) || !make_map(&mw, W, N, K, d)) return NNIS_ERR_UNSUPPORTED;
-        if (d == 64) return launch_gemm_tc<64, 4, GEMM_QKV>(ma, mw, g, pdl != 0, stream);
-        return launch_gemm_tc<128, 3, GEMM_QKV>(ma, mw, g, pdl != 0, stream);
+        mo = ma;  // not used: this epilogue scatters rows into the cache
+        g.out_by_tma = 0;
+        if (d == 64) NNIS_GEMM_TC64(GEMM_QKV, m_tiles * (N / 64));
+        NNIS_GEMM_TC128(128, GEMM_QKV, m_tiles * (N / 128));
     }
     if (mode == GEMM_GATED) {
         if (N % 2) return NNIS_ERR_UNSUPPORTED;
         if (!make_map(&ma, A, M, K, kBM) || !make_map(&mw, W, N, K, 64)) return NNIS_ERR_UNSUPPORTED;
-        return launch_gemm_tc<64, 3, GEMM_GATED>(ma, mw, g, pdl != 0, stream);
+        g.out_by_tma = (N / 2) % 8 == 0 && make_map(&mo, C, M, N / 2, kBM);
+        if (!g.out_by_tma) mo = ma;
+        NNIS_GEMM_TC128(64, GEMM_GATED, m_tiles * ((N / 2 + 63) / 64));
     }
-    long tiles128 = (long)((N + 127) / 128) * ((M + kBM - 1) / kBM);
+    long tiles128 = (long)((N + 127) / 128) * m_tiles;
     bool wide = tiles128 >= sms;
     if (!make_map(&ma, A, M, K, kBM) || !make_map(&mw, W, N, K, wide ? 128 : 64))
         return NNIS_ERR_UNSUPPORTED;
-    // three or four stages (about 100 KB): two CTAs share an SM, so one CTA's
-    // epilogue overlaps the other's products
+    g.out_by_tma = mode == GEMM_STORE ? (N % 8 == 0 && make_map(&mo, C, M, N, kBM))
+                                      : (N % 4 == 0 && make_map(&mo, C, M, N, kBM, 0, 4));
+    if (!g.out_by_tma) mo = ma;
 #define NNIS_GEMM_TC(MODE) \
-    return wide ? launch_gemm_tc<128, 3, MODE>(ma, mw, g, pdl != 0, stream) \
-                : launch_gemm_tc<64, 4, MODE>(ma, mw, g, pdl != 0, stream)
-    if (mode == GEMM_STORE) NNIS_GEMM_TC(GEMM_STORE);
-    if (mode == GEMM_STORE_F32) NNIS_GEMM_TC(GEMM_STORE_F32);
+    if (wide) NNIS_GEMM_TC128(128, MODE, tiles128); \
+    NNIS_GEMM_TC64(MODE, m_tiles * ((N + 63) / 64))
+    if (mode == GEMM_STORE) { NNIS_GEMM_TC(GEMM_STORE); }
+    if (mode == GEMM_STORE_F32) { NNIS_GEMM_TC(GEMM_STORE_F32); }
     NNIS_GEMM_TC(GEMM_ADD_F32);
+#undef NNIS_GEMM_TC64
+#undef NNIS_GEMM_TC128
 #undef NNIS_GEMM_TC
 }

@@ -20,6 +20,24 @@ __device__ __forceinline__ void tma_load_2d(void* dst_smem, const CUtensorMap* m
         : "memory");
 }
 
+// shared -> global tile store, and the same as an addition into the destination
+// (float32); both belong to the thread's current bulk group
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, const void* src_smem) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(c0), "r"(c1), "r"(smem_addr(src_smem))
+                 : "memory");
+}
+__device__ __forceinline__ void tma_add_2d(const CUtensorMap* map, int c0, int c1, const void* src_smem) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(c0), "r"(c1), "r"(smem_addr(src_smem))
+                 : "memory");
+}
+// closes the bulk group and waits until its stores have read their shared memory
+__device__ __forceinline__ void tma_store_commit_wait() {
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+
 __device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t columns) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_addr(dst_smem)),
@@ -117,30 +135,30 @@ static inline EncodeTiledFn encode_tiled() {
     return fn;
 }
 
-// [rows, K] row-major bfloat16 (rows `row_stride` elements apart; 0: packed), boxes
-// of box_rows x 64 columns, 128-byte swizzle.  Encoding a map costs the host a
+// [rows, K] row-major bfloat16 or float32 (`elem_bytes` 2 or 4; rows `row_stride`
+// elements apart; 0: packed), boxes of box_rows x 128 bytes, 128-byte swizzle.  Encoding a map costs the host a
 // microsecond or two and a step encodes hundreds (weights, caches and workspace
 // buffers at the same addresses every time), so the last maps are kept by key.
 struct MapKey {
     const void* ptr;
     long long rows, row_stride;
-    int K, box_rows;
+    int K, box_rows, elem_bytes;
     bool operator==(const MapKey& o) const {
         return ptr == o.ptr && rows == o.rows && row_stride == o.row_stride && K == o.K &&
-               box_rows == o.box_rows;
+               box_rows == o.box_rows && elem_bytes == o.elem_bytes;
     }
 };
 
 static inline bool make_map(CUtensorMap* map, const void* ptr, long long rows, int K, int box_rows,
-                            long long row_stride = 0) {
+                            long long row_stride = 0, int elem_bytes = 2) {
     constexpr int kSlots = 512;
     struct Slot { MapKey key; CUtensorMap map; bool used; };
     static Slot slots[kSlots];
     static std::mutex lock;
-    const MapKey key{ptr, rows, row_stride, K, box_rows};
+    const MapKey key{ptr, rows, row_stride, K, box_rows, elem_bytes};
     size_t h = (size_t)((uintptr_t)ptr >> 4) * 0x9E3779B97F4A7C15ull;
     h ^= (size_t)rows * 0xC2B2AE3D27D4EB4Full + (size_t)K * 0x165667B19E3779F9ull + (size_t)box_rows * 31u +
-         (size_t)row_stride * 0x27D4EB2F165667C5ull;
+         (size_t)row_stride * 0x27D4EB2F165667C5ull + (size_t)elem_bytes;
     Slot& slot = slots[(h >> 20) % kSlots];
     std::lock_guard<std::mutex> guard(lock);
     if (slot.used && slot.key == key) {
@@ -150,10 +168,10 @@ static inline bool make_map(CUtensorMap* map, const void* ptr, long long rows, i
     EncodeTiledFn fn = encode_tiled();
     if (!fn) return false;
     cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)(row_stride > 0 ? row_stride : K) * 2};
-    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};  // 64 bfloat16 = one 128-byte swizzle row
+    cuuint64_t strides[1] = {(cuuint64_t)(row_stride > 0 ? row_stride : K) * (cuuint64_t)elem_bytes};
+    cuuint32_t box[2] = {128u / (cuuint32_t)elem_bytes, (cuuint32_t)box_rows};  // one 128-byte swizzle row
     cuuint32_t elem[2] = {1, 1};
-    if (fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+    if (fn(map, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return false;
