@@ -29,7 +29,6 @@ namespace nnis {
 constexpr int kBM = 128;
 constexpr int kBK = 64;          // 64 bfloat16 = one 128-byte swizzle row
 constexpr int kUmmaK = 16;
-constexpr int kGemmThreads = 192;
 
 enum { GEMM_STORE = 0, GEMM_STORE_F32 = 1, GEMM_ADD_F32 = 2, GEMM_GATED = 3, GEMM_QKV = 4 };
 
@@ -53,15 +52,23 @@ struct GemmArgs {
 };
 
 // Two CTAs share an SM when their stages leave room for it.
-constexpr int gemm_ctas_per_sm(int bn, int stages, int mode, int ksub) {
+__host__ __device__ constexpr int gemm_ctas_per_sm(int bn, int stages, int mode, int ksub) {
     return stages * ksub * (kBM + (mode == GEMM_GATED ? 2 : 1) * bn) * kBK * 2 <= 110 * 1024 ? 2 : 1;
+}
+// A warp that is alone on its scheduler runs every instruction at full latency, so
+// a CTA that has its SM alone brings eight epilogue warps, two per quarter of the
+// rows, each taking every other chunk of 32 columns; with two CTAs per SM the four
+// epilogue warps of each leave the registers for both.
+__host__ __device__ constexpr int gemm_threads(int bn, int stages, int mode, int ksub) {
+    return gemm_ctas_per_sm(bn, stages, mode, ksub) == 1 ? 320 : 192;
 }
 
 // MODE GEMM_GATED: W holds gate rows then up rows ([2 I, K]); the CTA multiplies
 // A by a gate tile and by the matching up tile into two accumulators and writes
-// bf16(silu(gate) * up) to out [M, I].  MODE GEMM_QKV: BN equals the head size.
+// bf16(silu(gate) * up) to out [M, I].  MODE GEMM_QKV: a tile holds whole heads
+// (BN = 128: two heads of 64 or one of 128).
 template <int BN, int STAGES, int MODE, int KSUB>
-__global__ void __launch_bounds__(kGemmThreads, gemm_ctas_per_sm(BN, STAGES, MODE, KSUB))
+__global__ void __launch_bounds__(gemm_threads(BN, STAGES, MODE, KSUB), gemm_ctas_per_sm(BN, STAGES, MODE, KSUB))
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                const __grid_constant__ CUtensorMap map_out, GemmArgs g) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -69,8 +76,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     unsigned char* base = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int NB = MODE == GEMM_GATED ? 2 : 1;  // B tiles (and accumulators) per stage
+    constexpr int kEpiWarps = gemm_threads(BN, STAGES, MODE, KSUB) / 32 - 2;
+    constexpr int kColStep = 32 * (kEpiWarps / 4);  // columns between two chunks of one warp
     constexpr uint32_t kBytesA = kBM * kBK * 2, kBytesB = BN * kBK * 2;
-    constexpr uint32_t kTmemCols = NB * BN;
+    // tensor memory comes in powers of two of columns
+    constexpr uint32_t kTmemCols = NB * BN <= 64 ? 64 : NB * BN <= 128 ? 128 : NB * BN <= 256 ? 256 : 512;
     // a stage holds KSUB slices of 64 columns of K: [KSUB] A tiles, then [KSUB][NB] W tiles
     constexpr uint32_t kStageA = KSUB * kBytesA, kStageB = KSUB * NB * kBytesB;
     unsigned char* tile_a = base;
@@ -91,7 +101,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             mbar_init(&empty_bar[s], 1);
         }
         mbar_init(&acc_bar, 1);
-        mbar_init(&staged_bar, 4);
+        mbar_init(&staged_bar, kEpiWarps);
         abort_flag = 0;
         mbar_fence_init();
     }
@@ -174,40 +184,68 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else {
         // epilogue: warp w reads tensor-memory lanes 32 (w % 4) .. + 31 = tile rows
         const int quarter = warp & 3;
+        const int c_first = 32 * ((warp - 2) >> 2);  // this warp's first chunk of columns
         const int row = quarter * 32 + lane;
         const int m = m0 + row;
         const uint32_t lane_base = tmem_acc + ((uint32_t)(quarter * 32) << 16);
+        // GEMM_QKV: what the epilogue needs from global memory (the row's position,
+        // its cache page, the angles of this warp's first unit) is fetched while the
+        // products run
+        int pos = -1, page = 0;
+        float cs[32], sn[32];
+        if (MODE == GEMM_QKV) {
+            pos = m < g.M ? g.token_pos[m] : -1;
+            if (pos >= 0 && g.nkv > 0)
+                page = g.page_table[(size_t)g.token_seq[m] * g.table_cols + pos / g.page_size];
+            const int half = g.d / 2, c0 = (((warp - 2) >> 2) % (half / 32)) * 32;
+            if (pos >= 0 && g.sin_t) {
+                const float4* c4 = reinterpret_cast<const float4*>(g.cos_t + (size_t)pos * half + c0);
+                const float4* s4 = reinterpret_cast<const float4*>(g.sin_t + (size_t)pos * half + c0);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    float4 cv = c4[i], sv = s4[i];
+                    cs[i * 4] = cv.x; cs[i * 4 + 1] = cv.y; cs[i * 4 + 2] = cv.z; cs[i * 4 + 3] = cv.w;
+                    sn[i * 4] = sv.x; sn[i * 4 + 1] = sv.y; sn[i * 4 + 2] = sv.z; sn[i * 4 + 3] = sv.w;
+                }
+            }
+        }
         bool ok = mbar_wait(&acc_bar, 0);
         ok = __all_sync(0xffffffffu, ok) && !abort_flag;
         if (!ok) {
             abort_flag = 1;
         } else if (MODE == GEMM_QKV) {
             tc_fence_after();
-            // BN == head size: this thread holds one row of one head; columns j and
-            // j + BN/2 are a rotation pair, in chunks c0 and c0 + BN/2
-            const int head = n0 / g.d, half = BN / 2;
-            const bool is_q = head < g.nq, is_v = head >= g.nq + g.nkv;
-            const int pos = m < g.M ? g.token_pos[m] : -1;
-            bf16* dst = nullptr;
-            if (pos >= 0) {
+            // The tile holds BN / d whole heads; this thread holds one row of each.
+            // Columns j and j + d/2 of a head are a rotation pair, in chunks c0 and
+            // c0 + d/2.  The units of work (head of the tile, chunk) are dealt to the
+            // warps that share this quarter of the rows.
+            const int d = g.d, half = d / 2, chunks = half / 32;
+            const int first_unit = (warp - 2) >> 2;
+            int angles_of = first_unit % chunks;  // the chunk whose cos and sin are in registers
+#pragma unroll 1
+            for (int unit = first_unit; unit < (BN / d) * chunks; unit += kEpiWarps / 4) {
+                const int hh = unit / chunks, c0 = (unit % chunks) * 32;
+                const int head = n0 / d + hh;
+                if (head >= g.nq + 2 * g.nkv) break;
+                const bool is_q = head < g.nq, is_v = head >= g.nq + g.nkv;
+                const uint32_t cols = (uint32_t)(hh * d + c0);
+                uint32_t va[32], vb[32];
+                tmem_load32_issue(lane_base + cols, va);
+                tmem_load32_issue(lane_base + cols + (uint32_t)half, vb);
+                tmem_load_wait();
+                if (pos < 0) continue;
+                bf16* dst;
                 if (is_q) {
-                    dst = reinterpret_cast<bf16*>(g.out) + ((size_t)m * g.nq + head) * BN;
+                    dst = reinterpret_cast<bf16*>(g.out) + ((size_t)m * g.nq + head) * d;
                 } else {
                     int hk = is_v ? head - g.nq - g.nkv : head - g.nq;
-                    int page = g.page_table[(size_t)g.token_seq[m] * g.table_cols + pos / g.page_size];
                     dst = (is_v ? g.v_cache : g.k_cache) +
-                          ((size_t)(page * g.nkv + hk) * g.page_size + (pos % g.page_size)) * BN;
+                          ((size_t)(page * g.nkv + hk) * g.page_size + (pos % g.page_size)) * d;
                 }
-            }
-#pragma unroll 1
-            for (int c0 = 0; c0 < half; c0 += 32) {
-                uint32_t va[32], vb[32];
-                tmem_load32(lane_base + (uint32_t)c0, va);
-                tmem_load32(lane_base + (uint32_t)(c0 + half), vb);
-                if (pos < 0) continue;
+                const int nb = head * d + c0;  // column of W's rows, for the bias
                 uint32_t oa[16], ob[16];
-                float cs[32], sn[32];
-                if (g.sin_t && !is_v) {
+                if (g.sin_t && !is_v && (unit % chunks) != angles_of) {
+                    angles_of = unit % chunks;
                     const float4* c4 = reinterpret_cast<const float4*>(g.cos_t + (size_t)pos * half + c0);
                     const float4* s4 = reinterpret_cast<const float4*>(g.sin_t + (size_t)pos * half + c0);
 #pragma unroll
@@ -222,10 +260,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     float a0 = __uint_as_float(va[i]), a1 = __uint_as_float(va[i + 1]);
                     float b0 = __uint_as_float(vb[i]), b1 = __uint_as_float(vb[i + 1]);
                     if (g.bias) {
-                        a0 += g.bias[n0 + c0 + i];
-                        a1 += g.bias[n0 + c0 + i + 1];
-                        b0 += g.bias[n0 + c0 + half + i];
-                        b1 += g.bias[n0 + c0 + half + i + 1];
+                        a0 += g.bias[nb + i];
+                        a1 += g.bias[nb + i + 1];
+                        b0 += g.bias[nb + half + i];
+                        b1 += g.bias[nb + half + i + 1];
                     }
                     // q, k and v are bfloat16 before the rotation, as in the unfused path
                     a0 = __bfloat162float(__float2bfloat16_rn(a0));
@@ -264,14 +302,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             constexpr int kBoxCols = kOut16 ? 64 : 32;
             unsigned char* stage_row = base + (size_t)row * 128;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                uint32_t v[32];
-                tmem_load32(lane_base + (uint32_t)c0, v);
+            for (int c0 = c_first; c0 < BN; c0 += kColStep) {
+                uint32_t v[32], u[32];
+                tmem_load32_issue(lane_base + (uint32_t)c0, v);
+                if constexpr (MODE == GEMM_GATED) tmem_load32_issue(lane_base + (uint32_t)(BN + c0), u);
+                tmem_load_wait();
                 const int nb = n0 + c0;
                 float f[32];
-                if (MODE == GEMM_GATED) {
-                    uint32_t u[32];
-                    tmem_load32(lane_base + (uint32_t)(BN + c0), u);
+                if constexpr (MODE == GEMM_GATED) {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         float gv = __uint_as_float(v[i]), uv = __uint_as_float(u[i]);
@@ -279,7 +317,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             gv += g.bias[nb + i];
                             uv += g.bias[inter + nb + i];
                         }
-                        f[i] = __fdividef(gv, 1.0f + __expf(-gv)) * uv;
+                        // silu(g) * u with the two approximate instructions (2^x and 1/x,
+                        // relative error about 1e-7 each): the exact forms cost the
+                        // epilogue twice the time of the products
+                        float e, r;
+                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(gv * -1.4426950408889634f));
+                        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+                        f[i] = gv * r * uv;
                     }
                 } else {
 #pragma unroll
@@ -325,7 +369,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (g.out_by_tma) {
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&staged_bar);  // the four epilogue warps
+                if (lane == 0) mbar_arrive(&staged_bar);  // every epilogue warp
                 if (threadIdx.x == 64 && !mbar_wait(&staged_bar, 0)) {
                     abort_flag = 1;
                 } else if (threadIdx.x == 64) {
@@ -361,7 +405,7 @@ static int launch_gemm_tc(const CUtensorMap& ma, const CUtensorMap& mw, const CU
     int n_cols = MODE == GEMM_GATED ? g.N / 2 : g.N;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((n_cols + BN - 1) / BN, (g.M + kBM - 1) / kBM);
-    cfg.blockDim = dim3(kGemmThreads);
+    cfg.blockDim = dim3(gemm_threads(BN, STAGES, MODE, KSUB));
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -413,17 +457,21 @@ NNIS_API int nnis_gemm_tc(const void* A, const void* W, const float* bias, void*
         if ((d != 64 && d != 128) || N != (nq + 2 * nkv) * d || !token_pos) return NNIS_ERR_UNSUPPORTED;
         if (nkv > 0 && (!token_seq || !page_table || !k_cache || !v_cache || page_size <= 0))
             return NNIS_ERR_ARGUMENT;
-        if (!make_map(&ma, A, M, K, kBM) || !make_map(&mw, W, N, K, d)) return NNIS_ERR_UNSUPPORTED;
+        if (!make_map(&ma, A, M, K, kBM) || !make_map(&mw, W, N, K, 128)) return NNIS_ERR_UNSUPPORTED;
         mo = ma;  // not used: this epilogue scatters rows into the cache
         g.out_by_tma = 0;
-        if (d == 64) NNIS_GEMM_TC64(GEMM_QKV, m_tiles * (N / 64));
-        NNIS_GEMM_TC128(128, GEMM_QKV, m_tiles * (N / 128));
+        NNIS_GEMM_TC128(128, GEMM_QKV, m_tiles * ((N + 127) / 128));
     }
     if (mode == GEMM_GATED) {
         if (N % 2) return NNIS_ERR_UNSUPPORTED;
-        if (!make_map(&ma, A, M, K, kBM) || !make_map(&mw, W, N, K, 64)) return NNIS_ERR_UNSUPPORTED;
+        // wide outputs: 192 gate and 192 up columns per CTA, which has its SM alone
+        // (384 columns of tensor memory, 64 KB a stage); products of N = 192 run at
+        // the tensor cores' full rate, those of N = 64 at two thirds of it
+        const bool fat = N / 2 > 128;
+        if (!make_map(&ma, A, M, K, kBM) || !make_map(&mw, W, N, K, fat ? 192 : 64)) return NNIS_ERR_UNSUPPORTED;
         g.out_by_tma = (N / 2) % 8 == 0 && make_map(&mo, C, M, N / 2, kBM);
         if (!g.out_by_tma) mo = ma;
+        if (fat) return launch_gemm_tc<192, 3, GEMM_GATED, 1>(ma, mw, mo, g, pdl != 0, stream);
         NNIS_GEMM_TC128(64, GEMM_GATED, m_tiles * ((N / 2 + 63) / 64));
     }
     long tiles128 = (long)((N + 127) / 128) * m_tiles;
