@@ -6,7 +6,7 @@
 // One CTA owns 128 consecutive query tokens of one sequence, one query head and a
 // range of that tile's pages (all of them, or one of several chunks when the host
 // cuts long tiles so that there are CTAs enough for every SM and the late tiles of
-// a long prompt do not run alone at the end).  Its seven warps have fixed roles:
+// a long prompt do not run alone at the end).  Its eleven warps have fixed roles:
 //   warp 0   one lane issues TMA loads: the Q tile [128, 64] once, then a page of
 //            K and of V [64 keys, 64] per step of the loop into a ring of stages;
 //   warp 1   allocates tensor memory; one lane issues, per page,
@@ -17,10 +17,13 @@
 //                                              V as loaded, i.e. MN-major)
 //            (issuing a product and its barrier traffic costs one thread several
 //            hundred cycles a page, so each product has a thread of its own);
-//   warps 3-6  one query row per thread: read the row of S from tensor memory,
-//            mask it, keep the row's maximum and sum (float32, exp2), write P
-//            (bfloat16) into shared memory in the 128-byte-swizzled K-major layout
-//            the second product reads.
+//   warps 3-10 softmax, two warps per quarter of the rows: a thread has one query
+//            row and one half of each page's keys; it reads its 32 scores from
+//            tensor memory, masks them, keeps a maximum and a sum of its own
+//            (float32, exp2), and writes P (bfloat16) into shared memory in the
+//            128-byte-swizzled K-major layout the second product reads.  The halves
+//            have accumulators O of their own (the second product's first two
+//            K steps go to one, the last two to the other) and are merged at the end.
 // S and P are double-buffered.  O stays in tensor memory for the whole tile: the
 // maximum that P is taken against is only raised when a page's maximum exceeds it
 // by more than 8 (a factor 256, harmless in float32 and bfloat16); then the warp
@@ -44,7 +47,7 @@ constexpr int kTcRows = 128;     // queries per CTA
 constexpr int kTcD = 64;         // head size
 constexpr int kTcPage = 64;      // keys per page
 constexpr int kTcStages = 3;     // K/V pages in flight
-constexpr int kTcThreads = 224;
+constexpr int kTcThreads = 352;  // loader, two issuers, eight softmax warps
 constexpr float kTcLog2e = 1.4426950408889634f;
 constexpr int kTcPartial = kTcD + 2;  // floats per row of a chunk's result: O, maximum, sum
 constexpr float kTcRaise = 8.0f;  // log2 of how far a page's maximum may exceed the one in use
@@ -190,7 +193,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     unsigned char* k_s = p_s + 2 * kBytesQ;                      // stages x [64, 64]
     unsigned char* v_s = k_s + kTcStages * kBytesKV;
     __shared__ __align__(8) uint64_t q_full, kv_full[kTcStages], kv_empty[kTcStages];
-    __shared__ __align__(8) uint64_t s_full[2], s_free[2], p_ready[2], p_free[2], o_full;
+    __shared__ __align__(8) uint64_t s_full[2], s_free[2], p_ready[2], p_free[2], o_full, halves_met;
+    __shared__ float half_m[2][kTcRows], half_l[2][kTcRows];  // each half's maximum and sum, for the other
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile int abort_flag;
 
@@ -219,11 +223,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&s_full[b], 2);    // S(i) is there, and P's buffer of page i is free again
-            mbar_init(&s_free[b], 4);    // one arrival per softmax warp
-            mbar_init(&p_ready[b], 4);
+            mbar_init(&s_free[b], 8);    // one arrival per softmax warp
+            mbar_init(&p_ready[b], 8);
             mbar_init(&p_free[b], 1);
         }
         mbar_init(&o_full, 1);
+        mbar_init(&halves_met, 8);
         abort_flag = 0;
         mbar_fence_init();
     }
@@ -231,7 +236,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_s = tmem_base_s, tmem_o = tmem_base_s + 128;  // S: two buffers of 64 columns
+    // S: two buffers of 64 columns; O: one accumulator of 64 columns per half of a page's keys
+    const uint32_t tmem_s = tmem_base_s, tmem_o = tmem_base_s + 128;
 
     if (warp == 0) {
         if (lane == 0) {
@@ -292,9 +298,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 const uint64_t desc_p = desc_advance(desc_p0, (uint32_t)b * kBytesQ);
                 const uint64_t desc_v = desc_advance(desc_v0, (uint32_t)s * kBytesKV);
 #pragma unroll
-                for (int k = 0; k < kTcPage / 16; ++k)
-                    tc_mma(tmem_o, desc_advance(desc_p, k * 32), desc_advance(desc_v, k * 2048), idesc_o,
-                           (i | k) != 0);
+                for (int k = 0; k < kTcPage / 16; ++k)  // keys 0-31 into the first O, 32-63 into the second
+                    tc_mma(tmem_o + (k >> 1) * 64, desc_advance(desc_p, k * 32), desc_advance(desc_v, k * 2048),
+                           idesc_o, (i | (k & 1)) != 0);
                 tc_commit(&p_free[b]);
                 tc_commit(&s_full[b]);  // counts for page i + 2, which writes this buffer of P
                 tc_commit(&kv_empty[s]);
@@ -303,9 +309,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             else abort_flag = 1;
         }
     } else {
-        const int quarter = warp & 3;
+        // Softmax.  Two warps share each quarter of the rows (a warp alone on its
+        // scheduler hides no latency); a thread has one row and one half of every
+        // page's keys, with a running maximum, sum and accumulator O of its own for
+        // that half, so the halves never wait for each other until the end.
+        const int quarter = warp & 3, half = (warp - 3) >> 2;
         const int row = quarter * 32 + lane;
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        const uint32_t my_o = tmem_o + half * 64 + lane_base;
         const int pos = pos0 + row;
         const int lo_row = window > 0 ? pos - window + 1 : 0;
         // the keys every row of this warp sees whole: no masking on such pages
@@ -319,29 +330,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             ok = warp_wait(&s_full[b], (uint32_t)(i >> 1) & 1u, lane) && !abort_flag;
             if (!ok) break;
             tc_fence_after();
-            uint32_t sv[2][32];
-            tmem_load32_issue(tmem_s + b * 64 + lane_base, sv[0]);
-            tmem_load32_issue(tmem_s + b * 64 + lane_base + 32, sv[1]);
-            tmem_load_wait();
+            uint32_t sv[32];
+            tmem_load32(tmem_s + b * 64 + half * 32 + lane_base, sv);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&s_free[b]);  // this buffer may take the page after next
-            const int t0 = (first_page + i) * kTcPage;
-            if (t0 + kTcPage - 1 > warp_pos_min || t0 < warp_lo_max) {
+            const int t0 = (first_page + i) * kTcPage + half * 32;
+            if (t0 + 31 > warp_pos_min || t0 < warp_lo_max) {
 #pragma unroll
-                for (int h = 0; h < 2; ++h)
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) {
-                        int t = t0 + h * 32 + c;
-                        if (t > pos || t < lo_row) sv[h][c] = 0xff800000u;  // -inf
-                    }
+                for (int c = 0; c < 32; ++c)
+                    if (t0 + c > pos || t0 + c < lo_row) sv[c] = 0xff800000u;  // -inf
             }
             float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int c = 0; c < 32; ++c) {
-                mx[c & 3] = fmaxf(mx[c & 3], __uint_as_float(sv[0][c]));
-                mx[c & 3] = fmaxf(mx[c & 3], __uint_as_float(sv[1][c]));
-            }
+            for (int c = 0; c < 32; ++c) mx[c & 3] = fmaxf(mx[c & 3], __uint_as_float(sv[c]));
             const float m_page = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * sc;
             const float m_new = fmaxf(m_run, m_page);
             const bool raise = m_run != -INFINITY && m_new > m_run + kTcRaise;
@@ -355,10 +357,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll 1
                 for (int h = 0; h < 4; ++h) {
                     uint32_t ov[16];
-                    tmem_load16(tmem_o + lane_base + h * 16, ov);
+                    tmem_load16(my_o + h * 16, ov);
 #pragma unroll
                     for (int c = 0; c < 16; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * alpha);
-                    tmem_store16(tmem_o + lane_base + h * 16, ov);
+                    tmem_store16(my_o + h * 16, ov);
                 }
                 l_run *= alpha;
                 m_run = m_new;
@@ -367,20 +369,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             // (the product that read this buffer of P two pages ago is over: s_full said so)
             unsigned char* p_row = p_s + (size_t)b * kBytesQ + (size_t)row * 128;
             float ps[4] = {0.f, 0.f, 0.f, 0.f};
-            // P row: 8 chunks of 8 keys; chunk j lands at 16-byte slot j ^ (row % 8)
+            // P row: 8 chunks of 8 keys, four of them this thread's; chunk j lands at
+            // 16-byte slot j ^ (row % 8)
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < 4; ++j) {
                 uint32_t w[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     int c = j * 8 + e * 2;
-                    float p0 = ex2(fmaf(__uint_as_float(sv[c >> 5][c & 31]), sc, neg_base));
-                    float p1 = ex2(fmaf(__uint_as_float(sv[(c + 1) >> 5][(c + 1) & 31]), sc, neg_base));
+                    float p0 = ex2(fmaf(__uint_as_float(sv[c]), sc, neg_base));
+                    float p1 = ex2(fmaf(__uint_as_float(sv[c + 1]), sc, neg_base));
                     ps[e] += p0 + p1;
                     __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
                     w[e] = *reinterpret_cast<uint32_t*>(&pk);
                 }
-                *reinterpret_cast<uint4*>(p_row + ((j ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                *reinterpret_cast<uint4*>(p_row + (((half * 4 + j) ^ (row & 7)) << 4)) =
+                    make_uint4(w[0], w[1], w[2], w[3]);
             }
             l_run += (ps[0] + ps[1]) + (ps[2] + ps[3]);
             fence_async_smem();  // the tensor core reads P through the async proxy
@@ -388,47 +392,58 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_ready[b]);
         }
-        ok = ok && warp_wait(&o_full, 0, lane) && !abort_flag;
+        // the halves meet: each needs the other's maximum and sum
+        half_m[half][row] = m_run;
+        half_l[half][row] = l_run;
+        __syncwarp();
+        if (ok && lane == 0) mbar_arrive(&halves_met);
+        ok = ok && warp_wait(&halves_met, 0, lane) && warp_wait(&o_full, 0, lane) && !abort_flag;
         if (!ok) {
             abort_flag = 1;
-        } else if (n_chunks == 1) {
+        } else {
             tc_fence_after();
-            const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-            bf16* dst = out + (size_t)(row_base + row) * nq * kTcD + (size_t)hq * kTcD;
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                uint32_t ov[32];
-                tmem_load32(tmem_o + lane_base + h * 32, ov);
+            // this thread finishes 32 of the row's 64 output columns from both accumulators
+            const float m_a = half_m[0][row], m_b = half_m[1][row];
+            const float m_all = fmaxf(m_a, m_b);
+            const float w_a = m_a == -INFINITY ? 0.f : exp2f(m_a - m_all);
+            const float w_b = m_b == -INFINITY ? 0.f : exp2f(m_b - m_all);
+            const float l_all = w_a * half_l[0][row] + w_b * half_l[1][row];
+            uint32_t oa[32], ob[32];
+            tmem_load32_issue(tmem_o + lane_base + half * 32, oa);
+            tmem_load32_issue(tmem_o + 64 + lane_base + half * 32, ob);
+            tmem_load_wait();
+            tc_fence_before();
+            if (n_chunks == 1) {
+                const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
+                const float f_a = w_a * inv, f_b = w_b * inv;
                 if (row < rows) {
+                    bf16* dst = out + (size_t)(row_base + row) * nq * kTcD + (size_t)hq * kTcD + half * 32;
 #pragma unroll
                     for (int c = 0; c < 32; c += 8) {
                         uint32_t w[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            __nv_bfloat162 a = __floats2bfloat162_rn(__uint_as_float(ov[c + 2 * e]) * inv,
-                                                                     __uint_as_float(ov[c + 2 * e + 1]) * inv);
+                            float x0 = f_a * __uint_as_float(oa[c + 2 * e]) + f_b * __uint_as_float(ob[c + 2 * e]);
+                            float x1 = f_a * __uint_as_float(oa[c + 2 * e + 1]) + f_b * __uint_as_float(ob[c + 2 * e + 1]);
+                            __nv_bfloat162 a = __floats2bfloat162_rn(x0, x1);
                             w[e] = *reinterpret_cast<uint32_t*>(&a);
                         }
-                        *reinterpret_cast<uint4*>(dst + h * 32 + c) = make_uint4(w[0], w[1], w[2], w[3]);
+                        *reinterpret_cast<uint4*>(dst + c) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
                 }
-            }
-            tc_fence_before();
-        } else {
-            // one of several chunks: [kTcPartial][128 rows] float32 per (slot, head),
-            // column-major so that a warp's 32 rows are one 128-byte line
-            tc_fence_after();
-            float* dst = partial + ((size_t)(unit.w + chunk) * nq + hq) * (kTcPartial * kTcRows) + row;
+            } else {
+                // one of several chunks: [kTcPartial][128 rows] float32 per (slot, head),
+                // column-major so that a warp's 32 rows are one 128-byte line
+                float* dst = partial + ((size_t)(unit.w + chunk) * nq + hq) * (kTcPartial * kTcRows) + row;
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                uint32_t ov[32];
-                tmem_load32(tmem_o + lane_base + h * 32, ov);
-#pragma unroll
-                for (int c = 0; c < 32; ++c) dst[(size_t)(h * 32 + c) * kTcRows] = __uint_as_float(ov[c]);
+                for (int c = 0; c < 32; ++c)
+                    dst[(size_t)(half * 32 + c) * kTcRows] =
+                        w_a * __uint_as_float(oa[c]) + w_b * __uint_as_float(ob[c]);
+                if (half == 0) {
+                    dst[(size_t)kTcD * kTcRows] = m_all;
+                    dst[(size_t)(kTcD + 1) * kTcRows] = l_all;
+                }
             }
-            dst[(size_t)kTcD * kTcRows] = m_run;
-            dst[(size_t)(kTcD + 1) * kTcRows] = l_run;
-            tc_fence_before();
         }
     }
     tc_fence_before();
