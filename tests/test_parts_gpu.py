@@ -1,5 +1,6 @@
-"""Each part alone against its plain function, and a toy mixer with state of
-its own, defined here, registered, built and stepped without touching the
+"""Each part alone against its plain function, and toy parts defined here (a
+mixer with state of its own, a feed-forward that routes tokens to experts, another
+position encoding), registered, built and stepped without touching the
 framework's files."""
 import math
 
@@ -313,3 +314,135 @@ def test_schedule_runs_a_layer_twice_and_lets_a_layer_read_anothers_cache():
         got = engine.step([SequenceStep(slot, [tokens[t]], [0])])
         check_logits(got.cpu().numpy(), want[t:t + 1], "float32", f"schedule token {t}")
     engine.release_slot(slot)
+
+
+# ---------------------------------------------------------------------------
+# Two more toys, defined here and registered without a change to the framework:
+# a feed-forward that routes every token to one of a few small experts, and a
+# position encoding whose angles are those of RoPE at a fraction of the position.
+# They are no model's parts; they show what the FEED_FORWARDS and POSITIONS
+# registries ask of a new kind.
+# ---------------------------------------------------------------------------
+def _register_routed_and_interpolated():
+    from nnis_b200.parts import FEED_FORWARDS, POSITIONS, Part
+    from nnis_b200.parts.linear import STORE, linear
+    from nnis_b200.weights import WeightSpec
+
+    class TopOneExperts(Part):
+        device_only = False  # the routing decision is read on the host
+
+        def __init__(self, params, prefix, dtype, device):
+            super().__init__(params, prefix, dtype, device)
+            self.h, self.i, self.e = params["hidden_size"], params["expert_size"], params["experts"]
+
+        def weight_specs(self):
+            specs = {self.tensor_name("router"): WeightSpec((self.e, self.h), "matrix", fan_in=self.h)}
+            for e in range(self.e):
+                specs[self.tensor_name(f"expert{e}.up")] = WeightSpec((self.i, self.h), "matrix", fan_in=self.h)
+                specs[self.tensor_name(f"expert{e}.down")] = WeightSpec((self.h, self.i), "matrix", fan_in=self.i)
+            return specs
+
+        def load(self, tensors):
+            self.router = tensors[self.tensor_name("router")].float()
+            self.up = [tensors[self.tensor_name(f"expert{e}.up")] for e in range(self.e)]
+            self.down = [tensors[self.tensor_name(f"expert{e}.down")] for e in range(self.e)]
+
+        def forward(self, x, ctx, residual):
+            logits = x.float() @ self.router.t()                 # router logits in float32
+            prob = torch.softmax(logits, dim=-1)
+            choice = torch.argmax(logits, dim=-1)                # ties go to the lower expert
+            for e in range(self.e):
+                rows = torch.nonzero(choice == e).flatten()
+                if rows.numel() == 0:
+                    continue
+                xe = x[rows].contiguous()
+                mid = torch.empty(rows.numel(), self.i, dtype=x.dtype, device=x.device)
+                linear(xe, self.up[e], None, mid, STORE)         # the framework's own product kernels
+                mid = torch.relu(mid)
+                out = torch.empty(rows.numel(), self.h, dtype=x.dtype, device=x.device)
+                linear(mid, self.down[e], None, out, STORE)
+                residual[rows] += prob[rows, e, None] * out.float()
+
+    class InterpolatedRope(Part):
+        def __init__(self, params, prefix, dtype, device):
+            super().__init__(params, prefix, dtype, device)
+            d, factor = int(params["head_dim"]), float(params["factor"])
+            inv = 1.0 / torch.pow(torch.tensor(float(params["theta"])), 2 * torch.arange(d // 2).float() / d)
+            angle = (torch.arange(int(params["max_positions"])).float() / factor)[:, None] * inv[None, :]
+            self.cos, self.sin = torch.cos(angle).to(device), torch.sin(angle).to(device)
+
+        def rotary_tables(self):
+            return self.cos, self.sin
+
+    FEED_FORWARDS.register("toy_top1_experts", TopOneExperts)
+    POSITIONS.register("toy_interpolated_rope", InterpolatedRope)
+
+
+def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_run_in_a_model():
+    from nnis_b200.engine import Engine, SequenceStep
+    from nnis_b200.engine.model import DecoderModel
+    from nnis_b200.weights import random_tensors
+    _register_routed_and_interpolated()
+    H, V, I, E, nq, nkv, d, eps, factor = 40, 60, 24, 3, 4, 2, 16, 1e-5, 4.0
+    norm = lambda name: PartSpec("rmsnorm", {"size": H, "eps": eps, "name": name})
+    toy_pos = PartSpec("toy_interpolated_rope", {"head_dim": d, "theta": 10000.0, "max_positions": 512,
+                                                 "factor": factor})
+    attn0 = dict(attention_params(H, nq, nkv, d), position=toy_pos)
+    layers = (LayerSpec("l0", "prenorm", norm("n1"), PartSpec("attention", attn0), norm("n2"),
+                        PartSpec("toy_top1_experts", {"hidden_size": H, "expert_size": I, "experts": E})),
+              LayerSpec("l1", "prenorm", norm("n1"), PartSpec("attention", attention_params(H, nq, nkv, d)),
+                        norm("n2"),
+                        PartSpec("gated_mlp", {"hidden_size": H, "intermediate_size": I, "activation": "silu",
+                                               "bias": False, "names": {"gate": "g", "up": "u", "down": "d"}})))
+    spec = ModelSpec(architecture="ToyRouted", hidden_size=H, vocab_size=V, max_positions=512,
+                     embedding=PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H, "name": "emb"}),
+                     layers=layers, schedule=(ScheduleEntry(0), ScheduleEntry(1)), final_norm=norm("final"),
+                     head=PartSpec("linear_head", {"vocab_size": V, "hidden_size": H, "name": "head",
+                                                   "tied_to": "emb"}))
+    wanted = DecoderModel.weight_specs_of(spec)
+    assert "l0.expert2.down.weight" in wanted and "l0.router.weight" in wanted
+    w = random_tensors(wanted, seed=21, std=1.0, norm_std=0.1, std_by_fan_in=True)
+    w["l0.router.weight"] = w["l0.router.weight"] * 4  # choices well apart from ties
+    engine = Engine.from_spec(spec, w, dtype="float32", max_tokens=64 * 8, max_slots=2)
+
+    def plain(tokens):
+        T = len(tokens)
+        h = w["emb.weight"].double()[torch.tensor(tokens)]
+        inv = 1.0 / torch.pow(torch.tensor(10000.0, dtype=torch.float64), 2 * torch.arange(d // 2).double() / d)
+        for prefix, f in (("l0", factor), ("l1", 1.0)):
+            angle = (torch.arange(T).double() / f)[:, None] * inv[None, :]
+            cos, sin = torch.cos(angle), torch.sin(angle)
+            n = P.rms_norm(h, w[prefix + ".n1.weight"], eps)
+            q = P.rope_rotate_half(P.linear(n, w[prefix + ".q.weight"]).view(T, nq, d), cos, sin)
+            k = P.rope_rotate_half(P.linear(n, w[prefix + ".k.weight"]).view(T, nkv, d), cos, sin)
+            v = P.linear(n, w[prefix + ".v.weight"]).view(T, nkv, d)
+            h = h + P.linear(P.causal_attention(q, k, v).reshape(T, nq * d), w[prefix + ".o.weight"])
+            n = P.rms_norm(h, w[prefix + ".n2.weight"], eps)
+            if prefix == "l0":
+                logits = P.linear(n, w["l0.router.weight"])
+                prob, choice = torch.softmax(logits, -1), torch.argmax(logits, -1)
+                used.update(choice.tolist())
+                for t in range(T):
+                    e = int(choice[t])
+                    mid = torch.relu(P.linear(n[t:t + 1], w[f"l0.expert{e}.up.weight"]))
+                    h[t] = h[t] + prob[t, e] * P.linear(mid, w[f"l0.expert{e}.down.weight"])[0]
+            else:
+                h = h + P.linear(P.swiglu(P.linear(n, w["l1.g.weight"]), P.linear(n, w["l1.u.weight"])),
+                                 w["l1.d.weight"])
+        return P.linear(P.rms_norm(h, w["final.weight"], eps), w["emb.weight"])
+
+    used = set()
+    seqs = {"a": [3, 14, 15, 9, 26, 5, 35, 8, 9, 7, 9, 32], "b": [38, 4, 6, 26, 43]}
+    want = {k: plain(v) for k, v in seqs.items()}
+    assert len(used) > 1, "the toy router sent every token to one expert"
+    sa, sb = engine.acquire_slot(), engine.acquire_slot()
+    got = engine.step([SequenceStep(sa, seqs["a"][:9], range(9)), SequenceStep(sb, seqs["b"][:3], [2])])
+    check_logits(got.cpu().numpy(), torch.cat([want["a"][:9], want["b"][2:3]]), "float32", "routed prompt")
+    for t in range(2):
+        got = engine.step([SequenceStep(sa, [seqs["a"][9 + t]], [0]), SequenceStep(sb, [seqs["b"][3 + t]], [0])])
+        check_logits(got.cpu().numpy(), torch.stack([want["a"][9 + t], want["b"][3 + t]]), "float32",
+                     f"routed token {t}")
+    engine.release_slot(sb)
+    got = engine.step([SequenceStep(sa, [seqs["a"][11]], [0])])
+    check_logits(got.cpu().numpy(), want["a"][11:12], "float32", "routed tail")
+    engine.release_slot(sa)
