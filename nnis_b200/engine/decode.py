@@ -51,8 +51,13 @@ class GraphDecoder:
         self.seq = torch.arange(rows, dtype=torch.int32, device=dev)
         self.want = torch.arange(rows, dtype=torch.int32, device=dev)
         self.host_state = torch.empty(self.state_ints, dtype=torch.int32, pin_memory=True)
+        self._host_np = self.host_state.numpy()
         self._host_state_free = torch.cuda.Event()
         self._host_state_free.record()
+        # what the pinned copy holds per (group, row): the slot's table (a new list
+        # with every acquisition), how many of its pages, how many dropped in front;
+        # None: unknown (rows that were set one by one on the device)
+        self._mirror = None
         self.logits = torch.empty((rows, engine.spec.vocab_size), dtype=torch.float32, device=dev) \
             if want_logits else None
         self.picked = torch.zeros(rows, dtype=torch.int32, device=dev)
@@ -102,6 +107,7 @@ class GraphDecoder:
     def set_row(self, row: int, slot: int, token: int, position: int) -> None:
         """Put a sequence on a row: its next input token and that token's position."""
         cache = self.engine.cache
+        self._mirror = None  # the device copy now differs from the pinned one
         update = torch.tensor([token, position, slot], dtype=torch.int32).pin_memory()
         self.tokens[row:row + 1].copy_(update[0:1], non_blocking=True)
         self.pos[row:row + 1].copy_(update[1:2], non_blocking=True)
@@ -114,11 +120,13 @@ class GraphDecoder:
                                       non_blocking=True)
 
     def clear_row(self, row: int) -> None:
+        self._mirror = None
         self.pos[row:row + 1].fill_(-1)
 
     def sync_pages(self, row: int, slot: int) -> None:
         """After the cache reserved more room for ``slot``: send new page ids."""
         cache = self.engine.cache
+        self._mirror = None
         for g in range(len(self.tables)):
             pages = cache.page_table(g, slot)[:self.cols]
             line = self.host_tables[g][row]
@@ -129,18 +137,41 @@ class GraphDecoder:
 
     def upload(self, tokens: Sequence[int], positions: Sequence[int], slots: Sequence[int]) -> int:
         """Replace the state of all rows from the host in one copy: row r gets
-        the r-th sequence; rows beyond them are padding.  Returns the bytes sent."""
+        the r-th sequence; rows beyond them are padding.  Returns the bytes sent.
+        The pinned copy is kept between calls, so a step rewrites the tokens and
+        positions and only those page-table entries that changed."""
         cache = self.engine.cache
         rows, cols, n = self.rows, self.cols, len(tokens)
-        ints = list(tokens) + [0] * (rows - n) + list(positions) + [-1] * (rows - n) \
-            + list(slots) + [0] * (rows - n)
-        for g in range(len(self.tables)):
-            for slot in slots:
-                pages = cache.page_table(g, slot)[:cols]
-                ints += pages + [-1] * (cols - len(pages))
-            ints += [-1] * ((rows - n) * cols)
-        self._host_state_free.synchronize()
-        self.host_state.copy_(torch.tensor(ints, dtype=torch.int32))
+        self._host_state_free.synchronize()  # the copy out of the pinned buffer is over
+        st = self._host_np
+        fresh = self._mirror is None
+        if fresh:
+            st[:] = -1
+            self._mirror = [[None] * rows for _ in self.tables]
+        st[0:n] = tokens
+        st[n:rows] = 0
+        st[rows:rows + n] = positions
+        st[rows + n:2 * rows] = -1
+        st[2 * rows:2 * rows + n] = slots
+        st[2 * rows + n:3 * rows] = 0
+        for g, group in enumerate(cache.groups):
+            base = 3 * rows + g * rows * cols
+            mirror = self._mirror[g]
+            for r, slot in enumerate(slots):
+                table = cache.page_table(g, slot)
+                count = min(len(table), cols)
+                dropped = min(group.first_needed_page(cache.lengths[slot]), count) if group.window > 0 else 0
+                known = mirror[r]
+                if known is not None and known[0] is table and known[1] == count and known[2] == dropped:
+                    continue
+                line = st[base + r * cols:base + (r + 1) * cols]
+                if known is not None and known[0] is table and known[1] <= count and known[2] <= dropped:
+                    line[known[1]:count] = table[known[1]:count]
+                    line[known[2]:dropped] = -1
+                else:
+                    line[:count] = table[:count]
+                    line[count:] = -1
+                mirror[r] = (table, count, dropped)
         self.state.copy_(self.host_state, non_blocking=True)
         self._host_state_free.record()
         for g in range(len(self.tables)):  # the partial-update path starts from scratch next time
