@@ -1,0 +1,78 @@
+"""Long prompts through the engine with head size 64 (the size the tcgen05 prompt
+attention takes): prompts of many pages and several 128-query tiles, a prompt
+continued by a second chunk, single tokens after it, a layer with a window beside
+a layer without (two groups of the cache), in float32 and bfloat16 against the
+plain implementation."""
+import random
+from dataclasses import replace
+
+import pytest
+import torch
+
+import plain_llama as P
+from helpers import check_logits
+from nnis_b200.config.spec import PartSpec
+
+pytestmark = pytest.mark.gpu
+
+CFG = dict(architectures=["LlamaForCausalLM"], model_type="llama", vocab_size=300, hidden_size=128,
+           intermediate_size=200, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+           head_dim=64, max_position_embeddings=2048, rms_norm_eps=1e-5, rope_theta=10000.0,
+           hidden_act="silu", tie_word_embeddings=True, attention_bias=False, torch_dtype="float32")
+WINDOWS = [0, 150]
+
+
+def plain_forward(w, tokens, bf):
+    """plain_llama.forward with a window on the second layer."""
+    eps, T = CFG["rms_norm_eps"], len(tokens)
+    cos, sin = P.rope_tables(T, CFG["head_dim"], CFG["rope_theta"])
+    h = P.embed(w["model.embed_tokens.weight"], tokens)
+    for layer, window in enumerate(WINDOWS):
+        p = f"model.layers.{layer}."
+        n = P._round(P.rms_norm(h, w[p + "input_layernorm.weight"], eps), bf)
+        h = h + P.attention_layer(CFG, w, p + "self_attn.", n, cos, sin, bf, window)
+        n = P._round(P.rms_norm(h, w[p + "post_attention_layernorm.weight"], eps), bf)
+        h = h + P.mlp_layer(CFG, w, p + "mlp.", n, bf)
+    return P.linear(P._round(P.rms_norm(h, w["model.norm.weight"], eps), bf), w["model.embed_tokens.weight"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_prompts_in_chunks_with_and_without_a_window(dtype):
+    from nnis_b200.config import config_from_dict
+    from nnis_b200.engine import Engine, SequenceStep
+    from nnis_b200.engine.model import DecoderModel
+    from nnis_b200.weights import random_tensors
+    spec = config_from_dict(CFG).to_spec()
+    layers = list(spec.layers)
+    mixer = layers[1].mixer
+    layers[1] = replace(layers[1], mixer=PartSpec(mixer.kind, {**mixer.params, "window": WINDOWS[1]}))
+    spec = replace(spec, layers=tuple(layers))
+    tensors = random_tensors(DecoderModel.weight_specs_of(spec), seed=64, std=1.0, norm_std=0.1,
+                             std_by_fan_in=True)
+    bf = dtype == "bfloat16"
+    w = {k: (v.to(torch.bfloat16).float() if bf else v.float()) for k, v in tensors.items()}
+    engine = Engine.from_spec(spec, tensors, dtype=dtype, max_tokens=64 * 40, max_slots=3)
+    assert len(engine.cache.groups) == 2  # the windowed layer keeps pages of its own
+    rng = random.Random(5)
+    seqs = {"a": [rng.randrange(300) for _ in range(700)], "b": [rng.randrange(300) for _ in range(131)],
+            "c": [rng.randrange(300) for _ in range(64)]}
+    want = {k: plain_forward(w, v, bf) for k, v in seqs.items()}
+    slot = {k: engine.acquire_slot() for k in seqs}
+    # whole prompts of unequal length in one step (a: first chunk only)
+    picks = {"a": [0, 127, 128, 399], "b": [0, 63, 64, 130], "c": [63]}
+    got = engine.step([SequenceStep(slot["a"], seqs["a"][:400], picks["a"]),
+                       SequenceStep(slot["b"], seqs["b"], picks["b"]),
+                       SequenceStep(slot["c"], seqs["c"], picks["c"])])
+    rows = torch.cat([want[k][picks[k]] for k in ("a", "b", "c")])
+    check_logits(got.cpu().numpy(), rows, dtype, "first chunks")
+    engine.release_slot(slot["b"])
+    engine.release_slot(slot["c"])
+    # the second chunk of a starts inside a page and a tile, beyond the window of layer 1
+    got = engine.step([SequenceStep(slot["a"], seqs["a"][400:690], [0, 100, 289])])
+    check_logits(got.cpu().numpy(), want["a"][[400, 500, 689]], dtype, "second chunk")
+    for t in range(690, 700):
+        got = engine.step([SequenceStep(slot["a"], [seqs["a"][t]], [0])])
+        check_logits(got.cpu().numpy(), want["a"][t:t + 1], dtype, f"token {t}")
+    engine.release_slot(slot["a"])
+    engine.check_status()
+    engine.cache.check()
