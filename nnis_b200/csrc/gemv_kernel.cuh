@@ -161,6 +161,47 @@ gemv_kernel(GemvArgs a) {
             nw[j] = c < k4 ? reinterpret_cast<const float4*>(a.norm_w)[c] : make_float4(0.f, 0.f, 0.f, 0.f);
         }
     }
+    // What the epilogue of this warp's first unit needs from global memory does not
+    // come from the kernel just before this one either (the residual stream was last
+    // written two kernels back, positions and page tables before the step began), so
+    // it is fetched now, under that kernel's tail, instead of after the products.
+    const int r_lo = lane >> 2, c_lo = (lane & 3) * 2;  // rows r_lo, r_lo + 8; columns c_lo, c_lo + 1
+    const bool epi_warp = !SPLITK || warp == 0;
+    float2 old0[MTILES][2];          // ADD_F32: the destination's values
+    int pos0[MTILES][2], page0[MTILES][2];  // QKV: position and cache page of the row
+    float cos0[MTILES][4], sin0[MTILES][4];
+    if (EPI == EPI_ADD_F32 && epi_warp && first_unit < n_units) {
+        const int n0 = first_unit * 8 + c_lo;
+#pragma unroll
+        for (int t = 0; t < MTILES; ++t)
+#pragma unroll
+            for (int hrow = 0; hrow < 2; ++hrow) {
+                int m = t * 16 + r_lo + hrow * 8;
+                old0[t][hrow] = m < M ? *reinterpret_cast<const float2*>(
+                                            reinterpret_cast<const float*>(a.out) + (size_t)m * a.N + n0)
+                                      : make_float2(0.f, 0.f);
+            }
+    }
+    if (EPI == EPI_QKV && epi_warp && first_unit < n_units) {
+        const int na = unit_row<EPI>(a, first_unit, c_lo & 3);
+        const int head = na / a.d, j = na - head * a.d, hf = a.d >> 1;
+        const bool rotate = a.sin_t && head < a.nq + a.nkv;
+#pragma unroll
+        for (int t = 0; t < MTILES; ++t)
+#pragma unroll
+            for (int hrow = 0; hrow < 2; ++hrow) {
+                int m = t * 16 + r_lo + hrow * 8;
+                int pos = m < M ? a.token_pos[m] : -1;
+                pos0[t][hrow] = pos;
+                page0[t][hrow] = (pos >= 0 && head >= a.nq)
+                                     ? a.page_table[(size_t)a.token_seq[m] * a.table_cols + pos / a.page_size] : 0;
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    cos0[t][hrow * 2 + e] = (rotate && pos >= 0) ? a.cos_t[(size_t)pos * hf + j + e] : 1.f;
+                    sin0[t][hrow * 2 + e] = (rotate && pos >= 0) ? a.sin_t[(size_t)pos * hf + j + e] : 0.f;
+                }
+            }
+    }
     // Dependents are released only after this kernel's own wait: a kernel that
     // starts early may then rely on everything before its immediate predecessor
     // (the decode attention kernel reads old cache pages before its wait).
@@ -226,7 +267,6 @@ gemv_kernel(GemvArgs a) {
     // ---- units of eight output rows --------------------------------------------
     const int half = a.d >> 1;
     const int inter = a.N >> 1;
-    const int r_lo = lane >> 2, c_lo = (lane & 3) * 2;  // rows r_lo, r_lo + 8; columns c_lo, c_lo + 1
     float best_v[MTILES][2];
     int best_i[MTILES][2];
 #pragma unroll
@@ -318,15 +358,15 @@ gemv_kernel(GemvArgs a) {
                         reinterpret_cast<bf16*>(a.out)[(size_t)m * inter + na] =
                             __float2bfloat16_rn((va / (1.0f + expf(-va))) * vb);
                     } else {
-                        int pos = a.token_pos[m];
+                        int pos = i == 0 ? pos0[t][e >> 1] : a.token_pos[m];
                         if (pos < 0) continue;
                         int head = na / a.d, j = na - head * a.d;
                         va = round_bf16(va);
                         vb = round_bf16(vb);
                         bool is_v = head >= a.nq + a.nkv;
                         if (a.sin_t && !is_v) {
-                            float c = a.cos_t[(size_t)pos * half + j];
-                            float s = a.sin_t[(size_t)pos * half + j];
+                            float c = i == 0 ? cos0[t][e] : a.cos_t[(size_t)pos * half + j];
+                            float s = i == 0 ? sin0[t][e] : a.sin_t[(size_t)pos * half + j];
                             float ra = va * c - vb * s, rb = vb * c + va * s;
                             va = ra;
                             vb = rb;
@@ -339,8 +379,9 @@ gemv_kernel(GemvArgs a) {
                         } else {
                             int hk = is_v ? head - a.nq - a.nkv : head - a.nq;
                             bf16* cache = is_v ? a.v_cache : a.k_cache;
-                            int page = a.page_table[(size_t)a.token_seq[m] * a.table_cols +
-                                                    pos / a.page_size];
+                            int page = i == 0 ? page0[t][e >> 1]
+                                              : a.page_table[(size_t)a.token_seq[m] * a.table_cols +
+                                                             pos / a.page_size];
                             size_t dst = ((size_t)(page * a.nkv + hk) * a.page_size +
                                           (pos % a.page_size)) * a.d;
                             cache[dst + j] = ta;
@@ -366,7 +407,7 @@ gemv_kernel(GemvArgs a) {
                         *reinterpret_cast<float2*>(reinterpret_cast<float*>(a.out) + o) = make_float2(v0, v1);
                     } else if (EPI == EPI_ADD_F32) {
                         float2* p = reinterpret_cast<float2*>(reinterpret_cast<float*>(a.out) + o);
-                        float2 old = *p;
+                        float2 old = i == 0 ? old0[t][hrow] : *p;
                         *p = make_float2(old.x + v0, old.y + v1);
                     } else {
                         if (a.logits) *reinterpret_cast<float2*>(a.logits + o) = make_float2(v0, v1);
