@@ -31,8 +31,8 @@
 // tensor memory and goes on.  Sum and output are relative to the same maximum, so
 // the result is the exact softmax.
 // A CTA with all pages of its tile writes bfloat16 output rows; a chunk writes its
-// unnormalised rows, maxima and sums (float32) to scratch, and a second small
-// kernel merges the chunks of a tile.
+// unnormalised rows, maxima and sums (float32) to scratch, takes a ticket, and the
+// chunk that arrives last merges the chunks of the tile.
 // The host lists the units (sequence, first query, chunk) because sequences have
 // unequal lengths.  Every wait is bounded; a wait that runs out raises an abort flag that
 // every role sees, all warps still meet at the end and tensor memory is freed.
@@ -138,52 +138,14 @@ __device__ __forceinline__ void tmem_store16(uint32_t taddr, const uint32_t (&v)
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
-// Chunks of one (tile, head) -> bfloat16 output rows.  Thread = query row.
-__global__ void __launch_bounds__(kTcRows)
-attn_prefill_tc_merge_kernel(const int* __restrict__ merges, const int* __restrict__ seq_first_row,
-                             const int* __restrict__ seq_count, const float* __restrict__ partial,
-                             bf16* __restrict__ out, int nq) {
-    const int4 mg = reinterpret_cast<const int4*>(merges)[blockIdx.x];  // seq, q0, chunks, slot
-    const int hq = blockIdx.y, row = threadIdx.x;
-    if (row >= seq_count[mg.x] - mg.y) return;
-    const size_t stride = (size_t)nq * (kTcPartial * kTcRows);
-    const float* src = partial + ((size_t)mg.w * nq + hq) * (kTcPartial * kTcRows) + row;
-    float m = -INFINITY;
-    for (int c = 0; c < mg.z; ++c) m = fmaxf(m, src[c * stride + (size_t)kTcD * kTcRows]);
-    float acc[kTcD];
-#pragma unroll
-    for (int j = 0; j < kTcD; ++j) acc[j] = 0.f;
-    float l = 0.f;
-    for (int c = 0; c < mg.z; ++c) {
-        const float* s = src + c * stride;
-        const float mc = s[(size_t)kTcD * kTcRows];
-        if (mc == -INFINITY) continue;  // no key of this chunk was visible to the row
-        const float w = exp2f(mc - m);
-        l = fmaf(w, s[(size_t)(kTcD + 1) * kTcRows], l);
-#pragma unroll
-        for (int j = 0; j < kTcD; ++j) acc[j] = fmaf(w, s[(size_t)j * kTcRows], acc[j]);
-    }
-    const float inv = l > 0.f ? 1.0f / l : 0.f;
-    bf16* dst = out + (size_t)(seq_first_row[mg.x] + mg.y + row) * nq * kTcD + (size_t)hq * kTcD;
-#pragma unroll
-    for (int j = 0; j < kTcD; j += 8) {
-        uint32_t w[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            __nv_bfloat162 a = __floats2bfloat162_rn(acc[j + 2 * e] * inv, acc[j + 2 * e + 1] * inv);
-            w[e] = *reinterpret_cast<uint32_t*>(&a);
-        }
-        *reinterpret_cast<uint4*>(dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
-    }
-}
-
 __global__ void __launch_bounds__(kTcThreads, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const int* __restrict__ units,
                        const int* __restrict__ seq_first_row, const int* __restrict__ seq_start,
                        const int* __restrict__ seq_count, const int* __restrict__ page_table,
-                       int table_cols, bf16* __restrict__ out, float* __restrict__ partial, int nq, int nkv,
-                       int window, float scale, int* __restrict__ status) {
+                       int table_cols, bf16* __restrict__ out, float* __restrict__ partial,
+                       unsigned* __restrict__ tickets, int nq, int nkv, int window, float scale,
+                       int* __restrict__ status) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -195,6 +157,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     __shared__ __align__(8) uint64_t q_full, kv_full[kTcStages], kv_empty[kTcStages];
     __shared__ __align__(8) uint64_t s_full[2], s_free[2], p_ready[2], p_free[2], o_full, halves_met;
     __shared__ float half_m[2][kTcRows], half_l[2][kTcRows];  // each half's maximum and sum, for the other
+    __shared__ __align__(8) uint64_t chunk_written, last_known;
+    __shared__ int is_last_chunk;
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile int abort_flag;
 
@@ -229,6 +193,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         mbar_init(&o_full, 1);
         mbar_init(&halves_met, 8);
+        mbar_init(&chunk_written, 8);
+        mbar_init(&last_known, 1);
         abort_flag = 0;
         mbar_fence_init();
     }
@@ -432,9 +398,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     }
                 }
             } else {
-                // one of several chunks: [kTcPartial][128 rows] float32 per (slot, head),
-                // column-major so that a warp's 32 rows are one 128-byte line
-                float* dst = partial + ((size_t)(unit.w + chunk) * nq + hq) * (kTcPartial * kTcRows) + row;
+                // One of several chunks of this tile's pages: its unnormalised rows,
+                // maxima and sums go to scratch, [kTcPartial][128 rows] float32 per
+                // (slot, head), column-major so that a warp's 32 rows are one 128-byte
+                // line; the chunk that finds all others written merges them, in the
+                // order of the chunks whichever came last.
+                const size_t per_chunk_floats = (size_t)nq * (kTcPartial * kTcRows);
+                float* tile_partial = partial + ((size_t)unit.w * nq + hq) * (kTcPartial * kTcRows) + row;
+                float* dst = tile_partial + (size_t)chunk * per_chunk_floats;
 #pragma unroll
                 for (int c = 0; c < 32; ++c)
                     dst[(size_t)(half * 32 + c) * kTcRows] =
@@ -442,6 +413,55 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 if (half == 0) {
                     dst[(size_t)kTcD * kTcRows] = m_all;
                     dst[(size_t)(kTcD + 1) * kTcRows] = l_all;
+                }
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&chunk_written);
+                if (warp == 3 && lane == 0) {
+                    if (mbar_wait(&chunk_written, 0)) {
+                        unsigned* ticket = tickets + (size_t)unit.w * nq + hq;
+                        const bool last = atomicAdd(ticket, 1u) == (unsigned)n_chunks - 1u;
+                        if (last) *ticket = 0u;  // the next launch finds it zero
+                        is_last_chunk = last ? 1 : 0;
+                    } else {
+                        is_last_chunk = 0;
+                        abort_flag = 1;
+                    }
+                    mbar_arrive(&last_known);
+                }
+                if (warp_wait(&last_known, 0, lane) && is_last_chunk && !abort_flag) {
+                    __threadfence();
+                    float m_tile = -INFINITY;
+                    for (int c = 0; c < n_chunks; ++c)
+                        m_tile = fmaxf(m_tile, __ldcg(tile_partial + (size_t)c * per_chunk_floats + (size_t)kTcD * kTcRows));
+                    float acc[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) acc[j] = 0.f;
+                    float l_tile = 0.f;
+                    for (int c = 0; c < n_chunks; ++c) {
+                        const float* src = tile_partial + (size_t)c * per_chunk_floats;
+                        const float mc = __ldcg(src + (size_t)kTcD * kTcRows);
+                        if (mc == -INFINITY) continue;  // no key of this chunk was visible to the row
+                        const float wc = exp2f(mc - m_tile);
+                        l_tile = fmaf(wc, __ldcg(src + (size_t)(kTcD + 1) * kTcRows), l_tile);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            acc[j] = fmaf(wc, __ldcg(src + (size_t)(half * 32 + j) * kTcRows), acc[j]);
+                    }
+                    const float inv = l_tile > 0.f ? 1.0f / l_tile : 0.f;
+                    if (row < rows) {
+                        bf16* o_dst = out + (size_t)(row_base + row) * nq * kTcD + (size_t)hq * kTcD + half * 32;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                __nv_bfloat162 a = __floats2bfloat162_rn(acc[j + 2 * e] * inv, acc[j + 2 * e + 1] * inv);
+                                w[e] = *reinterpret_cast<uint32_t*>(&a);
+                            }
+                            *reinterpret_cast<uint4*>(o_dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    }
                 }
             }
         }
@@ -460,27 +480,27 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 // `units`: int32 [n_units, 4] = (sequence of the batch, first query of the tile
 // within this step's tokens of that sequence, chunk | chunks << 16, first scratch
 // slot of the tile), 128 queries per tile, the pages of a tile cut into `chunks`
-// equal ranges (the last may be shorter, none empty); `merges`: int32 [n_merges, 4]
-// = (sequence, first query, chunks, first slot) for the tiles with several chunks;
-// `partial`: float32 [slots, nq, 66, 128] scratch.  Per sequence `seq_first_row`,
-// `seq_start`, `seq_count` as for nnis_attention_prefill_mma.
+// equal ranges (the last may be shorter, none empty).  `partial`: float32
+// [slots, nq, 66, 128] scratch and `tickets`: [slots, nq] counters, zero before the
+// first launch and left zero, both only when tiles were cut.  Per sequence
+// `seq_first_row`, `seq_start`, `seq_count` as for nnis_attention_prefill_mma.
 // q: [n_tokens, nq * 64] bfloat16 with rows `q_stride` elements apart (a multiple
 // of 8).  Takes head size 64 with 64-key pages; else NNIS_ERR_UNSUPPORTED.
 NNIS_API int nnis_attention_prefill_tc(const void* q, int q_stride, int n_tokens, const void* k_cache,
                                        const void* v_cache, long long cache_rows, const int* units,
-                                       int n_units, const int* merges, int n_merges, float* partial,
+                                       int n_units, float* partial, unsigned* tickets,
                                        const int* seq_first_row, const int* seq_start,
                                        const int* seq_count, const int* page_table, int table_cols,
                                        void* out, int nq, int nkv, int d, int page_size, int window,
                                        float scale, int* status, cudaStream_t stream) {
     using namespace nnis;
     if (n_units <= 0 || n_tokens <= 0 || nq <= 0 || nkv <= 0 || nq % nkv || table_cols <= 0 ||
-        window < 0 || !units || cache_rows <= 0 || q_stride < nq * d || !(scale > 0.f) || n_merges < 0 ||
-        (n_merges > 0 && (!merges || !partial)))
+        window < 0 || !units || cache_rows <= 0 || q_stride < nq * d || !(scale > 0.f) ||
+        ((partial == nullptr) != (tickets == nullptr)))
         return NNIS_ERR_ARGUMENT;
     if (d != kTcD || page_size != kTcPage || nq > 65535 || q_stride % 8) return NNIS_ERR_UNSUPPORTED;
     if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out | (uintptr_t)units |
-         (uintptr_t)merges | (uintptr_t)partial) % 16)
+         (uintptr_t)partial) % 16)
         return NNIS_ERR_ALIGNMENT;
     CUtensorMap mq, mk, mv;
     if (!make_map(&mq, q, n_tokens, nq * kTcD, kTcRows, q_stride) ||
@@ -492,11 +512,6 @@ NNIS_API int nnis_attention_prefill_tc(const void* q, int q_stride, int n_tokens
     if (e != cudaSuccess) return (int)e;
     attn_prefill_tc_kernel<<<dim3(n_units, nq), kTcThreads, smem, stream>>>(
         mq, mk, mv, units, seq_first_row, seq_start, seq_count, page_table, table_cols, (bf16*)out,
-        partial, nq, nkv, window, scale, status);
-    e = cudaGetLastError();
-    if (e != cudaSuccess) return (int)e;
-    if (n_merges > 0)
-        attn_prefill_tc_merge_kernel<<<dim3(n_merges, nq), kTcRows, 0, stream>>>(
-            merges, seq_first_row, seq_count, partial, (bf16*)out, nq);
+        partial, tickets, nq, nkv, window, scale, status);
     NNIS_RETURN_LAUNCH();
 }

@@ -440,14 +440,12 @@ def prefill_tc_plan(counts, starts, window: int, heads: int, sms: int):
 
     A tile is 128 queries of one sequence; its keys are the pages from its first
     query's window start to its last query.  Tiles are cut into chunks of pages
-    when there would be CTAs (units x heads) for less than half of the SMs: chunks
-    of 32 pages if that gives enough, else of 16 (a chunk costs a CTA's start and
-    end and a pass of the merge kernel, about as much as eight pages, so cutting
-    pays only when most SMs would idle: one long prompt, few heads).  Returns
-    ``units`` int32 [n, 4] (sequence, first query, chunk | chunks << 16, first
-    scratch slot), longest first, ``merges`` int32 [m, 4] (sequence, first query,
-    chunks, first slot) for the tiles that were cut, and the number of scratch
-    slots."""
+    while there would be CTAs (units x heads) for fewer than one and a third of the
+    SMs: chunks of 32 pages if that gives enough, else of 16, else of 8 (a chunk
+    costs a CTA's start and end, a trip of its rows through scratch and, for the
+    last one of a tile, the merge).  Returns ``units`` int32 [n, 4] (sequence,
+    first query, chunk | chunks << 16, first scratch slot), longest first, and the
+    number of scratch slots."""
     import numpy as np
     tiles = []
     for i, (c, st) in enumerate(zip(counts, starts)):
@@ -456,12 +454,12 @@ def prefill_tc_plan(counts, starts, window: int, heads: int, sms: int):
             pos0 = int(st) + q0
             lo = max(0, pos0 - window + 1) if window > 0 else 0
             tiles.append((i, q0, (pos0 + rows - 1) // 64 - lo // 64 + 1))
-    chunk_pages = 16
-    for cand in (1 << 30, 32):
-        if 2 * sum(-(-p // cand) for _, _, p in tiles) * heads >= sms:
+    chunk_pages = 8
+    for cand in (1 << 30, 32, 16):
+        if 3 * sum(-(-p // cand) for _, _, p in tiles) * heads >= 4 * sms:
             chunk_pages = cand
             break
-    units, merges, slot = [], [], 0
+    units, slot = [], 0
     for i, q0, pages in tiles:
         n = -(-pages // chunk_pages)
         while n > 1 and (n - 1) * (-(-pages // n)) >= pages:  # no chunk may be empty
@@ -470,26 +468,25 @@ def prefill_tc_plan(counts, starts, window: int, heads: int, sms: int):
         for c in range(n):
             units.append((min(per, pages - c * per), i, q0, c | (n << 16), slot if n > 1 else 0))
         if n > 1:
-            merges.append((i, q0, n, slot))
             slot += n
     units.sort(key=lambda u: -u[0])
-    return (np.asarray([u[1:] for u in units], dtype=np.int32).reshape(-1, 4),
-            np.asarray(merges, dtype=np.int32).reshape(-1, 4), slot)
+    return np.asarray([u[1:] for u in units], dtype=np.int32).reshape(-1, 4), slot
 
 
 PREFILL_TC_PARTIAL = 66 * WIDE_QUERY_TILE  # float32 per (scratch slot, head)
 
 
 def attention_prefill_tc(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor,
-                         units: torch.Tensor, merges: Optional[torch.Tensor],
-                         partial: Optional[torch.Tensor], seq_first_row: torch.Tensor,
+                         units: torch.Tensor, partial: Optional[torch.Tensor],
+                         tickets: Optional[torch.Tensor], seq_first_row: torch.Tensor,
                          seq_start: torch.Tensor, seq_count: torch.Tensor, page_table: torch.Tensor,
                          out: torch.Tensor, heads: int, kv_heads: int, head_dim: int, window: int,
                          scale: float) -> None:
     """Prompt attention on tcgen05 (head size 64): packed query tokens, each over
-    its own sequence's keys in the paged cache.  ``units`` and ``merges`` come
-    from ``prefill_tc_plan``; ``partial`` is float32 scratch of
-    slots x heads x PREFILL_TC_PARTIAL values when tiles were cut."""
+    its own sequence's keys in the paged cache.  ``units`` comes from
+    ``prefill_tc_plan``; when it cuts tiles, ``partial`` is float32 scratch of
+    slots x heads x PREFILL_TC_PARTIAL values and ``tickets`` int32 [slots x heads],
+    zero before the first launch (the kernel leaves them zero)."""
     _cuda(k_cache, v_cache, units, seq_first_row, seq_start, seq_count, page_table, out)
     _need(q.is_cuda and q.dtype == torch.bfloat16 == k_cache.dtype == out.dtype,
           "attention_prefill_tc: bfloat16 tensors")
@@ -505,16 +502,14 @@ def attention_prefill_tc(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, 
         _need(t.dtype == torch.int32, "attention_prefill_tc: int32 tables")
     _need(units.dim() == 2 and units.shape[1] == 4 and units.shape[0] > 0 and units.is_contiguous(),
           "units: int32 [n_units, 4]")
-    n_merges = 0 if merges is None else merges.shape[0]
-    if n_merges:
-        _cuda(merges, partial)
-        _need(merges.dtype == torch.int32 and merges.dim() == 2 and merges.shape[1] == 4
-              and merges.is_contiguous(), "merges: int32 [n_merges, 4]")
-        _need(partial.dtype == torch.float32, "partial: float32 scratch")
+    if partial is not None:
+        _cuda(partial, tickets)
+        _need(partial.dtype == torch.float32 and tickets.dtype == torch.int32,
+              "partial: float32 scratch, tickets: int32")
     _check(_lib().nnis_attention_prefill_tc(
         _ptr(q), q_stride, out.shape[0], _ptr(k_cache), _ptr(v_cache),
         ctypes.c_longlong(pages * nkv * page_size), _ptr(units), units.shape[0],
-        _ptr(merges) if n_merges else None, n_merges, _ptr(partial) if n_merges else None,
+        _ptr(partial) if partial is not None else None, _ptr(tickets) if partial is not None else None,
         _ptr(seq_first_row), _ptr(seq_start), _ptr(seq_count), _ptr(page_table), page_table.shape[1],
         _ptr(out), heads, kv_heads, head_dim, page_size, window, ctypes.c_float(scale),
         _ptr(status_word(out.device)), _stream()),

@@ -79,7 +79,7 @@ class DecoderModel:
         """The work lists that the scheduled blocks want uploaded for a prompt step."""
         tables: Dict[str, object] = {}
         for layer in sorted({e.layer for e in self.spec.schedule}):
-            for name, arr in self.blocks[layer].step_tables(counts, starts).items():
+            for name, arr in self.blocks[layer].step_tables(counts, starts, tuple(tables)).items():
                 tables.setdefault(name, arr)
         return tables
 

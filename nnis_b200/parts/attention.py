@@ -17,6 +17,7 @@ from __future__ import annotations
 import math
 from typing import Dict, Mapping, Optional
 
+import numpy as np
 import torch
 
 from ..cache import PAGE_SIZE, KVRequest, KVView
@@ -92,16 +93,18 @@ class Attention(Part):
     def _tc_plan_name(self) -> str:
         return f"prefill_tc/window{self.window}/heads{self.heads}"
 
-    def step_tables(self, counts, starts):
-        """Units and merges of the tcgen05 prompt attention kernel (bfloat16, head
+    def step_tables(self, counts, starts, have=()):
+        """Units of the tcgen05 prompt attention kernel (bfloat16, head
         size 64), shared by all layers with this window and number of heads."""
         if self.dtype != torch.bfloat16 or not ops.attention_prefill_tc_takes(
                 self.head_dim, PAGE_SIZE, self.heads * self.head_dim):
             return {}
-        units, merges, _ = ops.prefill_tc_plan(counts, starts, self.window, self.heads,
-                                               ops.sm_count(self.device))
         name = self._tc_plan_name()
-        return {name + "/units": units, name + "/merges": merges}
+        if name + "/units" in have:
+            return {}
+        units, slots = ops.prefill_tc_plan(counts, starts, self.window, self.heads,
+                                           ops.sm_count(self.device))
+        return {name + "/units": units, name + "/slots": np.asarray([slots], dtype=np.int32)}
 
     # -- run --------------------------------------------------------------
     def _decode_kernels(self, ctx, n: int) -> bool:
@@ -184,14 +187,14 @@ class Attention(Part):
                 and ops.attention_prefill_tc_takes(d, cache.page_size, q_stride):
             # tcgen05 kernel: a CTA per (128 queries of a sequence, query head, chunk of pages)
             name = self._tc_plan_name()
-            merges = ctx.tables[name + "/merges"]
-            slots = int(ctx.host_tables[name + "/merges"][:, 2].sum())
-            partial = ws.get("attn_tc_partial", (slots * nq * ops.PREFILL_TC_PARTIAL,),
-                             torch.float32) if slots else None
+            slots = int(ctx.host_tables[name + "/slots"][0])
+            partial = tickets = None
+            if slots:  # tiles were cut: scratch for the chunks, tickets that stay zero between launches
+                partial = ws.get("attn_tc_partial", (slots * nq * ops.PREFILL_TC_PARTIAL,), torch.float32)
+                tickets = ws.zeros("attn_tc_tickets", (slots * nq,), torch.int32)
             ops.attention_prefill_tc(q_buf, q_stride, cache.k, cache.v, ctx.tables[name + "/units"],
-                                     merges if slots else None, partial, ctx.seq_first_row,
-                                     ctx.seq_start, ctx.seq_count, table, attn, nq, nkv, d,
-                                     self.window, self.scale)
+                                     partial, tickets, ctx.seq_first_row, ctx.seq_start, ctx.seq_count,
+                                     table, attn, nq, nkv, d, self.window, self.scale)
         elif self.dtype == torch.bfloat16 and not ctx.decode and ctx.q_tiles is not None \
                 and ops.attention_decode_mma_takes(d, cache.page_size):
             ops.attention_prefill_mma(q_buf, q_stride, cache.k, cache.v, ctx.q_tiles,

@@ -54,10 +54,11 @@ class Part:
         """Bytes of weights that one step reads."""
         return 0
 
-    def step_tables(self, counts, starts) -> Dict[str, Any]:
+    def step_tables(self, counts, starts, have=()) -> Dict[str, Any]:
         """Integer tables (numpy int32 arrays by name) that this part wants on the
         device for a prompt step whose sequences bring ``counts`` tokens after
-        ``starts`` cached ones: work lists of its kernels.  The engine uploads them
+        ``starts`` cached ones: work lists of its kernels.  ``have``: names that
+        another part has asked for already and need not be made again.  The engine uploads them
         with the step's other tables; ``ctx.tables[name]`` is the device copy and
         ``ctx.host_tables[name]`` the array.  A name spells out every size the table
         depends on, so parts with equal needs share one table.  Tables depend on

@@ -41,12 +41,12 @@ class PreNormBlock:
     def parameter_bytes(self) -> int:
         return sum(part.parameter_bytes() for part in self.parts())
 
-    def step_tables(self, counts, starts) -> Dict[str, object]:
+    def step_tables(self, counts, starts, have=()) -> Dict[str, object]:
         tables: Dict[str, object] = {}
         for part in self.parts():
             wants = getattr(part, "step_tables", None)
             if wants is not None:
-                for name, arr in wants(counts, starts).items():
+                for name, arr in wants(counts, starts, tuple(have) + tuple(tables)).items():
                     tables.setdefault(name, arr)
         return tables
 

@@ -602,7 +602,7 @@ def test_prompt_attention_on_tcgen05(nq, nkv, window, pad, sms):
     """Head size 64 on the fifth-generation tensor cores: whole prompts and later
     chunks of unequal length in one packed batch, 128 queries per tile, more pages
     than the ring of stages holds, queries inside wider rows (``pad``); tiles cut
-    into chunks of pages and merged (planned as for very many SMs), or whole (as for few)."""
+    into chunks of pages, merged by the last chunk to arrive (planned as for very many SMs), or whole (as for few)."""
     o = ops()
     d = 64
     lengths, new = [70, 1, 200, 64, 333, 129, 1500], [70, 1, 5, 64, 200, 65, 1500]
@@ -622,18 +622,20 @@ def test_prompt_attention_on_tcgen05(nq, nkv, window, pad, sms):
     kc, vc = case.k_cache.bfloat16().to(DEV), case.v_cache.bfloat16().to(DEV)
     starts = [L - c for L, c in zip(lengths, new)]
     first = [sum(new[:i]) for i in range(len(new))]
-    units, merges, slots = o.prefill_tc_plan(new, starts, window, nq, sms)
+    units, slots = o.prefill_tc_plan(new, starts, window, nq, sms)
     assert (slots > 0) == (sms == 1000 and window == 0)  # the long prompt is cut only when SMs would idle
     covered = sorted((int(u[0]), int(u[1]), int(u[2]) & 0xffff) for u in units)
     assert len(set(covered)) == len(covered)
     i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
     partial = torch.full((max(slots, 1) * nq * o.PREFILL_TC_PARTIAL,), float("nan"), device=DEV)
+    tickets = torch.zeros(max(slots, 1) * nq, dtype=torch.int32, device=DEV)
     out = torch.full((n, nq * d), 5.0, dtype=torch.bfloat16, device=DEV)
-    for _ in range(2):
-        o.attention_prefill_tc(qd, stride, kc, vc, i32(units), i32(merges) if slots else None,
-                               partial if slots else None, i32(first), i32(starts), i32(new),
+    for _ in range(2):  # the second launch finds the tickets as the first left them
+        o.attention_prefill_tc(qd, stride, kc, vc, i32(units), partial if slots else None,
+                               tickets if slots else None, i32(first), i32(starts), i32(new),
                                case.table.to(DEV), out, nq, nkv, d, window, 1.0 / math.sqrt(d))
     o.check_status(DEV)
+    assert int(tickets.abs().sum()) == 0
     r = 0
     for s, L in enumerate(lengths):
         full = P.causal_attention(case.q[s], case.k[s], case.v[s].bfloat16().float(), window)

@@ -6,7 +6,7 @@ def test_prompt_attention_plan_cuts_tiles_without_empty_chunks():
     for counts, starts, window in [([2048], [0], 0), ([700, 3], [100, 0], 0), ([5000], [0], 300),
                                    ([129], [64 * 37 + 5], 0)]:
         for sms in (1, 148, 10 ** 6):
-            units, merges, slots = o.prefill_tc_plan(counts, starts, window, 9, sms)
+            units, slots = o.prefill_tc_plan(counts, starts, window, 9, sms)
             per_tile = {}
             for s, q0, z, slot in units.tolist():
                 per_tile.setdefault((s, q0), []).append((z & 0xffff, z >> 16, slot))
@@ -21,4 +21,8 @@ def test_prompt_attention_plan_cuts_tiles_without_empty_chunks():
                 pages = (pos0 + rows - 1) // 64 - lo // 64 + 1
                 assert (n - 1) * (-(-pages // n)) < pages
                 used += n if n > 1 else 0
-            assert used == slots == int(merges[:, 2].sum()) if len(merges) else used == slots == 0
+                if n > 1:  # the chunks of a tile share its first scratch slot; tiles do not overlap
+                    assert len({slot for _, _, slot in chunks}) == 1
+            assert used == slots
+            firsts = sorted((chunks[0][2], chunks[0][1]) for chunks in per_tile.values() if chunks[0][1] > 1)
+            assert all(a[0] + a[1] <= b[0] for a, b in zip(firsts, firsts[1:]))
