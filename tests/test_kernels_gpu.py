@@ -548,6 +548,27 @@ def test_gemm_on_tcgen05(m, n, k):
     o.check_status(DEV)
 
 
+@pytest.mark.parametrize("m,n,k", [(2048, 1536, 64), (1500, 1290, 72), (2100, 1288, 136)])
+def test_gemm_on_tcgen05_wide_tiles(m, n, k):
+    """Enough 128-column tiles for every SM: the 128 x 128 tile shape, with outputs
+    that leave by TMA (rows on 16-byte boundaries) and one that cannot."""
+    o = ops()
+    g = torch.Generator().manual_seed(m + n)
+    a = torch.randn(m, k, generator=g).bfloat16()
+    w = (torch.randn(n, k, generator=g) / math.sqrt(k)).bfloat16()
+    bias = torch.randn(n, generator=g)
+    want = P.linear(a, w, bias)
+    out = torch.full((m, n), 7.0, dtype=torch.bfloat16, device=DEV)
+    o.gemm_tc(a.to(DEV), w.to(DEV), bias.to(DEV), out, o.STORE)
+    close(out, want, "bfloat16", "tcgen05 wide store")
+    base = torch.randn(m, n, generator=g)
+    acc = base.to(DEV).clone()
+    for _ in range(2):
+        o.gemm_tc(a.to(DEV), w.to(DEV), bias.to(DEV), acc, o.ADD_F32)
+    close(acc, base.double() + 2 * want, "float32", "tcgen05 wide add twice")
+    o.check_status(DEV)
+
+
 def test_gemm_on_tcgen05_many_k_blocks_reuse_every_stage():
     o = ops()
     g = torch.Generator().manual_seed(0)
@@ -644,7 +665,7 @@ def test_prompt_attention_on_tcgen05(nq, nkv, window, pad, sms):
 
 
 @pytest.mark.parametrize("m", [17, 128, 200])
-@pytest.mark.parametrize("inter,k", [(100, 72), (1536, 576), (64, 64)])
+@pytest.mark.parametrize("inter,k", [(100, 72), (1536, 576), (64, 64), (196, 136), (200, 64), (392, 72)])
 def test_gemm_on_tcgen05_gated_epilogue(m, inter, k):
     o = ops()
     g = torch.Generator().manual_seed(m + inter)
