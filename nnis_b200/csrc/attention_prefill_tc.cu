@@ -204,6 +204,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     tc_fence_after();
     // S: two buffers of 64 columns; O: one accumulator of 64 columns per half of a page's keys
     const uint32_t tmem_s = tmem_base_s, tmem_o = tmem_base_s + 128;
+    // launched as a programmatic dependent: the queries, and this step's keys and
+    // values, come from the kernel before this one; the set-up above ran under it
+    pdl_wait();
+    pdl_launch_dependents();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -485,14 +489,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 // first launch and left zero, both only when tiles were cut.  Per sequence
 // `seq_first_row`, `seq_start`, `seq_count` as for nnis_attention_prefill_mma.
 // q: [n_tokens, nq * 64] bfloat16 with rows `q_stride` elements apart (a multiple
-// of 8).  Takes head size 64 with 64-key pages; else NNIS_ERR_UNSUPPORTED.
+// of 8).  Takes head size 64 with 64-key pages; else NNIS_ERR_UNSUPPORTED.  `pdl`:
+// launch as a programmatic dependent of the kernel before it on the stream.
 NNIS_API int nnis_attention_prefill_tc(const void* q, int q_stride, int n_tokens, const void* k_cache,
                                        const void* v_cache, long long cache_rows, const int* units,
                                        int n_units, float* partial, unsigned* tickets,
                                        const int* seq_first_row, const int* seq_start,
                                        const int* seq_count, const int* page_table, int table_cols,
                                        void* out, int nq, int nkv, int d, int page_size, int window,
-                                       float scale, int* status, cudaStream_t stream) {
+                                       float scale, int* status, int pdl, cudaStream_t stream) {
     using namespace nnis;
     if (n_units <= 0 || n_tokens <= 0 || nq <= 0 || nkv <= 0 || nq % nkv || table_cols <= 0 ||
         window < 0 || !units || cache_rows <= 0 || q_stride < nq * d || !(scale > 0.f) ||
@@ -510,8 +515,18 @@ NNIS_API int nnis_attention_prefill_tc(const void* q, int q_stride, int n_tokens
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    attn_prefill_tc_kernel<<<dim3(n_units, nq), kTcThreads, smem, stream>>>(
-        mq, mk, mv, units, seq_first_row, seq_start, seq_count, page_table, table_cols, (bf16*)out,
-        partial, tickets, nq, nkv, window, scale, status);
-    NNIS_RETURN_LAUNCH();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_units, nq);
+    cfg.blockDim = dim3(kTcThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    e = cudaLaunchKernelEx(&cfg, attn_prefill_tc_kernel, mq, mk, mv, units, seq_first_row, seq_start,
+                           seq_count, page_table, table_cols, (bf16*)out, partial, tickets, nq, nkv,
+                           window, scale, status);
+    return e == cudaSuccess ? NNIS_OK : (int)e;
 }

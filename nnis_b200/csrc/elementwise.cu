@@ -3,6 +3,7 @@
 // The residual stream is float32 in both engine dtypes; T is the dtype of the
 // matrix-product operands (float or bfloat16).  Statistics, angles and the
 // activation are computed in float32 and rounded once on the store.
+#include "async_copy.cuh"
 #include "common.cuh"
 
 namespace nnis {
@@ -38,6 +39,9 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
                                float eps) {
     __shared__ float partial[32];
     __shared__ float scale_s;
+    // launched as a programmatic dependent: x comes from the kernel before this one
+    pdl_wait();
+    pdl_launch_dependents();
     int r = blockIdx.x;
     const float* in = x + (size_t)(rows ? rows[r] : r) * width;
     float ss = 0.f;
@@ -147,17 +151,28 @@ NNIS_API int nnis_embed(const void* table, int dtype, const int* tokens, float* 
     NNIS_RETURN_LAUNCH();
 }
 
+// `pdl`: launch as a programmatic dependent of the kernel before it on the stream
+// (the kernel waits for that kernel's results itself).
 NNIS_API int nnis_rmsnorm(const float* x, const int* rows, const float* w, void* y, int out_dtype,
-                          int n_rows, int width, float eps, cudaStream_t stream) {
+                          int n_rows, int width, float eps, int pdl, cudaStream_t stream) {
     if (n_rows <= 0 || width <= 0 || !(eps > 0.f)) return NNIS_ERR_ARGUMENT;
-    int threads = width >= 1024 ? 256 : (width >= 256 ? 128 : 32);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_rows);
+    cfg.blockDim = dim3(width >= 1024 ? 256 : (width >= 256 ? 128 : 32));
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    cudaError_t e;
     if (out_dtype == NNIS_DTYPE_F32)
-        rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, rows, w, (float*)y, width, eps);
+        e = cudaLaunchKernelEx(&cfg, rmsnorm_kernel<float>, x, rows, w, (float*)y, width, eps);
     else if (out_dtype == NNIS_DTYPE_BF16)
-        rmsnorm_kernel<bf16><<<n_rows, threads, 0, stream>>>(x, rows, w, (bf16*)y, width, eps);
+        e = cudaLaunchKernelEx(&cfg, rmsnorm_kernel<bf16>, x, rows, w, (bf16*)y, width, eps);
     else
         return NNIS_ERR_UNSUPPORTED;
-    NNIS_RETURN_LAUNCH();
+    return e == cudaSuccess ? NNIS_OK : (int)e;
 }
 
 NNIS_API int nnis_silu_mul(const float* gate_up, void* out, int out_dtype, long long n_rows,

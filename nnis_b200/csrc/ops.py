@@ -97,7 +97,7 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
     else:
         _need(x.shape[0] >= n, "x has fewer rows than out")
     _check(_lib().nnis_rmsnorm(_ptr(x), _ptr(rows), _ptr(weight), _ptr(out), code_of(out.dtype), n,
-                               width, ctypes.c_float(eps), _stream()), "rmsnorm")
+                               width, ctypes.c_float(eps), PDL, _stream()), "rmsnorm")
 
 
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
@@ -512,7 +512,7 @@ def attention_prefill_tc(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, 
         _ptr(partial) if partial is not None else None, _ptr(tickets) if partial is not None else None,
         _ptr(seq_first_row), _ptr(seq_start), _ptr(seq_count), _ptr(page_table), page_table.shape[1],
         _ptr(out), heads, kv_heads, head_dim, page_size, window, ctypes.c_float(scale),
-        _ptr(status_word(out.device)), _stream()),
+        _ptr(status_word(out.device)), PDL, _stream()),
         "attention_prefill_tc")
 
 
