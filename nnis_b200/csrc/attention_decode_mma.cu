@@ -271,54 +271,75 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __r
     if (n_splits == 1) return;
 
     // ---- the slice that arrives last merges all slices of its group ----------------
-    __threadfence();
+    // One thread takes the ticket: its fence, after the barrier, also covers what the
+    // other threads of the CTA wrote before the barrier.
     __syncthreads();
     unsigned* ticket = tickets + ((size_t)n * nkv + hk) * head_tiles + tile;
-    if (tid == 0) is_last = atomicAdd(ticket, 1u) == (unsigned)n_splits - 1u;
+    if (tid == 0) {
+        __threadfence();
+        is_last = atomicAdd(ticket, 1u) == (unsigned)n_splits - 1u;
+    }
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    // Every load of a phase is independent of the others, so each phase costs one
-    // trip to L2: (max, sum) of all slices -> weights in shared memory -> four
-    // interleaved groups of slices summed side by side -> the groups added in order.
-    float* w_s = reinterpret_cast<float*>(smem_raw);            // [n_splits, 16] weights
-    float* l_s = w_s + 64 * 16;                                 // [16] total sums
-    float* g_s = l_s + 16;                                      // [4, 16, D] group sums
-    for (int item = tid; item < n_splits * gcount; item += kMmaWarps * 32) {
-        int sp = item / gcount, row = item % gcount;
-        const float* r = partial + (((size_t)n * nq + hk * G + g0 + row) * n_splits + sp) * (size_t)(D + 2);
-        float mv = r[0], lv = r[1];
-        w_s[sp * 16 + row] = lv > 0.f ? mv : -INFINITY;  // the max, for now
-        w_s[(64 + sp) * 16 + row] = lv;                  // parked beyond the weights
-    }
-    __syncthreads();
-    if (tid < gcount) {
-        float mm = -INFINITY;
-        for (int sp = 0; sp < n_splits; ++sp) mm = fmaxf(mm, w_s[sp * 16 + tid]);
-        float ll = 0.f;
-        for (int sp = 0; sp < n_splits; ++sp) {
-            float mv = w_s[sp * 16 + tid];
-            float f = mv == -INFINITY ? 0.f : exp2f(mv - mm);
-            w_s[sp * 16 + tid] = f;
-            ll += w_s[(64 + sp) * 16 + tid] * f;
-        }
-        l_s[tid] = ll;
-    }
-    __syncthreads();
+    // One trip to L2: a thread owns (row, 8 dims, one of four interleaved groups of
+    // slices) and asks for the maxima, sums and outputs of its slices all at once;
+    // it folds them against the group's own maximum, and the four groups of a row
+    // meet in shared memory, added in the order of the groups.
+    float* g_ml = reinterpret_cast<float*>(smem_raw);           // [4, 16, 2] group maximum and sum
+    float* g_o = g_ml + 4 * 16 * 2;                             // [4, 16, D] group outputs
+    constexpr int kRound = 4;  // slices of a group asked for at once (all of them up to 16 slices)
     for (int item = tid; item < gcount * CH * 4; item += kMmaWarps * 32) {
         int grp4 = item & 3, rc = item >> 2;
         int row = rc / CH, chunk = rc % CH;
-        const float* rec = partial + ((size_t)n * nq + hk * G + g0 + row) * n_splits * (size_t)(D + 2) +
-                           2 + chunk * 8;
+        const float* rec = partial + ((size_t)n * nq + hk * G + g0 + row) * n_splits * (size_t)(D + 2);
+        float mm = -INFINITY, ll = 0.f;
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-        for (int sp = grp4; sp < n_splits; sp += 4) {
-            float f = w_s[sp * 16 + row];
-            const float* r = rec + (size_t)sp * (D + 2);
+        for (int first = grp4; first < n_splits; first += 4 * kRound) {
+            float mv[kRound], lv[kRound];
+            float2 ov[kRound][4];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) acc[e] = fmaf(r[e], f, acc[e]);
+            for (int i = 0; i < kRound; ++i) {
+                int sp = first + 4 * i;
+                mv[i] = -INFINITY;
+                lv[i] = 0.f;
+                if (sp < n_splits) {
+                    const float* r = rec + (size_t)sp * (D + 2);
+                    mv[i] = __ldcg(r);
+                    lv[i] = __ldcg(r + 1);
+                    const float2* o2 = reinterpret_cast<const float2*>(r + 2 + chunk * 8);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) ov[i][e] = __ldcg(o2 + e);
+                }
+            }
+            float m_new = mm;
+#pragma unroll
+            for (int i = 0; i < kRound; ++i)
+                if (lv[i] > 0.f) m_new = fmaxf(m_new, mv[i]);
+            if (m_new == -INFINITY) continue;
+            const float keep = mm == -INFINITY ? 0.f : exp2f(mm - m_new);
+            ll *= keep;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[e] *= keep;
+            mm = m_new;
+#pragma unroll
+            for (int i = 0; i < kRound; ++i) {
+                if (lv[i] > 0.f) {
+                    float f = exp2f(mv[i] - mm);
+                    ll = fmaf(lv[i], f, ll);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        acc[2 * e] = fmaf(ov[i][e].x, f, acc[2 * e]);
+                        acc[2 * e + 1] = fmaf(ov[i][e].y, f, acc[2 * e + 1]);
+                    }
+                }
+            }
         }
-        float* dst = g_s + ((size_t)grp4 * 16 + row) * D + chunk * 8;
+        if (chunk == 0) {
+            g_ml[(grp4 * 16 + row) * 2] = mm;
+            g_ml[(grp4 * 16 + row) * 2 + 1] = ll;
+        }
+        float* dst = g_o + ((size_t)grp4 * 16 + row) * D + chunk * 8;
 #pragma unroll
         for (int e = 0; e < 8; ++e) dst[e] = acc[e];
     }
@@ -326,13 +347,22 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __r
     for (int item = tid; item < gcount * CH; item += kMmaWarps * 32) {
         int row = item / CH, chunk = item % CH;
         int hq = hk * G + g0 + row;
-        float ll = l_s[row];
+        float mm = -INFINITY;
+#pragma unroll
+        for (int g4 = 0; g4 < 4; ++g4) mm = fmaxf(mm, g_ml[(g4 * 16 + row) * 2]);
+        float f[4], ll = 0.f;
+#pragma unroll
+        for (int g4 = 0; g4 < 4; ++g4) {
+            float gm = g_ml[(g4 * 16 + row) * 2];
+            f[g4] = gm == -INFINITY ? 0.f : exp2f(gm - mm);
+            ll = fmaf(g_ml[(g4 * 16 + row) * 2 + 1], f[g4], ll);
+        }
         float inv = ll > 0.f ? 1.0f / ll : 0.f;
         float acc[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-            const float* src = g_s + (size_t)row * D + chunk * 8 + e;
-            acc[e] = ((src[0] + src[16 * D]) + src[32 * D]) + src[48 * D];
+            const float* src = g_o + (size_t)row * D + chunk * 8 + e;
+            acc[e] = ((src[0] * f[0] + src[16 * D] * f[1]) + src[32 * D] * f[2]) + src[48 * D] * f[3];
         }
         bf16* dst = out + ((size_t)n * nq + hq) * D + chunk * 8;
         store4(dst, make_float4(acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv));
@@ -349,7 +379,7 @@ static int launch_mma(dim3 grid, bool pdl, cudaStream_t stream, const bf16* q, i
     size_t stage_bytes = 2 * (size_t)kPage * D * sizeof(bf16);
     int stages = D <= 64 ? 4 : 3;
     size_t smem = 16 * D * sizeof(bf16) + stages * stage_bytes;
-    size_t merge_bytes = ((size_t)kMmaWarps * 16 * D + 2 * 64 * 16 + 16) * sizeof(float);
+    size_t merge_bytes = ((size_t)kMmaWarps * 16 * D + 4 * 16 * 2) * sizeof(float);
     if (smem < merge_bytes) smem = merge_bytes;
     auto kernel = attn_decode_mma_kernel<D>;
     if (smem > 48 * 1024) {
