@@ -136,6 +136,19 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ t
 
 using namespace nnis;
 
+// A copy in either direction on the stream (pinned host memory on the host side),
+// for the few bytes a decode step exchanges with the host: one call, no allocation.
+NNIS_API int nnis_copy_async(void* dst, const void* src, long long bytes, cudaStream_t stream) {
+    if (!dst || !src || bytes <= 0) return NNIS_ERR_ARGUMENT;
+    cudaError_t e = cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDefault, stream);
+    return e == cudaSuccess ? NNIS_OK : (int)e;
+}
+
+NNIS_API int nnis_stream_synchronize(cudaStream_t stream) {
+    cudaError_t e = cudaStreamSynchronize(stream);
+    return e == cudaSuccess ? NNIS_OK : (int)e;
+}
+
 NNIS_API int nnis_embed(const void* table, int dtype, const int* tokens, float* hidden,
                         int n_tokens, int width, int vocab, int* status, cudaStream_t stream) {
     if (n_tokens <= 0 || width <= 0 || vocab <= 0 || !status) return NNIS_ERR_ARGUMENT;

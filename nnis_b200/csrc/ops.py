@@ -46,7 +46,14 @@ def _check(code: int, what: str, kernels: int = 1) -> None:
     raise KernelError(f"{what}: CUDA error {code} at launch")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> ctypes.c_void_p:
+    """The current stream's handle (the raw getter is some ten microseconds
+    cheaper than building a Stream object, and a decode step asks several times)."""
+    if _raw_stream is not None:
+        return ctypes.c_void_p(_raw_stream(torch.cuda.current_device()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -83,6 +90,24 @@ def embed(table: torch.Tensor, tokens: torch.Tensor, hidden: torch.Tensor,
     _need(status.dtype == torch.int32, "status: int32")
     _check(_lib().nnis_embed(_ptr(table), code_of(table.dtype), _ptr(tokens), _ptr(hidden), n, width,
                              table.shape[0], _ptr(status), _stream()), "embed")
+
+
+def copy_async(dst: torch.Tensor, src: torch.Tensor) -> None:
+    """dst <- src on the current stream, both contiguous and equally large; the host
+    side of the pair must be pinned memory for the copy to be asynchronous."""
+    _need(dst.is_contiguous() and src.is_contiguous(), "copy_async: contiguous tensors")
+    nbytes = src.numel() * src.element_size()
+    _need(nbytes == dst.numel() * dst.element_size(), "copy_async: sizes differ")
+    code = _lib().nnis_copy_async(_ptr(dst), _ptr(src), ctypes.c_longlong(nbytes), _stream())
+    if code != 0:
+        raise KernelError(f"copy_async: CUDA error {code}")
+
+
+def stream_synchronize() -> None:
+    """Wait for the current stream (what ``Stream.synchronize`` does, without the object)."""
+    code = _lib().nnis_stream_synchronize(_stream())
+    if code != 0:
+        raise KernelError(f"stream_synchronize: CUDA error {code}")
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,

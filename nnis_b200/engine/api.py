@@ -20,6 +20,7 @@ import torch
 from ..sampling import SamplingConfig
 from ..sampling import device as device_sampling
 from ..cache import PAGE_SIZE
+from ..csrc import ops
 from .decode import GraphDecoder
 from .engine import Engine, SequenceStep, StepError
 from .generate import (DEFAULT_MAX_NEW_TOKENS, GenerationConfig, GenerationRequest,
@@ -41,6 +42,8 @@ class EngineBackend:
         self._pinned = None
         self._picked = None
         self._picked_for = None
+        self._pick_host = None
+        self._pick_np = None
         self.h2d_bytes = 0  # counted from the tensors copied, for measurements
         self.d2h_bytes = 0
         parts = [p for b in engine.model.blocks for p in b.parts()]
@@ -79,9 +82,15 @@ class EngineBackend:
         return dec.logits[:len(batch)] if need_logits else None
 
     def greedy(self, logits: Optional[torch.Tensor]) -> List[int]:
-        if self._picked is not None:
-            self.d2h_bytes += self._picked.numel() * 4
-            return self._picked.tolist()  # the graph has picked already
+        if self._picked is not None:  # the graph has picked already
+            n = self._picked.numel()
+            self.d2h_bytes += n * 4
+            if self._pick_host is None or self._pick_host.numel() < n:
+                self._pick_host = torch.empty(max(n, self.max_rows), dtype=torch.int32, pin_memory=True)
+                self._pick_np = self._pick_host.numpy()
+            ops.copy_async(self._pick_host[:n], self._picked)
+            ops.stream_synchronize()
+            return self._pick_np[:n].tolist()
         out = self.engine.workspace.get("picked", (logits.shape[0],), torch.int32)
         device_sampling.greedy(logits, out)
         self.d2h_bytes += out.numel() * 4

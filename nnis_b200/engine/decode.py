@@ -172,7 +172,7 @@ class GraphDecoder:
                     line[:count] = table[:count]
                     line[count:] = -1
                 mirror[r] = (table, count, dropped)
-        self.state.copy_(self.host_state, non_blocking=True)
+        ops.copy_async(self.state, self.host_state)
         self._host_state_free.record()
         for g in range(len(self.tables)):  # the partial-update path starts from scratch next time
             self.host_tables[g] = [[None] * cols for _ in range(rows)]
