@@ -61,6 +61,45 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
     for (int i = threadIdx.x; i < width; i += blockDim.x) out[i] = from_float<T>((in[i] * s) * w[i]);
 }
 
+// The same for many rows of moderate width (a multiple of 4, at most 1,024): a
+// warp per row, the row kept in registers between the sum and the scaling, no
+// barrier; eight rows per CTA.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rmsnorm_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                    const float* __restrict__ w, T* __restrict__ y, int n_rows, int width, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31, r = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (r >= n_rows) return;
+    const float4* in = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * width);
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+    const int n4 = width >> 2;
+    float4 v[8];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        int c = lane + 32 * j;
+        v[j] = c < n4 ? in[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        ss = fmaf(v[j].x, v[j].x, ss);
+        ss = fmaf(v[j].y, v[j].y, ss);
+        ss = fmaf(v[j].z, v[j].z, ss);
+        ss = fmaf(v[j].w, v[j].w, ss);
+    }
+    ss = warp_sum(ss);
+    const float s = 1.0f / sqrtf(ss * (1.0f / (float)width) + eps);
+    T* out = y + (size_t)r * width;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        int c = lane + 32 * j;
+        if (c < n4) {
+            float4 g = w4[c];
+            store4(out + c * 4, make_float4((v[j].x * s) * g.x, (v[j].y * s) * g.y, (v[j].z * s) * g.z,
+                                            (v[j].w * s) * g.w));
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------
 // out[n, i] = silu(g[n, i]) * u[n, i]; gate and up are the two halves of one
 // float32 row [2 * inter].  NNIS: crates/nnis-model/src/fused_swiglu.rs:14-27.
@@ -169,9 +208,12 @@ NNIS_API int nnis_embed(const void* table, int dtype, const int* tokens, float* 
 NNIS_API int nnis_rmsnorm(const float* x, const int* rows, const float* w, void* y, int out_dtype,
                           int n_rows, int width, float eps, int pdl, cudaStream_t stream) {
     if (n_rows <= 0 || width <= 0 || !(eps > 0.f)) return NNIS_ERR_ARGUMENT;
+    // many rows of moderate width on 16-byte boundaries: a warp per row
+    const bool by_rows = n_rows >= 64 && width % 4 == 0 && width <= 1024 &&
+                         ((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) % 16 == 0;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(n_rows);
-    cfg.blockDim = dim3(width >= 1024 ? 256 : (width >= 256 ? 128 : 32));
+    cfg.gridDim = dim3(by_rows ? (n_rows + 7) / 8 : n_rows);
+    cfg.blockDim = dim3(by_rows ? 256 : (width >= 1024 ? 256 : (width >= 256 ? 128 : 32)));
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -180,9 +222,11 @@ NNIS_API int nnis_rmsnorm(const float* x, const int* rows, const float* w, void*
     cfg.numAttrs = pdl ? 1 : 0;
     cudaError_t e;
     if (out_dtype == NNIS_DTYPE_F32)
-        e = cudaLaunchKernelEx(&cfg, rmsnorm_kernel<float>, x, rows, w, (float*)y, width, eps);
+        e = by_rows ? cudaLaunchKernelEx(&cfg, rmsnorm_rows_kernel<float>, x, rows, w, (float*)y, n_rows, width, eps)
+                    : cudaLaunchKernelEx(&cfg, rmsnorm_kernel<float>, x, rows, w, (float*)y, width, eps);
     else if (out_dtype == NNIS_DTYPE_BF16)
-        e = cudaLaunchKernelEx(&cfg, rmsnorm_kernel<bf16>, x, rows, w, (bf16*)y, width, eps);
+        e = by_rows ? cudaLaunchKernelEx(&cfg, rmsnorm_rows_kernel<bf16>, x, rows, w, (bf16*)y, n_rows, width, eps)
+                    : cudaLaunchKernelEx(&cfg, rmsnorm_kernel<bf16>, x, rows, w, (bf16*)y, width, eps);
     else
         return NNIS_ERR_UNSUPPORTED;
     return e == cudaSuccess ? NNIS_OK : (int)e;

@@ -65,6 +65,24 @@ def test_rmsnorm(dtype, width):
 
 
 @pytest.mark.parametrize("dtype", list(DT))
+@pytest.mark.parametrize("width", [72, 576, 1000, 1024, 1028, 578])
+def test_rmsnorm_of_many_rows(dtype, width):
+    """Enough rows for the warp-per-row kernel (widths that are multiples of 4 up to
+    1,024) and widths beside it; rows picked through an index too."""
+    o = ops()
+    g = torch.Generator().manual_seed(width)
+    x = torch.randn(301, width, generator=g) * 2
+    w = 1 + 0.1 * torch.randn(width, generator=g)
+    out = torch.full((301, width), 9.0, dtype=DT[dtype], device=DEV)
+    o.rmsnorm(x.to(DEV), w.to(DEV), 1e-6, out)
+    close(out, P.rms_norm(x, w, 1e-6), dtype, "rmsnorm many rows")
+    rows = torch.randperm(301, generator=g)[:70].to(torch.int32)
+    out2 = torch.empty(70, width, dtype=DT[dtype], device=DEV)
+    o.rmsnorm(x.to(DEV), w.to(DEV), 1e-6, out2, rows.to(DEV))
+    close(out2, P.rms_norm(x[rows.long()], w, 1e-6), dtype, "rmsnorm picked rows")
+
+
+@pytest.mark.parametrize("dtype", list(DT))
 def test_silu_mul(dtype):
     o = ops()
     gu = torch.randn(7, 2 * 45) * 4
