@@ -464,11 +464,12 @@ def prefill_tc_plan(counts, starts, window: int, heads: int, sms: int):
     ``counts`` tokens after ``starts`` cached ones.
 
     A tile is 128 queries of one sequence; its keys are the pages from its first
-    query's window start to its last query.  Tiles are cut into chunks of pages
-    while there would be CTAs (units x heads) for fewer than one and a third of the
-    SMs: chunks of 32 pages if that gives enough, else of 16, else of 8 (a chunk
-    costs a CTA's start and end, a trip of its rows through scratch and, for the
-    last one of a tile, the merge).  Returns ``units`` int32 [n, 4] (sequence,
+    query's window start to its last query.  Two CTAs share an SM, so tiles are cut
+    into chunks of pages while there would be fewer CTAs (units x heads) than 1.7
+    per SM: the longest chunk of 32, 24, 16 or 12 pages that gives as many, else 8
+    (a chunk costs a CTA's start and end, a trip of its rows through scratch and,
+    for the last one of a tile, the merge; measured on one prompt of 1,024 / 2,048 /
+    4,096 tokens and 9 heads the best lengths were 8 / 12 / none).  Returns ``units`` int32 [n, 4] (sequence,
     first query, chunk | chunks << 16, first scratch slot), longest first, and the
     number of scratch slots."""
     import numpy as np
@@ -480,8 +481,8 @@ def prefill_tc_plan(counts, starts, window: int, heads: int, sms: int):
             lo = max(0, pos0 - window + 1) if window > 0 else 0
             tiles.append((i, q0, (pos0 + rows - 1) // 64 - lo // 64 + 1))
     chunk_pages = 8
-    for cand in (1 << 30, 32, 16):
-        if 3 * sum(-(-p // cand) for _, _, p in tiles) * heads >= 4 * sms:
+    for cand in (1 << 30, 32, 24, 16, 12):
+        if 10 * sum(-(-p // cand) for _, _, p in tiles) * heads >= 17 * sms:
             chunk_pages = cand
             break
     units, slot = [], 0
