@@ -4,7 +4,7 @@
 // One CTA computes a 128 x BN tile (BN = 64 or 128).  Its six warps have fixed
 // roles:
 //   warp 0  one lane issues TMA tile loads (cp.async.bulk.tensor, 128-byte
-//           swizzle) of A, one or two slices of 64 columns of K per stage, into a
+//           swizzle) of A, one, two or four slices of 64 columns of K per stage, into a
 //           ring of shared memory stages, each guarded by a "full" and an "empty"
 //           mbarrier; lane 0 of warp 2 does the same for W;
 //   warp 1  allocates tensor memory, and one lane issues tcgen05.mma
@@ -448,7 +448,7 @@ NNIS_API int nnis_gemm_tc(const void* A, const void* W, const float* bias, void*
     // than SMs a CTA takes about 192 KB instead, which keeps a microsecond of loads
     // in flight (a stage comes back about 1,000 cycles after its load is issued).
 #define NNIS_GEMM_TC64(MODE, CTAS) \
-    return (CTAS) <= sms ? launch_gemm_tc<64, 4, MODE, 2>(ma, mw, mo, g, pdl != 0, stream) \
+    return (CTAS) <= sms ? launch_gemm_tc<64, 2, MODE, 4>(ma, mw, mo, g, pdl != 0, stream) \
                          : launch_gemm_tc<64, 2, MODE, 2>(ma, mw, mo, g, pdl != 0, stream)
 #define NNIS_GEMM_TC128(BN, MODE, CTAS) \
     return (CTAS) <= sms ? launch_gemm_tc<BN, 3, MODE, 2>(ma, mw, mo, g, pdl != 0, stream) \
