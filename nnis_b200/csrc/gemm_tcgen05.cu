@@ -467,7 +467,7 @@ NNIS_API int nnis_gemm_tc(const void* A, const void* W, const float* bias, void*
         // wide outputs: 192 gate and 192 up columns per CTA, which has its SM alone
         // (384 columns of tensor memory, 64 KB a stage); products of N = 192 run at
         // the tensor cores' full rate, those of N = 64 at two thirds of it
-        const bool fat = N / 2 > 128;
+        const bool fat = N / 2 > 128 && 4 * m_tiles * ((N / 2 + 191) / 192) >= sms;  // enough fat tiles for a quarter of the SMs
         if (!make_map(&ma, A, M, K, kBM) || !make_map(&mw, W, N, K, fat ? 192 : 64)) return NNIS_ERR_UNSUPPORTED;
         g.out_by_tma = (N / 2) % 8 == 0 && make_map(&mo, C, M, N / 2, kBM);
         if (!g.out_by_tma) mo = ma;

@@ -263,6 +263,13 @@ def sm_count(device) -> int:
     return _sm_count[key]
 
 
+# Most rows for which the parts of a decode step choose the decode projection
+# kernel; with more rows (the fourth tile of 16) a norm kernel and the tcgen05 product
+# are faster, because every CTA of the projection kernel normalises and holds all
+# rows for itself.
+DECODE_GEMV_ROWS = int(__import__("os").environ.get("NNIS_DECODE_GEMV_ROWS", "48"))
+
+
 def gemv_takes(m: int, n: int, k: int, epilogue: int = EPI_STORE, device=None) -> bool:
     """Whether the decode projection kernel runs this shape (else the general
     kernels): at most 64 rows, K in steps of 16, N in steps of 8, operands that fit

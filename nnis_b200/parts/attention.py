@@ -109,11 +109,11 @@ class Attention(Part):
     # -- run --------------------------------------------------------------
     def _decode_kernels(self, ctx, n: int) -> bool:
         """The fused bfloat16 decode kernel for q, k, v: few rows, one token each."""
-        return (self.dtype == torch.bfloat16 and ctx.decode
+        return (self.dtype == torch.bfloat16 and ctx.decode and n <= ops.DECODE_GEMV_ROWS
                 and ops.gemv_takes(n, self.w_qkv.shape[0], self.hidden, ops.EPI_QKV, self.device))
 
     def _fused_out(self, ctx, n: int) -> bool:
-        return (self.dtype == torch.bfloat16 and ctx.decode
+        return (self.dtype == torch.bfloat16 and ctx.decode and n <= ops.DECODE_GEMV_ROWS
                 and ops.gemv_takes(n, self.hidden, self.heads * self.head_dim, ops.EPI_ADD_F32,
                                    self.device))
 

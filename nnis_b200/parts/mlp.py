@@ -58,11 +58,11 @@ class GatedMLP(Part):
 
     def _fused_gate_up(self, ctx, n: int) -> bool:
         """The fused bfloat16 decode kernel for gate/up (few rows, one token each)."""
-        return (self.dtype == torch.bfloat16 and ctx.decode
+        return (self.dtype == torch.bfloat16 and ctx.decode and n <= ops.DECODE_GEMV_ROWS
                 and ops.gemv_takes(n, 2 * self.inter, self.hidden, ops.EPI_GATED, self.device))
 
     def _fused_down(self, ctx, n: int) -> bool:
-        return (self.dtype == torch.bfloat16 and ctx.decode
+        return (self.dtype == torch.bfloat16 and ctx.decode and n <= ops.DECODE_GEMV_ROWS
                 and ops.gemv_takes(n, self.hidden, self.inter, ops.EPI_ADD_F32, self.device))
 
     def fuses_norm(self, norm, ctx, n: int) -> bool:
