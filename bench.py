@@ -247,6 +247,20 @@ def main() -> int:
             points = {"decode_b1": p1["tok_s"], "decode_b64": p64["tok_s"],
                       "decode_b1_hbm_frac": p1["gbs"] / pk["hbm_gbs"],
                       "decode_b64_hbm_frac": p64["gbs"] / pk["hbm_gbs"]}
+            # the regime of the reference's own published runs: one 3-token prompt, 32
+            # greedy tokens, wall clock around generate() (median of 5 after 2 warm-ups)
+            short = [rng.randrange(vocab) for _ in range(3)]
+            walls = []
+            for i in range(7):
+                torch.cuda.synchronize()
+                t_a = time.perf_counter()
+                out = llm.generate([short], max_new_tokens=32, stop_token_ids=())
+                torch.cuda.synchronize()
+                if i >= 2:
+                    walls.append(time.perf_counter() - t_a)
+                assert out[0].ok and len(out[0].token_ids) == 32
+            points["generate_3_plus_32_ms"] = sorted(walls)[len(walls) // 2] * 1e3
+            points["generate_3_plus_32_tok_s"] = 32 / sorted(walls)[len(walls) // 2]
         clocks.stop()
 
     line = {
