@@ -76,3 +76,29 @@ def test_long_prompts_in_chunks_with_and_without_a_window(dtype):
     engine.release_slot(slot["a"])
     engine.check_status()
     engine.cache.check()
+
+
+def test_a_recurring_long_prompt_is_replayed_from_a_graph_with_cut_tiles():
+    """The same prompt shape three times on fresh slots: run as it comes, captured,
+    replayed.  With one 1,500-token prompt the tcgen05 attention cuts its tiles into
+    chunks, whose scratch and tickets live in the captured step's own buffers."""
+    from nnis_b200.config import config_from_dict
+    from nnis_b200.engine import Engine, SequenceStep
+    from nnis_b200.engine.model import DecoderModel
+    from nnis_b200.weights import random_tensors
+    spec = config_from_dict(CFG).to_spec()
+    tensors = random_tensors(DecoderModel.weight_specs_of(spec), seed=65, std=1.0, norm_std=0.1,
+                             std_by_fan_in=True)
+    w = {k: v.to(torch.bfloat16).float() for k, v in tensors.items()}
+    engine = Engine.from_spec(spec, tensors, dtype="bfloat16", max_tokens=64 * 60, max_slots=2)
+    rng = random.Random(9)
+    picks = [0, 700, 1499]
+    for round_ in range(4):
+        tokens = [rng.randrange(300) for _ in range(1500)]
+        want = P.forward(CFG, w, tokens, True)
+        slot = engine.acquire_slot()
+        got = engine.step([SequenceStep(slot, tokens, picks)])
+        check_logits(got.cpu().numpy(), want[picks], "bfloat16", f"round {round_}")
+        engine.release_slot(slot)
+    assert any(e["graph"] is not None for e in engine._step_graphs.values())
+    engine.check_status()
