@@ -102,3 +102,54 @@ def test_a_recurring_long_prompt_is_replayed_from_a_graph_with_cut_tiles():
         engine.release_slot(slot)
     assert any(e["graph"] is not None for e in engine._step_graphs.values())
     engine.check_status()
+
+
+def test_a_decode_step_of_fifty_sequences_takes_the_product_kernels_and_matches():
+    """More than 48 rows in a decode step: norm kernel and tcgen05 products instead of
+    the decode projection kernel (bfloat16, head size 64), rows of unequal context."""
+    from nnis_b200.config import config_from_dict
+    from nnis_b200.engine import Engine, SequenceStep
+    from nnis_b200.engine.model import DecoderModel
+    from nnis_b200.weights import random_tensors
+    spec = config_from_dict(CFG).to_spec()
+    tensors = random_tensors(DecoderModel.weight_specs_of(spec), seed=66, std=1.0, norm_std=0.1,
+                             std_by_fan_in=True)
+    w = {k: v.to(torch.bfloat16).float() for k, v in tensors.items()}
+    engine = Engine.from_spec(spec, tensors, dtype="bfloat16", max_tokens=64 * 120, max_slots=50)
+    rng = random.Random(11)
+    seqs = [[rng.randrange(300) for _ in range(rng.choice([2, 5, 17, 64, 65, 130]) + 2)] for _ in range(50)]
+    slots = [engine.acquire_slot() for _ in seqs]
+    engine.step([SequenceStep(s, t[:-2], []) for s, t in zip(slots, seqs)])
+    want = [P.forward(CFG, w, t, True) for t in seqs]
+    for back in (2, 1):  # two decode steps of all fifty
+        got = engine.step([SequenceStep(s, [t[-back]], [0]) for s, t in zip(slots, seqs)])
+        check_logits(got.cpu().numpy(), torch.stack([x[len(t) - back] for x, t in zip(want, seqs)]),
+                     "bfloat16", f"decode step {3 - back} of fifty")
+    for s in slots:
+        engine.release_slot(s)
+    engine.check_status()
+
+
+def test_generation_of_fifty_prompts_agrees_with_stepping_the_engine():
+    """Through LLM.generate the fifty rows run in the 64-row decode graph (padding rows
+    beside them); the tokens must be those of plain greedy stepping with the same kernels."""
+    import tempfile
+    from nnis_b200 import LLM
+    from nnis_b200.engine import SequenceStep
+    from nnis_b200.weights import write_random_model
+    with tempfile.TemporaryDirectory() as d:
+        write_random_model(CFG, 67, d, std=1.0, norm_std=0.1, std_by_fan_in=True)
+        llm = LLM(d, dtype="bfloat16", max_tokens=64 * 120, max_batch=64)
+        rng = random.Random(12)
+        prompts = [[rng.randrange(300) for _ in range(rng.choice([1, 3, 8, 40]))] for _ in range(50)]
+        out = llm.generate(prompts, max_new_tokens=5, stop_token_ids=())
+        engine = llm.engine
+        for i in (0, 7, 23, 49):
+            slot = engine.acquire_slot()
+            logits = engine.step([SequenceStep(slot, prompts[i], [len(prompts[i]) - 1])])
+            toks = []
+            for _ in range(5):
+                toks.append(int(logits[0].argmax()))
+                logits = engine.step([SequenceStep(slot, [toks[-1]], [0])])
+            engine.release_slot(slot)
+            assert out[i].ok and list(out[i].token_ids) == toks, (i, out[i].token_ids, toks)
