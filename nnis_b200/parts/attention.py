@@ -100,7 +100,7 @@ class Attention(Part):
                 self.head_dim, PAGE_SIZE, self.heads * self.head_dim):
             return {}
         name = self._tc_plan_name()
-        if name + "/units" in have:
+        if name + "/units" in have or not ops.prefill_tc_pays(counts, starts, self.window):
             return {}
         units, slots = ops.prefill_tc_plan(counts, starts, self.window, self.heads,
                                            ops.sm_count(self.device))
