@@ -1,0 +1,56 @@
+"""Seeded random Llama shapes with head sizes 64 and 128 (the sizes the tensor-core
+kernels take) through the engine against the plain implementation: odd widths,
+grouped / multi-head / multi-query attention, biases, tied and separate heads,
+prompts of unequal length in one step, then single tokens."""
+import random
+
+import pytest
+import torch
+
+import plain_llama as P
+from helpers import check_logits
+
+pytestmark = pytest.mark.gpu
+
+
+def random_config(rng):
+    d = rng.choice([64, 64, 128])
+    nkv = rng.choice([1, 2, 3, 5])
+    nq = nkv * rng.choice([1, 2, 3])
+    return dict(architectures=["LlamaForCausalLM"], model_type="llama", vocab_size=rng.choice([300, 515, 1000]),
+                hidden_size=rng.choice([72, 200, 256, 328, 576]), intermediate_size=rng.choice([96, 200, 392, 1000]),
+                num_hidden_layers=2, num_attention_heads=nq, num_key_value_heads=nkv, head_dim=d,
+                max_position_embeddings=2048, rms_norm_eps=rng.choice([1e-5, 1e-6]),
+                rope_theta=rng.choice([10000.0, 100000.0]), hidden_act="silu",
+                tie_word_embeddings=rng.choice([True, False]), attention_bias=rng.choice([True, False]),
+                torch_dtype="float32")
+
+
+@pytest.mark.parametrize("seed", [11, 12, 13, 14, 15, 16])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_random_shape(seed, dtype):
+    from nnis_b200.config import config_from_dict
+    from nnis_b200.engine import Engine, SequenceStep
+    from nnis_b200.engine.model import DecoderModel
+    from nnis_b200.weights import random_tensors
+    rng = random.Random(seed)
+    cfg = random_config(rng)
+    spec = config_from_dict(cfg).to_spec()
+    tensors = random_tensors(DecoderModel.weight_specs_of(spec), seed=seed, std=1.0, norm_std=0.1,
+                             std_by_fan_in=True)
+    bf = dtype == "bfloat16"
+    w = {k: (v.to(torch.bfloat16).float() if bf else v.float()) for k, v in tensors.items()}
+    engine = Engine.from_spec(spec, tensors, dtype=dtype, max_tokens=64 * 40, max_slots=4)
+    lens = [rng.choice([3, 64, 129, 300, 700]), rng.choice([1, 65, 200])]
+    seqs = [[rng.randrange(cfg["vocab_size"]) for _ in range(n + 3)] for n in lens]
+    want = [P.forward(cfg, w, t, bf) for t in seqs]
+    slots = [engine.acquire_slot() for _ in seqs]
+    picks = [[0, n - 1] for n in lens]
+    got = engine.step([SequenceStep(s, t[:n], p) for s, t, n, p in zip(slots, seqs, lens, picks)])
+    check_logits(got.cpu().numpy(), torch.cat([x[p] for x, p in zip(want, picks)]), dtype, f"prompts of {cfg}")
+    for k in range(3):
+        got = engine.step([SequenceStep(s, [t[n + k]], [0]) for s, t, n in zip(slots, seqs, lens)])
+        check_logits(got.cpu().numpy(), torch.stack([x[n + k] for x, n in zip(want, lens)]), dtype,
+                     f"token {k} of {cfg}")
+    engine.check_status()
+    engine.cache.check()
