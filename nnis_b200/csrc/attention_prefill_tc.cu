@@ -179,6 +179,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int n_pages = min(per_chunk, tile_pages - chunk * per_chunk);  // >= 1 by the host's plan
     const int* table = page_table + (size_t)seq * table_cols;
 
+    if (threadIdx.x == 64) {
+        prefetch_tensormap(&map_q);
+        prefetch_tensormap(&map_k);
+        prefetch_tensormap(&map_v);
+    }
     if (threadIdx.x == 0) {
         mbar_init(&q_full, 1);
         for (int s = 0; s < kTcStages; ++s) {

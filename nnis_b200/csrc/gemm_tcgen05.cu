@@ -95,6 +95,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int k_blocks = (k_slices + KSUB - 1) / KSUB;
     const int inter = g.N >> 1;  // GEMM_GATED: columns of the output
 
+    if (threadIdx.x == 32) {
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_w);
+        if (g.out_by_tma) prefetch_tensormap(&map_out);
+    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&full_bar[s], 2);   // the two loaders
