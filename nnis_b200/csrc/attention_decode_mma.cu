@@ -372,15 +372,37 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __r
 }
 
 template <int D>
+constexpr int mma_stages() { return D <= 64 ? 4 : 3; }
+template <int D>
+constexpr size_t mma_smem_bytes() {
+    size_t stage_bytes = 2 * (size_t)kPage * D * sizeof(bf16);
+    size_t smem = 16 * D * sizeof(bf16) + mma_stages<D>() * stage_bytes;
+    size_t merge_bytes = ((size_t)kMmaWarps * 16 * D + 4 * 16 * 2) * sizeof(float);
+    return smem < merge_bytes ? merge_bytes : smem;
+}
+
+template <int D>
+static int resident_ctas_per_sm() {
+    auto kernel = attn_decode_mma_kernel<D>;
+    const size_t smem = mma_smem_bytes<D>();
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+            cudaSuccess)
+        return 0;
+    int blocks = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, kernel, kMmaWarps * 32, smem) !=
+        cudaSuccess)
+        return 0;
+    return blocks;
+}
+
+template <int D>
 static int launch_mma(dim3 grid, bool pdl, cudaStream_t stream, const bf16* q, int q_stride,
                       const bf16* k, const bf16* v, const int* pos, const int* seq, const int* table,
                       int cols, bf16* out, float* partial, unsigned* tickets, int nq, int nkv,
                       int window, float scale, int n_splits, int head_tiles) {
-    size_t stage_bytes = 2 * (size_t)kPage * D * sizeof(bf16);
-    int stages = D <= 64 ? 4 : 3;
-    size_t smem = 16 * D * sizeof(bf16) + stages * stage_bytes;
-    size_t merge_bytes = ((size_t)kMmaWarps * 16 * D + 4 * 16 * 2) * sizeof(float);
-    if (smem < merge_bytes) smem = merge_bytes;
+    const int stages = mma_stages<D>();
+    const size_t smem = mma_smem_bytes<D>();
     auto kernel = attn_decode_mma_kernel<D>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -404,6 +426,16 @@ static int launch_mma(dim3 grid, bool pdl, cudaStream_t stream, const bf16* q, i
 }
 
 }  // namespace nnis
+
+// How many CTAs of the kernel for head size `d` one SM holds at a time (0: head
+// size not taken, or the query failed).  The host cuts the key range so that all
+// CTAs of a step are resident together: a second, partly filled wave costs more
+// than shorter slices gain.
+NNIS_API int nnis_attention_decode_mma_ctas_per_sm(int d) {
+    if (d == 64) return nnis::resident_ctas_per_sm<64>();
+    if (d == 128) return nnis::resident_ctas_per_sm<128>();
+    return 0;
+}
 
 // Takes head sizes 64 and 128 with 64-key pages; anything else is refused with
 // NNIS_ERR_UNSUPPORTED and goes to the general decode kernel.  Scratch: with

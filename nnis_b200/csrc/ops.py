@@ -399,6 +399,20 @@ def attention_decode_mma_takes(head_dim: int, page_size: int) -> bool:
     return head_dim in (64, 128) and page_size == 64
 
 
+_decode_mma_resident: dict = {}
+
+
+def attention_decode_mma_resident(head_dim: int, device) -> int:
+    """How many CTAs of the tensor-core decode kernel the device holds at once."""
+    key = (head_dim, torch.device(device).index or 0)
+    if key not in _decode_mma_resident:
+        per_sm = int(_lib().nnis_attention_decode_mma_ctas_per_sm(int(head_dim)))
+        if per_sm <= 0:
+            raise RuntimeError(f"decode attention kernel for head size {head_dim}: occupancy query failed")
+        _decode_mma_resident[key] = per_sm * sm_count(device)
+    return _decode_mma_resident[key]
+
+
 def attention_decode_mma(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor,
                          token_pos: torch.Tensor, token_seq: torch.Tensor, page_table: torch.Tensor,
                          out: torch.Tensor, heads: int, kv_heads: int, head_dim: int, window: int,

@@ -17,7 +17,8 @@ from .workspace import Workspace
 
 _SM_COUNT = {}
 # tuning of the decode attention split: CTAs per SM to aim for, fewest keys per slice
-_FILL = int(os.environ.get("NNIS_DECODE_FILL", "8"))
+_FILL_ENV = os.environ.get("NNIS_DECODE_FILL")
+_FILL = int(_FILL_ENV or "8")
 _SLICE_KEYS = int(os.environ.get("NNIS_DECODE_SLICE_KEYS", "256"))
 
 
@@ -69,9 +70,15 @@ class StepContext:
         by_keys = max(1, -(-self.max_context // 128))
         return int(min(by_rows, by_keys, 64))
 
-    def decode_splits(self, ctas: int) -> int:
-        """The same for the decode kernel, whose CTAs (4 warps) each own a kv head
-        of a sequence: fill the SMs a few times over, at least 256 keys a slice."""
-        by_ctas = max(1, sm_count(self.tokens.device) * _FILL // max(1, ctas))
+    def decode_splits(self, ctas: int, resident: int = 0) -> int:
+        """The same for the decode kernels, whose CTAs (4 warps) each own a kv head
+        of a sequence, at least 256 keys a slice.  ``resident``: how many CTAs of the
+        kernel the device holds at once; the slices are then as many as still run
+        all together (at batch 64 three slices instead of two, one wave and a half,
+        cost 12 % of the step).  Without it: fill the SMs a few times over."""
+        if resident > 0 and _FILL_ENV is None:
+            by_ctas = max(1, resident // max(1, ctas))
+        else:
+            by_ctas = max(1, sm_count(self.tokens.device) * _FILL // max(1, ctas))
         by_keys = max(1, -(-self.max_context // _SLICE_KEYS))
         return int(min(by_ctas, by_keys, 64))
