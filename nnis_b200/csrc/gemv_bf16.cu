@@ -1,6 +1,8 @@
 // Entry point of the decode projections (see gemv_kernel.cuh for the kernel):
 // picks the launch shape for a problem and hands it to the instantiation for its
 // number of 16-row tiles of x (gemv_tiles1.cu .. gemv_tiles4.cu).
+#include <stdlib.h>
+
 #include "gemv_kernel.cuh"
 
 namespace nnis {
@@ -10,12 +12,17 @@ int gemv_launch_tiles2(const GemvArgs&, int, int, const GemvPlan&, bool, cudaStr
 int gemv_launch_tiles3(const GemvArgs&, int, int, const GemvPlan&, bool, cudaStream_t);
 int gemv_launch_tiles4(const GemvArgs&, int, int, const GemvPlan&, bool, cudaStream_t);
 
-// Shared memory of one CTA: x, the weight stages, the barriers, and with split K
-// the warps' partial sums.
-static size_t gemv_smem(int mtiles, int warps, int stages, int K, bool splitk) {
+// Shared memory of one CTA: x, the weight stages (eight rows of `kc` columns each),
+// the barriers, and with split K the warps' partial sums.
+static size_t gemv_smem(int mtiles, int warps, int stages, int K, int kc, bool splitk) {
     size_t sets = splitk ? 1 : (size_t)warps * stages;
-    return ((size_t)mtiles * 16 + sets * 8) * (K + 8) * sizeof(bf16) + (size_t)warps * stages * 8 +
-           (splitk ? (size_t)warps * mtiles * 4 * 32 * sizeof(float) : 0);
+    return ((size_t)mtiles * 16 * (K + 8) + sets * 8 * (kc + 8)) * sizeof(bf16) +
+           (size_t)warps * stages * 8 + (splitk ? (size_t)warps * mtiles * 4 * 32 * sizeof(float) : 0);
+}
+
+static int env_int(const char* name, int fallback) {
+    const char* v = getenv(name);
+    return v && *v ? atoi(v) : fallback;
 }
 
 static bool gemv_plan(int M, int N, int K, int sm_count, GemvPlan* plan) {
@@ -24,9 +31,12 @@ static bool gemv_plan(int M, int N, int K, int sm_count, GemvPlan* plan) {
     int mtiles = (M + 15) / 16;
     int units = N / 8;
     const size_t budget = 200 * 1024;
+    static const int chunk_min_k = env_int("NNIS_GEMV_CHUNK_MIN_K", 2048);
+    static const int chunk_cols = env_int("NNIS_GEMV_CHUNK_COLS", 512);
+    plan->kc = K;
     // Few units: one per CTA, its eight warps sharing K.
     {
-        size_t smem = gemv_smem(mtiles, 8, 1, K, true);
+        size_t smem = gemv_smem(mtiles, 8, 1, K, K, true);
         size_t per_sm = smem + 1024;
         int fit = (int)((220 * 1024) / per_sm);
         if (fit > 8) fit = 8;
@@ -36,11 +46,11 @@ static bool gemv_plan(int M, int N, int K, int sm_count, GemvPlan* plan) {
             return true;
         }
     }
-    for (int warps = 8; warps >= 4; warps -= 4) {
+    for (int warps = 8; warps >= 4 && K < chunk_min_k; warps -= 4) {
         // Many units: as many CTAs as fit (units are dealt to CTAs first), each
         // warp streaming its own units through one or two stages.
         for (int stages = 2; stages >= 1; --stages) {
-            size_t smem = gemv_smem(mtiles, warps, stages, K, false);
+            size_t smem = gemv_smem(mtiles, warps, stages, K, K, false);
             if (smem > budget) continue;
             int cap = smem > 110 * 1024 ? sms : sms * 2;
             int grid = units < cap ? units : cap;
@@ -51,7 +61,41 @@ static bool gemv_plan(int M, int N, int K, int sm_count, GemvPlan* plan) {
             return true;
         }
     }
+    // Long rows: a stage holds a chunk of K, two stages per warp, so that the
+    // copies of the next chunk run under the products of this one.
+    for (int kc = chunk_cols; kc >= 128; kc >>= 1) {
+        if (kc >= K) continue;
+        size_t smem = gemv_smem(mtiles, 8, 2, K, kc, false);
+        if (smem > budget) continue;
+        int cap = smem > 110 * 1024 ? sms : sms * 2;
+        plan->mtiles = mtiles; plan->warps = 8; plan->stages = 2; plan->grid = units < cap ? units : cap;
+        plan->splitk = false; plan->smem = smem; plan->kc = kc;
+        return true;
+    }
     return false;
+}
+
+// In how many slices of K a product with the ADD_F32 epilogue runs (each slice
+// a launch that adds its share into the output, in order): 1 when the kernel
+// takes the whole K, 0 when no slicing helps.  Rows of x longer than shared
+// memory are the reason: the kernel keeps all of x there.
+static int gemv_slices(int M, int N, int K, int sm_count, GemvPlan* plan) {
+    if (gemv_plan(M, N, K, sm_count, plan) && (plan->splitk || plan->kc == K)) return 1;
+    // Few output rows and long rows of K: slices short enough for the launch shape
+    // whose warps share K are faster than chunks that leave most warps without a unit.
+    int first = plan->kc != K ? 1 : 0;
+    for (int c = 2; c <= 16; ++c) {
+        if (K % (16 * c)) continue;
+        GemvPlan p;
+        if (!gemv_plan(M, N, K / c, sm_count, &p)) continue;
+        if (p.splitk) {
+            *plan = p;
+            return c;
+        }
+        if (!first) first = c;
+    }
+    if (first && gemv_plan(M, N, K / first, sm_count, plan)) return first;
+    return 0;
 }
 
 }  // namespace nnis
@@ -62,6 +106,13 @@ static bool gemv_plan(int M, int N, int K, int sm_count, GemvPlan* plan) {
 NNIS_API int nnis_gemv_takes(int M, int N, int K, int sm_count) {
     nnis::GemvPlan p;
     return nnis::gemv_plan(M, N, K, sm_count, &p) ? 1 : 0;
+}
+
+// Slices of K for the ADD_F32 epilogue with a plain prologue: 0 not taken, 1 one
+// launch, more: that many launches inside nnis_gemv_bf16.
+NNIS_API int nnis_gemv_slices(int M, int N, int K, int sm_count) {
+    nnis::GemvPlan p;
+    return nnis::gemv_slices(M, N, K, sm_count, &p);
 }
 
 // How many CTAs a launch with these sizes has: the ARGMAX scratch is
@@ -84,8 +135,11 @@ NNIS_API int nnis_gemv_bf16(const void* x, const float* hidden, const int* rows,
     using namespace nnis;
     if (M <= 0 || N <= 0 || K <= 0 || !w || !out) return NNIS_ERR_ARGUMENT;
     GemvPlan plan;
-    if (!gemv_plan(M, N, K, sm_count, &plan)) return NNIS_ERR_UNSUPPORTED;
     int pro = hidden ? PRO_NORM : PRO_PLAIN;
+    const bool may_slice = epilogue == EPI_ADD_F32 && pro == PRO_PLAIN;
+    const int slices = may_slice ? gemv_slices(M, N, K, sm_count, &plan)
+                                 : (gemv_plan(M, N, K, sm_count, &plan) ? 1 : 0);
+    if (slices == 0) return NNIS_ERR_UNSUPPORTED;
     if (pro == PRO_PLAIN && !x) return NNIS_ERR_ARGUMENT;
     if (pro == PRO_NORM && (!norm_w || !(eps > 0.f))) return NNIS_ERR_ARGUMENT;
     if (((uintptr_t)w | (uintptr_t)x | (uintptr_t)hidden | (uintptr_t)norm_w | (uintptr_t)out) % 16)
@@ -105,10 +159,21 @@ NNIS_API int nnis_gemv_bf16(const void* x, const float* hidden, const int* rows,
     a.v_cache = (bf16*)v_cache; a.nq = nq; a.nkv = nkv; a.d = d > 0 ? d : 8; a.page_size = page_size;
     a.logits = logits; a.best_val = best_val; a.best_idx = best_idx; a.ticket = ticket;
     a.next_tokens = next_tokens; a.next_pos = next_pos;
-    switch (plan.mtiles) {
-        case 1: return gemv_launch_tiles1(a, epilogue, pro, plan, pdl != 0, stream);
-        case 2: return gemv_launch_tiles2(a, epilogue, pro, plan, pdl != 0, stream);
-        case 3: return gemv_launch_tiles3(a, epilogue, pro, plan, pdl != 0, stream);
-        default: return gemv_launch_tiles4(a, epilogue, pro, plan, pdl != 0, stream);
+    a.ldx = K; a.ldw = K; a.kc = plan.kc; a.out_is_hot = 0;
+    a.K = K / slices;
+    for (int s = 0; s < slices; ++s) {
+        int rc;
+        switch (plan.mtiles) {
+            case 1: rc = gemv_launch_tiles1(a, epilogue, pro, plan, pdl != 0, stream); break;
+            case 2: rc = gemv_launch_tiles2(a, epilogue, pro, plan, pdl != 0, stream); break;
+            case 3: rc = gemv_launch_tiles3(a, epilogue, pro, plan, pdl != 0, stream); break;
+            default: rc = gemv_launch_tiles4(a, epilogue, pro, plan, pdl != 0, stream); break;
+        }
+        if (rc != NNIS_OK) return rc;
+        a.x += a.K;
+        a.w += a.K;
+        a.bias = nullptr;  // the first slice has added it
+        a.out_is_hot = 1;
     }
+    return NNIS_OK;
 }

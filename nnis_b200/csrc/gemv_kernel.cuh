@@ -51,6 +51,9 @@ struct GemvArgs {
     const float* bias;      // [N] or null
     void* out;              // see epilogues
     int M, N, K;
+    int ldx, ldw;           // elements between rows of x and of w (K unless a slice of K is taken)
+    int kc;                 // columns of K per weight stage (K: a stage holds whole rows)
+    int out_is_hot;         // ADD_F32: the kernel just before this one wrote `out` (a slice of K)
     int* status;            // set non-zero when a bounded wait runs out
     // QKV epilogue
     const int* token_pos;
@@ -109,11 +112,16 @@ gemv_kernel(GemvArgs a) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int K = a.K, M = a.M;
     const int KP = K + 8;  // padded row, in elements
+    // A weight stage holds eight rows of KC columns: all of K, or with long rows a
+    // chunk of it, so that a warp still has a stage in flight while it multiplies.
+    const int KC = SPLITK ? K : a.kc;
+    const int KCP = KC + 8;
+    const int n_chunks = SPLITK ? 1 : (K + KC - 1) / KC;
     bf16* xs = reinterpret_cast<bf16*>(smem_raw);                          // [MT, KP]
     // weight stages: one set per warp, or one shared set when the warps split K
-    bf16* wst = xs + (size_t)MT * KP + (SPLITK ? 0 : (size_t)warp * S * 8 * KP);
+    bf16* wst = xs + (size_t)MT * KP + (SPLITK ? 0 : (size_t)warp * S * 8 * KCP);
     constexpr int kSets = SPLITK ? 1 : WARPS * S;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(xs + (size_t)(MT + kSets * 8) * KP) + warp * S;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(xs + (size_t)MT * KP + (size_t)kSets * 8 * KCP) + warp * S;
     float* red = reinterpret_cast<float*>(bars - warp * S + WARPS * S);     // SPLITK: [WARPS, MTILES*4, 32]
     __shared__ float cta_val[WARPS][MT];
     __shared__ int cta_idx[WARPS][MT];
@@ -130,16 +138,21 @@ gemv_kernel(GemvArgs a) {
     const int k_end = SPLITK ? min(steps, (warp + 1) * steps_per_warp) * 16 : K;
     const uint32_t row_bytes = (uint32_t)(k_end - k_begin) * 2u;
 
-    auto issue = [&](int i) {  // lane 0 only
-        int unit = first_unit + i * unit_stride;
-        if (unit >= n_units || row_bytes == 0) return;
-        uint64_t* bar = bars + (i % S);
-        bf16* dst = wst + (size_t)(i % S) * 8 * KP + k_begin;
-        mbar_expect_tx(bar, 8u * row_bytes);
+    // stage j holds chunk j % n_chunks of this warp's unit number j / n_chunks
+    auto issue = [&](int j) {  // lane 0 only
+        const int i = n_chunks == 1 ? j : j / n_chunks;
+        const int unit = first_unit + i * unit_stride;
+        if (unit >= n_units) return;
+        const int kc0 = SPLITK ? k_begin : (j - i * n_chunks) * KC;
+        const uint32_t bytes = SPLITK ? row_bytes : (uint32_t)min(KC, K - kc0) * 2u;
+        if (bytes == 0) return;
+        uint64_t* bar = bars + (j % S);
+        bf16* dst = wst + (size_t)(j % S) * 8 * KCP + (SPLITK ? k_begin : 0);
+        mbar_expect_tx(bar, 8u * bytes);
 #pragma unroll
         for (int c = 0; c < 8; ++c)
-            bulk_load(dst + (size_t)c * KP, a.w + (size_t)unit_row<EPI>(a, unit, c) * K + k_begin,
-                      row_bytes, bar);
+            bulk_load(dst + (size_t)c * KCP, a.w + (size_t)unit_row<EPI>(a, unit, c) * a.ldw + kc0,
+                      bytes, bar);
     };
 
     // ---- weights first: they depend on no earlier kernel ---------------------
@@ -170,7 +183,7 @@ gemv_kernel(GemvArgs a) {
     float2 old0[MTILES][2];          // ADD_F32: the destination's values
     int pos0[MTILES][2], page0[MTILES][2];  // QKV: position and cache page of the row
     float cos0[MTILES][4], sin0[MTILES][4];
-    if (EPI == EPI_ADD_F32 && epi_warp && first_unit < n_units) {
+    if (EPI == EPI_ADD_F32 && epi_warp && first_unit < n_units && !a.out_is_hot) {
         const int n0 = first_unit * 8 + c_lo;
 #pragma unroll
         for (int t = 0; t < MTILES; ++t)
@@ -231,7 +244,13 @@ gemv_kernel(GemvArgs a) {
                         ss = fmaf(hv[j].w, hv[j].w, ss);
                     }
                 } else {
-                    for (int k = lane; k < K; k += 32) ss = fmaf(h[k], h[k], ss);
+                    for (int c = lane; c < k4; c += 32) {
+                        float4 v = h4[c];
+                        ss = fmaf(v.x, v.x, ss);
+                        ss = fmaf(v.y, v.y, ss);
+                        ss = fmaf(v.z, v.z, ss);
+                        ss = fmaf(v.w, v.w, ss);
+                    }
                 }
                 ss = warp_sum(ss);
                 float s = 1.0f / sqrtf(ss * (1.0f / (float)K) + a.eps);
@@ -246,8 +265,12 @@ gemv_kernel(GemvArgs a) {
                         }
                     }
                 } else {
-                    for (int k = lane; k < K; k += 32)
-                        xs[(size_t)m * KP + k] = __float2bfloat16_rn((h[k] * s) * a.norm_w[k]);
+                    const float4* w4 = reinterpret_cast<const float4*>(a.norm_w);
+                    for (int c = lane; c < k4; c += 32) {
+                        float4 v = h4[c], g = w4[c];
+                        store4(xs + (size_t)m * KP + c * 4,
+                               make_float4((v.x * s) * g.x, (v.y * s) * g.y, (v.z * s) * g.z, (v.w * s) * g.w));
+                    }
                 }
             } else {
                 for (int k = lane; k < K; k += 32) xs[(size_t)m * KP + k] = __float2bfloat16_rn(0.f);
@@ -258,7 +281,7 @@ gemv_kernel(GemvArgs a) {
         for (int c = threadIdx.x; c < MT * per_row; c += WARPS * 32) {
             int m = c / per_row, ch = c - m * per_row;
             uint4 v = make_uint4(0, 0, 0, 0);
-            if (m < M) v = *reinterpret_cast<const uint4*>(a.x + (size_t)m * K + ch * 8);
+            if (m < M) v = *reinterpret_cast<const uint4*>(a.x + (size_t)m * a.ldx + ch * 8);
             *reinterpret_cast<uint4*>(xs + (size_t)m * KP + ch * 8) = v;
         }
     }
@@ -278,35 +301,46 @@ gemv_kernel(GemvArgs a) {
     for (int i = 0;; ++i) {
         int unit = first_unit + i * unit_stride;
         if (unit >= n_units) break;
-        // the whole warp leaves together if any lane's wait ran out
-        if (row_bytes != 0 &&
-            !__all_sync(0xffffffffu, mbar_wait(bars + (i % S), (uint32_t)(i / S) & 1u))) {
-            failed = true;
-            if (!SPLITK) break;
-        }
-        const bf16* wbuf = wst + (size_t)(i % S) * 8 * KP;
         float acc[MTILES][4];
 #pragma unroll
         for (int t = 0; t < MTILES; ++t)
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[t][e] = 0.f;
-        // lanes 0-7: weight rows at columns k0..k0+7, lanes 8-15: k0+8..k0+15
-        const bf16* b_ptr = wbuf + (size_t)(lane & 7) * KP + ((lane >> 3) & 1) * 8;
         const bf16* a_ptr = xs + (size_t)(lane & 15) * KP + (lane >> 4) * 8;
         // with one tile of rows, two chains of products halve the dependent latency
         float acc2[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int ch = 0; ch < n_chunks; ++ch) {
+            const int j = i * n_chunks + ch;
+            const int kb = SPLITK ? k_begin : ch * KC;
+            const int ke = SPLITK ? k_end : min(K, kb + KC);
+            // the whole warp leaves together if any lane's wait ran out
+            if (ke > kb &&
+                !__all_sync(0xffffffffu, mbar_wait(bars + (j % S), (uint32_t)(j / S) & 1u))) {
+                failed = true;
+                break;
+            }
+            // lanes 0-7: weight rows at columns k0..k0+7, lanes 8-15: k0+8..k0+15; a
+            // stage of whole rows is indexed by k0, a chunk by k0 - kb
+            const bf16* b_ptr = wst + (size_t)(j % S) * 8 * KCP + (size_t)(lane & 7) * KCP +
+                                ((lane >> 3) & 1) * 8 - (SPLITK ? 0 : kb);
 #pragma unroll 4
-        for (int k0 = k_begin; k0 < k_end; k0 += 16) {
-            uint32_t b0, b1;
-            ldmatrix_x2(b0, b1, b_ptr + k0);
+            for (int k0 = kb; k0 < ke; k0 += 16) {
+                uint32_t b0, b1;
+                ldmatrix_x2(b0, b1, b_ptr + k0);
 #pragma unroll
-            for (int t = 0; t < MTILES; ++t) {
-                uint32_t af[4];
-                ldmatrix_x4(af, a_ptr + (size_t)t * 16 * KP + k0);
-                if (MTILES == 1 && (k0 & 16)) mma_bf16(acc2, af, b0, b1);
-                else mma_bf16(acc[t], af, b0, b1);
+                for (int t = 0; t < MTILES; ++t) {
+                    uint32_t af[4];
+                    ldmatrix_x4(af, a_ptr + (size_t)t * 16 * KP + k0);
+                    if (MTILES == 1 && (k0 & 16)) mma_bf16(acc2, af, b0, b1);
+                    else mma_bf16(acc[t], af, b0, b1);
+                }
+            }
+            if (!SPLITK) {
+                __syncwarp();  // every lane has read this stage: it may be filled again
+                if (lane == 0) issue(j + S);
             }
         }
+        if (failed && !SPLITK) break;
         if (MTILES == 1) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[0][e] += acc2[e];
@@ -327,9 +361,6 @@ gemv_kernel(GemvArgs a) {
                     for (int w = 1; w < WARPS; ++w) sum += red[((size_t)w * MTILES * 4 + t * 4 + e) * 32 + lane];
                     acc[t][e] = sum;
                 }
-        } else {
-            __syncwarp();  // every lane has read this stage: it may be filled again
-            if (lane == 0) issue(i + S);
         }
 
         // ---- epilogue: this thread holds rows r_lo (+8) and columns c_lo, c_lo + 1 ---
@@ -407,7 +438,7 @@ gemv_kernel(GemvArgs a) {
                         *reinterpret_cast<float2*>(reinterpret_cast<float*>(a.out) + o) = make_float2(v0, v1);
                     } else if (EPI == EPI_ADD_F32) {
                         float2* p = reinterpret_cast<float2*>(reinterpret_cast<float*>(a.out) + o);
-                        float2 old = i == 0 ? old0[t][hrow] : *p;
+                        float2 old = (i == 0 && !a.out_is_hot) ? old0[t][hrow] : *p;
                         *p = make_float2(old.x + v0, old.y + v1);
                     } else {
                         if (a.logits) *reinterpret_cast<float2*>(a.logits + o) = make_float2(v0, v1);
@@ -502,6 +533,7 @@ gemv_kernel(GemvArgs a) {
 
 struct GemvPlan {
     int mtiles, warps, stages, grid;
+    int kc;  // columns of K per weight stage
     bool splitk;
     size_t smem;
 };

@@ -277,7 +277,16 @@ def gemv_takes(m: int, n: int, k: int, epilogue: int = EPI_STORE, device=None) -
     if m > 64 or k % 16 or n % 8:
         return False
     sms = sm_count(device) if device is not None else 148
+    if epilogue == EPI_ADD_F32:  # may run as several launches over slices of K
+        return gemv_slices(m, n, k, device) >= 1
     return bool(_lib().nnis_gemv_takes(m, n, k, sms))
+
+
+def gemv_slices(m: int, n: int, k: int, device=None) -> int:
+    """Launches that an ADD_F32 product of these sizes takes (slices of K, each
+    adding its share in order); 0: not taken."""
+    sms = sm_count(device) if device is not None else 148
+    return int(_lib().nnis_gemv_slices(m, n, k, sms))
 
 
 def gemv_bf16(w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, epilogue: int,
@@ -356,7 +365,8 @@ def gemv_bf16(w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, 
         _ptr(page_table), cols, _ptr(cos), _ptr(sin), _ptr(k_cache), _ptr(v_cache), heads, kv_heads,
         head_dim, page_size, _ptr(logits), ctypes.c_void_p(best_val), ctypes.c_void_p(best_idx),
         ctypes.c_void_p(ticket), _ptr(next_tokens), _ptr(next_pos), _ptr(status_word(w.device)),
-        sm_count(w.device), PDL, _stream()), "gemv_bf16")
+        sm_count(w.device), PDL, _stream()), "gemv_bf16",
+        gemv_slices(m, n, k, w.device) if epilogue == EPI_ADD_F32 and hidden is None else 1)
 
 
 def argmax_scratch_ints(m: int, n: int, k: int, device) -> int:
@@ -587,10 +597,14 @@ def mma_ticket_count(n: int, heads: int, kv_heads: int) -> int:
 TC_GEMM = 0 if __import__("os").environ.get("NNIS_TC_GEMM", "1") == "0" else 1
 
 
+TC_FEW_ROWS_ELEMS = int(__import__("os").environ.get("NNIS_TC_FEW_ROWS_ELEMS", str(1 << 62)))
+
+
 def gemm_tc_takes(m: int, n: int, k: int) -> bool:
     """Whether the tcgen05 kernel runs this bfloat16 product (else CUDA cores):
     K a multiple of 8 (rows of 16 bytes for TMA) and enough rows to fill a tile."""
-    return bool(TC_GEMM) and m > 16 and k % 8 == 0 and -(-m // 128) <= 65535
+    few = m <= 16 and n * k < TC_FEW_ROWS_ELEMS
+    return bool(TC_GEMM) and not few and k % 8 == 0 and -(-m // 128) <= 65535
 
 
 GEMM_GATED, GEMM_QKV = 3, 4

@@ -168,7 +168,8 @@ class Attention(Part):
             # tensor-core kernel: a CTA per (kv head, up to 16 query heads, slice)
             tiles = -(-(nq // nkv) // 16)
             splits = ctx.decode_splits(n * nkv * tiles,
-                                       ops.attention_decode_mma_resident(d, self.device))
+                                       ops.attention_decode_mma_resident(d, self.device),
+                                       cache.page_size)
             partial = tickets = None
             if splits > 1:
                 partial = ws.get("attn_partial", (n * nq * splits * (d + 2),), torch.float32)

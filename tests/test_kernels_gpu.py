@@ -318,7 +318,7 @@ def test_temperature_sampling_follows_the_seeded_draws():
 def test_gemv_plain_epilogues_and_norm_prologue(m, n, k):
     o = ops()
     if not o.gemv_takes(m, n, k, device=DEV):
-        assert m > 32 and k == 1536  # x and the weight stages do not fit shared memory
+        assert m > 48 and k == 1536  # x and the weight stages do not fit shared memory
         return
     g = torch.Generator().manual_seed(m + n + k)
     w = (torch.randn(n, k, generator=g) / math.sqrt(k)).bfloat16()
@@ -343,6 +343,50 @@ def test_gemv_plain_epilogues_and_norm_prologue(m, n, k):
     o.gemv_bf16(w.to(DEV), None, out32, o.EPI_STORE_F32, hidden=hidden.to(DEV),
                 norm_weight=nw.to(DEV), eps=1e-5, rows=rows.to(DEV))
     close(out32, P.linear(normed, w), "float32", "gemv norm prologue")
+
+
+@pytest.mark.parametrize("m", [1, 8, 24])
+@pytest.mark.parametrize("n,k", [(4096, 2048), (1544, 4096), (2048, 8192), (520, 6144)])
+def test_gemv_long_rows_in_chunks_and_slices(m, n, k):
+    """Rows of K too long for whole-row weight stages stream in chunks; rows of x
+    too long for shared memory are taken by the adding epilogue alone, slice by slice."""
+    o = ops()
+    g = torch.Generator().manual_seed(m + n + k)
+    w = (torch.randn(n, k, generator=g) / math.sqrt(k)).bfloat16()
+    # one far column of K matters: a chunk or a slice left out would show
+    w[:, k - 3] = 1.0
+    bias = torch.randn(n, generator=g)
+    x = torch.randn(m, k, generator=g).bfloat16()
+    x[:, k - 3] = 4.0
+    want = P.linear(x, w, bias)
+    base = torch.randn(m, n, generator=g)
+    acc = base.to(DEV).clone()
+    assert o.gemv_takes(m, n, k, o.EPI_ADD_F32, DEV)
+    whole = o.gemv_takes(m, n, k, o.EPI_STORE_F32, DEV)
+    assert whole or o.gemv_slices(m, n, k, DEV) > 1
+    assert whole == (k * ((m + 15) // 16) <= 4096)  # all of x has to fit shared memory
+    o.gemv_bf16(w.to(DEV), bias.to(DEV), acc, o.EPI_ADD_F32, x=x.to(DEV))
+    close(acc, base.double() + want, "float32", "gemv add in slices")
+    if not whole:
+        with pytest.raises(o.KernelError, match="not taken"):
+            o.gemv_bf16(w.to(DEV), None, torch.empty(m, n, device=DEV), o.EPI_STORE_F32, x=x.to(DEV))
+        return
+    out32 = torch.empty(m, n, device=DEV)
+    o.gemv_bf16(w.to(DEV), bias.to(DEV), out32, o.EPI_STORE_F32, x=x.to(DEV))
+    close(out32, want, "float32", "gemv store f32, chunks")
+    hidden = torch.randn(m + 3, k, generator=g) * 2
+    hidden[:, k - 3] = 9.0
+    nw = 1 + 0.1 * torch.randn(k, generator=g)
+    rows = torch.randperm(m + 3, generator=g)[:m].to(torch.int32)
+    normed = P.rms_norm(hidden[rows.long()], nw, 1e-5).bfloat16()
+    o.gemv_bf16(w.to(DEV), None, out32, o.EPI_STORE_F32, hidden=hidden.to(DEV),
+                norm_weight=nw.to(DEV), eps=1e-5, rows=rows.to(DEV))
+    close(out32, P.linear(normed, w), "float32", "gemv norm prologue, long rows")
+    if n % 16 == 0:
+        inter = n // 2
+        out = torch.empty(m, inter, dtype=torch.bfloat16, device=DEV)
+        o.gemv_bf16(w.to(DEV), bias.to(DEV), out, o.EPI_GATED, x=x.to(DEV))
+        close(out, P.swiglu(want[:, :inter], want[:, inter:]), "bfloat16", "gemv gated, chunks")
 
 
 @pytest.mark.parametrize("m", [1, 5, 16, 33, 64])
