@@ -597,14 +597,10 @@ def mma_ticket_count(n: int, heads: int, kv_heads: int) -> int:
 TC_GEMM = 0 if __import__("os").environ.get("NNIS_TC_GEMM", "1") == "0" else 1
 
 
-TC_FEW_ROWS_ELEMS = int(__import__("os").environ.get("NNIS_TC_FEW_ROWS_ELEMS", str(1 << 62)))
-
-
 def gemm_tc_takes(m: int, n: int, k: int) -> bool:
     """Whether the tcgen05 kernel runs this bfloat16 product (else CUDA cores):
     K a multiple of 8 (rows of 16 bytes for TMA) and enough rows to fill a tile."""
-    few = m <= 16 and n * k < TC_FEW_ROWS_ELEMS
-    return bool(TC_GEMM) and not few and k % 8 == 0 and -(-m // 128) <= 65535
+    return bool(TC_GEMM) and m > 16 and k % 8 == 0 and -(-m // 128) <= 65535
 
 
 GEMM_GATED, GEMM_QKV = 3, 4
