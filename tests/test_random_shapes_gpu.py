@@ -54,3 +54,38 @@ def test_random_shape(seed, dtype):
                      f"token {k} of {cfg}")
     engine.check_status()
     engine.cache.check()
+
+
+@pytest.mark.parametrize("batch", [1, 8, 24])
+def test_wide_layers_decode_with_long_rows_of_k(batch):
+    """A layer as wide as the 1.7B shape (hidden 2,048, intermediate 8,192, 32 heads of 64):
+    the decode projections stream K in chunks there, and the down projection adds slice by
+    slice; prompts, then single tokens of a batch, against the plain implementation."""
+    from nnis_b200.config import config_from_dict
+    from nnis_b200.engine import Engine, SequenceStep
+    from nnis_b200.engine.model import DecoderModel
+    from nnis_b200.weights import random_tensors
+    cfg = dict(architectures=["LlamaForCausalLM"], model_type="llama", vocab_size=520, hidden_size=2048,
+               intermediate_size=8192, num_hidden_layers=1, num_attention_heads=32, num_key_value_heads=32,
+               max_position_embeddings=512, rms_norm_eps=1e-5, rope_theta=130000.0, hidden_act="silu",
+               tie_word_embeddings=True, attention_bias=False, torch_dtype="bfloat16")
+    spec = config_from_dict(cfg).to_spec()
+    tensors = random_tensors(DecoderModel.weight_specs_of(spec), seed=5, std=1.0, norm_std=0.1,
+                             std_by_fan_in=True)
+    w = {k: v.to(torch.bfloat16).float() for k, v in tensors.items()}
+    engine = Engine.from_spec(spec, tensors, dtype="bfloat16", max_tokens=64 * batch * 2, max_slots=batch)
+    rng = random.Random(batch)
+    lens = [rng.choice([2, 5, 9]) for _ in range(batch)]
+    seqs = [[rng.randrange(cfg["vocab_size"]) for _ in range(n + 2)] for n in lens]
+    checked = seqs[:3]  # the plain implementation is slow at this width
+    want = [P.forward(cfg, w, t, True) for t in checked]
+    slots = [engine.acquire_slot() for _ in seqs]
+    got = engine.step([SequenceStep(s, t[:n], [n - 1]) for s, t, n in zip(slots, seqs, lens)])
+    check_logits(got.cpu().numpy()[:len(checked)], torch.stack([x[n - 1] for x, n in zip(want, lens)]),
+                 "bfloat16", "wide prompts")
+    for k in range(2):
+        got = engine.step([SequenceStep(s, [t[n + k]], [0]) for s, t, n in zip(slots, seqs, lens)])
+        check_logits(got.cpu().numpy()[:len(checked)], torch.stack([x[n + k] for x, n in zip(want, lens)]),
+                     "bfloat16", f"wide token {k}")
+    engine.check_status()
+    engine.cache.check()
