@@ -323,18 +323,32 @@ gemv_kernel(GemvArgs a) {
             // stage of whole rows is indexed by k0, a chunk by k0 - kb
             const bf16* b_ptr = wst + (size_t)(j % S) * 8 * KCP + (size_t)(lane & 7) * KCP +
                                 ((lane >> 3) & 1) * 8 - (SPLITK ? 0 : kb);
-#pragma unroll 4
-            for (int k0 = kb; k0 < ke; k0 += 16) {
-                uint32_t b0, b1;
-                ldmatrix_x2(b0, b1, b_ptr + k0);
+            // The fragments of the next 16 columns are asked for before the products
+            // of these 16 are issued (two sets of registers), so that a product never
+            // waits for the shared-memory loads just ahead of it.
+            uint32_t bw[2][2], af[2][MTILES][4];
+            auto load_step = [&](int buf, int k0) {
+                ldmatrix_x2(bw[buf][0], bw[buf][1], b_ptr + k0);
+#pragma unroll
+                for (int t = 0; t < MTILES; ++t) ldmatrix_x4(af[buf][t], a_ptr + (size_t)t * 16 * KP + k0);
+            };
+            auto mma_step = [&](int buf) {
 #pragma unroll
                 for (int t = 0; t < MTILES; ++t) {
-                    uint32_t af[4];
-                    ldmatrix_x4(af, a_ptr + (size_t)t * 16 * KP + k0);
-                    if (MTILES == 1 && (k0 & 16)) mma_bf16(acc2, af, b0, b1);
-                    else mma_bf16(acc[t], af, b0, b1);
+                    if (MTILES == 1 && buf == 1) mma_bf16(acc2, af[buf][t], bw[buf][0], bw[buf][1]);
+                    else mma_bf16(acc[t], af[buf][t], bw[buf][0], bw[buf][1]);
                 }
+            };
+            int k0 = kb;
+            if (k0 < ke) load_step(0, k0);
+#pragma unroll 2
+            for (; k0 + 32 <= ke; k0 += 32) {
+                load_step(1, k0 + 16);
+                mma_step(0);
+                if (k0 + 32 < ke) load_step(0, k0 + 32);
+                mma_step(1);
             }
+            if (k0 < ke) mma_step(0);
             if (!SPLITK) {
                 __syncwarp();  // every lane has read this stage: it may be filled again
                 if (lane == 0) issue(j + S);
