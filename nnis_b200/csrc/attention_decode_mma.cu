@@ -141,15 +141,20 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __r
             for (int j = 0; j < 2; ++j)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
+            // all fragments of K first, then the products: none waits for the load just ahead of it
+            uint32_t kb[KS / 2][2][4];
+#pragma unroll
+            for (int kk = 0; kk < KS; kk += 2)
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+                    // four 8x8 tiles: keys j*8.., dims kk*16 .. kk*16+31
+                    ldmatrix_x4(kb[kk / 2][j], kt + swz<D>(key0 + j * 8 + (lane & 7), kk * 2 + (lane >> 3)));
 #pragma unroll
             for (int kk = 0; kk < KS; kk += 2) {
 #pragma unroll
                 for (int j = 0; j < 2; ++j) {
-                    // four 8x8 tiles: keys j*8.., dims kk*16 .. kk*16+31
-                    uint32_t b[4];
-                    ldmatrix_x4(b, kt + swz<D>(key0 + j * 8 + (lane & 7), kk * 2 + (lane >> 3)));
-                    mma_bf16(s[j], qa[kk], b[0], b[1]);
-                    mma_bf16(s[j], qa[kk + 1], b[2], b[3]);
+                    mma_bf16(s[j], qa[kk], kb[kk / 2][j][0], kb[kk / 2][j][1]);
+                    mma_bf16(s[j], qa[kk + 1], kb[kk / 2][j][2], kb[kk / 2][j][3]);
                 }
             }
             // mask, scale (in log2 units) and this slice's row maxima
@@ -190,18 +195,29 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __r
 #pragma unroll
             for (int r = 0; r < 2; ++r) l_run[r] = l_run[r] * alpha[r] + psum[r];
             // output: O = O * alpha + P . V
+            // the fragments of V four tiles ahead of their products
+            constexpr int kAhead = 4;  // pairs of n-tiles in flight
 #pragma unroll
-            for (int jn = 0; jn < NT; jn += 2) {
-                uint32_t b[4];
-                // keys 0-7 / 8-15 of this warp's slice, dims jn*8 .. jn*8+15
-                ldmatrix_x4_trans(b, vt + swz<D>(key0 + (lane & 15), jn + (lane >> 4)));
+            for (int j0 = 0; j0 < NT; j0 += 2 * kAhead) {
+                uint32_t vb[kAhead][4];
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    o[jn][e] *= alpha[e >> 1];
-                    o[jn + 1][e] *= alpha[e >> 1];
+                for (int a = 0; a < kAhead; ++a)
+                    // keys 0-7 / 8-15 of this warp's slice, dims jn*8 .. jn*8+15
+                    if (j0 + 2 * a < NT)
+                        ldmatrix_x4_trans(vb[a], vt + swz<D>(key0 + (lane & 15), j0 + 2 * a + (lane >> 4)));
+#pragma unroll
+                for (int a = 0; a < kAhead; ++a) {
+                    const int jn = j0 + 2 * a;
+                    if (jn < NT) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            o[jn][e] *= alpha[e >> 1];
+                            o[jn + 1][e] *= alpha[e >> 1];
+                        }
+                        mma_bf16(o[jn], pa, vb[a][0], vb[a][1]);
+                        mma_bf16(o[jn + 1], pa, vb[a][2], vb[a][3]);
+                    }
                 }
-                mma_bf16(o[jn], pa, b[0], b[1]);
-                mma_bf16(o[jn + 1], pa, b[2], b[3]);
             }
         }
         cp_async_wait<0>();
