@@ -26,3 +26,29 @@ def test_prompt_attention_plan_cuts_tiles_without_empty_chunks():
             assert used == slots
             firsts = sorted((chunks[0][2], chunks[0][1]) for chunks in per_tile.values() if chunks[0][1] > 1)
             assert all(a[0] + a[1] <= b[0] for a, b in zip(firsts, firsts[1:]))
+
+
+def test_decode_attention_slices_fill_waves():
+    """The slices of a decode step's key range: as many CTAs as run together, fewer
+    waves before shorter slices, never below 256 keys a slice."""
+    import torch
+    from nnis_b200.engine.context import StepContext
+    empty = torch.zeros(0, dtype=torch.int32)
+
+    def pick(ctas, context, resident=444):
+        ctx = StepContext(n_tokens=0, n_seqs=0, tokens=empty, token_pos=empty, token_seq=empty,
+                          seq_slots=empty, page_tables=[], workspace=None, decode=True, max_context=context)
+        return ctx.decode_splits(ctas, resident, 64)
+
+    # one wave where the groups divide the resident CTAs: batch 8, 16, 32, 64 of three kv heads
+    assert [pick(c, 4096) for c in (24, 48, 96, 192)] == [16, 9, 4, 2]
+    # a wave that would stay 42 % empty is cut further: 256 groups take three slices, two waves
+    assert pick(256, 4096) == 3
+    # more groups than resident CTAs: no slices at all
+    assert pick(2048, 4096) == 1
+    for ctas in (1, 3, 40, 100, 443, 445, 5000):
+        for context in (1, 64, 300, 4096, 8192, 100000):
+            s = pick(ctas, context)
+            assert 1 <= s <= 64 and (s - 1) * 256 < max(context, 1)
+    # short contexts are not cut
+    assert pick(3, 200) == 1 and pick(3, 512) == 2
