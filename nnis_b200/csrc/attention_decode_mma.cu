@@ -389,18 +389,25 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __r
 
 template <int D>
 constexpr int mma_stages() { return D <= 64 ? 4 : 3; }
+// `stages`: pages of K and V in flight per CTA, 2 to the default (0: the default).
+// One stage less lets another CTA live on the SM (four instead of three at head
+// size 64), which pays when the step's CTAs then fill one wave.
 template <int D>
-constexpr size_t mma_smem_bytes() {
+static int mma_stages_or_default(int stages) {
+    return stages >= 2 && stages <= mma_stages<D>() ? stages : mma_stages<D>();
+}
+template <int D>
+static size_t mma_smem_bytes(int stages) {
     size_t stage_bytes = 2 * (size_t)kPage * D * sizeof(bf16);
-    size_t smem = 16 * D * sizeof(bf16) + mma_stages<D>() * stage_bytes;
+    size_t smem = 16 * D * sizeof(bf16) + stages * stage_bytes;
     size_t merge_bytes = ((size_t)kMmaWarps * 16 * D + 4 * 16 * 2) * sizeof(float);
     return smem < merge_bytes ? merge_bytes : smem;
 }
 
 template <int D>
-static int resident_ctas_per_sm() {
+static int resident_ctas_per_sm(int stages) {
     auto kernel = attn_decode_mma_kernel<D>;
-    const size_t smem = mma_smem_bytes<D>();
+    const size_t smem = mma_smem_bytes<D>(mma_stages_or_default<D>(stages));
     if (smem > 48 * 1024 &&
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
             cudaSuccess)
@@ -416,9 +423,9 @@ template <int D>
 static int launch_mma(dim3 grid, bool pdl, cudaStream_t stream, const bf16* q, int q_stride,
                       const bf16* k, const bf16* v, const int* pos, const int* seq, const int* table,
                       int cols, bf16* out, float* partial, unsigned* tickets, int nq, int nkv,
-                      int window, float scale, int n_splits, int head_tiles) {
-    const int stages = mma_stages<D>();
-    const size_t smem = mma_smem_bytes<D>();
+                      int window, float scale, int n_splits, int head_tiles, int want_stages) {
+    const int stages = mma_stages_or_default<D>(want_stages);
+    const size_t smem = mma_smem_bytes<D>(stages);
     auto kernel = attn_decode_mma_kernel<D>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -447,10 +454,15 @@ static int launch_mma(dim3 grid, bool pdl, cudaStream_t stream, const bf16* q, i
 // size not taken, or the query failed).  The host cuts the key range so that all
 // CTAs of a step are resident together: a second, partly filled wave costs more
 // than shorter slices gain.
-NNIS_API int nnis_attention_decode_mma_ctas_per_sm(int d) {
-    if (d == 64) return nnis::resident_ctas_per_sm<64>();
-    if (d == 128) return nnis::resident_ctas_per_sm<128>();
+NNIS_API int nnis_attention_decode_mma_ctas_per_sm(int d, int stages) {
+    if (d == 64) return nnis::resident_ctas_per_sm<64>(stages);
+    if (d == 128) return nnis::resident_ctas_per_sm<128>(stages);
     return 0;
+}
+
+// The default number of stages for head size `d` (0: head size not taken).
+NNIS_API int nnis_attention_decode_mma_stages(int d) {
+    return d == 64 ? nnis::mma_stages<64>() : d == 128 ? nnis::mma_stages<128>() : 0;
 }
 
 // Takes head sizes 64 and 128 with 64-key pages; anything else is refused with
@@ -458,12 +470,13 @@ NNIS_API int nnis_attention_decode_mma_ctas_per_sm(int d) {
 // n_splits > 1, `partial` (n_tokens * nq * n_splits * (d + 2) floats) and
 // `tickets` (n_tokens * nkv * ceil(group / 16) counters, zero before the first
 // launch; the kernel leaves them zero).
-NNIS_API int nnis_attention_decode_mma(const void* q, int q_stride, const void* k_cache,
-                                       const void* v_cache, const int* token_pos,
-                                       const int* token_seq, const int* page_table, int table_cols,
-                                       void* out, float* partial, unsigned* tickets, int n_tokens,
-                                       int nq, int nkv, int d, int page_size, int window, float scale,
-                                       int n_splits, int pdl, cudaStream_t stream) {
+NNIS_API int nnis_attention_decode_mma_staged(const void* q, int q_stride, const void* k_cache,
+                                              const void* v_cache, const int* token_pos,
+                                              const int* token_seq, const int* page_table,
+                                              int table_cols, void* out, float* partial,
+                                              unsigned* tickets, int n_tokens, int nq, int nkv, int d,
+                                              int page_size, int window, float scale, int n_splits,
+                                              int stages, int pdl, cudaStream_t stream) {
     using namespace nnis;
     if (n_tokens <= 0 || nq <= 0 || nkv <= 0 || nq % nkv || table_cols <= 0 || n_splits <= 0 ||
         window < 0)
@@ -481,8 +494,22 @@ NNIS_API int nnis_attention_decode_mma(const void* q, int q_stride, const void* 
         return launch_mma<64>(grid, pdl != 0, stream, (const bf16*)q, q_stride, (const bf16*)k_cache,
                               (const bf16*)v_cache, token_pos, token_seq, page_table, table_cols,
                               (bf16*)out, partial, tickets, nq, nkv, window, scale, n_splits,
-                              head_tiles);
+                              head_tiles, stages);
     return launch_mma<128>(grid, pdl != 0, stream, (const bf16*)q, q_stride, (const bf16*)k_cache,
                            (const bf16*)v_cache, token_pos, token_seq, page_table, table_cols,
-                           (bf16*)out, partial, tickets, nq, nkv, window, scale, n_splits, head_tiles);
+                           (bf16*)out, partial, tickets, nq, nkv, window, scale, n_splits, head_tiles,
+                           stages);
+}
+
+// The same with the default number of stages.
+NNIS_API int nnis_attention_decode_mma(const void* q, int q_stride, const void* k_cache,
+                                       const void* v_cache, const int* token_pos,
+                                       const int* token_seq, const int* page_table, int table_cols,
+                                       void* out, float* partial, unsigned* tickets, int n_tokens,
+                                       int nq, int nkv, int d, int page_size, int window, float scale,
+                                       int n_splits, int pdl, cudaStream_t stream) {
+    return nnis_attention_decode_mma_staged(q, q_stride, k_cache, v_cache, token_pos, token_seq,
+                                            page_table, table_cols, out, partial, tickets, n_tokens,
+                                            nq, nkv, d, page_size, window, scale, n_splits, 0, pdl,
+                                            stream);
 }

@@ -410,13 +410,22 @@ def attention_decode_mma_takes(head_dim: int, page_size: int) -> bool:
 
 
 _decode_mma_resident: dict = {}
+# 1: the decode attention may run with one stage less where the wave model favours it
+DECODE_STAGE_CHOICE = int(__import__("os").environ.get("NNIS_DECODE_STAGE_CHOICE", "1")) \
+    and __import__("os").environ.get("NNIS_DECODE_FILL") is None
 
 
-def attention_decode_mma_resident(head_dim: int, device) -> int:
-    """How many CTAs of the tensor-core decode kernel the device holds at once."""
-    key = (head_dim, torch.device(device).index or 0)
+def attention_decode_mma_stages(head_dim: int) -> int:
+    """Pages of K and V that a CTA of the tensor-core decode kernel keeps in flight by default."""
+    return int(_lib().nnis_attention_decode_mma_stages(int(head_dim)))
+
+
+def attention_decode_mma_resident(head_dim: int, device, stages: int = 0) -> int:
+    """How many CTAs of the tensor-core decode kernel the device holds at once
+    (``stages`` pages in flight per CTA; 0: the default)."""
+    key = (head_dim, torch.device(device).index or 0, stages)
     if key not in _decode_mma_resident:
-        per_sm = int(_lib().nnis_attention_decode_mma_ctas_per_sm(int(head_dim)))
+        per_sm = int(_lib().nnis_attention_decode_mma_ctas_per_sm(int(head_dim), int(stages)))
         if per_sm <= 0:
             raise RuntimeError(f"decode attention kernel for head size {head_dim}: occupancy query failed")
         _decode_mma_resident[key] = per_sm * sm_count(device)
@@ -427,10 +436,11 @@ def attention_decode_mma(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, 
                          token_pos: torch.Tensor, token_seq: torch.Tensor, page_table: torch.Tensor,
                          out: torch.Tensor, heads: int, kv_heads: int, head_dim: int, window: int,
                          scale: float, n_splits: int = 1, partial: Optional[torch.Tensor] = None,
-                         tickets: Optional[torch.Tensor] = None) -> None:
+                         tickets: Optional[torch.Tensor] = None, stages: int = 0) -> None:
     """Decode attention on the tensor cores (head sizes 64 and 128).  With several
     splits the slice that finishes last merges them: ``out`` is always complete.
-    ``tickets``: int32 zeros, ``mma_ticket_count`` of them, left zero."""
+    ``tickets``: int32 zeros, ``mma_ticket_count`` of them, left zero.  ``stages``:
+    pages in flight per CTA (0: the default; fewer let more CTAs share an SM)."""
     _cuda(k_cache, v_cache, token_pos, token_seq, page_table, out, partial, tickets)
     _need(q.is_cuda and q.dtype == torch.bfloat16 == k_cache.dtype == out.dtype,
           "attention_decode_mma: bfloat16 tensors")
@@ -448,11 +458,11 @@ def attention_decode_mma(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, 
               "attention: partial scratch too small")
         _need(tickets is not None and tickets.dtype == torch.int32
               and tickets.numel() >= mma_ticket_count(n, heads, kv_heads), "attention: tickets")
-    _check(_lib().nnis_attention_decode_mma(
+    _check(_lib().nnis_attention_decode_mma_staged(
         _ptr(q), q_stride, _ptr(k_cache), _ptr(v_cache), _ptr(token_pos), _ptr(token_seq),
         _ptr(page_table), page_table.shape[1], _ptr(out), _ptr(partial), _ptr(tickets), n, heads,
-        kv_heads, head_dim, page_size, window, ctypes.c_float(scale), n_splits, PDL, _stream()),
-        "attention_decode_mma")
+        kv_heads, head_dim, page_size, window, ctypes.c_float(scale), n_splits, int(stages), PDL,
+        _stream()), "attention_decode_mma")
 
 
 def attention_prefill_mma(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor,

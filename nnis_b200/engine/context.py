@@ -73,22 +73,29 @@ class StepContext:
     def decode_splits(self, ctas: int, resident: int = 0, page_size: int = 64) -> int:
         """The same for the decode kernels, whose CTAs (4 warps) each own a kv head
         of a sequence, at least 256 keys a slice.  ``resident``: how many CTAs of the
-        kernel the device holds at once.  The CTAs then run in waves, a wave lasts as
-        long as one slice, and a slice costs its pages plus about four pages' time
-        of start and merge: the number of slices with the least waves x (pages per
-        slice + 4) is taken.  Measured on the 135M, 360M and 1.7B shapes at batch 8
-        to 64 this picks the fastest or second fastest of all choices (at batch 64 of
-        the 135M shape two slices, one wave; three slices, a wave and a third, cost
-        12 % of the step).  Without ``resident``: fill the SMs a few times over."""
-        by_keys = max(1, -(-self.max_context // _SLICE_KEYS))
+        kernel the device holds at once (see ``decode_plan``).  Without it: fill the
+        SMs a few times over."""
         if resident > 0 and _FILL_ENV is None:
-            pages = max(1, -(-self.max_context // page_size))
-            best, best_cost = 1, None
-            for s in range(1, int(min(by_keys, 64)) + 1):
-                waves = -(-ctas * s // resident)
-                cost = waves * (pages / s + 4.0)
-                if best_cost is None or cost < 0.97 * best_cost:  # more slices only for a clear gain
-                    best, best_cost = s, cost
-            return best
+            return self.decode_plan(ctas, resident, page_size)[0]
+        by_keys = max(1, -(-self.max_context // _SLICE_KEYS))
         by_ctas = max(1, sm_count(self.tokens.device) * _FILL // max(1, ctas))
         return int(min(by_ctas, by_keys, 64))
+
+    def decode_plan(self, ctas: int, resident: int, page_size: int = 64):
+        """(slices, cost) for a decode kernel of which ``resident`` CTAs run together.
+        The CTAs run in waves, a wave lasts as long as one slice, and a slice costs
+        its pages plus about four pages' time of start and merge: the number of
+        slices with the least waves x (pages per slice + 4) is taken, more slices only
+        for a gain of 3 %.  Measured on the 135M, 360M and 1.7B shapes at batch 8 to
+        64 this picks the fastest or second fastest of all choices (at batch 64 of
+        the 135M shape two slices, one wave; three slices, a wave and a third, cost
+        12 % of the step).  The cost serves to compare launch shapes of one kernel."""
+        by_keys = max(1, -(-self.max_context // _SLICE_KEYS))
+        pages = max(1, -(-self.max_context // page_size))
+        best, best_cost = 1, None
+        for s in range(1, int(min(by_keys, 64)) + 1):
+            waves = -(-ctas * s // max(1, resident))
+            cost = waves * (pages / s + 4.0)
+            if best_cost is None or cost < 0.97 * best_cost:  # more slices only for a clear gain
+                best, best_cost = s, cost
+        return best, best_cost

@@ -127,6 +127,22 @@ class Attention(Part):
         """The same with the block's norm folded into the first projection."""
         self._run(ctx, hidden, cache, hidden=hidden, norm=norm)
 
+    def _decode_shape(self, ctx, ctas: int, page_size: int):
+        """(slices, stages) of the tensor-core decode kernel for a step with ``ctas``
+        groups: the default stages, or one stage less (another CTA per SM) when that
+        promises 10 % by the wave model; ``NNIS_DECODE_FILL`` keeps the default."""
+        d = self.head_dim
+        best = (ctx.decode_splits(ctas, ops.attention_decode_mma_resident(d, self.device), page_size), 0)
+        if ops.DECODE_STAGE_CHOICE:
+            base = ctx.decode_plan(ctas, ops.attention_decode_mma_resident(d, self.device), page_size)
+            fewer = ops.attention_decode_mma_stages(d) - 1
+            if fewer >= 2:
+                other = ctx.decode_plan(ctas, ops.attention_decode_mma_resident(d, self.device, fewer),
+                                        page_size)
+                if other[1] < 0.9 * base[1]:
+                    best = (other[0], fewer)
+        return best
+
     def _run(self, ctx, residual, cache, x=None, hidden=None, norm=None) -> None:
         n = residual.shape[0]
         d, nq, nkv = self.head_dim, self.heads, self.kv_heads
@@ -167,16 +183,14 @@ class Attention(Part):
                 and ops.attention_decode_mma_takes(d, cache.page_size):
             # tensor-core kernel: a CTA per (kv head, up to 16 query heads, slice)
             tiles = -(-(nq // nkv) // 16)
-            splits = ctx.decode_splits(n * nkv * tiles,
-                                       ops.attention_decode_mma_resident(d, self.device),
-                                       cache.page_size)
+            splits, stages = self._decode_shape(ctx, n * nkv * tiles, cache.page_size)
             partial = tickets = None
             if splits > 1:
                 partial = ws.get("attn_partial", (n * nq * splits * (d + 2),), torch.float32)
                 tickets = ws.zeros("attn_tickets", (ops.mma_ticket_count(n, nq, nkv),), torch.int32)
             ops.attention_decode_mma(q_buf, q_stride, cache.k, cache.v, ctx.token_pos, ctx.token_seq,
                                      table, attn, nq, nkv, d, self.window, self.scale, splits,
-                                     partial, tickets)
+                                     partial, tickets, stages)
         elif self.dtype == torch.bfloat16 and ctx.decode and n <= 65535:
             tiles = -(-(nq // nkv) // 4)
             splits = ctx.decode_splits(n * nkv * tiles)

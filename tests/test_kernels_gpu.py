@@ -545,12 +545,15 @@ def test_attention_decode_on_tensor_cores(nq, nkv, d, window):
                                          window)[L - 1:].reshape(1, -1)
                       for s, L in enumerate(lengths)])
     tickets = torch.zeros(o.mma_ticket_count(n, nq, nkv), dtype=torch.int32, device=DEV)
-    for splits in (1, 2, 7, 1, 16):
+    # slices, and pages in flight per CTA (0: the default; fewer let more CTAs share an SM)
+    assert o.attention_decode_mma_resident(d, DEV, o.attention_decode_mma_stages(d) - 1) \
+        > o.attention_decode_mma_resident(d, DEV)
+    for splits, stages in ((1, 0), (2, 0), (7, 0), (1, 2), (16, 0), (3, 3), (5, 2)):
         out = torch.full((n, nq * d), 5.0, dtype=torch.bfloat16, device=DEV)
         partial = torch.empty(n * nq * splits * (d + 2), device=DEV) if splits > 1 else None
         o.attention_decode_mma(qd, nq * d, kc, vc, pos.to(DEV), seq.to(DEV), case.table.to(DEV), out,
-                               nq, nkv, d, window, 1.0 / math.sqrt(d), splits, partial, tickets)
-        close(out[:n - 1], want, "bfloat16", f"tensor-core decode attention splits {splits}")
+                               nq, nkv, d, window, 1.0 / math.sqrt(d), splits, partial, tickets, stages)
+        close(out[:n - 1], want, "bfloat16", f"tensor-core decode attention splits {splits} stages {stages}")
         assert float(out[n - 1].float().abs().max()) == 0
         assert int(tickets.abs().sum()) == 0
     assert not o.attention_decode_mma_takes(48, 64) and not o.attention_decode_mma_takes(64, 32)
