@@ -1,6 +1,9 @@
 """``nnis generate`` and ``nnis generate-batch`` with NNIS's options and rules
 (crates/nnis-cli/src/main.rs:21-23 usage and defaults, :179-365 and :367-498
-flag rules, :117-132 the JSON of generate-batch, :1348-1390 exit codes).
+flag rules, :117-132 the JSON of generate-batch, :1348-1390 exit codes), and
+``nnis validate``, the check of a model folder on the CPU that NNIS has as
+``nnis-hf validate`` (crates/nnis-cli/src/bin/nnis-hf.rs:17 usage, :86-130 flag
+rules, :279-299 tokenizer ids against the vocabulary, :345-478 the report).
 
 Additions: ``--model`` is a Hugging Face folder; ``--prompt-ids 1,2,3`` gives a
 prompt as token ids, and then ``--tokenizer`` may be left out (ids are printed);
@@ -20,6 +23,9 @@ GENERATE_BATCH_JSON_SCHEMA_VERSION = 1
 USAGE = """Usage:
   nnis generate --model DIR [--tokenizer FILE] --prompt TEXT | --prompt-ids IDS [--device N] [--max-new-tokens N] [--dtype bfloat16|float32] [--sample --seed U64] [--temperature F] [--top-k N] [--top-p F] [--stream]
   nnis generate-batch --model DIR [--tokenizer FILE] --prompt TEXT [--prompt TEXT ...] | --prompt-ids IDS [--prompt-ids IDS ...] --seed U64 [--seed U64 ...] [--device N] [--max-new-tokens N] [--dtype bfloat16|float32] [--temperature F] [--top-k N] [--top-p F] [--json]
+  nnis validate --model DIR [--tokenizer FILE] [--json] [--output FILE]
+
+`validate` checks config.json, the safetensors files (tensor names, shapes and dtypes against the model that config.json names) and, when a tokenizer is given or DIR/tokenizer.json exists, that its ids fit the vocabulary; it needs no GPU and reads no tensor. `--output FILE` requires `--json` and writes the report there, never over an existing file.
 
 Default decoding on `generate` is greedy. Opt-in `--sample` requires `--seed`. Optional `--temperature`, `--top-k`, and `--top-p` apply only with `--sample`. `--stream` is valid only with `--sample` and prints each token as it is emitted. `generate-batch` requires one `--seed` per prompt and always samples; `--json` emits versioned JSON. CUDA device ordinal defaults to 0."""
 
@@ -45,6 +51,7 @@ class GenerateArgs:
     top_k: Optional[int] = None
     top_p: Optional[float] = None
     command: str = "generate"
+    output: Optional[str] = None
 
 
 def _positive_float(flag: str, raw: str) -> float:
@@ -82,6 +89,8 @@ def parse_args(argv: List[str]) -> Optional[GenerateArgs]:
     if not argv or argv[0] in ("-h", "--help", "help"):
         return None
     command = argv[0]
+    if command == "validate":
+        return _parse_validate(argv[1:])
     if command not in ("generate", "generate-batch"):
         raise UsageError(f"unknown command {command!r}")
     a = GenerateArgs(command=command)
@@ -161,6 +170,96 @@ def parse_args(argv: List[str]) -> Optional[GenerateArgs]:
     return a
 
 
+def _parse_validate(rest: List[str]) -> Optional[GenerateArgs]:
+    a = GenerateArgs(command="validate")
+    seen = set()
+    it = iter(rest)
+    for flag in it:
+        if flag in ("-h", "--help"):
+            return None
+        if flag == "--json":
+            a.json = True
+            continue
+        if flag not in ("--model", "--tokenizer", "--output"):
+            raise UsageError(f"unknown validate argument {flag!r}")
+        try:
+            value = next(it)
+        except StopIteration:
+            raise UsageError(f"{flag} needs a value") from None
+        if flag in seen:
+            raise UsageError(f"{flag} given twice")
+        seen.add(flag)
+        if flag == "--model":
+            a.model_dir = value
+        elif flag == "--tokenizer":
+            a.tokenizer_file = value
+        else:
+            a.output = value
+    if not a.model_dir:
+        raise UsageError("--model is required")
+    if a.output is not None and not a.json:
+        raise UsageError("--output requires --json")
+    return a
+
+
+VALIDATE_SCHEMA = "nnis_b200.model-preflight@1"
+
+
+def validate(a: GenerateArgs, out=sys.stdout) -> int:
+    """0 when the folder can be loaded and run; 1 with the reason otherwise."""
+    import os
+
+    from ..config import read_config
+    from ..engine.model import DecoderModel
+    from ..weights import check_weights
+    report = {"schema": VALIDATE_SCHEMA, "model_directory": a.model_dir, "ready": False, "blocker": None}
+    try:
+        config = read_config(a.model_dir)
+        spec = config.to_spec()
+        raw = config.to_dict()
+        report["architecture"] = (raw.get("architectures") or [None])[0]
+        report["model_type"] = raw.get("model_type")
+        report["vocab_size"] = spec.vocab_size
+        report["layers"] = len(spec.schedule)
+        report["weights"] = check_weights(a.model_dir, DecoderModel.weight_specs_of(spec))
+        tokenizer_file = a.tokenizer_file
+        if tokenizer_file is None and os.path.isfile(os.path.join(a.model_dir, "tokenizer.json")):
+            tokenizer_file = os.path.join(a.model_dir, "tokenizer.json")
+        report["tokenizer_file"] = tokenizer_file
+        if tokenizer_file is not None:
+            from ..engine.api import load_tokenizer
+            vocab = load_tokenizer(tokenizer_file).get_vocab(True)
+            if not vocab:
+                raise ValueError("tokenizer vocabulary is empty")
+            top = max(vocab.values())
+            report["tokenizer"] = {"vocabulary_size": len(vocab), "maximum_token_id": top}
+            if top >= spec.vocab_size:
+                raise ValueError(f"tokenizer maximum token id {top} is out of range for model "
+                                 f"vocabulary {spec.vocab_size}")
+        report["ready"] = True
+    except Exception as e:  # every fault of the folder is the report's blocker
+        report["blocker"] = f"{type(e).__name__}: {e}"
+    if a.json:
+        text = json.dumps(report, indent=1) + "\n"
+        if a.output is not None:
+            # never over an existing file, and whole or not at all
+            tmp = f"{a.output}.tmp-{os.getpid()}"
+            with open(tmp, "x", encoding="utf-8") as f:
+                f.write(text)
+            try:
+                os.link(tmp, a.output)
+            finally:
+                os.unlink(tmp)
+        else:
+            out.write(text)
+    else:
+        out.write("NNIS_PREFLIGHT_" + ("READY" if report["ready"] else "BLOCKED") + "\n")
+        for key, value in report.items():
+            if key not in ("ready",):
+                out.write(f"{key}={json.dumps(value) if isinstance(value, (dict, list)) else value}\n")
+    return 0 if report["ready"] else 1
+
+
 def _policy(a: GenerateArgs, seed: int):
     from ..sampling import SamplingConfig
     return SamplingConfig(seed=seed, temperature=a.temperature if a.temperature is not None else 1.0,
@@ -168,6 +267,8 @@ def _policy(a: GenerateArgs, seed: int):
 
 
 def run(a: GenerateArgs, out=sys.stdout) -> int:
+    if a.command == "validate":
+        return validate(a, out)
     from ..engine.api import LLM
     from ..sampling import SAMPLING_POLICY_VERSION
     prompts = a.prompts if a.prompts else a.prompt_ids

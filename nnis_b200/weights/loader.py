@@ -73,8 +73,9 @@ def _kept_dtype(role: str, stored: torch.dtype, compute: torch.dtype) -> torch.d
     return compute
 
 
-def load_weights(model_dir: str, wanted: Mapping[str, WeightSpec], compute_dtype: torch.dtype,
-                 device: torch.device) -> Dict[str, torch.Tensor]:
+def _open_and_check(model_dir: str, wanted: Mapping[str, WeightSpec]):
+    """Opens the weight files and checks names, shapes and dtypes against what the
+    model wants: (open files, file of each tensor, ignored names) or one WeightError."""
     files = []
     try:
         for path in _discover(model_dir):
@@ -82,7 +83,13 @@ def load_weights(model_dir: str, wanted: Mapping[str, WeightSpec], compute_dtype
                 raise WeightError(f"{path}: symbolic links are not followed")
             files.append(SafetensorsFile(path))
     except SafetensorsError as e:
+        for f in files:
+            f.close()
         raise WeightError(str(e)) from None
+    except WeightError:
+        for f in files:
+            f.close()
+        raise
     try:
         where: Dict[str, SafetensorsFile] = {}
         duplicate: List[str] = []
@@ -92,8 +99,8 @@ def load_weights(model_dir: str, wanted: Mapping[str, WeightSpec], compute_dtype
                     duplicate.append(name)
                 where[name] = f
         missing = sorted(n for n in wanted if n not in where)
-        unexpected = sorted(n for n in where if n not in wanted
-                            and not any(p.match(n) for p in _IGNORED))
+        ignored = sorted(n for n in where if n not in wanted and any(p.match(n) for p in _IGNORED))
+        unexpected = sorted(n for n in where if n not in wanted and n not in ignored)
         wrong: List[str] = []
         for name, spec in wanted.items():
             if name not in where:
@@ -116,6 +123,40 @@ def load_weights(model_dir: str, wanted: Mapping[str, WeightSpec], compute_dtype
             if duplicate:
                 lines.append(f"  stored twice ({len(duplicate)}): " + ", ".join(sorted(duplicate)))
             raise WeightError("\n".join(lines))
+        return files, where, ignored
+    except Exception:
+        for f in files:
+            f.close()
+        raise
+
+
+def check_weights(model_dir: str, wanted: Mapping[str, WeightSpec]) -> Dict[str, object]:
+    """The loader's checks without reading a tensor: raises the same WeightError,
+    else says what it found (files, tensors taken and ignored, stored dtypes and
+    bytes).  NNIS's preflight of a model folder does the same on the CPU
+    (crates/nnis-cli/src/bin/nnis-hf.rs:345-478)."""
+    files, where, ignored = _open_and_check(model_dir, wanted)
+    try:
+        dtypes, stored_bytes = set(), 0
+        for name in wanted:
+            dtype, shape = where[name].meta(name)
+            dtypes.add(str(dtype).replace("torch.", ""))
+            count = 1
+            for extent in shape:
+                count *= int(extent)
+            stored_bytes += count * dtype.itemsize
+        return {"weight_files": [os.path.basename(f.path) for f in files],
+                "recognized_tensors": len(wanted), "ignored_tensors": len(ignored),
+                "stored_dtypes": sorted(dtypes), "stored_bytes": stored_bytes}
+    finally:
+        for f in files:
+            f.close()
+
+
+def load_weights(model_dir: str, wanted: Mapping[str, WeightSpec], compute_dtype: torch.dtype,
+                 device: torch.device) -> Dict[str, torch.Tensor]:
+    files, where, _ = _open_and_check(model_dir, wanted)
+    try:
         out: Dict[str, torch.Tensor] = {}
         for name, spec in wanted.items():
             t = where[name].tensor(name)

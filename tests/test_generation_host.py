@@ -218,3 +218,50 @@ def test_cli_rules():
     a = parse_args(["generate-batch", "--model", "m", "--prompt-ids", "1", "--prompt-ids", "2,3",
                     "--seed", "1", "--seed", "2", "--json"])
     assert a.seeds == [1, 2] and a.json and a.sample and len(a.prompt_ids) == 2
+
+
+def test_cli_validate_checks_a_folder_without_a_gpu(tmp_path):
+    """`nnis validate`: flag rules of NNIS's `nnis-hf validate`, a ready report for a good
+    folder, and the loader's one error as the blocker of a bad one."""
+    import io
+    import json
+    import os
+
+    from helpers import TINY_A, make_model
+    from nnis_b200.cli.main import main, validate
+    from nnis_b200.weights import SafetensorsFile, write_safetensors
+    with pytest.raises(UsageError, match="--model is required"):
+        parse_args(["validate"])
+    with pytest.raises(UsageError, match="--output requires --json"):
+        parse_args(["validate", "--model", "m", "--output", "r.json"])
+    with pytest.raises(UsageError, match="unknown validate argument"):
+        parse_args(["validate", "--model", "m", "--prompt", "x"])
+    good = make_model(str(tmp_path / "good"), TINY_A, seed=1)
+    args = parse_args(["validate", "--model", good, "--json"])
+    out = io.StringIO()
+    assert validate(args, out) == 0
+    report = json.loads(out.getvalue())
+    assert report["ready"] and report["blocker"] is None and report["vocab_size"] == TINY_A["vocab_size"]
+    assert report["weights"]["weight_files"] == ["model.safetensors"]
+    assert report["weights"]["recognized_tensors"] > 0 and report["layers"] == TINY_A["num_hidden_layers"]
+    # the report goes to a file whole, and never over an existing one
+    target = str(tmp_path / "report.json")
+    assert main(["validate", "--model", good, "--json", "--output", target]) == 0
+    assert json.load(open(target))["ready"]
+    assert main(["validate", "--model", good, "--json", "--output", target]) == 1
+    assert not [n for n in os.listdir(tmp_path) if ".tmp-" in n]
+    # a folder whose weights do not fit: one tensor gone, one of another shape
+    bad = make_model(str(tmp_path / "bad"), TINY_A, seed=1)
+    path = os.path.join(bad, "model.safetensors")
+    with SafetensorsFile(path) as f:
+        tensors = {n: f.tensor(n) for n in f.names()}
+    gone = sorted(n for n in tensors if n.endswith("down_proj.weight"))[0]
+    del tensors[gone]
+    tensors["model.norm.weight"] = tensors["model.norm.weight"][:-1].clone()
+    write_safetensors(path, tensors)
+    out = io.StringIO()
+    assert validate(parse_args(["validate", "--model", bad]), out) == 1
+    text = out.getvalue()
+    assert text.startswith("NNIS_PREFLIGHT_BLOCKED") and gone in text and "model.norm.weight" in text
+    # no config.json at all
+    assert main(["validate", "--model", str(tmp_path / "nothing")]) == 1
