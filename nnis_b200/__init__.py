@@ -20,6 +20,9 @@ def __getattr__(name):
     if name == "SamplingConfig":
         from .sampling import SamplingConfig
         return SamplingConfig
+    if name in ("execute", "ProcessContractError"):
+        from .cli import process
+        return getattr(process, name)
     if name == "Engine":
         from .engine import Engine
         return Engine

@@ -90,6 +90,21 @@ def test_command_line_generates(model_dirs):
     assert out["results"][0]["ok"] and not out["results"][1]["ok"]
     assert "vocabulary" in out["results"][1]["error"]
     assert run("generate", "--model", d, "--prompt-ids", "1", "--seed", "3").returncode == 2
+    assert run("validate", "--model", d).returncode == 0
+
+
+def test_process_entry_point_generates(model_dirs, tmp_path):
+    """`nnis_b200.execute` runs the command line as a bounded child and records its output."""
+    from nnis_b200 import execute
+    d = model_dirs["B"]
+    cfg = read_config_json(d)
+    w = load_plain_weights(d, as_bf16=False)
+    target = str(tmp_path / "result.json")
+    result = execute(d, prompt_ids=[5, 9, 1, 77], max_new_tokens=5, dtype="float32", result_path=target,
+                     timeout_seconds=600.0)
+    want = P.greedy_generate(cfg, w, [5, 9, 1, 77], 5, cfg.get("eos_token_id"))
+    assert result["output"]["stdout_utf8"].split() == [str(t) for t in want]
+    assert json.load(open(target)) == result
 
 
 @pytest.mark.parametrize("pipeline", [True, False])

@@ -265,3 +265,60 @@ def test_cli_validate_checks_a_folder_without_a_gpu(tmp_path):
     assert text.startswith("NNIS_PREFLIGHT_BLOCKED") and gone in text and "model.norm.weight" in text
     # no config.json at all
     assert main(["validate", "--model", str(tmp_path / "nothing")]) == 1
+
+
+def test_process_entry_point_checks_bounds_and_records(tmp_path):
+    """`nnis_b200.execute`: the request rules of NNIS's process wrapper, a child that is
+    ended at its deadline, output kept whole, and a record that never replaces a file."""
+    import json
+    import os
+    import stat
+    import time
+
+    from nnis_b200 import ProcessContractError, execute
+    model = tmp_path / "model"
+    model.mkdir()
+    tok = tmp_path / "tokenizer.json"
+    tok.write_text("{}")
+    ok = dict(model_dir=str(model), tokenizer_file=str(tok), prompt="Gravity is")
+    for change, word in (({"model_dir": str(tmp_path / "none")}, "regular directory"),
+                         ({"prompt": ""}, "UTF-8 bytes"), ({"prompt": "a\0b"}, "NUL"),
+                         ({"prompt": "x" * (1024 * 1024 + 1)}, "UTF-8 bytes"),
+                         ({"tokenizer_file": None}, "needs a tokenizer"),
+                         ({"tokenizer_file": str(tmp_path / "gone.json")}, "regular file"),
+                         ({"device_ordinal": -1}, "device ordinal"), ({"device_ordinal": True}, "device ordinal"),
+                         ({"max_new_tokens": 0}, "max-new-tokens"), ({"max_new_tokens": 65537}, "max-new-tokens"),
+                         ({"timeout_seconds": 0}, "timeout"), ({"prompt_ids": [1, 2]}, "not both"),
+                         ({"dtype": "float16"}, "dtype")):
+        with pytest.raises(ProcessContractError, match=word):
+            execute(**{**ok, **change})
+    link = tmp_path / "link"
+    os.symlink(model, link)
+    with pytest.raises(ProcessContractError, match="symlink"):
+        execute(**{**ok, "model_dir": str(link)})
+
+    def script(name, body):
+        path = tmp_path / name
+        path.write_text("#!/usr/bin/env python3\nimport sys, time\n" + body)
+        path.chmod(path.stat().st_mode | stat.S_IXUSR)
+        return str(path)
+
+    echo = script("echo", "print(' '.join(sys.argv[1:]))\nprint('note', file=sys.stderr)\n")
+    target = str(tmp_path / "result.json")
+    result = execute(**ok, max_new_tokens=5, result_path=target, nnis_bin=echo)
+    said = result["output"]["stdout_utf8"]
+    assert said.startswith("generate --model") and "--max-new-tokens 5" in said and "--prompt Gravity is" in said
+    assert result["output"]["stderr_utf8"] == "note\n" and result["sampling"] == "greedy"
+    assert result["inputs"]["max_new_tokens"] == 5 and result["contract"].startswith("nnis_b200.generation@")
+    assert json.load(open(target)) == result
+    with pytest.raises(ProcessContractError, match="exists already"):
+        execute(**ok, result_path=target, nnis_bin=echo)
+    ids = execute(model_dir=str(model), prompt_ids=[3, 1, 4], nnis_bin=echo)
+    assert "--prompt-ids 3,1,4" in ids["output"]["stdout_utf8"] and "--tokenizer" not in ids["output"]["stdout_utf8"]
+    with pytest.raises(RuntimeError, match="exit code 3"):
+        execute(**ok, nnis_bin=script("fail", "print('broken', file=sys.stderr)\nsys.exit(3)\n"))
+    t0 = time.monotonic()
+    with pytest.raises(TimeoutError):
+        execute(**ok, nnis_bin=script("hang", "time.sleep(60)\n"), timeout_seconds=0.5)
+    assert time.monotonic() - t0 < 20
+    assert not [n for n in os.listdir(tmp_path) if ".tmp-" in n]
