@@ -73,6 +73,7 @@ class GraphDecoder:
         self.launches_per_step = 0
         # host side of the rows
         self.host_tables = [[[-1] * self.cols for _ in range(rows)] for _ in range(n_groups)]
+        self._host_tables_unknown = False  # True: every entry of host_tables is None
         self._pinned_out: Optional[torch.Tensor] = None
 
     def _query_heads(self) -> int:
@@ -116,6 +117,7 @@ class GraphDecoder:
             pages = cache.page_table(g, slot)[:self.cols]
             line = pages + [-1] * (self.cols - len(pages))
             self.host_tables[g][row] = line
+            self._host_tables_unknown = False
             self.tables[g][row].copy_(torch.tensor(line, dtype=torch.int32).pin_memory(),
                                       non_blocking=True)
 
@@ -133,6 +135,7 @@ class GraphDecoder:
             for j, page in enumerate(pages):
                 if line[j] != page:
                     line[j] = page
+                    self._host_tables_unknown = False
                     self.tables[g][row, j:j + 1].fill_(page)
 
     def upload(self, tokens: Sequence[int], positions: Sequence[int], slots: Sequence[int]) -> int:
@@ -174,8 +177,10 @@ class GraphDecoder:
                 mirror[r] = (table, count, dropped)
         ops.copy_async(self.state, self.host_state)
         self._host_state_free.record()
-        for g in range(len(self.tables)):  # the partial-update path starts from scratch next time
-            self.host_tables[g] = [[None] * cols for _ in range(rows)]
+        if not self._host_tables_unknown:  # the partial-update path starts from scratch next time
+            for g in range(len(self.tables)):
+                self.host_tables[g] = [[None] * cols for _ in range(rows)]
+            self._host_tables_unknown = True
         return self.state_ints * 4
 
     # -- stepping -------------------------------------------------------------------
