@@ -2,6 +2,7 @@
 """Decode and prefill throughput of the SmolLM2-135M shape on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--shape 135m|360m|1.7b] [--batch B] [--layers L] [--skip-points] [--skip-e2e]
 
 A step is one decode step of a batch of 8 sequences whose context ends at 4,096
 tokens (prompt 2,048 + 2,048 decoded); ``value`` is decoded tokens per second,
@@ -33,6 +34,14 @@ SMOLLM2_135M = dict(
     intermediate_size=1536, num_hidden_layers=30, num_attention_heads=9, num_key_value_heads=3,
     max_position_embeddings=8192, rms_norm_eps=1e-5, rope_theta=100000.0, hidden_act="silu",
     tie_word_embeddings=True, attention_bias=False, torch_dtype="bfloat16")
+# The two larger shapes of the same family (BASELINE.json configs[3] and [4]): what differs from the above.
+SHAPES = {
+    "135m": ("SmolLM2-135M", {}),
+    "360m": ("SmolLM2-360M", dict(num_hidden_layers=32, hidden_size=960, intermediate_size=2560,
+                                  num_attention_heads=15, num_key_value_heads=5)),
+    "1.7b": ("SmolLM2-1.7B", dict(num_hidden_layers=24, hidden_size=2048, intermediate_size=8192,
+                                  num_attention_heads=32, num_key_value_heads=32, rope_theta=130000.0)),
+}
 CONTEXT = 4096
 PROMPT = 2048
 BATCH = 8
@@ -101,6 +110,8 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
     ap.add_argument("--skip-e2e", action="store_true", help="leave out the end-to-end run")
     ap.add_argument("--batch", type=int, default=BATCH, help="sequences of the main decode point")
+    ap.add_argument("--shape", default="135m", choices=sorted(SHAPES),
+                    help="layer sizes: the SmolLM2-135M shape (the benchmark) or a larger one of the family")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -123,6 +134,8 @@ def main() -> int:
 
     pk = peaks()
     cfg = dict(SMOLLM2_135M)
+    shape_name, shape_sizes = SHAPES[args.shape]
+    cfg.update(shape_sizes)
     full_layers = cfg["num_hidden_layers"]
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
@@ -134,8 +147,9 @@ def main() -> int:
 
     with tempfile.TemporaryDirectory() as tmp:
         write_random_model(cfg, seed=0, out_dir=tmp, std=1.0, norm_std=0.1, std_by_fan_in=True)
-        llm = LLM(tmp, dtype="bfloat16", device_ordinal=0, max_tokens=64 * (CONTEXT + 64),
-                  max_batch=64, pipeline_decode=False)
+        most_rows = max(args.batch, 1 if args.skip_points else 64)  # the cache holds the largest point
+        llm = LLM(tmp, dtype="bfloat16", device_ordinal=0, max_tokens=most_rows * (CONTEXT + 64),
+                  max_batch=max(most_rows, 1), pipeline_decode=False)
         engine = llm.engine
         spec = engine.spec
         mixer = engine.model.blocks[0].mixer
@@ -212,9 +226,9 @@ def main() -> int:
         e2e = None
         if not args.skip_e2e:
             e2e_new = min(K, 256) + 1
-            prompts = [[rng.randrange(vocab) for _ in range(CONTEXT - e2e_new)] for _ in range(BATCH)]
+            prompts = [[rng.randrange(vocab) for _ in range(CONTEXT - e2e_new)] for _ in range(args.batch)]
             llm.generate([p[:64] for p in prompts], max_new_tokens=4, stop_token_ids=())
-            llm.backend._decoder(BATCH, CONTEXT, False).capture()  # the graph the timed run will launch
+            llm.backend._decoder(args.batch, CONTEXT, False).capture()  # the graph the timed run will launch
             stamps = []
             h2d0, d2h0 = llm.backend.h2d_bytes + engine.h2d_bytes, llm.backend.d2h_bytes
             first_done = {}
@@ -222,7 +236,7 @@ def main() -> int:
             def on_token(i, t):
                 if i not in first_done:
                     first_done[i] = True
-                    if len(first_done) == BATCH:
+                    if len(first_done) == args.batch:
                         torch.cuda.synchronize()
                         stamps.append((time.perf_counter(), llm.backend.h2d_bytes + engine.h2d_bytes,
                                        llm.backend.d2h_bytes))
@@ -235,7 +249,7 @@ def main() -> int:
                 [r.error for r in results if not r.ok]
             t_first, h2d1, d2h1 = stamps[0]
             e2e_steps = e2e_new - 1
-            e2e = {"value": BATCH * e2e_steps / (t_end - t_first), "unit": "tokens/s",
+            e2e = {"value": args.batch * e2e_steps / (t_end - t_first), "unit": "tokens/s",
                    "h2d_bytes_per_step": (llm.backend.h2d_bytes + engine.h2d_bytes - h2d1) // e2e_steps,
                    "d2h_bytes_per_step": (llm.backend.d2h_bytes - d2h1) // e2e_steps,
                    "steps": e2e_steps}
@@ -264,12 +278,12 @@ def main() -> int:
         clocks.stop()
 
     line = {
-        "metric": "decode tok/s @ batch 8, context 4096 (SmolLM2-135M bf16)",
+        "metric": f"decode tok/s @ batch {args.batch}, context {CONTEXT} ({shape_name} bf16)",
         "value": main_point["tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": main_point["ms_per_step"], "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded random weights and token ids)",
         "impl": "ours",
-        "config": {"model": "SmolLM2-135M shape", "global_batch": args.batch, "seq_len": CONTEXT,
+        "config": {"model": f"{shape_name} shape", "global_batch": args.batch, "seq_len": CONTEXT,
                    "parallelism": "single GPU", "prompt_len": PROMPT, "layers": cfg["num_hidden_layers"],
                    "layers_of_shape": full_layers, "hidden_size": cfg["hidden_size"],
                    "intermediate_size": cfg["intermediate_size"], "heads": cfg["num_attention_heads"],

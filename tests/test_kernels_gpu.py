@@ -32,6 +32,22 @@ def ops():
     return o
 
 
+def away_from_bf16_ties(hidden, norm_weight, eps):
+    """`hidden` with the few values moved whose normed value lies within 3e-6 (relative)
+    of a bfloat16 rounding boundary: there the kernel's float32 norm and the float64
+    reference may round to different bfloat16 values, and one such value shifts a whole
+    row of products by more than the float32 bound.  With thousands of values per row
+    some lie that close; the kernels are compared on inputs where rounding is decided."""
+    hidden = hidden.clone()
+    for _ in range(50):
+        x = P.rms_norm(hidden, norm_weight, eps)
+        risky = (x * (1 + 3e-6)).bfloat16() != (x * (1 - 3e-6)).bfloat16()
+        if not bool(risky.any()):
+            return hidden
+        hidden[risky] *= 1.003
+    raise AssertionError("could not move the values away from rounding boundaries")
+
+
 @pytest.mark.parametrize("dtype", list(DT))
 def test_embed_and_bad_ids(dtype):
     o = ops()
@@ -487,15 +503,19 @@ def test_attention_decode_kernel(nq, nkv, d, window):
 
 
 @pytest.mark.parametrize("m", [1, 6, 16, 50])
-@pytest.mark.parametrize("n,k", [(8, 16), (1000, 80), (49152, 576)])
+@pytest.mark.parametrize("n,k", [(8, 16), (1000, 80), (49152, 576), (3000, 2048)])
 def test_gemv_argmax_epilogue_picks_moves_on_and_can_write_logits(m, n, k):
     o = ops()
+    if not o.gemv_takes(m, n, k, o.EPI_ARGMAX, DEV):
+        assert m > 32 and k == 2048  # 64 rows of x of this length do not fit shared memory
+        return
     g = torch.Generator().manual_seed(m + n)
     w = (torch.randn(n, k, generator=g) / math.sqrt(k)).bfloat16()
     w[n // 2] = w[3]  # two equal logits in every row: the lower index must win when they lead
     hidden = torch.randn(m, k, generator=g)
     hidden[0] = w[3].float() * 4  # row 0 is led by index 3 (and its twin)
     nw = torch.ones(k)
+    hidden = away_from_bf16_ties(hidden, nw, 1e-5)
     want_logits = P.linear(P.rms_norm(hidden, nw, 1e-5).bfloat16(), w)
     want = [P.argmax_lowest(r) for r in want_logits]
     assert want[0] == 3
