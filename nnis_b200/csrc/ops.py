@@ -8,6 +8,7 @@ here computes; without the compiled library nothing works, on purpose.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -231,7 +232,7 @@ def sample_temperature(logits: torch.Tensor, temperature: torch.Tensor, rng_stat
 
 EPI_STORE, EPI_STORE_F32, EPI_ADD_F32, EPI_GATED, EPI_QKV, EPI_ARGMAX = 0, 1, 2, 3, 4, 5
 # programmatic dependent launch between the decode kernels (NNIS_PDL=0 turns it off)
-PDL = 0 if __import__("os").environ.get("NNIS_PDL", "1") == "0" else 1
+PDL = 0 if os.environ.get("NNIS_PDL", "1") == "0" else 1
 _status = {}
 
 
@@ -267,7 +268,7 @@ def sm_count(device) -> int:
 # kernel; with more rows (the fourth tile of 16) a norm kernel and the tcgen05 product
 # are faster, because every CTA of the projection kernel normalises and holds all
 # rows for itself.
-DECODE_GEMV_ROWS = int(__import__("os").environ.get("NNIS_DECODE_GEMV_ROWS", "48"))
+DECODE_GEMV_ROWS = int(os.environ.get("NNIS_DECODE_GEMV_ROWS", "48"))
 
 
 def gemv_takes(m: int, n: int, k: int, epilogue: int = EPI_STORE, device=None) -> bool:
@@ -411,8 +412,8 @@ def attention_decode_mma_takes(head_dim: int, page_size: int) -> bool:
 
 _decode_mma_resident: dict = {}
 # 1: the decode attention may run with one stage less where the wave model favours it
-DECODE_STAGE_CHOICE = int(__import__("os").environ.get("NNIS_DECODE_STAGE_CHOICE", "1")) \
-    and __import__("os").environ.get("NNIS_DECODE_FILL") is None
+DECODE_STAGE_CHOICE = int(os.environ.get("NNIS_DECODE_STAGE_CHOICE", "1")) \
+    and os.environ.get("NNIS_DECODE_FILL") is None
 
 
 def attention_decode_mma_stages(head_dim: int) -> int:
@@ -492,7 +493,7 @@ def attention_prefill_mma(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor,
 
 
 WIDE_QUERY_TILE = 128  # queries per CTA of attention_prefill_tc
-TC_ATTENTION = 0 if __import__("os").environ.get("NNIS_TC_ATTENTION", "1") == "0" else 1
+TC_ATTENTION = 0 if os.environ.get("NNIS_TC_ATTENTION", "1") == "0" else 1
 
 
 def attention_prefill_tc_takes(head_dim: int, page_size: int, q_stride: int) -> bool:
@@ -604,7 +605,7 @@ def mma_ticket_count(n: int, heads: int, kv_heads: int) -> int:
     return n * kv_heads * (-(-(heads // kv_heads) // 16))
 
 
-TC_GEMM = 0 if __import__("os").environ.get("NNIS_TC_GEMM", "1") == "0" else 1
+TC_GEMM = 0 if os.environ.get("NNIS_TC_GEMM", "1") == "0" else 1
 
 
 def gemm_tc_takes(m: int, n: int, k: int) -> bool:
