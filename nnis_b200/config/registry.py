@@ -44,6 +44,15 @@ def config_from_dict(raw: Mapping[str, Any]):
 
 def read_config(model_dir: str):
     path = os.path.join(model_dir, "config.json")
+    if not os.path.isfile(path):
+        # NNIS's own folder carries its configuration in model.json
+        from ..weights.nnis_directory import (NnisDirectoryError, config_of_manifest, is_nnis_directory,
+                                              read_manifest)
+        if is_nnis_directory(model_dir):
+            try:
+                return config_from_dict(config_of_manifest(read_manifest(model_dir)))
+            except NnisDirectoryError as e:
+                raise ConfigError(str(e)) from None
     try:
         with open(path, "r", encoding="utf-8") as f:
             raw = json.load(f)

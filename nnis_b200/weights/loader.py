@@ -2,7 +2,8 @@
 
 The model says which tensors it wants (``WeightSpec`` by full name); the loader
 finds them in ``model.safetensors`` or in the shards that
-``model.safetensors.index.json`` names, and raises a single ``WeightError``
+``model.safetensors.index.json`` names (or, in a folder without those, in NNIS's
+own ``model.json`` with its raw tensor files: ``nnis_directory.py``), and raises a single ``WeightError``
 listing missing tensors, unexpected tensors and wrong shapes or dtypes.  NNIS
 reports the same faults one at a time
 (crates/nnis-model/src/safetensors_loader.rs:389-438 files, :711-724 shape and
@@ -23,6 +24,7 @@ from typing import Dict, Iterable, List, Mapping, Tuple
 
 import torch
 
+from .nnis_directory import MANIFEST, NnisDirectoryError, NnisDirectorySource
 from .safetensors_io import SafetensorsError, SafetensorsFile
 
 SINGLE_FILE = "model.safetensors"
@@ -65,6 +67,11 @@ def _discover(model_dir: str) -> List[str]:
     return shards
 
 
+def _has_safetensors(model_dir: str) -> bool:
+    return os.path.isfile(os.path.join(model_dir, SINGLE_FILE)) or \
+        os.path.isfile(os.path.join(model_dir, INDEX_FILE))
+
+
 def _kept_dtype(role: str, stored: torch.dtype, compute: torch.dtype) -> torch.dtype:
     if role == "table":
         return torch.int32
@@ -78,11 +85,14 @@ def _open_and_check(model_dir: str, wanted: Mapping[str, WeightSpec]):
     model wants: (open files, file of each tensor, ignored names) or one WeightError."""
     files = []
     try:
-        for path in _discover(model_dir):
-            if os.path.islink(path):
-                raise WeightError(f"{path}: symbolic links are not followed")
-            files.append(SafetensorsFile(path))
-    except SafetensorsError as e:
+        if not _has_safetensors(model_dir) and os.path.isfile(os.path.join(model_dir, MANIFEST)):
+            files.append(NnisDirectorySource(model_dir))  # NNIS's own folder: model.json + raw files
+        else:
+            for path in _discover(model_dir):
+                if os.path.islink(path):
+                    raise WeightError(f"{path}: symbolic links are not followed")
+                files.append(SafetensorsFile(path))
+    except (SafetensorsError, NnisDirectoryError) as e:
         for f in files:
             f.close()
         raise WeightError(str(e)) from None

@@ -193,3 +193,80 @@ def test_sharded_folder_and_float16_refusal(tmp_path):
     write_safetensors(os.path.join(d, "s1.safetensors"), {n: tensors[n] for n in names[:half]})
     with pytest.raises(WeightError, match="float16"):
         load_weights(d, wanted, torch.float32, torch.device("cpu"))
+
+
+def _tiny_a_as_nnis_directory(tmp_path):
+    from nnis_b200.weights import write_nnis_directory
+    d = make_model(str(tmp_path / "hf"), TINY_A, seed=2)
+    with SafetensorsFile(os.path.join(d, "model.safetensors")) as f:
+        tensors = {n: f.tensor(n) for n in f.names()}
+    cfg = json.load(open(os.path.join(d, "config.json")))
+    return d, cfg, tensors, write_nnis_directory(cfg, tensors, str(tmp_path / "nnis"))
+
+
+def test_nnis_model_folder_reads_as_the_same_model(tmp_path):
+    """model.json + raw files (NNIS's own folder): its names and transposed projections come
+    out as the tensors of the Hugging Face folder it was written from; the tied head is a
+    tensor of its own there."""
+    hf_dir, cfg, tensors, nnis_dir = _tiny_a_as_nnis_directory(tmp_path)
+    manifest = json.load(open(os.path.join(nnis_dir, "model.json")))
+    assert manifest["format"] == "nnis-model" and manifest["version"] == 1
+    by_name = {e["name"]: e for e in manifest["tensors"]}
+    H, V = TINY_A["hidden_size"], TINY_A["vocab_size"]
+    kvw = H // TINY_A["num_attention_heads"] * TINY_A["num_key_value_heads"]
+    assert by_name["layers.0.k_proj"]["shape"] == [H, kvw]  # [in, out]
+    assert by_name["token_embedding"]["shape"] == [V, H] and by_name["lm_head"]["shape"] == [H, V]
+    config = read_config(nnis_dir)
+    assert not config.tie_word_embeddings and config.hidden_size == H and config.vocab_size == V
+    assert config.rms_norm_eps == pytest.approx(TINY_A["rms_norm_eps"])
+    wanted = DecoderModel.weight_specs_of(config.to_spec())
+    got = load_weights(nnis_dir, wanted, torch.float32, torch.device("cpu"))
+    for name, t in tensors.items():
+        assert torch.equal(got[name], t.float()), name
+    assert torch.equal(got["lm_head.weight"], tensors["model.embed_tokens.weight"].float())
+    from nnis_b200.weights import check_weights
+    assert check_weights(nnis_dir, wanted)["weight_files"] == ["model.json"]
+
+
+def test_nnis_model_folder_faults(tmp_path):
+    from nnis_b200.weights import NnisDirectoryError, write_nnis_directory
+    hf_dir, cfg, tensors, nnis_dir = _tiny_a_as_nnis_directory(tmp_path)
+    path = os.path.join(nnis_dir, "model.json")
+    good = json.load(open(path))
+
+    def with_change(change):
+        m = json.loads(json.dumps(good))
+        change(m)
+        json.dump(m, open(path, "w"))
+
+    for change, word in ((lambda m: m.update(format="other"), "is not 'nnis-model'"),
+                         (lambda m: m.update(version=2), "supported version is 1"),
+                         (lambda m: m["tensors"][0].update(file="../x.bin"), "parent traversal"),
+                         (lambda m: m["tensors"][0].update(file="/abs.bin"), "parent traversal"),
+                         (lambda m: m["tensors"].append(dict(m["tensors"][0])), "duplicate tensor name"),
+                         (lambda m: m["tensors"][0].update(shape=[0, 3]), "non-zero dimensions"),
+                         (lambda m: m["tensors"][0].update(dtype="f16"), "not f32 or bf16"),
+                         (lambda m: m["config"].pop("rope_theta"), "config lacks rope_theta")):
+        with_change(change)
+        with pytest.raises(ConfigError, match=word):
+            read_config(nnis_dir)
+    # a file of the wrong length, an unknown tensor and a missing one: the loader's one error
+    with_change(lambda m: m["tensors"][0].update(shape=[m["tensors"][0]["shape"][0] + 1] + m["tensors"][0]["shape"][1:]))
+    wanted = DecoderModel.weight_specs_of(config_from_dict({**cfg, "tie_word_embeddings": False}).to_spec())
+    with pytest.raises(WeightError, match="requires"):
+        load_weights(nnis_dir, wanted, torch.float32, torch.device("cpu"))
+
+    def rename(m):
+        entry = next(e for e in m["tensors"] if e["name"] == "layers.1.up_proj")
+        entry["name"] = "layers.1.sideways_proj"
+    with_change(rename)
+    with pytest.raises(WeightError) as e:
+        load_weights(nnis_dir, wanted, torch.float32, torch.device("cpu"))
+    assert "missing (1): model.layers.1.mlp.up_proj.weight" in str(e.value)
+    assert "unexpected (1): layers.1.sideways_proj" in str(e.value)
+    # biases have no place in the format
+    d = make_model(str(tmp_path / "b"), TINY_B, seed=2)
+    with SafetensorsFile(os.path.join(d, "model.safetensors")) as f:
+        with_bias = {n: f.tensor(n) for n in f.names()}
+    with pytest.raises(NnisDirectoryError, match="no place"):
+        write_nnis_directory(json.load(open(os.path.join(d, "config.json"))), with_bias, str(tmp_path / "nb"))

@@ -155,3 +155,20 @@ def test_temperature_sampling_on_the_device_follows_the_seeded_draws(model_dirs)
         assert t == want or abs(cdf[t] - u) < 1e-9 * cdf[-1]
         logits = session.decode_one(t)
     session.close()
+
+
+def test_nnis_model_folder_generates_like_its_hugging_face_twin(model_dirs, tmp_path):
+    """A model.json + raw-files folder (NNIS's own format) loads and generates the same tokens."""
+    from nnis_b200 import LLM
+    from nnis_b200.weights import SafetensorsFile, write_nnis_directory
+    d = model_dirs["A"]  # no biases: the format has no place for them
+    with SafetensorsFile(os.path.join(d, "model.safetensors")) as f:
+        tensors = {n: f.tensor(n) for n in f.names()}
+    twin = write_nnis_directory(read_config_json(d), tensors, str(tmp_path / "nnis"))
+    prompts = [[5, 9, 1, 200, 33], [7]]
+    for dtype in ("float32", "bfloat16"):
+        want = LLM(d, dtype=dtype, max_tokens=64 * 8, max_batch=2).generate(prompts, max_new_tokens=8,
+                                                                          stop_token_ids=())
+        got = LLM(twin, dtype=dtype, max_tokens=64 * 8, max_batch=2).generate(prompts, max_new_tokens=8,
+                                                                            stop_token_ids=())
+        assert [r.token_ids for r in got] == [r.token_ids for r in want]
