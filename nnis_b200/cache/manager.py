@@ -182,6 +182,35 @@ class CacheManager:
                             g.pool.give(table[i])
                             table[i] = -1
 
+    def truncate(self, slot: int, length: int) -> None:
+        """Forget the positions from ``length`` on (NNIS: crates/nnis-rt/src/kv_cache.rs:181-183):
+        the pages beyond go back to their pools; what a kept page holds beyond the
+        length is never read and is written over by the next tokens.  Refused, with
+        nothing changed, where going back is not possible: fixed-size state has no
+        earlier value, and a windowed group may have given back pages that the
+        positions after ``length`` would read again."""
+        if not self.slots.is_held(slot):
+            raise SlotError(f"slot {slot} is not held")
+        if not 0 <= length <= self.lengths[slot]:
+            raise SlotError(f"slot {slot}: cannot truncate {self.lengths[slot]} positions to {length}")
+        if length == self.lengths[slot]:
+            return
+        if self._states:
+            raise SlotError("a sequence with fixed-size state cannot go back to an earlier length")
+        keep = -(-length // PAGE_SIZE)
+        for gi, g in enumerate(self.groups):
+            table = g.tables[slot]
+            if any(page < 0 for page in table[g.first_needed_page(length):keep]):
+                raise SlotError(f"slot {slot}: group {gi} (window {g.window}) has given back pages that "
+                                f"position {length} would read")
+        for g in self.groups:
+            table = g.tables[slot]
+            for page in table[keep:]:
+                if page >= 0:
+                    g.pool.give(page)
+            del table[keep:]
+        self.lengths[slot] = length
+
     def page_table(self, group: int, slot: int) -> List[int]:
         return self.groups[group].tables[slot]
 

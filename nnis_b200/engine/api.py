@@ -259,6 +259,11 @@ class InferenceSession:
         self.engine.release_slot(self.slot)
         self.slot = self.engine.acquire_slot()
 
+    def truncate(self, position: int) -> None:
+        """Back to ``position`` tokens, as NNIS's sessions allow
+        (crates/nnis-core/src/session.rs:430-445): the next ``decode_one`` follows them."""
+        self.engine.truncate(self.slot, int(position))
+
     def close(self) -> None:
         if self.slot is not None:
             self.engine.release_slot(self.slot)

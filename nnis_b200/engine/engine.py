@@ -115,6 +115,11 @@ class Engine:
     def release_slot(self, slot: int) -> None:
         self.cache.release(slot)
 
+    def truncate(self, slot: int, length: int) -> None:
+        """The sequence of ``slot`` forgets its positions from ``length`` on; its next
+        step goes on from there (see ``CacheManager.truncate`` for when that is refused)."""
+        self.cache.truncate(slot, length)
+
     # -- the step -----------------------------------------------------------
     def _stage(self, parts: List[np.ndarray], workspace: Optional[Workspace] = None) -> torch.Tensor:
         """Int arrays -> one pinned buffer -> one async copy -> int32 device tensor."""

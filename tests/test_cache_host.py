@@ -136,6 +136,10 @@ def test_random_traffic_loses_nothing():
                 live[s] = n
             except CacheFull:
                 pass
+        elif r < 0.9 and live:
+            s = rng.choice(list(live))
+            live[s] = rng.randrange(0, live[s] + 1)
+            c.truncate(s, live[s])
         elif live:
             s = rng.choice(list(live))
             c.release(s)
@@ -143,3 +147,50 @@ def test_random_traffic_loses_nothing():
         c.check()
         assert c.usage()["pages_held"] == [sum(-(-n // PAGE_SIZE) for n in live.values())]
         assert c.usage()["live_tokens"] == sum(live.values())
+
+
+def test_truncate_gives_pages_back_and_refuses_what_cannot_be_undone():
+    c = make(max_tokens=PAGE_SIZE * 8)
+    s = c.acquire()
+    c.reserve([s], [200])
+    c.commit([s], [200])
+    kept = list(c.page_table(0, s)[:2])
+    with pytest.raises(SlotError, match="cannot truncate"):
+        c.truncate(s, 201)
+    with pytest.raises(SlotError, match="cannot truncate"):
+        c.truncate(s, -1)
+    c.truncate(s, 200)  # nothing to do
+    c.truncate(s, 65)   # position 64 stays: two pages
+    assert c.length(s) == 65 and c.page_table(0, s) == kept and c.usage()["pages_held"] == [2]
+    c.truncate(s, 64)
+    assert c.page_table(0, s) == kept[:1]
+    c.reserve([s], [130])  # grows again from there
+    c.commit([s], [130])
+    assert c.length(s) == 130 and len(c.page_table(0, s)) == 3
+    c.truncate(s, 0)
+    assert c.usage()["pages_held"] == [0] and c.length(s) == 0
+    c.check()
+    other = c.acquire()
+    c.release(other)
+    with pytest.raises(SlotError, match="not held"):
+        c.truncate(other, 0)
+    # a windowed group: back to where the window still has its pages, not further
+    w = make(max_tokens=PAGE_SIZE * 8, requests=[KVRequest(1, 16, 70)])
+    s = w.acquire()
+    w.reserve([s], [300])
+    w.commit([s], [300])  # pages 0..2 were given back
+    w.truncate(s, 280)    # position 280 reads keys 211..: page 3 on
+    assert w.length(s) == 280 and w.usage()["pages_held"] == [2]
+    before = list(w.page_table(0, s))
+    with pytest.raises(SlotError, match="given back pages"):
+        w.truncate(s, 250)  # would read keys 181..: page 2 is gone
+    assert w.length(s) == 280 and w.page_table(0, s) == before
+    w.check()
+    # fixed-size state has no earlier value
+    st = make(requests=[KVRequest(1, 16), StateRequest((4,))])
+    s = st.acquire()
+    st.reserve([s], [10])
+    st.commit([s], [10])
+    with pytest.raises(SlotError, match="fixed-size state"):
+        st.truncate(s, 5)
+    assert st.length(s) == 10

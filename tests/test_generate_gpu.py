@@ -172,3 +172,34 @@ def test_nnis_model_folder_generates_like_its_hugging_face_twin(model_dirs, tmp_
         got = LLM(twin, dtype=dtype, max_tokens=64 * 8, max_batch=2).generate(prompts, max_new_tokens=8,
                                                                             stop_token_ids=())
         assert [r.token_ids for r in got] == [r.token_ids for r in want]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_session_truncates_and_goes_on(model_dirs, dtype):
+    """Back to an earlier length, then other tokens: the logits are those of the new
+    sequence as a whole, across a page boundary of the cache and within a page."""
+    import numpy as np
+    import torch
+
+    from helpers import check_logits
+    from nnis_b200 import LLM
+    d = model_dirs["B"]
+    cfg = read_config_json(d)
+    bf = dtype == "bfloat16"
+    w = load_plain_weights(d, as_bf16=bf)
+    llm = LLM(d, dtype=dtype, max_tokens=64 * 8, max_batch=2)
+    session = llm.new_session()
+    first = [(7 * i + 3) % cfg["vocab_size"] for i in range(70)]
+    session.prefill(first)
+    for t in (11, 12, 13):
+        session.decode_one(t)
+    for back_to, tail in ((60, [21, 22, 23, 24, 25, 26]), (65, [31]), (3, [41, 42])):
+        session.truncate(back_to)
+        assert session.position() == back_to
+        got = [session.decode_one(t) for t in tail]
+        want = P.forward(cfg, w, first[:back_to] + tail, bf)[back_to:]
+        check_logits(np.stack(got), want, dtype, f"after truncating to {back_to}")
+        first = first[:back_to] + tail
+    session.close()
+    llm.engine.cache.check()
+    assert llm.engine.cache.usage()["pages_held"] == [0]
