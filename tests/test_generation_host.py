@@ -1,5 +1,7 @@
 """The generation loop's decisions with a scripted backend, the host sampler,
 and the command line's rules (no GPU)."""
+import os
+
 import numpy as np
 import pytest
 
@@ -322,3 +324,71 @@ def test_process_entry_point_checks_bounds_and_records(tmp_path):
         execute(**ok, nnis_bin=script("hang", "time.sleep(60)\n"), timeout_seconds=0.5)
     assert time.monotonic() - t0 < 20
     assert not [n for n in os.listdir(tmp_path) if ".tmp-" in n]
+
+
+def test_replay_drives_the_step_function_and_keeps_slots(tmp_path, monkeypatch):
+    """The replay loop on a scripted engine: a slot per request from its first step to its
+    `end`, slots used again, logits written in the order of entries and of `want`, a report
+    for every step, and an error for a request that ends without having started."""
+    import json
+
+    import torch
+
+    from nnis_b200.engine import replay as R
+
+    class Stream:
+        def synchronize(self):
+            pass
+    monkeypatch.setattr(torch.cuda, "current_stream", lambda *a, **k: Stream())
+
+    class ScriptedEngine:
+        vocab = 5
+
+        def __init__(self):
+            self.free, self.held, self.calls, self.lengths = [1, 0], set(), [], {}
+
+        def acquire_slot(self):
+            slot = self.free.pop()
+            self.held.add(slot)
+            self.lengths[slot] = 0
+            return slot
+
+        def release_slot(self, slot):
+            self.held.remove(slot)
+            self.free.append(slot)
+
+        def step(self, batch):
+            rows = []
+            for s in batch:
+                assert s.slot in self.held
+                for w in s.want:  # a row says which slot, position and token it is for
+                    rows.append([s.slot, self.lengths[s.slot] + w, s.tokens[w], 0, 0])
+                self.lengths[s.slot] += len(s.tokens)
+            self.calls.append([(s.slot, list(s.tokens)) for s in batch])
+            return torch.tensor(rows, dtype=torch.float32).reshape(len(rows), self.vocab)
+
+        def check_status(self):
+            pass
+
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": [5, 17, 3], "want": [0, 2]},
+                                {"id": "b", "tokens": [9], "want": []}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": [4], "want": [0]}, {"id": "b", "tokens": [8], "want": [0]}],
+         "end": ["b"]},
+        {"step": 2, "entries": [{"id": "a", "tokens": [6], "want": []}], "end": ["a"]},
+        {"step": 7, "entries": [{"id": "c", "tokens": [1, 2], "want": [1]}], "end": ["c"]},
+    ]
+    engine, done = ScriptedEngine(), []
+    out = str(tmp_path / "out")
+    assert R.replay(engine, [json.dumps(s) for s in steps] + ["", "  "], out, done.append) == 4
+    assert done == [0, 1, 2, 7] and not engine.held
+    read = lambda n: np.fromfile(f"{out}/{n}.f32", dtype="<f4").reshape(-1, 5)[:, :3].tolist()
+    a, b = engine.calls[0][0][0], engine.calls[0][1][0]
+    assert a != b
+    assert read(0) == [[a, 0, 5], [a, 2, 3]]
+    assert read(1) == [[a, 3, 4], [b, 1, 8]]
+    assert sorted(os.listdir(out)) == ["0.f32", "1.f32", "7.f32"]  # step 2 wanted nothing
+    c = engine.calls[3][0][0]
+    assert c in (a, b) and read(7) == [[c, 1, 2]]  # a slot given back is used again, from length 0
+    with pytest.raises(R.StepError, match="never started"):
+        R.replay(ScriptedEngine(), [json.dumps({"step": 0, "entries": [], "end": ["x"]})], out)
