@@ -362,7 +362,7 @@ def test_gemv_plain_epilogues_and_norm_prologue(m, n, k):
 
 
 @pytest.mark.parametrize("m", [1, 8, 24])
-@pytest.mark.parametrize("n,k", [(4096, 2048), (1544, 4096), (2048, 8192), (520, 6144)])
+@pytest.mark.parametrize("n,k", [(4096, 2048), (1544, 4096), (2048, 8192), (520, 6144), (2400, 2080)])
 def test_gemv_long_rows_in_chunks_and_slices(m, n, k):
     """Rows of K too long for whole-row weight stages stream in chunks; rows of x
     too long for shared memory are taken by the adding epilogue alone, slice by slice."""
@@ -380,7 +380,9 @@ def test_gemv_long_rows_in_chunks_and_slices(m, n, k):
     assert o.gemv_takes(m, n, k, o.EPI_ADD_F32, DEV)
     whole = o.gemv_takes(m, n, k, o.EPI_STORE_F32, DEV)
     assert whole or o.gemv_slices(m, n, k, DEV) > 1
-    assert whole == (k * ((m + 15) // 16) <= 4096)  # all of x has to fit shared memory
+    # all of x has to fit shared memory beside the weight stages
+    assert whole or k * ((m + 15) // 16) > 4096
+    assert not whole or k < 8192
     o.gemv_bf16(w.to(DEV), bias.to(DEV), acc, o.EPI_ADD_F32, x=x.to(DEV))
     close(acc, base.double() + want, "float32", "gemv add in slices")
     if not whole:
@@ -393,6 +395,7 @@ def test_gemv_long_rows_in_chunks_and_slices(m, n, k):
     hidden = torch.randn(m + 3, k, generator=g) * 2
     hidden[:, k - 3] = 9.0
     nw = 1 + 0.1 * torch.randn(k, generator=g)
+    hidden = away_from_bf16_ties(hidden, nw, 1e-5)
     rows = torch.randperm(m + 3, generator=g)[:m].to(torch.int32)
     normed = P.rms_norm(hidden[rows.long()], nw, 1e-5).bfloat16()
     o.gemv_bf16(w.to(DEV), None, out32, o.EPI_STORE_F32, hidden=hidden.to(DEV),
