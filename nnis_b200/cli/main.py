@@ -24,8 +24,10 @@ USAGE = """Usage:
   nnis generate --model DIR [--tokenizer FILE] --prompt TEXT | --prompt-ids IDS [--device N] [--max-new-tokens N] [--dtype bfloat16|float32] [--sample --seed U64] [--temperature F] [--top-k N] [--top-p F] [--stream]
   nnis generate-batch --model DIR [--tokenizer FILE] --prompt TEXT [--prompt TEXT ...] | --prompt-ids IDS [--prompt-ids IDS ...] --seed U64 [--seed U64 ...] [--device N] [--max-new-tokens N] [--dtype bfloat16|float32] [--temperature F] [--top-k N] [--top-p F] [--json]
   nnis validate --model DIR [--tokenizer FILE] [--json] [--output FILE]
+  nnis random-model --config FILE --seed U64 --out DIR [--format hf|nnis]
 
 `validate` checks config.json, the safetensors files (tensor names, shapes and dtypes against the model that config.json names) and, when a tokenizer is given or DIR/tokenizer.json exists, that its ids fit the vocabulary; it needs no GPU and reads no tensor. `--output FILE` requires `--json` and writes the report there, never over an existing file.
+`random-model` writes a model folder with seeded random weights from a config.json (`hf`: config.json + model.safetensors; `nnis`: model.json + raw tensor files); it needs no GPU.
 
 Default decoding on `generate` is greedy. Opt-in `--sample` requires `--seed`. Optional `--temperature`, `--top-k`, and `--top-p` apply only with `--sample`. `--stream` is valid only with `--sample` and prints each token as it is emitted. `generate-batch` requires one `--seed` per prompt and always samples; `--json` emits versioned JSON. CUDA device ordinal defaults to 0."""
 
@@ -52,6 +54,8 @@ class GenerateArgs:
     top_p: Optional[float] = None
     command: str = "generate"
     output: Optional[str] = None
+    config_file: Optional[str] = None
+    folder_format: str = "hf"
 
 
 def _positive_float(flag: str, raw: str) -> float:
@@ -91,6 +95,8 @@ def parse_args(argv: List[str]) -> Optional[GenerateArgs]:
     command = argv[0]
     if command == "validate":
         return _parse_validate(argv[1:])
+    if command == "random-model":
+        return _parse_random_model(argv[1:])
     if command not in ("generate", "generate-batch"):
         raise UsageError(f"unknown command {command!r}")
     a = GenerateArgs(command=command)
@@ -202,6 +208,62 @@ def _parse_validate(rest: List[str]) -> Optional[GenerateArgs]:
     return a
 
 
+def _parse_random_model(rest: List[str]) -> Optional[GenerateArgs]:
+    a = GenerateArgs(command="random-model")
+    seen = set()
+    it = iter(rest)
+    for flag in it:
+        if flag in ("-h", "--help"):
+            return None
+        if flag not in ("--config", "--seed", "--out", "--format"):
+            raise UsageError(f"unknown random-model argument {flag!r}")
+        try:
+            value = next(it)
+        except StopIteration:
+            raise UsageError(f"{flag} needs a value") from None
+        if flag in seen:
+            raise UsageError(f"{flag} given twice")
+        seen.add(flag)
+        if flag == "--config":
+            a.config_file = value
+        elif flag == "--seed":
+            a.seeds = [_unsigned("--seed", value)]
+        elif flag == "--out":
+            a.output = value
+        elif value in ("hf", "nnis"):
+            a.folder_format = value
+        else:
+            raise UsageError(f"--format must be hf or nnis; got {value!r}")
+    for flag, given in (("--config", a.config_file), ("--seed", a.seeds), ("--out", a.output)):
+        if not given:
+            raise UsageError(f"{flag} is required")
+    return a
+
+
+def random_model(a: GenerateArgs, out=sys.stdout) -> int:
+    """A model folder with seeded random weights from the configuration in ``--config``."""
+    import os
+
+    from ..weights import SafetensorsFile, write_nnis_directory, write_random_model
+    with open(a.config_file, "r", encoding="utf-8") as f:
+        config = json.load(f)
+    if os.path.lexists(a.output) and (not os.path.isdir(a.output) or os.listdir(a.output)):
+        raise ValueError(f"{a.output} exists and is not an empty folder")
+    if a.folder_format == "hf":
+        write_random_model(config, a.seeds[0], a.output)
+    else:
+        import tempfile
+        with tempfile.TemporaryDirectory() as tmp:
+            write_random_model(config, a.seeds[0], tmp)
+            with SafetensorsFile(os.path.join(tmp, "model.safetensors")) as f:
+                tensors = {n: f.tensor(n) for n in f.names()}
+            with open(os.path.join(tmp, "config.json"), "r", encoding="utf-8") as f:
+                written = json.load(f)
+        write_nnis_directory(written, tensors, a.output)
+    out.write(f"{a.output}\n")
+    return 0
+
+
 VALIDATE_SCHEMA = "nnis_b200.model-preflight@1"
 
 
@@ -269,6 +331,8 @@ def _policy(a: GenerateArgs, seed: int):
 def run(a: GenerateArgs, out=sys.stdout) -> int:
     if a.command == "validate":
         return validate(a, out)
+    if a.command == "random-model":
+        return random_model(a, out)
     from ..engine.api import LLM
     from ..sampling import SAMPLING_POLICY_VERSION
     prompts = a.prompts if a.prompts else a.prompt_ids

@@ -392,3 +392,38 @@ def test_replay_drives_the_step_function_and_keeps_slots(tmp_path, monkeypatch):
     assert c in (a, b) and read(7) == [[c, 1, 2]]  # a slot given back is used again, from length 0
     with pytest.raises(R.StepError, match="never started"):
         R.replay(ScriptedEngine(), [json.dumps({"step": 0, "entries": [], "end": ["x"]})], out)
+
+
+def test_cli_random_model_writes_folders_that_validate(tmp_path):
+    import json
+
+    from helpers import TINY_A, TINY_B
+    from nnis_b200.cli.main import main
+    cfg = tmp_path / "a.json"
+    cfg.write_text(json.dumps(TINY_A))
+    for fmt in ("hf", "nnis"):
+        out = str(tmp_path / fmt)
+        assert main(["random-model", "--config", str(cfg), "--seed", "7", "--out", out, "--format", fmt]) == 0
+        assert main(["validate", "--model", out]) == 0
+        assert main(["random-model", "--config", str(cfg), "--seed", "7", "--out", out]) == 1  # not empty
+    assert sorted(os.listdir(tmp_path / "hf")) == ["config.json", "model.safetensors"]
+    assert "model.json" in os.listdir(tmp_path / "nnis")
+    # the same seed gives the same tensors in both forms
+    from nnis_b200.config import read_config
+    from nnis_b200.engine.model import DecoderModel
+    from nnis_b200.weights import load_weights
+    import torch
+    both = []
+    for fmt in ("hf", "nnis"):
+        d = str(tmp_path / fmt)
+        wanted = DecoderModel.weight_specs_of(read_config(d).to_spec())
+        both.append(load_weights(d, wanted, torch.float32, torch.device("cpu")))
+    for name, t in both[0].items():
+        assert torch.equal(t, both[1][name]), name
+    b = tmp_path / "b.json"
+    b.write_text(json.dumps(TINY_B))  # biases: no place in NNIS's own folder
+    assert main(["random-model", "--config", str(b), "--seed", "1", "--out", str(tmp_path / "b"), "--format", "nnis"]) == 1
+    for bad in (["random-model", "--seed", "1", "--out", "x"], ["random-model", "--config", "c", "--out", "x"],
+                ["random-model", "--config", "c", "--seed", "1", "--out", "x", "--format", "gguf"]):
+        with pytest.raises(UsageError):
+            parse_args(bad)
