@@ -89,3 +89,23 @@ def test_prefix_of_a_sequence_has_the_same_logits(tmp_path):
     assert float(full.abs().max()) > 0.1  # healthy weights give logits of some size
     rounded = P.forward(cfg, load_plain_weights(d, True), tokens, emulate_bf16=True)
     assert 0 < float((rounded - full).abs().max()) < 0.2 * float(full.abs().max())
+
+
+def test_bfloat16_rounding_is_to_nearest_even():
+    """The cases NNIS pins for its float32 -> bfloat16 conversion
+    (crates/nnis-rt/src/bf16.rs:32-49), for the conversion that the loader, the
+    random-weights mode and this file's bfloat16 emulation use."""
+    import numpy as np
+
+    def rounded(bits=None, value=None):
+        x = torch.tensor(np.array([bits], dtype=np.uint32).view(np.float32)) if bits is not None \
+            else torch.tensor([value], dtype=torch.float32)
+        return float(x.bfloat16().float())
+
+    one = int(np.array([1.0], dtype=np.float32).view(np.uint32)[0])
+    assert rounded(value=1.0) == 1.0 and rounded(value=0.0) == 0.0 and rounded(value=-2.5) == -2.5
+    assert rounded(bits=one + 0x8000) == 1.0            # an exact tie keeps the even mantissa
+    assert rounded(bits=one + 0x8001) == 1.0 + 2.0 ** -7  # just past the tie goes up
+    assert rounded(bits=one + 0x10000 + 0x8000) == 1.0 + 2.0 ** -6  # a tie above an odd mantissa goes up
+    assert rounded(value=float("inf")) == float("inf")
+    assert math.isnan(rounded(value=float("nan")))
