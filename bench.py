@@ -300,6 +300,11 @@ def main() -> int:
         "gpu_launches": main_point["launches"],
         "clocks": clocks.summary(windows),
     }
+    try:  # where the numbers were taken (NNIS's benchmarks carry such a record too)
+        line["environment"] = {"gpu": torch.cuda.get_device_name(0), "cuda": torch.version.cuda,
+                               "torch": torch.__version__, "python": sys.version.split()[0]}
+    except Exception:  # the record is a courtesy; the measurement stands without it
+        pass
     print(json.dumps(line))
     return 0
 
