@@ -14,7 +14,7 @@ def __getattr__(name):
     if name in ("LLM", "InferenceSession"):
         from .engine import api
         return getattr(api, name)
-    if name in ("GenerationConfig", "GenerationRequest", "GenerationResult"):
+    if name in ("GenerationConfig", "GenerationRequest", "GenerationResult", "StreamControl"):
         from .engine import generate
         return getattr(generate, name)
     if name == "SamplingConfig":

@@ -88,6 +88,10 @@ class CacheManager:
         self.pages_total = -(-max_tokens // PAGE_SIZE)
         self.slots = FreeList(max_slots, "slot")
         self.lengths: List[int] = [0] * max_slots
+        # counts what happened to a slot's page tables other than growth at their end
+        # (taken, given back, truncated): a copy of a table kept elsewhere is good only
+        # for the version it was made at
+        self.versions: List[int] = [0] * max_slots
         self.groups: List[_KVGroup] = []
         self._views: List[Optional[Union[KVView, StateView]]] = []
         by_key: Dict[Tuple[int, int, int], List[int]] = {}
@@ -123,6 +127,7 @@ class CacheManager:
     def acquire(self) -> int:
         slot = self.slots.take()
         self.lengths[slot] = 0
+        self.versions[slot] += 1
         for g in self.groups:
             g.tables[slot] = []
         for t in self._states:
@@ -137,6 +142,7 @@ class CacheManager:
                 if page >= 0:
                     g.pool.give(page)
         self.lengths[slot] = 0
+        self.versions[slot] += 1
         self.slots.give(slot)
 
     def length(self, slot: int) -> int:
@@ -210,6 +216,7 @@ class CacheManager:
                     g.pool.give(page)
             del table[keep:]
         self.lengths[slot] = length
+        self.versions[slot] += 1
 
     def page_table(self, group: int, slot: int) -> List[int]:
         return self.groups[group].tables[slot]

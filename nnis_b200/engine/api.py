@@ -24,7 +24,7 @@ from ..csrc import ops
 from .decode import GraphDecoder
 from .engine import Engine, SequenceStep, StepError
 from .generate import (DEFAULT_MAX_NEW_TOKENS, GenerationConfig, GenerationRequest,
-                       GenerationResult, Generator)
+                       GenerationResult, Generator, StreamControl)
 
 Prompt = Union[str, Sequence[int]]
 
@@ -224,9 +224,12 @@ class LLM:
     def generate(self, prompts: Sequence[Prompt], max_new_tokens: int = DEFAULT_MAX_NEW_TOKENS,
                  sampling: Union[None, SamplingConfig, Sequence[Optional[SamplingConfig]]] = None,
                  stop_token_ids: Optional[Sequence[int]] = None,
-                 on_token: Optional[Callable[[int, int], None]] = None) -> List[GenerationResult]:
+                 on_token: Optional[Callable[[int, int], Optional[StreamControl]]] = None
+                 ) -> List[GenerationResult]:
         """Greedy unless ``sampling`` is given (one policy for all prompts or one
-        per prompt).  ``stop_token_ids=None`` takes config.json's eos ids."""
+        per prompt).  ``stop_token_ids=None`` takes config.json's eos ids.
+        ``on_token(prompt index, token)`` sees tokens as they are emitted and may return
+        ``StreamControl.STOP`` to end that prompt's generation; the others go on."""
         stops = tuple(self.spec.stop_token_ids if stop_token_ids is None else stop_token_ids)
         if sampling is None or isinstance(sampling, SamplingConfig):
             sampling = [sampling] * len(prompts)
@@ -282,20 +285,39 @@ class InferenceSession:
         logits = self.engine.step([SequenceStep(self.slot, [int(token)], [0])])
         return logits[0].cpu().numpy()
 
-    def generate(self, input_ids: Sequence[int], generation: GenerationConfig) -> List[int]:
-        return self._generate(input_ids, generation, None)
+    def generate(self, input_ids: Sequence[int], generation: GenerationConfig,
+                 on_token: Optional[Callable[[int], Optional[StreamControl]]] = None,
+                 keep_context: bool = False) -> List[int]:
+        """Greedy generation on this session's own slot
+        (crates/nnis-model/src/runtime.rs:796-899).  Like NNIS it starts from an empty
+        session (``keep_context=True``: the prompt follows what the session holds) and
+        executes every emitted token, the last one and a stop token too, so that
+        afterwards ``position()`` is prompt + emitted tokens (runtime.rs:1264-1268) and
+        ``decode_one`` goes on from there."""
+        return self._generate(input_ids, generation, None, on_token, keep_context)
 
     def generate_sampled(self, input_ids: Sequence[int], generation: GenerationConfig,
-                         sampling: SamplingConfig) -> List[int]:
-        return self._generate(input_ids, generation, sampling)
+                         sampling: SamplingConfig, keep_context: bool = False) -> List[int]:
+        """crates/nnis-model/src/sampling.rs:216-255: seeded sampling on the host's
+        policy, every emitted token executed."""
+        return self._generate(input_ids, generation, sampling, None, keep_context)
 
-    def _generate(self, input_ids, generation, sampling) -> List[int]:
-        self.close()
-        try:
-            res = self.llm._generator.generate([GenerationRequest(list(input_ids), generation,
-                                                                  sampling)])[0]
-        finally:
-            self.slot = self.engine.acquire_slot()
+    def generate_sampled_streaming(self, input_ids: Sequence[int], generation: GenerationConfig,
+                                   sampling: SamplingConfig,
+                                   on_token: Callable[[int], Optional[StreamControl]],
+                                   keep_context: bool = False) -> List[int]:
+        """crates/nnis-model/src/streaming.rs:25-72: ``on_token(token)`` is called for
+        each emitted token once it has been executed; ``StreamControl.STOP`` ends the
+        generation cleanly and leaves the session ready to go on."""
+        return self._generate(input_ids, generation, sampling, on_token, keep_context)
+
+    def _generate(self, input_ids, generation, sampling, on_token, keep_context) -> List[int]:
+        if not keep_context:
+            self.reset()
+        request = GenerationRequest(list(input_ids), generation, sampling, slot=self.slot,
+                                    start=self.position())
+        callback = None if on_token is None else (lambda _i, t: on_token(t))
+        res = self.llm._generator.generate([request], callback)[0]
         if res.error is not None:
             raise ValueError(res.error)
         return res.token_ids

@@ -55,8 +55,9 @@ class GraphDecoder:
         self._host_state_free = torch.cuda.Event()
         self._host_state_free.record()
         # what the pinned copy holds per (group, row): the slot's table (a new list
-        # with every acquisition), how many of its pages, how many dropped in front;
-        # None: unknown (rows that were set one by one on the device)
+        # with every acquisition) and its version in the cache (a truncation shortens
+        # the list in place and later pages may differ), how many of its pages, how
+        # many dropped in front; None: unknown (rows that were set one by one on the device)
         self._mirror = None
         self.logits = torch.empty((rows, engine.spec.vocab_size), dtype=torch.float32, device=dev) \
             if want_logits else None
@@ -165,16 +166,18 @@ class GraphDecoder:
                 count = min(len(table), cols)
                 dropped = min(group.first_needed_page(cache.lengths[slot]), count) if group.window > 0 else 0
                 known = mirror[r]
-                if known is not None and known[0] is table and known[1] == count and known[2] == dropped:
+                version = cache.versions[slot]
+                same = known is not None and known[0] is table and known[3] == version
+                if same and known[1] == count and known[2] == dropped:
                     continue
                 line = st[base + r * cols:base + (r + 1) * cols]
-                if known is not None and known[0] is table and known[1] <= count and known[2] <= dropped:
+                if same and known[1] <= count and known[2] <= dropped:
                     line[known[1]:count] = table[known[1]:count]
                     line[known[2]:dropped] = -1
                 else:
                     line[:count] = table[:count]
                     line[count:] = -1
-                mirror[r] = (table, count, dropped)
+                mirror[r] = (table, count, dropped, version)
         ops.copy_async(self.state, self.host_state)
         self._host_state_free.record()
         if not self._host_tables_unknown:  # the partial-update path starts from scratch next time

@@ -6,12 +6,14 @@ same way as real ones.  NNIS has no such mode; its tests build weights by hand
 (crates/nnis-model/src/runtime.rs:1192-1261).
 
 Values: matrices N(0, std^2), norm weights 1 + N(0, norm_std^2) (or N(0,std^2)
-around zero when ``norm_center`` is 0), biases N(0, std^2); drawn in float32
-from one seeded CPU generator in the sorted order of tensor names, then stored
-in the configuration's dtype.
+around zero when ``norm_center`` is 0), biases N(0, std^2); each tensor is drawn
+in float32 from a CPU generator of its own, seeded with the seed and a hash of
+the tensor's name, so that a tensor's values depend on nothing but the seed, its
+name and its shape; then stored in the configuration's dtype.
 """
 from __future__ import annotations
 
+import hashlib
 import json
 import os
 from typing import Dict, Mapping, Optional
@@ -25,19 +27,26 @@ from .safetensors_io import write_safetensors
 _DTYPE = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 
 
+def tensor_seed(seed: int, name: str) -> int:
+    """The generator seed of one tensor: the model's seed xor the first eight bytes
+    of SHA-256 of the tensor's name (63 bits)."""
+    digest = hashlib.sha256(name.encode("utf-8")).digest()
+    return ((int(seed) & (2 ** 63 - 1)) ^ int.from_bytes(digest[:8], "little")) & (2 ** 63 - 1)
+
+
 def random_tensors(wanted: Mapping[str, WeightSpec], seed: int, std: float = 0.02,
                    norm_std: float = 0.01, norm_center: float = 1.0,
                    std_by_fan_in: bool = False) -> Dict[str, torch.Tensor]:
     """``std_by_fan_in`` draws projections with std / sqrt(fan_in): with std 1
     activations keep their size through the layers and attention scores are of
     order one, which tests of attention need."""
-    gen = torch.Generator(device="cpu")
-    gen.manual_seed(int(seed))
     out: Dict[str, torch.Tensor] = {}
     for name in sorted(wanted):
         spec = wanted[name]
         if spec.role == "table":
             raise ValueError(f"{name}: integer tables have no random mode")
+        gen = torch.Generator(device="cpu")
+        gen.manual_seed(tensor_seed(seed, name))
         x = torch.randn(spec.shape, generator=gen, dtype=torch.float32)
         if spec.init == "ones":
             out[name] = norm_center + x * norm_std

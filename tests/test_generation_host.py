@@ -124,13 +124,112 @@ def test_bad_requests_fail_alone():
     assert b.steps[0] == [(0, 1)]
 
 
-def test_a_failing_step_fails_its_batch_only_and_frees_slots():
-    b = ScriptedBackend(n_slots=2, fail_on_step=1)
+def test_a_failing_step_is_met_by_running_its_requests_alone():
+    """Each request is a failure domain of its own (crates/nnis-model/src/session_batch.rs:82-111):
+    when a step of a batch fails, its unfinished requests run again one by one; the one
+    that fails alone gets the error, the others their tokens, and no slot is lost."""
+    b = ScriptedBackend(n_slots=2, fail_on_step=1)  # fails once: both requests succeed alone
     reqs = [GenerationRequest([i + 1], GenerationConfig(3)) for i in range(3)]
     res = gen(b, max_batch=2).generate(reqs)
-    assert not res[0].ok and not res[1].ok and "boom" in res[0].error
-    assert res[2].ok and res[2].token_ids == expected([3], 3)
+    assert [r.token_ids for r in res] == [expected([i + 1], 3) for i in range(3)]
+    assert all(r.ok and r.finish_reason == "length" for r in res) and not b.held
+    assert b.steps[:3] == [[(0, 1), (1, 1)], "boom", [(0, 1)]]
+
+    class Poisoned(ScriptedBackend):  # every step that holds token 13 fails
+        def step(self, batch, need_logits=True):
+            if any(13 in list(s.tokens) + self.held.get(s.slot, []) for s in batch):
+                raise RuntimeError("poison")
+            return super().step(batch, need_logits)
+    b = Poisoned(n_slots=4)
+    reqs = [GenerationRequest([1], GenerationConfig(3)), GenerationRequest([13], GenerationConfig(3)),
+            GenerationRequest([2, 2], GenerationConfig(4))]
+    seen = []
+    res = gen(b).generate(reqs, on_token=lambda i, t: seen.append((i, t)))
+    assert res[0].token_ids == expected([1], 3) and res[2].token_ids == expected([2, 2], 4)
+    assert not res[1].ok and "poison" in res[1].error and res[1].finish_reason == "error"
+    assert not b.held and sorted(b.free) == list(range(4))
+    # the callback saw every token of the good requests once, in order
+    assert [t for i, t in seen if i == 0] == expected([1], 3)
+    assert [t for i, t in seen if i == 2] == expected([2, 2], 4)
+
+    # a failure in the middle of decoding: tokens already shown are not shown again
+    b = ScriptedBackend(n_slots=2, fail_on_step=2)
+    seen = []
+    reqs = [GenerationRequest([3], GenerationConfig(4)), GenerationRequest([4], GenerationConfig(4))]
+    res = gen(b).generate(reqs, on_token=lambda i, t: seen.append((i, t)))
+    assert [r.token_ids for r in res] == [expected([3], 4), expected([4], 4)]
+    assert [t for i, t in seen if i == 0] == expected([3], 4)
+    assert [t for i, t in seen if i == 1] == expected([4], 4)
+
+
+def test_the_callback_can_stop_one_request_of_a_batch():
+    """crates/nnis-model/src/streaming.rs:5-12,59-70: Stop ends that request cleanly
+    after the token it was called for; the slot goes back and the others go on."""
+    from nnis_b200.engine.generate import StreamControl
+    b = ScriptedBackend()
+    reqs = [GenerationRequest([1, 2, 3], GenerationConfig(6)), GenerationRequest([7], GenerationConfig(6))]
+
+    def on_token(i, t, seen={0: 0, 1: 0}):
+        seen[i] += 1
+        return StreamControl.STOP if (i == 1 and seen[i] == 2) else None
+    res = gen(b).generate(reqs, on_token)
+    assert res[0].token_ids == expected([1, 2, 3], 6) and res[0].finish_reason == "length"
+    assert res[1].token_ids == expected([7], 2) and res[1].finish_reason == "stop"
     assert not b.held
+    # stopping at the very first token
+    b = ScriptedBackend()
+    res = gen(b).generate(reqs[:1], lambda i, t: StreamControl.STOP)
+    assert res[0].token_ids == expected([1, 2, 3], 1) and res[0].finish_reason == "stop" and not b.held
+
+
+def test_a_request_on_its_callers_slot_executes_every_token_and_keeps_the_slot():
+    """crates/nnis-model/src/runtime.rs:814-846,1264-1268: after generation the
+    session holds prompt + emitted tokens, the last one and a stop token included."""
+    from nnis_b200.engine.generate import StreamControl
+    for stops, n, reason in (((), 4, "length"), ((expected([5, 6], 2)[1],), 2, "stop")):
+        b = ScriptedBackend()
+        slot = b.acquire_slot()
+        req = GenerationRequest([5, 6], GenerationConfig(4, stop_token_ids=stops), slot=slot)
+        res = gen(b).generate([req])[0]
+        assert res.token_ids == expected([5, 6], n, stops) and res.finish_reason == reason
+        assert b.held[slot] == [5, 6] + res.token_ids  # everything emitted was executed
+        assert list(b.held) == [slot]                  # and the slot is still the caller's
+    # stopped by the callback: the token it was shown has been executed already
+    b = ScriptedBackend()
+    slot = b.acquire_slot()
+    held_when_called = []
+
+    def on_token(i, t):
+        held_when_called.append(list(b.held[slot]))
+        return StreamControl.STOP if len(held_when_called) == 3 else StreamControl.CONTINUE
+    res = gen(b).generate([GenerationRequest([5, 6], GenerationConfig(9), slot=slot)], on_token)[0]
+    assert res.token_ids == expected([5, 6], 3) and res.finish_reason == "stop"
+    assert b.held[slot] == [5, 6] + res.token_ids
+    assert [h[-1] for h in held_when_called] == res.token_ids
+    # it goes on after what the slot holds already (start positions count for the capacity)
+    b = ScriptedBackend()
+    slot = b.acquire_slot()
+    b.held[slot] = [9, 9]
+    res = gen(b).generate([GenerationRequest([1], GenerationConfig(2), slot=slot, start=2)])[0]
+    assert res.token_ids == [19, 38] and b.held[slot] == [9, 9, 1, 19, 38]
+    res = gen(b, max_positions=8).generate([GenerationRequest([1], GenerationConfig(2), slot=slot, start=6)])[0]
+    assert not res.ok and "positions" in res.error
+
+
+def test_a_sampler_that_refuses_its_logits_ends_that_request_only():
+    class NaNForSlot(ScriptedBackend):
+        def step(self, batch, need_logits=True):
+            out = super().step(batch, need_logits)
+            for r, s in enumerate(batch):
+                if 42 in self.held[s.slot]:
+                    out[r, :] = np.nan
+            return out
+    b = NaNForSlot()
+    reqs = [GenerationRequest([42], GenerationConfig(3), SamplingConfig(seed=1).with_top_k(1)),
+            GenerationRequest([3], GenerationConfig(3), SamplingConfig(seed=2).with_top_k(1))]
+    res = gen(b).generate(reqs)
+    assert not res[0].ok and "Sampling" in res[0].error and res[0].token_ids == []
+    assert res[1].ok and res[1].token_ids == expected([3], 3) and not b.held
 
 
 def test_sampled_requests_use_their_own_seeded_sampler():
