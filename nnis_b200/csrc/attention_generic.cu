@@ -1,5 +1,6 @@
-// Attention over the paged cache for any head size (multiples of 16 up to 256),
-// any number of heads and groups, with an optional window: one warp per (query
+// Attention over the paged cache for any even head size up to 256 (NNIS asks for
+// an even one and no more: crates/nnis-model/src/config.rs:38-105), any number of
+// heads and groups, with an optional window: one warp per (query
 // token, query head) walks the visible keys 32 at a time with an online softmax
 // in float32.  It serves prompts and single decoded tokens alike, in float32 and
 // in bfloat16 storage; the key range may be split over several warps whose
@@ -60,12 +61,18 @@ attn_warp_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__ k_
                 row_index = (page * nkv + hk) * page_size + (t % page_size);
                 const T* krow = k_cache + (size_t)row_index * d;
                 float dot = 0.f;
-                for (int i = 0; i < d; i += 4) {
+                const int d4 = (d & 3) ? 0 : d;  // rows of a head size that is no multiple of
+                for (int i = 0; i < d4; i += 4) {  // four start on 8- or 4-byte boundaries only
                     float4 kv = load4(krow + i);
                     dot = fmaf(qs[i], kv.x, dot);
                     dot = fmaf(qs[i + 1], kv.y, dot);
                     dot = fmaf(qs[i + 2], kv.z, dot);
                     dot = fmaf(qs[i + 3], kv.w, dot);
+                }
+                for (int i = d4; i < d; i += 2) {
+                    float2 kv = load2(krow + i);
+                    dot = fmaf(qs[i], kv.x, dot);
+                    dot = fmaf(qs[i + 1], kv.y, dot);
                 }
                 s = dot * scale;
             }
@@ -186,7 +193,7 @@ NNIS_API int nnis_attention_generic(const void* q, int q_stride, const void* k_c
     if (n_tokens <= 0 || nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || table_cols <= 0 ||
         n_splits <= 0 || window < 0)
         return NNIS_ERR_ARGUMENT;
-    if (d <= 0 || d % 16 || d > 256) return NNIS_ERR_UNSUPPORTED;
+    if (d <= 0 || d % 2 || d > 256) return NNIS_ERR_UNSUPPORTED;
     if (nq > 65535 || n_splits > 65535) return NNIS_ERR_UNSUPPORTED;
     if (n_splits > 1 && !partial) return NNIS_ERR_ARGUMENT;
     if (dtype == NNIS_DTYPE_F32)

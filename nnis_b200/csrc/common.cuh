@@ -47,6 +47,14 @@ __device__ __forceinline__ float4 load4(const bf16* p) {
     return r;
 }
 
+// Two consecutive elements widened to float; the address must be aligned to two
+// elements (8 bytes for float, 4 for bfloat16).
+__device__ __forceinline__ float2 load2(const float* p) { return *reinterpret_cast<const float2*>(p); }
+__device__ __forceinline__ float2 load2(const bf16* p) {
+    uint32_t raw = *reinterpret_cast<const uint32_t*>(p);
+    return make_float2(__uint_as_float(raw << 16), __uint_as_float(raw & 0xffff0000u));
+}
+
 __device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
 __device__ __forceinline__ void store4(bf16* p, float4 v) {
     __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y);

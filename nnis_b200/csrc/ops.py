@@ -193,8 +193,8 @@ def attention_generic(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_c
     n = out.shape[0]
     pages, nkv, page_size, d = k_cache.shape
     _need(nkv == kv_heads and d == head_dim, "cache shape differs from the heads given")
-    _need(head_dim % 16 == 0 and 16 <= head_dim <= 256,
-          f"attention: head_dim {head_dim} is not a multiple of 16 in 16..256")
+    _need(head_dim % 2 == 0 and 2 <= head_dim <= 256,
+          f"attention: head_dim {head_dim} is not an even size in 2..256")
     _need(heads % kv_heads == 0, "attention: heads is not a multiple of kv_heads")
     _need(pages * nkv * page_size < 2 ** 31, "attention: the cache has too many rows")
     _need(out.shape[1] == heads * head_dim and out.dtype == k_cache.dtype == q.dtype,
@@ -404,6 +404,11 @@ def attention_decode(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_ca
         page_size, window, ctypes.c_float(scale), n_splits, 1 if merge else 0,
         _ptr(status_word(out.device)), PDL, _stream()),
         "attention_decode", 2 if n_splits > 1 and merge else 1)
+
+
+def attention_decode_takes(head_dim: int) -> bool:
+    """Head sizes of the CUDA-core decode kernel (whole 32-byte pieces of a row per lane)."""
+    return head_dim % 16 == 0 and 16 <= head_dim <= 256
 
 
 def attention_decode_mma_takes(head_dim: int, page_size: int) -> bool:

@@ -40,9 +40,8 @@ class Attention(Part):
         self.names = params["names"]
         if self.heads % self.kv_heads:
             raise ValueError(f"heads={self.heads} is not a multiple of kv_heads={self.kv_heads}")
-        if self.head_dim % 16 or not 16 <= self.head_dim <= 256:
-            raise ValueError(f"attention kernels take head sizes 16..256 in steps of 16; "
-                             f"got {self.head_dim}")
+        if self.head_dim % 2 or not 2 <= self.head_dim <= 256:
+            raise ValueError(f"attention kernels take even head sizes up to 256; got {self.head_dim}")
         pos = params["position"]
         self.position = POSITIONS.build(pos.kind, pos.params, prefix, dtype, device)
         self.scale = 1.0 / math.sqrt(float(self.head_dim))
@@ -110,6 +109,7 @@ class Attention(Part):
     def _decode_kernels(self, ctx, n: int) -> bool:
         """The fused bfloat16 decode kernel for q, k, v: few rows, one token each."""
         return (self.dtype == torch.bfloat16 and ctx.decode and n <= ops.DECODE_GEMV_ROWS
+                and self.head_dim % 16 == 0
                 and ops.gemv_takes(n, self.w_qkv.shape[0], self.hidden, ops.EPI_QKV, self.device))
 
     def _fused_out(self, ctx, n: int) -> bool:
@@ -191,7 +191,8 @@ class Attention(Part):
             ops.attention_decode_mma(q_buf, q_stride, cache.k, cache.v, ctx.token_pos, ctx.token_seq,
                                      table, attn, nq, nkv, d, self.window, self.scale, splits,
                                      partial, tickets, stages)
-        elif self.dtype == torch.bfloat16 and ctx.decode and n <= 65535:
+        elif self.dtype == torch.bfloat16 and ctx.decode and n <= 65535 \
+                and ops.attention_decode_takes(d):
             tiles = -(-(nq // nkv) // 4)
             splits = ctx.decode_splits(n * nkv * tiles)
             partial = ws.get("attn_partial", (n * nq * splits * (d + 2),), torch.float32) \

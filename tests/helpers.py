@@ -112,3 +112,74 @@ class TraceBuilder:
         self.lines.append(json.dumps(rec))
         self._step += 1
         return self._step - 1
+
+
+def ragged_batches(rng, vocab, trace, sequences, batches):
+    """Each batch: prompts of unequal lengths in one step, then one token each;
+    a request ends when its tokens are used up, so shorter ones end earlier.
+    ``batches``: per batch a list of (prompt length, total length)."""
+    for b, shape in enumerate(batches):
+        reqs = {}
+        for j, (prompt_len, total) in enumerate(shape):
+            rid = f"b{b}r{j}"
+            sequences[rid] = random_tokens(rng, total, vocab)
+            reqs[rid] = prompt_len
+        fed = dict(reqs)
+        ends = [rid for rid in reqs if fed[rid] == len(sequences[rid])]
+        trace.step([(rid, sequences[rid][:n], [n - 1]) for rid, n in reqs.items()], end=ends)
+        live = [rid for rid in reqs if rid not in ends]
+        while live:
+            entries = [(rid, sequences[rid][fed[rid]:fed[rid] + 1], [0]) for rid in live]
+            for rid in live:
+                fed[rid] += 1
+            ends = [rid for rid in live if fed[rid] == len(sequences[rid])]
+            trace.step(entries, end=ends)
+            live = [rid for rid in live if rid not in ends]
+
+
+def three_cuts(rng, vocab, whole=(1, 2, 33, 64, 65, 150), last32=(33, 70, 129),
+               batches=([(5, 13), (9, 12), (17, 40)], [(1, 13), (7, 8), (20, 32), (33, 45)],
+                        [(70, 75), (3, 3), (64, 66), (2, 80), (31, 33)])):
+    """One trace with the three ways of cutting work that every configuration is
+    held to: each request alone and whole (all positions wanted); a request with
+    its last 32 tokens one by one; batches of unequal lengths one after another,
+    whose shorter requests end earlier, so that slots and pages are used again.
+    Returns (trace, sequences by request id)."""
+    sequences, trace = {}, TraceBuilder()
+    for i, n in enumerate(whole):
+        rid = f"w{i}"
+        sequences[rid] = random_tokens(rng, n, vocab)
+        trace.step([(rid, sequences[rid], range(n))], end=[rid])
+    for i, n in enumerate(last32):
+        rid = f"l{i}"
+        toks = sequences[rid] = random_tokens(rng, n, vocab)
+        head = n - 32
+        trace.step([(rid, toks[:head], [head - 1])])
+        for t in range(head, n):
+            trace.step([(rid, toks[t:t + 1], [0])], end=[rid] if t == n - 1 else [])
+    ragged_batches(rng, vocab, trace, sequences, batches)
+    return trace, sequences
+
+
+def replay_against_plain(engine, model_dir: str, dtype: str, trace: "TraceBuilder", sequences,
+                         out_dir: str, what: str) -> None:
+    """Replay ``trace`` through ``engine`` and hold every written row to the plain
+    implementation's logits of the same request and position; afterwards the cache
+    must hold nothing."""
+    import plain_llama
+    from nnis_b200.engine.replay import replay
+    replay(engine, trace.lines, out_dir)
+    usage = engine.cache.usage()
+    assert usage["slots_held"] == 0 and not any(usage["pages_held"]), usage
+    engine.cache.check()
+    cfg = read_config_json(model_dir)
+    bf = dtype == "bfloat16"
+    w = load_plain_weights(model_dir, as_bf16=bf)
+    plain = {}
+    for step, rows in trace.rows.items():
+        got = read_step(out_dir, step, cfg["vocab_size"])
+        for rid, _ in rows:
+            if rid not in plain:
+                plain[rid] = plain_llama.forward(cfg, w, sequences[rid], emulate_bf16=bf)
+        want = torch.stack([plain[rid][pos] for rid, pos in rows])
+        check_logits(got, want, dtype, f"{what} {dtype} step {step}")

@@ -203,3 +203,87 @@ def test_session_truncates_and_goes_on(model_dirs, dtype):
     session.close()
     llm.engine.cache.check()
     assert llm.engine.cache.usage()["pages_held"] == [0]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("pipeline", [True, False])
+def test_a_session_goes_on_after_generate(model_dirs, dtype, pipeline):
+    """crates/nnis-model/src/runtime.rs:814-846,1264-1274: after ``generate`` the session
+    holds prompt + emitted tokens, every one of them executed, and a further
+    ``decode_one`` gives the logits of the whole sequence; with a stop token, with a
+    callback that stops, with sampling, and after what the session held before."""
+    import numpy as np
+
+    from helpers import check_logits
+    from nnis_b200 import LLM, GenerationConfig, SamplingConfig, StreamControl
+    d = model_dirs["A"]
+    cfg = read_config_json(d)
+    bf = dtype == "bfloat16"
+    w = load_plain_weights(d, as_bf16=bf)
+    llm = LLM(d, dtype=dtype, max_tokens=64 * 16, max_batch=2, pipeline_decode=pipeline)
+    session = llm.new_session()
+    prompt = [5, 9, 1, 200, 33]
+
+    def goes_on(tokens, what):
+        """The session holds ``tokens``; one more token's logits are the whole sequence's."""
+        assert session.position() == len(tokens), what
+        got = session.decode_one(17)
+        want = P.forward(cfg, w, list(tokens) + [17], bf)[-1:]
+        check_logits(got[None, :], want, dtype, what)
+
+    plain = P.greedy_generate(cfg, w, prompt, 9, None, bf)
+    out = session.generate(prompt, GenerationConfig(9))
+    assert out == plain
+    goes_on(prompt + out, "after a fixed length")
+    # a stop token is emitted, executed, and ends the generation
+    stop = plain[4]
+    out = session.generate(prompt, GenerationConfig(9, stop_token_ids=(stop,)))
+    assert out == plain[:plain.index(stop) + 1]
+    goes_on(prompt + out, "after a stop token")
+    # one token only
+    out = session.generate(prompt, GenerationConfig(1))
+    assert out == plain[:1]
+    goes_on(prompt + out, "after one token")
+    # the callback stops after the third token
+    seen = []
+    out = session.generate(prompt, GenerationConfig(9),
+                           on_token=lambda t: (seen.append(t), StreamControl.STOP if len(seen) == 3 else None)[1])
+    assert out == plain[:3] == seen
+    goes_on(prompt + out, "after the callback's stop")
+    # the next generation follows what the session holds
+    held = prompt + out + [17]
+    more = session.generate([40, 41], GenerationConfig(4), keep_context=True)
+    assert more == P.greedy_generate(cfg, w, held + [40, 41], 4, None, bf)
+    goes_on(held + [40, 41] + more, "after a generation that kept its context")
+    # sampled, streamed, stopped by the caller
+    policy = SamplingConfig(seed=3, temperature=0.9, top_k=30)
+    full = session.generate_sampled(prompt, GenerationConfig(6), policy)
+    assert session.position() == len(prompt) + 6
+    seen = []
+    out = session.generate_sampled_streaming(
+        prompt, GenerationConfig(6), policy,
+        lambda t: (seen.append(t), StreamControl.STOP if len(seen) == 2 else StreamControl.CONTINUE)[1])
+    assert out == full[:2] == seen
+    goes_on(prompt + out, "after a sampled stream that its caller stopped")
+    session.close()
+    assert llm.engine.cache.usage()["slots_held"] == 0
+
+
+def test_the_callback_stops_one_prompt_of_a_batch(model_dirs):
+    from nnis_b200 import LLM, StreamControl
+    d = model_dirs["C"]
+    cfg = read_config_json(d)
+    w = load_plain_weights(d, as_bf16=False)
+    prompts = [[3, 4, 5], [100, 200], [7]]
+    plain = [P.greedy_generate(cfg, w, p, 10, None) for p in prompts]
+    for pipeline in (True, False):
+        llm = LLM(d, dtype="float32", max_tokens=64 * 8, max_batch=4, pipeline_decode=pipeline)
+        count = {}
+
+        def on_token(i, t):
+            count[i] = count.get(i, 0) + 1
+            return StreamControl.STOP if (i == 1 and count[i] == 4) else None
+        got = llm.generate(prompts, max_new_tokens=10, stop_token_ids=(), on_token=on_token)
+        assert got[0].token_ids == plain[0] and got[2].token_ids == plain[2]
+        assert got[1].token_ids == plain[1][:4] and got[1].finish_reason == "stop"
+        assert llm.engine.cache.usage()["slots_held"] == 0

@@ -271,11 +271,12 @@ def test_padding_rows_store_nothing_and_come_out_zero():
 
 def test_sizes_the_kernels_do_not_take_are_refused():
     o = ops()
-    kc = torch.zeros(1, 1, 64, 24, device=DEV)
-    q = torch.zeros(1, 24, device=DEV)
     i = torch.zeros(1, dtype=torch.int32, device=DEV)
-    with pytest.raises(o.KernelError, match="multiple of 16"):
-        o.attention_generic(q, 24, kc, kc, i, i, i.view(1, 1), q.clone(), 1, 1, 24, 0, 1.0)
+    for d in (23, 258):  # an odd head size, one beyond 256
+        kc = torch.zeros(1, 1, 64, d, device=DEV)
+        q = torch.zeros(1, d, device=DEV)
+        with pytest.raises(o.KernelError, match="even size"):
+            o.attention_generic(q, d, kc, kc, i, i, i.view(1, 1), q.clone(), 1, 1, d, 0, 1.0)
     with pytest.raises(o.KernelError):
         o.gemm_simt(torch.zeros(2, 4), torch.zeros(2, 4), None, torch.zeros(2, 2), 0)  # CPU tensors
     with pytest.raises(o.KernelError):

@@ -13,7 +13,7 @@ import torch
 
 import plain_llama as P
 from helpers import (CONFIGS, TraceBuilder, check_logits, load_plain_weights, make_model,
-                     random_tokens, read_config_json, read_step)
+                     ragged_batches, random_tokens, read_config_json, read_step)
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -91,28 +91,6 @@ def test_last_32_tokens_one_by_one(models, name, dtype, tmp_path):
         for t in range(head, len(toks)):
             trace.step([(rid, toks[t:t + 1], [0])], end=[rid] if t == len(toks) - 1 else [])
     run_and_check(models, name, dtype, trace, sequences, tmp_path, "last32")
-
-
-def ragged_batches(rng, vocab, trace, sequences, batches):
-    """Each batch: prompts of unequal lengths in one step, then one token each;
-    a request ends when its tokens are used up, so shorter ones end earlier."""
-    for b, shape in enumerate(batches):
-        reqs = {}
-        for j, (prompt_len, total) in enumerate(shape):
-            rid = f"b{b}r{j}"
-            sequences[rid] = random_tokens(rng, total, vocab)
-            reqs[rid] = prompt_len
-        fed = dict(reqs)
-        ends = [rid for rid in reqs if fed[rid] == len(sequences[rid])]
-        trace.step([(rid, sequences[rid][:n], [n - 1]) for rid, n in reqs.items()], end=ends)
-        live = [rid for rid in reqs if rid not in ends]
-        while live:
-            entries = [(rid, sequences[rid][fed[rid]:fed[rid] + 1], [0]) for rid in live]
-            for rid in live:
-                fed[rid] += 1
-            ends = [rid for rid in live if fed[rid] == len(sequences[rid])]
-            trace.step(entries, end=ends)
-            live = [rid for rid in live if rid not in ends]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
