@@ -6,11 +6,13 @@
 
 A step is one decode step of a batch of 8 sequences whose context ends at 4,096
 tokens (prompt 2,048 + 2,048 decoded); ``value`` is decoded tokens per second,
-timed with CUDA events over K graph launches.  ``e2e`` is the same through the
-Python entry point with every step's tokens coming from and going back to the
-host.  The line also carries a 2,048-token prefill, the decode step's HBM
-roofline, and decoding at batch 1 and 64.  Weights are random (seeded), token
-ids are uniform random: no checkpoint or dataset is read.
+timed with CUDA events over K graph launches: the median of five such regions over
+the same range of contexts, as NNIS's own benchmarks take the median of five
+(crates/nnis-bench/src/lib.rs:362-428).  ``e2e`` is the same through the Python
+entry point with every step's tokens coming from and going back to the host, over
+256 steps whatever K is.  The line also carries a 2,048-token prefill, the decode
+step's HBM roofline, and decoding at batch 1 and 64.  Weights are random (seeded),
+token ids are uniform random: no checkpoint or dataset is read.
 """
 from __future__ import annotations
 
@@ -27,14 +29,13 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# The shape of SmolLM2-135M (BASELINE.json configs[2]); nothing below the
-# configuration knows these numbers.
+# The shape of SmolLM2-135M; nothing below the configuration knows these numbers.
 SMOLLM2_135M = dict(
     architectures=["LlamaForCausalLM"], model_type="llama", vocab_size=49152, hidden_size=576,
     intermediate_size=1536, num_hidden_layers=30, num_attention_heads=9, num_key_value_heads=3,
     max_position_embeddings=8192, rms_norm_eps=1e-5, rope_theta=100000.0, hidden_act="silu",
     tie_word_embeddings=True, attention_bias=False, torch_dtype="bfloat16")
-# The two larger shapes of the same family (BASELINE.json configs[3] and [4]): what differs from the above.
+# The two larger shapes of the same family: what differs from the above.
 SHAPES = {
     "135m": ("SmolLM2-135M", {}),
     "360m": ("SmolLM2-360M", dict(num_hidden_layers=32, hidden_size=960, intermediate_size=2560,
@@ -45,7 +46,10 @@ SHAPES = {
 CONTEXT = 4096
 PROMPT = 2048
 BATCH = 8
-FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+REPEATS = 5     # timed regions per point; the median is reported
+E2E_STEPS = 256  # decode steps of the end-to-end run
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+                  "source": "fallback"}
 
 
 def peaks():
@@ -54,6 +58,7 @@ def peaks():
         with open(path) as f:
             raw = json.load(f)
         return {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"]),
+                "bf16_tflops_sustained": float(raw.get("bf16_tflops_sustained", raw["bf16_tflops"])),
                 "source": "measured"}
     except (OSError, KeyError, ValueError, TypeError):
         return dict(FALLBACK_PEAKS)
@@ -65,14 +70,17 @@ class ClockSampler:
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self):
-        self.samples, self.proc = [], None
+    def __init__(self, gpu_id: str = "0"):
+        """``gpu_id``: what ``nvidia-smi -i`` takes for the GPU that the run is on (its
+        UUID: index 0 of this process need not be index 0 of the machine)."""
+        self.samples, self.proc, self.gpu_id = [], None, gpu_id
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                ["nvidia-smi", "-i", self.gpu_id, f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
@@ -97,7 +105,21 @@ class ClockSampler:
         reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i] == "Active"
                                                          for r in rows)]
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(rows)}
+                "reasons": reasons, "samples": len(rows), "gpu": self.gpu_id}
+
+
+def gpu_identity(torch) -> str:
+    """The UUID of this process's device 0 in nvidia-smi's spelling; "0" if it cannot be had."""
+    try:
+        uuid = str(torch.cuda.get_device_properties(0).uuid)
+        return uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+    except Exception:
+        return "0"
+
+
+def median(values):
+    values = sorted(values)
+    return values[len(values) // 2]
 
 
 def main() -> int:
@@ -142,7 +164,7 @@ def main() -> int:
     rng = random.Random(0)
     vocab = cfg["vocab_size"]
     K, W = args.steps, args.warmup
-    clocks = ClockSampler()
+    clocks = ClockSampler(gpu_identity(torch))
     windows = []
 
     with tempfile.TemporaryDirectory() as tmp:
@@ -152,8 +174,7 @@ def main() -> int:
                   max_batch=max(most_rows, 1), pipeline_decode=False)
         engine = llm.engine
         spec = engine.spec
-        mixer = engine.model.blocks[0].mixer
-        kv_bytes_per_token = 2 * len(spec.schedule) * mixer.kv_heads * mixer.head_dim * 2
+        kv_bytes_per_token = engine.cache.kv_bytes_per_token()
         weight_bytes = engine.model.parameter_bytes()
         clocks.start()
 
@@ -183,14 +204,17 @@ def main() -> int:
                 fed += n
             dec = GraphDecoder(engine, batch, CONTEXT)
             engine.cache.reserve(slots, [CONTEXT] * batch)
-            for r, s in enumerate(slots):
-                dec.set_row(r, s, rng.randrange(vocab), begin)
-            dec.capture()
-            for _ in range(warmup):
-                dec.launch()
-            before = ops.launch_count()
-            ms = timed(dec.launch, steps)
-            launches = dec.launches_per_step * steps + (ops.launch_count() - before)
+            regions = []
+            for rep in range(REPEATS):  # every region decodes the same positions again
+                for r, s in enumerate(slots):
+                    dec.set_row(r, s, rng.randrange(vocab), begin)
+                dec.capture()
+                for _ in range(warmup):
+                    dec.launch()
+                before = ops.launch_count()
+                regions.append(timed(dec.launch, steps))
+                launches = dec.launches_per_step * steps + (ops.launch_count() - before)
+            ms = median(regions)
             engine.cache.commit(slots, [CONTEXT] * batch)
             for s in slots:
                 engine.release_slot(s)
@@ -198,7 +222,8 @@ def main() -> int:
             step_bytes = weight_bytes + batch * mean_context * kv_bytes_per_token
             return {"tok_s": batch * steps / (ms * 1e-3), "ms_per_step": ms / steps,
                     "launches": launches, "bytes_per_step": step_bytes,
-                    "gbs": step_bytes / (ms / steps * 1e-3) / 1e9}
+                    "gbs": step_bytes / (ms / steps * 1e-3) / 1e9,
+                    "spread": (max(regions) - min(regions)) / ms}
 
         main_point = decode_point(args.batch, K, W)
 
@@ -212,20 +237,18 @@ def main() -> int:
 
         for _ in range(3):
             prefill_once()
-        reps = 5
-        prefill_ms = timed(prefill_once, reps) / reps
-        H, I = cfg["hidden_size"], cfg["intermediate_size"]
-        d, nq, nkv = mixer.head_dim, mixer.heads, mixer.kv_heads
-        per_layer = 2 * PROMPT * (H * (nq + 2 * nkv) * d + nq * d * H + 3 * H * I) \
-            + 4 * nq * d * PROMPT * (PROMPT + 1) / 2
-        prefill_flops = len(spec.schedule) * per_layer + 2 * H * vocab
+        prefill_ms = median([timed(prefill_once, 1) for _ in range(REPEATS)])
+        prefill_flops = engine.model.step_flops([PROMPT], [0], 1)  # what the parts say they compute
+        prefill_rate = prefill_flops / (prefill_ms * 1e-3)
         prefill = {"value": PROMPT / (prefill_ms * 1e-3), "tokens": PROMPT, "ms": prefill_ms,
-                   "frac": prefill_flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)}
+                   "frac": prefill_rate / (pk["bf16_tflops"] * 1e12),
+                   "frac_of_sustained": prefill_rate / (pk["bf16_tflops_sustained"] * 1e12),
+                   "tflops": prefill_rate / 1e12}
 
         # -- end to end: host tokens in and out every step -----------------------------
         e2e = None
         if not args.skip_e2e:
-            e2e_new = min(K, 256) + 1
+            e2e_new = E2E_STEPS + 1
             prompts = [[rng.randrange(vocab) for _ in range(CONTEXT - e2e_new)] for _ in range(args.batch)]
             llm.generate([p[:64] for p in prompts], max_new_tokens=4, stop_token_ids=())
             llm.backend._decoder(args.batch, CONTEXT, False).capture()  # the graph the timed run will launch
@@ -287,15 +310,17 @@ def main() -> int:
                    "parallelism": "single GPU", "prompt_len": PROMPT, "layers": cfg["num_hidden_layers"],
                    "layers_of_shape": full_layers, "hidden_size": cfg["hidden_size"],
                    "intermediate_size": cfg["intermediate_size"], "heads": cfg["num_attention_heads"],
-                   "kv_heads": cfg["num_key_value_heads"], "head_dim": mixer.head_dim,
+                   "kv_heads": cfg["num_key_value_heads"],
+                   "head_dim": cfg.get("head_dim") or cfg["hidden_size"] // cfg["num_attention_heads"],
                    "vocab_size": vocab, "rope_theta": cfg["rope_theta"],
                    "rms_norm_eps": cfg["rms_norm_eps"], "tied_embeddings": True,
                    "cache_page_tokens": 64, "l2": "inputs larger than L2 (weights + KV per step)",
-                   "peaks": pk["source"]},
+                   "peaks": pk["source"], "timing": f"median of {REPEATS} regions of K steps"},
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": main_point["gbs"], "peak": pk["hbm_gbs"],
                      "unit": "GB/s", "frac": main_point["gbs"] / pk["hbm_gbs"]},
         "points": points,
+        "spread": main_point["spread"],
         "e2e": e2e,
         "gpu_launches": main_point["launches"],
         "clocks": clocks.summary(windows),

@@ -44,6 +44,16 @@ class StateRequest:
 
 
 @dataclass
+class CacheSnapshot:
+    """What ``CacheManager.snapshot`` keeps of one sequence: its length and a copy of
+    its fixed-size state (keys and values need no copy: going back only forgets)."""
+    slot: int
+    owner: int
+    length: int
+    states: List[torch.Tensor]
+
+
+@dataclass
 class KVView:
     """What an attention-like part gets: its own layer of a group's storage."""
     group: int
@@ -92,6 +102,7 @@ class CacheManager:
         # (taken, given back, truncated): a copy of a table kept elsewhere is good only
         # for the version it was made at
         self.versions: List[int] = [0] * max_slots
+        self.owners: List[int] = [0] * max_slots  # how many sequences have held each slot
         self.groups: List[_KVGroup] = []
         self._views: List[Optional[Union[KVView, StateView]]] = []
         by_key: Dict[Tuple[int, int, int], List[int]] = {}
@@ -128,6 +139,7 @@ class CacheManager:
         slot = self.slots.take()
         self.lengths[slot] = 0
         self.versions[slot] += 1
+        self.owners[slot] += 1
         for g in self.groups:
             g.tables[slot] = []
         for t in self._states:
@@ -193,8 +205,9 @@ class CacheManager:
         the pages beyond go back to their pools; what a kept page holds beyond the
         length is never read and is written over by the next tokens.  Refused, with
         nothing changed, where going back is not possible: fixed-size state has no
-        earlier value, and a windowed group may have given back pages that the
-        positions after ``length`` would read again."""
+        earlier value (``snapshot`` and ``restore`` are the way back for such a model),
+        and a windowed group may have given back pages that the positions after
+        ``length`` would read again."""
         if not self.slots.is_held(slot):
             raise SlotError(f"slot {slot} is not held")
         if not 0 <= length <= self.lengths[slot]:
@@ -202,7 +215,11 @@ class CacheManager:
         if length == self.lengths[slot]:
             return
         if self._states:
-            raise SlotError("a sequence with fixed-size state cannot go back to an earlier length")
+            raise SlotError("a sequence with fixed-size state cannot go back to an earlier length "
+                            "(take a snapshot before the tokens that may be taken back, and restore it)")
+        self._forget_from(slot, length)
+
+    def _forget_from(self, slot: int, length: int) -> None:
         keep = -(-length // PAGE_SIZE)
         for gi, g in enumerate(self.groups):
             table = g.tables[slot]
@@ -218,8 +235,39 @@ class CacheManager:
         self.lengths[slot] = length
         self.versions[slot] += 1
 
+    def snapshot(self, slot: int) -> CacheSnapshot:
+        """What is needed to bring this sequence back to where it is now after further
+        steps: its length and a copy of its fixed-size state.  The way back for models
+        with state of fixed size, which ``truncate`` cannot serve; it works for any
+        model (with keys and values alone it is a truncation)."""
+        if not self.slots.is_held(slot):
+            raise SlotError(f"slot {slot} is not held")
+        return CacheSnapshot(slot, self.owners[slot], self.lengths[slot],
+                             [t[slot].clone() for t in self._states])
+
+    def restore(self, snapshot: CacheSnapshot) -> None:
+        """Back to the snapshot: later positions are forgotten, the state is what it
+        was.  Refused, with nothing changed, if the slot has been given back since, is
+        shorter than the snapshot, or a windowed group has dropped pages it would need."""
+        slot = snapshot.slot
+        if not self.slots.is_held(slot) or self.owners[slot] != snapshot.owner:
+            raise SlotError(f"slot {slot} is not held by the sequence of this snapshot any more")
+        if snapshot.length > self.lengths[slot]:
+            raise SlotError(f"slot {slot}: the snapshot holds {snapshot.length} positions, the "
+                            f"sequence only {self.lengths[slot]}")
+        if snapshot.length < self.lengths[slot]:
+            self._forget_from(slot, snapshot.length)
+        for t, kept in zip(self._states, snapshot.states):
+            t[slot].copy_(kept)
+
     def page_table(self, group: int, slot: int) -> List[int]:
         return self.groups[group].tables[slot]
+
+    def kv_bytes_per_token(self) -> int:
+        """Bytes of keys and values that one position of one sequence holds over all
+        layers (a windowed group counted like a full one)."""
+        return sum(2 * len(g.entries) * g.kv_heads * g.head_dim * g.k.element_size()
+                   for g in self.groups)
 
     # -- telemetry (crates/nnis-rt/src/kv_telemetry.rs:42-80) ----------------
     def usage(self) -> Dict[str, object]:

@@ -189,12 +189,11 @@ class LlamaConfig:
                 "activation": "silu", "bias": self.mlp_bias,
                 "names": {"gate": "mlp.gate_proj", "up": "mlp.up_proj",
                           "down": "mlp.down_proj"}})
-            layers.append(LayerSpec(
-                prefix=f"model.layers.{i}", block="prenorm",
-                mixer_norm=PartSpec("rmsnorm", {**norm.params, "name": "input_layernorm"}),
-                mixer=mixer,
-                ffn_norm=PartSpec("rmsnorm", {**norm.params, "name": "post_attention_layernorm"}),
-                ffn=ffn))
+            layers.append(LayerSpec(prefix=f"model.layers.{i}", block="prenorm", parts={
+                "mixer_norm": PartSpec("rmsnorm", {**norm.params, "name": "input_layernorm"}),
+                "mixer": mixer,
+                "ffn_norm": PartSpec("rmsnorm", {**norm.params, "name": "post_attention_layernorm"}),
+                "ffn": ffn}))
         spec = ModelSpec(
             architecture=self.architecture,
             hidden_size=self.hidden_size,

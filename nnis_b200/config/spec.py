@@ -6,8 +6,10 @@ no part and no engine file names an architecture.  The spec is plain data:
 
 * a ``PartSpec`` is a kind (a key of one of the part registries in
   ``nnis_b200.parts``) and the sizes and constants of that part;
-* a ``LayerSpec`` names the arrangement of a block and its four parts, chosen
-  layer by layer, so two layers of one model may differ in every part;
+* a ``LayerSpec`` names the arrangement of a block and, by role, the parts that
+  this arrangement is made of (``parts``: role -> ``PartSpec``; the arrangement's
+  class says which roles it knows), chosen layer by layer, so two layers of one
+  model may differ in every part and in how many they have;
 * ``schedule`` is the order in which layers run.  An entry may name a layer a
   second time (its weights are shared, its cache is its own), and
   ``cache_of`` lets an entry read the cache that an earlier entry wrote.
@@ -35,13 +37,18 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One block: ``prefix`` is the tensor-name prefix of its weights."""
+    """One block: ``prefix`` is the tensor-name prefix of its weights, ``block`` the
+    arrangement (a key of ``parts.BLOCKS``) and ``parts`` what it is made of, by the
+    roles that this arrangement knows (``prenorm``: mixer_norm, mixer, ffn_norm, ffn)."""
     prefix: str
     block: str
-    mixer_norm: PartSpec
-    mixer: PartSpec
-    ffn_norm: PartSpec
-    ffn: PartSpec
+    parts: Mapping[str, PartSpec]
+
+    def part(self, role: str) -> PartSpec:
+        if role not in self.parts:
+            raise KeyError(f"layer {self.prefix!r} ({self.block}) has no part {role!r}; "
+                           f"it has {sorted(self.parts)}")
+        return self.parts[role]
 
 
 @dataclass(frozen=True)

@@ -48,9 +48,16 @@ NNIS_API int nnis_attention_decode_noalloc(const void* q, int q_stride, const vo
                                            int table_cols, void* out, int n_tokens, int heads,
                                            int kv_heads, int head_dim, int page_size, int window,
                                            float scale, int n_splits, cudaStream_t stream) {
+    // Everything the kernel's own entry point would refuse is refused here first, so
+    // that a refused call puts nothing on the stream (not even the clearing below).
     if (n_tokens <= 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads || n_splits <= 0 ||
-        head_dim <= 0)
+        head_dim <= 0 || table_cols <= 0 || window < 0)
         return NNIS_ERR_ARGUMENT;
+    if ((head_dim != 64 && head_dim != 128) || page_size != 64 || n_tokens > 65535 || n_splits > 64)
+        return NNIS_ERR_UNSUPPORTED;
+    if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) % 16 ||
+        (q_stride % 8))
+        return NNIS_ERR_ALIGNMENT;
     unsigned long long floats =
         (unsigned long long)n_tokens * heads * n_splits * (unsigned long long)(head_dim + 2);
     unsigned long long tickets =
@@ -65,8 +72,11 @@ NNIS_API int nnis_attention_decode_noalloc(const void* q, int q_stride, const vo
                                                         (size_t)NNIS_NOALLOC_PARTIAL_FLOATS * 4u);
     // the tickets must start at zero; the last call may have left them otherwise
     // only if it was cut short, but clearing costs one small memset on the stream
-    cudaError_t e = cudaMemsetAsync(ticket_words, 0, (size_t)tickets * sizeof(unsigned), stream);
-    if (e != cudaSuccess) return (int)e;
+    // (a single slice takes no ticket)
+    if (n_splits > 1) {
+        cudaError_t e = cudaMemsetAsync(ticket_words, 0, (size_t)tickets * sizeof(unsigned), stream);
+        if (e != cudaSuccess) return (int)e;
+    }
     return nnis_attention_decode_mma(q, q_stride, k_cache, v_cache, token_pos, token_seq, page_table,
                                      table_cols, out, partial, ticket_words, n_tokens, heads, kv_heads,
                                      head_dim, page_size, window, scale, n_splits, /*pdl=*/0, stream);

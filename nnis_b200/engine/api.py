@@ -32,9 +32,12 @@ Prompt = Union[str, Sequence[int]]
 class EngineBackend:
     """What the generation loop needs of an engine."""
 
-    def __init__(self, engine: Engine, max_rows: int = 64, pipeline: bool = True):
+    def __init__(self, engine: Engine, max_rows: int = 64, pipeline: bool = True,
+                 max_step_tokens: int = 16384):
         self.engine = engine
         self.max_rows = max_rows
+        # most tokens of one prompt step; longer batches of prompts run in portions
+        self.max_step_tokens = max_step_tokens
         # True: all-greedy batches keep tokens on the device and the host reads
         # picks one step late.  False: every step's tokens come from the host.
         self.pipeline = pipeline
@@ -65,7 +68,7 @@ class EngineBackend:
         single = all(len(s.tokens) == 1 and list(s.want) == [0] for s in batch)
         if not single or self.decode_greedy is None or len(batch) > self.max_rows:
             self._picked = None
-            return self.engine.step(batch)
+            return self.engine.step_in_portions(batch, self.max_step_tokens)
         engine, cache = self.engine, self.engine.cache
         slots = [s.slot for s in batch]
         positions = [cache.length(s) for s in slots]
@@ -195,7 +198,8 @@ class LLM:
     def __init__(self, model_dir: str, dtype: str = "bfloat16", device_ordinal: int = 0,
                  device: Optional[str] = None, max_tokens: Optional[int] = None,
                  max_batch: int = 64, tokenizer_file: Optional[str] = None,
-                 pipeline_decode: bool = True, device_sampling: bool = False):
+                 pipeline_decode: bool = True, device_sampling: bool = False,
+                 max_step_tokens: int = 16384):
         device = device if device is not None else f"cuda:{int(device_ordinal)}"
         self.max_batch = max_batch
         if max_tokens is None:
@@ -204,7 +208,7 @@ class LLM:
                                       max_slots=max(max_batch, 1))
         self.spec = self.engine.spec
         self.tokenizer = load_tokenizer(tokenizer_file) if tokenizer_file else None
-        self.backend = EngineBackend(self.engine, max_batch, pipeline_decode)
+        self.backend = EngineBackend(self.engine, max_batch, pipeline_decode, max_step_tokens)
         self._generator = Generator(self.backend, self.spec.vocab_size,
                                     self.spec.max_positions, max_batch, max_tokens, device_sampling)
 
@@ -266,6 +270,15 @@ class InferenceSession:
         """Back to ``position`` tokens, as NNIS's sessions allow
         (crates/nnis-core/src/session.rs:430-445): the next ``decode_one`` follows them."""
         self.engine.truncate(self.slot, int(position))
+
+    def snapshot(self):
+        """Where the session is now, to come back to with ``restore`` after further
+        tokens: the way back for a model whose layers keep state of fixed size, which
+        cannot be truncated; for keys and values alone it is the same as ``truncate``."""
+        return self.engine.snapshot(self.slot)
+
+    def restore(self, snapshot) -> None:
+        self.engine.restore(snapshot)
 
     def close(self) -> None:
         if self.slot is not None:

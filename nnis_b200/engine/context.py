@@ -47,13 +47,11 @@ class StepContext:
     host_starts: Sequence[int] = field(default_factory=list)
     fixed_splits: int = 0  # > 0: a captured graph fixed the split count
     # per sequence of the batch (device int32 [n_seqs]): the packed row of its
-    # first token in this step, that token's position, its number of tokens; and
-    # the 64-query tiles of the step, [n_tiles, 2] = (sequence, first query).
+    # first token in this step, that token's position, its number of tokens.
     # None in decode steps and in contexts built without them.
     seq_first_row: Optional[torch.Tensor] = None
     seq_start: Optional[torch.Tensor] = None
     seq_count: Optional[torch.Tensor] = None
-    q_tiles: Optional[torch.Tensor] = None
     # what the parts asked for with ``step_tables``: device copies and the arrays
     tables: Dict[str, torch.Tensor] = field(default_factory=dict)
     host_tables: Dict[str, object] = field(default_factory=dict)

@@ -78,7 +78,7 @@ class GraphDecoder:
         self._pinned_out: Optional[torch.Tensor] = None
 
     def _query_heads(self) -> int:
-        heads = [getattr(b.mixer, "heads", 1) for b in self.engine.model.blocks]
+        heads = [getattr(part, "heads", 1) for b in self.engine.model.blocks for part in b.parts()]
         return max(heads) if heads else 1
 
     # -- the captured step ----------------------------------------------------

@@ -29,9 +29,9 @@ from .context import StepContext
 from .model import DecoderModel
 from .workspace import Workspace
 
-QUERY_TILE = 64  # queries per CTA of the prompt attention kernel
 GRAPH_MIN_TOKENS = 256  # prompt steps at least this large are captured when they recur
-MAX_STEP_GRAPHS = 4
+MAX_STEP_GRAPHS = 4     # captured prompt steps kept (each holds buffers of its own)
+MAX_SEEN_SHAPES = 64    # shapes seen once and remembered in case they come again
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
            "f32": torch.float32, torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
@@ -77,7 +77,8 @@ class Engine:
         self.model.bind_cache(self.cache)
         self.workspace = Workspace(self.device)
         self._staging: Optional[torch.Tensor] = None  # pinned host ints of one step
-        self._step_graphs: Dict[object, dict] = {}  # captured prompt steps by shape
+        self._step_graphs: Dict[object, dict] = {}  # captured prompt steps by shape, oldest use first
+        self._seen_shapes: Dict[object, bool] = {}  # shapes of large prompt steps seen once
         parts = [p for blk in self.model.blocks for p in blk.parts()]
         self._graph_safe = all(getattr(p, "device_only", True) for p in parts)
         self.h2d_bytes = 0  # bytes of step tables copied so far (for measurements)
@@ -119,6 +120,14 @@ class Engine:
         """The sequence of ``slot`` forgets its positions from ``length`` on; its next
         step goes on from there (see ``CacheManager.truncate`` for when that is refused)."""
         self.cache.truncate(slot, length)
+
+    def snapshot(self, slot: int):
+        """Keep what brings the sequence of ``slot`` back to where it is now (its
+        length and its fixed-size state); ``restore`` goes back to it."""
+        return self.cache.snapshot(slot)
+
+    def restore(self, snapshot) -> None:
+        self.cache.restore(snapshot)
 
     # -- the step -----------------------------------------------------------
     def _stage(self, parts: List[np.ndarray], workspace: Optional[Workspace] = None) -> torch.Tensor:
@@ -186,11 +195,8 @@ class Engine:
             parts.append(table.reshape(-1))
             cols.append(width)
         decode = all(c == 1 for c in counts)
-        n_tiles = 0
         if not decode:
-            tiles = [(i, q0) for i, c in enumerate(counts) for q0 in range(0, c, QUERY_TILE)]
-            n_tiles = len(tiles)
-            parts += [first_rows, i32(starts), i32(counts), i32(tiles)]
+            parts += [first_rows, i32(starts), i32(counts)]
             # 16-byte alignment for the tables the parts asked for
             parts.append(np.zeros(-int(sum(p.size for p in parts)) % 4, dtype=np.int32))
             extra = self.model.step_tables(counts, starts)
@@ -216,7 +222,6 @@ class Engine:
             host_slots=slots, host_counts=counts, host_starts=starts)
         if not decode:
             ctx.seq_first_row, ctx.seq_start, ctx.seq_count = take(b), take(b), take(b)
-            ctx.q_tiles = take(2 * n_tiles).view(-1, 2)
             take(-o % 4)
             for name, arr in extra.items():
                 ctx.tables[name] = take(arr.size).view(arr.shape)
@@ -231,25 +236,28 @@ class Engine:
         Large prompt steps whose shape (token counts, start positions, number of
         wanted places) comes a second time are captured as a CUDA graph with buffers
         of their own and replayed from then on: such a step is a few hundred small
-        launches, and the host is the slower side of them."""
+        launches, and the host is the slower side of them.  Shapes seen once are only
+        remembered (they cost nothing and push no graph out); of the captured ones the
+        least recently used goes when there are more than ``MAX_STEP_GRAPHS``."""
         key = None
         if sum(len(s.tokens) for s in batch) >= GRAPH_MIN_TOKENS and \
                 any(len(s.tokens) > 1 for s in batch) and self._graph_safe:
             key = (tuple(len(s.tokens) for s in batch),
-                   tuple(self.cache.lengths[s.slot] for s in batch),
+                   tuple(self.cache.length(s.slot) for s in batch),  # refuses slots that are not held
                    tuple(len(s.want) for s in batch))
         entry = self._step_graphs.get(key) if key is not None else None
-        if entry is not None and entry["graph"] is not None:
+        if entry is not None:
+            self._step_graphs[key] = self._step_graphs.pop(key)  # most recently used last
             ctx, d_want, slots, new_lengths = self.prepare(batch, entry["workspace"])
             entry["graph"].replay()
             self.cache.commit(slots, new_lengths)
             return entry["logits"].clone()
-        if key is not None and entry is None:
-            if len(self._step_graphs) >= MAX_STEP_GRAPHS:
-                self._step_graphs.pop(next(iter(self._step_graphs)))
-            self._step_graphs[key] = {"graph": None, "workspace": None, "logits": None}
-        elif key is not None:
-            return self._capture_step(batch, entry)
+        if key is not None and key in self._seen_shapes:
+            return self._capture_step(batch, key)
+        if key is not None:
+            if len(self._seen_shapes) >= MAX_SEEN_SHAPES:
+                self._seen_shapes.pop(next(iter(self._seen_shapes)))
+            self._seen_shapes[key] = True
         ctx, d_want, slots, new_lengths = self.prepare(batch)
         logits = torch.empty((d_want.numel(), self.spec.vocab_size), dtype=torch.float32,
                              device=self.device)
@@ -257,26 +265,75 @@ class Engine:
         self.cache.commit(slots, new_lengths)
         return logits
 
-    def _capture_step(self, batch: Sequence[SequenceStep], entry) -> torch.Tensor:
-        """Second time a prompt shape is seen: run it into buffers of its own under
-        capture, then launch the graph."""
+    def _capture_step(self, batch: Sequence[SequenceStep], key) -> torch.Tensor:
+        """Second time a prompt shape is seen: run it into buffers of its own (this
+        run's logits are the step's result), then record the same launches as a graph
+        for the next time."""
         workspace = Workspace(self.device)
         ctx, d_want, slots, new_lengths = self.prepare(batch, workspace)
         logits = torch.empty((d_want.numel(), self.spec.vocab_size), dtype=torch.float32,
                              device=self.device)
         side = torch.cuda.Stream(device=self.device)
         side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):  # allocates the workspace; results are overwritten below
+        with torch.cuda.stream(side):  # allocates the workspace and computes the step
             self.model.forward(ctx, d_want, logits)
         torch.cuda.current_stream().wait_stream(side)
+        result = logits.clone()
         workspace.frozen = True
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             self.model.forward(ctx, d_want, logits)
-        graph.replay()
         self.cache.commit(slots, new_lengths)
-        entry.update(graph=graph, workspace=workspace, logits=logits)
-        return logits.clone()
+        self._seen_shapes.pop(key, None)
+        while len(self._step_graphs) >= MAX_STEP_GRAPHS:
+            self._step_graphs.pop(next(iter(self._step_graphs)))  # the least recently used
+        self._step_graphs[key] = {"graph": graph, "workspace": workspace, "logits": logits}
+        return result
+
+    def step_in_portions(self, batch: Sequence[SequenceStep], max_step_tokens: int) -> torch.Tensor:
+        """The same result as ``step`` for prompts of any total length, run as several
+        steps of at most ``max_step_tokens`` tokens each, so that the step's scratch
+        (a few rows of the width and of the feed-forward's size per token) stays
+        bounded: sequences are taken in order, one that does not fit is cut and goes
+        on in the next portion (a later chunk starts from the cache like any other)."""
+        if max_step_tokens <= 0:
+            raise StepError("max_step_tokens must be positive")
+        if sum(len(s.tokens) for s in batch) <= max_step_tokens:
+            return self.step(batch)
+        for s in batch:
+            for w in s.want:
+                if not 0 <= int(w) < len(s.tokens):
+                    raise StepError(f"slot {s.slot}: wanted place {w} is outside its "
+                                    f"{len(s.tokens)} tokens")
+        portions, current, room = [], [], max_step_tokens
+        keys = []  # (sequence, wanted place) of every row, in the order the portions give them
+        for i, s in enumerate(batch):
+            done = 0
+            while done < len(s.tokens):
+                take = min(room, len(s.tokens) - done)
+                want = [int(w) - done for w in s.want if done <= int(w) < done + take]
+                current.append((SequenceStep(s.slot, s.tokens[done:done + take], want), i, done))
+                room -= take
+                done += take
+                if room == 0:
+                    portions.append(current)
+                    current, room = [], max_step_tokens
+        if current:
+            portions.append(current)
+        rows = []
+        for portion in portions:
+            rows.append(self.step([p[0] for p in portion]))
+            keys += [(i, done + w) for step, i, done in portion for w in step.want]
+        logits = torch.cat(rows, dim=0)
+        wanted = [(i, int(w)) for i, s in enumerate(batch) for w in s.want]
+        if keys == wanted:
+            return logits
+        # wanted places that were not in ascending order within a sequence
+        at = {}
+        for r, k in enumerate(keys):
+            at.setdefault(k, []).append(r)
+        order = [at[k].pop(0) for k in wanted]
+        return logits[torch.tensor(order, dtype=torch.long, device=logits.device)]
 
     def check_status(self) -> None:
         """Raise if a kernel flagged bad input since the last check (syncs)."""

@@ -12,7 +12,7 @@ import torch
 from ..cache import KVRequest, KVView, StateRequest
 from ..csrc import ops
 from ..config.spec import ModelSpec
-from ..parts import BLOCKS, NORMS, LinearHead, TokenEmbedding
+from ..parts import BLOCKS, EMBEDDINGS, HEADS, NORMS
 from ..weights.loader import WeightSpec
 
 
@@ -22,15 +22,16 @@ class DecoderModel:
         if dtype not in (torch.float32, torch.bfloat16):
             raise ValueError(f"compute dtype must be float32 or bfloat16; got {dtype}")
         self.spec, self.dtype, self.device = spec, dtype, torch.device(device)
-        self.embedding = TokenEmbedding(spec.embedding.params, "", dtype, self.device)
+        self.embedding = EMBEDDINGS.build(spec.embedding.kind, spec.embedding.params, "", dtype,
+                                          self.device)
         self.blocks = [BLOCKS.build(layer.block, layer, dtype, self.device) for layer in spec.layers]
         self.final_norm = NORMS.build(spec.final_norm.kind, spec.final_norm.params, "", dtype,
                                       self.device)
-        self.head = LinearHead(spec.head.params, "", dtype, self.device)
+        self.head = HEADS.build(spec.head.kind, spec.head.params, "", dtype, self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._pick_scratch: Dict[int, torch.Tensor] = {}
         for i, entry in enumerate(spec.schedule):
-            wants = self.blocks[entry.layer].mixer.cache_request()
+            wants = self.blocks[entry.layer].cache_request()
             if entry.cache_of is not None and wants is not None:
                 raise ValueError(f"schedule[{i}] reads the cache of entry {entry.cache_of} but its "
                                  f"mixer writes one of its own")
@@ -62,9 +63,17 @@ class DecoderModel:
             total += self.blocks[entry.layer].parameter_bytes()
         return total
 
+    def step_flops(self, counts, starts, wanted: int) -> float:
+        """Floating-point operations of one step (a multiply-add counts two): every
+        scheduled block over the step's tokens, and the head on the wanted rows."""
+        total = self.head.step_flops(counts, starts, wanted)
+        for entry in self.spec.schedule:
+            total += self.blocks[entry.layer].step_flops(counts, starts)
+        return total
+
     # -- cache ----------------------------------------------------------------
     def cache_requests(self) -> List[Optional[object]]:
-        return [None if e.cache_of is not None else self.blocks[e.layer].mixer.cache_request()
+        return [None if e.cache_of is not None else self.blocks[e.layer].cache_request()
                 for e in self.spec.schedule]
 
     def bind_cache(self, cache) -> None:
@@ -72,7 +81,7 @@ class DecoderModel:
         for i, entry in enumerate(self.spec.schedule):
             view = cache.view(entry.cache_of if entry.cache_of is not None else i)
             if entry.cache_of is not None:
-                self.blocks[entry.layer].mixer.check_shared_cache(view)
+                self.blocks[entry.layer].check_shared_cache(view)
             self._views.append(view)
 
     def step_tables(self, counts, starts) -> Dict[str, object]:
@@ -91,7 +100,7 @@ class DecoderModel:
         each wanted row, ``tokens``/``pos`` (the step's own inputs) move on to the
         next step on live rows; ``logits`` is written too when it is given."""
         r = picks.numel()
-        if self.head.fuses_norm(self.final_norm, r):
+        if getattr(self.head, "forward_pick", None) and self.head.fuses_norm(self.final_norm, r):
             self._run_blocks(ctx)
             ws = ctx.workspace
             hidden = ws.get("hidden", (ctx.n_tokens, self.spec.hidden_size), torch.float32)
@@ -124,7 +133,8 @@ class DecoderModel:
         ws = ctx.workspace
         hidden = self._run_blocks(ctx)
         r = logits.shape[0]
-        if r and self.head.fuses_norm(self.final_norm, r):
+        if r and getattr(self.head, "forward_normed", None) \
+                and self.head.fuses_norm(self.final_norm, r):
             self.head.forward_normed(hidden, self.final_norm, want_rows, logits)
         elif r:
             final = ws.get("final", (r, self.spec.hidden_size), self.dtype)

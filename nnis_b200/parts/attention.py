@@ -44,6 +44,9 @@ class Attention(Part):
             raise ValueError(f"attention kernels take even head sizes up to 256; got {self.head_dim}")
         pos = params["position"]
         self.position = POSITIONS.build(pos.kind, pos.params, prefix, dtype, device)
+        # False: the encoding has arithmetic of its own (``apply``), so the
+        # projection runs unfused and the kernels rotate nothing
+        self.position_in_kernel = bool(getattr(self.position, "in_kernel", True))
         self.scale = 1.0 / math.sqrt(float(self.head_dim))
         self.stored_kv = self.kv_heads if self.own_kv else 0
         self.w_qkv = self.b_qkv = self.w_o = self.b_o = None
@@ -88,28 +91,47 @@ class Attention(Part):
                 (self.kv_heads, view.page_size, self.head_dim) or view.window != self.window:
             raise ValueError("the shared cache does not fit this attention's heads or window")
 
+    def step_flops(self, counts, starts) -> float:
+        d, nq, nkv, H = self.head_dim, self.heads, self.kv_heads, self.hidden
+        tokens = sum(counts)
+        flops = 2.0 * tokens * H * ((nq + 2 * self.stored_kv) * d + nq * d)
+        for c, st in zip(counts, starts):  # scores and weighted values over the visible keys
+            keys = sum(min(st + q + 1, self.window) if self.window > 0 else st + q + 1
+                       for q in range(c)) if self.window > 0 else c * st + c * (c + 1) // 2
+            flops += 4.0 * nq * d * keys
+        return flops
+
     # -- work lists ---------------------------------------------------------
     def _tc_plan_name(self) -> str:
         return f"prefill_tc/window{self.window}/heads{self.heads}"
 
+    TILES_64 = "prefill_mma/tiles64"  # (sequence, first query) per 64 queries of the step
+
     def step_tables(self, counts, starts, have=()):
-        """Units of the tcgen05 prompt attention kernel (bfloat16, head
-        size 64), shared by all layers with this window and number of heads."""
-        if self.dtype != torch.bfloat16 or not ops.attention_prefill_tc_takes(
-                self.head_dim, PAGE_SIZE, self.heads * self.head_dim):
+        """Work lists of the bfloat16 prompt attention kernels: the units of the
+        tcgen05 kernel (head size 64), shared by all layers with this window and
+        number of heads, where that kernel pays; else the 64-query tiles of the
+        mma.sync kernel (head sizes 64 and 128), the same for every layer."""
+        if self.dtype != torch.bfloat16:
             return {}
         name = self._tc_plan_name()
-        if name + "/units" in have or not ops.prefill_tc_pays(counts, starts, self.window):
-            return {}
-        units, slots = ops.prefill_tc_plan(counts, starts, self.window, self.heads,
-                                           ops.sm_count(self.device))
-        return {name + "/units": units, name + "/slots": np.asarray([slots], dtype=np.int32)}
+        if ops.attention_prefill_tc_takes(self.head_dim, PAGE_SIZE, self.heads * self.head_dim) \
+                and ops.prefill_tc_pays(counts, starts, self.window):
+            if name + "/units" in have:
+                return {}
+            units, slots = ops.prefill_tc_plan(counts, starts, self.window, self.heads,
+                                               ops.sm_count(self.device))
+            return {name + "/units": units, name + "/slots": np.asarray([slots], dtype=np.int32)}
+        if ops.attention_decode_mma_takes(self.head_dim, PAGE_SIZE) and self.TILES_64 not in have:
+            tiles = [(i, q0) for i, c in enumerate(counts) for q0 in range(0, int(c), 64)]
+            return {self.TILES_64: np.asarray(tiles, dtype=np.int32).reshape(-1, 2)}
+        return {}
 
     # -- run --------------------------------------------------------------
     def _decode_kernels(self, ctx, n: int) -> bool:
         """The fused bfloat16 decode kernel for q, k, v: few rows, one token each."""
         return (self.dtype == torch.bfloat16 and ctx.decode and n <= ops.DECODE_GEMV_ROWS
-                and self.head_dim % 16 == 0
+                and self.head_dim % 16 == 0 and self.position_in_kernel
                 and ops.gemv_takes(n, self.w_qkv.shape[0], self.hidden, ops.EPI_QKV, self.device))
 
     def _fused_out(self, ctx, n: int) -> bool:
@@ -148,7 +170,7 @@ class Attention(Part):
         d, nq, nkv = self.head_dim, self.heads, self.kv_heads
         ws = ctx.workspace
         table = ctx.page_tables[cache.group]
-        tables = self.position.rotary_tables()
+        tables = self.position.rotary_tables() if self.position_in_kernel else None
         cos, sin = tables if tables is not None else (None, None)
         attn = ws.get("attn", (n, nq * d), self.dtype)
         if self._decode_kernels(ctx, n):
@@ -162,7 +184,7 @@ class Attention(Part):
                           v_cache=cache.v if self.own_kv else None, heads=nq,
                           kv_heads=self.stored_kv, head_dim=d, page_size=cache.page_size)
             q_buf, q_stride = q, nq * d
-        elif self.dtype == torch.bfloat16 and ops.gemm_tc_qkv_takes(d) \
+        elif self.dtype == torch.bfloat16 and ops.gemm_tc_qkv_takes(d) and self.position_in_kernel \
                 and ops.gemm_tc_takes(n, self.w_qkv.shape[0], self.hidden):
             # tensor-core product with bias, RoPE and the cache store in its epilogue
             q = ws.get("q", (n, nq * d), self.dtype)
@@ -175,6 +197,8 @@ class Attention(Part):
         else:
             qkv = ws.get("qkv", (n, (nq + 2 * self.stored_kv) * d), self.dtype)
             linear(x, self.w_qkv, self.b_qkv, qkv, STORE)
+            if not self.position_in_kernel:  # an encoding with arithmetic of its own
+                self.position.apply(qkv, ctx, nq, self.stored_kv, d)
             ops.rope_store(qkv, ctx.token_pos, ctx.token_seq, table if self.own_kv else None, cos,
                            sin, cache.k if self.own_kv else None, cache.v if self.own_kv else None,
                            nq, self.stored_kv, d, cache.page_size)
@@ -212,9 +236,9 @@ class Attention(Part):
             ops.attention_prefill_tc(q_buf, q_stride, cache.k, cache.v, ctx.tables[name + "/units"],
                                      partial, tickets, ctx.seq_first_row, ctx.seq_start, ctx.seq_count,
                                      table, attn, nq, nkv, d, self.window, self.scale)
-        elif self.dtype == torch.bfloat16 and not ctx.decode and ctx.q_tiles is not None \
+        elif self.dtype == torch.bfloat16 and not ctx.decode and self.TILES_64 in ctx.tables \
                 and ops.attention_decode_mma_takes(d, cache.page_size):
-            ops.attention_prefill_mma(q_buf, q_stride, cache.k, cache.v, ctx.q_tiles,
+            ops.attention_prefill_mma(q_buf, q_stride, cache.k, cache.v, ctx.tables[self.TILES_64],
                                       ctx.seq_first_row, ctx.seq_start, ctx.seq_count, table, attn,
                                       nq, nkv, d, self.window, self.scale)
         else:

@@ -9,10 +9,16 @@ learns which model it is in.  Every part says which tensors it wants
 registry              interface beyond ``weight_specs`` / ``load``
 ====================  =====================================================
 ``NORMS``             ``forward(x_f32 [n, width], out [m, width], rows=None)``
-``POSITIONS``         ``rotary_tables()`` -> (cos, sin) or None; ``apply(qk, ctx)``
+``POSITIONS``         ``rotary_tables()`` -> (cos, sin) or None, and, for an
+                      encoding with arithmetic of its own (``in_kernel = False``),
+                      ``apply(qkv, ctx, heads, kv_heads, head_dim)``
 ``MIXERS``            ``cache_request()``; ``forward(x, ctx, residual, cache)``
 ``FEED_FORWARDS``     ``forward(x, ctx, residual)``
-``BLOCKS``            ``forward(hidden_f32, ctx, cache)`` over four parts
+``BLOCKS``            ``forward(hidden_f32, ctx, cache)``; ``parts()``;
+                      ``cache_request()``, ``check_shared_cache(view)``
+``EMBEDDINGS``        ``forward(tokens, hidden_f32, status)``
+``HEADS``             ``forward(x, logits_f32)``; optionally ``fuses_norm``,
+                      ``forward_normed``, ``forward_pick`` (see ``LinearHead``)
 ====================  =====================================================
 
 Mixers and feed-forwards read ``x`` (operand dtype, ``[n, width]``) and *add*
@@ -54,6 +60,12 @@ class Part:
         """Bytes of weights that one step reads."""
         return 0
 
+    def step_flops(self, counts, starts) -> float:
+        """Floating-point operations (a multiply-add counts two) of one step whose
+        sequences bring ``counts`` tokens after ``starts`` cached ones: what a
+        measurement divides by the step's time."""
+        return 0.0
+
     def step_tables(self, counts, starts, have=()) -> Dict[str, Any]:
         """Integer tables (numpy int32 arrays by name) that this part wants on the
         device for a prompt step whose sequences bring ``counts`` tokens after
@@ -83,8 +95,32 @@ class Registry:
         return sorted(self._kinds)
 
 
+class PositionEncoding(Part):
+    """How positions reach query and key heads.  Two ways to say it:
+
+    * ``rotary_tables()`` returns float32 ``(cos, sin)`` of ``[positions, head_dim / 2]``
+      for the rotate-half pairing over the whole head (or None: heads stay as they
+      are); the mixer's kernels apply them, fused with the projection where they can;
+    * an encoding with other arithmetic (interleaved pairs, a rotated fraction of the
+      head, a learned table ...) sets ``in_kernel = False`` and implements ``apply``:
+      it changes the q and k heads of the packed rows ``qkv`` ``[n, (heads + 2 *
+      kv_heads) * head_dim]`` in place (v untouched; ``kv_heads`` is 0 when the rows
+      hold q only), at the positions ``ctx.token_pos`` (-1: a padding row, to be left
+      alone), before keys and values go to the cache.  The mixer then runs its
+      projection unfused, calls ``apply`` and stores the heads as they come back."""
+    in_kernel = True
+
+    def rotary_tables(self):
+        return None
+
+    def apply(self, qkv: torch.Tensor, ctx, heads: int, kv_heads: int, head_dim: int) -> None:
+        raise NotImplementedError(f"{type(self).__name__} sets in_kernel = False but has no apply()")
+
+
 NORMS = Registry("norm")
 POSITIONS = Registry("position encoding")
 MIXERS = Registry("mixer")
 FEED_FORWARDS = Registry("feed-forward")
 BLOCKS = Registry("block arrangement")
+EMBEDDINGS = Registry("embedding")
+HEADS = Registry("head")

@@ -1,12 +1,18 @@
-"""Arrangements of the four parts of a layer.
+"""Arrangements of the parts of a layer.
+
+``Block`` is what the model needs of an arrangement: its parts (for weights and
+work lists), what it wants of the cache, and ``forward``.  An arrangement reads
+its parts from ``LayerSpec.parts`` by the roles it knows, so one with other or more
+sub-layers (a post-norm, one norm for parallel branches, a third sub-layer) is a
+class registered in ``BLOCKS``, not a change here.
 
 ``prenorm``: h += mixer(norm1(h)); h += ffn(norm2(h)) - the order of NNIS's
-decoder (crates/nnis-model/src/runtime.rs:946-1097).  Another arrangement
-(post-norm, parallel attention and MLP) is another class registered here.
+decoder (crates/nnis-model/src/runtime.rs:946-1097); roles mixer_norm, mixer,
+ffn_norm, ffn.
 """
 from __future__ import annotations
 
-from typing import Dict, Mapping
+from typing import Dict, Mapping, Sequence
 
 import torch
 
@@ -14,19 +20,33 @@ from ..weights.loader import WeightSpec
 from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Part
 
 
-class PreNormBlock:
-    def __init__(self, layer_spec, dtype: torch.dtype, device: torch.device):
-        p = layer_spec.prefix
-        self.mixer_norm = NORMS.build(layer_spec.mixer_norm.kind, layer_spec.mixer_norm.params, p,
-                                      dtype, device)
-        self.mixer = MIXERS.build(layer_spec.mixer.kind, layer_spec.mixer.params, p, dtype, device)
-        self.ffn_norm = NORMS.build(layer_spec.ffn_norm.kind, layer_spec.ffn_norm.params, p, dtype,
-                                    device)
-        self.ffn = FEED_FORWARDS.build(layer_spec.ffn.kind, layer_spec.ffn.params, p, dtype, device)
-        self.dtype = dtype
+class Block:
+    """Base of the arrangements: subclasses build their parts in ``__init__`` (with
+    ``build``), list them in ``parts()`` and run them in ``forward``.  ``mixer`` is
+    the part that owns the layer's cache, if any."""
+    mixer = None
 
-    def parts(self):
-        return (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn)
+    def __init__(self, layer_spec, dtype: torch.dtype, device: torch.device):
+        self.spec = layer_spec
+        self.dtype = dtype
+        self.device = device
+
+    def build(self, registry, role: str) -> Part:
+        part = self.spec.part(role)
+        return registry.build(part.kind, part.params, self.spec.prefix, self.dtype, self.device)
+
+    def parts(self) -> Sequence[Part]:
+        raise NotImplementedError
+
+    def forward(self, hidden: torch.Tensor, ctx, cache) -> None:
+        raise NotImplementedError
+
+    # -- what the model asks of every arrangement --------------------------------
+    def cache_request(self):
+        return self.mixer.cache_request() if self.mixer is not None else None
+
+    def check_shared_cache(self, view) -> None:
+        self.mixer.check_shared_cache(view)
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         specs: Dict[str, WeightSpec] = {}
@@ -41,6 +61,9 @@ class PreNormBlock:
     def parameter_bytes(self) -> int:
         return sum(part.parameter_bytes() for part in self.parts())
 
+    def step_flops(self, counts, starts) -> float:
+        return sum(part.step_flops(counts, starts) for part in self.parts())
+
     def step_tables(self, counts, starts, have=()) -> Dict[str, object]:
         tables: Dict[str, object] = {}
         for part in self.parts():
@@ -49,6 +72,18 @@ class PreNormBlock:
                 for name, arr in wants(counts, starts, tuple(have) + tuple(tables)).items():
                     tables.setdefault(name, arr)
         return tables
+
+
+class PreNormBlock(Block):
+    def __init__(self, layer_spec, dtype: torch.dtype, device: torch.device):
+        super().__init__(layer_spec, dtype, device)
+        self.mixer_norm = self.build(NORMS, "mixer_norm")
+        self.mixer = self.build(MIXERS, "mixer")
+        self.ffn_norm = self.build(NORMS, "ffn_norm")
+        self.ffn = self.build(FEED_FORWARDS, "ffn")
+
+    def parts(self):
+        return (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn)
 
     def forward(self, hidden: torch.Tensor, ctx, cache) -> None:
         n, width = hidden.shape

@@ -12,7 +12,7 @@ import torch
 
 from ..csrc import ops
 from ..weights.loader import WeightSpec
-from .base import Part
+from .base import EMBEDDINGS, HEADS, Part
 from .linear import STORE_F32, linear
 
 
@@ -58,6 +58,9 @@ class LinearHead(Part):
     def parameter_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()
 
+    def step_flops(self, counts, starts, wanted: int = 0) -> float:
+        return 2.0 * self.vocab * self.width * wanted
+
     def forward(self, x: torch.Tensor, logits: torch.Tensor) -> None:
         linear(x, self.weight, None, logits, STORE_F32)
 
@@ -83,3 +86,7 @@ class LinearHead(Part):
         """Final norm of the wanted rows folded into the head (few rows)."""
         ops.gemv_bf16(self.weight, None, logits, ops.EPI_STORE_F32, hidden=hidden,
                       norm_weight=norm.weight, eps=norm.eps, rows=rows, m=logits.shape[0])
+
+
+EMBEDDINGS.register("token_embedding", TokenEmbedding)
+HEADS.register("linear_head", LinearHead)

@@ -56,6 +56,9 @@ class GatedMLP(Part):
         return sum(t.numel() * t.element_size()
                    for t in (self.w_gu, self.w_down, self.b_gu, self.b_down) if t is not None)
 
+    def step_flops(self, counts, starts) -> float:
+        return 2.0 * 3 * self.hidden * self.inter * sum(counts)
+
     def _fused_gate_up(self, ctx, n: int) -> bool:
         """The fused bfloat16 decode kernel for gate/up (few rows, one token each)."""
         return (self.dtype == torch.bfloat16 and ctx.decode and n <= ops.DECODE_GEMV_ROWS

@@ -194,3 +194,63 @@ def test_truncate_gives_pages_back_and_refuses_what_cannot_be_undone():
     with pytest.raises(SlotError, match="fixed-size state"):
         st.truncate(s, 5)
     assert st.length(s) == 10
+
+
+def test_snapshot_and_restore_bring_back_length_pages_and_state():
+    """The way back for a model with fixed-size state: truncate is refused, a
+    snapshot taken before the tokens that are taken back restores both."""
+    c = make(requests=[KVRequest(2, 16), StateRequest((3,))], max_slots=2)
+    s = c.acquire()
+    state = c.view(1).state
+    c.reserve([s], [70])
+    c.commit([s], [70])
+    state[s] = torch.tensor([1.0, 2.0, 3.0])
+    with pytest.raises(SlotError, match="snapshot"):
+        c.truncate(s, 10)
+    snap = c.snapshot(s)
+    c.reserve([s], [200])
+    c.commit([s], [200])
+    state[s] = torch.tensor([9.0, 9.0, 9.0])
+    assert len(c.page_table(0, s)) == 4
+    c.restore(snap)
+    assert c.length(s) == 70 and len(c.page_table(0, s)) == 2 and state[s].tolist() == [1.0, 2.0, 3.0]
+    assert c.usage()["pages_held"] == [2]
+    c.check()
+    c.restore(snap)  # again: nothing to forget, the state is written once more
+    # a snapshot of a longer sequence than the slot holds now, or of an earlier owner, is refused
+    later = c.snapshot(s)
+    later.length = 500
+    with pytest.raises(SlotError, match="only"):
+        c.restore(later)
+    c.release(s)
+    with pytest.raises(SlotError, match="any more"):
+        c.restore(snap)
+    again = c.acquire()
+    assert again == s
+    with pytest.raises(SlotError, match="any more"):
+        c.restore(snap)
+    c.release(again)
+    c.check()
+
+
+def test_a_slots_version_tells_copies_of_its_page_table_when_they_are_stale():
+    """Growth at the end keeps a slot's version; being taken, given back or truncated
+    changes it (a truncated table may grow back to the same length with other pages)."""
+    c = make(max_tokens=64 * 6, max_slots=2)
+    a, b = c.acquire(), c.acquire()
+    v0 = c.versions[a]
+    c.reserve([a], [130])
+    c.commit([a], [130])
+    assert c.versions[a] == v0
+    table, pages = c.page_table(0, a), list(c.page_table(0, a))
+    c.truncate(a, 64)
+    assert c.versions[a] == v0 + 1
+    c.reserve([b], [64])            # b takes the lowest page that a gave back
+    c.commit([b], [64])
+    c.reserve([a], [130])
+    c.commit([a], [130])
+    assert c.page_table(0, a) is table and len(table) == len(pages) and table != pages
+    c.release(a)
+    assert c.versions[a] == v0 + 2
+    c.release(b)
+    c.check()

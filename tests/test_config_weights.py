@@ -40,7 +40,7 @@ def test_smollm2_shape_needs_no_constant_in_code():
                torch_dtype="bfloat16", eos_token_id=0, bos_token_id=0, use_cache=True)
     spec = config_from_dict(raw).to_spec()
     assert len(spec.layers) == 30 and len(spec.schedule) == 30
-    assert spec.layers[0].mixer["head_dim"] == 64
+    assert spec.layers[0].part("mixer")["head_dim"] == 64
     assert spec.head["tied_to"] == "model.embed_tokens"
 
 

@@ -526,3 +526,69 @@ def test_cli_random_model_writes_folders_that_validate(tmp_path):
                 ["random-model", "--config", "c", "--seed", "1", "--out", "x", "--format", "gguf"]):
         with pytest.raises(UsageError):
             parse_args(bad)
+
+
+def test_the_graph_decoders_copy_of_a_page_table_follows_a_truncation(monkeypatch):
+    """GraphDecoder.upload keeps a pinned copy of every row's page table and rewrites
+    only what changed; a table that was truncated and grew back to the same length with
+    other pages must be rewritten (the slot's version says so)."""
+    import types
+
+    import torch
+
+    from nnis_b200.cache import CacheManager, KVRequest
+    from nnis_b200.engine import decode as D
+    cache = CacheManager([KVRequest(1, 16)], torch.float32, torch.device("cpu"), 64 * 6, 2, 1000)
+    dec = D.GraphDecoder.__new__(D.GraphDecoder)
+    dec.engine = types.SimpleNamespace(cache=cache)
+    dec.rows, dec.cols = 2, 4
+    dec.tables = [None]
+    dec.state_ints = 2 * (3 + 4)
+    dec.state = torch.zeros(dec.state_ints, dtype=torch.int32)
+    dec.host_state = torch.zeros(dec.state_ints, dtype=torch.int32)
+    dec._host_np = dec.host_state.numpy()
+    dec._host_state_free = types.SimpleNamespace(synchronize=lambda: None, record=lambda: None)
+    dec._mirror = None
+    dec.host_tables = [[[-1] * 4 for _ in range(2)]]
+    dec._host_tables_unknown = False
+    monkeypatch.setattr(D.ops, "copy_async", lambda dst, src: dst.copy_(src))
+    a, b = cache.acquire(), cache.acquire()
+    cache.reserve([a], [130])
+    cache.commit([a], [130])
+    line = lambda row: dec.state[6 + 4 * row:10 + 4 * row].tolist()
+    dec.upload([5], [129], [a])
+    assert line(0)[:3] == cache.page_table(0, a) and line(0)[3] == -1
+    cache.truncate(a, 64)
+    cache.reserve([b], [64])
+    cache.commit([b], [64])
+    cache.reserve([a], [130])
+    cache.commit([a], [130])
+    dec.upload([5], [129], [a])
+    assert line(0)[:3] == cache.page_table(0, a)
+
+
+def test_prompt_steps_are_cut_into_portions_in_order():
+    """Engine.step_in_portions on a scripted step: sequences in order, one that does not
+    fit is cut, wanted places follow their tokens, rows come back in the order asked for."""
+    import torch
+
+    from nnis_b200.engine.engine import Engine, SequenceStep
+    calls = []
+
+    class Scripted:
+        step_in_portions = Engine.step_in_portions
+
+        def step(self, batch):
+            calls.append([(s.slot, list(s.tokens), list(s.want)) for s in batch])
+            rows = [[s.slot, s.tokens[w]] for s in batch for w in s.want]
+            return torch.tensor(rows, dtype=torch.float32).reshape(len(rows), 2)
+    e = Scripted()
+    batch = [SequenceStep(0, list(range(100, 107)), [6, 0]), SequenceStep(1, list(range(200, 203)), [2]),
+             SequenceStep(2, list(range(300, 312)), [11, 3, 4])]
+    got = e.step_in_portions(batch, 5)
+    assert [sum(len(t) for _, t, _ in c) for c in calls] == [5, 5, 5, 5, 2]
+    assert calls[0] == [(0, [100, 101, 102, 103, 104], [0])]
+    assert calls[1] == [(0, [105, 106], [1]), (1, [200, 201, 202], [2])]
+    assert got.tolist() == [[0, 106], [0, 100], [1, 202], [2, 311], [2, 303], [2, 304]]
+    calls.clear()
+    assert e.step_in_portions(batch, 100).shape[0] == 6 and len(calls) == 1

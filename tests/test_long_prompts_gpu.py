@@ -44,8 +44,9 @@ def test_long_prompts_in_chunks_with_and_without_a_window(dtype):
     from nnis_b200.weights import random_tensors
     spec = config_from_dict(CFG).to_spec()
     layers = list(spec.layers)
-    mixer = layers[1].mixer
-    layers[1] = replace(layers[1], mixer=PartSpec(mixer.kind, {**mixer.params, "window": WINDOWS[1]}))
+    mixer = layers[1].part("mixer")
+    layers[1] = replace(layers[1], parts={**layers[1].parts, "mixer": PartSpec(
+        mixer.kind, {**mixer.params, "window": WINDOWS[1]})})
     spec = replace(spec, layers=tuple(layers))
     tensors = random_tensors(DecoderModel.weight_specs_of(spec), seed=64, std=1.0, norm_std=0.1,
                              std_by_fan_in=True)

@@ -16,6 +16,11 @@ DEV = torch.device("cuda:0")
 DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 
 
+def prenorm_layer(prefix, mixer_norm, mixer, ffn_norm, ffn):
+    return LayerSpec(prefix, "prenorm", {"mixer_norm": mixer_norm, "mixer": mixer,
+                                         "ffn_norm": ffn_norm, "ffn": ffn})
+
+
 def close(got, want, dtype, what=""):
     got, want = got.double().cpu(), want.double().cpu()
     t = dict(rtol=2e-5, atol=2e-5) if dtype == "float32" else dict(rtol=2e-2, atol=2e-2)
@@ -214,11 +219,10 @@ def test_a_toy_mixer_with_its_own_state_is_registered_built_and_stepped():
     _register_toy()
     H, V, I, eps = 24, 50, 40, 1e-5
     norm = lambda name: PartSpec("rmsnorm", {"size": H, "eps": eps, "name": name})
-    layers = tuple(LayerSpec(
-        prefix=f"blocks.{i}", block="prenorm", mixer_norm=norm("n1"),
-        mixer=PartSpec("toy_running_mean", {"width": H}), ffn_norm=norm("n2"),
-        ffn=PartSpec("gated_mlp", {"hidden_size": H, "intermediate_size": I, "activation": "silu",
-                                   "bias": False, "names": {"gate": "g", "up": "u", "down": "d"}}))
+    layers = tuple(prenorm_layer(
+        f"blocks.{i}", norm("n1"), PartSpec("toy_running_mean", {"width": H}), norm("n2"),
+        PartSpec("gated_mlp", {"hidden_size": H, "intermediate_size": I, "activation": "silu",
+                               "bias": False, "names": {"gate": "g", "up": "u", "down": "d"}}))
         for i in range(2))
     spec = ModelSpec(architecture="ToyRunningMean", hidden_size=H, vocab_size=V, max_positions=256,
                      embedding=PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H,
@@ -250,6 +254,13 @@ def test_a_toy_mixer_with_its_own_state_is_registered_built_and_stepped():
             check_logits(got.cpu().numpy(), torch.stack([want["a"][5 + t], want["b"][2 + t]]),
                          "float32", f"toy token {t} round {round_}")
         engine.release_slot(sb)
+        # the way back for a model with state: a snapshot before tokens that are taken back
+        with pytest.raises(Exception, match="snapshot"):
+            engine.truncate(sa, 3)
+        snap = engine.snapshot(sa)
+        engine.step([SequenceStep(sa, [11, 12, 13], [])])
+        engine.restore(snap)
+        assert engine.cache.length(sa) == 7
         got = engine.step([SequenceStep(sa, [seqs["a"][7]], [0])])
         check_logits(got.cpu().numpy(), want["a"][7:8], "float32", "toy tail")
         engine.release_slot(sa)
@@ -264,11 +275,11 @@ def test_schedule_runs_a_layer_twice_and_lets_a_layer_read_anothers_cache():
     norm = lambda name: PartSpec("rmsnorm", {"size": H, "eps": eps, "name": name})
     ffn = PartSpec("gated_mlp", {"hidden_size": H, "intermediate_size": I, "activation": "silu",
                                  "bias": False, "names": {"gate": "g", "up": "u", "down": "d"}})
-    layers = (LayerSpec("l0", "prenorm", norm("n1"), PartSpec("attention", attention_params(H, nq, nkv, d)),
-                        norm("n2"), ffn),
-              LayerSpec("l1", "prenorm", norm("n1"),
-                        PartSpec("attention", attention_params(H, nq, nkv, d, kv="shared")),
-                        norm("n2"), ffn))
+    layers = (prenorm_layer("l0", norm("n1"), PartSpec("attention", attention_params(H, nq, nkv, d)),
+                            norm("n2"), ffn),
+              prenorm_layer("l1", norm("n1"),
+                            PartSpec("attention", attention_params(H, nq, nkv, d, kv="shared")),
+                            norm("n2"), ffn))
     spec = ModelSpec(architecture="ToySchedule", hidden_size=H, vocab_size=V, max_positions=512,
                      embedding=PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H, "name": "emb"}),
                      layers=layers,
@@ -388,12 +399,12 @@ def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_run_in_a_model():
     toy_pos = PartSpec("toy_interpolated_rope", {"head_dim": d, "theta": 10000.0, "max_positions": 512,
                                                  "factor": factor})
     attn0 = dict(attention_params(H, nq, nkv, d), position=toy_pos)
-    layers = (LayerSpec("l0", "prenorm", norm("n1"), PartSpec("attention", attn0), norm("n2"),
-                        PartSpec("toy_top1_experts", {"hidden_size": H, "expert_size": I, "experts": E})),
-              LayerSpec("l1", "prenorm", norm("n1"), PartSpec("attention", attention_params(H, nq, nkv, d)),
-                        norm("n2"),
-                        PartSpec("gated_mlp", {"hidden_size": H, "intermediate_size": I, "activation": "silu",
-                                               "bias": False, "names": {"gate": "g", "up": "u", "down": "d"}})))
+    layers = (prenorm_layer("l0", norm("n1"), PartSpec("attention", attn0), norm("n2"),
+                            PartSpec("toy_top1_experts", {"hidden_size": H, "expert_size": I, "experts": E})),
+              prenorm_layer("l1", norm("n1"), PartSpec("attention", attention_params(H, nq, nkv, d)),
+                            norm("n2"),
+                            PartSpec("gated_mlp", {"hidden_size": H, "intermediate_size": I, "activation": "silu",
+                                                   "bias": False, "names": {"gate": "g", "up": "u", "down": "d"}})))
     spec = ModelSpec(architecture="ToyRouted", hidden_size=H, vocab_size=V, max_positions=512,
                      embedding=PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H, "name": "emb"}),
                      layers=layers, schedule=(ScheduleEntry(0), ScheduleEntry(1)), final_norm=norm("final"),
@@ -446,3 +457,175 @@ def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_run_in_a_model():
     got = engine.step([SequenceStep(sa, [seqs["a"][11]], [0])])
     check_logits(got.cpu().numpy(), want["a"][11:12], "float32", "routed tail")
     engine.release_slot(sa)
+
+
+# ---------------------------------------------------------------------------
+# Toys for the remaining seams, again registered from here: a block arrangement with
+# other sub-layers than the pre-norm one (a norm after the mixer, a third sub-layer),
+# position encodings with arithmetic of their own (pairs of neighbours; half of the
+# head), an embedding with a scale and a head with a soft cap.  No model's parts.
+# ---------------------------------------------------------------------------
+def _register_seam_toys():
+    from nnis_b200.csrc import ops
+    from nnis_b200.parts import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS,
+                                 Block, LinearHead, PositionEncoding, TokenEmbedding)
+
+    class SandwichBlock(Block):
+        """h += post(mixer(pre(h))); h += ffn(n2(h)); h += extra(n3(h))."""
+
+        def __init__(self, layer_spec, dtype, device):
+            super().__init__(layer_spec, dtype, device)
+            self.pre, self.post = self.build(NORMS, "pre"), self.build(NORMS, "post")
+            self.mixer = self.build(MIXERS, "mixer")
+            self.n2, self.ffn = self.build(NORMS, "n2"), self.build(FEED_FORWARDS, "ffn")
+            self.n3, self.extra = self.build(NORMS, "n3"), self.build(FEED_FORWARDS, "extra")
+
+        def parts(self):
+            return (self.pre, self.post, self.mixer, self.n2, self.ffn, self.n3, self.extra)
+
+        def forward(self, hidden, ctx, cache):
+            n, width = hidden.shape
+            normed = ctx.workspace.get("normed", (n, width), self.dtype)
+            branch = ctx.workspace.get("toy_branch", (n, width), torch.float32)
+            self.pre.forward(hidden, normed)
+            branch.zero_()
+            self.mixer.forward(normed, ctx, branch, cache)   # the mixer adds into what it is given
+            post = ctx.workspace.get("toy_post", (n, width), torch.float32)
+            self.post.forward(branch, post)
+            hidden += post
+            for norm, ffn in ((self.n2, self.ffn), (self.n3, self.extra)):
+                norm.forward(hidden, normed)
+                ffn.forward(normed, ctx, hidden)
+
+    def rotate(x, pos, pairs_a, pairs_b, inv_freq):
+        """x [n, heads, d] in place: (a, b) -> (a c - b s, b c + a s) at each row's position."""
+        angle = pos.clamp(min=0).float()[:, None] * inv_freq[None, :]
+        c, s_ = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
+        live = (pos >= 0)[:, None, None]
+        a, b = x[..., pairs_a].float(), x[..., pairs_b].float()
+        x[..., pairs_a] = torch.where(live, a * c - b * s_, a).to(x.dtype)
+        x[..., pairs_b] = torch.where(live, b * c + a * s_, b).to(x.dtype)
+
+    class PairRope(PositionEncoding):
+        """``interleaved``: pairs (2j, 2j + 1) over the whole head; else rotate-half
+        pairs over the first ``rotary_dim`` elements only."""
+        in_kernel = False
+
+        def __init__(self, params, prefix, dtype, device):
+            super().__init__(params, prefix, dtype, device)
+            d, r = int(params["head_dim"]), int(params.get("rotary_dim", params["head_dim"]))
+            self.inv = (1.0 / torch.pow(torch.tensor(float(params["theta"])),
+                                        2 * torch.arange(r // 2).float() / r)).to(device)
+            j = torch.arange(r // 2, device=device)
+            self.a, self.b = (2 * j, 2 * j + 1) if params.get("interleaved") else (j, j + r // 2)
+
+        def apply(self, qkv, ctx, heads, kv_heads, head_dim):
+            n = qkv.shape[0]
+            x = qkv[:, :(heads + kv_heads) * head_dim].view(n, heads + kv_heads, head_dim)
+            rotate(x, ctx.token_pos[:n], self.a, self.b, self.inv)
+
+    class ScaledEmbedding(TokenEmbedding):
+        def forward(self, tokens, hidden, status):
+            super().forward(tokens, hidden, status)
+            hidden *= float(self.params["scale"])
+
+    class CappedHead(LinearHead):
+        """logits = cap * tanh(x W^T / cap); no fused pick."""
+        forward_pick = None
+        forward_normed = None
+
+        def forward(self, x, logits):
+            super().forward(x, logits)
+            cap = float(self.params["cap"])
+            logits.copy_(cap * torch.tanh(logits / cap))
+
+    BLOCKS.register("toy_sandwich", SandwichBlock)
+    POSITIONS.register("toy_pair_rope", PairRope)
+    EMBEDDINGS.register("toy_scaled_embedding", ScaledEmbedding)
+    HEADS.register("toy_capped_head", CappedHead)
+
+
+def test_toy_arrangement_positions_embedding_and_head_need_no_change_to_the_framework():
+    from nnis_b200.engine import Engine, SequenceStep
+    from nnis_b200.engine.model import DecoderModel
+    from nnis_b200.weights import random_tensors
+    _register_seam_toys()
+    H, V, I, nq, nkv, d, eps, theta, scale, cap = 48, 70, 40, 3, 1, 16, 1e-5, 10000.0, 3.0, 2.5
+    norm = lambda name: PartSpec("rmsnorm", {"size": H, "eps": eps, "name": name})
+    mlp = lambda g, u, dn: PartSpec("gated_mlp", {"hidden_size": H, "intermediate_size": I, "activation": "silu",
+                                                  "bias": False, "names": {"gate": g, "up": u, "down": dn}})
+    pos0 = PartSpec("toy_pair_rope", {"head_dim": d, "theta": theta, "interleaved": True})
+    pos1 = PartSpec("toy_pair_rope", {"head_dim": d, "theta": theta, "rotary_dim": d // 2})
+    layers = (LayerSpec("l0", "toy_sandwich", {
+                  "pre": norm("pre"), "post": norm("post"),
+                  "mixer": PartSpec("attention", dict(attention_params(H, nq, nkv, d), position=pos0)),
+                  "n2": norm("n2"), "ffn": mlp("g", "u", "d"), "n3": norm("n3"), "extra": mlp("g2", "u2", "d2")}),
+              prenorm_layer("l1", norm("n1"),
+                            PartSpec("attention", dict(attention_params(H, nq, nkv, d), position=pos1)),
+                            norm("n2"), mlp("g", "u", "d")))
+    spec = ModelSpec(architecture="ToySeams", hidden_size=H, vocab_size=V, max_positions=512,
+                     embedding=PartSpec("toy_scaled_embedding", {"vocab_size": V, "hidden_size": H,
+                                                                 "name": "emb", "scale": scale}),
+                     layers=layers, schedule=(ScheduleEntry(0), ScheduleEntry(1)), final_norm=norm("final"),
+                     head=PartSpec("toy_capped_head", {"vocab_size": V, "hidden_size": H, "name": "head",
+                                                       "tied_to": None, "cap": cap}))
+    wanted = DecoderModel.weight_specs_of(spec)
+    assert {"l0.post.weight", "l0.n3.weight", "l0.d2.weight", "head.weight"} <= set(wanted)
+    w = random_tensors(wanted, seed=33, std=1.0, norm_std=0.1, std_by_fan_in=True)
+
+    def plain_rotate(x, interleaved, rotary):
+        T = x.shape[0]
+        inv = 1.0 / torch.pow(torch.tensor(theta, dtype=torch.float32), 2 * torch.arange(rotary // 2).float() / rotary)
+        ang = (torch.arange(T, dtype=torch.float32)[:, None] * inv[None, :]).double()
+        c, s_ = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        out = x.clone()
+        j = torch.arange(rotary // 2)
+        a, b = (2 * j, 2 * j + 1) if interleaved else (j, j + rotary // 2)
+        out[..., a] = x[..., a] * c - x[..., b] * s_
+        out[..., b] = x[..., b] * c + x[..., a] * s_
+        return out
+
+    def plain(tokens):
+        T = len(tokens)
+        h = w["emb.weight"].double()[torch.tensor(tokens)] * scale
+
+        def attn(prefix, n, interleaved, rotary):
+            q = plain_rotate(P.linear(n, w[prefix + ".q.weight"]).view(T, nq, d), interleaved, rotary)
+            k = plain_rotate(P.linear(n, w[prefix + ".k.weight"]).view(T, nkv, d), interleaved, rotary)
+            v = P.linear(n, w[prefix + ".v.weight"]).view(T, nkv, d)
+            return P.linear(P.causal_attention(q, k, v).reshape(T, nq * d), w[prefix + ".o.weight"])
+
+        def ffn(prefix, n, g, u, dn):
+            return P.linear(P.swiglu(P.linear(n, w[f"{prefix}.{g}.weight"]), P.linear(n, w[f"{prefix}.{u}.weight"])),
+                            w[f"{prefix}.{dn}.weight"])
+        h = h + P.rms_norm(attn("l0", P.rms_norm(h, w["l0.pre.weight"], eps), True, d), w["l0.post.weight"], eps)
+        h = h + ffn("l0", P.rms_norm(h, w["l0.n2.weight"], eps), "g", "u", "d")
+        h = h + ffn("l0", P.rms_norm(h, w["l0.n3.weight"], eps), "g2", "u2", "d2")
+        h = h + attn("l1", P.rms_norm(h, w["l1.n1.weight"], eps), False, d // 2)
+        h = h + ffn("l1", P.rms_norm(h, w["l1.n2.weight"], eps), "g", "u", "d")
+        return cap * torch.tanh(P.linear(P.rms_norm(h, w["final.weight"], eps), w["head.weight"]) / cap)
+
+    seqs = {"a": [3, 14, 15, 9, 26, 5, 35, 8, 9, 7, 9, 32, 38, 46], "b": [62, 64, 3, 38, 32]}
+    want = {k: plain(v) for k, v in seqs.items()}
+    for dtype_engine in ("float32",):
+        engine = Engine.from_spec(spec, w, dtype=dtype_engine, max_tokens=64 * 8, max_slots=2)
+        sa, sb = engine.acquire_slot(), engine.acquire_slot()
+        got = engine.step([SequenceStep(sa, seqs["a"][:9], range(9)), SequenceStep(sb, seqs["b"][:3], [2])])
+        check_logits(got.cpu().numpy(), torch.cat([want["a"][:9], want["b"][2:3]]), "float32", "seams prompt")
+        for t in range(2):
+            got = engine.step([SequenceStep(sa, [seqs["a"][9 + t]], [0]), SequenceStep(sb, [seqs["b"][3 + t]], [0])])
+            check_logits(got.cpu().numpy(), torch.stack([want["a"][9 + t], want["b"][3 + t]]), "float32",
+                         f"seams token {t}")
+        engine.release_slot(sb)
+        got = engine.step([SequenceStep(sa, seqs["a"][11:], range(3))])
+        check_logits(got.cpu().numpy(), want["a"][11:], "float32", "seams tail chunk")
+        engine.release_slot(sa)
+    # the same model generates through the entry point's loop (no fused pick: the head has none)
+    from nnis_b200.engine.api import EngineBackend
+    from nnis_b200.engine.generate import GenerationConfig, GenerationRequest, Generator
+    gen = Generator(EngineBackend(engine, 2), V, 512, 2, 64 * 8)
+    res = gen.generate([GenerationRequest(seqs["a"][:4], GenerationConfig(5))])[0]
+    toks = list(seqs["a"][:4])
+    for _ in range(5):
+        toks.append(P.argmax_lowest(plain(toks)[-1]))
+    assert res.ok and res.token_ids == toks[4:]

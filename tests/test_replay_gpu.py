@@ -217,3 +217,25 @@ def test_recurring_prompt_shapes_are_replayed_from_a_graph(models, dtype, tmp_pa
     run_and_check(models, name, dtype, trace, sequences, tmp_path, "graph replay")
     assert len(engine._step_graphs) > before
     assert any(e["graph"] is not None for e in engine._step_graphs.values())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_prompts_in_portions_give_the_logits_of_one_step(models, dtype):
+    """Long batches of prompts are run as several steps of a bounded number of tokens;
+    the cuts fall inside sequences, pages and tiles and change nothing."""
+    from nnis_b200.engine import SequenceStep
+    name = "B"
+    rng = random.Random(12)
+    vocab = CONFIGS[name]["vocab_size"]
+    engine = engine_for(models, name, dtype)
+    seqs = [random_tokens(rng, n, vocab) for n in (70, 5, 131, 64)]
+    wants = [[69, 0, 33], [4], [0, 64, 130, 65], []]
+    for limit in (48, 64, 1000):
+        slots = [engine.acquire_slot() for _ in seqs]
+        got = engine.step_in_portions([SequenceStep(s, t, w) for s, t, w in zip(slots, seqs, wants)], limit)
+        want = torch.stack([plain_logits(models, name, dtype, t)[w] for t, ws in zip(seqs, wants) for w in ws])
+        check_logits(got.cpu().numpy(), want, dtype, f"portions of {limit}")
+        assert [engine.cache.length(s) for s in slots] == [len(t) for t in seqs]
+        for s in slots:
+            engine.release_slot(s)
+    assert engine.cache.usage()["pages_held"] == [0]

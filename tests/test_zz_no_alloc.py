@@ -47,6 +47,21 @@ def _call_noalloc(lib, q, kc, vc, pos, seq, table, out, nq, nkv, d, window, spli
         ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
 
 
+def _plain(q, kc, vc, table, lengths, nq, nkv, d, window):
+    """The plain implementation's attention (tests/plain_llama.py) for the one query of
+    each sequence: its keys and values gathered from the pages in order."""
+    import plain_llama as P
+    rows = []
+    for s, L in enumerate(lengths):
+        pages = table[s, :-(-L // 64)].tolist()
+        k = torch.cat([kc[p] for p in pages], dim=1)[:, :L].transpose(0, 1).float().cpu()   # [L, nkv, d]
+        v = torch.cat([vc[p] for p in pages], dim=1)[:, :L].transpose(0, 1).float().cpu()
+        qs = torch.zeros(L, nq, d)
+        qs[L - 1] = q[s].float().cpu().view(nq, d)
+        rows.append(P.causal_attention(qs, k, v, window)[L - 1].reshape(nq * d))
+    return torch.stack(rows)
+
+
 def test_no_alloc_entry_point_matches_the_ordinary_one_twice_in_a_row():
     from nnis_b200.csrc import build, ops
     lib = build.load()
@@ -69,6 +84,12 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_twice_in_a_row():
         diff = (got.float() - want.float()).abs().max().item()
         assert torch.isclose(got.float(), want.float(), rtol=1.6e-2, atol=1e-2).all(), \
             f"call {call}: max abs diff {diff}"
+        # ... and both against the plain implementation, which shares no code with them
+        plain = _plain(q, kc, vc, table, lengths, nq, nkv, d, window)
+        for name, t in (("no-alloc", got), ("ordinary", want)):
+            assert torch.isclose(t.float().cpu().double(), plain, rtol=1.6e-2, atol=1e-2).all(), \
+                f"call {call}: {name} entry point against the plain attention: max abs diff " \
+                f"{(t.float().cpu().double() - plain).abs().max().item()}"
 
 
 def test_no_alloc_entry_point_refuses_what_does_not_fit():
@@ -80,3 +101,39 @@ def test_no_alloc_entry_point_refuses_what_does_not_fit():
     assert _call_noalloc(lib, q, kc, vc, pos, seq, table, out, 32, 32, 128, 0, 64) == \
         NNIS_ERR_NOALLOC_TOO_LARGE
     torch.cuda.synchronize()
+    # sizes the kernel does not take are refused before anything is put on the stream
+    assert _call_noalloc(lib, q, kc, vc, pos, seq, table, out, 32, 32, 96, 0, 2) == -2
+    assert _call_noalloc(lib, q, kc, vc, pos, seq, table, out, 32, 32, 128, 0, 65) == -2
+
+
+def test_no_alloc_entry_point_takes_exactly_what_fits():
+    """The largest calls that the fixed array holds run and are right at their last
+    rows, whose records and tickets lie at the array's end; the next larger ones are
+    refused.  Records: a record is head_dim + 2 floats (66 or 130), so no call comes to
+    2^20 floats exactly; 126 tokens x 8 heads x 8 slices x 130 = 1,048,320 is the
+    largest of its shape and 127 tokens do not fit.  Tickets: 512 tokens x 8 kv heads
+    are 4,096 exactly; 513 tokens are refused."""
+    from nnis_b200.csrc import build, ops
+    lib = build.load()
+    for nq, nkv, d, splits, n, fits in ((8, 8, 128, 8, 126, True), (8, 8, 128, 8, 127, False),
+                                        (8, 8, 64, 2, 512, True), (8, 8, 64, 2, 513, False)):
+        lengths = [130 + (i % 5) for i in range(n)]
+        q, kc, vc, pos, seq, table = _case(11, nq, nkv, d, lengths)
+        got = torch.zeros(n, nq * d, dtype=torch.bfloat16, device=DEV)
+        floats, tickets_needed = n * nq * splits * (d + 2), ops.mma_ticket_count(n, nq, nkv)
+        assert (floats <= 1 << 20 and tickets_needed <= 4096) == fits
+        rc = _call_noalloc(lib, q, kc, vc, pos, seq, table, got, nq, nkv, d, 0, splits)
+        torch.cuda.synchronize()
+        if not fits:
+            assert rc == NNIS_ERR_NOALLOC_TOO_LARGE
+            continue
+        assert rc == 0
+        want = torch.empty_like(got)
+        partial = torch.empty(floats, device=DEV)
+        tickets = torch.zeros(tickets_needed, dtype=torch.int32, device=DEV)
+        ops.attention_decode_mma(q, nq * d, kc, vc, pos, seq, table, want, nq, nkv, d, 0,
+                                 1.0 / math.sqrt(d), splits, partial, tickets)
+        assert torch.isclose(got.float(), want.float(), rtol=1.6e-2, atol=1e-2).all()
+        last = [n - 1]
+        plain = _plain(q[last], kc, vc, table[last], [lengths[-1]], nq, nkv, d, 0)
+        assert torch.isclose(got[last].float().cpu().double(), plain, rtol=1.6e-2, atol=1e-2).all()
