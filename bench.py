@@ -122,6 +122,64 @@ def median(values):
     return values[len(values) // 2]
 
 
+def timeline(engine, batch, path, rng, vocab):
+    """One decode step at context 4,096 as the GPU's own timer saw it: per launch of the
+    decode kernels its begin and end, and when its first and last CTA got past the wait
+    for the kernel before, relative to the step's first begin; then sums per kernel."""
+    import torch
+
+    from nnis_b200.csrc import ops
+    from nnis_b200.engine import SequenceStep
+    from nnis_b200.engine.decode import GraphDecoder
+    begin = CONTEXT - 16
+    slots = [engine.acquire_slot() for _ in range(batch)]
+    fed = 0
+    while fed < begin:
+        n = min(PROMPT, begin - fed)
+        per_step = max(1, 16384 // n)
+        for i in range(0, batch, per_step):
+            engine.step([SequenceStep(s, [rng.randrange(vocab) for _ in range(n)], [])
+                         for s in slots[i:i + per_step]])
+        fed += n
+    dec = GraphDecoder(engine, batch, CONTEXT)
+    engine.cache.reserve(slots, [CONTEXT] * batch)
+    for r, s in enumerate(slots):
+        dec.set_row(r, s, rng.randrange(vocab), begin)
+    buf = ops.trace_begin(4096)
+    dec.capture()  # the warm-up run takes slots as well; the captured launches take the later half
+    names = ops.trace_end()
+    for _ in range(4):
+        dec.launch()
+    torch.cuda.synchronize()
+    ops.trace_clear()
+    dec.launch()
+    torch.cuda.synchronize()
+    half = len(names) // 2
+    rows = buf[half:2 * half].cpu().tolist()
+    names = names[half:]
+    t0 = min(r[0] for r in rows)
+    by_name = {}
+    with open(path, "w") as f:
+        f.write(f"# one decode step, batch {batch}, context {CONTEXT}, {len(dec.chains)} chain(s); ns after the "
+                f"step's first CTA\n# launch kernel begin past_wait_first past_wait_last mark1_first "
+                f"mark1_last mark2_first mark2_last end duration\n# marks: projections x staged / "
+                f"products done; attention pages done / ticket taken\n")
+        big = 1 << 62
+        for i, (name, r) in enumerate(zip(names, rows)):
+            rel = [(v - t0 if 0 < v < big else -1) for v in r]
+            b, e, w0, w1 = rel[0], rel[1], rel[2], rel[3]
+            f.write(f"{i} {name.replace(' ', '_')} {b} {w0} {w1} {rel[4]} {rel[5]} {rel[6]} {rel[7]} {e} {e - b}\n")
+            total = by_name.setdefault(name, [0, 0, 0])
+            total[0] += 1
+            total[1] += e - b
+            total[2] += e - (w1 if w1 >= 0 else b)
+        f.write(f"# step: {max(r[1] for r in rows) - t0} ns\n")
+        for name, (count, dur, after) in sorted(by_name.items()):
+            f.write(f"# {name}: {count} launches, mean begin-to-end {dur / count:.0f} ns, "
+                    f"mean last-wait-to-end {after / count:.0f} ns\n")
+    print(open(path).read()[-1500:])
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -132,6 +190,9 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
     ap.add_argument("--skip-e2e", action="store_true", help="leave out the end-to-end run")
     ap.add_argument("--batch", type=int, default=BATCH, help="sequences of the main decode point")
+    ap.add_argument("--timeline", metavar="FILE", default=None,
+                    help="instead of the benchmark: write the timeline of one decode step of the main "
+                         "point (begin, end and wait of every launch of the decode kernels) to FILE")
     ap.add_argument("--shape", default="135m", choices=sorted(SHAPES),
                     help="layer sizes: the SmolLM2-135M shape (the benchmark) or a larger one of the family")
     args = ap.parse_args()
@@ -225,6 +286,10 @@ def main() -> int:
                     "gbs": step_bytes / (ms / steps * 1e-3) / 1e9,
                     "spread": (max(regions) - min(regions)) / ms}
 
+        if args.timeline:
+            timeline(engine, args.batch, args.timeline, rng, vocab)
+            clocks.stop()
+            return 0
         main_point = decode_point(args.batch, K, W)
 
         # -- prefill of 2,048 tokens ------------------------------------------------

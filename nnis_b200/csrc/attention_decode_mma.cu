@@ -33,7 +33,8 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __r
                        const int* __restrict__ token_seq, const int* __restrict__ page_table,
                        int table_cols, bf16* __restrict__ out, float* __restrict__ partial,
                        unsigned* __restrict__ tickets, int nq, int nkv, int window, float scale,
-                       int n_splits, int head_tiles, int stages) {
+                       int n_splits, int head_tiles, int stages, unsigned long long* trace) {
+    trace_mark(trace, 0);
     constexpr int CH = D / 8;    // 16-byte chunks per row
     constexpr int NT = D / 8;    // n-tiles of the output
     constexpr int KS = D / 16;   // k-steps of the score product
@@ -106,6 +107,8 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __r
         for (; issued < stages - 1 && issued != hot; ++issued) load_page(issued);
         pdl_wait();
         pdl_launch_dependents();
+        trace_mark(trace, 2);
+        trace_mark(trace, 3);
         for (; issued < stages - 1; ++issued) load_page(issued);
 
         // the group's query rows, zero beyond the group
@@ -232,6 +235,8 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __r
         pdl_launch_dependents();
     }
     __syncthreads();  // everyone is done with the tiles: reuse them for the merge
+    trace_mark(trace, 4);
+    trace_mark(trace, 5);
 
     // ---- merge the four warps: (m, l) through sm_ml, outputs through the tiles ----
     float* o_s = reinterpret_cast<float*>(smem_raw);  // [warps, 16, D] float32
@@ -284,7 +289,10 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __r
             for (int e = 0; e < 8; ++e) rec[2 + chunk * 8 + e] = acc[e];
         }
     }
-    if (n_splits == 1) return;
+    if (n_splits == 1) {
+        trace_mark(trace, 1);
+        return;
+    }
 
     // ---- the slice that arrives last merges all slices of its group ----------------
     // One thread takes the ticket: its fence, after the barrier, also covers what the
@@ -296,7 +304,12 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __r
         is_last = atomicAdd(ticket, 1u) == (unsigned)n_splits - 1u;
     }
     __syncthreads();
-    if (!is_last) return;
+    trace_mark(trace, 6);
+    trace_mark(trace, 7);
+    if (!is_last) {
+        trace_mark(trace, 1);
+        return;
+    }
     __threadfence();
     // One trip to L2: a thread owns (row, 8 dims, one of four interleaved groups of
     // slices) and asks for the maxima, sums and outputs of its slices all at once;
@@ -385,6 +398,7 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __r
         store4(dst + 4, make_float4(acc[4] * inv, acc[5] * inv, acc[6] * inv, acc[7] * inv));
     }
     if (tid == 0) *ticket = 0u;
+    trace_mark(trace, 1);
 }
 
 template <int D>
@@ -444,7 +458,7 @@ static int launch_mma(dim3 grid, bool pdl, cudaStream_t stream, const bf16* q, i
     cfg.numAttrs = pdl ? 1 : 0;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, q, q_stride, k, v, pos, seq, table, cols, out,
                                        partial, tickets, nq, nkv, window, scale, n_splits, head_tiles,
-                                       stages);
+                                       stages, trace_slot("attention decode"));
     return e == cudaSuccess ? NNIS_OK : (int)e;
 }
 

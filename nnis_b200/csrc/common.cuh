@@ -77,4 +77,22 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
+// The timeline of a step (trace.cu): the next slot of the trace buffer for a launch
+// of the named kernel, or null when no trace is being taken.
+unsigned long long* trace_slot(const char* name);
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// even words: the earliest CTA; odd words: the latest
+__device__ __forceinline__ void trace_mark(unsigned long long* slot, int word) {
+    if (slot && threadIdx.x == 0) {
+        if (word & 1) atomicMax(slot + word, global_ns());
+        else atomicMin(slot + word, global_ns());
+    }
+}
+
 }  // namespace nnis

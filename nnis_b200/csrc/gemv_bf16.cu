@@ -123,7 +123,10 @@ NNIS_API int nnis_gemv_grid(int M, int N, int K, int sm_count) {
 }
 
 // Scratch: the ARGMAX epilogue uses `best_val`, `best_idx` ([M, nnis_gemv_grid()]
-// each) and `ticket` (one zeroed counter, left zero).
+// each) and `ticket` (one zeroed counter, left zero).  `pdl`: bit 0 launches the kernel
+// as a programmatic dependent of the one before it; bit 1 lets the kernel after it
+// start together with this one (only for a successor that reads nothing of this step
+// before its own wait).
 NNIS_API int nnis_gemv_bf16(const void* x, const float* hidden, const int* rows, const float* norm_w,
                             float eps, const void* w, const float* bias, void* out, int M, int N,
                             int K, int epilogue, const int* token_pos, const int* token_seq,
@@ -142,7 +145,8 @@ NNIS_API int nnis_gemv_bf16(const void* x, const float* hidden, const int* rows,
     if (slices == 0) return NNIS_ERR_UNSUPPORTED;
     if (pro == PRO_PLAIN && !x) return NNIS_ERR_ARGUMENT;
     if (pro == PRO_NORM && (!norm_w || !(eps > 0.f))) return NNIS_ERR_ARGUMENT;
-    if (((uintptr_t)w | (uintptr_t)x | (uintptr_t)hidden | (uintptr_t)norm_w | (uintptr_t)out) % 16)
+    if (((uintptr_t)w | (uintptr_t)x | (uintptr_t)hidden | (uintptr_t)norm_w) % 16 ||
+        (uintptr_t)out % (epilogue == EPI_ARGMAX ? 4 : 16))  // the picks are single words
         return NNIS_ERR_ALIGNMENT;
     if (epilogue == EPI_QKV) {
         if (!token_pos || d <= 0 || d % 8 || N != (nq + 2 * nkv) * d) return NNIS_ERR_ARGUMENT;
@@ -160,14 +164,18 @@ NNIS_API int nnis_gemv_bf16(const void* x, const float* hidden, const int* rows,
     a.logits = logits; a.best_val = best_val; a.best_idx = best_idx; a.ticket = ticket;
     a.next_tokens = next_tokens; a.next_pos = next_pos;
     a.ldx = K; a.ldw = K; a.kc = plan.kc; a.out_is_hot = 0;
+    a.release_early = (pdl & 2) && slices == 1 ? 1 : 0;
     a.K = K / slices;
+    static const char* const kNames[] = {"gemv store", "gemv store_f32", "gemv add_f32", "gemv gated",
+                                         "gemv qkv", "gemv argmax"};
     for (int s = 0; s < slices; ++s) {
         int rc;
+        a.trace = trace_slot(epilogue >= 0 && epilogue <= 5 ? kNames[epilogue] : "gemv");
         switch (plan.mtiles) {
-            case 1: rc = gemv_launch_tiles1(a, epilogue, pro, plan, pdl != 0, stream); break;
-            case 2: rc = gemv_launch_tiles2(a, epilogue, pro, plan, pdl != 0, stream); break;
-            case 3: rc = gemv_launch_tiles3(a, epilogue, pro, plan, pdl != 0, stream); break;
-            default: rc = gemv_launch_tiles4(a, epilogue, pro, plan, pdl != 0, stream); break;
+            case 1: rc = gemv_launch_tiles1(a, epilogue, pro, plan, (pdl & 1) != 0, stream); break;
+            case 2: rc = gemv_launch_tiles2(a, epilogue, pro, plan, (pdl & 1) != 0, stream); break;
+            case 3: rc = gemv_launch_tiles3(a, epilogue, pro, plan, (pdl & 1) != 0, stream); break;
+            default: rc = gemv_launch_tiles4(a, epilogue, pro, plan, (pdl & 1) != 0, stream); break;
         }
         if (rc != NNIS_OK) return rc;
         a.x += a.K;

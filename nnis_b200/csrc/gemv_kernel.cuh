@@ -54,6 +54,7 @@ struct GemvArgs {
     int ldx, ldw;           // elements between rows of x and of w (K unless a slice of K is taken)
     int kc;                 // columns of K per weight stage (K: a stage holds whole rows)
     int out_is_hot;         // ADD_F32: the kernel just before this one wrote `out` (a slice of K)
+    int release_early;      // the kernel after this one may start at once (see below)
     int* status;            // set non-zero when a bounded wait runs out
     // QKV epilogue
     const int* token_pos;
@@ -72,6 +73,7 @@ struct GemvArgs {
     unsigned* ticket;       // one counter, zero between launches
     int* next_tokens;       // optional: tokens of the next step (picked) ...
     int* next_pos;          // ... and their positions (+1 on live rows)
+    unsigned long long* trace;  // this launch's slot of the step's timeline, or null
 };
 
 __device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
@@ -110,6 +112,14 @@ gemv_kernel(GemvArgs a) {
     constexpr int MT = MTILES * 16;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    trace_mark(a.trace, 0);
+    // A caller that knows what runs next may let it start with this kernel instead of
+    // after this kernel's wait: it must be a kernel that reads, before its own wait,
+    // nothing that any kernel of the step writes (the decode attention reads positions,
+    // page ids and old cache pages there), and that releases its own dependents only
+    // after its wait, so that kernels further on still find everything before their
+    // immediate predecessor complete.
+    if (a.release_early) pdl_launch_dependents();
     const int K = a.K, M = a.M;
     const int KP = K + 8;  // padded row, in elements
     // A weight stage holds eight rows of KC columns: all of K, or with long rows a
@@ -219,7 +229,9 @@ gemv_kernel(GemvArgs a) {
     // starts early may then rely on everything before its immediate predecessor
     // (the decode attention kernel reads old cache pages before its wait).
     pdl_wait();
-    pdl_launch_dependents();
+    if (!a.release_early) pdl_launch_dependents();
+    trace_mark(a.trace, 2);
+    trace_mark(a.trace, 3);
 
     // ---- x into shared memory ------------------------------------------------
     if (PRO == PRO_NORM) {
@@ -286,6 +298,8 @@ gemv_kernel(GemvArgs a) {
         }
     }
     __syncthreads();
+    trace_mark(a.trace, 4);
+    trace_mark(a.trace, 5);
 
     // ---- units of eight output rows --------------------------------------------
     const int half = a.d >> 1;
@@ -355,6 +369,10 @@ gemv_kernel(GemvArgs a) {
             }
         }
         if (failed && !SPLITK) break;
+        if (i == 0) {
+            trace_mark(a.trace, 6);
+            trace_mark(a.trace, 7);
+        }
         if (MTILES == 1) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[0][e] += acc2[e];
@@ -470,6 +488,7 @@ gemv_kernel(GemvArgs a) {
         }
     }
     if (failed && lane == 0 && a.status) atomicExch(a.status, 2);
+    if (EPI != EPI_ARGMAX) trace_mark(a.trace, 1);
 
     if (EPI == EPI_ARGMAX) {
         // the four lanes of a row hold its candidates: fold them, then the warps,
@@ -542,6 +561,7 @@ gemv_kernel(GemvArgs a) {
             }
             if (threadIdx.x == 0) *a.ticket = 0u;
         }
+        trace_mark(a.trace, 1);
     }
 }
 

@@ -233,6 +233,9 @@ def sample_temperature(logits: torch.Tensor, temperature: torch.Tensor, rng_stat
 EPI_STORE, EPI_STORE_F32, EPI_ADD_F32, EPI_GATED, EPI_QKV, EPI_ARGMAX = 0, 1, 2, 3, 4, 5
 # programmatic dependent launch between the decode kernels (NNIS_PDL=0 turns it off)
 PDL = 0 if os.environ.get("NNIS_PDL", "1") == "0" else 1
+# NNIS_EARLY_RELEASE=1: the QKV projection of a decode step lets the attention kernel start with it
+# instead of after its own wait (measured: no gain with the kernels as they are)
+EARLY_RELEASE = 1 if os.environ.get("NNIS_EARLY_RELEASE", "0") == "1" else 0
 _status = {}
 
 
@@ -300,13 +303,16 @@ def gemv_bf16(w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, 
               v_cache: Optional[torch.Tensor] = None, heads: int = 0, kv_heads: int = 0,
               head_dim: int = 0, page_size: int = 0, logits: Optional[torch.Tensor] = None,
               scratch: Optional[torch.Tensor] = None, next_tokens: Optional[torch.Tensor] = None,
-              next_pos: Optional[torch.Tensor] = None) -> None:
+              next_pos: Optional[torch.Tensor] = None, release_early: bool = False) -> None:
     """A decode-step projection with its prologue and epilogue fused (at most 64
     rows).  The input is ``x`` (bfloat16 [m, k]) or ``hidden`` (float32 residual
     rows, normed with ``norm_weight``/``eps`` on the way in; ``rows`` picks them).
     EPI_ARGMAX writes
     int32 picks to ``out``; ``scratch`` (int32, ``argmax_scratch_ints``) is its
-    workspace, ``logits`` optional, ``next_tokens``/``next_pos`` the decode state."""
+    workspace, ``logits`` optional, ``next_tokens``/``next_pos`` the decode state.
+    ``release_early``: the kernel launched after this one may start together with it
+    (only for a successor that reads, before its own wait, nothing that a kernel of
+    the step writes: the tensor-core decode attention)."""
     _cuda(w, bias, out, x, hidden, norm_weight, rows, token_pos, token_seq, page_table, cos, sin,
           k_cache, v_cache, logits, scratch, next_tokens, next_pos)
     n, k = w.shape
@@ -366,7 +372,8 @@ def gemv_bf16(w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, 
         _ptr(page_table), cols, _ptr(cos), _ptr(sin), _ptr(k_cache), _ptr(v_cache), heads, kv_heads,
         head_dim, page_size, _ptr(logits), ctypes.c_void_p(best_val), ctypes.c_void_p(best_idx),
         ctypes.c_void_p(ticket), _ptr(next_tokens), _ptr(next_pos), _ptr(status_word(w.device)),
-        sm_count(w.device), PDL, _stream()), "gemv_bf16",
+        sm_count(w.device), PDL | (2 if release_early and PDL and EARLY_RELEASE else 0), _stream()),
+        "gemv_bf16",
         gemv_slices(m, n, k, w.device) if epilogue == EPI_ADD_F32 and hidden is None else 1)
 
 
@@ -678,3 +685,35 @@ def advance(tokens: torch.Tensor, pos: torch.Tensor, picked: torch.Tensor) -> No
     n = tokens.numel()
     _need(pos.numel() == n and picked.numel() >= n, "advance: sizes differ")
     _check(_lib().nnis_advance(_ptr(tokens), _ptr(pos), _ptr(picked), n, _stream()), "advance")
+
+
+# ---------------------------------------------------------------------------
+# The timeline of a step (trace.cu), for measurements.
+_trace_buffer: Optional[torch.Tensor] = None
+
+
+def trace_begin(capacity: int = 2048, device="cuda:0") -> torch.Tensor:
+    """From now on every launch of an instrumented kernel (decode projections, decode
+    attention) takes a slot of the returned buffer, int64 [capacity, 8]: first CTA's
+    begin, last CTA's end, first and last CTA past the wait for the kernel before, and
+    first and last CTA at two marks inside the kernel, in nanoseconds of the GPU's timer.  A graph captured meanwhile keeps its slots."""
+    global _trace_buffer
+    _trace_buffer = torch.zeros((capacity, 8), dtype=torch.int64, device=device)
+    trace_clear()
+    _lib().nnis_trace_set(_ptr(_trace_buffer), capacity)
+    return _trace_buffer
+
+
+def trace_clear() -> None:
+    """Before the replay that is to be read: earliest words to the largest value, latest to zero."""
+    _trace_buffer[:, 0::2] = torch.iinfo(torch.int64).max
+    _trace_buffer[:, 1::2] = 0
+
+
+def trace_end():
+    """Stops handing out slots; returns the names of the launches that took one."""
+    lib = _lib()
+    lib.nnis_trace_name.restype = ctypes.c_char_p
+    names = [lib.nnis_trace_name(i).decode() for i in range(int(lib.nnis_trace_count()))]
+    lib.nnis_trace_set(None, 0)
+    return names

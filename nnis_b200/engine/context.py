@@ -46,6 +46,7 @@ class StepContext:
     host_counts: Sequence[int] = field(default_factory=list)
     host_starts: Sequence[int] = field(default_factory=list)
     fixed_splits: int = 0  # > 0: a captured graph fixed the split count
+    share: int = 1  # steps that run side by side on the device (chains of a decode graph)
     # per sequence of the batch (device int32 [n_seqs]): the packed row of its
     # first token in this step, that token's position, its number of tokens.
     # None in decode steps and in contexts built without them.
@@ -90,6 +91,7 @@ class StepContext:
         12 % of the step).  The cost serves to compare launch shapes of one kernel."""
         by_keys = max(1, -(-self.max_context // _SLICE_KEYS))
         pages = max(1, -(-self.max_context // page_size))
+        resident = max(1, resident // max(1, self.share))  # its share of the device
         best, best_cost = 1, None
         for s in range(1, int(min(by_keys, 64)) + 1):
             waves = -(-ctas * s // max(1, resident))

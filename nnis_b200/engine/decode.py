@@ -1,5 +1,13 @@
 """Decoding as one CUDA graph per step, with the batch's state on the device.
 
+The rows of a step are dealt to a few *chains*: each chain runs the whole model over
+its own rows on a stream of its own, and the graph holds the chains side by side.  A
+decode step of a small model is a chain of some hundred short kernels, each waiting
+for the one before it; what bounds it is the latency of that chain, not the bytes.
+Rows do not depend on one another, so two or four chains of fewer rows each overlap
+their latencies, while the weights that the chains read one shortly after the other
+come from DRAM once and from L2 afterwards.
+
 A ``GraphDecoder`` holds, for a fixed number of rows, the current token and
 position of each row, its slot's page tables and the picked tokens.  One graph
 runs embedding, every block, final norm, head and the pick, then moves each live
@@ -15,6 +23,7 @@ overlap with the second form's stops.
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional, Sequence
 
 import torch
@@ -26,8 +35,21 @@ from .context import StepContext, sm_count
 from .workspace import Workspace
 
 
+def chains_for(rows: int) -> int:
+    """How many chains the rows of a decode step are dealt to (``NNIS_DECODE_CHAINS``
+    sets it; measured on the SmolLM2-135M shape, see the decode step's notes)."""
+    forced = os.environ.get("NNIS_DECODE_CHAINS")
+    if forced:
+        return max(1, min(int(forced), rows))
+    # measured on the SmolLM2-135M shape at context 4,096: two chains of four rows take
+    # 0.84 ms a step against 0.75 ms for one chain of eight (the kernels of one chain keep
+    # the other's off the SMs they hold); at 64 rows two chains gain 3 %
+    return 2 if rows >= 32 else 1
+
+
 class GraphDecoder:
-    def __init__(self, engine, rows: int, max_context: int, want_logits: bool = False):
+    def __init__(self, engine, rows: int, max_context: int, want_logits: bool = False,
+                 chains: Optional[int] = None):
         self.engine = engine
         self.want_logits = want_logits
         self.rows = rows
@@ -62,14 +84,18 @@ class GraphDecoder:
         self.logits = torch.empty((rows, engine.spec.vocab_size), dtype=torch.float32, device=dev) \
             if want_logits else None
         self.picked = torch.zeros(rows, dtype=torch.int32, device=dev)
-        self.workspace = Workspace(dev)
-        warps_wanted = sm_count(dev) * 16
-        n_heads = max(1, rows * self._query_heads())
-        splits = int(min(max(1, warps_wanted // n_heads), max(1, -(-self.max_context // 128)), 64))
-        self.ctx = StepContext(
-            n_tokens=rows, n_seqs=rows, tokens=self.tokens, token_pos=self.pos, token_seq=self.seq,
-            seq_slots=self.slots, page_tables=self.tables, workspace=self.workspace, decode=True,
-            max_context=self.max_context, fixed_splits=splits)
+        # the chains: consecutive runs of rows, each with a context, buffers and a
+        # stream of its own
+        n_chains = max(1, min(chains if chains is not None else chains_for(rows), rows))
+        per = -(-rows // n_chains)
+        self.chains = []
+        for a in range(0, rows, per):
+            b = min(rows, a + per)
+            self.chains.append((a, b, self._context(a, b), torch.cuda.Stream(device=dev) if a else None))
+        for _, _, ctx, _ in self.chains:
+            ctx.share = len(self.chains)
+        self.ctx = self.chains[0][2]          # what a step with one chain runs
+        self.workspace = self.ctx.workspace
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.launches_per_step = 0
         # host side of the rows
@@ -77,14 +103,46 @@ class GraphDecoder:
         self._host_tables_unknown = False  # True: every entry of host_tables is None
         self._pinned_out: Optional[torch.Tensor] = None
 
+    def _context(self, a: int, b: int) -> StepContext:
+        """The step context of rows a..b-1 as a batch of their own."""
+        n = b - a
+        warps_wanted = sm_count(self.device) * 16
+        n_heads = max(1, n * self._query_heads())
+        splits = int(min(max(1, warps_wanted // n_heads), max(1, -(-self.max_context // 128)), 64))
+        return StepContext(
+            n_tokens=n, n_seqs=n, tokens=self.tokens[a:b], token_pos=self.pos[a:b],
+            token_seq=self.seq[:n], seq_slots=self.slots[a:b],
+            page_tables=[t[a:b] for t in self.tables], workspace=Workspace(self.device), decode=True,
+            max_context=self.max_context, fixed_splits=splits)
+
     def _query_heads(self) -> int:
         heads = [getattr(part, "heads", 1) for b in self.engine.model.blocks for part in b.parts()]
         return max(heads) if heads else 1
 
     # -- the captured step ----------------------------------------------------
+    def _run_chain(self, a: int, b: int, ctx: StepContext) -> None:
+        self.engine.model.forward_and_pick(
+            ctx, self.want[:b - a], self.picked[a:b], self.logits[a:b] if self.logits is not None else None,
+            self.tokens[a:b], self.pos[a:b])
+
     def _body(self) -> None:
-        self.engine.model.forward_and_pick(self.ctx, self.want, self.picked, self.logits, self.tokens,
-                                           self.pos)
+        """Every chain on its stream: the first on the current one, the others forked
+        from it and joined to it again (inside a capture that makes parallel branches)."""
+        main = torch.cuda.current_stream()
+        fork = torch.cuda.Event()
+        fork.record(main)
+        joins = []
+        for a, b, ctx, stream in self.chains[1:]:
+            stream.wait_event(fork)
+            with torch.cuda.stream(stream):
+                self._run_chain(a, b, ctx)
+                done = torch.cuda.Event()
+                done.record(stream)
+                joins.append(done)
+        a, b, ctx, _ = self.chains[0]
+        self._run_chain(a, b, ctx)
+        for done in joins:
+            main.wait_event(done)
 
     def capture(self) -> None:
         if self.graph is not None:
@@ -96,7 +154,8 @@ class GraphDecoder:
         with torch.cuda.stream(side):
             self._body()
         torch.cuda.current_stream().wait_stream(side)
-        self.workspace.frozen = True
+        for _, _, ctx, _ in self.chains:
+            ctx.workspace.frozen = True
         graph = torch.cuda.CUDAGraph()
         before = ops.launch_count()
         with torch.cuda.graph(graph):

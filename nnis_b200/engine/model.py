@@ -29,7 +29,6 @@ class DecoderModel:
                                       self.device)
         self.head = HEADS.build(spec.head.kind, spec.head.params, "", dtype, self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self._pick_scratch: Dict[int, torch.Tensor] = {}
         for i, entry in enumerate(spec.schedule):
             wants = self.blocks[entry.layer].cache_request()
             if entry.cache_of is not None and wants is not None:
@@ -104,13 +103,9 @@ class DecoderModel:
             self._run_blocks(ctx)
             ws = ctx.workspace
             hidden = ws.get("hidden", (ctx.n_tokens, self.spec.hidden_size), torch.float32)
-            need = self.head.pick_scratch_ints(r)
-            scratch = self._pick_scratch.get(need)
-            if scratch is None:
-                # zeroed once (the kernel leaves its ticket at zero) and kept for
-                # good: a captured graph holds its address
-                scratch = torch.zeros(need, dtype=torch.int32, device=self.device)
-                self._pick_scratch[need] = scratch
+            # zeroed once (the kernel leaves its ticket at zero) and kept with the step's
+            # other buffers: steps that may run side by side have workspaces of their own
+            scratch = ws.zeros("pick_scratch", (self.head.pick_scratch_ints(r),), torch.int32)
             self.head.forward_pick(hidden, self.final_norm, want_rows, picks, scratch, logits,
                                    tokens, pos)
             return

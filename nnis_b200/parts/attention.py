@@ -173,6 +173,9 @@ class Attention(Part):
         tables = self.position.rotary_tables() if self.position_in_kernel else None
         cos, sin = tables if tables is not None else (None, None)
         attn = ws.get("attn", (n, nq * d), self.dtype)
+        # the tensor-core decode attention: a CTA per (kv head, up to 16 query heads, slice)
+        mma_decode = self.dtype == torch.bfloat16 and ctx.decode and n <= 65535 \
+            and ops.attention_decode_mma_takes(d, cache.page_size)
         if self._decode_kernels(ctx, n):
             q = ws.get("q", (n, nq * d), self.dtype)
             ops.gemv_bf16(self.w_qkv, self.b_qkv, q, ops.EPI_QKV, x=x, hidden=hidden,
@@ -182,7 +185,10 @@ class Attention(Part):
                           page_table=table if self.own_kv else None, cos=cos, sin=sin,
                           k_cache=cache.k if self.own_kv else None,
                           v_cache=cache.v if self.own_kv else None, heads=nq,
-                          kv_heads=self.stored_kv, head_dim=d, page_size=cache.page_size)
+                          kv_heads=self.stored_kv, head_dim=d, page_size=cache.page_size,
+                          # that attention kernel reads only positions, page ids and old
+                          # pages before its wait: it may start together with this one
+                          release_early=mma_decode)
             q_buf, q_stride = q, nq * d
         elif self.dtype == torch.bfloat16 and ops.gemm_tc_qkv_takes(d) and self.position_in_kernel \
                 and ops.gemm_tc_takes(n, self.w_qkv.shape[0], self.hidden):
@@ -203,9 +209,7 @@ class Attention(Part):
                            sin, cache.k if self.own_kv else None, cache.v if self.own_kv else None,
                            nq, self.stored_kv, d, cache.page_size)
             q_buf, q_stride = qkv, qkv.shape[1]
-        if self.dtype == torch.bfloat16 and ctx.decode and n <= 65535 \
-                and ops.attention_decode_mma_takes(d, cache.page_size):
-            # tensor-core kernel: a CTA per (kv head, up to 16 query heads, slice)
+        if mma_decode:
             tiles = -(-(nq // nkv) // 16)
             splits, stages = self._decode_shape(ctx, n * nkv * tiles, cache.page_size)
             partial = tickets = None

@@ -44,7 +44,7 @@ def build(dtype, max_rows):
     return engine, plain
 
 
-def decode_rows(engine, ends, rng):
+def decode_rows(engine, ends, rng, chains=None):
     """Fill the cache up to ``end - STEPS`` tokens per row, then STEPS graph launches as
     bench.py makes them.  Returns per row the whole sequence (the picks appended) and
     the logits of each launch."""
@@ -63,7 +63,7 @@ def decode_rows(engine, ends, rng):
                 fed[r] += n
                 budget -= n
         engine.step(batch)
-    dec = GraphDecoder(engine, rows, CONTEXT, want_logits=True)
+    dec = GraphDecoder(engine, rows, CONTEXT, want_logits=True, chains=chains)
     engine.cache.reserve(slots, list(ends))
     for r in range(rows):
         dec.set_row(r, slots[r], seqs[r][-1], len(seqs[r]) - 1)
@@ -95,25 +95,32 @@ def check_rows(seqs, logits, ends, plain, dtype, which, what):
                 assert seqs[r][ends[r] - STEPS + 1 + t] == int(torch.argmax(want[t])), (what, r, t)
 
 
-@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
-def test_eight_rows_decode_to_context_4096_through_the_graph(dtype):
+@pytest.mark.parametrize("dtype,chains", [("bfloat16", None), ("bfloat16", 1), ("float32", None)])
+def test_eight_rows_decode_to_context_4096_through_the_graph(dtype, chains):
+    """``chains``: None is what the benchmark launches (the rows dealt to chains that run
+    side by side), 1 the whole batch as one chain."""
     engine, plain = build(dtype, 8)
     ends = [4096, 4090, 3000, 2049, 300, 64 + STEPS, 70, 4096]
-    seqs, logits, dec = decode_rows(engine, ends, random.Random(8))
-    if dtype == "bfloat16":  # the benchmark's cut of the key range at batch 8
+    seqs, logits, dec = decode_rows(engine, ends, random.Random(8), chains)
+    if dtype == "bfloat16":  # the key range is cut into 16 slices of 256 keys
         mixer = engine.model.blocks[0].mixer
-        assert mixer._decode_shape(dec.ctx, 8 * 3, 64) == (16, 0)
+        rows = dec.chains[0][1] - dec.chains[0][0]
+        assert mixer._decode_shape(dec.ctx, rows * 3, 64) == (16, 0)
     check_rows(seqs, logits, ends, plain, dtype, [0, 3, 5, 7], f"8 rows {dtype}")
     assert engine.cache.usage()["pages_held"] == [0]
 
 
-def test_sixty_four_rows_of_unequal_context_decode_through_the_graph():
+@pytest.mark.parametrize("chains", [None, 1])
+def test_sixty_four_rows_of_unequal_context_decode_through_the_graph(chains):
     engine, plain = build("bfloat16", 64)
     rng = random.Random(64)
     ends = [4096, 2500, 6 + STEPS, 4096] + [rng.randrange(STEPS + 1, 4097) for _ in range(59)] + [4095]
-    seqs, logits, dec = decode_rows(engine, ends, rng)
+    seqs, logits, dec = decode_rows(engine, ends, rng, chains)
     mixer = engine.model.blocks[0].mixer
-    splits, stages = mixer._decode_shape(dec.ctx, 64 * 3, 64)
-    assert 1 < splits <= 4 and stages == 3, (splits, stages)  # the three-page launch shape, few slices
+    rows = dec.chains[0][1] - dec.chains[0][0]
+    splits, stages = mixer._decode_shape(dec.ctx, rows * 3, 64)
+    assert 1 < splits <= 4, (splits, stages)  # few long slices
+    if chains == 1:
+        assert stages == 3  # the launch shape with three pages in flight, one wave of 576 CTAs
     check_rows(seqs, logits, ends, plain, "bfloat16", [0, 1, 2, 63], "64 rows")
     assert engine.cache.usage()["pages_held"] == [0]
