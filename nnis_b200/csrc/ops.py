@@ -233,9 +233,9 @@ def sample_temperature(logits: torch.Tensor, temperature: torch.Tensor, rng_stat
 EPI_STORE, EPI_STORE_F32, EPI_ADD_F32, EPI_GATED, EPI_QKV, EPI_ARGMAX = 0, 1, 2, 3, 4, 5
 # programmatic dependent launch between the decode kernels (NNIS_PDL=0 turns it off)
 PDL = 0 if os.environ.get("NNIS_PDL", "1") == "0" else 1
-# NNIS_EARLY_RELEASE=1: the QKV projection of a decode step lets the attention kernel start with it
-# instead of after its own wait (measured: no gain with the kernels as they are)
-EARLY_RELEASE = 1 if os.environ.get("NNIS_EARLY_RELEASE", "0") == "1" else 0
+# The QKV projection of a decode step lets attention_decode_tma start with it instead of after
+# its own wait, so that the copies of old pages run under it (NNIS_EARLY_RELEASE=0: off)
+EARLY_RELEASE = 0 if os.environ.get("NNIS_EARLY_RELEASE", "1") == "0" else 1
 _status = {}
 
 
@@ -312,7 +312,7 @@ def gemv_bf16(w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, 
     workspace, ``logits`` optional, ``next_tokens``/``next_pos`` the decode state.
     ``release_early``: the kernel launched after this one may start together with it
     (only for a successor that reads, before its own wait, nothing that a kernel of
-    the step writes: the tensor-core decode attention)."""
+    the step writes: attention_decode_tma)."""
     _cuda(w, bias, out, x, hidden, norm_weight, rows, token_pos, token_seq, page_table, cos, sin,
           k_cache, v_cache, logits, scratch, next_tokens, next_pos)
     n, k = w.shape
@@ -416,6 +416,72 @@ def attention_decode(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_ca
 def attention_decode_takes(head_dim: int) -> bool:
     """Head sizes of the CUDA-core decode kernel (whole 32-byte pieces of a row per lane)."""
     return head_dim % 16 == 0 and 16 <= head_dim <= 256
+
+
+TMA_ATTENTION = 0 if os.environ.get("NNIS_TMA_ATTENTION", "1") == "0" else 1
+_tma_ctas_per_sm: dict = {}
+
+
+def attention_decode_tma_max_pages(head_dim: int) -> int:
+    """Pages of one slice that attention_decode_tma holds (all at once, in shared memory)."""
+    return int(_lib().nnis_attention_decode_tma_max_pages(int(head_dim)))
+
+
+def attention_decode_tma_plan(n: int, heads: int, kv_heads: int, head_dim: int, page_size: int,
+                              table_cols: int, device, share: int = 1) -> int:
+    """Into how many slices attention_decode_tma cuts ``table_cols`` pages for a step of ``n``
+    sequences, or 0 when the step is not for that kernel: it takes head sizes 64 and 128,
+    slices of four pages (more for page tables beyond 64 x 4 columns, up to what fits), and
+    only steps whose CTAs are all resident together (few sequences, or short contexts);
+    other steps stream their slices through the ring of attention_decode_mma.  ``share``:
+    steps that run side by side on the device."""
+    if not TMA_ATTENTION or head_dim not in (64, 128) or page_size != 64 or n > 65535:
+        return 0
+    splits = min(64, -(-table_cols // 4))
+    per = -(-table_cols // splits)
+    if per > attention_decode_tma_max_pages(head_dim):
+        return 0
+    key = (head_dim, per, torch.device(device).index or 0)
+    if key not in _tma_ctas_per_sm:
+        _tma_ctas_per_sm[key] = int(_lib().nnis_attention_decode_tma_ctas_per_sm(head_dim, per))
+    ctas = n * kv_heads * (-(-(heads // kv_heads) // 16)) * splits
+    resident = _tma_ctas_per_sm[key] * sm_count(device) // max(1, share)
+    return splits if 0 < ctas <= resident else 0
+
+
+def attention_decode_tma(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                         token_pos: torch.Tensor, token_seq: torch.Tensor, page_table: torch.Tensor,
+                         out: torch.Tensor, heads: int, kv_heads: int, head_dim: int, window: int,
+                         scale: float, n_splits: int, partial: Optional[torch.Tensor] = None,
+                         tickets: Optional[torch.Tensor] = None) -> None:
+    """Decode attention with every page of a slice in shared memory at once (``n_splits``
+    from ``attention_decode_tma_plan``): pages by TMA, a warp per page.  Scratch as for
+    ``attention_decode_mma``."""
+    _cuda(k_cache, v_cache, token_pos, token_seq, page_table, out, partial, tickets)
+    _need(q.is_cuda and q.dtype == torch.bfloat16 == k_cache.dtype == out.dtype,
+          "attention_decode_tma: bfloat16 tensors")
+    n = out.shape[0]
+    pages, nkv, page_size, d = k_cache.shape
+    _need(nkv == kv_heads and d == head_dim, "cache shape differs from the heads given")
+    _need(head_dim in (64, 128) and page_size == 64, "attention_decode_tma: head size 64 or 128, pages of 64")
+    _need(heads % kv_heads == 0, "attention: heads is not a multiple of kv_heads")
+    _need(pages * nkv * page_size < 2 ** 31, "attention: the cache has too many rows")
+    _need(out.shape[1] == heads * head_dim and n <= 65535, "attention: out [n <= 65535, heads * d]")
+    most = attention_decode_tma_max_pages(head_dim)
+    _need(1 <= n_splits <= 64 and -(-page_table.shape[1] // n_splits) <= most,
+          f"attention_decode_tma: at most 64 slices of at most {most} pages")
+    if n_splits > 1:
+        _need(partial is not None and partial.dtype == torch.float32
+              and partial.numel() >= n * heads * n_splits * (head_dim + 2),
+              "attention: partial scratch too small")
+        _need(tickets is not None and tickets.dtype == torch.int32
+              and tickets.numel() >= mma_ticket_count(n, heads, kv_heads), "attention: tickets")
+    _check(_lib().nnis_attention_decode_tma(
+        _ptr(q), q_stride, _ptr(k_cache), _ptr(v_cache), ctypes.c_longlong(pages * nkv * page_size),
+        _ptr(token_pos), _ptr(token_seq), _ptr(page_table), page_table.shape[1], _ptr(out),
+        _ptr(partial), _ptr(tickets), n, heads, kv_heads, head_dim, page_size, window,
+        ctypes.c_float(scale), n_splits, _ptr(status_word(out.device)), PDL, _stream()),
+        "attention_decode_tma")
 
 
 def attention_decode_mma_takes(head_dim: int, page_size: int) -> bool:

@@ -176,6 +176,9 @@ class Attention(Part):
         # the tensor-core decode attention: a CTA per (kv head, up to 16 query heads, slice)
         mma_decode = self.dtype == torch.bfloat16 and ctx.decode and n <= 65535 \
             and ops.attention_decode_mma_takes(d, cache.page_size)
+        # ... or, with few sequences, short slices whose pages are all in shared memory at once
+        tma_splits = ops.attention_decode_tma_plan(
+            n, nq, nkv, d, cache.page_size, table.shape[1], self.device, ctx.share) if mma_decode else 0
         if self._decode_kernels(ctx, n):
             q = ws.get("q", (n, nq * d), self.dtype)
             ops.gemv_bf16(self.w_qkv, self.b_qkv, q, ops.EPI_QKV, x=x, hidden=hidden,
@@ -188,7 +191,7 @@ class Attention(Part):
                           kv_heads=self.stored_kv, head_dim=d, page_size=cache.page_size,
                           # that attention kernel reads only positions, page ids and old
                           # pages before its wait: it may start together with this one
-                          release_early=mma_decode)
+                          release_early=tma_splits > 0)
             q_buf, q_stride = q, nq * d
         elif self.dtype == torch.bfloat16 and ops.gemm_tc_qkv_takes(d) and self.position_in_kernel \
                 and ops.gemm_tc_takes(n, self.w_qkv.shape[0], self.hidden):
@@ -209,7 +212,15 @@ class Attention(Part):
                            sin, cache.k if self.own_kv else None, cache.v if self.own_kv else None,
                            nq, self.stored_kv, d, cache.page_size)
             q_buf, q_stride = qkv, qkv.shape[1]
-        if mma_decode:
+        if tma_splits:
+            partial = tickets = None
+            if tma_splits > 1:
+                partial = ws.get("attn_partial", (n * nq * tma_splits * (d + 2),), torch.float32)
+                tickets = ws.zeros("attn_tickets", (ops.mma_ticket_count(n, nq, nkv),), torch.int32)
+            ops.attention_decode_tma(q_buf, q_stride, cache.k, cache.v, ctx.token_pos, ctx.token_seq,
+                                     table, attn, nq, nkv, d, self.window, self.scale, tma_splits,
+                                     partial, tickets)
+        elif mma_decode:
             tiles = -(-(nq // nkv) // 16)
             splits, stages = self._decode_shape(ctx, n * nkv * tiles, cache.page_size)
             partial = tickets = None

@@ -583,6 +583,100 @@ def test_attention_decode_on_tensor_cores(nq, nkv, d, window):
     assert not o.attention_decode_mma_takes(48, 64) and not o.attention_decode_mma_takes(64, 32)
 
 
+@pytest.mark.parametrize("nq,nkv,d", [(9, 3, 64), (4, 4, 64), (32, 1, 64), (20, 1, 128), (6, 2, 128)])
+@pytest.mark.parametrize("window", [0, 100])
+def test_attention_decode_fed_by_tma(nq, nkv, d, window):
+    """Every page of a slice in shared memory at once (pages by TMA, a warp per page): head
+    sizes 64 and 128, groups below, at and above 16 heads, contexts from one key to many
+    pages, a padding row, one slice to sixteen, stale values in pages beyond each length."""
+    o = ops()
+    lengths = [1, 64, 65, 300, 1000, 7, 129]
+    case = PagedCase(lengths, [1] * len(lengths), nq, nkv, d, "bfloat16", seed=nq + d)
+    case.fill_cache()
+    for s, L in enumerate(lengths):
+        pg = int(case.table[s, (L - 1) // 64])
+        case.k_cache[pg, :, (L - 1) % 64] = case.k[s][L - 1]
+        case.v_cache[pg, :, (L - 1) % 64] = case.v[s][L - 1]
+    pos, seq, q, _, _ = case.packed()
+    pos = torch.cat([pos, torch.tensor([-1], dtype=torch.int32)])
+    seq = torch.cat([seq, torch.tensor([0], dtype=torch.int32)])
+    n = pos.numel()
+    qd = torch.cat([q.reshape(n - 1, -1), torch.ones(1, nq * d)]).bfloat16().to(DEV)
+    kc, vc = case.k_cache.bfloat16().to(DEV), case.v_cache.bfloat16().to(DEV)
+    want = torch.cat([P.causal_attention(case.q[s], case.k[s], case.v[s].bfloat16().float(),
+                                         window)[L - 1:].reshape(1, -1)
+                      for s, L in enumerate(lengths)])
+    cols = case.table.shape[1]
+    assert cols == 16
+    most = o.attention_decode_tma_max_pages(d)
+    assert most == (8 if d == 64 else 6)
+    tickets = torch.zeros(o.mma_ticket_count(n, nq, nkv), dtype=torch.int32, device=DEV)
+    for splits in (2, 3, 4, 7, 16):
+        if -(-cols // splits) > most:
+            continue  # eight pages of head size 128 do not fit a CTA's shared memory
+        out = torch.full((n, nq * d), 5.0, dtype=torch.bfloat16, device=DEV)
+        partial = torch.full((n * nq * splits * (d + 2),), float("nan"), device=DEV)
+        o.attention_decode_tma(qd, nq * d, kc, vc, pos.to(DEV), seq.to(DEV), case.table.to(DEV), out,
+                               nq, nkv, d, window, 1.0 / math.sqrt(d), splits, partial, tickets)
+        close(out[:n - 1], want, "bfloat16", f"decode attention by TMA, {splits} slices")
+        assert float(out[n - 1].float().abs().max()) == 0
+        assert int(tickets.abs().sum()) == 0
+    with pytest.raises(o.KernelError, match="slices of at most"):
+        o.attention_decode_tma(qd, nq * d, kc, vc, pos.to(DEV), seq.to(DEV), case.table.to(DEV), out,
+                               nq, nkv, d, window, 1.0 / math.sqrt(d), 1)  # 16 pages in one slice
+    # one slice: a context of up to four pages needs no scratch
+    short = PagedCase([200, 3], [1, 1], nq, nkv, d, "bfloat16", seed=5)
+    short.fill_cache()
+    for s, L in enumerate(short.lengths):
+        pg = int(short.table[s, (L - 1) // 64])
+        short.k_cache[pg, :, (L - 1) % 64] = short.k[s][L - 1]
+        short.v_cache[pg, :, (L - 1) % 64] = short.v[s][L - 1]
+    spos, sseq, sq, _, _ = short.packed()
+    out = torch.empty(2, nq * d, dtype=torch.bfloat16, device=DEV)
+    o.attention_decode_tma(sq.reshape(2, -1).bfloat16().to(DEV), nq * d, short.k_cache.bfloat16().to(DEV),
+                           short.v_cache.bfloat16().to(DEV), spos.to(DEV), sseq.to(DEV), short.table.to(DEV),
+                           out, nq, nkv, d, window, 1.0 / math.sqrt(d), 1)
+    want = torch.cat([P.causal_attention(short.q[s], short.k[s], short.v[s].bfloat16().float(),
+                                         window)[L - 1:].reshape(1, -1) for s, L in enumerate(short.lengths)])
+    close(out, want, "bfloat16", "decode attention by TMA, one slice")
+    o.check_status(DEV)
+    # the plan: few sequences take it, many do not; short contexts need one slice
+    assert o.attention_decode_tma_plan(2, nq, nkv, d, 64, 64, DEV) == 16
+    assert o.attention_decode_tma_plan(1, nq, nkv, d, 64, 1, DEV) == 1
+    assert o.attention_decode_tma_plan(4000, nq, nkv, d, 64, 64, DEV) == 0
+    assert o.attention_decode_tma_plan(2, nq, nkv, d, 64, 1000, DEV) == 0  # slices would be too long
+    assert o.attention_decode_tma_plan(2, nq, nkv, 48, 64, 8, DEV) == 0
+
+
+def test_decode_attention_by_tma_finds_one_far_key():
+    o = ops()
+    nq, nkv, d, L, far = 8, 2, 64, 900, 77
+    case = PagedCase([L], [1], nq, nkv, d, "bfloat16", seed=9, scale=0.3)
+    for h in range(nkv):
+        case.k[0][far, h] = case.q[0][L - 1, h * 4] * 30.0
+    case.k[0] = case.k[0].bfloat16().float()
+    case.v[0][far] = 7.0
+    case.fill_cache()
+    pg = int(case.table[0, (L - 1) // 64])
+    case.k_cache[pg, :, (L - 1) % 64] = case.k[0][L - 1]
+    case.v_cache[pg, :, (L - 1) % 64] = case.v[0][L - 1]
+    pos, seq, q, _, _ = case.packed()
+    qd = q.reshape(1, -1).bfloat16().to(DEV)
+    kc, vc = case.k_cache.bfloat16().to(DEV), case.v_cache.bfloat16().to(DEV)
+    tickets = torch.zeros(o.mma_ticket_count(1, nq, nkv), dtype=torch.int32, device=DEV)
+    for window, sees in ((0, True), (L - far, True), (L - far - 1, False)):
+        for splits in (2, 5, 15):
+            out = torch.empty(1, nq * d, dtype=torch.bfloat16, device=DEV)
+            partial = torch.full((nq * splits * (d + 2),), float("nan"), device=DEV)
+            o.attention_decode_tma(qd, nq * d, kc, vc, pos.to(DEV), seq.to(DEV), case.table.to(DEV),
+                                   out, nq, nkv, d, window, 1.0 / math.sqrt(d), splits, partial, tickets)
+            want = P.causal_attention(case.q[0], case.k[0], case.v[0].bfloat16().float(),
+                                      window)[L - 1:].reshape(1, -1)
+            close(out, want, "bfloat16", f"far key window {window} slices {splits}")
+            lead = out.view(nq, d)[0::4].float()
+            assert bool((lead > 6.5).all()) == sees
+
+
 def test_tensor_core_decode_attention_finds_one_far_key():
     o = ops()
     nq, nkv, d, L, far = 8, 2, 64, 900, 77
