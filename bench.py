@@ -122,6 +122,59 @@ def median(values):
     return values[len(values) // 2]
 
 
+def write_timeline(path, title, names, rows, marks):
+    """The table of one traced step: per launch its begin, first and last CTA past the wait
+    for the kernel before, two inner marks, end and duration, relative to the step's first
+    begin; then sums per kernel."""
+    t0 = min(r[0] for r in rows)
+    by_name = {}
+    big = 1 << 62
+    with open(path, "w") as f:
+        f.write(f"# {title}; ns after the step's first CTA\n# launch kernel begin past_wait_first past_wait_last "
+                f"mark1_first mark1_last mark2_first mark2_last end duration\n# marks: {marks}\n")
+        for i, (name, r) in enumerate(zip(names, rows)):
+            rel = [(v - t0 if 0 < v < big else -1) for v in r]
+            b, e, w1 = rel[0], rel[1], rel[3]
+            f.write(f"{i} {name.replace(' ', '_')} {b} {rel[2]} {w1} {rel[4]} {rel[5]} {rel[6]} {rel[7]} {e} {e - b}\n")
+            total = by_name.setdefault(name, [0, 0, 0])
+            total[0] += 1
+            total[1] += e - b
+            total[2] += e - (w1 if w1 >= 0 else b)
+        f.write(f"# step: {max(r[1] for r in rows) - t0} ns\n")
+        for name, (count, dur, after) in sorted(by_name.items()):
+            f.write(f"# {name}: {count} launches, mean begin-to-end {dur / count:.0f} ns, "
+                    f"mean last-wait-to-end {after / count:.0f} ns, sum of the latter {after / 1000:.0f} us\n")
+    print(open(path).read()[-1800:])
+
+
+def prefill_timeline(engine, path, rng, vocab):
+    """One prompt step of 2,048 tokens as the GPU's own timer saw it (the instrumented
+    kernels: tcgen05 products, prompt attention, the norms of many rows)."""
+    import torch
+
+    from nnis_b200.csrc import ops
+    from nnis_b200.engine import SequenceStep
+    prompt = [rng.randrange(vocab) for _ in range(PROMPT)]
+
+    def once():
+        slot = engine.acquire_slot()
+        engine.step([SequenceStep(slot, prompt, [PROMPT - 1])])
+        engine.release_slot(slot)
+    once()                      # seen once
+    buf = ops.trace_begin(4096)
+    once()                      # run into its own buffers and captured: both take slots
+    names = ops.trace_end()
+    for _ in range(3):
+        once()
+    torch.cuda.synchronize()
+    ops.trace_clear()
+    once()
+    torch.cuda.synchronize()
+    half = len(names) // 2
+    write_timeline(path, f"one prompt step of {PROMPT} tokens", names[half:], buf[half:2 * half].cpu().tolist(),
+                   "none inside these kernels")
+
+
 def timeline(engine, batch, path, rng, vocab):
     """One decode step at context 4,096 as the GPU's own timer saw it: per launch of the
     decode kernels its begin and end, and when its first and last CTA got past the wait
@@ -155,29 +208,9 @@ def timeline(engine, batch, path, rng, vocab):
     dec.launch()
     torch.cuda.synchronize()
     half = len(names) // 2
-    rows = buf[half:2 * half].cpu().tolist()
-    names = names[half:]
-    t0 = min(r[0] for r in rows)
-    by_name = {}
-    with open(path, "w") as f:
-        f.write(f"# one decode step, batch {batch}, context {CONTEXT}, {len(dec.chains)} chain(s); ns after the "
-                f"step's first CTA\n# launch kernel begin past_wait_first past_wait_last mark1_first "
-                f"mark1_last mark2_first mark2_last end duration\n# marks: projections x staged / "
-                f"products done; attention pages done / ticket taken\n")
-        big = 1 << 62
-        for i, (name, r) in enumerate(zip(names, rows)):
-            rel = [(v - t0 if 0 < v < big else -1) for v in r]
-            b, e, w0, w1 = rel[0], rel[1], rel[2], rel[3]
-            f.write(f"{i} {name.replace(' ', '_')} {b} {w0} {w1} {rel[4]} {rel[5]} {rel[6]} {rel[7]} {e} {e - b}\n")
-            total = by_name.setdefault(name, [0, 0, 0])
-            total[0] += 1
-            total[1] += e - b
-            total[2] += e - (w1 if w1 >= 0 else b)
-        f.write(f"# step: {max(r[1] for r in rows) - t0} ns\n")
-        for name, (count, dur, after) in sorted(by_name.items()):
-            f.write(f"# {name}: {count} launches, mean begin-to-end {dur / count:.0f} ns, "
-                    f"mean last-wait-to-end {after / count:.0f} ns\n")
-    print(open(path).read()[-1500:])
+    write_timeline(path, f"one decode step, batch {batch}, context {CONTEXT}, {len(dec.chains)} chain(s)",
+                   names[half:], buf[half:2 * half].cpu().tolist(),
+                   "projections x staged / products done; attention pages done / ticket taken")
 
 
 def main() -> int:
@@ -192,7 +225,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=BATCH, help="sequences of the main decode point")
     ap.add_argument("--timeline", metavar="FILE", default=None,
                     help="instead of the benchmark: write the timeline of one decode step of the main "
-                         "point (begin, end and wait of every launch of the decode kernels) to FILE")
+                         "point (begin, end and wait of every launch of the decode kernels) to FILE; "
+                         "with --batch 0, of the 2,048-token prompt step")
     ap.add_argument("--shape", default="135m", choices=sorted(SHAPES),
                     help="layer sizes: the SmolLM2-135M shape (the benchmark) or a larger one of the family")
     args = ap.parse_args()
@@ -230,7 +264,7 @@ def main() -> int:
 
     with tempfile.TemporaryDirectory() as tmp:
         write_random_model(cfg, seed=0, out_dir=tmp, std=1.0, norm_std=0.1, std_by_fan_in=True)
-        most_rows = max(args.batch, 1 if args.skip_points else 64)  # the cache holds the largest point
+        most_rows = max(args.batch, 1, 1 if args.skip_points or args.timeline else 64)  # the cache holds the largest point
         llm = LLM(tmp, dtype="bfloat16", device_ordinal=0, max_tokens=most_rows * (CONTEXT + 64),
                   max_batch=max(most_rows, 1), pipeline_decode=False)
         engine = llm.engine
@@ -287,7 +321,10 @@ def main() -> int:
                     "spread": (max(regions) - min(regions)) / ms}
 
         if args.timeline:
-            timeline(engine, args.batch, args.timeline, rng, vocab)
+            if args.batch == 0:
+                prefill_timeline(engine, args.timeline, rng, vocab)
+            else:
+                timeline(engine, args.batch, args.timeline, rng, vocab)
             clocks.stop()
             return 0
         main_point = decode_point(args.batch, K, W)

@@ -145,7 +145,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const int* __restrict__ seq_count, const int* __restrict__ page_table,
                        int table_cols, bf16* __restrict__ out, float* __restrict__ partial,
                        unsigned* __restrict__ tickets, int nq, int nkv, int window, float scale,
-                       int* __restrict__ status) {
+                       int* __restrict__ status, unsigned long long* trace) {
+    trace_mark(trace, 0);
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -213,6 +214,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // values, come from the kernel before this one; the set-up above ran under it
     pdl_wait();
     pdl_launch_dependents();
+    trace_mark(trace, 2);
+    trace_mark(trace, 3);
 
     if (warp == 0) {
         if (lane == 0) {
@@ -482,6 +485,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         tmem_dealloc(tmem_base_s, 256);
     }
     if (threadIdx.x == 0 && abort_flag && status) atomicExch(status, 4);
+    trace_mark(trace, 1);
 }
 
 }  // namespace nnis
@@ -532,6 +536,6 @@ NNIS_API int nnis_attention_prefill_tc(const void* q, int q_stride, int n_tokens
     cfg.numAttrs = pdl ? 1 : 0;
     e = cudaLaunchKernelEx(&cfg, attn_prefill_tc_kernel, mq, mk, mv, units, seq_first_row, seq_start,
                            seq_count, page_table, table_cols, (bf16*)out, partial, tickets, nq, nkv,
-                           window, scale, status);
+                           window, scale, status, trace_slot("attention prompt (tcgen05)"));
     return e == cudaSuccess ? NNIS_OK : (int)e;
 }

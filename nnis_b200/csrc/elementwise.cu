@@ -67,11 +67,18 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
 template <typename T>
 __global__ void __launch_bounds__(256)
 rmsnorm_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows,
-                    const float* __restrict__ w, T* __restrict__ y, int n_rows, int width, float eps) {
+                    const float* __restrict__ w, T* __restrict__ y, int n_rows, int width, float eps,
+                    unsigned long long* trace) {
+    trace_mark(trace, 0);
     pdl_wait();
     pdl_launch_dependents();
+    trace_mark(trace, 2);
+    trace_mark(trace, 3);
     const int lane = threadIdx.x & 31, r = blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (r >= n_rows) return;
+    if (r >= n_rows) {
+        trace_mark(trace, 1);
+        return;
+    }
     const float4* in = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * width);
     const float4* w4 = reinterpret_cast<const float4*>(w);
     const int n4 = width >> 2;
@@ -98,6 +105,7 @@ rmsnorm_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows,
                                             (v[j].w * s) * g.w));
         }
     }
+    trace_mark(trace, 1);
 }
 
 // ---------------------------------------------------------------------------
@@ -222,10 +230,10 @@ NNIS_API int nnis_rmsnorm(const float* x, const int* rows, const float* w, void*
     cfg.numAttrs = pdl ? 1 : 0;
     cudaError_t e;
     if (out_dtype == NNIS_DTYPE_F32)
-        e = by_rows ? cudaLaunchKernelEx(&cfg, rmsnorm_rows_kernel<float>, x, rows, w, (float*)y, n_rows, width, eps)
+        e = by_rows ? cudaLaunchKernelEx(&cfg, rmsnorm_rows_kernel<float>, x, rows, w, (float*)y, n_rows, width, eps, trace_slot("rmsnorm rows"))
                     : cudaLaunchKernelEx(&cfg, rmsnorm_kernel<float>, x, rows, w, (float*)y, width, eps);
     else if (out_dtype == NNIS_DTYPE_BF16)
-        e = by_rows ? cudaLaunchKernelEx(&cfg, rmsnorm_rows_kernel<bf16>, x, rows, w, (bf16*)y, n_rows, width, eps)
+        e = by_rows ? cudaLaunchKernelEx(&cfg, rmsnorm_rows_kernel<bf16>, x, rows, w, (bf16*)y, n_rows, width, eps, trace_slot("rmsnorm rows"))
                     : cudaLaunchKernelEx(&cfg, rmsnorm_kernel<bf16>, x, rows, w, (bf16*)y, width, eps);
     else
         return NNIS_ERR_UNSUPPORTED;

@@ -49,6 +49,7 @@ struct GemmArgs {
     bf16* k_cache;
     bf16* v_cache;
     int nq, nkv, d, page_size;
+    unsigned long long* trace;  // this launch's slot of the step's timeline, or null
 };
 
 // Two CTAs share an SM when their stages leave room for it.
@@ -71,6 +72,7 @@ template <int BN, int STAGES, int MODE, int KSUB>
 __global__ void __launch_bounds__(gemm_threads(BN, STAGES, MODE, KSUB), gemm_ctas_per_sm(BN, STAGES, MODE, KSUB))
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                const __grid_constant__ CUtensorMap map_out, GemmArgs g) {
+    trace_mark(g.trace, 0);
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // the swizzle pattern follows address bits: tiles start on 1024-byte boundaries
     unsigned char* base = reinterpret_cast<unsigned char*>(
@@ -116,38 +118,47 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     tc_fence_after();
     const uint32_t tmem_acc = tmem_base_s;
 
-    // A depends on the kernel before this one; W does not, but both come through
-    // the same ring, so wait first
-    pdl_wait();
-    pdl_launch_dependents();
-
     // Issuing a TMA load costs its thread about 130 cycles, so A and W each have a
     // loader of their own: lane 0 of warp 0 and lane 0 of warp 2 (which joins the
     // epilogue afterwards).  Each announces its own bytes; a stage is full when both
     // have arrived and all bytes are there.
+    auto load_stage = [&](bool loads_a, int kb) {
+        const int s = kb % STAGES;
+        // (slices beyond K arrive as zeros and are not multiplied)
+        mbar_expect_tx(&full_bar[s], loads_a ? kStageA : kStageB);
+#pragma unroll
+        for (int h = 0; h < KSUB; ++h) {
+            const int k0 = (kb * KSUB + h) * kBK;
+            if (loads_a) {
+                tma_load_2d(tile_a + (size_t)s * kStageA + (size_t)h * kBytesA, &map_a, k0, m0,
+                            &full_bar[s]);
+            } else {
+                unsigned char* b_dst = tile_b + (size_t)s * kStageB + (size_t)h * NB * kBytesB;
+                tma_load_2d(b_dst, &map_w, k0, n0, &full_bar[s]);
+                if (NB == 2) tma_load_2d(b_dst + kBytesB, &map_w, k0, inter + n0, &full_bar[s]);
+            }
+        }
+    };
+    // A depends on the kernel before this one; W does not: the first stages of W are
+    // asked for before the wait, under that kernel's tail
+    int w_ahead = 0;
+    if (warp == 2 && lane == 0)
+        for (; w_ahead < k_blocks && w_ahead < STAGES; ++w_ahead) load_stage(false, w_ahead);
+    pdl_wait();
+    pdl_launch_dependents();
+    trace_mark(g.trace, 2);
+    trace_mark(g.trace, 3);
+
     if (lane == 0 && (warp == 0 || warp == 2)) {
         const bool loads_a = warp == 0;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = loads_a ? 0 : w_ahead; kb < k_blocks; ++kb) {
             int s = kb % STAGES;
             if (kb >= STAGES && !mbar_wait(&empty_bar[s], (uint32_t)(kb / STAGES - 1) & 1u)) {
                 abort_flag = 1;
                 break;
             }
             if (abort_flag) break;
-            // (slices beyond K arrive as zeros and are not multiplied)
-            mbar_expect_tx(&full_bar[s], loads_a ? kStageA : kStageB);
-#pragma unroll
-            for (int h = 0; h < KSUB; ++h) {
-                const int k0 = (kb * KSUB + h) * kBK;
-                if (loads_a) {
-                    tma_load_2d(tile_a + (size_t)s * kStageA + (size_t)h * kBytesA, &map_a, k0, m0,
-                                &full_bar[s]);
-                } else {
-                    unsigned char* b_dst = tile_b + (size_t)s * kStageB + (size_t)h * NB * kBytesB;
-                    tma_load_2d(b_dst, &map_w, k0, n0, &full_bar[s]);
-                    if (NB == 2) tma_load_2d(b_dst + kBytesB, &map_w, k0, inter + n0, &full_bar[s]);
-                }
-            }
+            load_stage(loads_a, kb);
         }
     }
     __syncwarp();
@@ -396,6 +407,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         tmem_dealloc(tmem_acc, kTmemCols);
     }
     if (threadIdx.x == 0 && abort_flag && g.status) atomicExch(g.status, 3);
+    trace_mark(g.trace, 1);
 }
 
 template <int BN, int STAGES, int MODE, int KSUB>
@@ -445,6 +457,8 @@ NNIS_API int nnis_gemm_tc(const void* A, const void* W, const float* bias, void*
     g.token_pos = token_pos; g.token_seq = token_seq; g.page_table = page_table;
     g.table_cols = table_cols; g.cos_t = cos_t; g.sin_t = sin_t; g.k_cache = (bf16*)k_cache;
     g.v_cache = (bf16*)v_cache; g.nq = nq; g.nkv = nkv; g.d = d; g.page_size = page_size;
+    static const char* const kNames[] = {"gemm store", "gemm store_f32", "gemm add_f32", "gemm gated", "gemm qkv"};
+    g.trace = trace_slot(mode >= 0 && mode <= 4 ? kNames[mode] : "gemm");
     int sms = sm_count > 0 ? sm_count : 148;
     CUtensorMap ma, mw, mo;
     const long m_tiles = (M + kBM - 1) / kBM;
