@@ -41,10 +41,13 @@ def chains_for(rows: int) -> int:
     forced = os.environ.get("NNIS_DECODE_CHAINS")
     if forced:
         return max(1, min(int(forced), rows))
-    # measured on the SmolLM2-135M shape at context 4,096: two chains of four rows take
+    # Measured at context 4,096: on the SmolLM2-135M shape two chains of four rows take
     # 0.84 ms a step against 0.75 ms for one chain of eight (the kernels of one chain keep
-    # the other's off the SMs they hold); at 64 rows two chains gain 3 %
-    return 2 if rows >= 32 else 1
+    # the other's off the SMs they hold), and two chains of 32 rows gain 3 % over one of 64;
+    # on the 360M and 1.7B shapes two chains of 32 lose a quarter (rows beyond 48 take the
+    # tcgen05 products, two chains of 32 the decode projections with long rows of K).  One
+    # chain is the rule; the switch is for measurements.
+    return 1
 
 
 class GraphDecoder:

@@ -95,32 +95,35 @@ def check_rows(seqs, logits, ends, plain, dtype, which, what):
                 assert seqs[r][ends[r] - STEPS + 1 + t] == int(torch.argmax(want[t])), (what, r, t)
 
 
-@pytest.mark.parametrize("dtype,chains", [("bfloat16", None), ("bfloat16", 1), ("float32", None)])
+@pytest.mark.parametrize("dtype,chains", [("bfloat16", None), ("bfloat16", 2), ("float32", None)])
 def test_eight_rows_decode_to_context_4096_through_the_graph(dtype, chains):
-    """``chains``: None is what the benchmark launches (the rows dealt to chains that run
-    side by side), 1 the whole batch as one chain."""
+    """``chains``: None is what the benchmark launches (one chain of all rows); 2 deals
+    the rows to two chains that run side by side in the graph."""
     engine, plain = build(dtype, 8)
     ends = [4096, 4090, 3000, 2049, 300, 64 + STEPS, 70, 4096]
     seqs, logits, dec = decode_rows(engine, ends, random.Random(8), chains)
-    if dtype == "bfloat16":  # the key range is cut into 16 slices of 256 keys
-        mixer = engine.model.blocks[0].mixer
+    if dtype == "bfloat16":  # 16 slices of 256 keys, every page of a slice in shared memory at once
+        from nnis_b200.csrc import ops
         rows = dec.chains[0][1] - dec.chains[0][0]
-        assert mixer._decode_shape(dec.ctx, rows * 3, 64) == (16, 0)
+        assert ops.attention_decode_tma_plan(rows, 9, 3, 64, 64, dec.cols, engine.device, len(dec.chains)) == 16
     check_rows(seqs, logits, ends, plain, dtype, [0, 3, 5, 7], f"8 rows {dtype}")
     assert engine.cache.usage()["pages_held"] == [0]
 
 
-@pytest.mark.parametrize("chains", [None, 1])
+@pytest.mark.parametrize("chains", [None, 4])
 def test_sixty_four_rows_of_unequal_context_decode_through_the_graph(chains):
     engine, plain = build("bfloat16", 64)
     rng = random.Random(64)
     ends = [4096, 2500, 6 + STEPS, 4096] + [rng.randrange(STEPS + 1, 4097) for _ in range(59)] + [4095]
     seqs, logits, dec = decode_rows(engine, ends, rng, chains)
+    from nnis_b200.csrc import ops
     mixer = engine.model.blocks[0].mixer
     rows = dec.chains[0][1] - dec.chains[0][0]
+    # too many CTAs to be resident together: the slices stream through the ring
+    assert ops.attention_decode_tma_plan(rows, 9, 3, 64, 64, dec.cols, engine.device, len(dec.chains)) == 0
     splits, stages = mixer._decode_shape(dec.ctx, rows * 3, 64)
     assert 1 < splits <= 4, (splits, stages)  # few long slices
-    if chains == 1:
+    if len(dec.chains) == 1:
         assert stages == 3  # the launch shape with three pages in flight, one wave of 576 CTAs
     check_rows(seqs, logits, ends, plain, "bfloat16", [0, 1, 2, 63], "64 rows")
     assert engine.cache.usage()["pages_held"] == [0]
