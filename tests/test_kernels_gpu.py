@@ -396,8 +396,14 @@ def test_gemv_long_rows_in_chunks_and_slices(m, n, k):
     hidden = torch.randn(m + 3, k, generator=g) * 2
     hidden[:, k - 3] = 9.0
     nw = 1 + 0.1 * torch.randn(k, generator=g)
-    hidden = away_from_bf16_ties(hidden, nw, 1e-5)
     rows = torch.randperm(m + 3, generator=g)[:m].to(torch.int32)
+    # the inputs as drawn, rounding ties and all, held to the bound of a bfloat16 value: a
+    # normed value that rounds the other way moves its products by one bfloat16 step
+    o.gemv_bf16(w.to(DEV), None, out32, o.EPI_STORE_F32, hidden=hidden.to(DEV),
+                norm_weight=nw.to(DEV), eps=1e-5, rows=rows.to(DEV))
+    close(out32, P.linear(P.rms_norm(hidden[rows.long()], nw, 1e-5).bfloat16(), w), "bfloat16",
+          "gemv norm prologue, long rows, inputs as drawn")
+    hidden = away_from_bf16_ties(hidden, nw, 1e-5)
     normed = P.rms_norm(hidden[rows.long()], nw, 1e-5).bfloat16()
     o.gemv_bf16(w.to(DEV), None, out32, o.EPI_STORE_F32, hidden=hidden.to(DEV),
                 norm_weight=nw.to(DEV), eps=1e-5, rows=rows.to(DEV))
@@ -519,6 +525,14 @@ def test_gemv_argmax_epilogue_picks_moves_on_and_can_write_logits(m, n, k):
     hidden = torch.randn(m, k, generator=g)
     hidden[0] = w[3].float() * 4  # row 0 is led by index 3 (and its twin)
     nw = torch.ones(k)
+    # the inputs as drawn, held to the bound of a bfloat16 value (see away_from_bf16_ties)
+    raw_logits = torch.zeros(m, n, device=DEV)
+    o.gemv_bf16(w.to(DEV), None, torch.empty(m, dtype=torch.int32, device=DEV), o.EPI_ARGMAX,
+                hidden=hidden.to(DEV), norm_weight=nw.to(DEV), eps=1e-5,
+                rows=torch.arange(m, dtype=torch.int32, device=DEV), m=m, logits=raw_logits,
+                scratch=torch.zeros(o.argmax_scratch_ints(m, n, k, DEV), dtype=torch.int32, device=DEV))
+    close(raw_logits, P.linear(P.rms_norm(hidden, nw, 1e-5).bfloat16(), w), "bfloat16",
+          "argmax logits, inputs as drawn")
     hidden = away_from_bf16_ties(hidden, nw, 1e-5)
     want_logits = P.linear(P.rms_norm(hidden, nw, 1e-5).bfloat16(), w)
     want = [P.argmax_lowest(r) for r in want_logits]

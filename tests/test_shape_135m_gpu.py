@@ -1,14 +1,16 @@
-"""The SmolLM2-135M shape with random weights: the engine's float32 and bfloat16
-logits against the plain float64 implementation, a prompt in one step and its
-last tokens one by one.  The shape comes from a config.json like any other; only
-this file knows its numbers."""
+"""The SmolLM2-135M shape with all its 30 layers and random weights: the engine's
+float32 and bfloat16 logits against the plain float64 implementation, through the three
+cuts of work (whole, last tokens one by one, unequal batches one after another with
+slots and pages used again, prompts that cross a page), and its greedy tokens.  The
+shape comes from a config.json like any other; only this file knows its numbers."""
 import random
 
 import pytest
 import torch
 
 import plain_llama as P
-from helpers import TraceBuilder, check_logits, load_plain_weights, make_model, read_config_json, read_step
+from helpers import (load_plain_weights, make_model, read_config_json, read_step, replay_against_plain,
+                     three_cuts)
 
 pytestmark = pytest.mark.gpu
 
@@ -27,24 +29,19 @@ def model_dir(tmp_path_factory):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_135m_shape_matches_the_plain_implementation(model_dir, dtype, tmp_path):
     from nnis_b200.engine import Engine
-    from nnis_b200.engine.replay import replay
-    rng = random.Random(7)
-    tokens = [rng.randrange(49152) for _ in range(40)]
-    bf = dtype == "bfloat16"
-    want = P.forward(read_config_json(model_dir), load_plain_weights(model_dir, as_bf16=bf), tokens,
-                     emulate_bf16=bf)
-    engine = Engine.from_dir(model_dir, dtype=dtype, max_tokens=256)
-    trace = TraceBuilder()
-    trace.step([("r", tokens[:32], range(32))])
-    for t in range(32, 40):
-        trace.step([("r", tokens[t:t + 1], [0])], end=["r"] if t == 39 else [])
+    engine = Engine.from_dir(model_dir, dtype=dtype, max_tokens=64 * 16)
+    trace, sequences = three_cuts(
+        random.Random(7), 49152, whole=(40,), last32=(70,),
+        batches=([(5, 9), (66, 69), (17, 18)], [(1, 4), (64, 66), (2, 3), (31, 33)]))
     out = str(tmp_path / "out")
-    replay(engine, trace.lines, out)
-    check_logits(read_step(out, 0, 49152), want[:32], dtype, f"135M {dtype} prompt")
-    for t in range(32, 40):
-        check_logits(read_step(out, t - 31, 49152), want[t:t + 1], dtype, f"135M {dtype} token {t}")
-    # greedy tokens agree wherever the plain logits have a clear winner
-    got_last = torch.from_numpy(read_step(out, 8, 49152))[0]
-    top2 = torch.topk(want[39], 2).values
-    if float(top2[0] - top2[1]) > 0.05 * float(want[39].abs().max()):
-        assert int(got_last.argmax()) == int(want[39].argmax())
+    replay_against_plain(engine, model_dir, dtype, trace, sequences, out, "135M")
+    # greedy tokens: at every position of the whole request where the plain logits have
+    # a clear winner the engine picks it (and such positions exist)
+    bf = dtype == "bfloat16"
+    want = P.forward(read_config_json(model_dir), load_plain_weights(model_dir, as_bf16=bf),
+                     sequences["w0"], emulate_bf16=bf)
+    got = torch.from_numpy(read_step(out, 0, 49152))
+    top2 = torch.topk(want, 2, dim=-1).values
+    clear = (top2[:, 0] - top2[:, 1]) > 0.05 * want.abs().amax(dim=-1)
+    assert int(clear.sum()) >= 5, "the prompt has too few positions with a clear winner"
+    assert torch.equal(got.argmax(dim=-1)[clear], want.argmax(dim=-1)[clear])
