@@ -147,6 +147,17 @@ gemv_kernel(GemvArgs a) {
     const int k_begin = SPLITK ? min(steps, warp * steps_per_warp) * 16 : 0;
     const int k_end = SPLITK ? min(steps, (warp + 1) * steps_per_warp) * 16 : K;
     const uint32_t row_bytes = (uint32_t)(k_end - k_begin) * 2u;
+    // With the warps sharing K, one tile of rows and x as it is (no norm), a warp needs
+    // only its own columns of x and takes them from global memory straight into the
+    // registers of its products: no trip of x through shared memory, no barrier for it.
+    // (The same with the norm in front, the warps exchanging their shares of each row's
+    // sum of squares, was measured slower: its registers keep the next kernel's CTAs
+    // from becoming resident early.)
+    constexpr bool kDirect = SPLITK && PRO == PRO_PLAIN && MTILES == 1;
+    // 16-column steps of one warp: K <= 1,536 with eight warps
+    constexpr int kDirectSteps = kDirect ? 12 : 1;
+    const bool direct = kDirect && steps_per_warp <= kDirectSteps;
+    uint32_t ax[kDirectSteps][4];
 
     // stage j holds chunk j % n_chunks of this warp's unit number j / n_chunks
     auto issue = [&](int j) {  // lane 0 only
@@ -233,7 +244,7 @@ gemv_kernel(GemvArgs a) {
     trace_mark(a.trace, 2);
     trace_mark(a.trace, 3);
 
-    // ---- x into shared memory ------------------------------------------------
+    // ---- x into shared memory (or, see above, straight into registers) ---------
     if (PRO == PRO_NORM) {
         const bool in_regs = k4 <= 32 * NW;
         for (int m = warp; m < MT; m += WARPS) {
@@ -288,6 +299,20 @@ gemv_kernel(GemvArgs a) {
                 for (int k = lane; k < K; k += 32) xs[(size_t)m * KP + k] = __float2bfloat16_rn(0.f);
             }
         }
+    } else if (direct) {
+        // this warp's columns of x, each lane the values of its place in the 16 x 16
+        // operand tiles of the products: rows lane / 4 and + 8, columns 2 (lane % 4) and + 8
+        const int g = lane >> 2, t2 = (lane & 3) * 2;
+        const bf16* x0 = a.x + (size_t)g * a.ldx + k_begin + t2;
+        const bf16* x1 = x0 + (size_t)8 * a.ldx;
+#pragma unroll
+        for (int s = 0; s < kDirectSteps; ++s) {
+            const bool in_k = k_begin + s * 16 < k_end;
+            ax[s][0] = in_k && g < M ? *reinterpret_cast<const uint32_t*>(x0 + s * 16) : 0u;
+            ax[s][1] = in_k && g + 8 < M ? *reinterpret_cast<const uint32_t*>(x1 + s * 16) : 0u;
+            ax[s][2] = in_k && g < M ? *reinterpret_cast<const uint32_t*>(x0 + s * 16 + 8) : 0u;
+            ax[s][3] = in_k && g + 8 < M ? *reinterpret_cast<const uint32_t*>(x1 + s * 16 + 8) : 0u;
+        }
     } else {
         const int per_row = K >> 3;  // 16-byte chunks
         for (int c = threadIdx.x; c < MT * per_row; c += WARPS * 32) {
@@ -297,7 +322,7 @@ gemv_kernel(GemvArgs a) {
             *reinterpret_cast<uint4*>(xs + (size_t)m * KP + ch * 8) = v;
         }
     }
-    __syncthreads();
+    if (!direct) __syncthreads();
     trace_mark(a.trace, 4);
     trace_mark(a.trace, 5);
 
@@ -353,6 +378,20 @@ gemv_kernel(GemvArgs a) {
                     else mma_bf16(acc[t], af[buf][t], bw[buf][0], bw[buf][1]);
                 }
             };
+            if (direct) {
+                // x is in registers already: the weights' fragments of all steps first, then
+                // the products, on two chains
+                uint32_t bd[kDirectSteps][2];
+#pragma unroll
+                for (int s = 0; s < kDirectSteps; ++s)
+                    if (kb + s * 16 < ke) ldmatrix_x2(bd[s][0], bd[s][1], b_ptr + kb + s * 16);
+#pragma unroll
+                for (int s = 0; s < kDirectSteps; ++s)
+                    if (kb + s * 16 < ke) {
+                        if (s & 1) mma_bf16(acc2, ax[s], bd[s][0], bd[s][1]);
+                        else mma_bf16(acc[0], ax[s], bd[s][0], bd[s][1]);
+                    }
+            } else {
             int k0 = kb;
             if (k0 < ke) load_step(0, k0);
 #pragma unroll 2
@@ -363,6 +402,7 @@ gemv_kernel(GemvArgs a) {
                 mma_step(1);
             }
             if (k0 < ke) mma_step(0);
+            }
             if (!SPLITK) {
                 __syncwarp();  // every lane has read this stage: it may be filled again
                 if (lane == 0) issue(j + S);
