@@ -71,6 +71,13 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
+// The sum over each half of a warp (lanes 0-15, 16-31); every lane calls it.
+__device__ __forceinline__ float half_warp_sum(float v) {
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));

@@ -11,6 +11,9 @@ int gemv_launch_tiles1(const GemvArgs&, int, int, const GemvPlan&, bool, cudaStr
 int gemv_launch_tiles2(const GemvArgs&, int, int, const GemvPlan&, bool, cudaStream_t);
 int gemv_launch_tiles3(const GemvArgs&, int, int, const GemvPlan&, bool, cudaStream_t);
 int gemv_launch_tiles4(const GemvArgs&, int, int, const GemvPlan&, bool, cudaStream_t);
+// gemv_rowtile.cu: the kernel for more rows than one tile and few output features
+int gemv_rowtile_units(int M, int N, int K, int epilogue, int pro, int sm_count);
+int gemv_launch_rowtile(const GemvArgs&, int, int, int, bool, cudaStream_t);
 
 // Shared memory of one CTA: x, the weight stages (eight rows of `kc` columns each),
 // the barriers, and with split K the warps' partial sums.
@@ -115,6 +118,17 @@ NNIS_API int nnis_gemv_slices(int M, int N, int K, int sm_count) {
     return nnis::gemv_slices(M, N, K, sm_count, &p);
 }
 
+// Which kernel nnis_gemv_bf16 runs for a product: 2 the one that cuts the rows into
+// tiles (gemv_rowtile.cu: more than 16 rows, few output features), 1 the one whose
+// CTAs hold all rows (at most 64), 0 neither.  `normed`: with the norm prologue.
+NNIS_API int nnis_gemv_kind(int M, int N, int K, int epilogue, int normed, int sm_count) {
+    using namespace nnis;
+    if (gemv_rowtile_units(M, N, K, epilogue, normed ? PRO_NORM : PRO_PLAIN, sm_count) > 0) return 2;
+    GemvPlan p;
+    if (epilogue == EPI_ADD_F32 && !normed) return gemv_slices(M, N, K, sm_count, &p) >= 1 ? 1 : 0;
+    return gemv_plan(M, N, K, sm_count, &p) ? 1 : 0;
+}
+
 // How many CTAs a launch with these sizes has: the ARGMAX scratch is
 // [M, this many] values and indices.
 NNIS_API int nnis_gemv_grid(int M, int N, int K, int sm_count) {
@@ -138,10 +152,14 @@ NNIS_API int nnis_gemv_bf16(const void* x, const float* hidden, const int* rows,
     using namespace nnis;
     if (M <= 0 || N <= 0 || K <= 0 || !w || !out) return NNIS_ERR_ARGUMENT;
     GemvPlan plan;
+    plan.kc = K;
     int pro = hidden ? PRO_NORM : PRO_PLAIN;
+    // more rows than a tile and few output features: the kernel that cuts the rows
+    const int rowtile_units = gemv_rowtile_units(M, N, K, epilogue, pro, sm_count);
     const bool may_slice = epilogue == EPI_ADD_F32 && pro == PRO_PLAIN;
-    const int slices = may_slice ? gemv_slices(M, N, K, sm_count, &plan)
-                                 : (gemv_plan(M, N, K, sm_count, &plan) ? 1 : 0);
+    const int slices = rowtile_units > 0 ? 1
+                       : may_slice      ? gemv_slices(M, N, K, sm_count, &plan)
+                                        : (gemv_plan(M, N, K, sm_count, &plan) ? 1 : 0);
     if (slices == 0) return NNIS_ERR_UNSUPPORTED;
     if (pro == PRO_PLAIN && !x) return NNIS_ERR_ARGUMENT;
     if (pro == PRO_NORM && (!norm_w || !(eps > 0.f))) return NNIS_ERR_ARGUMENT;
@@ -168,8 +186,14 @@ NNIS_API int nnis_gemv_bf16(const void* x, const float* hidden, const int* rows,
     a.K = K / slices;
     static const char* const kNames[] = {"gemv store", "gemv store_f32", "gemv add_f32", "gemv gated",
                                          "gemv qkv", "gemv argmax"};
+    static const char* const kRowNames[] = {"gemv rows store", "gemv rows store_f32", "gemv rows add_f32",
+                                            "gemv rows gated", "gemv rows qkv"};
     for (int s = 0; s < slices; ++s) {
         int rc;
+        if (rowtile_units > 0) {
+            a.trace = trace_slot(epilogue >= 0 && epilogue <= 4 ? kRowNames[epilogue] : "gemv rows");
+            return gemv_launch_rowtile(a, epilogue, pro, rowtile_units, (pdl & 1) != 0, stream);
+        }
         a.trace = trace_slot(epilogue >= 0 && epilogue <= 5 ? kNames[epilogue] : "gemv");
         switch (plan.mtiles) {
             case 1: rc = gemv_launch_tiles1(a, epilogue, pro, plan, (pdl & 1) != 0, stream); break;

@@ -101,6 +101,178 @@ __device__ __forceinline__ int unit_row(const GemvArgs& a, int unit, int c) {
     return unit * 8 + c;
 }
 
+// What the epilogue of one tile of 16 rows needs from global memory and that no product
+// decides: fetched before the wait of programmatic dependent launch (the residual stream
+// was last written two kernels back, positions and page tables before the step began).
+// A lane holds rows r_lo = lane / 4 and r_lo + 8 of the tile, columns c_lo = 2 (lane % 4)
+// and c_lo + 1 of the unit.
+struct EpiTile {
+    float2 old[2];                  // ADD_F32: the destination's values (first unit only)
+    int pos[2], page[2];            // QKV: the rows' positions and cache pages
+    float cs[4], sn[4];             // QKV: the rotation at those positions (first unit only)
+
+};
+
+// QKV: where a head's values go.  Row m of a query head lies at base + m * row_step (the
+// packed q rows); a row of a key or value head at base + place * row_step + page * page_step
+// (its place in the head's part of its cache page).
+template <int EPI>
+__device__ __forceinline__ void qkv_head(const GemvArgs& a, int head, bf16*& base, size_t& row_step,
+                                         size_t& page_step) {
+    if (head < a.nq) {
+        base = reinterpret_cast<bf16*>(a.out) + (size_t)head * a.d;
+        row_step = (size_t)a.nq * a.d;
+        page_step = 0;
+    } else {
+        const bool is_v = head >= a.nq + a.nkv;
+        const int hk = is_v ? head - a.nq - a.nkv : head - a.nq;
+        base = (is_v ? a.v_cache : a.k_cache) + (size_t)hk * a.page_size * a.d;
+        row_step = (size_t)a.d;
+        page_step = (size_t)a.nkv * a.page_size * a.d;
+    }
+}
+
+// `every_unit`: the warp goes on to other units with what it fetched for the rows (else
+// the cache page of a row is looked up only if this unit is of a key or value head).
+template <int EPI>
+__device__ __forceinline__ void epi_preload(const GemvArgs& a, int unit, int row0, int lane, bool every_unit,
+                                            EpiTile& p) {
+    const int r_lo = lane >> 2, c_lo = (lane & 3) * 2;
+    if (EPI == EPI_ADD_F32 && !a.out_is_hot) {
+        const int n0 = unit * 8 + c_lo;
+#pragma unroll
+        for (int hrow = 0; hrow < 2; ++hrow) {
+            int m = row0 + r_lo + hrow * 8;
+            p.old[hrow] = m < a.M ? *reinterpret_cast<const float2*>(
+                                        reinterpret_cast<const float*>(a.out) + (size_t)m * a.N + n0)
+                                  : make_float2(0.f, 0.f);
+        }
+    }
+    if (EPI == EPI_QKV) {
+        const int na = unit_row<EPI>(a, unit, c_lo & 3);
+        const int head = na / a.d, j = na - head * a.d, hf = a.d >> 1;
+        const bool rotate = a.sin_t && head < a.nq + a.nkv;
+        const bool paged = a.nkv > 0 && (every_unit || head >= a.nq);
+#pragma unroll
+        for (int hrow = 0; hrow < 2; ++hrow) {
+            int m = row0 + r_lo + hrow * 8;
+            int pos = m < a.M ? a.token_pos[m] : -1;
+            p.pos[hrow] = pos;
+            // (the row's page holds for every unit)
+            p.page[hrow] = pos >= 0 && paged
+                               ? a.page_table[(size_t)a.token_seq[m] * a.table_cols + pos / a.page_size] : 0;
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                p.cs[hrow * 2 + e] = (rotate && pos >= 0) ? a.cos_t[(size_t)pos * hf + j + e] : 1.f;
+                p.sn[hrow * 2 + e] = (rotate && pos >= 0) ? a.sin_t[(size_t)pos * hf + j + e] : 0.f;
+            }
+        }
+    }
+}
+
+// The epilogue of one tile of 16 rows of one unit: `v` are this lane's four sums
+// (rows r_lo, r_lo + 8 x columns c_lo, c_lo + 1).  `first`: p.old, p.cs and p.sn were
+// fetched for this unit.  Every lane of the warp must call it (the halves of a pair
+// change hands by shuffle).  ARGMAX keeps the best of the lane's columns per row.
+template <int EPI>
+__device__ __forceinline__ void epi_finish(const GemvArgs& a, int unit, int row0, int lane,
+                                           const float (&v)[4], const EpiTile& p, bool first,
+                                           float (&best_v)[2], int (&best_i)[2]) {
+    const int r_lo = lane >> 2, c_lo = (lane & 3) * 2;
+    const int M = a.M;
+    if (EPI == EPI_GATED || EPI == EPI_QKV) {
+        // columns 0-3 pair with 4-7: the lanes of the second half hand theirs over
+        const bool low = (lane & 3) < 2;
+        const int n_a = unit_row<EPI>(a, unit, c_lo & 3);  // even: this lane finishes n_a, n_a + 1
+        const int n_b = unit_row<EPI>(a, unit, (c_lo & 3) + 4);
+        float pv[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) pv[e] = __shfl_xor_sync(0xffffffffu, v[e], 2);
+        if (!low) return;
+        float bias_a[2] = {0.f, 0.f}, bias_b[2] = {0.f, 0.f};
+        if (a.bias) {
+            bias_a[0] = a.bias[n_a]; bias_a[1] = a.bias[n_a + 1];
+            bias_b[0] = a.bias[n_b]; bias_b[1] = a.bias[n_b + 1];
+        }
+        // QKV: what the unit decides (a unit lies inside one head)
+        const int half = a.d >> 1, inter = a.N >> 1;
+        int head = 0, j = 0;
+        bf16* base = nullptr;
+        size_t row_step = 0, page_step = 0;
+        if (EPI == EPI_QKV) {
+            head = n_a / a.d;
+            j = n_a - head * a.d;
+            qkv_head<EPI>(a, head, base, row_step, page_step);
+        }
+        const bool rotate = EPI == EPI_QKV && a.sin_t && head < a.nq + a.nkv;
+#pragma unroll
+        for (int hrow = 0; hrow < 2; ++hrow) {
+            int m = row0 + r_lo + hrow * 8;
+            if (m >= M) continue;
+            float va[2], vb[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                va[e] = v[hrow * 2 + e] + bias_a[e];
+                vb[e] = pv[hrow * 2 + e] + bias_b[e];
+            }
+            if (EPI == EPI_GATED) {
+                *reinterpret_cast<uint32_t*>(reinterpret_cast<bf16*>(a.out) + (size_t)m * inter + n_a) =
+                    pack_bf16((va[0] / (1.0f + expf(-va[0]))) * vb[0],
+                              (va[1] / (1.0f + expf(-va[1]))) * vb[1]);
+            } else {
+                int pos = p.pos[hrow];
+                if (pos < 0) continue;
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    va[e] = round_bf16(va[e]);
+                    vb[e] = round_bf16(vb[e]);
+                    if (rotate) {
+                        float c = first ? p.cs[hrow * 2 + e] : a.cos_t[(size_t)pos * half + j + e];
+                        float sn = first ? p.sn[hrow * 2 + e] : a.sin_t[(size_t)pos * half + j + e];
+                        float ra = va[e] * c - vb[e] * sn, rb = vb[e] * c + va[e] * sn;
+                        va[e] = ra;
+                        vb[e] = rb;
+                    }
+                }
+                bf16* o = head < a.nq ? base + (size_t)m * row_step
+                                      : base + (size_t)(pos % a.page_size) * row_step +
+                                            (size_t)p.page[hrow] * page_step;
+                *reinterpret_cast<uint32_t*>(o + j) = pack_bf16(va[0], va[1]);
+                *reinterpret_cast<uint32_t*>(o + j + half) = pack_bf16(vb[0], vb[1]);
+            }
+        }
+    } else {
+        const int n0 = unit * 8 + c_lo;
+        const float b0v = a.bias ? a.bias[n0] : 0.f, b1v = a.bias ? a.bias[n0 + 1] : 0.f;
+#pragma unroll
+        for (int hrow = 0; hrow < 2; ++hrow) {
+            int m = row0 + r_lo + hrow * 8;
+            if (m >= M) continue;
+            float v0 = v[hrow * 2] + b0v, v1 = v[hrow * 2 + 1] + b1v;
+            size_t o = (size_t)m * a.N + n0;
+            if (EPI == EPI_STORE) {
+                *reinterpret_cast<uint32_t*>(reinterpret_cast<bf16*>(a.out) + o) = pack_bf16(v0, v1);
+            } else if (EPI == EPI_STORE_F32) {
+                *reinterpret_cast<float2*>(reinterpret_cast<float*>(a.out) + o) = make_float2(v0, v1);
+            } else if (EPI == EPI_ADD_F32) {
+                float2* q = reinterpret_cast<float2*>(reinterpret_cast<float*>(a.out) + o);
+                float2 old = (first && !a.out_is_hot) ? p.old[hrow] : *q;
+                *q = make_float2(old.x + v0, old.y + v1);
+            } else {
+                if (a.logits) *reinterpret_cast<float2*>(a.logits + o) = make_float2(v0, v1);
+                if (better(v0, n0, best_v[hrow], best_i[hrow])) {
+                    best_v[hrow] = v0;
+                    best_i[hrow] = n0;
+                }
+                if (better(v1, n0 + 1, best_v[hrow], best_i[hrow])) {
+                    best_v[hrow] = v1;
+                    best_i[hrow] = n0 + 1;
+                }
+            }
+        }
+    }
+}
+
 // MTILES tiles of 16 rows of x; WARPS warps per CTA; S stages of weights per warp.
 // SPLITK: the CTA owns one unit and its warps share K (each a run of 16-column
 // steps), which shortens the chain of dependent products when there are fewer
@@ -136,6 +308,7 @@ gemv_kernel(GemvArgs a) {
     __shared__ float cta_val[WARPS][MT];
     __shared__ int cta_idx[WARPS][MT];
     __shared__ bool is_last;
+    __shared__ __align__(8) uint64_t xbar;  // the bulk copies of x complete here
 
     const int n_units = a.N >> 3;
     const int unit_stride = SPLITK ? gridDim.x : gridDim.x * WARPS;
@@ -180,6 +353,7 @@ gemv_kernel(GemvArgs a) {
     if (lane == 0) {
 #pragma unroll
         for (int s = 0; s < S; ++s) mbar_init(bars + s, 1);
+        if (warp == 0) mbar_init(&xbar, 1);
         mbar_fence_init();
 #pragma unroll
         for (int s = 0; s < S; ++s) issue(s);
@@ -196,54 +370,31 @@ gemv_kernel(GemvArgs a) {
         }
     }
     // What the epilogue of this warp's first unit needs from global memory does not
-    // come from the kernel just before this one either (the residual stream was last
-    // written two kernels back, positions and page tables before the step began), so
-    // it is fetched now, under that kernel's tail, instead of after the products.
-    const int r_lo = lane >> 2, c_lo = (lane & 3) * 2;  // rows r_lo, r_lo + 8; columns c_lo, c_lo + 1
-    const bool epi_warp = !SPLITK || warp == 0;
-    float2 old0[MTILES][2];          // ADD_F32: the destination's values
-    int pos0[MTILES][2], page0[MTILES][2];  // QKV: position and cache page of the row
-    float cos0[MTILES][4], sin0[MTILES][4];
-    if (EPI == EPI_ADD_F32 && epi_warp && first_unit < n_units && !a.out_is_hot) {
-        const int n0 = first_unit * 8 + c_lo;
+    // come from the kernel just before this one either, so it is fetched now, under that
+    // kernel's tail, instead of after the products.
+    const int r_lo = lane >> 2;
+    // A warp finishes all tiles of rows of its own units; with the warps sharing K,
+    // warp t finishes tile t of the CTA's unit (the sums and the epilogue of the tiles
+    // then run side by side instead of in one warp).
+    constexpr int ET = SPLITK ? 1 : MTILES;
+    const bool epi_warp = !SPLITK || warp < MTILES;
+    auto tile_of = [&](int tt) { return SPLITK ? warp : tt; };
+    EpiTile pre[ET];
+    if (epi_warp && first_unit < n_units) {
 #pragma unroll
-        for (int t = 0; t < MTILES; ++t)
-#pragma unroll
-            for (int hrow = 0; hrow < 2; ++hrow) {
-                int m = t * 16 + r_lo + hrow * 8;
-                old0[t][hrow] = m < M ? *reinterpret_cast<const float2*>(
-                                            reinterpret_cast<const float*>(a.out) + (size_t)m * a.N + n0)
-                                      : make_float2(0.f, 0.f);
-            }
-    }
-    if (EPI == EPI_QKV && epi_warp && first_unit < n_units) {
-        const int na = unit_row<EPI>(a, first_unit, c_lo & 3);
-        const int head = na / a.d, j = na - head * a.d, hf = a.d >> 1;
-        const bool rotate = a.sin_t && head < a.nq + a.nkv;
-#pragma unroll
-        for (int t = 0; t < MTILES; ++t)
-#pragma unroll
-            for (int hrow = 0; hrow < 2; ++hrow) {
-                int m = t * 16 + r_lo + hrow * 8;
-                int pos = m < M ? a.token_pos[m] : -1;
-                pos0[t][hrow] = pos;
-                page0[t][hrow] = (pos >= 0 && head >= a.nq)
-                                     ? a.page_table[(size_t)a.token_seq[m] * a.table_cols + pos / a.page_size] : 0;
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    cos0[t][hrow * 2 + e] = (rotate && pos >= 0) ? a.cos_t[(size_t)pos * hf + j + e] : 1.f;
-                    sin0[t][hrow * 2 + e] = (rotate && pos >= 0) ? a.sin_t[(size_t)pos * hf + j + e] : 0.f;
-                }
-            }
+        for (int tt = 0; tt < ET; ++tt) epi_preload<EPI>(a, first_unit, tile_of(tt) * 16, lane, !SPLITK, pre[tt]);
     }
     // Dependents are released only after this kernel's own wait: a kernel that
     // starts early may then rely on everything before its immediate predecessor
     // (the decode attention kernel reads old cache pages before its wait).
+    if (PRO == PRO_PLAIN) __syncthreads();  // every warp sees the barrier of x initialised
     pdl_wait();
     if (!a.release_early) pdl_launch_dependents();
+
     trace_mark(a.trace, 2);
     trace_mark(a.trace, 3);
 
+    bool failed = false;
     // ---- x into shared memory (or, see above, straight into registers) ---------
     if (PRO == PRO_NORM) {
         const bool in_regs = k4 <= 32 * NW;
@@ -314,29 +465,37 @@ gemv_kernel(GemvArgs a) {
             ax[s][3] = in_k && g + 8 < M ? *reinterpret_cast<const uint32_t*>(x1 + s * 16 + 8) : 0u;
         }
     } else {
-        const int per_row = K >> 3;  // 16-byte chunks
-        for (int c = threadIdx.x; c < MT * per_row; c += WARPS * 32) {
-            int m = c / per_row, ch = c - m * per_row;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (m < M) v = *reinterpret_cast<const uint4*>(a.x + (size_t)m * a.ldx + ch * 8);
-            *reinterpret_cast<uint4*>(xs + (size_t)m * KP + ch * 8) = v;
+        // whole rows by bulk copies, all of them in flight at once (loads through
+        // registers keep too few bytes in flight to fill the SM's path from L2 when
+        // there are many rows); rows past M are zeroed here
+        if (warp == 0) {
+            if (lane == 0) mbar_expect_tx(&xbar, (uint32_t)M * (uint32_t)K * 2u);
+            __syncwarp();
+            for (int m = lane; m < M; m += 32)
+                bulk_load(xs + (size_t)m * KP, a.x + (size_t)m * a.ldx, (uint32_t)K * 2u, &xbar);
         }
+        const int per_row = K >> 3;  // 16-byte chunks
+        for (int c = threadIdx.x; c < (MT - M) * per_row; c += WARPS * 32) {
+            int m = M + c / per_row, ch = c % per_row;
+            *reinterpret_cast<uint4*>(xs + (size_t)m * KP + ch * 8) = make_uint4(0, 0, 0, 0);
+        }
+        const bool arrived = mbar_wait(&xbar, 0);
+        // the zeroed rows; and the whole CTA knows if a wait ran out (it goes on, flagged,
+        // through its bounded waits: no CTA leaves with copies into its memory in flight)
+        failed = __syncthreads_or(!arrived) != 0;
     }
-    if (!direct) __syncthreads();
+    if (PRO == PRO_NORM) __syncthreads();
     trace_mark(a.trace, 4);
     trace_mark(a.trace, 5);
 
     // ---- units of eight output rows --------------------------------------------
-    const int half = a.d >> 1;
-    const int inter = a.N >> 1;
-    float best_v[MTILES][2];
-    int best_i[MTILES][2];
+    float best_v[ET][2];
+    int best_i[ET][2];
 #pragma unroll
-    for (int t = 0; t < MTILES; ++t) {
-        best_v[t][0] = best_v[t][1] = -FLT_MAX;
-        best_i[t][0] = best_i[t][1] = -1;
+    for (int tt = 0; tt < ET; ++tt) {
+        best_v[tt][0] = best_v[tt][1] = -FLT_MAX;
+        best_i[tt][0] = best_i[tt][1] = -1;
     }
-    bool failed = false;
     for (int i = 0;; ++i) {
         int unit = first_unit + i * unit_stride;
         if (unit >= n_units) break;
@@ -417,115 +576,32 @@ gemv_kernel(GemvArgs a) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[0][e] += acc2[e];
         }
+        float eacc[ET][4];  // the sums that this warp finishes
         if (SPLITK) {
-            // partial sums of the warps, added by warp 0 in warp order
+            // partial sums of the warps, added in warp order; warp t takes tile t
 #pragma unroll
             for (int t = 0; t < MTILES; ++t)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) red[((size_t)warp * MTILES * 4 + t * 4 + e) * 32 + lane] = acc[t][e];
+                for (int e = 0; e < 4; ++e) red[((size_t)(warp * MTILES + t) * 4 + e) * 32 + lane] = acc[t][e];
             __syncthreads();
-            if (warp != 0) break;  // one unit per CTA: the other warps are done
+            if (warp >= MTILES) break;  // one unit per CTA: the other warps are done
 #pragma unroll
-            for (int t = 0; t < MTILES; ++t)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    float sum = acc[t][e];
-                    for (int w = 1; w < WARPS; ++w) sum += red[((size_t)w * MTILES * 4 + t * 4 + e) * 32 + lane];
-                    acc[t][e] = sum;
-                }
-        }
-
-        // ---- epilogue: this thread holds rows r_lo (+8) and columns c_lo, c_lo + 1 ---
-        if (EPI == EPI_GATED || EPI == EPI_QKV) {
-            // columns 0-3 pair with 4-7: the lanes of the second half hand theirs over
-            const bool low = (lane & 3) < 2;
-            const int n_a = unit_row<EPI>(a, unit, c_lo & 3);
-            const int n_b = unit_row<EPI>(a, unit, (c_lo & 3) + 4);
-#pragma unroll
-            for (int t = 0; t < MTILES; ++t) {
-                float pv[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) pv[e] = __shfl_xor_sync(0xffffffffu, acc[t][e], 2);
-                if (!low) continue;
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    int m = t * 16 + r_lo + (e >> 1) * 8;
-                    if (m >= M) continue;
-                    int na = n_a + (e & 1), nb = n_b + (e & 1);
-                    float va = acc[t][e], vb = pv[e];
-                    if (a.bias) {
-                        va += a.bias[na];
-                        vb += a.bias[nb];
-                    }
-                    if (EPI == EPI_GATED) {
-                        reinterpret_cast<bf16*>(a.out)[(size_t)m * inter + na] =
-                            __float2bfloat16_rn((va / (1.0f + expf(-va))) * vb);
-                    } else {
-                        int pos = i == 0 ? pos0[t][e >> 1] : a.token_pos[m];
-                        if (pos < 0) continue;
-                        int head = na / a.d, j = na - head * a.d;
-                        va = round_bf16(va);
-                        vb = round_bf16(vb);
-                        bool is_v = head >= a.nq + a.nkv;
-                        if (a.sin_t && !is_v) {
-                            float c = i == 0 ? cos0[t][e] : a.cos_t[(size_t)pos * half + j];
-                            float s = i == 0 ? sin0[t][e] : a.sin_t[(size_t)pos * half + j];
-                            float ra = va * c - vb * s, rb = vb * c + va * s;
-                            va = ra;
-                            vb = rb;
-                        }
-                        bf16 ta = __float2bfloat16_rn(va), tb = __float2bfloat16_rn(vb);
-                        if (head < a.nq) {
-                            bf16* o = reinterpret_cast<bf16*>(a.out) + ((size_t)m * a.nq + head) * a.d;
-                            o[j] = ta;
-                            o[j + half] = tb;
-                        } else {
-                            int hk = is_v ? head - a.nq - a.nkv : head - a.nq;
-                            bf16* cache = is_v ? a.v_cache : a.k_cache;
-                            int page = i == 0 ? page0[t][e >> 1]
-                                              : a.page_table[(size_t)a.token_seq[m] * a.table_cols +
-                                                             pos / a.page_size];
-                            size_t dst = ((size_t)(page * a.nkv + hk) * a.page_size +
-                                          (pos % a.page_size)) * a.d;
-                            cache[dst + j] = ta;
-                            cache[dst + j + half] = tb;
-                        }
-                    }
-                }
+            for (int e = 0; e < 4; ++e) {
+                float sum = red[((size_t)warp * 4 + e) * 32 + lane];
+                for (int w = 1; w < WARPS; ++w) sum += red[((size_t)(w * MTILES + warp) * 4 + e) * 32 + lane];
+                eacc[0][e] = sum;
             }
         } else {
-            const int n0 = unit * 8 + c_lo;
-            const float b0v = a.bias ? a.bias[n0] : 0.f, b1v = a.bias ? a.bias[n0 + 1] : 0.f;
 #pragma unroll
-            for (int t = 0; t < MTILES; ++t) {
+            for (int tt = 0; tt < ET; ++tt)
 #pragma unroll
-                for (int hrow = 0; hrow < 2; ++hrow) {
-                    int m = t * 16 + r_lo + hrow * 8;
-                    if (m >= M) continue;
-                    float v0 = acc[t][hrow * 2] + b0v, v1 = acc[t][hrow * 2 + 1] + b1v;
-                    size_t o = (size_t)m * a.N + n0;
-                    if (EPI == EPI_STORE) {
-                        *reinterpret_cast<uint32_t*>(reinterpret_cast<bf16*>(a.out) + o) = pack_bf16(v0, v1);
-                    } else if (EPI == EPI_STORE_F32) {
-                        *reinterpret_cast<float2*>(reinterpret_cast<float*>(a.out) + o) = make_float2(v0, v1);
-                    } else if (EPI == EPI_ADD_F32) {
-                        float2* p = reinterpret_cast<float2*>(reinterpret_cast<float*>(a.out) + o);
-                        float2 old = (i == 0 && !a.out_is_hot) ? old0[t][hrow] : *p;
-                        *p = make_float2(old.x + v0, old.y + v1);
-                    } else {
-                        if (a.logits) *reinterpret_cast<float2*>(a.logits + o) = make_float2(v0, v1);
-                        if (better(v0, n0, best_v[t][hrow], best_i[t][hrow])) {
-                            best_v[t][hrow] = v0;
-                            best_i[t][hrow] = n0;
-                        }
-                        if (better(v1, n0 + 1, best_v[t][hrow], best_i[t][hrow])) {
-                            best_v[t][hrow] = v1;
-                            best_i[t][hrow] = n0 + 1;
-                        }
-                    }
-                }
-            }
+                for (int e = 0; e < 4; ++e) eacc[tt][e] = acc[SPLITK ? 0 : tt][e];
         }
+
+        // ---- epilogue -----------------------------------------------------------
+#pragma unroll
+        for (int tt = 0; tt < ET; ++tt)
+            epi_finish<EPI>(a, unit, tile_of(tt) * 16, lane, eacc[tt], pre[tt], i == 0, best_v[tt], best_i[tt]);
     }
     if (failed && lane == 0 && a.status) atomicExch(a.status, 2);
     if (EPI != EPI_ARGMAX) trace_mark(a.trace, 1);
@@ -534,28 +610,29 @@ gemv_kernel(GemvArgs a) {
         // the four lanes of a row hold its candidates: fold them, then the warps,
         // then the CTAs; the last CTA to arrive finishes the rows.
 #pragma unroll
-        for (int t = 0; t < MTILES; ++t)
+        for (int tt = 0; tt < ET; ++tt)
 #pragma unroll
             for (int hrow = 0; hrow < 2; ++hrow) {
 #pragma unroll
                 for (int o = 1; o < 4; o <<= 1) {
-                    float ov = __shfl_xor_sync(0xffffffffu, best_v[t][hrow], o);
-                    int oi = __shfl_xor_sync(0xffffffffu, best_i[t][hrow], o);
-                    if (oi >= 0 && better(ov, oi, best_v[t][hrow], best_i[t][hrow])) {
-                        best_v[t][hrow] = ov;
-                        best_i[t][hrow] = oi;
+                    float ov = __shfl_xor_sync(0xffffffffu, best_v[tt][hrow], o);
+                    int oi = __shfl_xor_sync(0xffffffffu, best_i[tt][hrow], o);
+                    if (oi >= 0 && better(ov, oi, best_v[tt][hrow], best_i[tt][hrow])) {
+                        best_v[tt][hrow] = ov;
+                        best_i[tt][hrow] = oi;
                     }
                 }
-                if ((lane & 3) == 0) {
-                    cta_val[warp][t * 16 + r_lo + hrow * 8] = best_v[t][hrow];
-                    cta_idx[warp][t * 16 + r_lo + hrow * 8] = best_i[t][hrow];
+                // (with the warps sharing K a row has one candidate: its tile's warp's)
+                if (epi_warp && (lane & 3) == 0) {
+                    cta_val[SPLITK ? 0 : warp][tile_of(tt) * 16 + r_lo + hrow * 8] = best_v[tt][hrow];
+                    cta_idx[SPLITK ? 0 : warp][tile_of(tt) * 16 + r_lo + hrow * 8] = best_i[tt][hrow];
                 }
             }
         __syncthreads();
         for (int m = threadIdx.x; m < M; m += WARPS * 32) {
             float bv = -FLT_MAX;
             int bi = -1;
-            for (int w = 0; w < WARPS; ++w) {
+            for (int w = 0; w < (SPLITK ? 1 : WARPS); ++w) {
                 if (cta_idx[w][m] >= 0 && better(cta_val[w][m], cta_idx[w][m], bv, bi)) {
                     bv = cta_val[w][m];
                     bi = cta_idx[w][m];

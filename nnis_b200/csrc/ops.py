@@ -267,29 +267,49 @@ def sm_count(device) -> int:
     return _sm_count[key]
 
 
-# Most rows for which the parts of a decode step choose the decode projection
-# kernel; with more rows (the fourth tile of 16) a norm kernel and the tcgen05 product
-# are faster, because every CTA of the projection kernel normalises and holds all
-# rows for itself.
+# The decode projections have two kernels: one whose CTAs hold all rows of x for eight
+# output features each (at most 64 rows), and one that cuts the rows into tiles of 16
+# (more than 16 rows, few output features, every CTA resident at once).  Where only the
+# first applies, the parts choose it up to DECODE_GEMV_ROWS rows, and fold the norm before
+# a projection into it up to GEMV_NORM_ROWS rows: every CTA of that kernel normalises all
+# rows for itself, through registers, which with more than a tile of rows costs more than
+# a norm kernel of its own.  Beyond that the general kernels (tcgen05) run.
 DECODE_GEMV_ROWS = int(os.environ.get("NNIS_DECODE_GEMV_ROWS", "48"))
+GEMV_NORM_ROWS = int(os.environ.get("NNIS_GEMV_NORM_ROWS", "16"))
+# Most wanted rows for which the head runs as the decode projection kernel (with the final
+# norm and the greedy pick folded in); with more, its products on mma.sync tiles cost more
+# than the weights' way from memory, and the norm, the tcgen05 product and the pick run
+# as kernels of their own.
+GEMV_HEAD_ROWS = int(os.environ.get("NNIS_GEMV_HEAD_ROWS", "48"))
 
 
-def gemv_takes(m: int, n: int, k: int, epilogue: int = EPI_STORE, device=None) -> bool:
-    """Whether the decode projection kernel runs this shape (else the general
-    kernels): at most 64 rows, K in steps of 16, N in steps of 8, operands that fit
-    shared memory."""
-    if m > 64 or k % 16 or n % 8:
-        return False
+def gemv_kind(m: int, n: int, k: int, epilogue: int = EPI_STORE, device=None, normed: bool = False) -> int:
+    """Which decode projection kernel runs this product: 2 the one over tiles of rows, 1
+    the one whose CTAs hold all rows, 0 neither (the general kernels must run)."""
     sms = sm_count(device) if device is not None else 148
-    if epilogue == EPI_ADD_F32:  # may run as several launches over slices of K
-        return gemv_slices(m, n, k, device) >= 1
-    return bool(_lib().nnis_gemv_takes(m, n, k, sms))
+    return int(_lib().nnis_gemv_kind(m, n, k, epilogue, 1 if normed else 0, sms))
+
+
+def gemv_takes(m: int, n: int, k: int, epilogue: int = EPI_STORE, device=None, normed: bool = False) -> bool:
+    """Whether a decode projection kernel can run this shape: K in steps of 16, N in
+    steps of 8, operands that fit shared memory; at most 64 rows, or up to 128 where the
+    kernel over tiles of rows applies."""
+    return gemv_kind(m, n, k, epilogue, device, normed) > 0
+
+
+def gemv_pays(m: int, n: int, k: int, epilogue: int = EPI_STORE, device=None, normed: bool = False) -> bool:
+    """Whether the parts of a decode step should choose a decode projection kernel for
+    this product (see the thresholds above)."""
+    kind = gemv_kind(m, n, k, epilogue, device, normed)
+    return kind == 2 or (kind == 1 and m <= DECODE_GEMV_ROWS and (not normed or m <= GEMV_NORM_ROWS))
 
 
 def gemv_slices(m: int, n: int, k: int, device=None) -> int:
     """Launches that an ADD_F32 product of these sizes takes (slices of K, each
     adding its share in order); 0: not taken."""
     sms = sm_count(device) if device is not None else 148
+    if gemv_kind(m, n, k, EPI_ADD_F32, device) == 2:
+        return 1
     return int(_lib().nnis_gemv_slices(m, n, k, sms))
 
 
@@ -328,7 +348,8 @@ def gemv_bf16(w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, 
     else:
         _need(x is not None and x.dtype == torch.bfloat16 and x.shape[1] == k, "gemv: x bfloat16 [m, k]")
         m = x.shape[0] if m is None else m
-    _need(gemv_takes(m, n, k, epilogue, w.device), f"gemv: shape m={m} n={n} k={k} is not taken")
+    _need(gemv_takes(m, n, k, epilogue, w.device, hidden is not None),
+          f"gemv: shape m={m} n={n} k={k} is not taken")
     if bias is not None:
         _need(bias.dtype == torch.float32 and bias.numel() == n, "gemv: bias float32 [n]")
     if epilogue == EPI_STORE:

@@ -128,19 +128,19 @@ class Attention(Part):
         return {}
 
     # -- run --------------------------------------------------------------
-    def _decode_kernels(self, ctx, n: int) -> bool:
+    def _decode_kernels(self, ctx, n: int, normed: bool = False) -> bool:
         """The fused bfloat16 decode kernel for q, k, v: few rows, one token each."""
-        return (self.dtype == torch.bfloat16 and ctx.decode and n <= ops.DECODE_GEMV_ROWS
+        return (self.dtype == torch.bfloat16 and ctx.decode
                 and self.head_dim % 16 == 0 and self.position_in_kernel
-                and ops.gemv_takes(n, self.w_qkv.shape[0], self.hidden, ops.EPI_QKV, self.device))
+                and ops.gemv_pays(n, self.w_qkv.shape[0], self.hidden, ops.EPI_QKV, self.device, normed))
 
     def _fused_out(self, ctx, n: int) -> bool:
-        return (self.dtype == torch.bfloat16 and ctx.decode and n <= ops.DECODE_GEMV_ROWS
-                and ops.gemv_takes(n, self.hidden, self.heads * self.head_dim, ops.EPI_ADD_F32,
-                                   self.device))
+        return (self.dtype == torch.bfloat16 and ctx.decode
+                and ops.gemv_pays(n, self.hidden, self.heads * self.head_dim, ops.EPI_ADD_F32,
+                                  self.device))
 
     def fuses_norm(self, norm, ctx, n: int) -> bool:
-        return getattr(norm, "kind", None) == "rmsnorm" and self._decode_kernels(ctx, n)
+        return getattr(norm, "kind", None) == "rmsnorm" and self._decode_kernels(ctx, n, normed=True)
 
     def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor, cache: KVView) -> None:
         self._run(ctx, residual, cache, x=x)
@@ -179,7 +179,7 @@ class Attention(Part):
         # ... or, with few sequences, short slices whose pages are all in shared memory at once
         tma_splits = ops.attention_decode_tma_plan(
             n, nq, nkv, d, cache.page_size, table.shape[1], self.device, ctx.share) if mma_decode else 0
-        if self._decode_kernels(ctx, n):
+        if self._decode_kernels(ctx, n, normed=hidden is not None):
             q = ws.get("q", (n, nq * d), self.dtype)
             ops.gemv_bf16(self.w_qkv, self.b_qkv, q, ops.EPI_QKV, x=x, hidden=hidden,
                           norm_weight=norm.weight if norm is not None else None,

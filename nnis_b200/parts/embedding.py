@@ -66,7 +66,8 @@ class LinearHead(Part):
 
     def fuses_norm(self, norm, rows: int) -> bool:
         return (getattr(norm, "kind", None) == "rmsnorm" and self.dtype == torch.bfloat16
-                and ops.gemv_takes(rows, self.vocab, self.width, ops.EPI_STORE_F32, self.device))
+                and rows <= ops.GEMV_HEAD_ROWS
+                and ops.gemv_takes(rows, self.vocab, self.width, ops.EPI_STORE_F32, self.device, True))
 
     def forward_pick(self, hidden: torch.Tensor, norm, rows: torch.Tensor, picks: torch.Tensor,
                      scratch: torch.Tensor, logits: Optional[torch.Tensor] = None,

@@ -59,17 +59,17 @@ class GatedMLP(Part):
     def step_flops(self, counts, starts) -> float:
         return 2.0 * 3 * self.hidden * self.inter * sum(counts)
 
-    def _fused_gate_up(self, ctx, n: int) -> bool:
+    def _fused_gate_up(self, ctx, n: int, normed: bool = False) -> bool:
         """The fused bfloat16 decode kernel for gate/up (few rows, one token each)."""
-        return (self.dtype == torch.bfloat16 and ctx.decode and n <= ops.DECODE_GEMV_ROWS
-                and ops.gemv_takes(n, 2 * self.inter, self.hidden, ops.EPI_GATED, self.device))
+        return (self.dtype == torch.bfloat16 and ctx.decode
+                and ops.gemv_pays(n, 2 * self.inter, self.hidden, ops.EPI_GATED, self.device, normed))
 
     def _fused_down(self, ctx, n: int) -> bool:
-        return (self.dtype == torch.bfloat16 and ctx.decode and n <= ops.DECODE_GEMV_ROWS
-                and ops.gemv_takes(n, self.hidden, self.inter, ops.EPI_ADD_F32, self.device))
+        return (self.dtype == torch.bfloat16 and ctx.decode
+                and ops.gemv_pays(n, self.hidden, self.inter, ops.EPI_ADD_F32, self.device))
 
     def fuses_norm(self, norm, ctx, n: int) -> bool:
-        return getattr(norm, "kind", None) == "rmsnorm" and self._fused_gate_up(ctx, n)
+        return getattr(norm, "kind", None) == "rmsnorm" and self._fused_gate_up(ctx, n, normed=True)
 
     def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor) -> None:
         self._run(ctx, residual, x=x)
@@ -82,7 +82,7 @@ class GatedMLP(Part):
         n = residual.shape[0]
         ws = ctx.workspace
         act = ws.get("act", (n, self.inter), self.dtype)
-        if self._fused_gate_up(ctx, n):
+        if self._fused_gate_up(ctx, n, normed=hidden is not None):
             ops.gemv_bf16(self.w_gu, self.b_gu, act, ops.EPI_GATED, x=x, hidden=hidden,
                           norm_weight=norm.weight if norm is not None else None,
                           eps=norm.eps if norm is not None else 0.0, m=n)

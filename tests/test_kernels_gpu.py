@@ -330,13 +330,20 @@ def test_temperature_sampling_follows_the_seeded_draws():
 # ---------------------------------------------------------------------------
 # the fused bfloat16 decode kernels
 # ---------------------------------------------------------------------------
-@pytest.mark.parametrize("m", [1, 2, 3, 8, 11, 16, 17, 40, 64])
-@pytest.mark.parametrize("n,k", [(8, 16), (104, 80), (960, 576), (1000, 1536)])
+@pytest.mark.parametrize("m", [1, 2, 3, 8, 11, 16, 17, 33, 40, 64, 100, 128])
+@pytest.mark.parametrize("n,k", [(8, 16), (104, 80), (960, 576), (1000, 1536), (3072, 576)])
 def test_gemv_plain_epilogues_and_norm_prologue(m, n, k):
+    """Both kernels of the decode projections: the one whose CTAs hold all rows (up to 64)
+    and, from 17 rows on where every CTA is resident at once, the one over tiles of rows."""
     o = ops()
-    if not o.gemv_takes(m, n, k, device=DEV):
-        assert m > 48 and k == 1536  # x and the weight stages do not fit shared memory
-        return
+    kind = o.gemv_kind(m, n, k, o.EPI_STORE, DEV)
+    if n == 3072 and m >= 64:
+        # more CTAs over tiles of rows than are resident at once: the other kernel, up to its 64 rows
+        assert kind == (1 if m == 64 else 0)
+        if kind == 0:
+            return
+    else:
+        assert kind == (1 if m <= 16 else 2)
     g = torch.Generator().manual_seed(m + n + k)
     w = (torch.randn(n, k, generator=g) / math.sqrt(k)).bfloat16()
     bias = torch.randn(n, generator=g)
@@ -353,9 +360,20 @@ def test_gemv_plain_epilogues_and_norm_prologue(m, n, k):
     o.gemv_bf16(w.to(DEV), bias.to(DEV), acc, o.EPI_ADD_F32, x=x.to(DEV))
     close(acc, base.double() + want, "float32", "gemv add")
     # norm prologue with gathered rows
+    if not o.gemv_takes(m, n, k, o.EPI_STORE_F32, DEV, True):
+        # with the normalised rows beside the weights only one CTA fits an SM
+        assert (k == 1536 and m > 64) or (n == 3072 and m > 64)
+        return
     hidden = torch.randn(m + 5, k, generator=g) * 2
     nw = 1 + 0.1 * torch.randn(k, generator=g)
     rows = torch.randperm(m + 5, generator=g)[:m].to(torch.int32)
+    # the inputs as drawn, rounding ties and all, held to the bound of a bfloat16 value ...
+    o.gemv_bf16(w.to(DEV), None, out32, o.EPI_STORE_F32, hidden=hidden.to(DEV),
+                norm_weight=nw.to(DEV), eps=1e-5, rows=rows.to(DEV))
+    close(out32, P.linear(P.rms_norm(hidden[rows.long()], nw, 1e-5).bfloat16(), w), "bfloat16",
+          "gemv norm prologue, inputs as drawn")
+    # ... and, with the few values moved whose rounding is not decided, to the float32 bound
+    hidden = away_from_bf16_ties(hidden, nw, 1e-5)
     normed = P.rms_norm(hidden[rows.long()], nw, 1e-5).bfloat16()
     o.gemv_bf16(w.to(DEV), None, out32, o.EPI_STORE_F32, hidden=hidden.to(DEV),
                 norm_weight=nw.to(DEV), eps=1e-5, rows=rows.to(DEV))
@@ -415,11 +433,14 @@ def test_gemv_long_rows_in_chunks_and_slices(m, n, k):
         close(out, P.swiglu(want[:, :inter], want[:, inter:]), "bfloat16", "gemv gated, chunks")
 
 
-@pytest.mark.parametrize("m", [1, 5, 16, 33, 64])
-def test_gemv_gated_epilogue(m):
+@pytest.mark.parametrize("m", [1, 5, 16, 33, 64, 81])
+@pytest.mark.parametrize("k,inter", [(80, 100), (576, 1536)])
+def test_gemv_gated_epilogue(m, k, inter):
     o = ops()
+    if not o.gemv_takes(m, 2 * inter, k, o.EPI_GATED, DEV):
+        assert m > 64 and inter == 1536  # more CTAs over tiles of rows than are resident at once
+        return
     g = torch.Generator().manual_seed(m)
-    k, inter = 80, 100
     w = (torch.randn(2 * inter, k, generator=g) / math.sqrt(k) * 3).bfloat16()
     bias = torch.randn(2 * inter, generator=g)
     x = torch.randn(m, k, generator=g).bfloat16()
@@ -430,19 +451,24 @@ def test_gemv_gated_epilogue(m):
 
 
 @pytest.mark.parametrize("nq,nkv,d,rotate", [(6, 2, 16, True), (3, 1, 48, True), (4, 4, 64, False),
-                                             (2, 0, 32, True)])
-def test_gemv_qkv_epilogue_rotates_and_stores(nq, nkv, d, rotate):
+                                             (2, 0, 32, True), (9, 3, 64, True)])
+@pytest.mark.parametrize("copies", [1, 7, 20])
+def test_gemv_qkv_epilogue_rotates_and_stores(nq, nkv, d, rotate, copies):
+    """Five rows (one of them padding), or several times these rows with a cache of their
+    own each: more than a tile of rows goes to the kernel over tiles of rows."""
     o = ops()
     g = torch.Generator().manual_seed(nq * d)
-    m, k, page = 5, 48, 64
+    m, k, page = 5 * copies, 48, 64
     n = (nq + 2 * nkv) * d
+    assert o.gemv_kind(m, n, k, o.EPI_QKV, DEV) == (1 if m <= 16 else 2)
     w = (torch.randn(n, k, generator=g) / math.sqrt(k)).bfloat16()
     bias = torch.randn(n, generator=g)
     x = torch.randn(m, k, generator=g).bfloat16()
-    pos = torch.tensor([0, 63, 64, -1, 130], dtype=torch.int32)
-    seq = torch.tensor([0, 1, 2, 0, 3], dtype=torch.int32)
-    table = torch.tensor([[5, -1, -1], [2, -1, -1], [7, 1, -1], [0, 3, 4]], dtype=torch.int32)
-    kc = torch.zeros(8, max(nkv, 1), page, d, dtype=torch.bfloat16, device=DEV)
+    pos = torch.tensor([0, 63, 64, -1, 130] * copies, dtype=torch.int32)
+    seq = torch.cat([torch.tensor([0, 1, 2, 0, 3], dtype=torch.int32) + 4 * c for c in range(copies)])
+    base = torch.tensor([[5, -1, -1], [2, -1, -1], [7, 1, -1], [0, 3, 4]], dtype=torch.int32)
+    table = torch.cat([torch.where(base >= 0, base + 8 * c, base) for c in range(copies)])
+    kc = torch.zeros(8 * copies, max(nkv, 1), page, d, dtype=torch.bfloat16, device=DEV)
     vc = torch.zeros_like(kc)
     cos, sin = P.rope_tables(200, d, 10000.0)
     q_out = torch.full((m, nq * d), 9.0, dtype=torch.bfloat16, device=DEV)
@@ -468,13 +494,17 @@ def test_gemv_qkv_epilogue_rotates_and_stores(nq, nkv, d, rotate):
             close(kc[pg, :, p % page], rk, "bfloat16", "k")
             close(vc[pg, :, p % page], heads[nq + nkv:], "bfloat16", "v")
     if nkv:
-        assert int((kc.float().abs().sum(-1) > 0).sum()) == 4 * nkv  # nothing else was written
+        assert int((kc.float().abs().sum(-1) > 0).sum()) == 4 * nkv * copies  # nothing else was written
 
 
 def test_gemv_refuses_what_it_does_not_take():
     o = ops()
-    assert not o.gemv_takes(65, 64, 64) and not o.gemv_takes(4, 64, 56) and not o.gemv_takes(4, 68, 64)
-    assert o.gemv_takes(64, 64, 64) and not o.gemv_takes(64, 64, 4096)
+    assert not o.gemv_takes(129, 64, 64) and not o.gemv_takes(4, 64, 56) and not o.gemv_takes(4, 68, 64)
+    assert o.gemv_takes(64, 64, 64) and o.gemv_takes(128, 64, 64) and not o.gemv_takes(64, 64, 4096)
+    # more than 64 rows: only the kernel over tiles of rows, which wants every CTA resident
+    # (and has no picking epilogue)
+    assert not o.gemv_takes(80, 49152, 576) and not o.gemv_takes(80, 64, 64, o.EPI_ARGMAX)
+    assert o.gemv_kind(64, 49152, 576) == 1 and o.gemv_kind(17, 64, 64, o.EPI_ARGMAX) == 1
     with pytest.raises(o.KernelError, match="not taken"):
         o.gemv_bf16(torch.zeros(68, 64, dtype=torch.bfloat16, device=DEV), None,
                     torch.zeros(2, 68, dtype=torch.bfloat16, device=DEV), o.EPI_STORE,
