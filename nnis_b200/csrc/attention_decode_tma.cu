@@ -67,7 +67,7 @@ __device__ __forceinline__ unsigned ticket_take(unsigned* ticket) {
 }
 
 template <int D>
-__global__ void __launch_bounds__(kClThreads, 3)
+__global__ void __launch_bounds__(kClThreads, D == 64 ? 5 : 3)
 attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const bf16* k_cache,
                        const bf16* v_cache, const bf16* __restrict__ q, int q_stride,

@@ -101,6 +101,21 @@ static int gemv_slices(int M, int N, int K, int sm_count, GemvPlan* plan) {
     return 0;
 }
 
+// The kernel over tiles of rows: in how many slices of K it runs a product (0: it does
+// not take it), and with how many units per CTA.  Only the adding epilogue may be cut:
+// each slice a launch that adds its share into the output, in order.
+static int rowtile_slices(int M, int N, int K, int epilogue, int pro, int sm_count, int* units) {
+    *units = gemv_rowtile_units(M, N, K, epilogue, pro, sm_count);
+    if (*units > 0) return 1;
+    if (epilogue != EPI_ADD_F32 || pro != PRO_PLAIN) return 0;
+    for (int c = 2; c <= 3; ++c) {  // (more launches than that cost more than the general kernel)
+        if (K % (16 * c)) continue;
+        *units = gemv_rowtile_units(M, N, K / c, epilogue, pro, sm_count);
+        if (*units > 0) return c;
+    }
+    return 0;
+}
+
 }  // namespace nnis
 
 // Whether nnis_gemv_bf16 takes a shape (1) or the caller must use the general
@@ -115,7 +130,9 @@ NNIS_API int nnis_gemv_takes(int M, int N, int K, int sm_count) {
 // launch, more: that many launches inside nnis_gemv_bf16.
 NNIS_API int nnis_gemv_slices(int M, int N, int K, int sm_count) {
     nnis::GemvPlan p;
-    return nnis::gemv_slices(M, N, K, sm_count, &p);
+    int units;
+    int rows = nnis::rowtile_slices(M, N, K, nnis::EPI_ADD_F32, nnis::PRO_PLAIN, sm_count, &units);
+    return rows > 0 ? rows : nnis::gemv_slices(M, N, K, sm_count, &p);
 }
 
 // Which kernel nnis_gemv_bf16 runs for a product: 2 the one that cuts the rows into
@@ -123,10 +140,24 @@ NNIS_API int nnis_gemv_slices(int M, int N, int K, int sm_count) {
 // CTAs hold all rows (at most 64), 0 neither.  `normed`: with the norm prologue.
 NNIS_API int nnis_gemv_kind(int M, int N, int K, int epilogue, int normed, int sm_count) {
     using namespace nnis;
-    if (gemv_rowtile_units(M, N, K, epilogue, normed ? PRO_NORM : PRO_PLAIN, sm_count) > 0) return 2;
+    int units;
+    if (rowtile_slices(M, N, K, epilogue, normed ? PRO_NORM : PRO_PLAIN, sm_count, &units) > 0) return 2;
     GemvPlan p;
     if (epilogue == EPI_ADD_F32 && !normed) return gemv_slices(M, N, K, sm_count, &p) >= 1 ? 1 : 0;
     return gemv_plan(M, N, K, sm_count, &p) ? 1 : 0;
+}
+
+// The same questions for the kernel whose CTAs hold all rows alone (what bit 2 of
+// nnis_gemv_bf16's `pdl` selects).
+NNIS_API int nnis_gemv_units_takes(int M, int N, int K, int epilogue, int normed, int sm_count) {
+    nnis::GemvPlan p;
+    if (epilogue == nnis::EPI_ADD_F32 && !normed) return nnis::gemv_slices(M, N, K, sm_count, &p) >= 1 ? 1 : 0;
+    return nnis::gemv_plan(M, N, K, sm_count, &p) ? 1 : 0;
+}
+
+NNIS_API int nnis_gemv_units_slices(int M, int N, int K, int sm_count) {
+    nnis::GemvPlan p;
+    return nnis::gemv_slices(M, N, K, sm_count, &p);
 }
 
 // How many CTAs a launch with these sizes has: the ARGMAX scratch is
@@ -140,7 +171,8 @@ NNIS_API int nnis_gemv_grid(int M, int N, int K, int sm_count) {
 // each) and `ticket` (one zeroed counter, left zero).  `pdl`: bit 0 launches the kernel
 // as a programmatic dependent of the one before it; bit 1 lets the kernel after it
 // start together with this one (only for a successor that reads nothing of this step
-// before its own wait).
+// before its own wait); bit 2: not the kernel over tiles of rows, even where it applies
+// (for comparisons).
 NNIS_API int nnis_gemv_bf16(const void* x, const float* hidden, const int* rows, const float* norm_w,
                             float eps, const void* w, const float* bias, void* out, int M, int N,
                             int K, int epilogue, const int* token_pos, const int* token_seq,
@@ -155,9 +187,10 @@ NNIS_API int nnis_gemv_bf16(const void* x, const float* hidden, const int* rows,
     plan.kc = K;
     int pro = hidden ? PRO_NORM : PRO_PLAIN;
     // more rows than a tile and few output features: the kernel that cuts the rows
-    const int rowtile_units = gemv_rowtile_units(M, N, K, epilogue, pro, sm_count);
+    int rowtile_units = 0;
+    const int rowtile_cuts = (pdl & 4) ? 0 : rowtile_slices(M, N, K, epilogue, pro, sm_count, &rowtile_units);
     const bool may_slice = epilogue == EPI_ADD_F32 && pro == PRO_PLAIN;
-    const int slices = rowtile_units > 0 ? 1
+    const int slices = rowtile_cuts > 0 ? rowtile_cuts
                        : may_slice      ? gemv_slices(M, N, K, sm_count, &plan)
                                         : (gemv_plan(M, N, K, sm_count, &plan) ? 1 : 0);
     if (slices == 0) return NNIS_ERR_UNSUPPORTED;
@@ -190,16 +223,17 @@ NNIS_API int nnis_gemv_bf16(const void* x, const float* hidden, const int* rows,
                                             "gemv rows gated", "gemv rows qkv"};
     for (int s = 0; s < slices; ++s) {
         int rc;
-        if (rowtile_units > 0) {
+        if (rowtile_cuts > 0) {
             a.trace = trace_slot(epilogue >= 0 && epilogue <= 4 ? kRowNames[epilogue] : "gemv rows");
-            return gemv_launch_rowtile(a, epilogue, pro, rowtile_units, (pdl & 1) != 0, stream);
-        }
+            rc = gemv_launch_rowtile(a, epilogue, pro, rowtile_units, (pdl & 1) != 0, stream);
+        } else {
         a.trace = trace_slot(epilogue >= 0 && epilogue <= 5 ? kNames[epilogue] : "gemv");
         switch (plan.mtiles) {
             case 1: rc = gemv_launch_tiles1(a, epilogue, pro, plan, (pdl & 1) != 0, stream); break;
             case 2: rc = gemv_launch_tiles2(a, epilogue, pro, plan, (pdl & 1) != 0, stream); break;
             case 3: rc = gemv_launch_tiles3(a, epilogue, pro, plan, (pdl & 1) != 0, stream); break;
             default: rc = gemv_launch_tiles4(a, epilogue, pro, plan, (pdl & 1) != 0, stream); break;
+        }
         }
         if (rc != NNIS_OK) return rc;
         a.x += a.K;

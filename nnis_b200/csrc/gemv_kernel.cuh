@@ -101,6 +101,53 @@ __device__ __forceinline__ int unit_row(const GemvArgs& a, int unit, int c) {
     return unit * 8 + c;
 }
 
+// The norm prologue for rows too long for a lane's registers, in two passes over the
+// row, each with eight loads in flight per lane (a loop of single loads would wait for L2
+// once per iteration).  A lane takes the float4 at `first`, `first` + STRIDE, ...
+template <int STRIDE>
+__device__ __forceinline__ float row_square_sum(const float4* h4, int k4, int first) {
+    float ss = 0.f;
+    for (int c0 = first; c0 < k4; c0 += STRIDE * 8) {
+        float4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            int c = c0 + STRIDE * j;
+            v[j] = c < k4 ? h4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            ss = fmaf(v[j].x, v[j].x, ss);
+            ss = fmaf(v[j].y, v[j].y, ss);
+            ss = fmaf(v[j].z, v[j].z, ss);
+            ss = fmaf(v[j].w, v[j].w, ss);
+        }
+    }
+    return ss;
+}
+
+// ... and the row scaled by `sc`, weighted and rounded to bfloat16 at `dst`.
+template <int STRIDE>
+__device__ __forceinline__ void row_scale_store(const float4* h4, const float4* w4, int k4, int first,
+                                                float sc, bf16* dst) {
+    for (int c0 = first; c0 < k4; c0 += STRIDE * 8) {
+        float4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            int c = c0 + STRIDE * j;
+            v[j] = c < k4 ? h4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            int c = c0 + STRIDE * j;
+            if (c < k4) {
+                const float4 g = w4[c];
+                store4(dst + c * 4, make_float4((v[j].x * sc) * g.x, (v[j].y * sc) * g.y,
+                                                (v[j].z * sc) * g.z, (v[j].w * sc) * g.w));
+            }
+        }
+    }
+}
+
 // What the epilogue of one tile of 16 rows needs from global memory and that no product
 // decides: fetched before the wait of programmatic dependent launch (the residual stream
 // was last written two kernels back, positions and page tables before the step began).

@@ -1,33 +1,48 @@
-// Decode projections for more rows of x than one tile of 16, with few output
-// features (a model's width, not its vocabulary): y[M, N] = x[M, K] . W[N, K]^T.
+// Decode projections with few output features (a model's width, not its vocabulary):
+// y[M, N] = x[M, K] . W[N, K]^T, the rows of x cut into tiles of 16.
 //
-// With many rows the kernel of gemv_kernel.cuh, whose CTAs each hold all rows of x
-// for eight output features, is bound by x: every CTA fetches all of it after the
-// wait of programmatic dependent launch, M / 8 times the bytes of W in total, all
-// CTAs asking L2 for the same lines at once.  Here the rows are cut instead:
+// The kernel of gemv_kernel.cuh gives a CTA all rows of x for eight output features.
+// With many rows it is bound by x: every CTA fetches all of it after the wait of
+// programmatic dependent launch, M / 8 times the bytes of W in total, all CTAs asking L2
+// for the same lines at once.  Here
 //
-//  * CTA (bx, by) owns NU units of eight output features (bx) for ONE tile of 16
-//    rows (by).  Its weights (NU * 8 rows of W, whole) come by bulk copies issued
-//    before the wait, so W is read once per tile of rows from L2, under the kernel
-//    before this one; after the wait a CTA needs only its 16 rows of x.
-//  * The eight warps share K.  With x as it is (no norm) a warp takes its columns
-//    of the 16 rows from global memory straight into the registers of its
-//    products, eight bytes a load: a lane's four consecutive columns stand for the
-//    two pairs of columns (2t, 2t+1 and 2t+8, 2t+9) that the tensor-core tile wants
-//    from it, and the weights are read from shared memory in the same order, so the
-//    sum over K is the same sum.  With the norm in front the warps normalise the
-//    rows into shared memory first, half a warp to a row, two rows at a time.
-//  * The partial sums meet in shared memory; warp u adds those of unit u in warp
-//    order (deterministic) and runs its epilogue (the ones of gemv_kernel.cuh,
-//    except ARGMAX).
+//  * CTA (bx, by) owns NU units of eight output features (bx) for ONE tile of 16 rows
+//    (by).  Its weights (NU * 8 rows of W, whole) come by bulk copies issued before the
+//    wait, so W is read once per tile of rows from L2, under the kernel before this one;
+//    after the wait a CTA needs only its 16 rows of x.
+//  * The eight warps share K.  With x as it is (no norm) a warp takes its columns of the
+//    16 rows from global memory straight into the registers of its products, eight bytes
+//    a load: a lane's four consecutive columns stand for the two pairs of columns (2t,
+//    2t+1 and 2t+8, 2t+9) that the tensor-core tile wants from it, and the weights are
+//    read from shared memory in the same order, so the sum over K is the same sum.  With
+//    the norm in front the warps normalise the rows into shared memory first: a warp to a
+//    row with at most eight rows, else half a warp to a row, two rows at a time.
+//  * The partial sums meet in shared memory, in the place of the weights; warp u adds
+//    those of unit u in warp order (deterministic) and runs its epilogue (the ones of
+//    gemv_kernel.cuh, except ARGMAX).
+//  * A decode step is a chain of short kernels, each of which starts while the one before
+//    it still runs (to fetch its weights) and must find room beside it: registers and
+//    shared memory per CTA are held down on purpose (__maxnreg__; with at most eight rows
+//    the second half of the tile of x is one row of zeros), so that this kernel's CTAs
+//    and those of the decode attention kernel (three to an SM) are resident together.
 #include "gemv_kernel.cuh"
 
 namespace nnis {
 
 constexpr int kRowtileWarps = 8;
-constexpr int kRowtileDirectSteps = 12;  // 16-column steps of one warp in registers: K <= 1,536
+// 16-column steps of one warp of x in registers: K <= 768, or K <= 1,536 (LONGK)
+__host__ __device__ constexpr int rowtile_direct_steps(bool longk) { return longk ? 12 : 6; }
 
-__host__ __device__ constexpr int rowtile_ctas_per_sm(int pro) { return pro == PRO_NORM ? 3 : 2; }
+// Registers per thread (see above), and the CTAs that fit an SM by them.
+__host__ __device__ constexpr int rowtile_registers(int pro, bool longk) {
+    return pro == PRO_NORM ? 80 : longk ? 128 : 104;
+}
+__host__ __device__ constexpr int rowtile_ctas_per_sm(int pro, bool longk) {
+    return 65536 / (kRowtileWarps * 32 * rowtile_registers(pro, longk));
+}
+
+// Rows of the normalised x in shared memory: a tile, or eight rows and one of zeros.
+__host__ __device__ constexpr int rowtile_x_rows(int M) { return M <= 8 ? 9 : 16; }
 
 // Elements between rows of W in shared memory.  Read by ldmatrix (norm prologue:
 // rows of 16 bytes, eight of them a phase) the stride must be 16 bytes off a multiple
@@ -37,12 +52,12 @@ __host__ __device__ constexpr int rowtile_w_stride(int K, int pro) {
     return pro == PRO_NORM ? K + 8 : K + ((16 - K % 64) + 64) % 64;
 }
 
-template <int EPI, int PRO, int NU>
-__global__ void __launch_bounds__(kRowtileWarps * 32, rowtile_ctas_per_sm(PRO))
+template <int EPI, int PRO, int NU, bool LONGK>
+__global__ void __maxnreg__(rowtile_registers(PRO, LONGK))
 gemv_rowtile_kernel(GemvArgs a) {
     constexpr int WARPS = kRowtileWarps;
     constexpr bool kDirect = PRO == PRO_PLAIN;
-    constexpr int kSteps = kDirect ? kRowtileDirectSteps : 1;
+    constexpr int kSteps = kDirect ? rowtile_direct_steps(LONGK) : 1;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t wbar;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -54,8 +69,9 @@ gemv_rowtile_kernel(GemvArgs a) {
     const int unit0 = blockIdx.x * NU;
     const int units_here = min(NU, n_units - unit0);
     bf16* ws = reinterpret_cast<bf16*>(smem_raw);                       // [NU * 8, KPW]
-    bf16* xs = ws + (size_t)NU * 8 * KPW;                               // [16, KP], norm prologue only
-    float* stash = reinterpret_cast<float*>(xs + (kDirect ? 0 : (size_t)16 * KP));  // [K], norm prologue only
+    const int xrows = rowtile_x_rows(a.M);
+    bf16* xs = ws + (size_t)NU * 8 * KPW;                               // [xrows, KP], norm prologue only
+    float* stash = reinterpret_cast<float*>(xs + (kDirect ? 0 : (size_t)xrows * KP));  // [K], more than 8 rows only
     // the partial sums take the place of the weights once every warp is through with them
     float* red = reinterpret_cast<float*>(smem_raw);                    // [WARPS, NU, 4, 32]
 
@@ -77,14 +93,24 @@ gemv_rowtile_kernel(GemvArgs a) {
             bulk_load(ws + (size_t)r * KPW, a.w + (size_t)unit_row<EPI>(a, unit0 + (r >> 3), r & 7) * a.ldw,
                       (uint32_t)K * 2u, &wbar);
     }
-    // ... the norm weights into shared memory, and what the epilogue needs.  This
-    // preamble has to fit under the tail of the kernel before, so its loads are asked
-    // for before the first of them is used.
+    // ... the norm weights and what the epilogue needs.  This preamble has to fit under
+    // the tail of the kernel before, so its loads are asked for before the first of them
+    // is used.  With at most eight rows a warp normalises one row and keeps its share of
+    // the norm weights in registers; with more they go to shared memory.
     constexpr int NW = 12;  // float4 of a row per lane of a half warp kept in registers: covers K <= 768
+    constexpr int NWF = 6;  // ... per lane of a whole warp
     constexpr int kStashPer = 2;  // float4 per thread: the stash covers K <= 2,048
     const int k4 = K >> 2;
-    const bool stashed = PRO == PRO_NORM && k4 <= kStashPer * WARPS * 32;
-    float4 sv[kStashPer];
+    const bool few = a.M <= 8;
+    const bool stashed = PRO == PRO_NORM && !few && k4 <= kStashPer * WARPS * 32;
+    float4 sv[kStashPer], nw[NWF];
+    if (PRO == PRO_NORM && few) {
+#pragma unroll
+        for (int j = 0; j < NWF; ++j) {
+            int c = lane + 32 * j;
+            nw[j] = c < k4 ? reinterpret_cast<const float4*>(a.norm_w)[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
     if (stashed) {
 #pragma unroll
         for (int j = 0; j < kStashPer; ++j) {
@@ -128,6 +154,47 @@ gemv_rowtile_kernel(GemvArgs a) {
             ax[s][2] = va.y;
             ax[s][3] = vb.y;
         }
+    } else if (few) {
+        // a warp to a row (row 8, of zeros, is warp 0's second)
+        for (int r = warp; r < xrows; r += WARPS) {
+            const int m = row0 + r;
+            if (r < 8 && m < a.M) {
+                const float4* h4 = reinterpret_cast<const float4*>(a.hidden + (size_t)(a.rows ? a.rows[m] : m) * K);
+                if (k4 <= 32 * NWF) {
+                    float4 hv[NWF];
+                    float ss = 0.f;
+#pragma unroll
+                    for (int j = 0; j < NWF; ++j) {
+                        int c = lane + 32 * j;
+                        hv[j] = c < k4 ? h4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+#pragma unroll
+                    for (int j = 0; j < NWF; ++j) {
+                        ss = fmaf(hv[j].x, hv[j].x, ss);
+                        ss = fmaf(hv[j].y, hv[j].y, ss);
+                        ss = fmaf(hv[j].z, hv[j].z, ss);
+                        ss = fmaf(hv[j].w, hv[j].w, ss);
+                    }
+                    ss = warp_sum(ss);
+                    const float sc = 1.0f / sqrtf(ss * (1.0f / (float)K) + a.eps);
+#pragma unroll
+                    for (int j = 0; j < NWF; ++j) {
+                        int c = lane + 32 * j;
+                        if (c < k4)
+                            store4(xs + (size_t)r * KP + c * 4,
+                                   make_float4((hv[j].x * sc) * nw[j].x, (hv[j].y * sc) * nw[j].y,
+                                               (hv[j].z * sc) * nw[j].z, (hv[j].w * sc) * nw[j].w));
+                    }
+                } else {
+                    const float ss = warp_sum(row_square_sum<32>(h4, k4, lane));
+                    const float sc = 1.0f / sqrtf(ss * (1.0f / (float)K) + a.eps);
+                    row_scale_store<32>(h4, w4, k4, lane, sc, xs + (size_t)r * KP);
+                }
+            } else {
+                for (int k = lane * 2; k < K; k += 64) *reinterpret_cast<uint32_t*>(xs + (size_t)r * KP + k) = 0u;
+            }
+        }
+        __syncthreads();
     } else {
         // half a warp to a row: the warp's two rows are in flight together
         const int hl = lane & 15;
@@ -152,13 +219,7 @@ gemv_rowtile_kernel(GemvArgs a) {
                 ss = fmaf(hv[j].w, hv[j].w, ss);
             }
         } else if (live) {
-            for (int c = hl; c < k4; c += 16) {
-                float4 v = h4[c];
-                ss = fmaf(v.x, v.x, ss);
-                ss = fmaf(v.y, v.y, ss);
-                ss = fmaf(v.z, v.z, ss);
-                ss = fmaf(v.w, v.w, ss);
-            }
+            ss = row_square_sum<16>(h4, k4, hl);
         }
         ss = half_warp_sum(ss);
         const float sc = 1.0f / sqrtf(ss * (1.0f / (float)K) + a.eps);
@@ -176,11 +237,7 @@ gemv_rowtile_kernel(GemvArgs a) {
                 }
             }
         } else {
-            for (int c = hl; c < k4; c += 16) {
-                float4 v = h4[c], g = w4[c];
-                store4(xs + (size_t)r * KP + c * 4,
-                       make_float4((v.x * sc) * g.x, (v.y * sc) * g.y, (v.z * sc) * g.z, (v.w * sc) * g.w));
-            }
+            row_scale_store<16>(h4, w4, k4, hl, sc, xs + (size_t)r * KP);
         }
         __syncthreads();
     }
@@ -213,7 +270,8 @@ gemv_rowtile_kernel(GemvArgs a) {
     } else {
         // lanes 0-7: weight rows at columns k0..k0+7, lanes 8-15: k0+8..k0+15
         const bf16* b_ptr = ws + (size_t)(lane & 7) * KPW + ((lane >> 3) & 1) * 8;
-        const bf16* a_ptr = xs + (size_t)(lane & 15) * KP + (lane >> 4) * 8;
+        // (with the row of zeros, the lanes of rows 8-15 all read it)
+        const bf16* a_ptr = xs + (size_t)min(lane & 15, xrows - 1) * KP + (lane >> 4) * 8;
 #pragma unroll 2
         for (int k0 = k_begin; k0 < k_end; k0 += 16) {
             uint32_t af[4], bw[NU][2];
@@ -250,41 +308,45 @@ gemv_rowtile_kernel(GemvArgs a) {
     trace_mark(a.trace, 1);
 }
 
-static size_t rowtile_smem(int nu, int K, int pro) {
-    size_t operands = ((size_t)nu * 8 * rowtile_w_stride(K, pro) + (pro == PRO_NORM ? (size_t)16 * (K + 8) : 0)) * sizeof(bf16) +
-                      (pro == PRO_NORM ? (size_t)K * sizeof(float) : 0);
+static size_t rowtile_smem(int M, int nu, int K, int pro) {
+    size_t operands = (size_t)nu * 8 * rowtile_w_stride(K, pro) * sizeof(bf16);
+    if (pro == PRO_NORM)
+        operands += (size_t)rowtile_x_rows(M) * (K + 8) * sizeof(bf16) + (M > 8 ? (size_t)K * sizeof(float) : 0);
     size_t sums = (size_t)kRowtileWarps * nu * 4 * 32 * sizeof(float);
     return operands > sums ? operands : sums;
 }
 
-// Units per CTA for a product of these sizes, or 0 when this kernel does not take
-// it: more than one tile of rows (at most eight), K in steps of 16 (at most 1,536
-// without the norm: a warp's share of x lives in registers), no ARGMAX epilogue,
-// and every CTA resident at once, so that all of W is asked for before the wait.
+// Units per CTA for a product of these sizes, or 0 when this kernel does not take it:
+// at most eight tiles of rows, K in steps of 16 (at most 1,536 without the norm: a
+// warp's share of x lives in registers), no ARGMAX epilogue, and every CTA resident at
+// once, so that all of W is asked for before the wait.
 int gemv_rowtile_units(int M, int N, int K, int epilogue, int pro, int sm_count) {
-    if (M <= 16 || M > 128 || K <= 0 || K % 16 || N <= 0 || N % 8) return 0;
+    if (M <= 0 || M > 128 || K <= 0 || K % 16 || N <= 0 || N % 8) return 0;
     if (epilogue == EPI_ARGMAX) return 0;
-    if (pro == PRO_PLAIN && K > kRowtileDirectSteps * 16 * kRowtileWarps) return 0;
+    if (pro == PRO_PLAIN && K > rowtile_direct_steps(true) * 16 * kRowtileWarps) return 0;
+    const bool longk = pro == PRO_PLAIN && K > rowtile_direct_steps(false) * 16 * kRowtileWarps;
     const int sms = sm_count > 0 ? sm_count : 148;
     const int mtiles = (M + 15) / 16, units = N / 8;
-    // as many units per CTA as there are tiles of rows keeps the number of CTAs near the
-    // number of units, and the bytes of x a CTA fetches after the wait below those of W
-    for (int nu = mtiles >= 3 ? 4 : 2; nu <= 4; nu *= 2) {
-        if (nu > kRowtileWarps) break;
-        size_t smem = rowtile_smem(nu, K, pro);
+    // With one tile of rows: the fewest units per CTA that leave room on the SMs for the
+    // kernels before and after (CTAs for at most one and a half SMs' worth).  With more:
+    // as many units as tiles of rows keeps the number of CTAs near the number of units, and
+    // the bytes of x that a CTA fetches after the wait below those of W.
+    for (int nu = mtiles == 1 ? 1 : mtiles == 2 ? 2 : 4; nu <= 4; nu *= 2) {
+        size_t smem = rowtile_smem(M, nu, K, pro);
         if (smem > 200 * 1024) continue;
         int fit = (int)((220 * 1024) / (smem + 1024));
-        if (fit > rowtile_ctas_per_sm(pro)) fit = rowtile_ctas_per_sm(pro);
+        if (fit > rowtile_ctas_per_sm(pro, longk)) fit = rowtile_ctas_per_sm(pro, longk);
         long ctas = (long)mtiles * ((units + nu - 1) / nu);
-        if (fit >= 1 && ctas <= (long)sms * fit) return nu;
+        long room = mtiles == 1 ? (long)sms * 3 / 2 : (long)sms * fit;
+        if (fit >= 1 && ctas <= room && ctas <= (long)sms * fit) return nu;
     }
     return 0;
 }
 
-template <int EPI, int PRO, int NU>
+template <int EPI, int PRO, int NU, bool LONGK>
 static int launch_rowtile_final(const GemvArgs& a, bool pdl, cudaStream_t stream) {
-    auto kernel = gemv_rowtile_kernel<EPI, PRO, NU>;
-    const size_t smem = rowtile_smem(NU, a.K, PRO);
+    auto kernel = gemv_rowtile_kernel<EPI, PRO, NU, LONGK>;
+    const size_t smem = rowtile_smem(a.M, NU, a.K, PRO);
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
@@ -305,8 +367,17 @@ static int launch_rowtile_final(const GemvArgs& a, bool pdl, cudaStream_t stream
 
 template <int EPI, int PRO>
 static int launch_rowtile_units(const GemvArgs& a, int nu, bool pdl, cudaStream_t stream) {
-    if (nu == 2) return launch_rowtile_final<EPI, PRO, 2>(a, pdl, stream);
-    if (nu == 4) return launch_rowtile_final<EPI, PRO, 4>(a, pdl, stream);
+    // (with the norm in front x is in shared memory: one variant for every K)
+    const bool longk = PRO == PRO_PLAIN && a.K > rowtile_direct_steps(false) * 16 * kRowtileWarps;
+    if (longk) {
+        if (nu == 1) return launch_rowtile_final<EPI, PRO, 1, PRO == PRO_PLAIN>(a, pdl, stream);
+        if (nu == 2) return launch_rowtile_final<EPI, PRO, 2, PRO == PRO_PLAIN>(a, pdl, stream);
+        if (nu == 4) return launch_rowtile_final<EPI, PRO, 4, PRO == PRO_PLAIN>(a, pdl, stream);
+    } else {
+        if (nu == 1) return launch_rowtile_final<EPI, PRO, 1, false>(a, pdl, stream);
+        if (nu == 2) return launch_rowtile_final<EPI, PRO, 2, false>(a, pdl, stream);
+        if (nu == 4) return launch_rowtile_final<EPI, PRO, 4, false>(a, pdl, stream);
+    }
     return NNIS_ERR_UNSUPPORTED;
 }
 

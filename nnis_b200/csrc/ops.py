@@ -283,10 +283,14 @@ GEMV_NORM_ROWS = int(os.environ.get("NNIS_GEMV_NORM_ROWS", "16"))
 GEMV_HEAD_ROWS = int(os.environ.get("NNIS_GEMV_HEAD_ROWS", "48"))
 
 
-def gemv_kind(m: int, n: int, k: int, epilogue: int = EPI_STORE, device=None, normed: bool = False) -> int:
+def gemv_kind(m: int, n: int, k: int, epilogue: int = EPI_STORE, device=None, normed: bool = False,
+              rows_kernel: bool = True) -> int:
     """Which decode projection kernel runs this product: 2 the one over tiles of rows, 1
-    the one whose CTAs hold all rows, 0 neither (the general kernels must run)."""
+    the one whose CTAs hold all rows, 0 neither (the general kernels must run).
+    ``rows_kernel=False``: as if the first did not exist."""
     sms = sm_count(device) if device is not None else 148
+    if not rows_kernel:
+        return int(_lib().nnis_gemv_units_takes(m, n, k, epilogue, 1 if normed else 0, sms))
     return int(_lib().nnis_gemv_kind(m, n, k, epilogue, 1 if normed else 0, sms))
 
 
@@ -304,12 +308,12 @@ def gemv_pays(m: int, n: int, k: int, epilogue: int = EPI_STORE, device=None, no
     return kind == 2 or (kind == 1 and m <= DECODE_GEMV_ROWS and (not normed or m <= GEMV_NORM_ROWS))
 
 
-def gemv_slices(m: int, n: int, k: int, device=None) -> int:
+def gemv_slices(m: int, n: int, k: int, device=None, rows_kernel: bool = True) -> int:
     """Launches that an ADD_F32 product of these sizes takes (slices of K, each
     adding its share in order); 0: not taken."""
     sms = sm_count(device) if device is not None else 148
-    if gemv_kind(m, n, k, EPI_ADD_F32, device) == 2:
-        return 1
+    if not rows_kernel:
+        return int(_lib().nnis_gemv_units_slices(m, n, k, sms))
     return int(_lib().nnis_gemv_slices(m, n, k, sms))
 
 
@@ -323,7 +327,8 @@ def gemv_bf16(w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, 
               v_cache: Optional[torch.Tensor] = None, heads: int = 0, kv_heads: int = 0,
               head_dim: int = 0, page_size: int = 0, logits: Optional[torch.Tensor] = None,
               scratch: Optional[torch.Tensor] = None, next_tokens: Optional[torch.Tensor] = None,
-              next_pos: Optional[torch.Tensor] = None, release_early: bool = False) -> None:
+              next_pos: Optional[torch.Tensor] = None, release_early: bool = False,
+              rows_kernel: bool = True) -> None:
     """A decode-step projection with its prologue and epilogue fused (at most 64
     rows).  The input is ``x`` (bfloat16 [m, k]) or ``hidden`` (float32 residual
     rows, normed with ``norm_weight``/``eps`` on the way in; ``rows`` picks them).
@@ -332,7 +337,8 @@ def gemv_bf16(w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, 
     workspace, ``logits`` optional, ``next_tokens``/``next_pos`` the decode state.
     ``release_early``: the kernel launched after this one may start together with it
     (only for a successor that reads, before its own wait, nothing that a kernel of
-    the step writes: attention_decode_tma)."""
+    the step writes: attention_decode_tma).  ``rows_kernel=False``: the kernel whose CTAs
+    hold all rows even where the one over tiles of rows applies (for comparisons)."""
     _cuda(w, bias, out, x, hidden, norm_weight, rows, token_pos, token_seq, page_table, cos, sin,
           k_cache, v_cache, logits, scratch, next_tokens, next_pos)
     n, k = w.shape
@@ -348,7 +354,7 @@ def gemv_bf16(w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, 
     else:
         _need(x is not None and x.dtype == torch.bfloat16 and x.shape[1] == k, "gemv: x bfloat16 [m, k]")
         m = x.shape[0] if m is None else m
-    _need(gemv_takes(m, n, k, epilogue, w.device, hidden is not None),
+    _need(gemv_kind(m, n, k, epilogue, w.device, hidden is not None, rows_kernel) > 0,
           f"gemv: shape m={m} n={n} k={k} is not taken")
     if bias is not None:
         _need(bias.dtype == torch.float32 and bias.numel() == n, "gemv: bias float32 [n]")
@@ -393,9 +399,10 @@ def gemv_bf16(w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, 
         _ptr(page_table), cols, _ptr(cos), _ptr(sin), _ptr(k_cache), _ptr(v_cache), heads, kv_heads,
         head_dim, page_size, _ptr(logits), ctypes.c_void_p(best_val), ctypes.c_void_p(best_idx),
         ctypes.c_void_p(ticket), _ptr(next_tokens), _ptr(next_pos), _ptr(status_word(w.device)),
-        sm_count(w.device), PDL | (2 if release_early and PDL and EARLY_RELEASE else 0), _stream()),
+        sm_count(w.device),
+        PDL | (2 if release_early and PDL and EARLY_RELEASE else 0) | (0 if rows_kernel else 4), _stream()),
         "gemv_bf16",
-        gemv_slices(m, n, k, w.device) if epilogue == EPI_ADD_F32 and hidden is None else 1)
+        gemv_slices(m, n, k, w.device, rows_kernel) if epilogue == EPI_ADD_F32 and hidden is None else 1)
 
 
 def argmax_scratch_ints(m: int, n: int, k: int, device) -> int:

@@ -343,40 +343,50 @@ def test_gemv_plain_epilogues_and_norm_prologue(m, n, k):
         if kind == 0:
             return
     else:
-        assert kind == (1 if m <= 16 else 2)
+        assert kind == 2
+    kernels = [True] if kind == 2 else []
+    if o.gemv_kind(m, n, k, o.EPI_STORE, DEV, rows_kernel=False):
+        kernels.append(False)
+    assert kernels and (len(kernels) == 2 or m > 48)
+    for rows_kernel in kernels:
+        _gemv_plain_and_norm(o, m, n, k, rows_kernel)
+
+
+def _gemv_plain_and_norm(o, m, n, k, rows_kernel):
     g = torch.Generator().manual_seed(m + n + k)
     w = (torch.randn(n, k, generator=g) / math.sqrt(k)).bfloat16()
     bias = torch.randn(n, generator=g)
     x = torch.randn(m, k, generator=g).bfloat16()
     want = P.linear(x, w, bias)
     out = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
-    o.gemv_bf16(w.to(DEV), bias.to(DEV), out, o.EPI_STORE, x=x.to(DEV))
+    o.gemv_bf16(w.to(DEV), bias.to(DEV), out, o.EPI_STORE, x=x.to(DEV), rows_kernel=rows_kernel)
     close(out, want, "bfloat16", "gemv store")
     out32 = torch.empty(m, n, device=DEV)
-    o.gemv_bf16(w.to(DEV), None, out32, o.EPI_STORE_F32, x=x.to(DEV))
+    o.gemv_bf16(w.to(DEV), None, out32, o.EPI_STORE_F32, x=x.to(DEV), rows_kernel=rows_kernel)
     close(out32, P.linear(x, w), "float32", "gemv store f32")
     base = torch.randn(m, n, generator=g)
     acc = base.to(DEV).clone()
-    o.gemv_bf16(w.to(DEV), bias.to(DEV), acc, o.EPI_ADD_F32, x=x.to(DEV))
+    o.gemv_bf16(w.to(DEV), bias.to(DEV), acc, o.EPI_ADD_F32, x=x.to(DEV), rows_kernel=rows_kernel)
     close(acc, base.double() + want, "float32", "gemv add")
     # norm prologue with gathered rows
-    if not o.gemv_takes(m, n, k, o.EPI_STORE_F32, DEV, True):
-        # with the normalised rows beside the weights only one CTA fits an SM
-        assert (k == 1536 and m > 64) or (n == 3072 and m > 64)
+    if not o.gemv_kind(m, n, k, o.EPI_STORE_F32, DEV, True, rows_kernel):
+        # with the normalised rows beside the weights only one CTA fits an SM, or (the
+        # kernel whose CTAs hold all rows) x and the weight stages do not fit together
+        assert m > 48
         return
     hidden = torch.randn(m + 5, k, generator=g) * 2
     nw = 1 + 0.1 * torch.randn(k, generator=g)
     rows = torch.randperm(m + 5, generator=g)[:m].to(torch.int32)
     # the inputs as drawn, rounding ties and all, held to the bound of a bfloat16 value ...
     o.gemv_bf16(w.to(DEV), None, out32, o.EPI_STORE_F32, hidden=hidden.to(DEV),
-                norm_weight=nw.to(DEV), eps=1e-5, rows=rows.to(DEV))
+                norm_weight=nw.to(DEV), eps=1e-5, rows=rows.to(DEV), rows_kernel=rows_kernel)
     close(out32, P.linear(P.rms_norm(hidden[rows.long()], nw, 1e-5).bfloat16(), w), "bfloat16",
           "gemv norm prologue, inputs as drawn")
     # ... and, with the few values moved whose rounding is not decided, to the float32 bound
     hidden = away_from_bf16_ties(hidden, nw, 1e-5)
     normed = P.rms_norm(hidden[rows.long()], nw, 1e-5).bfloat16()
     o.gemv_bf16(w.to(DEV), None, out32, o.EPI_STORE_F32, hidden=hidden.to(DEV),
-                norm_weight=nw.to(DEV), eps=1e-5, rows=rows.to(DEV))
+                norm_weight=nw.to(DEV), eps=1e-5, rows=rows.to(DEV), rows_kernel=rows_kernel)
     close(out32, P.linear(normed, w), "float32", "gemv norm prologue")
 
 
@@ -445,22 +455,28 @@ def test_gemv_gated_epilogue(m, k, inter):
     bias = torch.randn(2 * inter, generator=g)
     x = torch.randn(m, k, generator=g).bfloat16()
     y = P.linear(x, w, bias)
-    out = torch.empty(m, inter, dtype=torch.bfloat16, device=DEV)
-    o.gemv_bf16(w.to(DEV), bias.to(DEV), out, o.EPI_GATED, x=x.to(DEV))
-    close(out, P.swiglu(y[:, :inter], y[:, inter:]), "bfloat16", "gemv gated")
+    for rows_kernel in (True, False):  # both kernels where both take the shape
+        if not o.gemv_kind(m, 2 * inter, k, o.EPI_GATED, DEV, rows_kernel=rows_kernel):
+            continue
+        out = torch.empty(m, inter, dtype=torch.bfloat16, device=DEV)
+        o.gemv_bf16(w.to(DEV), bias.to(DEV), out, o.EPI_GATED, x=x.to(DEV), rows_kernel=rows_kernel)
+        close(out, P.swiglu(y[:, :inter], y[:, inter:]), "bfloat16", "gemv gated")
 
 
 @pytest.mark.parametrize("nq,nkv,d,rotate", [(6, 2, 16, True), (3, 1, 48, True), (4, 4, 64, False),
                                              (2, 0, 32, True), (9, 3, 64, True)])
 @pytest.mark.parametrize("copies", [1, 7, 20])
-def test_gemv_qkv_epilogue_rotates_and_stores(nq, nkv, d, rotate, copies):
+@pytest.mark.parametrize("rows_kernel", [True, False])
+def test_gemv_qkv_epilogue_rotates_and_stores(nq, nkv, d, rotate, copies, rows_kernel):
     """Five rows (one of them padding), or several times these rows with a cache of their
     own each: more than a tile of rows goes to the kernel over tiles of rows."""
     o = ops()
     g = torch.Generator().manual_seed(nq * d)
     m, k, page = 5 * copies, 48, 64
     n = (nq + 2 * nkv) * d
-    assert o.gemv_kind(m, n, k, o.EPI_QKV, DEV) == (1 if m <= 16 else 2)
+    assert o.gemv_kind(m, n, k, o.EPI_QKV, DEV) == 2
+    if not rows_kernel and m > 64:
+        return  # the kernel whose CTAs hold all rows takes 64
     w = (torch.randn(n, k, generator=g) / math.sqrt(k)).bfloat16()
     bias = torch.randn(n, generator=g)
     x = torch.randn(m, k, generator=g).bfloat16()
@@ -476,7 +492,7 @@ def test_gemv_qkv_epilogue_rotates_and_stores(nq, nkv, d, rotate, copies):
                 token_seq=seq.to(DEV), page_table=table.to(DEV) if nkv else None,
                 cos=cos.float().to(DEV) if rotate else None, sin=sin.float().to(DEV) if rotate else None,
                 k_cache=kc if nkv else None, v_cache=vc if nkv else None, heads=nq, kv_heads=nkv,
-                head_dim=d, page_size=page)
+                head_dim=d, page_size=page, rows_kernel=rows_kernel)
     y = P.linear(x, w, bias).bfloat16().double()
     for i in range(m):
         p = int(pos[i])
@@ -505,6 +521,7 @@ def test_gemv_refuses_what_it_does_not_take():
     # (and has no picking epilogue)
     assert not o.gemv_takes(80, 49152, 576) and not o.gemv_takes(80, 64, 64, o.EPI_ARGMAX)
     assert o.gemv_kind(64, 49152, 576) == 1 and o.gemv_kind(17, 64, 64, o.EPI_ARGMAX) == 1
+    assert o.gemv_kind(8, 960, 576) == 2 and o.gemv_kind(8, 960, 576, rows_kernel=False) == 1
     with pytest.raises(o.KernelError, match="not taken"):
         o.gemv_bf16(torch.zeros(68, 64, dtype=torch.bfloat16, device=DEV), None,
                     torch.zeros(2, 68, dtype=torch.bfloat16, device=DEV), o.EPI_STORE,
