@@ -61,6 +61,7 @@ class KVView:
     v: torch.Tensor
     page_size: int
     window: int
+    ahead: int = 0  # elements from k (and v) to those of the group's layer that runs next; 0: none
 
 
 @dataclass
@@ -120,7 +121,9 @@ class CacheManager:
             if isinstance(r, KVRequest):
                 gi, j = group_of[i]
                 g = self.groups[gi]
-                self._views.append(KVView(gi, g.k[j], g.v[j], PAGE_SIZE, g.window))
+                nxt = (j + 1) % len(g.entries)  # (after the last layer: the first, in the next step)
+                self._views.append(KVView(gi, g.k[j], g.v[j], PAGE_SIZE, g.window,
+                                          (nxt - j) * g.k[0].numel()))
             elif isinstance(r, StateRequest):
                 t = torch.zeros((max_slots, *r.shape), dtype=r.dtype, device=self.device)
                 self._states.append(t)

@@ -59,6 +59,11 @@ __device__ __forceinline__ int tile_off(int row, int chunk) {
     return (chunk >> 3) * (kClPage * 64) + row * 64 + (((chunk & 7) ^ (row & 7)) << 3);
 }
 
+// asks `bytes` (a multiple of 16) at a 16-byte aligned address into L2; nothing waits for it
+__device__ __forceinline__ void l2_prefetch(const void* p, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
 // counts an arrival; orders this CTA's earlier writes before it and its later reads after it
 __device__ __forceinline__ unsigned ticket_take(unsigned* ticket) {
     unsigned old;
@@ -75,7 +80,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
                        const int* __restrict__ page_table, int table_cols, bf16* __restrict__ out,
                        float* __restrict__ partial, unsigned* __restrict__ tickets, int nq, int nkv,
                        int window, float scale, int n_splits, int head_tiles, int per, int* status,
-                       unsigned long long* trace) {
+                       long long ahead, unsigned long long* trace) {
     trace_mark(trace, 0);
     constexpr int CH = D / 8;    // 16-byte chunks per row
     constexpr int NT = D / 8;    // n-tiles of the output
@@ -289,6 +294,13 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
     __syncthreads();  // everyone is done with the tiles: reuse them for the merge
     trace_mark(trace, 4);
     trace_mark(trace, 5);
+    // The same pages of the cache that is read next (`ahead` elements on: the next layer
+    // of the group) are asked into L2 now: its kernel starts some ten microseconds on.
+    if (ahead != 0 && tid < count) {
+        const size_t row0 = (size_t)(ids[begin - p0 + tid] * nkv + hk) * kClPage;
+        l2_prefetch(k_cache + ahead + row0 * D, TILE * (uint32_t)sizeof(bf16));
+        l2_prefetch(v_cache + ahead + row0 * D, TILE * (uint32_t)sizeof(bf16));
+    }
 
     // ---- merge the four warps: (m, l) through sm_ml, outputs through the tiles ----
     float* o_s = reinterpret_cast<float*>(tiles);                  // [warps, 16, D] float32
@@ -469,7 +481,7 @@ static int launch_tma(dim3 grid, int per, bool pdl, cudaStream_t stream, const C
                       const CUtensorMap& mv, const bf16* k_cache, const bf16* v_cache, const bf16* q,
                       int q_stride, const int* pos, const int* seq, const int* table, int cols,
                       bf16* out, float* partial, unsigned* tickets, int nq, int nkv, int window,
-                      float scale, int head_tiles, int* status) {
+                      float scale, int head_tiles, int* status, long long ahead) {
     const size_t smem = tma_smem_bytes<D>(per);
     auto kernel = attn_decode_tma_kernel<D>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -486,7 +498,7 @@ static int launch_tma(dim3 grid, int per, bool pdl, cudaStream_t stream, const C
     cfg.numAttrs = pdl ? 1 : 0;
     e = cudaLaunchKernelEx(&cfg, kernel, mk, mv, k_cache, v_cache, q, q_stride, pos, seq, table, cols,
                            out, partial, tickets, nq, nkv, window, scale, (int)grid.z, head_tiles, per,
-                           status, trace_slot("attention decode (tma)"));
+                           status, ahead, trace_slot("attention decode (tma)"));
     return e == cudaSuccess ? NNIS_OK : (int)e;
 }
 
@@ -524,14 +536,17 @@ NNIS_API int nnis_attention_decode_tma_ctas_per_sm(int d, int per) {
 // nnis_attention_decode_mma: with n_splits > 1, `partial` (n_tokens * nq * n_splits *
 // (d + 2) floats) and `tickets` (n_tokens * nkv * ceil(group / 16) counters, zero before
 // the first launch; the kernel leaves them zero).  `cache_rows`: pages x kv heads x 64,
-// the rows of the cache seen as a matrix of head_dim columns.
+// the rows of the cache seen as a matrix of head_dim columns.  `ahead`: elements from these
+// caches to the ones that are read next (the next layer's), whose same pages this kernel
+// asks into L2; 0: none.
 NNIS_API int nnis_attention_decode_tma(const void* q, int q_stride, const void* k_cache,
                                        const void* v_cache, long long cache_rows,
                                        const int* token_pos, const int* token_seq,
                                        const int* page_table, int table_cols, void* out,
                                        float* partial, unsigned* tickets, int n_tokens, int nq,
                                        int nkv, int d, int page_size, int window, float scale,
-                                       int n_splits, int* status, int pdl, cudaStream_t stream) {
+                                       int n_splits, long long ahead, int* status, int pdl,
+                                       cudaStream_t stream) {
     using namespace nnis;
     if (n_tokens <= 0 || nq <= 0 || nkv <= 0 || nq % nkv || table_cols <= 0 || n_splits <= 0 ||
         window < 0 || cache_rows <= 0)
@@ -554,9 +569,9 @@ NNIS_API int nnis_attention_decode_tma(const void* q, int q_stride, const void* 
         return launch_tma<64>(grid, per, pdl != 0, stream, mk, mv, (const bf16*)k_cache,
                               (const bf16*)v_cache, (const bf16*)q, q_stride, token_pos, token_seq,
                               page_table, table_cols, (bf16*)out, partial, tickets, nq, nkv, window,
-                              scale, head_tiles, status);
+                              scale, head_tiles, status, ahead);
     return launch_tma<128>(grid, per, pdl != 0, stream, mk, mv, (const bf16*)k_cache,
                            (const bf16*)v_cache, (const bf16*)q, q_stride, token_pos, token_seq,
                            page_table, table_cols, (bf16*)out, partial, tickets, nq, nkv, window, scale,
-                           head_tiles, status);
+                           head_tiles, status, ahead);
 }

@@ -446,6 +446,9 @@ def attention_decode_takes(head_dim: int) -> bool:
     return head_dim % 16 == 0 and 16 <= head_dim <= 256
 
 
+# Whether the decode attention kernel for few sequences asks the same pages of the layer that
+# runs next into L2 when it is through with its own (batch 8 of the 135M shape: +2 %).
+KV_PREFETCH = os.environ.get("NNIS_KV_PREFETCH", "1") == "1"
 TMA_ATTENTION = 0 if os.environ.get("NNIS_TMA_ATTENTION", "1") == "0" else 1
 _tma_ctas_per_sm: dict = {}
 
@@ -481,10 +484,11 @@ def attention_decode_tma(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, 
                          token_pos: torch.Tensor, token_seq: torch.Tensor, page_table: torch.Tensor,
                          out: torch.Tensor, heads: int, kv_heads: int, head_dim: int, window: int,
                          scale: float, n_splits: int, partial: Optional[torch.Tensor] = None,
-                         tickets: Optional[torch.Tensor] = None) -> None:
+                         tickets: Optional[torch.Tensor] = None, ahead: int = 0) -> None:
     """Decode attention with every page of a slice in shared memory at once (``n_splits``
     from ``attention_decode_tma_plan``): pages by TMA, a warp per page.  Scratch as for
-    ``attention_decode_mma``."""
+    ``attention_decode_mma``.  ``ahead``: elements from these caches to the ones read next
+    (the next layer's), whose same pages the kernel asks into L2; 0: none."""
     _cuda(k_cache, v_cache, token_pos, token_seq, page_table, out, partial, tickets)
     _need(q.is_cuda and q.dtype == torch.bfloat16 == k_cache.dtype == out.dtype,
           "attention_decode_tma: bfloat16 tensors")
@@ -508,7 +512,8 @@ def attention_decode_tma(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, 
         _ptr(q), q_stride, _ptr(k_cache), _ptr(v_cache), ctypes.c_longlong(pages * nkv * page_size),
         _ptr(token_pos), _ptr(token_seq), _ptr(page_table), page_table.shape[1], _ptr(out),
         _ptr(partial), _ptr(tickets), n, heads, kv_heads, head_dim, page_size, window,
-        ctypes.c_float(scale), n_splits, _ptr(status_word(out.device)), PDL, _stream()),
+        ctypes.c_float(scale), n_splits, ctypes.c_longlong(ahead), _ptr(status_word(out.device)), PDL,
+        _stream()),
         "attention_decode_tma")
 
 

@@ -219,7 +219,8 @@ class Attention(Part):
                 tickets = ws.zeros("attn_tickets", (ops.mma_ticket_count(n, nq, nkv),), torch.int32)
             ops.attention_decode_tma(q_buf, q_stride, cache.k, cache.v, ctx.token_pos, ctx.token_seq,
                                      table, attn, nq, nkv, d, self.window, self.scale, tma_splits,
-                                     partial, tickets)
+                                     partial, tickets,
+                                     ahead=getattr(cache, "ahead", 0) if ops.KV_PREFETCH else 0)
         elif mma_decode:
             tiles = -(-(nq // nkv) // 16)
             splits, stages = self._decode_shape(ctx, n * nkv * tiles, cache.page_size)
