@@ -11,7 +11,10 @@ the same range of contexts, as NNIS's own benchmarks take the median of five
 (crates/nnis-bench/src/lib.rs:362-428).  ``e2e`` is the same through the Python
 entry point with every step's tokens coming from and going back to the host, over
 256 steps whatever K is.  The line also carries a 2,048-token prefill, the decode
-step's HBM roofline, and decoding at batch 1 and 64.  Weights are random (seeded),
+step's HBM roofline, decoding at batch 1 and 64, and ``kernels``: per kernel of one
+more decode step, taken outside every timed region with the kernels' own readings of
+the GPU's timer, its launches and the microseconds from its last CTA getting past the
+wait for the kernel before to its end, summed over the launches.  Weights are random (seeded),
 token ids are uniform random: no checkpoint or dataset is read.
 """
 from __future__ import annotations
@@ -145,6 +148,24 @@ def write_timeline(path, title, names, rows, marks):
             f.write(f"# {name}: {count} launches, mean begin-to-end {dur / count:.0f} ns, "
                     f"mean last-wait-to-end {after / count:.0f} ns, sum of the latter {after / 1000:.0f} us\n")
     print(open(path).read()[-1800:])
+
+
+def kernel_times(names, rows):
+    """Per kernel of one traced step: launches, and microseconds from the moment its last
+    CTA got past the wait for the kernel before to its end (its link in the step's chain),
+    summed over the launches; and the step from its first CTA to its last."""
+    big = 1 << 62
+    out = {}
+    for name, r in zip(names, rows):
+        begin, end, last_wait = r[0], r[1], r[3]
+        start = last_wait if 0 < last_wait < big else begin
+        entry = out.setdefault(name, {"launches": 0, "us": 0.0})
+        entry["launches"] += 1
+        entry["us"] += (end - start) / 1000.0
+    for entry in out.values():
+        entry["us"] = round(entry["us"], 1)
+    out["step"] = {"launches": len(rows), "us": round((max(r[1] for r in rows) - min(r[0] for r in rows)) / 1000.0, 1)}
+    return out
 
 
 def prefill_timeline(engine, path, rng, vocab):
@@ -285,8 +306,10 @@ def main() -> int:
             windows.append((t0, clocks.mark()))
             return start.elapsed_time(end)
 
-        def decode_point(batch, steps, warmup):
-            """Device-timed decode: the contexts end at CONTEXT after the timed steps."""
+        def decode_point(batch, steps, warmup, traced=False):
+            """Device-timed decode: the contexts end at CONTEXT after the timed steps.
+            ``traced``: afterwards one more step with the kernels' own clock readings
+            (outside every timed region), summed per kernel."""
             begin = CONTEXT - steps - warmup
             slots = [engine.acquire_slot() for _ in range(batch)]
             fed = 0
@@ -310,7 +333,22 @@ def main() -> int:
                 regions.append(timed(dec.launch, steps))
                 launches = dec.launches_per_step * steps + (ops.launch_count() - before)
             ms = median(regions)
-            engine.cache.commit(slots, [CONTEXT] * batch)
+            kernels = None
+            if traced:
+                seen = GraphDecoder(engine, batch, CONTEXT)  # (its launches get slots of the trace at capture)
+                for r, s in enumerate(slots):
+                    seen.set_row(r, s, rng.randrange(vocab), begin)
+                buf = ops.trace_begin(4096)
+                seen.capture()  # the warm-up run takes slots as well; the captured launches the later half
+                names = ops.trace_end()
+                for _ in range(3):
+                    seen.launch()
+                torch.cuda.synchronize()
+                ops.trace_clear()
+                seen.launch()
+                torch.cuda.synchronize()
+                half = len(names) // 2
+                kernels = kernel_times(names[half:], buf[half:2 * half].cpu().tolist())
             for s in slots:
                 engine.release_slot(s)
             mean_context = CONTEXT - (steps + 1) / 2.0
@@ -318,7 +356,7 @@ def main() -> int:
             return {"tok_s": batch * steps / (ms * 1e-3), "ms_per_step": ms / steps,
                     "launches": launches, "bytes_per_step": step_bytes,
                     "gbs": step_bytes / (ms / steps * 1e-3) / 1e9,
-                    "spread": (max(regions) - min(regions)) / ms}
+                    "spread": (max(regions) - min(regions)) / ms, "kernels": kernels}
 
         if args.timeline:
             if args.batch == 0:
@@ -327,7 +365,7 @@ def main() -> int:
                 timeline(engine, args.batch, args.timeline, rng, vocab)
             clocks.stop()
             return 0
-        main_point = decode_point(args.batch, K, W)
+        main_point = decode_point(args.batch, K, W, traced=True)
 
         # -- prefill of 2,048 tokens ------------------------------------------------
         prompt = [rng.randrange(vocab) for _ in range(PROMPT)]
@@ -427,6 +465,7 @@ def main() -> int:
         "spread": main_point["spread"],
         "e2e": e2e,
         "gpu_launches": main_point["launches"],
+        "kernels": main_point["kernels"],
         "clocks": clocks.summary(windows),
     }
     try:  # where the numbers were taken (NNIS's benchmarks carry such a record too)
