@@ -193,7 +193,7 @@ def prefill_timeline(engine, path, rng, vocab):
     torch.cuda.synchronize()
     half = len(names) // 2
     write_timeline(path, f"one prompt step of {PROMPT} tokens", names[half:], buf[half:2 * half].cpu().tolist(),
-                   "none inside these kernels")
+                   "products: first operands arrived / all products complete")
 
 
 def timeline(engine, batch, path, rng, vocab):

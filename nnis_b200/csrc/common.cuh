@@ -94,6 +94,14 @@ __device__ __forceinline__ unsigned long long global_ns() {
     return t;
 }
 
+// the same from a thread that the caller picks (one per CTA)
+__device__ __forceinline__ void trace_mark_here(unsigned long long* slot, int word) {
+    if (slot) {
+        if (word & 1) atomicMax(slot + word, global_ns());
+        else atomicMin(slot + word, global_ns());
+    }
+}
+
 // even words: the earliest CTA; odd words: the latest
 __device__ __forceinline__ void trace_mark(unsigned long long* slot, int word) {
     if (slot && threadIdx.x == 0) {

@@ -177,6 +177,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     break;
                 }
                 tc_fence_after();
+                if (kb == 0) {  // the first operands have arrived
+                    trace_mark_here(g.trace, 4);
+                    trace_mark_here(g.trace, 5);
+                }
 #pragma unroll
                 for (int h = 0; h < KSUB; ++h) {
                     if (kb * KSUB + h >= k_slices) break;
@@ -226,6 +230,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
         }
         bool ok = mbar_wait(&acc_bar, 0);
+        if (warp == 2 && lane == 0) {  // the products are complete
+            trace_mark_here(g.trace, 6);
+            trace_mark_here(g.trace, 7);
+        }
         ok = __all_sync(0xffffffffu, ok) && !abort_flag;
         if (!ok) {
             abort_flag = 1;
