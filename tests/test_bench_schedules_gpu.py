@@ -127,3 +127,20 @@ def test_sixty_four_rows_of_unequal_context_decode_through_the_graph(chains):
         assert stages == 3  # the launch shape with three pages in flight, one wave of 576 CTAs
     check_rows(seqs, logits, ends, plain, "bfloat16", [0, 1, 2, 63], "64 rows")
     assert engine.cache.usage()["pages_held"] == [0]
+
+
+def test_eighty_rows_decode_through_the_graph():
+    """More rows than the kernel whose CTAs hold all rows takes (64): five tiles of rows in the
+    kernel over tiles of rows, and the head as norm, tcgen05 product and pick."""
+    engine, plain = build("bfloat16", 80)
+    from nnis_b200.csrc import ops
+    hidden, inter = CFG["hidden_size"], CFG["intermediate_size"]
+    for n, k, epi, normed in [((9 + 6) * 64, hidden, ops.EPI_QKV, True), (hidden, 9 * 64, ops.EPI_ADD_F32, False),
+                              (2 * inter, hidden, ops.EPI_GATED, True), (hidden, inter, ops.EPI_ADD_F32, False)]:
+        assert ops.gemv_kind(80, n, k, epi, engine.device, normed) == 2
+        assert ops.gemv_kind(80, n, k, epi, engine.device, normed, rows_kernel=False) == 0
+    rng = random.Random(80)
+    ends = [1500, 6 + STEPS, 1499] + [rng.randrange(STEPS + 1, 1501) for _ in range(76)] + [777]
+    seqs, logits, dec = decode_rows(engine, ends, rng)
+    check_rows(seqs, logits, ends, plain, "bfloat16", [0, 1, 2, 40, 79], "80 rows")
+    assert engine.cache.usage()["pages_held"] == [0]
