@@ -25,6 +25,8 @@
 //    shared memory per CTA are held down on purpose (__maxnreg__; with at most eight rows
 //    the second half of the tile of x is one row of zeros), so that this kernel's CTAs
 //    and those of the decode attention kernel (three to an SM) are resident together.
+#include <stdlib.h>
+
 #include "gemv_kernel.cuh"
 
 namespace nnis {
@@ -327,11 +329,15 @@ int gemv_rowtile_units(int M, int N, int K, int epilogue, int pro, int sm_count)
     const bool longk = pro == PRO_PLAIN && K > rowtile_direct_steps(false) * 16 * kRowtileWarps;
     const int sms = sm_count > 0 ? sm_count : 148;
     const int mtiles = (M + 15) / 16, units = N / 8;
-    // With one tile of rows: the fewest units per CTA that leave room on the SMs for the
-    // kernels before and after (CTAs for at most one and a half SMs' worth).  With more:
+    // With one tile of rows: few units per CTA, and CTAs for at most one and a half SMs'
+    // worth, which leaves room on the SMs for the kernels before and after.  With more:
     // as many units as tiles of rows keeps the number of CTAs near the number of units, and
     // the bytes of x that a CTA fetches after the wait below those of W.
-    for (int nu = mtiles == 1 ? 1 : mtiles == 2 ? 2 : 4; nu <= 4; nu *= 2) {
+    // (one tile of rows: two units a CTA from 64 units on measured as one unit at batch 8 of
+    // the 135M shape and 3 % better at batch 1: fewer CTAs in the way of the attention kernel's)
+    static const int min_units = getenv("NNIS_ROWTILE_MIN_UNITS") ? atoi(getenv("NNIS_ROWTILE_MIN_UNITS")) : 0;
+    const int first = mtiles >= 3 ? 4 : mtiles == 2 ? 2 : min_units > 0 ? min_units : units >= 64 ? 2 : 1;
+    for (int nu = first; nu <= 4; nu *= 2) {
         size_t smem = rowtile_smem(M, nu, K, pro);
         if (smem > 200 * 1024) continue;
         int fit = (int)((220 * 1024) / (smem + 1024));
