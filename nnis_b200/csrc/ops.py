@@ -449,6 +449,7 @@ def attention_decode_takes(head_dim: int) -> bool:
 # Whether the decode attention kernel for few sequences asks the same pages of the layer that
 # runs next into L2 when it is through with its own (batch 8 of the 135M shape: +2 %).
 KV_PREFETCH = os.environ.get("NNIS_KV_PREFETCH", "1") == "1"
+TMA_SLICE_PAGES = int(os.environ.get("NNIS_TMA_SLICE_PAGES", "0"))  # 0: chosen by the plan
 TMA_ATTENTION = 0 if os.environ.get("NNIS_TMA_ATTENTION", "1") == "0" else 1
 _tma_ctas_per_sm: dict = {}
 
@@ -461,23 +462,39 @@ def attention_decode_tma_max_pages(head_dim: int) -> int:
 def attention_decode_tma_plan(n: int, heads: int, kv_heads: int, head_dim: int, page_size: int,
                               table_cols: int, device, share: int = 1) -> int:
     """Into how many slices attention_decode_tma cuts ``table_cols`` pages for a step of ``n``
-    sequences, or 0 when the step is not for that kernel: it takes head sizes 64 and 128,
-    slices of four pages (more for page tables beyond 64 x 4 columns, up to what fits), and
+    sequences, or 0 when the step is not for that kernel: it takes head sizes 64 and 128 and
     only steps whose CTAs are all resident together (few sequences, or short contexts);
-    other steps stream their slices through the ring of attention_decode_mma.  ``share``:
-    steps that run side by side on the device."""
+    other steps stream their slices through the ring of attention_decode_mma.  Slices are of
+    four pages (more for page tables beyond 64 x 4 columns, up to what fits); when that makes
+    more CTAs than two per SM, of six pages if those CTAs are resident two to an SM: fewer
+    partial records and fewer CTAs that wait for room beside the projection's (batch 8 of the
+    135M shape: 0.637 -> 0.618 ms a step; at batch 1, where CTAs are few, four pages are
+    4 % ahead).  ``share``: steps that run side by side on the device.
+    ``NNIS_TMA_SLICE_PAGES`` fixes the pages of a slice."""
     if not TMA_ATTENTION or head_dim not in (64, 128) or page_size != 64 or n > 65535:
         return 0
-    splits = min(64, -(-table_cols // 4))
-    per = -(-table_cols // splits)
-    if per > attention_decode_tma_max_pages(head_dim):
-        return 0
-    key = (head_dim, per, torch.device(device).index or 0)
-    if key not in _tma_ctas_per_sm:
-        _tma_ctas_per_sm[key] = int(_lib().nnis_attention_decode_tma_ctas_per_sm(head_dim, per))
-    ctas = n * kv_heads * (-(-(heads // kv_heads) // 16)) * splits
-    resident = _tma_ctas_per_sm[key] * sm_count(device) // max(1, share)
-    return splits if 0 < ctas <= resident else 0
+    groups = n * kv_heads * (-(-(heads // kv_heads) // 16))
+    sms = sm_count(device) // max(1, share)
+
+    def plan(pages: int):
+        splits = min(64, -(-table_cols // pages))
+        per = -(-table_cols // splits)
+        if per > attention_decode_tma_max_pages(head_dim):
+            return 0, 0, 0
+        key = (head_dim, per, torch.device(device).index or 0)
+        if key not in _tma_ctas_per_sm:
+            _tma_ctas_per_sm[key] = int(_lib().nnis_attention_decode_tma_ctas_per_sm(head_dim, per))
+        return splits, groups * splits, _tma_ctas_per_sm[key]
+
+    if TMA_SLICE_PAGES:
+        splits, ctas, fit = plan(TMA_SLICE_PAGES)
+        return splits if 0 < ctas <= fit * sms else 0
+    splits, ctas, fit = plan(4)
+    if ctas > 2 * sms:
+        wide, wide_ctas, wide_fit = plan(6)
+        if 0 < wide_ctas <= min(wide_fit, 2) * sms:
+            return wide
+    return splits if 0 < ctas <= fit * sms else 0
 
 
 def attention_decode_tma(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor,

@@ -1,7 +1,7 @@
 """The schedules that the benchmark times, held to the plain implementation logit by
 logit: decoding through ``GraphDecoder`` (the captured step with programmatic dependent
 launches, the fused head and pick, the tensor-core decode attention with its slices)
-at contexts that end at 4,096, with 8 rows (16 slices of 256 keys) and with 64 rows of
+at contexts that end at 4,096, with 8 rows (11 slices of up to 384 keys) and with 64 rows of
 unequal contexts (few slices, the launch shape with three pages in flight).
 
 The model is narrow (width 128, two layers) so that the float64 oracle stays cheap,
@@ -102,10 +102,12 @@ def test_eight_rows_decode_to_context_4096_through_the_graph(dtype, chains):
     engine, plain = build(dtype, 8)
     ends = [4096, 4090, 3000, 2049, 300, 64 + STEPS, 70, 4096]
     seqs, logits, dec = decode_rows(engine, ends, random.Random(8), chains)
-    if dtype == "bfloat16":  # 16 slices of 256 keys, every page of a slice in shared memory at once
+    if dtype == "bfloat16":  # 11 slices of up to 384 keys, every page of a slice in shared memory at once
         from nnis_b200.csrc import ops
         rows = dec.chains[0][1] - dec.chains[0][0]
-        assert ops.attention_decode_tma_plan(rows, 9, 3, 64, 64, dec.cols, engine.device, len(dec.chains)) == 16
+        assert ops.attention_decode_tma_plan(rows, 9, 3, 64, 64, dec.cols, engine.device, len(dec.chains)) == 11
+        # (with few enough sequences: 16 slices of 256 keys)
+        assert ops.attention_decode_tma_plan(2, 9, 3, 64, 64, dec.cols, engine.device) == 16
     check_rows(seqs, logits, ends, plain, dtype, [0, 3, 5, 7], f"8 rows {dtype}")
     assert engine.cache.usage()["pages_held"] == [0]
 
