@@ -36,11 +36,12 @@ constexpr int kRowtileWarps = 8;
 __host__ __device__ constexpr int rowtile_direct_steps(bool longk) { return longk ? 12 : 6; }
 
 // Registers per thread (see above), and the CTAs that fit an SM by them.
-__host__ __device__ constexpr int rowtile_registers(int pro, bool longk) {
-    return pro == PRO_NORM ? 80 : longk ? 128 : 104;
+__host__ __device__ constexpr int rowtile_registers(int epi, int pro, bool longk) {
+    // (the QKV epilogue holds positions, pages and angles: at 80 registers it spills)
+    return pro == PRO_NORM ? (epi == EPI_QKV ? 88 : 80) : longk ? 128 : 104;
 }
-__host__ __device__ constexpr int rowtile_ctas_per_sm(int pro, bool longk) {
-    return 65536 / (kRowtileWarps * 32 * rowtile_registers(pro, longk));
+__host__ __device__ constexpr int rowtile_ctas_per_sm(int epi, int pro, bool longk) {
+    return 65536 / (kRowtileWarps * 32 * rowtile_registers(epi, pro, longk));
 }
 
 // Rows of the normalised x in shared memory: a tile, or eight rows and one of zeros.
@@ -55,7 +56,7 @@ __host__ __device__ constexpr int rowtile_w_stride(int K, int pro) {
 }
 
 template <int EPI, int PRO, int NU, bool LONGK>
-__global__ void __maxnreg__(rowtile_registers(PRO, LONGK))
+__global__ void __maxnreg__(rowtile_registers(EPI, PRO, LONGK))
 gemv_rowtile_kernel(GemvArgs a) {
     constexpr int WARPS = kRowtileWarps;
     constexpr bool kDirect = PRO == PRO_PLAIN;
@@ -341,7 +342,7 @@ int gemv_rowtile_units(int M, int N, int K, int epilogue, int pro, int sm_count)
         size_t smem = rowtile_smem(M, nu, K, pro);
         if (smem > 200 * 1024) continue;
         int fit = (int)((220 * 1024) / (smem + 1024));
-        if (fit > rowtile_ctas_per_sm(pro, longk)) fit = rowtile_ctas_per_sm(pro, longk);
+        if (fit > rowtile_ctas_per_sm(epilogue, pro, longk)) fit = rowtile_ctas_per_sm(epilogue, pro, longk);
         long ctas = (long)mtiles * ((units + nu - 1) / nu);
         long room = mtiles == 1 ? (long)sms * 3 / 2 : (long)sms * fit;
         if (fit >= 1 && ctas <= room && ctas <= (long)sms * fit) return nu;
