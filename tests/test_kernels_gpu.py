@@ -685,6 +685,16 @@ def test_attention_decode_fed_by_tma(nq, nkv, d, window):
     with pytest.raises(o.KernelError, match="slices of at most"):
         o.attention_decode_tma(qd, nq * d, kc, vc, pos.to(DEV), seq.to(DEV), case.table.to(DEV), out,
                                nq, nkv, d, window, 1.0 / math.sqrt(d), 1)  # 16 pages in one slice
+    # the same while it asks the pages of a cache that lies further on (or back) into L2: the
+    # layer of its group that runs next; nothing of the result may change
+    both_k, both_v = torch.stack([kc, kc]), torch.stack([vc, vc])
+    for layer, ahead in ((0, kc.numel()), (1, -kc.numel())):
+        out = torch.full((n, nq * d), 5.0, dtype=torch.bfloat16, device=DEV)
+        partial = torch.full((n * nq * 4 * (d + 2),), float("nan"), device=DEV)
+        o.attention_decode_tma(qd, nq * d, both_k[layer], both_v[layer], pos.to(DEV), seq.to(DEV),
+                               case.table.to(DEV), out, nq, nkv, d, window, 1.0 / math.sqrt(d), 4, partial,
+                               tickets, ahead=ahead)
+        close(out[:n - 1], want, "bfloat16", f"decode attention by TMA, asking pages {ahead} elements on")
     # one slice: a context of up to four pages needs no scratch
     short = PagedCase([200, 3], [1, 1], nq, nkv, d, "bfloat16", seed=5)
     short.fill_cache()
@@ -707,6 +717,36 @@ def test_attention_decode_fed_by_tma(nq, nkv, d, window):
     assert o.attention_decode_tma_plan(4000, nq, nkv, d, 64, 64, DEV) == 0
     assert o.attention_decode_tma_plan(2, nq, nkv, d, 64, 1000, DEV) == 0  # slices would be too long
     assert o.attention_decode_tma_plan(2, nq, nkv, 48, 64, 8, DEV) == 0
+
+
+def test_attention_decode_fed_by_tma_with_more_ctas_than_two_per_sm():
+    """Many sequences: more CTAs than two per SM take the build of the kernel that leaves
+    room for three (fewer registers); the same results."""
+    o = ops()
+    nq, nkv, d = 9, 3, 64
+    rng = np.random.default_rng(3)
+    lengths = [int(x) for x in rng.integers(1, 1000, size=40)] + [1000, 64, 65]
+    case = PagedCase(lengths, [1] * len(lengths), nq, nkv, d, "bfloat16", seed=11)
+    case.fill_cache()
+    for s, L in enumerate(lengths):
+        pg = int(case.table[s, (L - 1) // 64])
+        case.k_cache[pg, :, (L - 1) % 64] = case.k[s][L - 1]
+        case.v_cache[pg, :, (L - 1) % 64] = case.v[s][L - 1]
+    pos, seq, q, _, _ = case.packed()
+    n = pos.numel()
+    splits = 4
+    assert n * nkv * splits > 2 * o.sm_count(DEV)
+    qd = q.reshape(n, -1).bfloat16().to(DEV)
+    kc, vc = case.k_cache.bfloat16().to(DEV), case.v_cache.bfloat16().to(DEV)
+    want = torch.cat([P.causal_attention(case.q[s], case.k[s], case.v[s].bfloat16().float(), 0)[L - 1:].reshape(1, -1)
+                      for s, L in enumerate(lengths)])
+    tickets = torch.zeros(o.mma_ticket_count(n, nq, nkv), dtype=torch.int32, device=DEV)
+    out = torch.full((n, nq * d), 5.0, dtype=torch.bfloat16, device=DEV)
+    partial = torch.full((n * nq * splits * (d + 2),), float("nan"), device=DEV)
+    o.attention_decode_tma(qd, nq * d, kc, vc, pos.to(DEV), seq.to(DEV), case.table.to(DEV), out,
+                           nq, nkv, d, 0, 1.0 / math.sqrt(d), splits, partial, tickets)
+    close(out, want, "bfloat16", "decode attention by TMA, 43 sequences")
+    assert int(tickets.abs().sum()) == 0
 
 
 def test_decode_attention_by_tma_finds_one_far_key():
