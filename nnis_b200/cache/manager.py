@@ -103,6 +103,9 @@ class CacheManager:
         # (taken, given back, truncated): a copy of a table kept elsewhere is good only
         # for the version it was made at
         self.versions: List[int] = [0] * max_slots
+        # counts every change of any page table, growth included: while it stands still a
+        # copy of the tables of the same slots needs no look
+        self.epoch = 0
         self.owners: List[int] = [0] * max_slots  # how many sequences have held each slot
         self.groups: List[_KVGroup] = []
         self._views: List[Optional[Union[KVView, StateView]]] = []
@@ -142,6 +145,7 @@ class CacheManager:
         slot = self.slots.take()
         self.lengths[slot] = 0
         self.versions[slot] += 1
+        self.epoch += 1
         self.owners[slot] += 1
         for g in self.groups:
             g.tables[slot] = []
@@ -158,6 +162,7 @@ class CacheManager:
                     g.pool.give(page)
         self.lengths[slot] = 0
         self.versions[slot] += 1
+        self.epoch += 1
         self.slots.give(slot)
 
     def length(self, slot: int) -> int:
@@ -188,7 +193,10 @@ class CacheManager:
         for slot, n in zip(slots, new_lengths):
             for g in self.groups:
                 table = g.tables[slot]
-                table.extend(g.pool.take_many(-(-n // PAGE_SIZE) - len(table)))
+                more = -(-n // PAGE_SIZE) - len(table)
+                if more > 0:
+                    table.extend(g.pool.take_many(more))
+                    self.epoch += 1
 
     def commit(self, slots: Sequence[int], new_lengths: Sequence[int]) -> None:
         """The step has been issued: lengths advance, windowed groups give back
@@ -202,6 +210,7 @@ class CacheManager:
                         if table[i] >= 0:
                             g.pool.give(table[i])
                             table[i] = -1
+                            self.epoch += 1
 
     def truncate(self, slot: int, length: int) -> None:
         """Forget the positions from ``length`` on (NNIS: crates/nnis-rt/src/kv_cache.rs:181-183):
@@ -237,6 +246,7 @@ class CacheManager:
             del table[keep:]
         self.lengths[slot] = length
         self.versions[slot] += 1
+        self.epoch += 1
 
     def snapshot(self, slot: int) -> CacheSnapshot:
         """What is needed to bring this sequence back to where it is now after further

@@ -84,6 +84,9 @@ class GraphDecoder:
         # the list in place and later pages may differ), how many of its pages, how
         # many dropped in front; None: unknown (rows that were set one by one on the device)
         self._mirror = None
+        # the cache's epoch and the slots at the last look at the tables (see upload)
+        self._tables_seen = None
+        self._windowed = any(g.window > 0 for g in engine.cache.groups)
         self.logits = torch.empty((rows, engine.spec.vocab_size), dtype=torch.float32, device=dev) \
             if want_logits else None
         self.picked = torch.zeros(rows, dtype=torch.int32, device=dev)
@@ -215,12 +218,19 @@ class GraphDecoder:
             st[:] = -1
             self._mirror = [[None] * rows for _ in self.tables]
         st[0:n] = tokens
-        st[n:rows] = 0
         st[rows:rows + n] = positions
-        st[rows + n:2 * rows] = -1
-        st[2 * rows:2 * rows + n] = slots
-        st[2 * rows + n:3 * rows] = 0
-        for g, group in enumerate(cache.groups):
+        same_rows = not fresh and self._tables_seen is not None and self._tables_seen[1] == tuple(slots)
+        if not same_rows:  # (else the padding rows and the slots stand as they were written)
+            st[n:rows] = 0
+            st[rows + n:2 * rows] = -1
+            st[2 * rows:2 * rows + n] = slots
+            st[2 * rows + n:3 * rows] = 0
+        # (no page table has changed since these slots' tables were last looked at, and no
+        # windowed group drops pages by length alone: nothing to look at)
+        seen = (cache.epoch, tuple(slots))
+        groups = () if not fresh and seen == self._tables_seen and not self._windowed else enumerate(cache.groups)
+        self._tables_seen = seen
+        for g, group in groups:
             base = 3 * rows + g * rows * cols
             mirror = self._mirror[g]
             for r, slot in enumerate(slots):
