@@ -29,6 +29,7 @@ namespace nnis {
 constexpr int kBM = 128;
 constexpr int kBK = 64;          // 64 bfloat16 = one 128-byte swizzle row
 constexpr int kUmmaK = 16;
+constexpr int kMaxKSplits = 4;   // CTAs that may share a tile of the adding product
 
 enum { GEMM_STORE = 0, GEMM_STORE_F32 = 1, GEMM_ADD_F32 = 2, GEMM_GATED = 3, GEMM_QKV = 4 };
 
@@ -38,6 +39,13 @@ struct GemmArgs {
     int M, N, K;
     int* status;
     int out_by_tma;  // the output's rows start on 16-byte boundaries: tiles leave through shared memory
+    // GEMM_ADD_F32 with few tiles and a long K: CTA (x, y, z) takes the z-th run of k-blocks,
+    // leaves its sums in `split_scratch` ([tile, split, 128 rows, BN] float32) and takes a
+    // ticket; the CTA of a tile that arrives last adds the splits' sums in the order of
+    // the splits (deterministic) and adds the result into the output
+    int k_splits;
+    float* split_scratch;
+    unsigned* split_tickets;  // one per tile, zero between launches
     // GEMM_QKV: rotate-half RoPE of q and k heads at each row's position, q to
     // `out` [M, nq * d], k and v into the paged cache (one head per column tile)
     const int* token_pos;
@@ -68,7 +76,9 @@ __host__ __device__ constexpr int gemm_threads(int bn, int stages, int mode, int
 // A by a gate tile and by the matching up tile into two accumulators and writes
 // bf16(silu(gate) * up) to out [M, I].  MODE GEMM_QKV: a tile holds whole heads
 // (BN = 128: two heads of 64 or one of 128).
-template <int BN, int STAGES, int MODE, int KSUB>
+// SPLIT: K cut among the CTAs of a tile (GemmArgs::k_splits), a build of its own so that
+// the others carry none of it.
+template <int BN, int STAGES, int MODE, int KSUB, bool SPLIT = false>
 __global__ void __launch_bounds__(gemm_threads(BN, STAGES, MODE, KSUB), gemm_ctas_per_sm(BN, STAGES, MODE, KSUB))
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                const __grid_constant__ CUtensorMap map_out, GemmArgs g) {
@@ -87,14 +97,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     constexpr uint32_t kStageA = KSUB * kBytesA, kStageB = KSUB * NB * kBytesB;
     unsigned char* tile_a = base;
     unsigned char* tile_b = base + (size_t)STAGES * kStageA;
-    __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar, staged_bar;
+    __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar, staged_bar, split_bar, split_done;
     __shared__ uint32_t tmem_base_s;
+    __shared__ int split_last;
     __shared__ volatile int abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.y * kBM, n0 = blockIdx.x * BN;
     const int k_slices = (g.K + kBK - 1) / kBK;
-    const int k_blocks = (k_slices + KSUB - 1) / KSUB;
+    const int k_blocks_all = (k_slices + KSUB - 1) / KSUB;
+    // this CTA's run of k-blocks (all of them without a split of K)
+    const int kb_per = SPLIT ? (k_blocks_all + g.k_splits - 1) / g.k_splits : k_blocks_all;
+    const int kb_first = SPLIT ? (int)blockIdx.z * kb_per : 0;
+    const int k_blocks = SPLIT ? max(0, min(kb_per, k_blocks_all - kb_first)) : k_blocks_all;
     const int inter = g.N >> 1;  // GEMM_GATED: columns of the output
 
     if (threadIdx.x == 32) {
@@ -109,6 +124,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         mbar_init(&acc_bar, 1);
         mbar_init(&staged_bar, kEpiWarps);
+        mbar_init(&split_bar, kEpiWarps);
+        mbar_init(&split_done, 1);
         abort_flag = 0;
         mbar_fence_init();
     }
@@ -128,7 +145,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         mbar_expect_tx(&full_bar[s], loads_a ? kStageA : kStageB);
 #pragma unroll
         for (int h = 0; h < KSUB; ++h) {
-            const int k0 = (kb * KSUB + h) * kBK;
+            const int k0 = ((kb_first + kb) * KSUB + h) * kBK;
             if (loads_a) {
                 tma_load_2d(tile_a + (size_t)s * kStageA + (size_t)h * kBytesA, &map_a, k0, m0,
                             &full_bar[s]);
@@ -183,7 +200,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
 #pragma unroll
                 for (int h = 0; h < KSUB; ++h) {
-                    if (kb * KSUB + h >= k_slices) break;
+                    if ((kb_first + kb) * KSUB + h >= k_slices) break;
                     const uint64_t da = desc_advance(desc_a0, (uint32_t)s * kStageA + h * kBytesA);
                     const uint64_t db = desc_advance(desc_b0, (uint32_t)s * kStageB + h * NB * kBytesB);
 #pragma unroll
@@ -325,12 +342,82 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             constexpr bool kOut16 = MODE == GEMM_STORE || MODE == GEMM_GATED;
             constexpr int kBoxCols = kOut16 ? 64 : 32;
             unsigned char* stage_row = base + (size_t)row * 128;
+            // With K split among CTAs: this CTA's sums to scratch, a ticket, and only the CTA
+            // of the tile that arrives last goes on, with the sums of all splits.
+            constexpr bool split = SPLIT && MODE == GEMM_ADD_F32;
+            const size_t tile_id = (size_t)blockIdx.y * gridDim.x + blockIdx.x;
+            float* tile_sums = g.split_scratch + (tile_id * (size_t)g.k_splits * kBM + row) * BN;
+            bool finishes = true;
+            if constexpr (split) {
+                float* mine = tile_sums + (size_t)blockIdx.z * kBM * BN;
 #pragma unroll 1
-            for (int c0 = c_first; c0 < BN; c0 += kColStep) {
+                for (int c0 = c_first; c0 < BN; c0 += kColStep) {
+                    uint32_t v[32];
+                    tmem_load32_issue(lane_base + (uint32_t)c0, v);
+                    tmem_load_wait();
+                    if (m < g.M) {  // (rows beyond M are never read)
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            __stcg(reinterpret_cast<float4*>(mine + c0) + j,
+                                   make_float4(__uint_as_float(v[j * 4]), __uint_as_float(v[j * 4 + 1]),
+                                               __uint_as_float(v[j * 4 + 2]), __uint_as_float(v[j * 4 + 3])));
+                    }
+                }
+                // every epilogue warp has written (bounded waits, as everywhere: a warp that
+                // gave up earlier must not leave the others waiting for ever)
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&split_bar);
+                if (threadIdx.x == 64) {
+                    split_last = 0;
+                    if (mbar_wait(&split_bar, 0)) {
+                        unsigned old;
+                        asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;"
+                                     : "=r"(old) : "l"(g.split_tickets + tile_id) : "memory");
+                        split_last = old == (unsigned)g.k_splits - 1u;
+                        if (split_last) g.split_tickets[tile_id] = 0u;  // (every split has arrived)
+                    } else {
+                        abort_flag = 1;
+                    }
+                    mbar_arrive(&split_done);
+                }
+                if (!mbar_wait(&split_done, 0)) abort_flag = 1;
+                finishes = split_last != 0 && !abort_flag;
+            }
+#pragma unroll 1
+            for (int c0 = c_first; c0 < BN && finishes; c0 += kColStep) {
                 uint32_t v[32], u[32];
-                tmem_load32_issue(lane_base + (uint32_t)c0, v);
-                if constexpr (MODE == GEMM_GATED) tmem_load32_issue(lane_base + (uint32_t)(BN + c0), u);
-                tmem_load_wait();
+                if constexpr (split) {
+                    // the splits' sums of this row: all asked for at once (one trip to L2),
+                    // added in the order of the splits
+                    float4 part[kMaxKSplits][8];
+#pragma unroll
+                    for (int z = 0; z < kMaxKSplits; ++z) {
+                        const float4* src = reinterpret_cast<const float4*>(tile_sums + (size_t)z * kBM * BN + c0);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            part[z][j] = z < g.k_splits && m < g.M ? __ldcg(src + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        float4 sum = part[0][j];
+#pragma unroll
+                        for (int z = 1; z < kMaxKSplits; ++z) {
+                            sum.x += part[z][j].x;
+                            sum.y += part[z][j].y;
+                            sum.z += part[z][j].z;
+                            sum.w += part[z][j].w;
+                        }
+                        v[j * 4] = __float_as_uint(sum.x);
+                        v[j * 4 + 1] = __float_as_uint(sum.y);
+                        v[j * 4 + 2] = __float_as_uint(sum.z);
+                        v[j * 4 + 3] = __float_as_uint(sum.w);
+                    }
+                } else {
+                    tmem_load32_issue(lane_base + (uint32_t)c0, v);
+                    if constexpr (MODE == GEMM_GATED) tmem_load32_issue(lane_base + (uint32_t)(BN + c0), u);
+                    tmem_load_wait();
+                }
                 const int nb = n0 + c0;
                 float f[32];
                 if constexpr (MODE == GEMM_GATED) {
@@ -390,7 +477,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     }
                 }
             }
-            if (g.out_by_tma) {
+            if (g.out_by_tma && finishes) {
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&staged_bar);  // every epilogue warp
@@ -418,18 +505,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     trace_mark(g.trace, 1);
 }
 
-template <int BN, int STAGES, int MODE, int KSUB>
+template <int BN, int STAGES, int MODE, int KSUB, bool SPLIT = false>
 static int launch_gemm_tc(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mo,
                           const GemmArgs& g, bool pdl,
                           cudaStream_t stream) {
     constexpr int NB = MODE == GEMM_GATED ? 2 : 1;
     size_t smem = (size_t)STAGES * KSUB * (kBM + NB * BN) * kBK * 2 + 1024;
-    auto kernel = gemm_tc_kernel<BN, STAGES, MODE, KSUB>;
+    auto kernel = gemm_tc_kernel<BN, STAGES, MODE, KSUB, SPLIT>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     int n_cols = MODE == GEMM_GATED ? g.N / 2 : g.N;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((n_cols + BN - 1) / BN, (g.M + kBM - 1) / kBM);
+    cfg.gridDim = dim3((n_cols + BN - 1) / BN, (g.M + kBM - 1) / kBM, g.k_splits);
     cfg.blockDim = dim3(gemm_threads(BN, STAGES, MODE, KSUB));
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
@@ -442,18 +529,54 @@ static int launch_gemm_tc(const CUtensorMap& ma, const CUtensorMap& mw, const CU
     return e == cudaSuccess ? NNIS_OK : (int)e;
 }
 
+// Into how many runs of k-blocks the adding product cuts K: more than one where 64-column
+// tiles are fewer than half the SMs and K is long (a decode step of many rows through a
+// projection with a long K: the 1.7B shape's down projection at 64 rows has 32 tiles, each
+// streaming a megabyte of weights).  Stages hold 256 columns of K here; every run gets at
+// least four of them, no run is empty.
+static int gemm_k_splits(long tiles64, int K, int sms) {
+    const int k_blocks = (K + 4 * kBK - 1) / (4 * kBK);
+    if (tiles64 * 2 > sms || k_blocks < 8) return 1;
+    long want = sms / tiles64;
+    if (want > k_blocks / 4) want = k_blocks / 4;
+    if (want > kMaxKSplits) want = kMaxKSplits;
+    if (want < 2) return 1;
+    const int per = (k_blocks + (int)want - 1) / (int)want;
+    return (k_blocks + per - 1) / per;
+}
+
 }  // namespace nnis
+
+// How many CTAs share a tile of the adding product of these sizes (1: no split of K),
+// and the scratch that takes: `*floats` float32 and `*tiles` tickets.
+NNIS_API int nnis_gemm_tc_splits(int M, int N, int K, int sm_count, long long* floats, int* tiles) {
+    using namespace nnis;
+    const int sms = sm_count > 0 ? sm_count : 148;
+    const long m_tiles = (M + kBM - 1) / kBM;
+    const long tiles128 = (long)((N + 127) / 128) * m_tiles;
+    const long tiles64 = m_tiles * ((N + 63) / 64);
+    const int splits = tiles128 >= sms ? 1 : gemm_k_splits(tiles64, K, sms);
+    if (floats) *floats = splits > 1 ? tiles64 * splits * (long long)(kBM * 64) : 0;
+    if (tiles) *tiles = splits > 1 ? (int)tiles64 : 0;
+    return splits;
+}
 
 // Modes: 0 store bfloat16, 1 store float32, 2 add into float32, 3 gated
 // (W = [gate rows; up rows], out [M, N / 2] = bf16(silu(gate) * up)), 4 QKV (bias,
 // RoPE, q to out [M, nq * d], k and v into the paged cache; d must be 64 or 128).
 // Refuses (NNIS_ERR_UNSUPPORTED): K not a multiple of 8, grids too large, a
 // driver without tensor-map encoding; operands must be 16-byte aligned.
+// `split_scratch` (`split_floats` float32) and `split_tickets` (`split_tiles` counters,
+// zero before the first launch; the kernel leaves them zero) are optional: with them the
+// adding mode cuts a long K among several CTAs per tile where tiles are few (see
+// nnis_gemm_tc_splits).
 NNIS_API int nnis_gemm_tc(const void* A, const void* W, const float* bias, void* C, int M, int N,
                           int K, int mode, const int* token_pos, const int* token_seq,
                           const int* page_table, int table_cols, const float* cos_t,
                           const float* sin_t, void* k_cache, void* v_cache, int nq, int nkv, int d,
-                          int page_size, int sm_count, int* status, int pdl, cudaStream_t stream) {
+                          int page_size, float* split_scratch, long long split_floats,
+                          unsigned* split_tickets, int split_tiles, int sm_count, int* status, int pdl,
+                          cudaStream_t stream) {
     using namespace nnis;
     if (M <= 0 || N <= 0 || K <= 0 || !A || !W || !C || mode < 0 || mode > 4) return NNIS_ERR_ARGUMENT;
     if (K % 8) return NNIS_ERR_UNSUPPORTED;
@@ -465,6 +588,7 @@ NNIS_API int nnis_gemm_tc(const void* A, const void* W, const float* bias, void*
     g.token_pos = token_pos; g.token_seq = token_seq; g.page_table = page_table;
     g.table_cols = table_cols; g.cos_t = cos_t; g.sin_t = sin_t; g.k_cache = (bf16*)k_cache;
     g.v_cache = (bf16*)v_cache; g.nq = nq; g.nkv = nkv; g.d = d; g.page_size = page_size;
+    g.k_splits = 1; g.split_scratch = nullptr; g.split_tickets = nullptr;
     static const char* const kNames[] = {"gemm store", "gemm store_f32", "gemm add_f32", "gemm gated", "gemm qkv"};
     g.trace = trace_slot(mode >= 0 && mode <= 4 ? kNames[mode] : "gemm");
     int sms = sm_count > 0 ? sm_count : 148;
@@ -494,7 +618,10 @@ NNIS_API int nnis_gemm_tc(const void* A, const void* W, const float* bias, void*
         // wide outputs: 192 gate and 192 up columns per CTA, which has its SM alone
         // (384 columns of tensor memory, 64 KB a stage); products of N = 192 run at
         // the tensor cores' full rate, those of N = 64 at two thirds of it
-        const bool fat = N / 2 > 128 && 4 * m_tiles * ((N / 2 + 191) / 192) >= sms;  // enough fat tiles for a quarter of the SMs
+        // (with enough fat tiles for half of the SMs; with fewer, as with one tile of rows in
+        // a decode step of many sequences, three times as many narrow tiles pull the weights
+        // from memory faster: 1.7B shape at 64 rows 28 -> 18 us)
+        const bool fat = N / 2 > 128 && 2 * m_tiles * ((N / 2 + 191) / 192) >= sms;
         if (!make_map(&ma, A, M, K, kBM) || !make_map(&mw, W, N, K, fat ? 192 : 64)) return NNIS_ERR_UNSUPPORTED;
         g.out_by_tma = (N / 2) % 8 == 0 && make_map(&mo, C, M, N / 2, kBM);
         if (!g.out_by_tma) mo = ma;
@@ -513,6 +640,13 @@ NNIS_API int nnis_gemm_tc(const void* A, const void* W, const float* bias, void*
     NNIS_GEMM_TC64(MODE, m_tiles * ((N + 63) / 64))
     if (mode == GEMM_STORE) { NNIS_GEMM_TC(GEMM_STORE); }
     if (mode == GEMM_STORE_F32) { NNIS_GEMM_TC(GEMM_STORE_F32); }
+    const long tiles64 = m_tiles * ((N + 63) / 64);
+    const int splits = wide ? 1 : gemm_k_splits(tiles64, K, sms);
+    if (splits > 1 && split_scratch && split_tickets && tiles64 <= split_tiles &&
+        tiles64 * splits * (long long)(kBM * 64) <= split_floats) {
+        g.k_splits = splits; g.split_scratch = split_scratch; g.split_tickets = split_tickets;
+        return launch_gemm_tc<64, 2, GEMM_ADD_F32, 4, true>(ma, mw, mo, g, pdl != 0, stream);
+    }
     NNIS_GEMM_TC(GEMM_ADD_F32);
 #undef NNIS_GEMM_TC64
 #undef NNIS_GEMM_TC128

@@ -750,12 +750,16 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out:
             token_seq: Optional[torch.Tensor] = None, page_table: Optional[torch.Tensor] = None,
             cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None,
             k_cache: Optional[torch.Tensor] = None, v_cache: Optional[torch.Tensor] = None,
-            heads: int = 0, kv_heads: int = 0, head_dim: int = 0, page_size: int = 0) -> None:
+            heads: int = 0, kv_heads: int = 0, head_dim: int = 0, page_size: int = 0,
+            split_scratch: Optional[torch.Tensor] = None,
+            split_tickets: Optional[torch.Tensor] = None) -> None:
     """out (op)= a . w^T + bias on the tensor cores (tcgen05, float32 accumulation
     in tensor memory); bfloat16 operands.  Modes: STORE, STORE_F32, ADD_F32,
     GEMM_GATED (w = [gate; up] rows, out bfloat16 [m, n / 2] = silu(gate) * up) and
     GEMM_QKV (bias, RoPE at each row's position, q to out [m, heads * d], k and v
-    into the paged cache; head_dim 64 or 128)."""
+    into the paged cache; head_dim 64 or 128).  ADD_F32 with ``split_scratch`` (float32)
+    and ``split_tickets`` (int32, zero; left zero) of the sizes ``gemm_tc_splits`` names
+    may cut K among several CTAs per tile; their sums are added in a fixed order."""
     _cuda(a, w, bias, out, token_pos, token_seq, page_table, cos, sin, k_cache, v_cache)
     m, k = a.shape
     n = w.shape[0]
@@ -783,11 +787,27 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out:
         _need(tuple(out.shape) == (m, n), "gemm_tc: out [m, n]")
         _need(out.dtype == (torch.bfloat16 if mode == STORE else torch.float32), "gemm_tc: out dtype vs mode")
     cols = page_table.shape[1] if page_table is not None else 0
+    scratch, tickets = (split_scratch, split_tickets) if mode == ADD_F32 else (None, None)
+    _cuda(scratch, tickets)
     _check(_lib().nnis_gemm_tc(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), m, n, k, mode, _ptr(token_pos),
                                _ptr(token_seq), _ptr(page_table), cols, _ptr(cos), _ptr(sin),
                                _ptr(k_cache), _ptr(v_cache), heads, kv_heads, head_dim, page_size,
+                               _ptr(scratch), ctypes.c_longlong(scratch.numel() if scratch is not None else 0),
+                               _ptr(tickets), tickets.numel() if tickets is not None else 0,
                                sm_count(a.device), _ptr(status_word(a.device)), PDL, _stream()),
            "gemm_tc")
+
+
+# Whether the adding product may cut a long K among CTAs (few tiles): parts/linear.py asks.
+GEMM_SPLIT_K = os.environ.get("NNIS_GEMM_SPLIT_K", "1") == "1"
+
+
+def gemm_tc_splits(m: int, n: int, k: int, device=None):
+    """(CTAs that share a tile of the adding product, float32 of scratch, tickets)."""
+    floats, tiles = ctypes.c_longlong(0), ctypes.c_int(0)
+    sms = sm_count(device) if device is not None else 148
+    splits = int(_lib().nnis_gemm_tc_splits(m, n, k, sms, ctypes.byref(floats), ctypes.byref(tiles)))
+    return splits, int(floats.value), int(tiles.value)
 
 
 def gemm_tc_qkv_takes(head_dim: int) -> bool:

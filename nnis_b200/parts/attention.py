@@ -266,7 +266,7 @@ class Attention(Part):
         if self._fused_out(ctx, n):
             ops.gemv_bf16(self.w_o, self.b_o, residual, ops.EPI_ADD_F32, x=attn)
         else:
-            linear(attn, self.w_o, self.b_o, residual, ADD_F32)
+            linear(attn, self.w_o, self.b_o, residual, ADD_F32, ws)
 
 
 MIXERS.register("attention", Attention)

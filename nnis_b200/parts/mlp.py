@@ -96,7 +96,7 @@ class GatedMLP(Part):
         if self._fused_down(ctx, n):
             ops.gemv_bf16(self.w_down, self.b_down, residual, ops.EPI_ADD_F32, x=act)
         else:
-            linear(act, self.w_down, self.b_down, residual, ADD_F32)
+            linear(act, self.w_down, self.b_down, residual, ADD_F32, ws)
 
 
 FEED_FORWARDS.register("gated_mlp", GatedMLP)

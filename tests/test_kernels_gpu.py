@@ -853,6 +853,38 @@ def test_gemm_on_tcgen05_wide_tiles(m, n, k):
     o.check_status(DEV)
 
 
+@pytest.mark.parametrize("m,n,k", [(64, 2048, 8192), (33, 192, 2048 + 72), (130, 320, 4096), (17, 64, 2048)])
+def test_gemm_on_tcgen05_adds_with_k_cut_among_ctas(m, n, k):
+    """Few tiles and a long K: several CTAs share a tile, each a run of k-blocks; their sums
+    meet in scratch and the one that arrives last adds them in the order of the runs, so two
+    launches give the same bits.  One far column of K matters: a run left out would show."""
+    o = ops()
+    splits, floats, tiles = o.gemm_tc_splits(m, n, k, DEV)
+    assert splits > 1 and floats == tiles * splits * 128 * 64 and tiles == -(-m // 128) * -(-n // 64)
+    assert o.gemm_tc_splits(2048, n, k, DEV)[0] == 1 or n < 512  # many tiles: no split
+    g = torch.Generator().manual_seed(m + n)
+    a = torch.randn(m, k, generator=g).bfloat16()
+    w = (torch.randn(n, k, generator=g) / math.sqrt(k)).bfloat16()
+    a[:, k - 5] = 3.0
+    w[:, k - 5] = 1.0
+    bias = torch.randn(n, generator=g)
+    want = P.linear(a, w, bias)
+    base = torch.randn(m, n, generator=g)
+    scratch = torch.full((floats,), float("nan"), device=DEV)
+    tickets = torch.zeros(tiles, dtype=torch.int32, device=DEV)
+    outs = []
+    for _ in range(2):
+        acc = base.to(DEV).clone()
+        o.gemm_tc(a.to(DEV), w.to(DEV), bias.to(DEV), acc, o.ADD_F32, split_scratch=scratch, split_tickets=tickets)
+        close(acc, base.double() + want, "float32", "tcgen05 add, K cut among CTAs")
+        outs.append(acc)
+    assert torch.equal(outs[0], outs[1]) and int(tickets.abs().sum()) == 0
+    whole = base.to(DEV).clone()  # the same without scratch: one CTA a tile, one long float32 sum
+    o.gemm_tc(a.to(DEV), w.to(DEV), bias.to(DEV), whole, o.ADD_F32)
+    assert float((whole - outs[0]).abs().max()) < 2e-4
+    o.check_status(DEV)
+
+
 def test_gemm_on_tcgen05_many_k_blocks_reuse_every_stage():
     o = ops()
     g = torch.Generator().manual_seed(0)
