@@ -56,11 +56,12 @@ def test_random_shape(seed, dtype):
     engine.cache.check()
 
 
-@pytest.mark.parametrize("batch", [1, 8, 24])
+@pytest.mark.parametrize("batch", [1, 8, 24, 64])
 def test_wide_layers_decode_with_long_rows_of_k(batch):
     """A layer as wide as the 1.7B shape (hidden 2,048, intermediate 8,192, 32 heads of 64):
     the decode projections stream K in chunks there, and the down projection adds slice by
-    slice; prompts, then single tokens of a batch, against the plain implementation."""
+    slice; with 64 rows the tcgen05 products run, the down projection with K cut among the
+    CTAs of a tile; prompts, then single tokens of a batch, against the plain implementation."""
     from nnis_b200.config import config_from_dict
     from nnis_b200.engine import Engine, SequenceStep
     from nnis_b200.engine.model import DecoderModel
@@ -74,6 +75,10 @@ def test_wide_layers_decode_with_long_rows_of_k(batch):
                              std_by_fan_in=True)
     w = {k: v.to(torch.bfloat16).float() for k, v in tensors.items()}
     engine = Engine.from_spec(spec, tensors, dtype="bfloat16", max_tokens=64 * batch * 2, max_slots=batch)
+    if batch == 64:
+        from nnis_b200.csrc import ops
+        assert ops.gemm_tc_splits(batch, 2048, 8192, engine.device)[0] == 4
+        assert not ops.gemv_pays(batch, 2048, 8192, ops.EPI_ADD_F32, engine.device)
     rng = random.Random(batch)
     lens = [rng.choice([2, 5, 9]) for _ in range(batch)]
     seqs = [[rng.randrange(cfg["vocab_size"]) for _ in range(n + 2)] for n in lens]
