@@ -42,6 +42,7 @@ class EngineBackend:
         # picks one step late.  False: every step's tokens come from the host.
         self.pipeline = pipeline
         self._decoders = {}
+        self._views = {}
         self._pinned = None
         self._picked = None
         self._picked_for = None
@@ -65,24 +66,37 @@ class EngineBackend:
         picks).  Steps in which every sequence brings one token and wants its
         logits run as a CUDA graph whose inputs (tokens, positions, page tables)
         come from the host in one copy."""
-        single = all(len(s.tokens) == 1 and list(s.want) == [0] for s in batch)
+        single = True
+        for s in batch:
+            want = s.want
+            if len(s.tokens) != 1 or len(want) != 1 or want[0] != 0:
+                single = False
+                break
         if not single or self.decode_greedy is None or len(batch) > self.max_rows:
             self._picked = None
             return self.engine.step_in_portions(batch, self.max_step_tokens)
         engine, cache = self.engine, self.engine.cache
-        slots = [s.slot for s in batch]
-        positions = [cache.length(s) for s in slots]
+        vocab = engine.spec.vocab_size
+        slots, tokens = [], []
         for s in batch:
-            if not 0 <= int(s.tokens[0]) < engine.spec.vocab_size:
+            token = int(s.tokens[0])
+            if not 0 <= token < vocab:
                 raise StepError(f"slot {s.slot}: token {s.tokens[0]} is outside the vocabulary")
+            slots.append(s.slot)
+            tokens.append(token)
+        positions = [cache.length(s) for s in slots]
         new_lengths = [p + 1 for p in positions]
         cache.reserve(slots, new_lengths)
         dec = self._decoder(len(batch), max(new_lengths), need_logits)
-        self.h2d_bytes += dec.upload([int(s.tokens[0]) for s in batch], positions, slots)
+        self.h2d_bytes += dec.upload(tokens, positions, slots)
         dec.launch()
         cache.commit(slots, new_lengths)
-        self._picked = dec.picked[:len(batch)]
-        return dec.logits[:len(batch)] if need_logits else None
+        n = len(batch)
+        views = self._views.get((id(dec), n))
+        if views is None:  # (slicing a tensor costs microseconds: once per decoder and row count)
+            views = self._views[(id(dec), n)] = (dec.picked[:n], dec.logits[:n] if dec.logits is not None else None)
+        self._picked = views[0]
+        return views[1] if need_logits else None
 
     def greedy(self, logits: Optional[torch.Tensor]) -> List[int]:
         if self._picked is not None:  # the graph has picked already
