@@ -2,7 +2,8 @@
 """Decode and prefill throughput of the SmolLM2-135M shape on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--shape 135m|360m|1.7b] [--batch B] [--layers L] [--skip-points] [--skip-e2e]
+                    [--shape 135m|360m|1.7b] [--batch B] [--context C] [--layers L] [--skip-points]
+                    [--skip-e2e]
 
 A step is one decode step of a batch of 8 sequences whose context ends at 4,096
 tokens (prompt 2,048 + 2,048 decoded); ``value`` is decoded tokens per second,
@@ -235,6 +236,7 @@ def timeline(engine, batch, path, rng, vocab):
 
 
 def main() -> int:
+    global CONTEXT
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=256)
@@ -244,6 +246,8 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
     ap.add_argument("--skip-e2e", action="store_true", help="leave out the end-to-end run")
     ap.add_argument("--batch", type=int, default=BATCH, help="sequences of the main decode point")
+    ap.add_argument("--context", type=int, default=CONTEXT,
+                    help="tokens at which the decoded contexts end (the metric's: 4096)")
     ap.add_argument("--timeline", metavar="FILE", default=None,
                     help="instead of the benchmark: write the timeline of one decode step of the main "
                          "point (begin, end and wait of every launch of the decode kernels) to FILE; "
@@ -251,6 +255,7 @@ def main() -> int:
     ap.add_argument("--shape", default="135m", choices=sorted(SHAPES),
                     help="layer sizes: the SmolLM2-135M shape (the benchmark) or a larger one of the family")
     args = ap.parse_args()
+    CONTEXT = max(args.context, 64)
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
                           "Memorithm/NNIS is a Rust workspace (cargo, NVRTC); pip cannot install it "
@@ -274,6 +279,7 @@ def main() -> int:
     cfg = dict(SMOLLM2_135M)
     shape_name, shape_sizes = SHAPES[args.shape]
     cfg.update(shape_sizes)
+    cfg["max_position_embeddings"] = max(cfg["max_position_embeddings"], CONTEXT)
     full_layers = cfg["num_hidden_layers"]
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
@@ -286,7 +292,7 @@ def main() -> int:
     with tempfile.TemporaryDirectory() as tmp:
         write_random_model(cfg, seed=0, out_dir=tmp, std=1.0, norm_std=0.1, std_by_fan_in=True)
         most_rows = max(args.batch, 1, 1 if args.skip_points or args.timeline else 64)  # the cache holds the largest point
-        llm = LLM(tmp, dtype="bfloat16", device_ordinal=0, max_tokens=most_rows * (CONTEXT + 64),
+        llm = LLM(tmp, dtype="bfloat16", device_ordinal=0, max_tokens=max(most_rows * (CONTEXT + 64), 4 * (PROMPT + 64)),
                   max_batch=max(most_rows, 1), pipeline_decode=False)
         engine = llm.engine
         spec = engine.spec
