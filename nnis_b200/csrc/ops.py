@@ -449,6 +449,7 @@ def attention_decode_takes(head_dim: int) -> bool:
 # Whether the decode attention kernel for few sequences asks the same pages of the layer that
 # runs next into L2 when it is through with its own (batch 8 of the 135M shape: +2 %).
 KV_PREFETCH = os.environ.get("NNIS_KV_PREFETCH", "1") == "1"
+PREFILL_SHORT_CHUNKS = os.environ.get("NNIS_PREFILL_SHORT_CHUNKS", "1") == "1"
 TMA_SLICE_PAGES = int(os.environ.get("NNIS_TMA_SLICE_PAGES", "0"))  # 0: chosen by the plan
 TMA_ATTENTION = 0 if os.environ.get("NNIS_TMA_ATTENTION", "1") == "0" else 1
 _tma_ctas_per_sm: dict = {}
@@ -639,7 +640,9 @@ def prefill_tc_plan(counts, starts, window: int, heads: int, sms: int):
     per SM: the longest chunk of 32, 24, 16 or 12 pages that gives as many, else 8
     (a chunk costs a CTA's start and end, a trip of its rows through scratch and,
     for the last one of a tile, the merge; measured on one prompt of 1,024 / 2,048 /
-    4,096 tokens and 9 heads the best lengths were 8 / 12 / none).  Returns ``units`` int32 [n, 4] (sequence,
+    4,096 tokens and 9 heads the best lengths were 8 / 12 / none); then the shortest
+    chunks from 8 pages on with which the CTAs still fit one wave of two to an SM (2,048
+    tokens: 11 pages, 288 CTAs; a CTA walks its pages one after another).  Returns ``units`` int32 [n, 4] (sequence,
     first query, chunk | chunks << 16, first scratch slot), longest first, and the
     number of scratch slots.  ``prefill_tc_pays`` says whether the step is worth this
     kernel at all."""
@@ -656,6 +659,13 @@ def prefill_tc_plan(counts, starts, window: int, heads: int, sms: int):
         if 10 * sum(-(-p // cand) for _, _, p in tiles) * heads >= 17 * sms:
             chunk_pages = cand
             break
+    if PREFILL_SHORT_CHUNKS and chunk_pages > 8 and chunk_pages < (1 << 30):
+        # A CTA walks its pages one after another (1.3 us a page): where the CTAs still fit
+        # one wave of two to an SM with shorter chunks, the shortest such chunks end first.
+        for cand in range(8, chunk_pages):
+            if sum(-(-p // cand) for _, _, p in tiles) * heads <= 2 * sms:
+                chunk_pages = cand
+                break
     units, slot = [], 0
     for i, q0, pages in tiles:
         n = -(-pages // chunk_pages)
