@@ -52,3 +52,34 @@ def test_decode_attention_slices_fill_waves():
             assert 1 <= s <= 64 and (s - 1) * 256 < max(context, 1)
     # short contexts are not cut
     assert pick(3, 200) == 1 and pick(3, 512) == 2
+
+
+def test_prompt_attention_plan_takes_the_shortest_chunks_that_fit_one_wave():
+    """One prompt of 2,048 tokens, nine heads, 148 SMs: chunks of 12 pages are the longest
+    that give enough CTAs, chunks of 11 the shortest with which two CTAs to an SM still hold
+    them all (a CTA walks its pages one after another: the longest chunk ends last)."""
+    from nnis_b200.csrc import ops as o
+    units, _ = o.prefill_tc_plan([2048], [0], 0, 9, 148)
+    chunks = {}
+    for s, q0, z, slot in units.tolist():
+        chunks[q0] = z >> 16
+    assert len(units) * 9 <= 2 * 148 and len(units) == 32
+    assert chunks[2048 - 128] == 3 and chunks[0] == 1 and chunks[128 * 10] == 2  # 32, 2 and 22 pages
+    # 4,096 tokens: a tile a CTA fills a wave; 1,024: chunks of eight pages as before
+    assert len(o.prefill_tc_plan([4096], [0], 0, 9, 148)[0]) == 32
+    assert max(z >> 16 for _, _, z, _ in o.prefill_tc_plan([1024], [0], 0, 9, 148)[0].tolist()) == 2
+
+
+def test_bench_sums_a_traced_step_per_kernel():
+    import importlib.util
+    import os
+    spec = importlib.util.spec_from_file_location("bench", os.path.join(os.path.dirname(__file__), "..", "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    big = 1 << 62
+    # per launch: begin, end, first and last past the wait, marks
+    rows = [[1000, 4000, 1500, 2000, big, 0, big, 0], [3500, 9000, 4500, 5000, big, 0, big, 0],
+            [8000, 9500, big, 0, big, 0, big, 0]]
+    got = bench.kernel_times(["a", "b", "a"], rows)
+    assert got["a"] == {"launches": 2, "us": 3.5} and got["b"] == {"launches": 1, "us": 4.0}
+    assert got["step"] == {"launches": 3, "us": 8.5}
