@@ -71,13 +71,11 @@ __device__ __forceinline__ unsigned ticket_take(unsigned* ticket) {
     return old;
 }
 
-// MINB: CTAs per SM that the registers must leave room for.  Three CTAs of 167 registers
-// fill an SM's register file, and the projection kernel that this one starts beside keeps
-// its CTAs' registers until it ends: with 96 registers (a few values spilled) three CTAs
-// and a projection's fit together.  Where two CTAs per SM are all it takes, the kernel
-// keeps its registers.
-template <int D, int MINB>
-__global__ void __launch_bounds__(kClThreads, MINB)
+// Three CTAs of 167 registers fill an SM's register file; a build held to 96 registers
+// (so that three CTAs and a projection's fit together) spilled a few values inside its
+// loops and was slower wherever it was tried, with two and with three CTAs to an SM.
+template <int D>
+__global__ void __launch_bounds__(kClThreads, 3)
 attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const bf16* k_cache,
                        const bf16* v_cache, const bf16* __restrict__ q, int q_stride,
@@ -488,15 +486,7 @@ static int launch_tma(dim3 grid, int per, bool pdl, cudaStream_t stream, const C
                       bf16* out, float* partial, unsigned* tickets, int nq, int nkv, int window,
                       float scale, int head_tiles, int* status, long long ahead) {
     const size_t smem = tma_smem_bytes<D>(per);
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-            sms = 148;
-    }
-    const bool two_fit = (long)grid.x * grid.y * grid.z <= 2l * sms;
-    auto kernel = two_fit || D != 64 ? attn_decode_tma_kernel<D, 3> : attn_decode_tma_kernel<D, D == 64 ? 5 : 3>;
+    auto kernel = attn_decode_tma_kernel<D>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     cudaLaunchConfig_t cfg = {};
@@ -518,7 +508,7 @@ static int launch_tma(dim3 grid, int per, bool pdl, cudaStream_t stream, const C
 // How many CTAs of this kernel, each holding `per` pages, one SM runs at once.
 template <int D>
 static int tma_ctas_per_sm(int per) {
-    auto kernel = attn_decode_tma_kernel<D, D == 64 ? 5 : 3>;  // the variant for many CTAs
+    auto kernel = attn_decode_tma_kernel<D>;
     const size_t smem = tma_smem_bytes<D>(per);
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return 0;

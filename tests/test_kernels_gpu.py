@@ -720,8 +720,8 @@ def test_attention_decode_fed_by_tma(nq, nkv, d, window):
 
 
 def test_attention_decode_fed_by_tma_with_more_ctas_than_two_per_sm():
-    """Many sequences: more CTAs than two per SM take the build of the kernel that leaves
-    room for three (fewer registers); the same results."""
+    """Many sequences: more CTAs than two per SM (three fill an SM's registers, so the last
+    of them start when the first have left); the same results."""
     o = ops()
     nq, nkv, d = 9, 3, 64
     rng = np.random.default_rng(3)
