@@ -137,11 +137,14 @@ NNIS_API int nnis_gemv_slices(int M, int N, int K, int sm_count) {
 
 // Which kernel nnis_gemv_bf16 runs for a product: 2 the one that cuts the rows into
 // tiles (gemv_rowtile.cu: more than 16 rows, few output features), 1 the one whose
-// CTAs hold all rows (at most 64), 0 neither.  `normed`: with the norm prologue.
+// CTAs hold all rows (at most 64), 0 neither.  `normed`: the prologue (0 x as it is, 1
+// the norm, 2 x weighted and the rows' sums of squares in shares: the first kernel only).
 NNIS_API int nnis_gemv_kind(int M, int N, int K, int epilogue, int normed, int sm_count) {
     using namespace nnis;
     int units;
-    if (rowtile_slices(M, N, K, epilogue, normed ? PRO_NORM : PRO_PLAIN, sm_count, &units) > 0) return 2;
+    const int pro = normed == 2 ? PRO_SCALED : normed ? PRO_NORM : PRO_PLAIN;
+    if (rowtile_slices(M, N, K, epilogue, pro, sm_count, &units) > 0) return 2;
+    if (pro == PRO_SCALED) return 0;
     GemvPlan p;
     if (epilogue == EPI_ADD_F32 && !normed) return gemv_slices(M, N, K, sm_count, &p) >= 1 ? 1 : 0;
     return gemv_plan(M, N, K, sm_count, &p) ? 1 : 0;
@@ -173,19 +176,27 @@ NNIS_API int nnis_gemv_grid(int M, int N, int K, int sm_count) {
 // start together with this one (only for a successor that reads nothing of this step
 // before its own wait); bit 2: not the kernel over tiles of rows, even where it applies
 // (for comparisons).
+// `emit_x`, `emit_w`, `emit_ss` (ADD_F32, optional): the output rows times the weights
+// `emit_w` [N] in bfloat16 [M, N], and per row and eight columns the sum of the output's
+// squares [M, N / 8], for a product that follows with `ss_parts` [M, K / 8]: x is then such
+// an `emit_x`, and `eps` the norm's (the kernel over tiles of rows only).
 NNIS_API int nnis_gemv_bf16(const void* x, const float* hidden, const int* rows, const float* norm_w,
                             float eps, const void* w, const float* bias, void* out, int M, int N,
                             int K, int epilogue, const int* token_pos, const int* token_seq,
                             const int* page_table, int table_cols, const float* cos_t,
                             const float* sin_t, void* k_cache, void* v_cache, int nq, int nkv, int d,
                             int page_size, float* logits, float* best_val, int* best_idx,
-                            unsigned* ticket, int* next_tokens, int* next_pos, int* status,
+                            unsigned* ticket, int* next_tokens, int* next_pos, void* emit_x,
+                            const float* emit_w, float* emit_ss, const float* ss_parts, int* status,
                             int sm_count, int pdl, cudaStream_t stream) {
     using namespace nnis;
     if (M <= 0 || N <= 0 || K <= 0 || !w || !out) return NNIS_ERR_ARGUMENT;
     GemvPlan plan;
     plan.kc = K;
-    int pro = hidden ? PRO_NORM : PRO_PLAIN;
+    int pro = hidden ? PRO_NORM : ss_parts ? PRO_SCALED : PRO_PLAIN;
+    if (hidden && ss_parts) return NNIS_ERR_ARGUMENT;
+    if (emit_x && (epilogue != EPI_ADD_F32 || !emit_w || !emit_ss)) return NNIS_ERR_ARGUMENT;
+    if (((uintptr_t)emit_x | (uintptr_t)emit_w) % 8) return NNIS_ERR_ALIGNMENT;
     // more rows than a tile and few output features: the kernel that cuts the rows
     int rowtile_units = 0;
     const int rowtile_cuts = (pdl & 4) ? 0 : rowtile_slices(M, N, K, epilogue, pro, sm_count, &rowtile_units);
@@ -194,8 +205,9 @@ NNIS_API int nnis_gemv_bf16(const void* x, const float* hidden, const int* rows,
                        : may_slice      ? gemv_slices(M, N, K, sm_count, &plan)
                                         : (gemv_plan(M, N, K, sm_count, &plan) ? 1 : 0);
     if (slices == 0) return NNIS_ERR_UNSUPPORTED;
-    if (pro == PRO_PLAIN && !x) return NNIS_ERR_ARGUMENT;
+    if (pro != PRO_NORM && !x) return NNIS_ERR_ARGUMENT;
     if (pro == PRO_NORM && (!norm_w || !(eps > 0.f))) return NNIS_ERR_ARGUMENT;
+    if (pro == PRO_SCALED && (rowtile_cuts != 1 || !(eps > 0.f))) return NNIS_ERR_UNSUPPORTED;
     if (((uintptr_t)w | (uintptr_t)x | (uintptr_t)hidden | (uintptr_t)norm_w) % 16 ||
         (uintptr_t)out % (epilogue == EPI_ARGMAX ? 4 : 16))  // the picks are single words
         return NNIS_ERR_ALIGNMENT;
@@ -214,6 +226,8 @@ NNIS_API int nnis_gemv_bf16(const void* x, const float* hidden, const int* rows,
     a.v_cache = (bf16*)v_cache; a.nq = nq; a.nkv = nkv; a.d = d > 0 ? d : 8; a.page_size = page_size;
     a.logits = logits; a.best_val = best_val; a.best_idx = best_idx; a.ticket = ticket;
     a.next_tokens = next_tokens; a.next_pos = next_pos;
+    a.emit_x = nullptr; a.emit_w = emit_w; a.emit_ss = emit_ss;
+    a.ss_parts = ss_parts; a.ss_units = K / 8;
     a.ldx = K; a.ldw = K; a.kc = plan.kc; a.out_is_hot = 0;
     a.release_early = (pdl & 2) && slices == 1 ? 1 : 0;
     a.K = K / slices;
@@ -223,6 +237,7 @@ NNIS_API int nnis_gemv_bf16(const void* x, const float* hidden, const int* rows,
                                             "gemv rows gated", "gemv rows qkv"};
     for (int s = 0; s < slices; ++s) {
         int rc;
+        if (s == slices - 1) a.emit_x = (bf16*)emit_x;  // the sums are whole after the last slice
         if (rowtile_cuts > 0) {
             a.trace = trace_slot(epilogue >= 0 && epilogue <= 4 ? kRowNames[epilogue] : "gemv rows");
             rc = gemv_launch_rowtile(a, epilogue, pro, rowtile_units, (pdl & 1) != 0, stream);

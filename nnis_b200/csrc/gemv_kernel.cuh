@@ -39,7 +39,10 @@
 namespace nnis {
 
 enum { EPI_STORE = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_GATED = 3, EPI_QKV = 4, EPI_ARGMAX = 5 };
-enum { PRO_PLAIN = 0, PRO_NORM = 1 };
+// PRO_SCALED (gemv_rowtile.cu only): x is bf16(h * w_norm), what an ADD_F32 epilogue before
+// this kernel emitted with its shares of each row's sum of squares; the rows' scales
+// 1 / sqrt(mean of squares + eps) are applied to the float32 sums, after the products.
+enum { PRO_PLAIN = 0, PRO_NORM = 1, PRO_SCALED = 2 };
 
 struct GemvArgs {
     const bf16* x;          // [M, K] (plain prologue)
@@ -74,6 +77,16 @@ struct GemvArgs {
     int* next_tokens;       // optional: tokens of the next step (picked) ...
     int* next_pos;          // ... and their positions (+1 on live rows)
     unsigned long long* trace;  // this launch's slot of the step's timeline, or null
+    // ADD_F32 epilogue, optional: the norm that follows this projection, begun here.  For
+    // every value of the residual stream that it has just summed the epilogue also writes
+    // bf16(value * emit_w[column]) to emit_x [M, N] and, per unit of eight columns and row,
+    // the sum of the eight squares to emit_ss [M, N / 8].
+    bf16* emit_x;
+    const float* emit_w;
+    float* emit_ss;
+    // PRO_SCALED prologue: those shares of the rows' sums of squares, [M, ss_units]
+    const float* ss_parts;
+    int ss_units;
 };
 
 __device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
@@ -157,7 +170,7 @@ struct EpiTile {
     float2 old[2];                  // ADD_F32: the destination's values (first unit only)
     int pos[2], page[2];            // QKV: the rows' positions and cache pages
     float cs[4], sn[4];             // QKV: the rotation at those positions (first unit only)
-
+    float2 ew;                      // ADD_F32 that emits: the next norm's weights (first unit only)
 };
 
 // QKV: where a head's values go.  Row m of a query head lies at base + m * row_step (the
@@ -195,6 +208,8 @@ __device__ __forceinline__ void epi_preload(const GemvArgs& a, int unit, int row
                                   : make_float2(0.f, 0.f);
         }
     }
+    if (EPI == EPI_ADD_F32 && a.emit_x)
+        p.ew = *reinterpret_cast<const float2*>(a.emit_w + unit * 8 + c_lo);
     if (EPI == EPI_QKV) {
         const int na = unit_row<EPI>(a, unit, c_lo & 3);
         const int head = na / a.d, j = na - head * a.d, hf = a.d >> 1;
@@ -291,6 +306,9 @@ __device__ __forceinline__ void epi_finish(const GemvArgs& a, int unit, int row0
     } else {
         const int n0 = unit * 8 + c_lo;
         const float b0v = a.bias ? a.bias[n0] : 0.f, b1v = a.bias ? a.bias[n0 + 1] : 0.f;
+        float emit_sq[2] = {0.f, 0.f};  // ADD_F32 that emits: this lane's two squares of each row
+        float2 ew = make_float2(0.f, 0.f);
+        if (EPI == EPI_ADD_F32 && a.emit_x) ew = first ? p.ew : *reinterpret_cast<const float2*>(a.emit_w + n0);
 #pragma unroll
         for (int hrow = 0; hrow < 2; ++hrow) {
             int m = row0 + r_lo + hrow * 8;
@@ -304,7 +322,13 @@ __device__ __forceinline__ void epi_finish(const GemvArgs& a, int unit, int row0
             } else if (EPI == EPI_ADD_F32) {
                 float2* q = reinterpret_cast<float2*>(reinterpret_cast<float*>(a.out) + o);
                 float2 old = (first && !a.out_is_hot) ? p.old[hrow] : *q;
-                *q = make_float2(old.x + v0, old.y + v1);
+                const float2 sum = make_float2(old.x + v0, old.y + v1);
+                *q = sum;
+                if (a.emit_x) {
+                    *reinterpret_cast<uint32_t*>(a.emit_x + o) =
+                        pack_bf16(sum.x * ew.x, sum.y * ew.y);
+                    emit_sq[hrow] = fmaf(sum.x, sum.x, sum.y * sum.y);
+                }
             } else {
                 if (a.logits) *reinterpret_cast<float2*>(a.logits + o) = make_float2(v0, v1);
                 if (better(v0, n0, best_v[hrow], best_i[hrow])) {
@@ -315,6 +339,17 @@ __device__ __forceinline__ void epi_finish(const GemvArgs& a, int unit, int row0
                     best_v[hrow] = v1;
                     best_i[hrow] = n0 + 1;
                 }
+            }
+        }
+        if (EPI == EPI_ADD_F32 && a.emit_x) {  // (uniform over the warp: every lane shuffles)
+#pragma unroll
+            for (int hrow = 0; hrow < 2; ++hrow) {
+                // the four lanes of a row, in lane order: columns 0-1, 2-3, 4-5, 6-7
+                float sq = emit_sq[hrow];
+                sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+                sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+                int m = row0 + r_lo + hrow * 8;
+                if ((lane & 3) == 0 && m < M) a.emit_ss[(size_t)m * (a.N >> 3) + unit] = sq;
             }
         }
     }

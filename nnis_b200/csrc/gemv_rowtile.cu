@@ -20,6 +20,14 @@
 //  * The partial sums meet in shared memory, in the place of the weights; warp u adds
 //    those of unit u in warp order (deterministic) and runs its epilogue (the ones of
 //    gemv_kernel.cuh, except ARGMAX).
+//  * A norm between two of these products can be shared out between them (PRO_SCALED).
+//    The projection before it, whose epilogue holds the new residual values in registers,
+//    also writes them times the norm's weights, in bfloat16, and each unit's share of the
+//    rows' sums of squares; the projection after it takes that x as it is and multiplies
+//    its float32 sums by the rows' scales, which it adds up from the shares while its
+//    products run: y = scale(row) . (W . (h * w)) is the same sum as W . (h * scale * w)
+//    up to the place of one rounding.  It saves the second kernel the float32 rows, the
+//    pass through shared memory and a barrier between its wait and its products.
 //  * A decode step is a chain of short kernels, each of which starts while the one before
 //    it still runs (to fetch its weights) and must find room beside it: registers and
 //    shared memory per CTA are held down on purpose (__maxnreg__; with at most eight rows
@@ -38,7 +46,8 @@ __host__ __device__ constexpr int rowtile_direct_steps(bool longk) { return long
 // Registers per thread (see above), and the CTAs that fit an SM by them.
 __host__ __device__ constexpr int rowtile_registers(int epi, int pro, bool longk) {
     // (the QKV epilogue holds positions, pages and angles: at 80 registers it spills)
-    return pro == PRO_NORM ? (epi == EPI_QKV ? 88 : 80) : longk ? 128 : 104;
+    // (x as the kernel before weighted it: as few registers as with the norm, while K is short)
+    return pro == PRO_NORM || (pro == PRO_SCALED && !longk) ? (epi == EPI_QKV ? 88 : 80) : longk ? 128 : 104;
 }
 __host__ __device__ constexpr int rowtile_ctas_per_sm(int epi, int pro, bool longk) {
     return 65536 / (kRowtileWarps * 32 * rowtile_registers(epi, pro, longk));
@@ -59,10 +68,12 @@ template <int EPI, int PRO, int NU, bool LONGK>
 __global__ void __maxnreg__(rowtile_registers(EPI, PRO, LONGK))
 gemv_rowtile_kernel(GemvArgs a) {
     constexpr int WARPS = kRowtileWarps;
-    constexpr bool kDirect = PRO == PRO_PLAIN;
+    constexpr bool kDirect = PRO != PRO_NORM;
+    constexpr bool kScaled = PRO == PRO_SCALED;
     constexpr int kSteps = kDirect ? rowtile_direct_steps(LONGK) : 1;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t wbar;
+    __shared__ float row_scale[16];  // PRO_SCALED: 1 / sqrt(mean of squares + eps) of the tile's rows
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     trace_mark(a.trace, 0);
     if (a.release_early) pdl_launch_dependents();
@@ -156,6 +167,22 @@ gemv_rowtile_kernel(GemvArgs a) {
             ax[s][1] = vb.x;
             ax[s][2] = va.y;
             ax[s][3] = vb.y;
+        }
+        if (kScaled) {
+            // sixteen threads to a row add up its shares, each in a fixed order
+            const int r = threadIdx.x >> 4, part = threadIdx.x & 15;
+            const bool live = row0 + r < a.M;
+            const float* parts = a.ss_parts + (size_t)(live ? row0 + r : 0) * a.ss_units;
+            float ss = 0.f;
+            for (int j0 = part; j0 < a.ss_units; j0 += 16 * 8) {
+                float sv8[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) sv8[j] = live && j0 + 16 * j < a.ss_units ? parts[j0 + 16 * j] : 0.f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) ss += sv8[j];
+            }
+            ss = half_warp_sum(ss);
+            if (part == 0) row_scale[r] = 1.0f / sqrtf(ss * (1.0f / (float)K) + a.eps);
         }
     } else if (few) {
         // a warp to a row (row 8, of zeros, is warp 0's second)
@@ -303,6 +330,13 @@ gemv_rowtile_kernel(GemvArgs a) {
             for (int w = 1; w < WARPS; ++w) v += red[((size_t)(w * NU + warp) * 4 + e) * 32 + lane];
             sum[e] = v;
         }
+        if (kScaled) {  // (written before the two barriers above)
+            const float s_lo = row_scale[lane >> 2], s_hi = row_scale[(lane >> 2) + 8];
+            sum[0] *= s_lo;
+            sum[1] *= s_lo;
+            sum[2] *= s_hi;
+            sum[3] *= s_hi;
+        }
         float best_v[2] = {0.f, 0.f};
         int best_i[2] = {-1, -1};
         epi_finish<EPI>(a, unit0 + warp, row0, lane, sum, pre, true, best_v, best_i);
@@ -326,8 +360,9 @@ static size_t rowtile_smem(int M, int nu, int K, int pro) {
 int gemv_rowtile_units(int M, int N, int K, int epilogue, int pro, int sm_count) {
     if (M <= 0 || M > 128 || K <= 0 || K % 16 || N <= 0 || N % 8) return 0;
     if (epilogue == EPI_ARGMAX) return 0;
-    if (pro == PRO_PLAIN && K > rowtile_direct_steps(true) * 16 * kRowtileWarps) return 0;
-    const bool longk = pro == PRO_PLAIN && K > rowtile_direct_steps(false) * 16 * kRowtileWarps;
+    if (pro != PRO_NORM && K > rowtile_direct_steps(true) * 16 * kRowtileWarps) return 0;
+    if (pro == PRO_SCALED && epilogue != EPI_QKV && epilogue != EPI_GATED) return 0;
+    const bool longk = pro != PRO_NORM && K > rowtile_direct_steps(false) * 16 * kRowtileWarps;
     const int sms = sm_count > 0 ? sm_count : 148;
     const int mtiles = (M + 15) / 16, units = N / 8;
     // With one tile of rows: few units per CTA, and CTAs for at most one and a half SMs'
@@ -375,11 +410,11 @@ static int launch_rowtile_final(const GemvArgs& a, bool pdl, cudaStream_t stream
 template <int EPI, int PRO>
 static int launch_rowtile_units(const GemvArgs& a, int nu, bool pdl, cudaStream_t stream) {
     // (with the norm in front x is in shared memory: one variant for every K)
-    const bool longk = PRO == PRO_PLAIN && a.K > rowtile_direct_steps(false) * 16 * kRowtileWarps;
+    const bool longk = PRO != PRO_NORM && a.K > rowtile_direct_steps(false) * 16 * kRowtileWarps;
     if (longk) {
-        if (nu == 1) return launch_rowtile_final<EPI, PRO, 1, PRO == PRO_PLAIN>(a, pdl, stream);
-        if (nu == 2) return launch_rowtile_final<EPI, PRO, 2, PRO == PRO_PLAIN>(a, pdl, stream);
-        if (nu == 4) return launch_rowtile_final<EPI, PRO, 4, PRO == PRO_PLAIN>(a, pdl, stream);
+        if (nu == 1) return launch_rowtile_final<EPI, PRO, 1, PRO != PRO_NORM>(a, pdl, stream);
+        if (nu == 2) return launch_rowtile_final<EPI, PRO, 2, PRO != PRO_NORM>(a, pdl, stream);
+        if (nu == 4) return launch_rowtile_final<EPI, PRO, 4, PRO != PRO_NORM>(a, pdl, stream);
     } else {
         if (nu == 1) return launch_rowtile_final<EPI, PRO, 1, false>(a, pdl, stream);
         if (nu == 2) return launch_rowtile_final<EPI, PRO, 2, false>(a, pdl, stream);
@@ -395,6 +430,8 @@ int gemv_launch_rowtile(const GemvArgs& a, int epi, int pro, int nu, bool pdl, c
     if (epi == EPI_QKV && pro == PRO_PLAIN) NNIS_ROWTILE(EPI_QKV, PRO_PLAIN);
     if (epi == EPI_GATED && pro == PRO_NORM) NNIS_ROWTILE(EPI_GATED, PRO_NORM);
     if (epi == EPI_GATED && pro == PRO_PLAIN) NNIS_ROWTILE(EPI_GATED, PRO_PLAIN);
+    if (epi == EPI_QKV && pro == PRO_SCALED) NNIS_ROWTILE(EPI_QKV, PRO_SCALED);
+    if (epi == EPI_GATED && pro == PRO_SCALED) NNIS_ROWTILE(EPI_GATED, PRO_SCALED);
     if (epi == EPI_ADD_F32 && pro == PRO_PLAIN) NNIS_ROWTILE(EPI_ADD_F32, PRO_PLAIN);
     if (epi == EPI_STORE && pro == PRO_PLAIN) NNIS_ROWTILE(EPI_STORE, PRO_PLAIN);
     if (epi == EPI_STORE_F32 && pro == PRO_PLAIN) NNIS_ROWTILE(EPI_STORE_F32, PRO_PLAIN);

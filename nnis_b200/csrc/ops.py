@@ -284,14 +284,29 @@ GEMV_HEAD_ROWS = int(os.environ.get("NNIS_GEMV_HEAD_ROWS", "48"))
 
 
 def gemv_kind(m: int, n: int, k: int, epilogue: int = EPI_STORE, device=None, normed: bool = False,
-              rows_kernel: bool = True) -> int:
+              rows_kernel: bool = True, shared_norm: bool = False) -> int:
     """Which decode projection kernel runs this product: 2 the one over tiles of rows, 1
     the one whose CTAs hold all rows, 0 neither (the general kernels must run).
-    ``rows_kernel=False``: as if the first did not exist."""
+    ``rows_kernel=False``: as if the first did not exist.  ``shared_norm``: with the norm
+    before it begun by the projection before that (see ``gemv_bf16``'s ``emit``)."""
     sms = sm_count(device) if device is not None else 148
+    if shared_norm:
+        return int(_lib().nnis_gemv_kind(m, n, k, epilogue, 2, sms)) if rows_kernel else 0
     if not rows_kernel:
         return int(_lib().nnis_gemv_units_takes(m, n, k, epilogue, 1 if normed else 0, sms))
     return int(_lib().nnis_gemv_kind(m, n, k, epilogue, 1 if normed else 0, sms))
+
+
+# A norm between two decode projections, shared out between them (both halves or neither).
+# (bit 0: the norm before a gated feed-forward, bit 1: the norm before q, k, v)
+SHARED_NORM = int(os.environ.get("NNIS_SHARED_NORM", "3"))
+
+
+def gemv_shares_norm(m: int, n: int, k: int, epilogue: int, device=None) -> bool:
+    """Whether the decode projection of these sizes can take its input from the epilogue of
+    the projection before it (``gemv_bf16`` with ``emit`` there and ``shares`` here)."""
+    return bool(SHARED_NORM & (2 if epilogue == EPI_QKV else 1)) \
+        and gemv_kind(m, n, k, epilogue, device, shared_norm=True) == 2
 
 
 def gemv_takes(m: int, n: int, k: int, epilogue: int = EPI_STORE, device=None, normed: bool = False) -> bool:
@@ -328,7 +343,8 @@ def gemv_bf16(w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, 
               head_dim: int = 0, page_size: int = 0, logits: Optional[torch.Tensor] = None,
               scratch: Optional[torch.Tensor] = None, next_tokens: Optional[torch.Tensor] = None,
               next_pos: Optional[torch.Tensor] = None, release_early: bool = False,
-              rows_kernel: bool = True) -> None:
+              rows_kernel: bool = True, emit: Optional[tuple] = None,
+              shares: Optional[torch.Tensor] = None) -> None:
     """A decode-step projection with its prologue and epilogue fused (at most 64
     rows).  The input is ``x`` (bfloat16 [m, k]) or ``hidden`` (float32 residual
     rows, normed with ``norm_weight``/``eps`` on the way in; ``rows`` picks them).
@@ -338,9 +354,16 @@ def gemv_bf16(w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, 
     ``release_early``: the kernel launched after this one may start together with it
     (only for a successor that reads, before its own wait, nothing that a kernel of
     the step writes: attention_decode_tma).  ``rows_kernel=False``: the kernel whose CTAs
-    hold all rows even where the one over tiles of rows applies (for comparisons)."""
+    hold all rows even where the one over tiles of rows applies (for comparisons).
+
+    A norm between two projections can be shared out between them.  ``emit`` (EPI_ADD_F32)
+    is ``(x_next, norm_weight, shares)``: the epilogue also writes the rows it has summed,
+    times ``norm_weight`` (float32 [n]), to ``x_next`` (bfloat16 [m, n]) and every eight
+    columns' sum of squares to ``shares`` (float32 [m, n / 8]).  The projection after it
+    takes ``x=x_next, shares=shares, eps=`` the norm's, and scales its sums by
+    ``1 / sqrt(mean of squares + eps)`` (``gemv_shares_norm`` says whether it can)."""
     _cuda(w, bias, out, x, hidden, norm_weight, rows, token_pos, token_seq, page_table, cos, sin,
-          k_cache, v_cache, logits, scratch, next_tokens, next_pos)
+          k_cache, v_cache, logits, scratch, next_tokens, next_pos, shares, *(emit or ()))
     n, k = w.shape
     _need(w.dtype == torch.bfloat16, "gemv: bfloat16 weights")
     if hidden is not None:
@@ -354,8 +377,24 @@ def gemv_bf16(w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, 
     else:
         _need(x is not None and x.dtype == torch.bfloat16 and x.shape[1] == k, "gemv: x bfloat16 [m, k]")
         m = x.shape[0] if m is None else m
-    _need(gemv_kind(m, n, k, epilogue, w.device, hidden is not None, rows_kernel) > 0,
-          f"gemv: shape m={m} n={n} k={k} is not taken")
+    if shares is not None:
+        _need(hidden is None and eps > 0.0, "gemv: shares come with x and the norm's eps")
+        _need(shares.dtype == torch.float32 and tuple(shares.shape) == (m, k // 8) and shares.is_contiguous(),
+              "gemv: shares float32 [m, k / 8]")
+        _need(gemv_kind(m, n, k, epilogue, w.device, rows_kernel=rows_kernel, shared_norm=True) == 2,
+              f"gemv: shape m={m} n={n} k={k} takes no shared norm")
+    else:
+        _need(gemv_kind(m, n, k, epilogue, w.device, hidden is not None, rows_kernel) > 0,
+              f"gemv: shape m={m} n={n} k={k} is not taken")
+    emit_x = emit_w = emit_ss = None
+    if emit is not None:
+        emit_x, emit_w, emit_ss = emit
+        _need(epilogue == EPI_ADD_F32, "gemv: only the adding epilogue emits")
+        _need(emit_x.dtype == torch.bfloat16 and tuple(emit_x.shape) == (m, n) and emit_x.is_contiguous(),
+              "gemv: emit x bfloat16 [m, n]")
+        _need(emit_w.dtype == torch.float32 and emit_w.numel() == n, "gemv: emit weight float32 [n]")
+        _need(emit_ss.dtype == torch.float32 and tuple(emit_ss.shape) == (m, n // 8) and emit_ss.is_contiguous(),
+              "gemv: emit shares float32 [m, n / 8]")
     if bias is not None:
         _need(bias.dtype == torch.float32 and bias.numel() == n, "gemv: bias float32 [n]")
     if epilogue == EPI_STORE:
@@ -398,7 +437,8 @@ def gemv_bf16(w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, 
         _ptr(x), _ptr(hidden), _ptr(rows), _ptr(norm_weight), ctypes.c_float(eps), _ptr(w), _ptr(bias), _ptr(out), m, n, k, epilogue, _ptr(token_pos), _ptr(token_seq),
         _ptr(page_table), cols, _ptr(cos), _ptr(sin), _ptr(k_cache), _ptr(v_cache), heads, kv_heads,
         head_dim, page_size, _ptr(logits), ctypes.c_void_p(best_val), ctypes.c_void_p(best_idx),
-        ctypes.c_void_p(ticket), _ptr(next_tokens), _ptr(next_pos), _ptr(status_word(w.device)),
+        ctypes.c_void_p(ticket), _ptr(next_tokens), _ptr(next_pos), _ptr(emit_x), _ptr(emit_w),
+        _ptr(emit_ss), _ptr(shares), _ptr(status_word(w.device)),
         sm_count(w.device),
         PDL | (2 if release_early and PDL and EARLY_RELEASE else 0) | (0 if rows_kernel else 4), _stream()),
         "gemv_bf16",

@@ -56,6 +56,20 @@ class StepContext:
     # what the parts asked for with ``step_tables``: device copies and the arrays
     tables: Dict[str, torch.Tensor] = field(default_factory=dict)
     host_tables: Dict[str, object] = field(default_factory=dict)
+    # A norm shared out between the projection before it and the one after it (decode
+    # steps; see ``parts.base.SharedNorm``).  ``next_norm``: set by the model while a block
+    # runs, the norm that the block after it applies first if that block will take it begun.
+    # ``emit_for``: set by a block while one of its parts runs, the norm that reads the
+    # residual after that part.  ``shared_norm``: what the part left, until the block that
+    # owns the norm takes it.
+    next_norm: object = None
+    emit_for: object = None
+    shared_norm: object = None
+
+    def take_shared_norm(self, norm):
+        """What the part before left of ``norm``'s work, or None; nothing is kept."""
+        begun, self.shared_norm = self.shared_norm, None
+        return begun if begun is not None and begun.norm is norm else None
 
     def attention_splits(self, query_rows: int) -> int:
         """How many ways to cut each query's key range so the GPU is full when

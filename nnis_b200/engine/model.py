@@ -118,8 +118,14 @@ class DecoderModel:
     def _run_blocks(self, ctx) -> torch.Tensor:
         hidden = ctx.workspace.get("hidden", (ctx.n_tokens, self.spec.hidden_size), torch.float32)
         self.embedding.forward(ctx.tokens, hidden, self.status)
-        for i, entry in enumerate(self.spec.schedule):
+        schedule = self.spec.schedule
+        for i, entry in enumerate(schedule):
+            # a block may begin the first norm of the block after it, if that one takes it
+            ask = getattr(self.blocks[schedule[i + 1].layer], "first_shared_norm", None) \
+                if i + 1 < len(schedule) else None
+            ctx.next_norm = ask(ctx, ctx.n_tokens) if ask is not None else None
             self.blocks[entry.layer].forward(hidden, ctx, self._views[i])
+        ctx.next_norm = ctx.shared_norm = None
         return hidden
 
     def forward(self, ctx, want_rows: torch.Tensor, logits: torch.Tensor) -> None:

@@ -23,7 +23,7 @@ import torch
 from ..cache import PAGE_SIZE, KVRequest, KVView
 from ..csrc import ops
 from ..weights.loader import WeightSpec
-from .base import MIXERS, POSITIONS, Part
+from .base import MIXERS, POSITIONS, Part, begin_norm
 from .linear import ADD_F32, STORE, linear
 
 
@@ -142,8 +142,18 @@ class Attention(Part):
     def fuses_norm(self, norm, ctx, n: int) -> bool:
         return getattr(norm, "kind", None) == "rmsnorm" and self._decode_kernels(ctx, n, normed=True)
 
+    def shares_norm(self, norm, ctx, n: int) -> bool:
+        """Whether the q, k, v projection can end a norm that the projection before it began."""
+        return (getattr(norm, "kind", None) == "rmsnorm" and self.dtype == torch.bfloat16 and ctx.decode
+                and self.head_dim % 16 == 0 and self.position_in_kernel
+                and ops.gemv_shares_norm(n, self.w_qkv.shape[0], self.hidden, ops.EPI_QKV, self.device))
+
     def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor, cache: KVView) -> None:
         self._run(ctx, residual, cache, x=x)
+
+    def forward_shared(self, begun, residual: torch.Tensor, ctx, cache: KVView) -> None:
+        """The same on rows that the part before left weighted, with their sums of squares."""
+        self._run(ctx, residual, cache, begun=begun)
 
     def forward_normed(self, hidden: torch.Tensor, norm, ctx, cache: KVView) -> None:
         """The same with the block's norm folded into the first projection."""
@@ -165,7 +175,7 @@ class Attention(Part):
                     best = (other[0], fewer)
         return best
 
-    def _run(self, ctx, residual, cache, x=None, hidden=None, norm=None) -> None:
+    def _run(self, ctx, residual, cache, x=None, hidden=None, norm=None, begun=None) -> None:
         n = residual.shape[0]
         d, nq, nkv = self.head_dim, self.heads, self.kv_heads
         ws = ctx.workspace
@@ -179,10 +189,13 @@ class Attention(Part):
         # ... or, with few sequences, short slices whose pages are all in shared memory at once
         tma_splits = ops.attention_decode_tma_plan(
             n, nq, nkv, d, cache.page_size, table.shape[1], self.device, ctx.share) if mma_decode else 0
-        if self._decode_kernels(ctx, n, normed=hidden is not None):
+        if begun is not None or self._decode_kernels(ctx, n, normed=hidden is not None):
             q = ws.get("q", (n, nq * d), self.dtype)
+            if begun is not None:
+                x, norm = begun.x, begun.norm
             ops.gemv_bf16(self.w_qkv, self.b_qkv, q, ops.EPI_QKV, x=x, hidden=hidden,
-                          norm_weight=norm.weight if norm is not None else None,
+                          shares=begun.shares if begun is not None else None,
+                          norm_weight=norm.weight if hidden is not None else None,
                           eps=norm.eps if norm is not None else 0.0, m=n,
                           token_pos=ctx.token_pos, token_seq=ctx.token_seq,
                           page_table=table if self.own_kv else None, cos=cos, sin=sin,
@@ -264,7 +277,8 @@ class Attention(Part):
             ops.attention_generic(q_buf, q_stride, cache.k, cache.v, ctx.token_pos, ctx.token_seq,
                                   table, attn, nq, nkv, d, self.window, self.scale, splits, partial)
         if self._fused_out(ctx, n):
-            ops.gemv_bf16(self.w_o, self.b_o, residual, ops.EPI_ADD_F32, x=attn)
+            ops.gemv_bf16(self.w_o, self.b_o, residual, ops.EPI_ADD_F32, x=attn,
+                          emit=begin_norm(ctx, n, self.hidden))
         else:
             linear(attn, self.w_o, self.b_o, residual, ADD_F32, ws)
 

@@ -12,10 +12,13 @@ registry              interface beyond ``weight_specs`` / ``load``
 ``POSITIONS``         ``rotary_tables()`` -> (cos, sin) or None, and, for an
                       encoding with arithmetic of its own (``in_kernel = False``),
                       ``apply(qkv, ctx, heads, kv_heads, head_dim)``
-``MIXERS``            ``cache_request()``; ``forward(x, ctx, residual, cache)``
-``FEED_FORWARDS``     ``forward(x, ctx, residual)``
+``MIXERS``            ``cache_request()``; ``forward(x, ctx, residual, cache)``;
+                      optionally ``fuses_norm``/``forward_normed`` and
+                      ``shares_norm``/``forward_shared`` (see ``SharedNorm``)
+``FEED_FORWARDS``     ``forward(x, ctx, residual)``; optionally the same
 ``BLOCKS``            ``forward(hidden_f32, ctx, cache)``; ``parts()``;
-                      ``cache_request()``, ``check_shared_cache(view)``
+                      ``cache_request()``, ``check_shared_cache(view)``;
+                      optionally ``first_shared_norm(ctx, n)``
 ``EMBEDDINGS``        ``forward(tokens, hidden_f32, status)``
 ``HEADS``             ``forward(x, logits_f32)``; optionally ``fuses_norm``,
                       ``forward_normed``, ``forward_pick`` (see ``LinearHead``)
@@ -27,11 +30,44 @@ float32 in every dtype, and a fused epilogue may add in place.
 """
 from __future__ import annotations
 
+from dataclasses import dataclass
 from typing import Any, Callable, Dict, Mapping, Optional
 
 import torch
 
 from ..weights.loader import WeightSpec
+
+
+@dataclass
+class SharedNorm:
+    """A norm of the residual rows begun by the part that wrote them last.
+
+    In a decode step the kernel that adds a part's output to the residual has the new
+    values in registers.  When the block tells it which norm reads them next
+    (``ctx.emit_for``) and that norm is an RMSNorm, it can also write ``x`` = the rows times
+    the norm's weights (bfloat16 [n, width]) and ``shares`` = every eight columns' sum of
+    squares (float32 [n, width / 8]); the part after the norm then runs its first
+    projection on ``x`` and multiplies its float32 sums by 1 / sqrt(mean of squares + eps):
+    the same sum with one rounding moved.  Offered by a part through ``begin_norm`` when it
+    runs its last projection as a decode kernel; taken by a part that has
+    ``shares_norm(norm, ctx, n)`` and ``forward_shared(begun, residual, ctx[, cache])``.
+    Nothing breaks if no part offers or takes it: the block falls back to the norm."""
+    norm: Any
+    x: torch.Tensor
+    shares: torch.Tensor
+
+
+def begin_norm(ctx, n: int, width: int):
+    """For a part about to add ``[n, width]`` to the residual with a decode kernel: the
+    ``emit`` argument of ``ops.gemv_bf16`` if the block named the norm that follows
+    (``ctx.emit_for``), else None.  Leaves the ``SharedNorm`` in the context."""
+    norm = getattr(ctx, "emit_for", None)
+    if norm is None or getattr(norm, "kind", None) != "rmsnorm" or width % 8:
+        return None
+    x = ctx.workspace.get("normed_shared", (n, width), torch.bfloat16)
+    shares = ctx.workspace.get("norm_shares", (n, width // 8), torch.float32)
+    ctx.shared_norm = SharedNorm(norm, x, shares)
+    return (x, norm.weight, shares)
 
 
 class Part:

@@ -8,7 +8,9 @@ class registered in ``BLOCKS``, not a change here.
 
 ``prenorm``: h += mixer(norm1(h)); h += ffn(norm2(h)) - the order of NNIS's
 decoder (crates/nnis-model/src/runtime.rs:946-1097); roles mixer_norm, mixer,
-ffn_norm, ffn.
+ffn_norm, ffn.  In decode steps a norm may be shared out between the projections on
+either side of it (``parts.base.SharedNorm``): the block tells the part before a norm
+which norm follows, and hands what that part left to the part after it.
 """
 from __future__ import annotations
 
@@ -85,20 +87,40 @@ class PreNormBlock(Block):
     def parts(self):
         return (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn)
 
+    @staticmethod
+    def _shares(part, norm, ctx, n: int) -> bool:
+        return bool(getattr(part, "shares_norm", None)) and part.shares_norm(norm, ctx, n)
+
+    def first_shared_norm(self, ctx, n: int):
+        """The norm this block applies first, if its mixer will take it begun by the part
+        that runs before this block (asked by the model before that part runs)."""
+        return self.mixer_norm if self._shares(self.mixer, self.mixer_norm, ctx, n) else None
+
     def forward(self, hidden: torch.Tensor, ctx, cache) -> None:
         n, width = hidden.shape
         normed = ctx.workspace.get("normed", (n, width), self.dtype)
+        begun = ctx.take_shared_norm(self.mixer_norm)
+        # the mixer's last projection may begin the norm before the feed-forward
+        ctx.emit_for = self.ffn_norm if self._shares(self.ffn, self.ffn_norm, ctx, n) else None
+        if begun is not None:
+            self.mixer.forward_shared(begun, hidden, ctx, cache)
         # a part may fold the norm before it into its first kernel (decode steps)
-        if getattr(self.mixer, "fuses_norm", None) and self.mixer.fuses_norm(self.mixer_norm, ctx, n):
+        elif getattr(self.mixer, "fuses_norm", None) and self.mixer.fuses_norm(self.mixer_norm, ctx, n):
             self.mixer.forward_normed(hidden, self.mixer_norm, ctx, cache)
         else:
             self.mixer_norm.forward(hidden, normed)
             self.mixer.forward(normed, ctx, hidden, cache)
-        if getattr(self.ffn, "fuses_norm", None) and self.ffn.fuses_norm(self.ffn_norm, ctx, n):
+        begun = ctx.take_shared_norm(self.ffn_norm)
+        # ... and the feed-forward's the first norm of the block that runs next
+        ctx.emit_for = ctx.next_norm
+        if begun is not None:
+            self.ffn.forward_shared(begun, hidden, ctx)
+        elif getattr(self.ffn, "fuses_norm", None) and self.ffn.fuses_norm(self.ffn_norm, ctx, n):
             self.ffn.forward_normed(hidden, self.ffn_norm, ctx)
         else:
             self.ffn_norm.forward(hidden, normed)
             self.ffn.forward(normed, ctx, hidden)
+        ctx.emit_for = None
 
 
 BLOCKS.register("prenorm", PreNormBlock)

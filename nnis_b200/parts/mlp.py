@@ -16,7 +16,7 @@ import torch
 
 from ..csrc import ops
 from ..weights.loader import WeightSpec
-from .base import FEED_FORWARDS, Part
+from .base import FEED_FORWARDS, Part, begin_norm
 from .linear import ADD_F32, STORE_F32, linear
 
 
@@ -71,18 +71,30 @@ class GatedMLP(Part):
     def fuses_norm(self, norm, ctx, n: int) -> bool:
         return getattr(norm, "kind", None) == "rmsnorm" and self._fused_gate_up(ctx, n, normed=True)
 
+    def shares_norm(self, norm, ctx, n: int) -> bool:
+        """Whether gate/up can end a norm that the projection before it began."""
+        return (getattr(norm, "kind", None) == "rmsnorm" and self.dtype == torch.bfloat16 and ctx.decode
+                and ops.gemv_shares_norm(n, 2 * self.inter, self.hidden, ops.EPI_GATED, self.device))
+
     def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor) -> None:
         self._run(ctx, residual, x=x)
+
+    def forward_shared(self, begun, residual: torch.Tensor, ctx) -> None:
+        """The same on rows that the part before left weighted, with their sums of squares."""
+        self._run(ctx, residual, begun=begun)
 
     def forward_normed(self, hidden: torch.Tensor, norm, ctx) -> None:
         """The same with the block's norm folded into the gate/up projection."""
         self._run(ctx, hidden, hidden=hidden, norm=norm)
 
-    def _run(self, ctx, residual, x=None, hidden=None, norm=None) -> None:
+    def _run(self, ctx, residual, x=None, hidden=None, norm=None, begun=None) -> None:
         n = residual.shape[0]
         ws = ctx.workspace
         act = ws.get("act", (n, self.inter), self.dtype)
-        if self._fused_gate_up(ctx, n, normed=hidden is not None):
+        if begun is not None:
+            ops.gemv_bf16(self.w_gu, self.b_gu, act, ops.EPI_GATED, x=begun.x, shares=begun.shares,
+                          eps=begun.norm.eps, m=n)
+        elif self._fused_gate_up(ctx, n, normed=hidden is not None):
             ops.gemv_bf16(self.w_gu, self.b_gu, act, ops.EPI_GATED, x=x, hidden=hidden,
                           norm_weight=norm.weight if norm is not None else None,
                           eps=norm.eps if norm is not None else 0.0, m=n)
@@ -94,7 +106,8 @@ class GatedMLP(Part):
             linear(x, self.w_gu, self.b_gu, gate_up, STORE_F32)
             ops.silu_mul(gate_up, act)
         if self._fused_down(ctx, n):
-            ops.gemv_bf16(self.w_down, self.b_down, residual, ops.EPI_ADD_F32, x=act)
+            ops.gemv_bf16(self.w_down, self.b_down, residual, ops.EPI_ADD_F32, x=act,
+                          emit=begin_norm(ctx, n, self.hidden))
         else:
             linear(act, self.w_down, self.b_down, residual, ADD_F32, ws)
 

@@ -493,8 +493,15 @@ def test_gemv_qkv_epilogue_rotates_and_stores(nq, nkv, d, rotate, copies, rows_k
                 cos=cos.float().to(DEV) if rotate else None, sin=sin.float().to(DEV) if rotate else None,
                 k_cache=kc if nkv else None, v_cache=vc if nkv else None, heads=nq, kv_heads=nkv,
                 head_dim=d, page_size=page, rows_kernel=rows_kernel)
-    y = P.linear(x, w, bias).bfloat16().double()
-    for i in range(m):
+    _qkv_matches(P.linear(x, w, bias), q_out, kc, vc, pos, seq, table, nq, nkv, d, page, rotate, copies)
+
+
+def _qkv_matches(y, q_out, kc, vc, pos, seq, table, nq, nkv, d, page, rotate, copies):
+    """`y` [m, (nq + 2 nkv) d], the projection's output before rounding and rotation,
+    against what the QKV epilogue left in `q_out` and the caches."""
+    cos, sin = P.rope_tables(200, d, 10000.0)
+    y = y.bfloat16().double()
+    for i in range(y.shape[0]):
         p = int(pos[i])
         if p < 0:
             assert float((q_out[i].float() - 9.0).abs().max()) == 0  # padding row untouched
@@ -511,6 +518,90 @@ def test_gemv_qkv_epilogue_rotates_and_stores(nq, nkv, d, rotate, copies, rows_k
             close(vc[pg, :, p % page], heads[nq + nkv:], "bfloat16", "v")
     if nkv:
         assert int((kc.float().abs().sum(-1) > 0).sum()) == 4 * nkv * copies  # nothing else was written
+
+
+@pytest.mark.parametrize("m", [1, 8, 11, 16, 40, 100])
+@pytest.mark.parametrize("width,inter", [(576, 1536), (80, 112), (1536, 3072), (960, 2560)])
+def test_gemv_shares_a_norm_between_two_projections(m, width, inter):
+    """The adding epilogue begins the norm that follows it (rows times the norm's weights,
+    shares of the sums of squares); the gated and the QKV projection end it on their sums.
+    The rows differ in size by factors up to 13, so that a row scaled by another row's
+    factor would show."""
+    o = ops()
+    g = torch.Generator().manual_seed(m + width)
+    eps = 1e-5
+    w_down = (torch.randn(width, inter, generator=g) / math.sqrt(inter)).bfloat16()
+    x = torch.randn(m, inter, generator=g).bfloat16()
+    size = 1.0 + 3.0 * (torch.arange(m) % 5).double()
+    x = (x.double() * size[:, None]).bfloat16()
+    base = torch.randn(m, width, generator=g) * size[:, None].float()
+    nw = 1 + 0.1 * torch.randn(width, generator=g)
+    want = base.double() + P.linear(x, w_down)
+    took = 0
+    for rows_kernel in (True, False):
+        if not o.gemv_kind(m, width, inter, o.EPI_ADD_F32, DEV, rows_kernel=rows_kernel):
+            continue
+        took += 1
+        acc = base.to(DEV).clone()
+        x_next = torch.full((m, width), 7.0, dtype=torch.bfloat16, device=DEV)
+        shares = torch.full((m, width // 8), -1.0, device=DEV)
+        o.gemv_bf16(w_down.to(DEV), None, acc, o.EPI_ADD_F32, x=x.to(DEV), rows_kernel=rows_kernel,
+                    emit=(x_next, nw.to(DEV), shares))
+        close(acc, want, "float32", "gemv add that emits")
+        # of the sums as the kernel has them: the weighted rows to the bit, the squares to rounding
+        assert torch.equal(x_next, (acc * nw.to(DEV)).bfloat16())
+        close(shares, acc.double().view(m, width // 8, 8).square().sum(-1), "float32", "shares of the squares")
+    if not took:
+        assert m > 64 and inter > 1536  # neither kernel: the general product runs, which shares no norm
+        return
+    if not o.gemv_shares_norm(m, 2 * inter, width, o.EPI_GATED, DEV):
+        # more CTAs over tiles of rows than are resident at once
+        assert (m > 64 or inter > 1536) and width != 80
+        return
+    # the norm with its one rounding where the kernels have it: on the weighted rows, before the scale
+    hidden = acc.cpu().double()
+    normed = x_next.cpu().double() / torch.sqrt(hidden.square().mean(-1, keepdim=True) + eps)
+    close(normed, P.rms_norm(acc.cpu(), nw, eps), "bfloat16", "the rows normed in two halves")
+    w_gu = (torch.randn(2 * inter, width, generator=g) / math.sqrt(width) * 3).bfloat16()
+    bias = torch.randn(2 * inter, generator=g)
+    out = torch.empty(m, inter, dtype=torch.bfloat16, device=DEV)
+    o.gemv_bf16(w_gu.to(DEV), bias.to(DEV), out, o.EPI_GATED, x=x_next, shares=shares, eps=eps)
+    y = P.linear(normed, w_gu, bias)
+    close(out, P.swiglu(y[:, :inter], y[:, inter:]), "bfloat16", "gemv gated after a shared norm")
+    # the QKV projection: rows at positions of their own, one of five a padding row
+    nq, nkv, d, page = 3, 1, 32, 64
+    n = (nq + 2 * nkv) * d
+    assert o.gemv_shares_norm(m, n, width, o.EPI_QKV, DEV)
+    copies = (m + 4) // 5
+    pos = torch.tensor([0, 63, 64, -1, 130] * copies, dtype=torch.int32)[:m]
+    seq = torch.cat([torch.tensor([0, 1, 2, 0, 3], dtype=torch.int32) + 4 * c for c in range(copies)])[:m]
+    tbl = torch.tensor([[5, -1, -1], [2, -1, -1], [7, 1, -1], [0, 3, 4]], dtype=torch.int32)
+    table = torch.cat([torch.where(tbl >= 0, tbl + 8 * c, tbl) for c in range(copies)])
+    kc = torch.zeros(8 * copies, nkv, page, d, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    cos, sin = P.rope_tables(200, d, 10000.0)
+    w_qkv = (torch.randn(n, width, generator=g) / math.sqrt(width)).bfloat16()
+    bias = torch.randn(n, generator=g)
+    q_out = torch.full((m, nq * d), 9.0, dtype=torch.bfloat16, device=DEV)
+    o.gemv_bf16(w_qkv.to(DEV), bias.to(DEV), q_out, o.EPI_QKV, x=x_next, shares=shares, eps=eps,
+                token_pos=pos.to(DEV), token_seq=seq.to(DEV), page_table=table.to(DEV),
+                cos=cos.float().to(DEV), sin=sin.float().to(DEV), k_cache=kc, v_cache=vc, heads=nq,
+                kv_heads=nkv, head_dim=d, page_size=page)
+    y = P.linear(normed, w_qkv, bias)
+    live = int((pos >= 0).sum())
+    for i in range(m):
+        p = int(pos[i])
+        if p < 0:
+            assert float((q_out[i].float() - 9.0).abs().max()) == 0
+            continue
+        heads = y[i].bfloat16().double().view(nq + 2 * nkv, d)
+        close(q_out[i].view(nq, d), P.rope_rotate_half(heads[:nq][None], cos[p:p + 1], sin[p:p + 1])[0],
+              "bfloat16", "q after a shared norm")
+        pg = int(table[int(seq[i]), p // page])
+        close(kc[pg, :, p % page], P.rope_rotate_half(heads[nq:nq + nkv][None], cos[p:p + 1], sin[p:p + 1])[0],
+              "bfloat16", "k after a shared norm")
+        close(vc[pg, :, p % page], heads[nq + nkv:], "bfloat16", "v after a shared norm")
+    assert int((kc.float().abs().sum(-1) > 0).sum()) == live * nkv
 
 
 def test_gemv_refuses_what_it_does_not_take():

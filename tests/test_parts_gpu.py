@@ -4,6 +4,7 @@ position encoding), registered, built and stepped without touching the
 framework's files."""
 import math
 
+import numpy as np
 import pytest
 import torch
 
@@ -629,3 +630,46 @@ def test_toy_arrangement_positions_embedding_and_head_need_no_change_to_the_fram
     for _ in range(5):
         toks.append(P.argmax_lowest(plain(toks)[-1]))
     assert res.ok and res.token_ids == toks[4:]
+
+
+# ---------------------------------------------------------------------------
+# A norm shared out between the projections on either side of it (decode steps)
+# ---------------------------------------------------------------------------
+def test_norms_are_shared_between_projections_where_both_sides_take_them(tmp_path, monkeypatch):
+    """Three layers: in a decode step every norm but the first and the last is begun by the
+    projection before it (five of them), the logits match the plain implementation as they
+    do with the norms run whole, and a mixer that knows nothing of it is left alone."""
+    from helpers import TINY_B, load_plain_weights, make_model, read_config_json
+    from nnis_b200 import LLM
+    from nnis_b200.csrc import ops
+    d = make_model(str(tmp_path), TINY_B, seed=77)
+    cfg, w = read_config_json(d), load_plain_weights(d, as_bf16=True)
+    ids = [5, 9, 1, 200, 33, 17, 4, 4, 250, 3, 99]
+    want = P.forward(cfg, w, ids, True)
+    seen = {"emit": 0, "shares": 0}
+    real = ops.gemv_bf16
+
+    def counting(*args, **kwargs):
+        seen["emit"] += kwargs.get("emit") is not None
+        seen["shares"] += kwargs.get("shares") is not None
+        return real(*args, **kwargs)
+
+    monkeypatch.setattr(ops, "gemv_bf16", counting)
+    got = {}
+    for shared in (3, 0):
+        monkeypatch.setattr(ops, "SHARED_NORM", shared)
+        seen.update(emit=0, shares=0)
+        llm = LLM(d, dtype="bfloat16", max_tokens=64 * 4, max_batch=2)
+        session = llm.new_session()
+        rows = [session.prefill(ids[:6])]
+        assert seen == {"emit": 0, "shares": 0}  # a prompt step shares nothing
+        rows += [session.decode_one(t) for t in ids[6:]]
+        steps = len(ids) - 6
+        layers = cfg["num_hidden_layers"]
+        assert seen == ({"emit": steps * (2 * layers - 1), "shares": steps * (2 * layers - 1)} if shared
+                        else {"emit": 0, "shares": 0})
+        got[shared] = np.stack(rows)
+        check_logits(got[shared], want[5:], "bfloat16", f"shared norms {shared}")
+        session.close()
+    # the two ways differ by roundings only
+    assert np.abs(got[3] - got[0]).max() <= 0.03 * max(1.0, float(np.abs(got[0]).max()))

@@ -83,3 +83,84 @@ def test_bench_sums_a_traced_step_per_kernel():
     got = bench.kernel_times(["a", "b", "a"], rows)
     assert got["a"] == {"launches": 2, "us": 3.5} and got["b"] == {"launches": 1, "us": 4.0}
     assert got["step"] == {"launches": 3, "us": 8.5}
+
+
+def test_a_begun_norm_is_handed_on_once_and_only_to_the_block_that_owns_it():
+    """What a part leaves of a norm in the step's context: taken by the norm it names,
+    dropped when another norm asks first, never seen twice; and the prenorm arrangement
+    offers a norm only where the part after it says it takes it."""
+    import torch
+    from nnis_b200.engine.context import StepContext
+    from nnis_b200.parts.base import SharedNorm, begin_norm
+    from nnis_b200.parts.block import PreNormBlock
+    empty = torch.zeros(0, dtype=torch.int32)
+
+    class Space:
+        def get(self, name, shape, dtype):
+            return torch.zeros(shape, dtype=dtype)
+
+    ctx = StepContext(n_tokens=0, n_seqs=0, tokens=empty, token_pos=empty, token_seq=empty,
+                      seq_slots=empty, page_tables=[], workspace=Space(), decode=True, max_context=1)
+
+    class Norm:
+        kind = "rmsnorm"
+        weight = torch.ones(16)
+        eps = 1e-5
+
+    a, b = Norm(), Norm()
+    assert begin_norm(ctx, 3, 16) is None and ctx.shared_norm is None  # no block asked for it
+    ctx.emit_for = a
+    x, weight, shares = begin_norm(ctx, 3, 16)
+    assert x.shape == (3, 16) and x.dtype == torch.bfloat16 and shares.shape == (3, 2) and weight is a.weight
+    assert isinstance(ctx.shared_norm, SharedNorm)
+    assert ctx.take_shared_norm(a).x is x and ctx.take_shared_norm(a) is None
+    begin_norm(ctx, 3, 16)
+    assert ctx.take_shared_norm(b) is None and ctx.take_shared_norm(a) is None  # dropped, not kept
+    assert begin_norm(ctx, 3, 12) is None  # a width that is no multiple of eight
+    other = Norm()
+    other.kind = "layernorm"
+    ctx.emit_for = other
+    assert begin_norm(ctx, 3, 16) is None
+
+    # the arrangement: which norm each part is told about, and what reaches the parts
+    calls = []
+
+    class Mixer:
+        def forward(self, x, ctx, residual, cache):
+            calls.append(("mixer", ctx.emit_for))
+
+    class SharingFfn:
+        def shares_norm(self, norm, ctx, n):
+            return True
+
+        def forward(self, x, ctx, residual):
+            calls.append(("ffn", ctx.emit_for))
+
+        def forward_shared(self, begun, residual, ctx):
+            calls.append(("ffn shared", begun.norm))
+
+    class PlainNorm(Norm):
+        def forward(self, hidden, out, rows=None):
+            pass
+
+    block = PreNormBlock.__new__(PreNormBlock)
+    block.dtype = torch.bfloat16
+    block.mixer_norm, block.ffn_norm = PlainNorm(), PlainNorm()
+    block.mixer, block.ffn = Mixer(), SharingFfn()
+    ctx.emit_for = None
+    ctx.next_norm = a
+    hidden = torch.zeros(3, 16)
+    assert block.first_shared_norm(ctx, 3) is None  # this mixer takes no begun norm
+    block.forward(hidden, ctx, None)
+    # the mixer was told of the feed-forward's norm and left nothing: the norm ran whole;
+    # the feed-forward was told of the next block's first norm
+    assert calls == [("mixer", block.ffn_norm), ("ffn", a)] and ctx.emit_for is None
+
+    class EmittingMixer(Mixer):
+        def forward(self, x, ctx, residual, cache):
+            begin_norm(ctx, 3, 16)
+
+    calls.clear()
+    block.mixer = EmittingMixer()
+    block.forward(hidden, ctx, None)
+    assert calls == [("ffn shared", block.ffn_norm)] and ctx.shared_norm is None
