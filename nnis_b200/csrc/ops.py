@@ -506,7 +506,8 @@ def attention_decode_tma_plan(n: int, heads: int, kv_heads: int, head_dim: int, 
     sequences, or 0 when the step is not for that kernel: it takes head sizes 64 and 128 and
     only steps whose CTAs are all resident together (few sequences, or short contexts);
     other steps stream their slices through the ring of attention_decode_mma.  Slices are of
-    four pages (more for page tables beyond 64 x 4 columns, up to what fits); when that makes
+    four pages (more for page tables beyond 64 x 4 columns, up to what fits; with more than 16
+    slices of four pages, of eight or six pages where those CTAs are resident); when four pages make
     more CTAs than two per SM, of six pages if those CTAs are resident two to an SM: fewer
     partial records and fewer CTAs that wait for room beside the projection's (batch 8 of the
     135M shape: 0.637 -> 0.618 ms a step; at batch 1, where CTAs are few, four pages are
@@ -531,6 +532,15 @@ def attention_decode_tma_plan(n: int, heads: int, kv_heads: int, head_dim: int, 
         splits, ctas, fit = plan(TMA_SLICE_PAGES)
         return splits if 0 < ctas <= fit * sms else 0
     splits, ctas, fit = plan(4)
+    if splits > 16:
+        # The slice that arrives last asks for 16 partial records a trip to L2: beyond 16 slices
+        # (contexts beyond 4,096) the longest slices whose CTAs are still all resident, eight pages
+        # one to an SM or six pages two to an SM (one sequence at context 16,384: 0.592 -> 0.512 ms
+        # a step, two at 8,192: 0.540 -> 0.493)
+        for pages in (8, 6):
+            long_splits, long_ctas, long_fit = plan(pages)
+            if 0 < long_ctas <= min(long_fit, 2) * sms:
+                return long_splits
     if ctas > 2 * sms:
         wide, wide_ctas, wide_fit = plan(6)
         if 0 < wide_ctas <= min(wide_fit, 2) * sms:

@@ -810,6 +810,71 @@ def test_attention_decode_fed_by_tma(nq, nkv, d, window):
     assert o.attention_decode_tma_plan(2, nq, nkv, 48, 64, 8, DEV) == 0
 
 
+def test_attention_decode_fed_by_tma_long_contexts_in_many_slices():
+    """Contexts of thousands of keys in 16 to 64 slices (eight pages down to two a slice): the
+    slice that arrives last merges more records than it asks for in one trip.  In every
+    sequence one far key (a few hundred keys in) is made to stand out for one head, so that a
+    slice left out of a merge would change the result; the same for the newest key."""
+    o = ops()
+    nq, nkv, d = 9, 3, 64
+    lengths = [8192, 5003, 4097]
+    case = PagedCase(lengths, [1] * len(lengths), nq, nkv, d, "bfloat16", seed=21)
+    for s, L in enumerate(lengths):
+        far = 300 + 700 * s
+        q_far = case.q[s][L - 1, (s % nkv) * 3]
+        # (a score two above the logarithm of the sum of all others: some nine tenths of the weight)
+        score = math.log(1.65 * L) + 2.0
+        case.k[s][far, s % nkv] = (q_far * (score * math.sqrt(d) / float(q_far.square().sum()))).bfloat16().float()
+        case.v[s][far] = 7.0
+    case.fill_cache()
+    for s, L in enumerate(lengths):
+        pg = int(case.table[s, (L - 1) // 64])
+        case.k_cache[pg, :, (L - 1) % 64] = case.k[s][L - 1]
+        case.v_cache[pg, :, (L - 1) % 64] = case.v[s][L - 1]
+    pos, seq, q, _, _ = case.packed()
+    n = pos.numel()
+    qd = q.reshape(n, -1).bfloat16().to(DEV)
+    kc, vc = case.k_cache.bfloat16().to(DEV), case.v_cache.bfloat16().to(DEV)
+
+    def newest_query(q_last, k, v):
+        """The plain function's last row alone (it is quadratic in the length): every key is
+        visible to the newest query."""
+        out = torch.empty(nq, d, dtype=torch.float64)
+        for hq in range(nq):
+            hk = hq // (nq // nkv)
+            p = torch.softmax((k[:, hk].double() @ q_last[hq].double()) / math.sqrt(d), dim=0)
+            out[hq] = p @ v[:, hk].double()
+        return out
+
+    short = slice(0, 130)
+    close(newest_query(case.q[0][129], case.k[0][short], case.v[0][short]),
+          P.causal_attention(case.q[0][short], case.k[0][short], case.v[0][short])[-1], "float32", "the last row")
+    want = torch.cat([newest_query(case.q[s][L - 1], case.k[s], case.v[s].bfloat16().float()).reshape(1, -1)
+                      for s, L in enumerate(lengths)])
+    # the far key decides its head's output: most of the weight lies on it
+    assert all(float(want[s, (s % nkv) * 3 * d:(s % nkv) * 3 * d + d].mean()) > 4.5 for s in range(len(lengths)))
+    cols = case.table.shape[1]
+    assert cols == 128
+    tickets = torch.zeros(o.mma_ticket_count(n, nq, nkv), dtype=torch.int32, device=DEV)
+    for splits in (16, 22, 32, 43, 64):
+        out = torch.full((n, nq * d), 5.0, dtype=torch.bfloat16, device=DEV)
+        partial = torch.full((n * nq * splits * (d + 2),), float("nan"), device=DEV)
+        for _ in range(2):  # (the tickets come back to zero: a second launch finds them so)
+            o.attention_decode_tma(qd, nq * d, kc, vc, pos.to(DEV), seq.to(DEV), case.table.to(DEV), out,
+                                   nq, nkv, d, 0, 1.0 / math.sqrt(d), splits, partial, tickets)
+        close(out, want, "bfloat16", f"decode attention by TMA, {splits} slices of a long context")
+        assert int(tickets.abs().sum()) == 0
+    o.check_status(DEV)
+    # the plan: beyond 16 slices of four pages, the longest slices whose CTAs are all resident
+    assert o.attention_decode_tma_plan(1, nq, nkv, d, 64, 128, DEV) == 16   # eight pages, 48 CTAs
+    assert o.attention_decode_tma_plan(3, nq, nkv, d, 64, 128, DEV) == 16   # 144 CTAs, one to an SM
+    assert o.attention_decode_tma_plan(4, nq, nkv, d, 64, 128, DEV) == 22   # six pages, two to an SM
+    assert o.attention_decode_tma_plan(1, nq, nkv, d, 64, 256, DEV) == 32
+    assert o.attention_decode_tma_plan(2, nq, nkv, d, 64, 256, DEV) == 43
+    assert o.attention_decode_tma_plan(3, nq, nkv, d, 64, 256, DEV) == 0    # the ring kernel's
+    assert o.attention_decode_tma_plan(8, nq, nkv, d, 64, 64, DEV) == 11    # (as before at 4,096)
+
+
 def test_attention_decode_fed_by_tma_with_more_ctas_than_two_per_sm():
     """Many sequences: more CTAs than two per SM (three fill an SM's registers, so the last
     of them start when the first have left); the same results."""
