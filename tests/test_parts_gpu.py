@@ -673,3 +673,115 @@ def test_norms_are_shared_between_projections_where_both_sides_take_them(tmp_pat
         session.close()
     # the two ways differ by roundings only
     assert np.abs(got[3] - got[0]).max() <= 0.03 * max(1.0, float(np.abs(got[0]).max()))
+
+
+# ---------------------------------------------------------------------------
+# A toy norm (mean and variance, weight and bias), registered from here: the parts around
+# it may fold or share an RMSNorm but must leave any other norm to itself.
+# ---------------------------------------------------------------------------
+def _register_toy_norm():
+    from nnis_b200.parts import NORMS
+    from nnis_b200.parts.base import Part
+    from nnis_b200.weights.loader import WeightSpec
+
+    class CenteredNorm(Part):
+        kind = "toy_centered_norm"
+
+        def __init__(self, params, prefix, dtype, device):
+            super().__init__(params, prefix, dtype, device)
+            self.size, self.eps = int(params["size"]), float(params["eps"])
+            self.stem = params["name"]
+            self.weight = self.bias = None
+
+        def weight_specs(self):
+            return {self.tensor_name(self.stem): WeightSpec((self.size,), "vector", init="ones"),
+                    self.tensor_name(self.stem, "bias"): WeightSpec((self.size,), "vector")}
+
+        def load(self, tensors):
+            self.weight = tensors[self.tensor_name(self.stem)]
+            self.bias = tensors[self.tensor_name(self.stem, "bias")]
+
+        def forward(self, x, out, rows=None):
+            x = x if rows is None else x[rows.long()]
+            centered = x - x.mean(-1, keepdim=True)
+            out.copy_(centered / torch.sqrt(centered.square().mean(-1, keepdim=True) + self.eps)
+                      * self.weight + self.bias)
+
+    NORMS.register("toy_centered_norm", CenteredNorm)
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+def test_a_toy_norm_runs_beside_norms_that_are_folded_and_shared(dtype, monkeypatch):
+    """Layer 0 has the toy norm twice, layer 1 RMSNorms.  In a bfloat16 decode step the toy
+    norms run as they are (no projection folds or shares them), the first RMSNorm of layer 1 is
+    begun by layer 0's down projection and the second by layer 1's O projection: two norms
+    change hands a step.  Prompts of unequal length, then single tokens, against the plain
+    functions."""
+    from nnis_b200.csrc import ops
+    from nnis_b200.engine import Engine, SequenceStep
+    from nnis_b200.engine.model import DecoderModel
+    from nnis_b200.weights import random_tensors
+    _register_toy_norm()
+    H, V, I, nq, nkv, d, eps = 64, 96, 112, 4, 2, 16, 1e-5
+    rms = lambda name: PartSpec("rmsnorm", {"size": H, "eps": eps, "name": name})
+    toy = lambda name: PartSpec("toy_centered_norm", {"size": H, "eps": eps, "name": name})
+    names = {"q": "self_attn.q_proj", "k": "self_attn.k_proj", "v": "self_attn.v_proj", "o": "self_attn.o_proj"}
+    attn = PartSpec("attention", dict(attention_params(H, nq, nkv, d), names=names))
+    mlp = PartSpec("gated_mlp", {"hidden_size": H, "intermediate_size": I, "activation": "silu", "bias": False,
+                                 "names": {"gate": "mlp.gate_proj", "up": "mlp.up_proj", "down": "mlp.down_proj"}})
+    layers = (prenorm_layer("l0", toy("n1"), attn, toy("n2"), mlp),
+              prenorm_layer("l1", rms("n1"), attn, rms("n2"), mlp))
+    spec = ModelSpec(architecture="ToyNorm", hidden_size=H, vocab_size=V, max_positions=512,
+                     embedding=PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H, "name": "emb"}),
+                     layers=layers, schedule=(ScheduleEntry(0), ScheduleEntry(1)), final_norm=rms("final"),
+                     head=PartSpec("linear_head", {"vocab_size": V, "hidden_size": H, "name": "head",
+                                                   "tied_to": "emb"}))
+    wanted = DecoderModel.weight_specs_of(spec)
+    assert "l0.n1.bias" in wanted and "l1.n1.bias" not in wanted
+    w = random_tensors(wanted, seed=31, std=1.0, norm_std=0.1, std_by_fan_in=True)
+    bf = dtype == "bfloat16"
+    engine = Engine.from_spec(spec, w, dtype=dtype, max_tokens=64 * 8, max_slots=2)
+    pw = {k: (v.bfloat16().double() if bf and v.dim() == 2 else v.double()) for k, v in w.items()}
+    cfg = {"hidden_size": H, "num_attention_heads": nq, "num_key_value_heads": nkv, "head_dim": d}
+    cos, sin = P.rope_tables(512, d, 10000.0)
+
+    def plain(tokens):
+        h = pw["emb.weight"][torch.tensor(tokens)]
+        for prefix in ("l0", "l1"):
+            for norm_name, part in (("n1", "attention"), ("n2", "mlp")):
+                if prefix == "l0":
+                    c = h - h.mean(-1, keepdim=True)
+                    n = c / torch.sqrt(c.square().mean(-1, keepdim=True) + eps)
+                    n = n * pw[f"l0.{norm_name}.weight"] + pw[f"l0.{norm_name}.bias"]
+                else:
+                    n = P.rms_norm(h, pw[f"l1.{norm_name}.weight"], eps)
+                n = P._round(n, bf)
+                if part == "attention":
+                    h = h + P.attention_layer(cfg, pw, prefix + ".self_attn.", n, cos, sin, bf)
+                else:
+                    h = h + P.mlp_layer(cfg, pw, prefix + ".mlp.", n, bf)
+        return P.linear(P._round(P.rms_norm(h, pw["final.weight"], eps), bf), pw["emb.weight"])
+
+    seen = {"emit": 0, "shares": 0}
+    real = ops.gemv_bf16
+
+    def counting(*args, **kwargs):
+        seen["emit"] += kwargs.get("emit") is not None
+        seen["shares"] += kwargs.get("shares") is not None
+        return real(*args, **kwargs)
+
+    monkeypatch.setattr(ops, "gemv_bf16", counting)
+    g = torch.Generator().manual_seed(3)
+    seqs = {"a": torch.randint(0, V, (30,), generator=g).tolist(), "b": torch.randint(0, V, (11,), generator=g).tolist()}
+    want = {k: plain(v) for k, v in seqs.items()}
+    sa, sb = engine.acquire_slot(), engine.acquire_slot()
+    got = engine.step([SequenceStep(sa, seqs["a"][:25], [0, 24]), SequenceStep(sb, seqs["b"][:6], [5])])
+    check_logits(got.cpu().numpy(), torch.stack([want["a"][0], want["a"][24], want["b"][5]]), dtype, "toy norm prompt")
+    assert seen == {"emit": 0, "shares": 0}
+    for t in range(5):
+        got = engine.step([SequenceStep(sa, [seqs["a"][25 + t]], [0]), SequenceStep(sb, [seqs["b"][6 + t]], [0])])
+        check_logits(got.cpu().numpy(), torch.stack([want["a"][25 + t], want["b"][6 + t]]), dtype,
+                     f"toy norm token {t}")
+    assert seen == ({"emit": 10, "shares": 10} if bf else {"emit": 0, "shares": 0})
+    engine.release_slot(sa)
+    engine.release_slot(sb)
