@@ -50,7 +50,7 @@ constexpr int kClWarps = 4;
 constexpr int kClThreads = kClWarps * 32;
 constexpr int kClPage = 64;
 constexpr int kMaxPages = 8;       // pages of one slice, all in shared memory at once
-constexpr int kMaxSlices = 64;
+constexpr int kMaxSlices = 128;
 
 // element offset of 16-byte chunk `chunk` of row `row` in a tile of 64 rows that TMA
 // wrote as D / 64 boxes of 64 x 64 elements, each with the 128-byte swizzle

@@ -519,7 +519,7 @@ def attention_decode_tma_plan(n: int, heads: int, kv_heads: int, head_dim: int, 
     sms = sm_count(device) // max(1, share)
 
     def plan(pages: int):
-        splits = min(64, -(-table_cols // pages))
+        splits = min(128, -(-table_cols // pages))
         per = -(-table_cols // splits)
         if per > attention_decode_tma_max_pages(head_dim):
             return 0, 0, 0
@@ -568,8 +568,8 @@ def attention_decode_tma(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, 
     _need(pages * nkv * page_size < 2 ** 31, "attention: the cache has too many rows")
     _need(out.shape[1] == heads * head_dim and n <= 65535, "attention: out [n <= 65535, heads * d]")
     most = attention_decode_tma_max_pages(head_dim)
-    _need(1 <= n_splits <= 64 and -(-page_table.shape[1] // n_splits) <= most,
-          f"attention_decode_tma: at most 64 slices of at most {most} pages")
+    _need(1 <= n_splits <= 128 and -(-page_table.shape[1] // n_splits) <= most,
+          f"attention_decode_tma: at most 128 slices of at most {most} pages")
     if n_splits > 1:
         _need(partial is not None and partial.dtype == torch.float32
               and partial.numel() >= n * heads * n_splits * (head_dim + 2),

@@ -856,7 +856,7 @@ def test_attention_decode_fed_by_tma_long_contexts_in_many_slices():
     cols = case.table.shape[1]
     assert cols == 128
     tickets = torch.zeros(o.mma_ticket_count(n, nq, nkv), dtype=torch.int32, device=DEV)
-    for splits in (16, 22, 32, 43, 64):
+    for splits in (16, 22, 32, 43, 64, 86, 128):
         out = torch.full((n, nq * d), 5.0, dtype=torch.bfloat16, device=DEV)
         partial = torch.full((n * nq * splits * (d + 2),), float("nan"), device=DEV)
         for _ in range(2):  # (the tickets come back to zero: a second launch finds them so)
@@ -872,6 +872,9 @@ def test_attention_decode_fed_by_tma_long_contexts_in_many_slices():
     assert o.attention_decode_tma_plan(1, nq, nkv, d, 64, 256, DEV) == 32
     assert o.attention_decode_tma_plan(2, nq, nkv, d, 64, 256, DEV) == 43
     assert o.attention_decode_tma_plan(3, nq, nkv, d, 64, 256, DEV) == 0    # the ring kernel's
+    assert o.attention_decode_tma_plan(1, nq, nkv, d, 64, 384, DEV) == 48   # 24,576 keys: eight pages
+    assert o.attention_decode_tma_plan(1, nq, nkv, d, 64, 512, DEV) == 86   # 32,768 keys: six pages
+    assert o.attention_decode_tma_plan(2, nq, nkv, d, 64, 512, DEV) == 0
     assert o.attention_decode_tma_plan(8, nq, nkv, d, 64, 64, DEV) == 11    # (as before at 4,096)
 
 
