@@ -70,18 +70,25 @@ rmsnorm_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows,
                     const float* __restrict__ w, T* __restrict__ y, int n_rows, int width, float eps,
                     unsigned long long* trace) {
     trace_mark(trace, 0);
+    const int lane = threadIdx.x & 31, r = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+    const int n4 = width >> 2;
+    // the norm's weights depend on no kernel: they are fetched before the wait
+    float4 g[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        int c = lane + 32 * j;
+        g[j] = c < n4 ? w4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     pdl_wait();
     pdl_launch_dependents();
     trace_mark(trace, 2);
     trace_mark(trace, 3);
-    const int lane = threadIdx.x & 31, r = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (r >= n_rows) {
         trace_mark(trace, 1);
         return;
     }
     const float4* in = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * width);
-    const float4* w4 = reinterpret_cast<const float4*>(w);
-    const int n4 = width >> 2;
     float4 v[8];
     float ss = 0.f;
 #pragma unroll
@@ -99,11 +106,9 @@ rmsnorm_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows,
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
         int c = lane + 32 * j;
-        if (c < n4) {
-            float4 g = w4[c];
-            store4(out + c * 4, make_float4((v[j].x * s) * g.x, (v[j].y * s) * g.y, (v[j].z * s) * g.z,
-                                            (v[j].w * s) * g.w));
-        }
+        if (c < n4)
+            store4(out + c * 4, make_float4((v[j].x * s) * g[j].x, (v[j].y * s) * g[j].y, (v[j].z * s) * g[j].z,
+                                            (v[j].w * s) * g[j].w));
     }
     trace_mark(trace, 1);
 }
