@@ -500,13 +500,45 @@ def attention_decode_tma_max_pages(head_dim: int) -> int:
     return int(_lib().nnis_attention_decode_tma_max_pages(int(head_dim)))
 
 
+def tma_slices(groups: int, table_cols: int, sms: int, most_pages: int, fit, fixed_pages: int = 0) -> int:
+    """The rule behind ``attention_decode_tma_plan``, free of the device: ``groups`` CTAs per
+    slice (sequences x kv heads x tiles of query heads), ``table_cols`` pages to cut, ``sms``
+    SMs, at most ``most_pages`` pages a slice, and ``fit(pages)`` the CTAs of that many pages
+    that one SM holds at once.  Returns the number of slices, 0: not for this kernel."""
+    def plan(pages: int):
+        splits = min(128, -(-table_cols // pages))
+        per = -(-table_cols // splits)
+        if per > most_pages:
+            return 0, 0, 0
+        return splits, groups * splits, fit(per)
+
+    if fixed_pages:
+        splits, ctas, room = plan(fixed_pages)
+        return splits if 0 < ctas <= room * sms else 0
+    splits, ctas, room = plan(4)
+    if splits > 16:
+        # The slice that arrives last asks for 16 partial records a trip to L2: beyond 16 slices
+        # (contexts beyond 4,096) the longest slices whose CTAs are still all resident, eight pages
+        # one to an SM or six pages two to an SM (one sequence at context 16,384: 0.592 -> 0.512 ms
+        # a step, two at 8,192: 0.540 -> 0.493)
+        for pages in (8, 6):
+            long_splits, long_ctas, long_room = plan(pages)
+            if 0 < long_ctas <= min(long_room, 2) * sms:
+                return long_splits
+    if ctas > 2 * sms:
+        wide, wide_ctas, wide_room = plan(6)
+        if 0 < wide_ctas <= min(wide_room, 2) * sms:
+            return wide
+    return splits if 0 < ctas <= room * sms else 0
+
+
 def attention_decode_tma_plan(n: int, heads: int, kv_heads: int, head_dim: int, page_size: int,
                               table_cols: int, device, share: int = 1) -> int:
     """Into how many slices attention_decode_tma cuts ``table_cols`` pages for a step of ``n``
     sequences, or 0 when the step is not for that kernel: it takes head sizes 64 and 128 and
     only steps whose CTAs are all resident together (few sequences, or short contexts);
     other steps stream their slices through the ring of attention_decode_mma.  Slices are of
-    four pages (more for page tables beyond 64 x 4 columns, up to what fits; with more than 16
+    four pages (more for page tables beyond 128 x 4 columns, up to what fits; with more than 16
     slices of four pages, of eight or six pages where those CTAs are resident); when four pages make
     more CTAs than two per SM, of six pages if those CTAs are resident two to an SM: fewer
     partial records and fewer CTAs that wait for room beside the projection's (batch 8 of the
@@ -518,34 +550,13 @@ def attention_decode_tma_plan(n: int, heads: int, kv_heads: int, head_dim: int, 
     groups = n * kv_heads * (-(-(heads // kv_heads) // 16))
     sms = sm_count(device) // max(1, share)
 
-    def plan(pages: int):
-        splits = min(128, -(-table_cols // pages))
-        per = -(-table_cols // splits)
-        if per > attention_decode_tma_max_pages(head_dim):
-            return 0, 0, 0
-        key = (head_dim, per, torch.device(device).index or 0)
+    def fit(pages: int) -> int:
+        key = (head_dim, pages, torch.device(device).index or 0)
         if key not in _tma_ctas_per_sm:
-            _tma_ctas_per_sm[key] = int(_lib().nnis_attention_decode_tma_ctas_per_sm(head_dim, per))
-        return splits, groups * splits, _tma_ctas_per_sm[key]
+            _tma_ctas_per_sm[key] = int(_lib().nnis_attention_decode_tma_ctas_per_sm(head_dim, pages))
+        return _tma_ctas_per_sm[key]
 
-    if TMA_SLICE_PAGES:
-        splits, ctas, fit = plan(TMA_SLICE_PAGES)
-        return splits if 0 < ctas <= fit * sms else 0
-    splits, ctas, fit = plan(4)
-    if splits > 16:
-        # The slice that arrives last asks for 16 partial records a trip to L2: beyond 16 slices
-        # (contexts beyond 4,096) the longest slices whose CTAs are still all resident, eight pages
-        # one to an SM or six pages two to an SM (one sequence at context 16,384: 0.592 -> 0.512 ms
-        # a step, two at 8,192: 0.540 -> 0.493)
-        for pages in (8, 6):
-            long_splits, long_ctas, long_fit = plan(pages)
-            if 0 < long_ctas <= min(long_fit, 2) * sms:
-                return long_splits
-    if ctas > 2 * sms:
-        wide, wide_ctas, wide_fit = plan(6)
-        if 0 < wide_ctas <= min(wide_fit, 2) * sms:
-            return wide
-    return splits if 0 < ctas <= fit * sms else 0
+    return tma_slices(groups, table_cols, sms, attention_decode_tma_max_pages(head_dim), fit, TMA_SLICE_PAGES)
 
 
 def attention_decode_tma(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor,

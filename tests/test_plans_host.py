@@ -164,3 +164,38 @@ def test_a_begun_norm_is_handed_on_once_and_only_to_the_block_that_owns_it():
     block.mixer = EmittingMixer()
     block.forward(hidden, ctx, None)
     assert calls == [("ffn shared", block.ffn_norm)] and ctx.shared_norm is None
+
+
+def test_decode_attention_by_tma_takes_the_longest_slices_that_stay_resident():
+    """The slices of the decode attention whose pages are all in shared memory at once, on a
+    device of 148 SMs that holds three CTAs of four pages, two of five or six, one of seven or
+    eight to an SM (head size 64): four pages; six where four make more CTAs than two to an
+    SM; beyond 16 slices, eight or six where those CTAs are all resident; else not this kernel."""
+    from nnis_b200.csrc.ops import tma_slices
+    fit = lambda pages: 3 if pages <= 4 else 2 if pages <= 6 else 1
+
+    def slices(sequences, pages, kv_heads=3, fixed=0):
+        return tma_slices(sequences * kv_heads, pages, 148, 8, fit, fixed)
+
+    # context 4,096 (64 pages): one to six sequences 16 slices of four pages, seven and eight
+    # 11 slices of six (two CTAs to an SM), nine 16 of four again (297 CTAs of six pages are one too
+    # many for two to an SM; 432 of four fit three to an SM), ten and more none
+    assert [slices(n, 64) for n in (1, 2, 6, 7, 8, 9)] == [16, 16, 16, 11, 11, 16]
+    assert slices(10, 64) == 0 and slices(64, 64) == 0
+    # short contexts: one slice, many sequences
+    assert slices(1, 1) == 1 and slices(40, 4) == 1 and slices(200, 4) == 0
+    # beyond 16 slices of four pages: eight pages one to an SM, six pages two to an SM
+    assert slices(1, 128) == 16 and slices(3, 128) == 16 and slices(4, 128) == 22
+    assert slices(1, 256) == 32 and slices(2, 256) == 43 and slices(3, 256) == 0
+    assert slices(1, 384) == 48 and slices(1, 512) == 86 and slices(2, 512) == 0
+    # never more than 128 slices, never more than eight pages a slice
+    assert slices(1, 1024) == 0 and slices(1, 1000, kv_heads=1) == 125 and slices(1, 1025, kv_heads=1) == 0
+    # a fixed slice length is taken if its CTAs are resident
+    assert slices(8, 64, fixed=4) == 16 and slices(8, 64, fixed=8) == 0 and slices(2, 64, fixed=8) == 8
+    for n in (1, 2, 3, 5, 8, 13, 40):
+        for pages in (1, 3, 16, 17, 63, 64, 65, 100, 128, 129, 255, 256, 400, 512, 700):
+            s = slices(n, pages)
+            if s:
+                per = -(-pages // s)
+                assert 1 <= s <= 128 and per <= 8 and s * per >= pages
+                assert n * 3 * s <= 148 * fit(per)
