@@ -24,13 +24,12 @@ overlap with the second form's stops.
 from __future__ import annotations
 
 import os
-from typing import Dict, List, Optional, Sequence
+from typing import Optional, Sequence
 
 import torch
 
 from ..cache import PAGE_SIZE
 from ..csrc import ops
-from ..sampling import device as device_sampling
 from .context import StepContext, sm_count
 from .workspace import Workspace
 

@@ -9,7 +9,6 @@ from typing import Dict, List, Mapping, Optional
 
 import torch
 
-from ..cache import KVRequest, KVView, StateRequest
 from ..csrc import ops
 from ..config.spec import ModelSpec
 from ..parts import BLOCKS, EMBEDDINGS, HEADS, NORMS

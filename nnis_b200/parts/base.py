@@ -31,7 +31,7 @@ float32 in every dtype, and a fused epilogue may add in place.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Callable, Dict, Mapping, Optional
+from typing import Any, Callable, Dict, Mapping
 
 import torch
 

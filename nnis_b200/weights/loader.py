@@ -20,7 +20,7 @@ import json
 import os
 import re
 from dataclasses import dataclass
-from typing import Dict, Iterable, List, Mapping, Tuple
+from typing import Dict, List, Mapping, Tuple
 
 import torch
 

@@ -16,7 +16,7 @@ from __future__ import annotations
 import hashlib
 import json
 import os
-from typing import Dict, Mapping, Optional
+from typing import Dict, Mapping
 
 import torch
 

@@ -5,12 +5,11 @@ import os
 import pytest
 import torch
 
-from helpers import CONFIGS, TINY_A, TINY_B, make_model
+from helpers import TINY_A, TINY_B, make_model
 from nnis_b200.config import (ConfigError, LlamaConfig, config_from_dict, known_architectures,
                               read_config)
 from nnis_b200.engine.model import DecoderModel
-from nnis_b200.weights import (SafetensorsFile, WeightError, WeightSpec, load_weights,
-                               write_safetensors)
+from nnis_b200.weights import SafetensorsFile, WeightError, load_weights, write_safetensors
 
 
 def test_llama_config_reads_every_key():
