@@ -199,3 +199,62 @@ def test_decode_attention_by_tma_takes_the_longest_slices_that_stay_resident():
                 per = -(-pages // s)
                 assert 1 <= s <= 128 and per <= 8 and s * per >= pages
                 assert n * 3 * s <= 148 * fit(per)
+
+
+def _ops_with_the_library():
+    """The kernels' library holds the rules of which kernel takes which product as plain host
+    functions; they need no GPU, only the library (built with nvcc at first use)."""
+    import pytest
+    from nnis_b200.csrc import ops
+    try:
+        ops._lib()
+    except Exception as e:  # no compiler here
+        pytest.skip(f"the kernels' library is not built here: {e}")
+    return ops
+
+
+def test_which_kernel_takes_the_projections_of_a_decode_step():
+    """On 148 SMs, for the SmolLM2 shapes: 2 the kernel over tiles of rows, 1 the kernel whose
+    CTAs hold all rows, 0 neither (norm kernel and tensor-core product); and where the norm
+    before QKV and before gate/up can be shared out between the projections around it."""
+    o = _ops_with_the_library()
+
+    def plans(H, inter, nq, nkv, d, m):
+        qkv = (nq + 2 * nkv) * d
+        return dict(qkv=o.gemv_kind(m, qkv, H, o.EPI_QKV, None, True),
+                    qkv_shares=o.gemv_kind(m, qkv, H, o.EPI_QKV, shared_norm=True) == 2,
+                    out=o.gemv_kind(m, H, nq * d, o.EPI_ADD_F32),
+                    gate_up=o.gemv_kind(m, 2 * inter, H, o.EPI_GATED, None, True),
+                    gate_up_shares=o.gemv_kind(m, 2 * inter, H, o.EPI_GATED, shared_norm=True) == 2,
+                    down=o.gemv_kind(m, H, inter, o.EPI_ADD_F32), down_slices=o.gemv_slices(m, H, inter))
+
+    small, middle, large = (576, 1536, 9, 3, 64), (960, 2560, 15, 5, 64), (2048, 8192, 32, 32, 64)
+    # the benchmark's shape: everything over tiles of rows up to 64 rows, both norms shared
+    for m in (1, 8, 16, 48, 64):
+        assert plans(*small, m) == dict(qkv=2, qkv_shares=True, out=2, gate_up=2, gate_up_shares=True,
+                                        down=2, down_slices=1), m
+    # at 128 rows gate/up has more CTAs than are resident at once
+    p = plans(*small, 128)
+    assert (p["qkv"], p["out"], p["down"], p["gate_up"], p["gate_up_shares"]) == (2, 2, 2, 0, False)
+    # the 360M shape: the same up to 16 rows, its down projection in two slices of K;
+    # from 48 rows on gate/up (640 units) leaves the kernel over tiles of rows and shares no norm
+    for m in (1, 8, 16):
+        assert plans(*middle, m) == dict(qkv=2, qkv_shares=True, out=2, gate_up=2, gate_up_shares=True,
+                                         down=2, down_slices=2), m
+    for m in (48, 64):
+        p = plans(*middle, m)
+        assert (p["qkv"], p["qkv_shares"], p["gate_up"], p["gate_up_shares"]) == (2, True, 1, False), m
+    # the 1.7B shape: rows of 2,048 are longer than a warp's share of x in registers, so the
+    # norm stays in the prologue of the kernel whose CTAs hold all rows, and nothing is shared;
+    # the down projection (K = 8,192) runs in four slices of K
+    for m in (1, 8, 16):
+        p = plans(*large, m)
+        assert (p["qkv"], p["qkv_shares"], p["gate_up"], p["gate_up_shares"]) == (1, False, 1, False), m
+        assert (p["out"], p["down"], p["down_slices"]) == (2, 1, 4), m
+    # what no decode kernel takes: more than 128 rows, K off a multiple of 16, N off a multiple of 8
+    assert o.gemv_kind(129, 576, 576, o.EPI_ADD_F32) == 0 and o.gemv_kind(8, 576, 568, o.EPI_ADD_F32) == 0
+    assert o.gemv_kind(8, 572, 576, o.EPI_ADD_F32) == 0
+    # a shared norm ends only in the QKV and the gated epilogue
+    assert o.gemv_kind(8, 576, 576, o.EPI_STORE, shared_norm=True) == 0
+    # the adding tensor-core product cuts a long K among CTAs only where tiles are few
+    assert o.gemm_tc_splits(64, 2048, 8192)[0] == 4 and o.gemm_tc_splits(2048, 576, 1536)[0] == 1
